@@ -1,0 +1,153 @@
+/*
+ * deltarule_sm100 -- C ABI of the B200 (sm_100a) delta-rule linear-attention kernels.
+ *
+ * Every entry point replaces one or more pure-JAX functions of LinearNexus
+ * (paths below are relative to the LinearNexus source tree).  The caller owns every
+ * buffer; all pointers are DEVICE pointers unless a name ends in `_host`; kernels are
+ * enqueued on `stream` (a cudaStream_t passed as void*) and the call returns without
+ * synchronising.  The library allocates no device memory in any entry point of this
+ * header; scratch comes from the caller (`workspace`, sized by dr_workspace_bytes).
+ *
+ * Tensors are contiguous in one of two layouts selected by DrDesc.layout:
+ *   DR_LAYOUT_BHTD : q,k [B,H,T,K]  v,o [B,H,T,V]  beta [B,H,T]  g [B,H,T] or [B,H,T,K]
+ *   DR_LAYOUT_BTHD : q,k [B,T,H,K]  v,o [B,T,H,V]  beta [B,T,H]  g [B,T,H] or [B,T,H,K]
+ * The recurrent state is always [B,H,K,V] float32 with S[k][v], o = S^T q.
+ *
+ * Return value: DR_OK (0) or a negative DrStatus; dr_strerror() names it.
+ */
+#ifndef DELTARULE_SM100_H_
+#define DELTARULE_SM100_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum DrVariant {
+  DR_DELTA = 0, /* DeltaNet: no decay, no in-op l2norm   (modules/linear_attn/delta_net.py) */
+  DR_GATED = 1, /* Gated DeltaNet: scalar log-decay g    (modules/linear_attn/gated_deltanet.py) */
+  DR_KDA = 2    /* KDA: per-channel log-decay g[...,K]   (modules/linear_attn/kda.py) */
+} DrVariant;
+
+typedef enum DrDtype { DR_F32 = 0, DR_BF16 = 1 } DrDtype;
+
+typedef enum DrLayout { DR_LAYOUT_BHTD = 0, DR_LAYOUT_BTHD = 1 } DrLayout;
+
+typedef enum DrStatus {
+  DR_OK = 0,
+  DR_ERR_NULL = -1,        /* a required pointer is null */
+  DR_ERR_SHAPE = -2,       /* B,H,T,K,V or chunk out of the supported range */
+  DR_ERR_DTYPE = -3,       /* unknown dtype tag or unsupported combination */
+  DR_ERR_ALIGN = -4,       /* a pointer is not 16-byte aligned */
+  DR_ERR_WORKSPACE = -5,   /* workspace too small (see dr_workspace_bytes) */
+  DR_ERR_VARIANT = -6,     /* unknown variant, or g missing/present against the variant */
+  DR_ERR_CHUNK = -7,       /* chunk size not accepted (Gated/KDA: must be a multiple of 16) */
+  DR_ERR_CUDA = -8,        /* a CUDA runtime call failed; see dr_last_cuda_error() */
+  DR_ERR_UNSUPPORTED = -9, /* valid request that no kernel of this build covers */
+  DR_ERR_DEVICE = -10      /* a kernel reported a problem through the status word */
+} DrStatus;
+
+/* Which kernel family serves a chunk-forward call. */
+typedef enum DrChunkPath {
+  DR_PATH_AUTO = 0,   /* tensor-core kernel when the shape qualifies, else the fp32 kernel */
+  DR_PATH_FP32 = 1,   /* CUDA-core fp32 chunk kernel (any K,V multiple of 16 up to 256) */
+  DR_PATH_TCGEN05 = 2 /* tcgen05/TMEM bf16-operand kernel (K=V=128, chunk 64, bf16 q,k,v) */
+} DrChunkPath;
+
+/* Values the device status word can take (written by kernels, never trapped). */
+#define DR_DEV_OK 0
+#define DR_DEV_TIMEOUT 1 /* a bounded wait on an mbarrier ran out */
+#define DR_DEV_BOUNDS 2  /* an index check failed (debug builds) */
+
+typedef struct DrDesc {
+  int32_t variant;       /* DrVariant */
+  int32_t layout;        /* DrLayout */
+  int32_t B, H, T, K, V; /* T is the number of tokens (1 for dr_step) */
+  int32_t chunk;         /* chunk size C for the chunk entry points, ignored elsewhere */
+  int32_t qkv_dtype;     /* DrDtype of q, k, v (and of do / dq, dk, dv in the backward) */
+  int32_t g_dtype;       /* DrDtype of g (ignored for DR_DELTA) */
+  int32_t out_dtype;     /* DrDtype of o */
+  int32_t use_qk_l2norm; /* 1: normalise q,k rows as x/(||x||+1e-6) inside the kernel */
+  float scale;           /* multiplies q after normalisation */
+  int32_t path;          /* DrChunkPath, chunk entry points only */
+  int32_t reserved[2];   /* must be zero */
+} DrDesc;
+
+/* Library / build identification, e.g. "deltarule_sm100 0.1 (sm_100a)". */
+const char* dr_version(void);
+
+/* Text for a DrStatus. */
+const char* dr_strerror(int status);
+
+/* cudaError_t (as int) of the most recent failing CUDA call made by this library on the
+ * calling thread, 0 if none. */
+int dr_last_cuda_error(void);
+
+/* Number of kernel launches this library has issued since load (all threads); the
+ * benchmark reports the difference across its timed region. */
+uint64_t dr_launch_count(void);
+
+/* Name of the kernel family the most recent call on this thread dispatched to
+ * ("step", "recurrent", "chunk_fp32", "chunk_tcgen05", "bwd", ...). */
+const char* dr_last_path(void);
+
+/* Bytes of caller-provided scratch that dr_chunk_fwd (op=0) or dr_chunk_bwd (op=1)
+ * needs for `desc`; 0 when none is needed.  Negative DrStatus (cast) on a bad desc. */
+int64_t dr_workspace_bytes(const DrDesc* desc, int op);
+
+/*
+ * Chunkwise forward.  Replaces
+ *   delta_rule_chunkwise        modules/linear_attn/delta_net.py:216-354
+ *   gated_delta_rule_chunkwise  modules/linear_attn/gated_deltanet.py:232-534
+ *   kda_chunkwise               modules/linear_attn/kda.py:350-655
+ * g: null for DR_DELTA.  beta: float32.  h0: float32 [B,H,K,V] or null (zero state).
+ * o: desc->out_dtype.  hT: float32 [B,H,K,V] or null (final state not wanted).
+ * status_dev: one int32 in device memory, or null; kernels OR problems into it.
+ * A ragged tail (T % chunk != 0) behaves as the reference's zero padding does.
+ */
+int dr_chunk_fwd(const DrDesc* desc, const void* q, const void* k, const void* v, const void* g,
+                 const float* beta, const float* h0, void* o, float* hT, void* workspace,
+                 size_t workspace_bytes, int32_t* status_dev, void* stream);
+
+/*
+ * Token-by-token forward.  Replaces
+ *   delta_rule_recurrent         modules/linear_attn/delta_net.py:126-213
+ *   delta_rule_recurrent_pallas  kernels/pallas/delta_rule.py:47-281
+ *   gated_delta_rule_recurrent   modules/linear_attn/gated_deltanet.py:136-229
+ *   kda_recurrent                modules/linear_attn/kda.py:179-283
+ * Same argument meaning as dr_chunk_fwd; needs no workspace.
+ */
+int dr_recurrent_fwd(const DrDesc* desc, const void* q, const void* k, const void* v,
+                     const void* g, const float* beta, const float* h0, void* o, float* hT,
+                     void* stream);
+
+/*
+ * Single-token decode step (desc->T must be 1).  Replaces
+ *   delta_rule_step        modules/linear_attn/delta_net.py:357-397
+ *   gated_delta_rule_step  modules/linear_attn/gated_deltanet.py:539-597
+ *   kda_step               modules/linear_attn/kda.py:286-347
+ * q,k [B,H,K]  v [B,H,V]  g [B,H] or [B,H,K]  beta [B,H] float32.
+ * state_in/state_out: float32 [B,H,K,V]; they may be the same pointer (in-place update of
+ * the decode cache, the case the kernel is tuned for).  o [B,H,V] in desc->out_dtype.
+ */
+int dr_step(const DrDesc* desc, const void* q, const void* k, const void* v, const void* g,
+            const float* beta, const float* state_in, float* state_out, void* o, void* stream);
+
+/*
+ * Backward of the chunkwise/recurrent forward (the reference has no backward function:
+ * its gradients are jax.grad through the three *_chunkwise functions cited above).
+ * Inputs: the forward inputs, d_o [like o, desc->qkv_dtype] and d_hT (float32 [B,H,K,V] or
+ * null).  Outputs: dq,dk [like q], dv [like v] in desc->qkv_dtype; dbeta float32 [like beta];
+ * dg float32 [like g] (null for DR_DELTA); dh0 float32 [B,H,K,V] or null.
+ */
+int dr_chunk_bwd(const DrDesc* desc, const void* q, const void* k, const void* v, const void* g,
+                 const float* beta, const float* h0, const void* d_o, const float* d_hT, void* dq,
+                 void* dk, void* dv, float* dbeta, float* dg, float* dh0, void* workspace,
+                 size_t workspace_bytes, int32_t* status_dev, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DELTARULE_SM100_H_ */

@@ -1,0 +1,20 @@
+"""B200 (sm_100a) delta-rule linear-attention kernels behind the LinearNexus op signatures.
+
+``from linearnexus_b200 import gated_delta_rule_chunkwise`` is the drop-in for
+``linearnexus.modules.linear_attn.gated_delta_rule_chunkwise`` (torch CUDA tensors instead of
+jax arrays).  The compute lives in ``libdeltarule_sm100.so`` (C ABI: include/deltarule_sm100.h).
+"""
+
+from .backend import KernelBackend, backend_availability, select_kernel_backend
+from .ops import (delta_rule_chunkwise, delta_rule_recurrent, delta_rule_recurrent_pallas,
+                  delta_rule_step, gated_delta_rule_chunkwise, gated_delta_rule_recurrent,
+                  gated_delta_rule_step, kda_chunkwise, kda_recurrent, kda_step)
+from .state import DeltaNetState, GatedDeltaNetState, KDAState
+
+__all__ = [
+    "delta_rule_recurrent", "delta_rule_chunkwise", "delta_rule_step", "delta_rule_recurrent_pallas",
+    "gated_delta_rule_recurrent", "gated_delta_rule_chunkwise", "gated_delta_rule_step",
+    "kda_recurrent", "kda_chunkwise", "kda_step",
+    "DeltaNetState", "GatedDeltaNetState", "KDAState",
+    "KernelBackend", "backend_availability", "select_kernel_backend",
+]

@@ -1,0 +1,136 @@
+"""Loader and ctypes bindings for ``libdeltarule_sm100.so`` (the C ABI in include/deltarule_sm100.h).
+
+The library is built in-tree by :func:`build_library` (``nvcc`` for sm_100a) and loaded from
+the package directory.  There is no fallback: if the shared object is missing or a call
+fails, an exception is raised.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+import threading
+from pathlib import Path
+
+_PKG = Path(__file__).resolve().parent
+_ROOT = _PKG.parent
+LIB_PATH = _PKG / "libdeltarule_sm100.so"
+_SOURCES = ["dr_api.cu"]
+_HEADERS = ["dr_common.cuh", "dr_step.cuh", "dr_recurrent.cuh", "dr_chunk_fp32.cuh",
+            "dr_chunk_sm100.cuh", "dr_bwd.cuh"]
+
+# DrVariant / DrDtype / DrLayout / DrChunkPath (include/deltarule_sm100.h)
+DR_DELTA, DR_GATED, DR_KDA = 0, 1, 2
+DR_F32, DR_BF16 = 0, 1
+DR_LAYOUT_BHTD, DR_LAYOUT_BTHD = 0, 1
+DR_PATH_AUTO, DR_PATH_FP32, DR_PATH_TCGEN05 = 0, 1, 2
+
+EXPORTS = ["dr_version", "dr_strerror", "dr_last_cuda_error", "dr_launch_count", "dr_last_path",
+           "dr_workspace_bytes", "dr_chunk_fwd", "dr_recurrent_fwd", "dr_step", "dr_chunk_bwd"]
+
+
+class DrDesc(ctypes.Structure):
+    _fields_ = [
+        ("variant", ctypes.c_int32), ("layout", ctypes.c_int32),
+        ("B", ctypes.c_int32), ("H", ctypes.c_int32), ("T", ctypes.c_int32),
+        ("K", ctypes.c_int32), ("V", ctypes.c_int32), ("chunk", ctypes.c_int32),
+        ("qkv_dtype", ctypes.c_int32), ("g_dtype", ctypes.c_int32), ("out_dtype", ctypes.c_int32),
+        ("use_qk_l2norm", ctypes.c_int32), ("scale", ctypes.c_float), ("path", ctypes.c_int32),
+        ("reserved", ctypes.c_int32 * 2),
+    ]
+
+
+class DeltaRuleError(RuntimeError):
+    """A C-ABI call returned a negative DrStatus."""
+
+    def __init__(self, status: int, text: str, where: str):
+        super().__init__(f"{where}: {text} (DrStatus {status})")
+        self.status = status
+
+
+def nvcc_command(out: Path | None = None, extra: list[str] | None = None) -> list[str]:
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+           "-shared", "-Xcompiler", "-fPIC", f"-I{_ROOT / 'include'}", f"-I{_PKG / 'csrc'}"]
+    cmd += extra or []
+    cmd += ["-o", str(out or LIB_PATH)] + [str(_PKG / "csrc" / s) for s in _SOURCES]
+    return cmd
+
+
+def library_is_stale() -> bool:
+    if not LIB_PATH.exists():
+        return True
+    t = LIB_PATH.stat().st_mtime
+    deps = [_PKG / "csrc" / f for f in _SOURCES + _HEADERS] + [_ROOT / "include" / "deltarule_sm100.h"]
+    return any(d.exists() and d.stat().st_mtime > t for d in deps)
+
+
+def build_library(force: bool = False, verbose: bool = False) -> Path:
+    """Compile the CUDA sources for sm_100a into the package directory (cross-compiles without a GPU)."""
+    if force or library_is_stale():
+        cmd = nvcc_command()
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if verbose or res.returncode:
+            print(" ".join(cmd))
+            print(res.stdout, res.stderr)
+        if res.returncode:
+            raise RuntimeError("nvcc failed building libdeltarule_sm100.so:\n" + res.stderr)
+    return LIB_PATH
+
+
+_lib = None
+_lock = threading.Lock()
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library (once) and declare the argument types of every export."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not LIB_PATH.exists():
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'` "
+                "(there is no CPU or PyTorch fallback for these ops)")
+        lib = ctypes.CDLL(str(LIB_PATH))
+        vp, fp, ip = ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p
+        dp = ctypes.POINTER(DrDesc)
+        lib.dr_version.restype = ctypes.c_char_p
+        lib.dr_strerror.restype = ctypes.c_char_p
+        lib.dr_strerror.argtypes = [ctypes.c_int]
+        lib.dr_last_cuda_error.restype = ctypes.c_int
+        lib.dr_launch_count.restype = ctypes.c_uint64
+        lib.dr_last_path.restype = ctypes.c_char_p
+        lib.dr_workspace_bytes.restype = ctypes.c_int64
+        lib.dr_workspace_bytes.argtypes = [dp, ctypes.c_int]
+        lib.dr_chunk_fwd.restype = ctypes.c_int
+        lib.dr_chunk_fwd.argtypes = [dp, vp, vp, vp, vp, fp, fp, vp, fp, vp, ctypes.c_size_t, ip, vp]
+        lib.dr_recurrent_fwd.restype = ctypes.c_int
+        lib.dr_recurrent_fwd.argtypes = [dp, vp, vp, vp, vp, fp, fp, vp, fp, vp]
+        lib.dr_step.restype = ctypes.c_int
+        lib.dr_step.argtypes = [dp, vp, vp, vp, vp, fp, fp, fp, vp, vp]
+        lib.dr_chunk_bwd.restype = ctypes.c_int
+        lib.dr_chunk_bwd.argtypes = [dp, vp, vp, vp, vp, fp, fp, vp, fp, vp, vp, vp, fp, fp, fp, vp,
+                                     ctypes.c_size_t, ip, vp]
+        _lib = lib
+    return _lib
+
+
+def check(status: int, where: str) -> None:
+    if status < 0:
+        lib = load()
+        text = lib.dr_strerror(status).decode()
+        if status == -8:
+            text += f" (cudaError {lib.dr_last_cuda_error()})"
+        raise DeltaRuleError(status, text, where)
+
+
+def launch_count() -> int:
+    return int(load().dr_launch_count())
+
+
+def last_path() -> str:
+    return load().dr_last_path().decode()

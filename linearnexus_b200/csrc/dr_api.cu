@@ -1,0 +1,203 @@
+// C ABI of the delta-rule kernels: argument validation and dispatch.  No device memory is
+// allocated here; every launch goes to the caller's stream.
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+
+#include "deltarule_sm100.h"
+#include "dr_chunk_fp32.cuh"
+#include "dr_chunk_sm100.cuh"
+#include "dr_bwd.cuh"
+#include "dr_common.cuh"
+#include "dr_recurrent.cuh"
+#include "dr_step.cuh"
+
+namespace {
+
+std::atomic<uint64_t> g_launches{0};
+thread_local int tl_cuda_error = 0;
+thread_local const char* tl_path = "none";
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline bool dtype_ok(int d) { return d == DR_F32 || d == DR_BF16; }
+
+int check_cuda(cudaError_t e) {
+  if (e == cudaSuccess) return DR_OK;
+  tl_cuda_error = (int)e;
+  return DR_ERR_CUDA;
+}
+
+// Checks shared by every entry point.
+int validate_common(const DrDesc* d, bool need_chunk) {
+  if (!d) return DR_ERR_NULL;
+  if (d->variant < DR_DELTA || d->variant > DR_KDA) return DR_ERR_VARIANT;
+  if (d->layout != DR_LAYOUT_BHTD && d->layout != DR_LAYOUT_BTHD) return DR_ERR_SHAPE;
+  if (d->B < 1 || d->H < 1 || d->T < 1) return DR_ERR_SHAPE;
+  if ((int64_t)d->B * d->H > (int64_t)1 << 24) return DR_ERR_SHAPE;
+  if (d->K < 4 || d->K > 256 || d->K % 4) return DR_ERR_SHAPE;
+  if (d->V < 4 || d->V > 256 || d->V % 4) return DR_ERR_SHAPE;
+  if (!dtype_ok(d->qkv_dtype) || !dtype_ok(d->out_dtype)) return DR_ERR_DTYPE;
+  if (d->variant != DR_DELTA && !dtype_ok(d->g_dtype)) return DR_ERR_DTYPE;
+  if (d->reserved[0] || d->reserved[1]) return DR_ERR_SHAPE;
+  if (need_chunk) {
+    if (d->chunk < 1) return DR_ERR_CHUNK;
+    // The reference raises ValueError when chunk_size % 16 != 0 for Gated DeltaNet and KDA
+    // (gated_deltanet.py:318-321, kda.py:438-441); DeltaNet has no such rule.
+    if (d->variant != DR_DELTA && d->chunk % 16) return DR_ERR_CHUNK;
+    if (d->path < DR_PATH_AUTO || d->path > DR_PATH_TCGEN05) return DR_ERR_UNSUPPORTED;
+  }
+  return DR_OK;
+}
+
+dr::FwdParams make_fwd(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
+                       const float* beta, const float* h0, void* o, float* hT, int32_t* status) {
+  dr::FwdParams p;
+  p.q = q; p.k = k; p.v = v; p.g = g; p.beta = beta; p.h0 = h0; p.o = o; p.hT = hT;
+  p.status = status;
+  p.map.B = d->B; p.map.H = d->H; p.map.T = d->T; p.map.bthd = d->layout == DR_LAYOUT_BTHD;
+  p.K = d->K; p.V = d->V; p.C = d->chunk;
+  p.variant = d->variant; p.qkv_dt = d->qkv_dtype; p.g_dt = d->g_dtype; p.out_dt = d->out_dtype;
+  p.l2norm = d->use_qk_l2norm; p.scale = d->scale;
+  return p;
+}
+
+int validate_fwd_ptrs(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
+                      const float* beta, const float* h0, void* o, float* hT) {
+  if (!q || !k || !v || !beta || !o) return DR_ERR_NULL;
+  if (d->variant == DR_DELTA ? g != nullptr : g == nullptr) return DR_ERR_VARIANT;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(beta) ||
+      (g && !aligned16(g)) || (h0 && !aligned16(h0)) || (hT && !aligned16(hT)))
+    return DR_ERR_ALIGN;
+  return DR_OK;
+}
+
+bool tcgen05_eligible(const DrDesc* d) {
+  return dr::sm100::kAvailable && d->K == 128 && d->V == 128 && d->chunk == 64 &&
+         d->qkv_dtype == DR_BF16 && (d->variant == DR_GATED || d->variant == DR_DELTA) &&
+         (d->variant == DR_DELTA || d->g_dtype == DR_F32);
+}
+
+bool fp32_chunk_eligible(const DrDesc* d) { return d->chunk <= 64 && d->K <= 128; }
+
+}  // namespace
+
+extern "C" {
+
+const char* dr_version(void) { return "deltarule_sm100 0.1 (sm_100a)"; }
+
+const char* dr_strerror(int s) {
+  switch (s) {
+    case DR_OK: return "ok";
+    case DR_ERR_NULL: return "a required pointer is null";
+    case DR_ERR_SHAPE: return "shape out of the supported range (K,V multiples of 4 in [4,256]; B,H,T >= 1)";
+    case DR_ERR_DTYPE: return "unknown or unsupported dtype tag";
+    case DR_ERR_ALIGN: return "pointer not 16-byte aligned";
+    case DR_ERR_WORKSPACE: return "workspace too small";
+    case DR_ERR_VARIANT: return "unknown variant, or g given/missing against the variant";
+    case DR_ERR_CHUNK: return "chunk size not accepted (Gated DeltaNet / KDA need a multiple of 16)";
+    case DR_ERR_CUDA: return "CUDA runtime error";
+    case DR_ERR_UNSUPPORTED: return "no kernel of this build covers the request";
+    case DR_ERR_DEVICE: return "a kernel reported a device-side problem";
+    default: return "unknown status";
+  }
+}
+
+int dr_last_cuda_error(void) { return tl_cuda_error; }
+uint64_t dr_launch_count(void) { return g_launches.load(); }
+const char* dr_last_path(void) { return tl_path; }
+
+int64_t dr_workspace_bytes(const DrDesc* d, int op) {
+  int s = validate_common(d, true);
+  if (s != DR_OK) return s;
+  if (op == 0) return 0;
+  if (op == 1) return dr::bwd_workspace_bytes(d);
+  return DR_ERR_UNSUPPORTED;
+}
+
+int dr_chunk_fwd(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
+                 const float* beta, const float* h0, void* o, float* hT, void* workspace,
+                 size_t workspace_bytes, int32_t* status_dev, void* stream) {
+  (void)workspace; (void)workspace_bytes;
+  int s = validate_common(d, true);
+  if (s != DR_OK) return s;
+  s = validate_fwd_ptrs(d, q, k, v, g, beta, h0, o, hT);
+  if (s != DR_OK) return s;
+  const dr::FwdParams p = make_fwd(d, q, k, v, g, beta, h0, o, hT, status_dev);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int path = d->path;
+  if (path == DR_PATH_AUTO) path = tcgen05_eligible(d) ? DR_PATH_TCGEN05 : DR_PATH_FP32;
+  if (path == DR_PATH_TCGEN05) {
+    if (!tcgen05_eligible(d)) return DR_ERR_UNSUPPORTED;
+    tl_path = "chunk_tcgen05";
+    g_launches.fetch_add(1);
+    return check_cuda(dr::sm100::launch_chunk(p, st));
+  }
+  if (fp32_chunk_eligible(d)) {
+    tl_path = "chunk_fp32";
+    g_launches.fetch_add(1);
+    return check_cuda(dr::launch_chunk_fp32(p, st));
+  }
+  // Chunks longer than 64 or K > 128: the chunk form and the token recurrence are the same
+  // function of the inputs, so the register-resident recurrence serves these shapes.
+  tl_path = "recurrent";
+  g_launches.fetch_add(1);
+  return check_cuda(dr::launch_recurrent(p, st));
+}
+
+int dr_recurrent_fwd(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
+                     const float* beta, const float* h0, void* o, float* hT, void* stream) {
+  int s = validate_common(d, false);
+  if (s != DR_OK) return s;
+  s = validate_fwd_ptrs(d, q, k, v, g, beta, h0, o, hT);
+  if (s != DR_OK) return s;
+  const dr::FwdParams p = make_fwd(d, q, k, v, g, beta, h0, o, hT, nullptr);
+  tl_path = "recurrent";
+  g_launches.fetch_add(1);
+  return check_cuda(dr::launch_recurrent(p, reinterpret_cast<cudaStream_t>(stream)));
+}
+
+int dr_step(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
+            const float* beta, const float* state_in, float* state_out, void* o, void* stream) {
+  int s = validate_common(d, false);
+  if (s != DR_OK) return s;
+  if (d->T != 1) return DR_ERR_SHAPE;
+  if (!q || !k || !v || !beta || !o || !state_in || !state_out) return DR_ERR_NULL;
+  if (d->variant == DR_DELTA ? g != nullptr : g == nullptr) return DR_ERR_VARIANT;
+  if (!aligned16(state_in) || !aligned16(state_out) || !aligned16(q) || !aligned16(k) ||
+      !aligned16(v) || !aligned16(o))
+    return DR_ERR_ALIGN;
+  dr::StepParams p;
+  p.q = q; p.k = k; p.v = v; p.g = g; p.beta = beta; p.s_in = state_in; p.s_out = state_out; p.o = o;
+  p.K = d->K; p.V = d->V;
+  p.variant = d->variant; p.qkv_dt = d->qkv_dtype; p.g_dt = d->g_dtype; p.out_dt = d->out_dtype;
+  p.l2norm = d->use_qk_l2norm; p.scale = d->scale;
+  tl_path = "step";
+  g_launches.fetch_add(1);
+  return check_cuda(dr::launch_step(p, (int64_t)d->B * d->H, reinterpret_cast<cudaStream_t>(stream)));
+}
+
+int dr_chunk_bwd(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
+                 const float* beta, const float* h0, const void* d_o, const float* d_hT, void* dq,
+                 void* dk, void* dv, float* dbeta, float* dg, float* dh0, void* workspace,
+                 size_t workspace_bytes, int32_t* status_dev, void* stream) {
+  (void)status_dev;
+  int s = validate_common(d, true);
+  if (s != DR_OK) return s;
+  if (!q || !k || !v || !beta || !d_o || !dq || !dk || !dv || !dbeta) return DR_ERR_NULL;
+  if (d->variant == DR_DELTA ? (g != nullptr || dg != nullptr) : (g == nullptr || dg == nullptr))
+    return DR_ERR_VARIANT;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(d_o) || !aligned16(dq) ||
+      !aligned16(dk) || !aligned16(dv) || !aligned16(workspace))
+    return DR_ERR_ALIGN;
+  const int64_t need = dr::bwd_workspace_bytes(d);
+  if (need < 0) return (int)need;
+  if ((int64_t)workspace_bytes < need || (need > 0 && !workspace)) return DR_ERR_WORKSPACE;
+  tl_path = "bwd";
+  int launches = 0;
+  cudaError_t e = dr::launch_bwd(d, q, k, v, g, beta, h0, d_o, d_hT, dq, dk, dv, dbeta, dg, dh0,
+                                 workspace, reinterpret_cast<cudaStream_t>(stream), &launches);
+  g_launches.fetch_add(launches);
+  return check_cuda(e);
+}
+
+}  // extern "C"

@@ -1,0 +1,58 @@
+// Shared device/host helpers for the delta-rule kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "deltarule_sm100.h"
+
+namespace dr {
+
+// Addressing of one (batch, head) sequence inside a [B,H,T,D] or [B,T,H,D] tensor.
+// Element index of token t, feature d is  base(b,h,D) + t * tok(D) + d.
+struct SeqMap {
+  int B, H, T;
+  int bthd;  // 0: [B,H,T,D]   1: [B,T,H,D]
+  __host__ __device__ inline int64_t base(int b, int h, int D) const {
+    return bthd ? ((int64_t)b * T * H + h) * D : ((int64_t)b * H + h) * (int64_t)T * D;
+  }
+  __host__ __device__ inline int64_t tok(int D) const { return bthd ? (int64_t)H * D : D; }
+};
+
+__device__ __forceinline__ float ld_elem(const void* p, int64_t i, int dt) {
+  return dt == DR_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i])
+                       : reinterpret_cast<const float*>(p)[i];
+}
+
+__device__ __forceinline__ void st_elem(void* p, int64_t i, int dt, float x) {
+  if (dt == DR_BF16)
+    reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(x);
+  else
+    reinterpret_cast<float*>(p)[i] = x;
+}
+
+__device__ __forceinline__ float warp_sum(float x) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  return x;
+}
+
+// Parameters every forward kernel takes (plain struct passed by value).
+struct FwdParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* g;      // null for DR_DELTA
+  const float* beta;
+  const float* h0;    // null: zero state
+  void* o;
+  float* hT;          // null: not wanted
+  int32_t* status;    // device status word or null
+  SeqMap map;
+  int K, V, C;
+  int variant, qkv_dt, g_dt, out_dt, l2norm;
+  float scale;
+};
+
+}  // namespace dr

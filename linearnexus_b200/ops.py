@@ -1,0 +1,249 @@
+"""Host-side mirror of the LinearNexus delta-rule op signatures over the sm_100a C ABI.
+
+Each function keeps the name, argument order, keyword defaults, accepted shapes, output
+dtypes and error behaviour of the LinearNexus function it replaces (cited per function,
+paths relative to the LinearNexus tree); the arrays are torch CUDA tensors and the work is
+done by ``libdeltarule_sm100.so``.  There is no CPU path: CPU tensors raise.
+
+Layout: ``[B, H, T, D]`` as in the reference.  A tensor that is a transposed view of a
+contiguous ``[B, T, H, D]`` array (the blocks' pre-transpose layout,
+modules/linear_attn/gated_deltanet.py:785-795) is consumed in place without a copy when all
+sequence inputs share that layout.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import (DR_BF16, DR_DELTA, DR_F32, DR_GATED, DR_KDA, DR_LAYOUT_BHTD, DR_LAYOUT_BTHD,
+                   DR_PATH_AUTO, DR_PATH_FP32, DR_PATH_TCGEN05, DrDesc)
+
+Tensor = torch.Tensor
+_NATIVE = {torch.float32: DR_F32, torch.bfloat16: DR_BF16}
+_PATHS = {None: DR_PATH_AUTO, "auto": DR_PATH_AUTO, "fp32": DR_PATH_FP32, "tcgen05": DR_PATH_TCGEN05}
+
+# Kernel family used by the chunk entry point when a call does not say; tests set it to
+# force one family ("fp32" / "tcgen05").
+default_chunk_path: Optional[str] = None
+
+
+def _ptr(t: Optional[Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream(dev) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+
+def _require_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("linearnexus_b200 ops run on CUDA tensors only (there is no CPU fallback)")
+
+
+def _native(t: Tensor) -> Tensor:
+    """q/k/v/g travel as fp32 or bf16; other float types are widened to fp32."""
+    return t if t.dtype in _NATIVE else t.to(torch.float32)
+
+
+def _is_bthd_view(t: Tensor) -> bool:
+    return t.dim() >= 3 and not t.is_contiguous() and t.transpose(1, 2).is_contiguous()
+
+
+def _layout(seq_tensors) -> Tuple[int, list]:
+    """Pick [B,H,T,D] (copying if needed) or the zero-copy [B,T,H,D] view layout."""
+    ts = [t for t in seq_tensors if t is not None]
+    if ts[0].shape[1] > 1 and ts[0].shape[2] > 1 and all(_is_bthd_view(t) for t in ts):
+        return DR_LAYOUT_BTHD, list(seq_tensors)
+    return DR_LAYOUT_BHTD, [None if t is None else t.contiguous() for t in seq_tensors]
+
+
+def _state(initial_state, B, H, K, V, dev) -> Optional[Tensor]:
+    if initial_state is None:
+        return None
+    if tuple(initial_state.shape) != (B, H, K, V):
+        raise ValueError(f"initial_state must be [B,H,K,V]={B, H, K, V}, got {tuple(initial_state.shape)}")
+    return initial_state.to(device=dev, dtype=torch.float32).contiguous()
+
+
+def _desc(variant, layout, B, H, T, K, V, chunk, qkv, g, out_dtype, l2norm, scale, path=None) -> DrDesc:
+    d = DrDesc()
+    d.variant, d.layout = variant, layout
+    d.B, d.H, d.T, d.K, d.V, d.chunk = B, H, T, K, V, chunk
+    d.qkv_dtype = _NATIVE[qkv.dtype]
+    d.g_dtype = _NATIVE[g.dtype] if g is not None else DR_F32
+    d.out_dtype = _NATIVE[out_dtype]
+    d.use_qk_l2norm = int(bool(l2norm))
+    d.scale = float(scale)
+    if path not in _PATHS:
+        raise ValueError(f"unknown chunk path {path!r}")
+    d.path = _PATHS[path]
+    return d
+
+
+def _seq_forward(kind, variant, q, k, v, g, beta, initial_state, scale, chunk_size, l2norm,
+                 out_dtype, path=None):
+    _require_cuda(q, k, v, g, beta, initial_state)
+    if q.dim() != 4 or k.shape != q.shape or v.dim() != 4 or v.shape[:3] != q.shape[:3]:
+        raise ValueError(f"expected q,k [B,H,T,K] and v [B,H,T,V]; got {tuple(q.shape)}, {tuple(k.shape)}, {tuple(v.shape)}")
+    B, H, T, K = q.shape
+    V = v.shape[-1]
+    if scale is None:
+        scale = K ** -0.5
+    if beta.dim() == 4:
+        beta = beta.squeeze(-1)
+    if tuple(beta.shape) != (B, H, T):
+        raise ValueError(f"beta must be [B,H,T], got {tuple(beta.shape)}")
+    if variant == DR_GATED and tuple(g.shape) != (B, H, T):
+        raise ValueError(f"g must be [B,H,T], got {tuple(g.shape)}")
+    if variant == DR_KDA and tuple(g.shape) != (B, H, T, K):
+        raise ValueError(f"g must be [B,H,T,K], got {tuple(g.shape)}")
+    dev = q.device
+    common = torch.float32 if any(t.dtype not in _NATIVE for t in (q, k, v)) or len({q.dtype, k.dtype, v.dtype}) > 1 else q.dtype
+    qn, kn, vn = (t.to(common) for t in (q, k, v))
+    gn = None if g is None else _native(g)
+    bn = beta.to(torch.float32)
+    layout, (qn, kn, vn, gn, bn) = _layout([qn, kn, vn, gn, bn])
+    h0 = _state(initial_state, B, H, K, V, dev)
+    native_out = out_dtype if out_dtype in _NATIVE else torch.float32
+    if layout == DR_LAYOUT_BTHD:
+        o = torch.empty((B, T, H, V), dtype=native_out, device=dev).transpose(1, 2)
+    else:
+        o = torch.empty((B, H, T, V), dtype=native_out, device=dev)
+    hT = torch.empty((B, H, K, V), dtype=torch.float32, device=dev)
+    d = _desc(variant, layout, B, H, T, K, V, chunk_size, qn, gn, native_out, l2norm, scale,
+              path if path is not None else default_chunk_path)
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        if kind == "chunk":
+            st = lib.dr_chunk_fwd(ctypes.byref(d), _ptr(qn), _ptr(kn), _ptr(vn), _ptr(gn), _ptr(bn),
+                                  _ptr(h0), _ptr(o), _ptr(hT), None, 0, None, _stream(dev))
+        else:
+            st = lib.dr_recurrent_fwd(ctypes.byref(d), _ptr(qn), _ptr(kn), _ptr(vn), _ptr(gn), _ptr(bn),
+                                      _ptr(h0), _ptr(o), _ptr(hT), _stream(dev))
+    if st == -7:
+        raise ValueError(f"chunk_size (BT={chunk_size}) must be divisible by BC=16.")
+    _lib.check(st, f"dr_{kind}_fwd")
+    return (o if o.dtype == out_dtype else o.to(out_dtype)), hT
+
+
+def _step(variant, q, k, v, g, beta, state, scale, l2norm, out_dtype, inplace=False):
+    _require_cuda(q, k, v, g, beta, state)
+    if q.dim() != 3 or k.shape != q.shape or v.dim() != 3:
+        raise ValueError("expected q,k [B,H,K] and v [B,H,V]")
+    B, H, K = q.shape
+    V = v.shape[-1]
+    if scale is None:
+        scale = K ** -0.5
+    if tuple(state.shape) != (B, H, K, V):
+        raise ValueError(f"state must be [B,H,K,V]={B, H, K, V}, got {tuple(state.shape)}")
+    dev = q.device
+    common = torch.float32 if any(t.dtype not in _NATIVE for t in (q, k, v)) or len({q.dtype, k.dtype, v.dtype}) > 1 else q.dtype
+    qn, kn, vn = (t.to(common).contiguous() for t in (q, k, v))
+    gn = None if g is None else _native(g).contiguous()
+    bn = beta.to(torch.float32).contiguous()
+    if inplace:
+        if state.dtype != torch.float32 or not state.is_contiguous():
+            raise ValueError("in-place decode needs a contiguous float32 state cache")
+        s_in = s_out = state
+    else:
+        s_in = state.to(torch.float32).contiguous()
+        s_out = torch.empty_like(s_in)
+    native_out = out_dtype if out_dtype in _NATIVE else torch.float32
+    o = torch.empty((B, H, V), dtype=native_out, device=dev)
+    d = _desc(variant, DR_LAYOUT_BHTD, B, H, 1, K, V, 0, qn, gn, native_out, l2norm, scale)
+    with torch.cuda.device(dev):
+        st = _lib.load().dr_step(ctypes.byref(d), _ptr(qn), _ptr(kn), _ptr(vn), _ptr(gn), _ptr(bn),
+                                 _ptr(s_in), _ptr(s_out), _ptr(o), _stream(dev))
+    _lib.check(st, "dr_step")
+    return (o if o.dtype == out_dtype else o.to(out_dtype)), s_out
+
+
+# ------------------------------------------------------------------------------------------
+# DeltaNet  (modules/linear_attn/delta_net.py)
+# ------------------------------------------------------------------------------------------
+
+def delta_rule_recurrent(q, k, v, beta, initial_state=None, scale=None, backend=None) -> Tuple[Tensor, Tensor]:
+    """Token recurrence, no decay, no l2norm inside (delta_net.py:126-213).
+
+    ``backend`` is accepted for signature compatibility; every value runs the CUDA kernel
+    (the reference's silent fallback to its JAX path, delta_net.py:150-156, has no counterpart).
+    Returns ``(o.astype(q.dtype) [B,H,T,V], final_state float32 [B,H,K,V])``."""
+    return _seq_forward("recurrent", DR_DELTA, q, k, v, None, beta, initial_state, scale, 0, False, q.dtype)
+
+
+def delta_rule_chunkwise(q, k, v, beta, initial_state=None, chunk_size=64, scale=None, backend=None,
+                         path=None) -> Tuple[Tensor, Tensor]:
+    """WY chunk form (delta_net.py:216-354).  Any ``chunk_size`` >= 1; ``backend`` ignored as in the reference."""
+    return _seq_forward("chunk", DR_DELTA, q, k, v, None, beta, initial_state, scale, chunk_size, False, q.dtype, path)
+
+
+def delta_rule_step(q, k, v, beta, state, scale=None) -> Tuple[Tensor, Tensor]:
+    """One decode token (delta_net.py:357-397); beta may be [B,H] or [B,H,1]."""
+    if beta.dim() == 3:
+        beta = beta.squeeze(-1)
+    return _step(DR_DELTA, q, k, v, None, beta, state, scale, False, q.dtype)
+
+
+def delta_rule_recurrent_pallas(q, k, v, beta, initial_state=None, scale=None) -> Tuple[Tensor, Tensor]:
+    """Drop-in for the Pallas kernel entry point (kernels/pallas/delta_rule.py:47-281): same
+    maths as :func:`delta_rule_recurrent` and the same RuntimeError guards on key_dim % 32 and
+    value_dim % 64 (kernels/pallas/delta_rule.py:108-115)."""
+    if not q.is_cuda:
+        raise RuntimeError("the sm_100a delta-rule kernel is not usable on this machine: tensors are not on a CUDA device")
+    if q.shape[-1] % 32 != 0:
+        raise RuntimeError("delta-rule kernel entry requires key_dim to be a multiple of 32")
+    if v.shape[-1] % 64 != 0:
+        raise RuntimeError("delta-rule kernel entry requires value_dim to be a multiple of 64")
+    return delta_rule_recurrent(q, k, v, beta, initial_state, scale)
+
+
+# ------------------------------------------------------------------------------------------
+# Gated DeltaNet  (modules/linear_attn/gated_deltanet.py)
+# ------------------------------------------------------------------------------------------
+
+def gated_delta_rule_recurrent(q, k, v, g, beta, scale=None, initial_state=None, use_qk_l2norm=True):
+    """Scalar-decay token recurrence (gated_deltanet.py:136-229)."""
+    return _seq_forward("recurrent", DR_GATED, q, k, v, g, beta, initial_state, scale, 0, use_qk_l2norm, q.dtype)
+
+
+def gated_delta_rule_chunkwise(q, k, v, g, beta, scale=None, initial_state=None, chunk_size=64,
+                               use_qk_l2norm=True, path=None):
+    """Chunk form with scalar decay (gated_deltanet.py:232-534).  ``chunk_size % 16 != 0`` raises
+    ValueError as the reference does (:318-321).  The kernel normalises q,k in fp32 (the
+    reference does it in the input dtype, :273-275 -- strictly less accurate for bf16)."""
+    return _seq_forward("chunk", DR_GATED, q, k, v, g, beta, initial_state, scale, chunk_size, use_qk_l2norm, q.dtype, path)
+
+
+def gated_delta_rule_step(q, k, v, g, beta, state, scale=None, use_qk_l2norm=True, inplace=False):
+    """One decode token (gated_deltanet.py:539-597).  ``inplace=True`` (an extension) updates the
+    float32 ``state`` cache in place and returns it, which is what a serving loop wants; the
+    default returns a new state like the functional reference."""
+    return _step(DR_GATED, q, k, v, g, beta, state, scale, use_qk_l2norm, q.dtype, inplace)
+
+
+# ------------------------------------------------------------------------------------------
+# KDA  (modules/linear_attn/kda.py)
+# ------------------------------------------------------------------------------------------
+
+def kda_recurrent(q, k, v, g, beta, scale=None, initial_state=None, use_qk_l2norm=True):
+    """Per-channel-decay token recurrence (kda.py:179-283)."""
+    return _seq_forward("recurrent", DR_KDA, q, k, v, g, beta, initial_state, scale, 0, use_qk_l2norm, q.dtype)
+
+
+def kda_step(q, k, v, g, beta, state, scale=None, use_qk_l2norm=True, inplace=False):
+    """One decode token (kda.py:286-347).  The output takes the STATE's dtype, as in the
+    reference (kda.py:347)."""
+    return _step(DR_KDA, q, k, v, g, beta, state, scale, use_qk_l2norm, state.dtype, inplace)
+
+
+def kda_chunkwise(q, k, v, g, beta, scale=None, initial_state=None, chunk_size=64, use_qk_l2norm=True,
+                  path=None, out_dtype=None):
+    """Chunk form with per-channel decay (kda.py:350-655).  The output is float32 whatever the
+    input dtype, as in the reference (kda.py:416,655); ``out_dtype`` (an extension) overrides it."""
+    return _seq_forward("chunk", DR_KDA, q, k, v, g, beta, initial_state, scale, chunk_size, use_qk_l2norm,
+                        torch.float32 if out_dtype is None else out_dtype, path)

@@ -1,0 +1,86 @@
+"""CPU tests of the drop-in boundary: the library loads, exports every symbol the header
+declares, and host-side validation returns the documented status codes (no kernel runs)."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+import linearnexus_b200 as L
+from linearnexus_b200 import _lib
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _header_functions():
+    text = (ROOT / "include" / "deltarule_sm100.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(dr_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    names = _header_functions()
+    assert set(_lib.EXPORTS) <= set(names)
+    for n in names:
+        assert hasattr(lib, n), n
+    assert b"sm_100a" in lib.dr_version()
+
+
+def test_desc_struct_matches_header():
+    assert ctypes.sizeof(_lib.DrDesc) == 16 * 4
+
+
+def _desc(**kw):
+    d = _lib.DrDesc()
+    d.variant, d.layout, d.B, d.H, d.T, d.K, d.V, d.chunk = 1, 0, 1, 1, 64, 128, 128, 64
+    d.qkv_dtype = d.g_dtype = d.out_dtype = 0
+    d.scale = 1.0
+    for k, v in kw.items():
+        setattr(d, k, v)
+    return d
+
+
+def test_validation_status_codes():
+    lib = _lib.load()
+    call = lambda d, g=8: lib.dr_chunk_fwd(ctypes.byref(d), 16, 16, 16, g, 16, None, 16, None, None, 0, None, None)
+    assert lib.dr_chunk_fwd(ctypes.byref(_desc()), None, 16, 16, 16, 16, None, 16, None, None, 0, None, None) == -1
+    assert call(_desc(K=130)) == -2
+    assert call(_desc(V=1024)) == -2
+    assert call(_desc(qkv_dtype=7)) == -3
+    assert call(_desc(), g=16 + 4) == -4          # misaligned g
+    assert call(_desc(variant=0), g=16) == -6     # DeltaNet must not get g
+    assert call(_desc(variant=1), g=None) == -6   # Gated DeltaNet needs g
+    assert call(_desc(chunk=24), g=16) == -7      # reference: ValueError when chunk % 16 != 0
+    assert call(_desc(variant=5), g=16) == -6
+    assert lib.dr_step(ctypes.byref(_desc(T=2)), 16, 16, 16, 16, 16, 16, 16, 16, None) == -2
+    assert lib.dr_workspace_bytes(ctypes.byref(_desc()), 0) == 0
+    for s in range(-10, 1):
+        assert lib.dr_strerror(s)
+
+
+def test_ops_refuse_cpu_tensors():
+    q = torch.randn(1, 1, 16, 16)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        L.gated_delta_rule_chunkwise(q, q, q, torch.zeros(1, 1, 16), torch.ones(1, 1, 16))
+    with pytest.raises(RuntimeError):
+        L.delta_rule_recurrent_pallas(q, q, q, torch.ones(1, 1, 16))
+
+
+def test_backend_selection_is_single_backend():
+    assert L.select_kernel_backend(None) == L.KernelBackend.SM100
+    assert L.select_kernel_backend("pallas") == L.KernelBackend.SM100
+    assert L.select_kernel_backend("reference") == L.KernelBackend.SM100
+    with pytest.raises(ValueError):
+        L.select_kernel_backend("tpu")
+
+
+def test_state_factories_cpu():
+    s = L.GatedDeltaNetState.zeros(2, 4, 16, 32, key_dim_total=64, value_dim=128, device="cpu")
+    assert s.S.shape == (2, 4, 16, 32) and s.S.dtype == torch.float32
+    assert s.conv_state_q.shape == (2, 3, 64) and s.conv_state_v.shape == (2, 3, 128)
+    s = L.KDAState.zeros(2, 4, 16, 32, device="cpu")
+    assert s.conv_state_q is None
+    s = L.DeltaNetState.zeros(2, 4, 16, 32, conv_channels=64, device="cpu")
+    assert s.conv_state.shape == (2, 3, 64)
