@@ -147,6 +147,16 @@ int dr_chunk_bwd(const DrDesc* desc, const void* q, const void* k, const void* v
                  void* dk, void* dv, float* dbeta, float* dg, float* dh0, void* workspace,
                  size_t workspace_bytes, int32_t* status_dev, void* stream);
 
+/*
+ * Debug entry with no counterpart in the reference: runs one 128 x n x kd bf16 product
+ * D = A * B^T through the tcgen05/TMEM plumbing the chunk kernel uses (A [128][kd] row-major
+ * read from shared memory or staged in tensor memory; B given as [n][kd] (K-major) or as
+ * [kd][n] (MN-major)), so the GPU tests can pin the descriptor encodings against a plain
+ * matmul.  n in {64,128}; kd in {32,64,96,128}.  d_out: float32 [128][n].
+ */
+int dr_debug_umma_selftest(const void* a, const void* b, float* d_out, int kd, int n, int a_in_tmem,
+                           int b_mn_major, int32_t* status_dev, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -18,7 +18,7 @@ _ROOT = _PKG.parent
 LIB_PATH = _PKG / "libdeltarule_sm100.so"
 _SOURCES = ["dr_api.cu"]
 _HEADERS = ["dr_common.cuh", "dr_step.cuh", "dr_recurrent.cuh", "dr_chunk_fp32.cuh",
-            "dr_chunk_sm100.cuh", "dr_bwd.cuh"]
+            "dr_chunk_sm100.cuh", "dr_bwd.cuh", "dr_tcgen05.cuh", "dr_umma_selftest.cuh"]
 
 # DrVariant / DrDtype / DrLayout / DrChunkPath (include/deltarule_sm100.h)
 DR_DELTA, DR_GATED, DR_KDA = 0, 1, 2
@@ -27,7 +27,8 @@ DR_LAYOUT_BHTD, DR_LAYOUT_BTHD = 0, 1
 DR_PATH_AUTO, DR_PATH_FP32, DR_PATH_TCGEN05 = 0, 1, 2
 
 EXPORTS = ["dr_version", "dr_strerror", "dr_last_cuda_error", "dr_launch_count", "dr_last_path",
-           "dr_workspace_bytes", "dr_chunk_fwd", "dr_recurrent_fwd", "dr_step", "dr_chunk_bwd"]
+           "dr_workspace_bytes", "dr_chunk_fwd", "dr_recurrent_fwd", "dr_step", "dr_chunk_bwd",
+           "dr_debug_umma_selftest"]
 
 
 class DrDesc(ctypes.Structure):
@@ -115,6 +116,8 @@ def load() -> ctypes.CDLL:
         lib.dr_chunk_bwd.restype = ctypes.c_int
         lib.dr_chunk_bwd.argtypes = [dp, vp, vp, vp, vp, fp, fp, vp, fp, vp, vp, vp, fp, fp, fp, vp,
                                      ctypes.c_size_t, ip, vp]
+        lib.dr_debug_umma_selftest.restype = ctypes.c_int
+        lib.dr_debug_umma_selftest.argtypes = [vp, vp, fp, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ip, vp]
         _lib = lib
     return _lib
 

@@ -176,6 +176,16 @@ int dr_step(const DrDesc* d, const void* q, const void* k, const void* v, const 
   return check_cuda(dr::launch_step(p, (int64_t)d->B * d->H, reinterpret_cast<cudaStream_t>(stream)));
 }
 
+int dr_debug_umma_selftest(const void* a, const void* b, float* d_out, int kd, int n, int a_in_tmem,
+                            int b_mn_major, int32_t* status_dev, void* stream) {
+  if (!a || !b || !d_out) return DR_ERR_NULL;
+  if ((n != 64 && n != 128) || kd < 32 || kd > 128 || kd % 32) return DR_ERR_SHAPE;
+  tl_path = "umma_selftest";
+  g_launches.fetch_add(1);
+  return check_cuda(dr::sm100::launch_umma_selftest(a, b, d_out, kd, n, a_in_tmem, b_mn_major, status_dev,
+                                                    reinterpret_cast<cudaStream_t>(stream)));
+}
+
 int dr_chunk_bwd(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
                  const float* beta, const float* h0, const void* d_o, const float* d_hT, void* dq,
                  void* dk, void* dv, float* dbeta, float* dg, float* dh0, void* workspace,
