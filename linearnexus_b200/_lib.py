@@ -15,7 +15,8 @@ from pathlib import Path
 
 _PKG = Path(__file__).resolve().parent
 _ROOT = _PKG.parent
-LIB_PATH = _PKG / "libdeltarule_sm100.so"
+# DELTARULE_SM100_LIB points the loader at another build of the same library (profiling builds).
+LIB_PATH = Path(os.environ.get("DELTARULE_SM100_LIB", _PKG / "libdeltarule_sm100.so"))
 _SOURCES = ["dr_api.cu"]
 _HEADERS = ["dr_common.cuh", "dr_step.cuh", "dr_recurrent.cuh", "dr_chunk_fp32.cuh",
             "dr_chunk_sm100.cuh", "dr_bwd.cuh", "dr_tcgen05.cuh", "dr_umma_selftest.cuh"]

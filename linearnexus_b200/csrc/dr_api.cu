@@ -176,6 +176,16 @@ int dr_step(const DrDesc* d, const void* q, const void* k, const void* v, const 
   return check_cuda(dr::launch_step(p, (int64_t)d->B * d->H, reinterpret_cast<cudaStream_t>(stream)));
 }
 
+#ifdef DR_PROFILE
+// Profiling builds only: copies (and clears) the per-phase cycle counters of the chunk kernel.
+int dr_debug_read_profile(unsigned long long* out64_host) {
+  cudaError_t e = cudaMemcpyFromSymbol(out64_host, dr::sm100::g_prof, sizeof(unsigned long long) * 64);
+  if (e != cudaSuccess) return check_cuda(e);
+  unsigned long long z[64] = {0};
+  return check_cuda(cudaMemcpyToSymbol(dr::sm100::g_prof, z, sizeof(z)));
+}
+#endif
+
 int dr_debug_umma_selftest(const void* a, const void* b, float* d_out, int kd, int n, int a_in_tmem,
                             int b_mn_major, int32_t* status_dev, void* stream) {
   if (!a || !b || !d_out) return DR_ERR_NULL;

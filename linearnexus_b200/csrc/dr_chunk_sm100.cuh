@@ -1,22 +1,35 @@
 // Chunkwise gated delta-rule forward on the Blackwell tensor cores (tcgen05 + TMEM).
 //
-// Shape: K = V = 128, chunk C = 64, bf16 q/k/v/o, fp32 g/beta/state.  One CTA of 128 threads
-// owns one (batch, head) sequence; the fp32 state lives TRANSPOSED in tensor memory
-// (S^T: lane = value column v, column = key row k) for the whole sequence, so every product of
-// the chunk recurrence has M = 128 = V and the per-thread epilogues own one value column.
+// Shape: K = V = 128, chunk C = 64, bf16 q/k/v/o, fp32 g/beta/state.  One CTA of 512 threads
+// owns one (batch, head) sequence.  The fp32 state lives TRANSPOSED in tensor memory for the
+// whole sequence (S^T: lane = value column v, column = key row k), so every product has
+// M = 128 and each epilogue thread owns one value column.
 //
-// Per chunk (G = cumulative log decay inside the chunk, L = its last row):
-//   (1) D1 = [K^;Q^] K^^T                       128x64x128   smem x smem
-//       A_kk = beta_i D1[i][j] e^{G_i-G_j} (i>j)  ->  T = (I + A_kk)^-1 on the CUDA cores (fp32)
-//       A_qk = D1[64+i][j] e^{G_i-G_j} (i>=j)     ->  bf16 operand
-//   (2) D2 = S^T [K^;Q^]^T                       128x128x128  tmem(bf16 copy of S^T) x smem
-//       R^T[v][c] = beta_c (V[c][v] - D2[v][c] e^{G_c})                        -> bf16 -> tmem
-//   (3) D3 = R^T T^T = V_new^T                   128x64x64    tmem x smem
-//   (4) D4 = V_new^T A_qk^T                      128x64x64    tmem x smem
-//       O^T[v][i] = e^{G_i} D2[v][64+i] + D4[v][i]
-//   (5) S^T = e^{G_L} S^T + (V_new^T e^{G_L-G_c}) K^   128x128x64   tmem x smem (K^ read MN-major)
-// The shared-memory tile [K^;Q^] is stored once as 8x8 core matrices and serves as the A operand
-// of (1), the K-major B operand of (1) and (2), and the MN-major B operand of (5).
+// Two groups of eight warps run as a two-stage pipeline over the chunks of the sequence (two
+// warps share each 32-lane quarter of tensor memory and split the columns of every epilogue):
+//
+//   PRODUCER (warps 0-7): everything that does not depend on the state.
+//     K,Q rows arrive by 1-D bulk copies (cp.async.bulk + mbarrier) one chunk ahead; V rows are
+//     scattered straight into their core-matrix tile by 16-byte cp.async.
+//     l2-normalise K^,Q^ (fp32) -> core-matrix tile [K^;Q^]
+//     (1) D1 = [K^;Q^] K^^T                          128x64x128  smem x smem
+//         A_kk = beta_i D1[i][j] e^{G_i-G_j} (i>j);  A_qk = D1[64+i][j] e^{G_i-G_j} (i>=j) -> bf16 tile
+//         T = (I + A_kk)^-1: blocked forward substitution on the CUDA cores (fp32)
+//         -> Tb = T diag(beta), Tw = T diag(beta e^G)   bf16 tiles
+//     (2) U^T = V^T Tb^T  -> TMEM (stage accumulator)  128x64x64   smem(MN-major) x smem
+//         W^T = K^^T Tw^T -> TMEM -> bf16 tile W       128x64x64   smem(MN-major) x smem
+//   CONSUMER (warps 8-15): the serial chain over the state.
+//         bf16 copy of S^T for the products; fp32 S^T pre-multiplied by e^{G_L}
+//     (3) V_new^T = U^T - S^T W^T  (accumulated onto the producer's U^T with negate-A)   128x64x128
+//         Dq = S^T Q^^T                                                                   128x64x128
+//     (4) Do = V_new^T A_qk^T                                                             128x64x64
+//     (5) S^T += (V_new^T e^{G_L-G_c}) K^   (K^ read MN-major)                             128x128x64
+//         O^T[v][i] = e^{G_i} Dq[v][i] + Do[v][i], written one chunk late so that it overlaps (3)
+//
+// The [K^;Q^] tile is stored once as 8x8 core matrices and serves as A and B of (1), MN-major
+// A of (2), K-major B of (3) and MN-major B of (5).  Every wait on an mbarrier is bounded; a
+// wait that runs out sets DR_DEV_TIMEOUT in the status word and the kernel finishes without
+// further waiting.
 #pragma once
 
 #include "dr_common.cuh"
@@ -27,207 +40,370 @@ namespace dr {
 namespace sm100 {
 
 constexpr bool kAvailable = true;
-constexpr int kThreads = 128;
+constexpr int kThreads = 512;
+constexpr int kGroup = 256;
 constexpr int kC = 64, kD = 128;
 
-// tensor-memory columns (32-bit x 128 lanes each)
-constexpr uint32_t TM_S = 0;      // S^T fp32                    128 cols
-constexpr uint32_t TM_SB = 128;   // bf16 copy of S^T (A operand)  64 cols
-constexpr uint32_t TM_D2 = 192;   // S^T [K^;Q^]^T               128 cols
-constexpr uint32_t TM_D3 = 320;   // D1, then V_new^T, then D4     64 cols
-constexpr uint32_t TM_RA = 384;   // R^T, then V_new^T (bf16)      32 cols
-constexpr uint32_t TM_VB = 416;   // decayed V_new^T (bf16)        32 cols
+// tensor-memory columns (32-bit x 128 lanes each): 512 in total
+constexpr uint32_t TM_S = 0;      // S^T fp32                                   128
+constexpr uint32_t TM_SB = 128;   // bf16 copy of S^T (A operand)                 64
+constexpr uint32_t TM_D1 = 192;   // producer scratch: D1, then W^T               64
+constexpr uint32_t TM_DU = 256;   // 2 stages x 64: U^T -> V_new^T -> Do          128
+constexpr uint32_t TM_DQ = 384;   // S^T Q^^T                                     64
+constexpr uint32_t TM_VA = 448;   // V_new^T bf16                                 32
+constexpr uint32_t TM_VB = 480;   // decayed V_new^T bf16                         32
 constexpr uint32_t TM_COLS = 512;
 
-// shared-memory map (bytes)
-constexpr int SM_QK = 0;                       // [K^ (64 rows); Q^ (64 rows)] x 128, core-matrix tiled: 32 KB
-constexpr int QK_RBS = 16 * 128;               // row-block stride of SM_QK
-constexpr int SM_V = SM_QK + 128 * 128 * 2;    // V chunk [64][128] bf16 row-major, reused as the O staging tile: 16 KB
-constexpr int SM_T = SM_V + 64 * 128 * 2;      // T [64][64] bf16 core-matrix tiled: 8 KB
-constexpr int SM_AQK = SM_T + 64 * 64 * 2;     // A_qk [64][64] bf16 core-matrix tiled: 8 KB
-constexpr int A_RBS = 8 * 128;                 // row-block stride of SM_T / SM_AQK
-constexpr int SM_AKK = SM_AQK + 64 * 64 * 2;   // A_kk fp32 [64][65]
-constexpr int AKK_LD = 65;
-constexpr int SM_G = SM_AKK + 64 * AKK_LD * 4; // G[64], beta[64], e^G[64], e^{G_L-G}[64]
-constexpr int SM_TOTAL = SM_G + 4 * 64 * 4;
+// shared-memory map (bytes).  Per stage (two stages):
+constexpr int RBS = 16 * 128;                 // row-block stride of the 128-column core-matrix tiles
+constexpr int A_RBS = 8 * 128;                // row-block stride of the 64-column tiles
+constexpr int ST_QK = 0;                      // [K^ (64 rows); Q^ (64 rows)] x 128   32 KB
+constexpr int ST_W = ST_QK + 128 * 128 * 2;   // W [64][128]; reused as the O staging tile  16 KB
+constexpr int ST_AQK = ST_W + 64 * 128 * 2;   // A_qk [64][64]                           8 KB
+constexpr int ST_SC = ST_AQK + 64 * 64 * 2;   // G, e^G, e^{G_L-G}, beta: 4 x 64 floats  1 KB
+constexpr int STAGE_BYTES = ST_SC + 4 * 64 * 4;
+// Producer-private:
+constexpr int SM_V = 2 * STAGE_BYTES;         // V [64][128] core-matrix tile           16 KB
+constexpr int SM_TB = SM_V + 64 * 128 * 2;    // T diag(beta)        [64][64] bf16
+constexpr int SM_TW = SM_TB + 64 * 64 * 2;    // T diag(beta e^G)    [64][64] bf16
+constexpr int LDT = 68;                       // row stride (floats) of the fp32 64x64 matrices
+constexpr int SM_AKK = SM_TW + 64 * 64 * 2;   // A_kk fp32 [64][68]
+constexpr int SM_T32 = SM_AKK + 64 * LDT * 4; // T fp32 [64][68]
+constexpr int SM_RAW = SM_T32 + 64 * LDT * 4; // raw K rows, raw Q rows [64][128] bf16 row-major  32 KB
+constexpr int SM_TOTAL = SM_RAW + 2 * 64 * 128 * 2;
+
+// Optional per-phase cycle counters (CTA 0 only), compiled in with -DDR_PROFILE.
+#ifdef DR_PROFILE
+__device__ unsigned long long g_prof[64];
+#define PROF_DECL unsigned long long prof_t0 = clock64();
+#define PROF(idx)                                              \
+  do {                                                         \
+    if (blockIdx.x == 0 && gt == 0) {                          \
+      const unsigned long long prof_t = clock64();             \
+      atomicAdd(&g_prof[idx], prof_t - prof_t0);               \
+      prof_t0 = prof_t;                                        \
+    }                                                          \
+  } while (0)
+#else
+#define PROF_DECL
+#define PROF(idx)
+#endif
+
+struct Ctl {
+  uint64_t full[2], empty[2], barP, bar1, bar2, raw;
+  uint32_t tmem_base;
+  int abort;
+};
+
+__device__ __forceinline__ void group_sync(int id) { asm volatile("bar.sync %0, 256;" ::"r"(id) : "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// T = (I + A)^-1 for a strictly lower-triangular 64x64 A (fp32, row stride LDT) by blocked forward
+// substitution with 16x16 diagonal blocks, all 256 threads of the producer group.  sT receives
+// the lower triangle of T; its upper-right 32x32 quadrant is scratch; the upper-right 16x16 blocks
+// of its two diagonal 32x32 quadrants must be zero on entry and stay zero.
+__device__ __forceinline__ void block_inverse_64(const float* __restrict__ sA, float* __restrict__ sT, int gt) {
+  // diagonal blocks: one thread per column of each 16x16 block
+  if (gt < 64) {
+    const int o = (gt >> 4) * 16, c = gt & 15;
+    float x[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float acc = (i == c) ? 1.f : 0.f;
+#pragma unroll
+      for (int j = 0; j < i; ++j) acc -= sA[(o + i) * LDT + o + j] * x[j];
+      x[i] = acc;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) sT[(o + i) * LDT + o + c] = x[i];
+  }
+  group_sync(1);
+  // level 1: T_10 = -T_11 (A_10 T_00) and T_32 = -T_33 (A_32 T_22); thread -> 1 row x 2 columns
+  {
+    const int pr = gt >> 7;                     // pair 0: rows 16..31 / cols 0..15;  pair 1: rows 48..63 / cols 32..47
+    const int row = (gt & 127) >> 3, c2 = (gt & 7) * 2;
+    const int r0 = 32 * pr + 16, c0 = 32 * pr;  // block row / column origin
+    const int xc = 32 + 16 * pr;                // scratch columns in the upper-right quadrant (rows 0..15)
+    float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const float a = sA[(r0 + row) * LDT + c0 + k];
+      const float2 t = *reinterpret_cast<const float2*>(sT + (c0 + k) * LDT + c0 + c2);
+      a0 += a * t.x; a1 += a * t.y;
+    }
+    *reinterpret_cast<float2*>(sT + row * LDT + xc + c2) = make_float2(a0, a1);
+    group_sync(1);
+    a0 = a1 = 0.f;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const float a = sT[(r0 + row) * LDT + r0 + k];
+      const float2 t = *reinterpret_cast<const float2*>(sT + k * LDT + xc + c2);
+      a0 -= a * t.x; a1 -= a * t.y;
+    }
+    *reinterpret_cast<float2*>(sT + (r0 + row) * LDT + c0 + c2) = make_float2(a0, a1);
+  }
+  group_sync(1);
+  // level 2: T[32:64][0:32] = -T[32:64][32:64] (A[32:64][0:32] T[0:32][0:32]); thread -> 1 row x 4 columns
+  {
+    const int row = gt >> 3, c4 = (gt & 7) * 4;
+    float x0 = 0.f, x1 = 0.f, x2 = 0.f, x3 = 0.f;
+#pragma unroll 8
+    for (int k = 0; k < 32; ++k) {
+      const float a = sA[(32 + row) * LDT + k];
+      const float4 t = *reinterpret_cast<const float4*>(sT + k * LDT + c4);
+      x0 += a * t.x; x1 += a * t.y; x2 += a * t.z; x3 += a * t.w;
+    }
+    // (every read of the level-1 scratch finished before the barrier above)
+    *reinterpret_cast<float4*>(sT + row * LDT + 32 + c4) = make_float4(x0, x1, x2, x3);
+    group_sync(1);
+    x0 = x1 = x2 = x3 = 0.f;
+#pragma unroll 8
+    for (int k = 0; k < 32; ++k) {
+      const float a = sT[(32 + row) * LDT + 32 + k];
+      const float4 t = *reinterpret_cast<const float4*>(sT + k * LDT + 32 + c4);
+      x0 -= a * t.x; x1 -= a * t.y; x2 -= a * t.z; x3 -= a * t.w;
+    }
+    *reinterpret_cast<float4*>(sT + (32 + row) * LDT + c4) = make_float4(x0, x1, x2, x3);
+  }
+  group_sync(1);
+}
 
 __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ __align__(8) uint64_t bar;
-  __shared__ uint32_t tmem_base_s;
-  __shared__ int abort_s;
+  __shared__ __align__(8) Ctl ctl;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int gt = tid & (kGroup - 1);     // thread index inside its group of eight warps
+  const int hs = gt >> 7;                // which of the two warps sharing a tensor-memory lane quarter
+  const int l128 = gt & 127;             // tensor-memory lane owned by this thread
+  const bool producer = tid < kGroup;
   const int T = p.map.T;
   const int unit = blockIdx.x;
   const int b = unit / p.map.H, h = unit % p.map.H;
   const int64_t qk_base = p.map.base(b, h, kD), qk_tok = p.map.tok(kD);
   const int64_t s_base = p.map.base(b, h, 1), s_tok = p.map.tok(1);
-  const __nv_bfloat16* gq = reinterpret_cast<const __nv_bfloat16*>(p.q);
-  const __nv_bfloat16* gk = reinterpret_cast<const __nv_bfloat16*>(p.k);
-  const __nv_bfloat16* gv = reinterpret_cast<const __nv_bfloat16*>(p.v);
-  __nv_bfloat16* go = reinterpret_cast<__nv_bfloat16*>(p.o);
-  const float* gg = reinterpret_cast<const float*>(p.g);
-
-  uint8_t* sQK = smem + SM_QK;
-  __nv_bfloat16* sV = reinterpret_cast<__nv_bfloat16*>(smem + SM_V);
-  uint8_t* sT = smem + SM_T;
-  uint8_t* sAqk = smem + SM_AQK;
-  float* sAkk = reinterpret_cast<float*>(smem + SM_AKK);
-  float* sG = reinterpret_cast<float*>(smem + SM_G);
-  float* sBeta = sG + 64;
-  float* sEG = sG + 128;
-  float* sW = sG + 192;
 
   if (warp == 0) {
-    tc::tmem_alloc(tc::smem_u32(&tmem_base_s), TM_COLS);
+    tc::tmem_alloc(tc::smem_u32(&ctl.tmem_base), TM_COLS);
     tc::tmem_relinquish();
   }
   if (tid == 0) {
-    tc::mbar_init(tc::smem_u32(&bar), 1);
+    tc::mbar_init(tc::smem_u32(&ctl.full[0]), kGroup);
+    tc::mbar_init(tc::smem_u32(&ctl.full[1]), kGroup);
+    tc::mbar_init(tc::smem_u32(&ctl.empty[0]), kGroup);
+    tc::mbar_init(tc::smem_u32(&ctl.empty[1]), kGroup);
+    tc::mbar_init(tc::smem_u32(&ctl.barP), 1);
+    tc::mbar_init(tc::smem_u32(&ctl.bar1), 1);
+    tc::mbar_init(tc::smem_u32(&ctl.bar2), 1);
+    tc::mbar_init(tc::smem_u32(&ctl.raw), 1);
     tc::fence_mbar_init();
-    abort_s = 0;
+    ctl.abort = 0;
   }
   tc::tc_fence_before();
   __syncthreads();
   tc::tc_fence_after();
-  const uint32_t tbase = tmem_base_s;
-  const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
-  const uint32_t bar_a = tc::smem_u32(&bar);
-  uint32_t phase = 0;
+  const uint32_t tbase = ctl.tmem_base;
+  const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+  volatile int* abort_p = &ctl.abort;
 
-  auto wait_mma = [&]() {
-    if (!abort_s) {
-      if (!tc::mbar_wait_bounded(bar_a, phase, kWaitLimit)) {
-        abort_s = 1;
+  auto wait_bar = [&](uint64_t* bar, uint32_t parity) {
+    if (!*abort_p) {
+      if (!tc::mbar_wait_bounded(tc::smem_u32(bar), parity, kWaitLimit)) {
+        *abort_p = 1;
         if (p.status) atomicOr(p.status, DR_DEV_TIMEOUT);
       }
     }
-    phase ^= 1;
-    tc::tc_fence_after();
   };
 
-  // ---- initial state: S^T[v][k] = h0[k][v] (thread = value column v) -------------------------
-  {
-    const float* h0 = p.h0 ? p.h0 + (int64_t)unit * kD * kD : nullptr;
-    for (int c0 = 0; c0 < kD; c0 += 32) {
-      uint32_t r[32];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) r[j] = h0 ? __float_as_uint(h0[(c0 + j) * kD + tid]) : 0u;
-      tc::tmem_st32(tbase + TM_S + lane_addr + c0, r);
-    }
-    tc::tc_wait_st();
-  }
-
   const uint32_t id_n64 = tc::idesc_bf16(128, 64, 0, 0);
-  const uint32_t id_n128 = tc::idesc_bf16(128, 128, 0, 0);
-  const uint32_t id_n128_mn = tc::idesc_bf16(128, 128, 0, 1);
-  const uint32_t aQK = tc::smem_u32(sQK), aT = tc::smem_u32(sT), aAqk = tc::smem_u32(sAqk);
-
+  const uint32_t id_n64_amn = tc::idesc_bf16(128, 64, 1, 0);
+  const uint32_t id_n64_neg = id_n64 | (1u << 13);
+  const uint32_t id_n128_bmn = tc::idesc_bf16(128, 128, 0, 1);
   const int nchunks = (T + kC - 1) / kC;
-  for (int n = 0; n < nchunks; ++n) {
-    const int t0 = n * kC;
-    const int rows = min(kC, T - t0);
-    __syncthreads();  // previous chunk's readers of smem are done
-    // ---- P1: stage K^, Q^ (fp32 l2norm, q scaled), V, g, beta --------------------------------
-    {
-      const int r = tid >> 1, half = tid & 1;  // row r, columns [64*half, 64*half+64)
-      const bool live = r < rows;
-#pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        const __nv_bfloat16* src = (which == 0 ? gk : gq) + qk_base + (int64_t)(t0 + r) * qk_tok + 64 * half;
-        uint4 raw[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) raw[j] = live ? reinterpret_cast<const uint4*>(src)[j] : make_uint4(0, 0, 0, 0);
-        float ss = 0.f;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[j]);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 f = __bfloat1622float2(h2[e]);
-            ss += f.x * f.x + f.y * f.y;
-          }
+
+  if (producer) {
+    // =========================== PRODUCER ===========================================================
+    const __nv_bfloat16* gq = reinterpret_cast<const __nv_bfloat16*>(p.q);
+    const __nv_bfloat16* gk = reinterpret_cast<const __nv_bfloat16*>(p.k);
+    const __nv_bfloat16* gv = reinterpret_cast<const __nv_bfloat16*>(p.v);
+    const float* gg = reinterpret_cast<const float*>(p.g);
+    uint8_t* sV = smem + SM_V;
+    uint8_t* sTb = smem + SM_TB;
+    uint8_t* sTw = smem + SM_TW;
+    float* sAkk = reinterpret_cast<float*>(smem + SM_AKK);
+    float* sT32 = reinterpret_cast<float*>(smem + SM_T32);
+    const uint8_t* sRaw = smem + SM_RAW;
+    const uint32_t aRaw = tc::smem_u32(sRaw), rawbar = tc::smem_u32(&ctl.raw);
+    uint32_t phP = 0;
+
+    // K,Q rows of chunk m -> raw staging (bulk copies; bytes counted on ctl.raw)
+    auto issue_raw = [&](int m) {
+      const int t0m = m * kC, rowsm = min(kC, T - t0m);
+      if (qk_tok == kD) {  // rows of one (batch, head) are contiguous: one copy per matrix
+        if (gt == 0) {
+          tc::mbar_arrive_expect_tx(rawbar, 2u * rowsm * 256u);
+          tc::bulk_g2s(aRaw, gk + qk_base + (int64_t)t0m * qk_tok, rowsm * 256u, rawbar);
+          tc::bulk_g2s(aRaw + 64 * 256, gq + qk_base + (int64_t)t0m * qk_tok, rowsm * 256u, rawbar);
         }
-        float mul = which == 0 ? 1.f : p.scale;
-        if (p.l2norm) {
-          ss += __shfl_xor_sync(0xffffffffu, ss, 1);
-          mul = mul / (sqrtf(ss) + 1e-6f);
-        }
-        const int row = which == 0 ? r : 64 + r;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[j]);
-          uint4 out;
-          uint32_t* o32 = reinterpret_cast<uint32_t*>(&out);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 f = __bfloat1622float2(h2[e]);
-            o32[e] = tc::pack_bf16(f.x * mul, f.y * mul);
-          }
-          *reinterpret_cast<uint4*>(sQK + tc::core_off(row, 64 * half + 8 * j, QK_RBS)) = out;
+      } else if (warp == 0) {  // strided rows: one 256-byte copy per row
+        if (lane == 0) tc::mbar_arrive_expect_tx(rawbar, 2u * rowsm * 256u);
+        __syncwarp();
+        for (int r = lane; r < rowsm; r += 32) {
+          tc::bulk_g2s(aRaw + r * 256, gk + qk_base + (int64_t)(t0m + r) * qk_tok, 256u, rawbar);
+          tc::bulk_g2s(aRaw + 64 * 256 + r * 256, gq + qk_base + (int64_t)(t0m + r) * qk_tok, 256u, rawbar);
         }
       }
-      // V rows: 64 rows x 256 B; thread handles 8 x 16 B of row r, half
+    };
+    // V rows of chunk m -> core-matrix tile, 16 bytes per cp.async; thread -> (row in block, k-block)
+    auto issue_v = [&](int m) {
+      const int t0m = m * kC, rowsm = min(kC, T - t0m);
+      const int rin = gt & 7, kb = (gt >> 3) & 15, rbh = gt >> 7;
+#pragma unroll
+      for (int rb2 = 0; rb2 < 4; ++rb2) {
+        const int r = (2 * rb2 + rbh) * 8 + rin;
+        const bool live = r < rowsm;
+        const __nv_bfloat16* src = gv + qk_base + (int64_t)(t0m + (live ? r : 0)) * qk_tok + kb * 8;
+        tc::cp_async16(tc::smem_u32(sV + tc::core_off(r, kb * 8, RBS)), src, live);
+      }
+      tc::cp_async_commit();
+    };
+
+    for (int i = gt; i < 64 * LDT; i += kGroup) sT32[i] = 0.f;
+    float g_next = 0.f, b_next = 0.f;
+    if (nchunks > 0) {
+      issue_raw(0);
+      issue_v(0);
+      if (gt < 64 && gt < min(kC, T)) {
+        b_next = p.beta[s_base + (int64_t)gt * s_tok];
+        g_next = gg ? gg[s_base + (int64_t)gt * s_tok] : 0.f;
+      }
+    }
+    PROF_DECL
+    for (int n = 0; n < nchunks; ++n) {
+      const int s = n & 1;
+      uint8_t* st = smem + s * STAGE_BYTES;
+      uint8_t* sQK = st + ST_QK;
+      uint8_t* sWt = st + ST_W;
+      uint8_t* sAqk = st + ST_AQK;
+      float* sG = reinterpret_cast<float*>(st + ST_SC);
+      float* sEG = sG + 64;
+      float* sWd = sG + 128;
+      float* sBeta = sG + 192;
+      const int t0 = n * kC;
+      const int rows = min(kC, T - t0);
+      if (n >= 2) wait_bar(&ctl.empty[s], ((n >> 1) - 1) & 1);
+      PROF(0);
+      if (gt < 64) {
+        sBeta[gt] = b_next;
+        sG[gt] = g_next;
+      }
+      wait_bar(&ctl.raw, n & 1);
+      PROF(1);
+      // ---- fp32 l2norm of the K,Q rows; write the [K^;Q^] core-matrix tile ------------------------------
       {
-        const __nv_bfloat16* src = gv + qk_base + (int64_t)(t0 + r) * qk_tok + 64 * half;
+        const int m = hs;  // warps 0-3: K rows, warps 4-7: Q rows
+        const int rin = l128 & 7, kbq = (l128 >> 3) & 3, w4 = l128 >> 5;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint4 x = live ? reinterpret_cast<const uint4*>(src)[j] : make_uint4(0, 0, 0, 0);
-          reinterpret_cast<uint4*>(sV + r * kD + 64 * half)[j] = x;
+        for (int rbl = 0; rbl < 2; ++rbl) {
+          const int row = 8 * (2 * w4 + rbl) + rin;
+          const bool live = row < rows;
+          uint4 c[4];
+          float ss = 0.f;
+#pragma unroll
+          for (int it = 0; it < 4; ++it) {
+            const int kb = 4 * it + kbq;
+            c[it] = live ? *reinterpret_cast<const uint4*>(sRaw + m * 64 * 256 + row * 256 + kb * 16)
+                         : make_uint4(0, 0, 0, 0);
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&c[it]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = __bfloat1622float2(h2[e]);
+              ss += f.x * f.x + f.y * f.y;
+            }
+          }
+          float mul = m == 0 ? 1.f : p.scale;
+          if (p.l2norm) {
+            ss += __shfl_xor_sync(0xffffffffu, ss, 8);
+            ss += __shfl_xor_sync(0xffffffffu, ss, 16);
+            mul = mul / (sqrtf(ss) + 1e-6f);
+          }
+#pragma unroll
+          for (int it = 0; it < 4; ++it) {
+            const int kb = 4 * it + kbq;
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&c[it]);
+            uint4 out;
+            uint32_t* o32 = reinterpret_cast<uint32_t*>(&out);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = __bfloat1622float2(h2[e]);
+              o32[e] = tc::pack_bf16(f.x * mul, f.y * mul);
+            }
+            *reinterpret_cast<uint4*>(sQK + tc::core_off(64 * m + row, kb * 8, RBS)) = out;
+          }
         }
       }
-      if (tid < 64) {
-        const bool lv = tid < rows;
-        sBeta[tid] = lv ? p.beta[s_base + (int64_t)(t0 + tid) * s_tok] : 0.f;
-        sG[tid] = (lv && gg) ? gg[s_base + (int64_t)(t0 + tid) * s_tok] : 0.f;
+      tc::fence_async_smem();
+      group_sync(1);
+      // raw staging is free again: prefetch the next chunk's K,Q rows and its g, beta
+      if (n + 1 < nchunks) {
+        issue_raw(n + 1);
+        g_next = 0.f; b_next = 0.f;
+        if (gt < 64 && t0 + kC + gt < T) {
+          b_next = p.beta[s_base + (int64_t)(t0 + kC + gt) * s_tok];
+          g_next = gg ? gg[s_base + (int64_t)(t0 + kC + gt) * s_tok] : 0.f;
+        }
       }
-    }
-    __syncthreads();
-    if (warp == 0) {  // inclusive scan of g over the 64 rows
-      float a = sG[lane], bq = sG[lane + 32];
+      // ---- (1) D1 = [K^;Q^] K^^T ----------------------------------------------------------------------
+      if (gt == 0) {
+        tc::tc_fence_after();
+        const uint32_t aQK = tc::smem_u32(sQK);
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const float x = __shfl_up_sync(0xffffffffu, a, o);
-        const float y = __shfl_up_sync(0xffffffffu, bq, o);
-        if (lane >= o) { a += x; bq += y; }
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t ad = tc::smem_desc(aQK + ks * 256, 128, RBS);
+          tc::mma_ss(tbase + TM_D1, ad, ad, id_n64, ks > 0);  // B = first 64 rows of the same tile
+        }
+        tc::mma_commit(tc::smem_u32(&ctl.barP));
       }
-      const float tot = __shfl_sync(0xffffffffu, a, 31);
-      bq += tot;
-      const float last = __shfl_sync(0xffffffffu, bq, 31);
-      sG[lane] = a; sG[lane + 32] = bq;
-      sEG[lane] = __expf(a); sEG[lane + 32] = __expf(bq);
-      sW[lane] = __expf(fminf(last - a, 0.f)); sW[lane + 32] = __expf(fminf(last - bq, 0.f));
-    }
-    tc::fence_async_smem();
-    tc::tc_fence_before();
-    __syncthreads();
-    // ---- P2: D1 = [K^;Q^] K^^T ------------------------------------------------------------------
-    if (tid == 0) {
+      if (warp == 1) {  // inclusive scan of g over the 64 rows (overlaps the product above)
+        float a = sG[lane], bq = sG[lane + 32];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const float x = __shfl_up_sync(0xffffffffu, a, o);
+          const float y = __shfl_up_sync(0xffffffffu, bq, o);
+          if (lane >= o) { a += x; bq += y; }
+        }
+        const float tot = __shfl_sync(0xffffffffu, a, 31);
+        bq += tot;
+        const float last = __shfl_sync(0xffffffffu, bq, 31);
+        sG[lane] = a; sG[lane + 32] = bq;
+        sEG[lane] = __expf(a); sEG[lane + 32] = __expf(bq);
+        sWd[lane] = __expf(fminf(last - a, 0.f)); sWd[lane + 32] = __expf(fminf(last - bq, 0.f));
+      }
+      group_sync(1);  // scan results visible to the whole group
+      PROF(2);
+      wait_bar(&ctl.barP, phP); phP ^= 1;
       tc::tc_fence_after();
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const uint64_t ad = tc::smem_desc(aQK + ks * 256, 128, QK_RBS);
-        tc::mma_ss(tbase + TM_D3, ad, ad, id_n64, ks > 0);  // B = first 64 rows of the same tile
-      }
-      tc::mma_commit(bar_a);
-    }
-    wait_mma();
-    // ---- P3: A_kk (fp32, rows 0..63) and A_qk (bf16 operand, rows 64..127) -----------------------
-    {
-      const int i = tid & 63;
-      const float Gi = sG[i], bi = sBeta[i];
-#pragma unroll
-      for (int c0 = 0; c0 < 64; c0 += 32) {
+      PROF(3);
+      {
+        const int i = l128 & 63, c0 = 32 * hs;
+        const float Gi = sG[i], bi = sBeta[i];
         uint32_t r[32];
-        tc::tmem_ld32(tbase + TM_D3 + lane_addr + c0, r);
+        tc::tmem_ld32(tbase + TM_D1 + lane_addr + c0, r);
         tc::tc_wait_ld();
-        if (tid < 64) {
+        if (l128 < 64) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int jj = c0 + j;
-            const float x = __uint_as_float(r[j]) * __expf(fminf(Gi - sG[jj], 0.f)) * bi;
-            sAkk[i * AKK_LD + jj] = jj < i ? x : 0.f;
+          for (int j4 = 0; j4 < 8; ++j4) {
+            float4 o4;
+            float* o = reinterpret_cast<float*>(&o4);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int jj = c0 + 4 * j4 + e;
+              const float x = __uint_as_float(r[4 * j4 + e]) * __expf(fminf(Gi - sG[jj], 0.f)) * bi;
+              o[e] = jj < i ? x : 0.f;
+            }
+            *reinterpret_cast<float4*>(sAkk + i * LDT + c0 + 4 * j4) = o4;
           }
         } else {
 #pragma unroll
@@ -247,155 +423,239 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
           }
         }
       }
-    }
-    tc::tc_fence_before();
-    __syncthreads();
-    // ---- P4: T = (I + A_kk)^-1, one column per thread (threads 0..63); state pass (all) ----------
-    if (tid < 64) {
-      float x[64];
+      tc::tc_fence_before();
+      group_sync(1);
+      PROF(4);
+      // ---- T = (I + A_kk)^-1;  Tb = T diag(beta), Tw = T diag(beta e^G) ----------------------------------
+      block_inverse_64(sAkk, sT32, gt);
+      {
+        const int rin = gt & 7, jb = (gt >> 3) & 7, rbq = gt >> 6;
+        float bj[8], bw[8];
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        float acc = (i == tid) ? 1.f : 0.f;
-        const float* arow = sAkk + i * AKK_LD;
+        for (int e = 0; e < 8; ++e) {
+          bj[e] = sBeta[8 * jb + e];
+          bw[e] = bj[e] * sEG[8 * jb + e];
+        }
 #pragma unroll
-        for (int j = 0; j < i; ++j) acc -= arow[j] * x[j];
-        x[i] = acc;
+        for (int j = 0; j < 2; ++j) {
+          const int i = 8 * (4 * j + rbq) + rin;
+          const float4 t0v = *reinterpret_cast<const float4*>(sT32 + i * LDT + 8 * jb);
+          const float4 t1v = *reinterpret_cast<const float4*>(sT32 + i * LDT + 8 * jb + 4);
+          float t[8] = {t0v.x, t0v.y, t0v.z, t0v.w, t1v.x, t1v.y, t1v.z, t1v.w};
+#pragma unroll
+          for (int e = 0; e < 8; ++e) t[e] = (8 * jb + e <= i) ? t[e] : 0.f;
+          uint4 ob, ow;
+          uint32_t* pb = reinterpret_cast<uint32_t*>(&ob);
+          uint32_t* pw = reinterpret_cast<uint32_t*>(&ow);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            pb[e] = tc::pack_bf16(t[2 * e] * bj[2 * e], t[2 * e + 1] * bj[2 * e + 1]);
+            pw[e] = tc::pack_bf16(t[2 * e] * bw[2 * e], t[2 * e + 1] * bw[2 * e + 1]);
+          }
+          const uint32_t off = tc::core_off(i, 8 * jb, A_RBS);
+          *reinterpret_cast<uint4*>(sTb + off) = ob;
+          *reinterpret_cast<uint4*>(sTw + off) = ow;
+        }
       }
+      tc::cp_async_wait_all();  // this chunk's V tile has landed
+      tc::fence_async_smem();
+      group_sync(1);
+      PROF(5);
+      // ---- (2) W^T = K^^T Tw^T -> scratch;  U^T = V^T Tb^T -> stage accumulator ---------------------------
+      if (gt == 0) {
+        tc::tc_fence_after();
+        const uint32_t aV = tc::smem_u32(sV), aK = tc::smem_u32(sQK);
+        const uint32_t aTb = tc::smem_u32(sTb), aTw = tc::smem_u32(sTw);
 #pragma unroll
-      for (int i = 0; i < 64; ++i)
-        *reinterpret_cast<__nv_bfloat16*>(sT + tc::core_off(i, tid, A_RBS)) = __float2bfloat16_rn(x[i]);
-    }
-    {
-      // S^T: bf16 copy of the undecayed state for (2); fp32 master pre-multiplied by e^{G_L} for (5)
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint64_t ad = tc::smem_desc(aK + ks * 2 * RBS, RBS, 128);   // MN-major, 16 chunk rows per step
+          const uint64_t bd = tc::smem_desc(aTw + ks * 256, 128, A_RBS);
+          tc::mma_ss(tbase + TM_D1, ad, bd, id_n64_amn, ks > 0);
+        }
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint64_t ad = tc::smem_desc(aV + ks * 2 * RBS, RBS, 128);
+          const uint64_t bd = tc::smem_desc(aTb + ks * 256, 128, A_RBS);
+          tc::mma_ss(tbase + TM_DU + 64 * s, ad, bd, id_n64_amn, ks > 0);
+        }
+        tc::mma_commit(tc::smem_u32(&ctl.barP));
+      }
+      wait_bar(&ctl.barP, phP); phP ^= 1;
       tc::tc_fence_after();
-      const float gl = sEG[63];
-#pragma unroll
-      for (int c0 = 0; c0 < kD; c0 += 32) {
-        uint32_t r[32], pk[16];
-        tc::tmem_ld32(tbase + TM_S + lane_addr + c0, r);
+      PROF(6);
+      if (n + 1 < nchunks) issue_v(n + 1);  // the V tile is free again
+      // ---- W^T[k][c] (lane = k) -> bf16 tile W[c][k] (K-major B operand of (3)) ----------------------------
+      {
+        const int c0 = 32 * hs;
+        uint32_t r[32];
+        tc::tmem_ld32(tbase + TM_D1 + lane_addr + c0, r);
         tc::tc_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 16; ++j) pk[j] = tc::pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+        for (int j = 0; j < 32; ++j)
+          *reinterpret_cast<__nv_bfloat16*>(sWt + tc::core_off(c0 + j, l128, RBS)) = __float2bfloat16_rn(__uint_as_float(r[j]));
+      }
+      tc::fence_async_smem();
+      tc::tc_fence_before();
+      mbar_arrive(tc::smem_u32(&ctl.full[s]));
+      PROF(7);
+    }
+  } else {
+    // =========================== CONSUMER ===========================================================
+    __nv_bfloat16* go = reinterpret_cast<__nv_bfloat16*>(p.o);
+    uint32_t ph1 = 0, ph2 = 0;
+    // initial state: S^T[v][k] = h0[k][v] (thread = value column v, half of the key columns)
+    {
+      const float* h0 = p.h0 ? p.h0 + (int64_t)unit * kD * kD : nullptr;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * gl);
-        tc::tmem_st16(tbase + TM_SB + lane_addr + c0 / 2, pk);
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c0 = 64 * hs + 32 * cc;
+        uint32_t r[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = h0 ? __float_as_uint(h0[(c0 + j) * kD + l128]) : 0u;
         tc::tmem_st32(tbase + TM_S + lane_addr + c0, r);
       }
       tc::tc_wait_st();
     }
-    tc::fence_async_smem();
-    tc::tc_fence_before();
-    __syncthreads();
-    // ---- P5: D2 = S^T [K^;Q^]^T --------------------------------------------------------------------
-    if (tid == 0) {
+    // O^T of chunk m: e^{G_i} Dq + Do -> staging tile (the stage's W region, no longer needed)
+    // -> coalesced store; then releases stage m&1 to the producer.
+    auto final_epilogue = [&](int m) {
+      const int sm_ = m & 1;
+      uint8_t* stm = smem + sm_ * STAGE_BYTES;
+      const float* sEGm = reinterpret_cast<const float*>(stm + ST_SC) + 64;
+      __nv_bfloat16* sO = reinterpret_cast<__nv_bfloat16*>(stm + ST_W);
+      const int t0m = m * kC;
+      const int rowsm = min(kC, T - t0m);
+      {
+        const int c0 = 32 * hs;
+        uint32_t rq[32], ro[32];
+        tc::tmem_ld32(tbase + TM_DQ + lane_addr + c0, rq);
+        tc::tmem_ld32(tbase + TM_DU + 64 * sm_ + lane_addr + c0, ro);
+        tc::tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int i = c0 + j;
+          sO[i * kD + l128] = __float2bfloat16_rn(sEGm[i] * __uint_as_float(rq[j]) + __uint_as_float(ro[j]));
+        }
+      }
+      tc::tc_fence_before();
+      group_sync(2);
+      const int r = gt >> 2, qtr = gt & 3;
+      if (r < rowsm) {
+        __nv_bfloat16* dst = go + qk_base + (int64_t)(t0m + r) * qk_tok + 32 * qtr;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          reinterpret_cast<uint4*>(dst)[j] = reinterpret_cast<const uint4*>(sO + r * kD + 32 * qtr)[j];
+      }
+      mbar_arrive(tc::smem_u32(&ctl.empty[sm_]));
+    };
+
+    PROF_DECL
+    for (int n = 0; n < nchunks; ++n) {
+      const int s = n & 1;
+      uint8_t* st = smem + s * STAGE_BYTES;
+      const uint32_t aQK = tc::smem_u32(st + ST_QK), aW = tc::smem_u32(st + ST_W), aAqk = tc::smem_u32(st + ST_AQK);
+      const float* sEG = reinterpret_cast<const float*>(st + ST_SC) + 64;
+      const float* sWd = sEG + 64;
+      wait_bar(&ctl.full[s], (n >> 1) & 1);
       tc::tc_fence_after();
+      PROF(16);
+      // ---- state pass: bf16 copy of S^T for the products; fp32 master pre-multiplied by e^{G_L} --------
+      {
+        const float gl = sEG[63];
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const uint64_t bd = tc::smem_desc(aQK + ks * 256, 128, QK_RBS);
-        tc::mma_ts(tbase + TM_D2, tbase + TM_SB + ks * 8, bd, id_n128, ks > 0);
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c0 = 64 * hs + 32 * cc;
+          uint32_t r[32], pk[16];
+          tc::tmem_ld32(tbase + TM_S + lane_addr + c0, r);
+          tc::tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) pk[j] = tc::pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * gl);
+          tc::tmem_st16(tbase + TM_SB + lane_addr + c0 / 2, pk);
+          tc::tmem_st32(tbase + TM_S + lane_addr + c0, r);
+        }
+        tc::tc_wait_st();
       }
-      tc::mma_commit(bar_a);
-    }
-    wait_mma();
-    // ---- P6: R^T[v][c] = beta_c (V[c][v] - D2[v][c] e^{G_c}) -> bf16 A operand -----------------------
+      tc::tc_fence_before();
+      group_sync(2);
+      PROF(17);
+      // ---- (3) V_new^T = U^T - S^T W^T --------------------------------------------------------------------
+      if (gt == 0) {
+        tc::tc_fence_after();
 #pragma unroll
-    for (int c0 = 0; c0 < 64; c0 += 32) {
-      uint32_t r[32], pk[16];
-      tc::tmem_ld32(tbase + TM_D2 + lane_addr + c0, r);
-      tc::tc_wait_ld();
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const int c = c0 + 2 * j;
-        const float a0 = sBeta[c] * (__bfloat162float(sV[c * kD + tid]) - __uint_as_float(r[2 * j]) * sEG[c]);
-        const float a1 = sBeta[c + 1] * (__bfloat162float(sV[(c + 1) * kD + tid]) - __uint_as_float(r[2 * j + 1]) * sEG[c + 1]);
-        pk[j] = tc::pack_bf16(a0, a1);
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t bd = tc::smem_desc(aW + ks * 256, 128, RBS);
+          tc::mma_ts(tbase + TM_DU + 64 * s, tbase + TM_SB + ks * 8, bd, id_n64_neg, 1);
+        }
+        tc::mma_commit(tc::smem_u32(&ctl.bar1));
       }
-      tc::tmem_st16(tbase + TM_RA + lane_addr + c0 / 2, pk);
-    }
-    tc::tc_wait_st();
-    tc::tc_fence_before();
-    __syncthreads();
-    // ---- P7: D3 = R^T T^T = V_new^T ---------------------------------------------------------------------
-    if (tid == 0) {
+      if (n > 0) final_epilogue(n - 1);  // overlaps (3); frees Dq and the other stage
+      tc::tc_fence_before();
+      group_sync(2);
+      PROF(18);
+      if (gt == 0) {  // Dq = S^T Q^^T   (Q^ = rows 64..127 of the tile)
+        tc::tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t bd = tc::smem_desc(aQK + 8 * RBS + ks * 256, 128, RBS);
+          tc::mma_ts(tbase + TM_DQ, tbase + TM_SB + ks * 8, bd, id_n64, ks > 0);
+        }
+      }
+      wait_bar(&ctl.bar1, ph1); ph1 ^= 1;
       tc::tc_fence_after();
+      PROF(19);
+      // ---- V_new^T -> bf16 (plain, and decayed by e^{G_L - G_c}) ---------------------------------------------
+      {
+        const int c0 = 32 * hs;
+        uint32_t r[32], pa[16], pb[16];
+        tc::tmem_ld32(tbase + TM_DU + 64 * s + lane_addr + c0, r);
+        tc::tc_wait_ld();
 #pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {
-        const uint64_t bd = tc::smem_desc(aT + ks * 256, 128, A_RBS);
-        tc::mma_ts(tbase + TM_D3, tbase + TM_RA + ks * 8, bd, id_n64, ks > 0);
+        for (int j = 0; j < 16; ++j) {
+          const float x0 = __uint_as_float(r[2 * j]), x1 = __uint_as_float(r[2 * j + 1]);
+          pa[j] = tc::pack_bf16(x0, x1);
+          pb[j] = tc::pack_bf16(x0 * sWd[c0 + 2 * j], x1 * sWd[c0 + 2 * j + 1]);
+        }
+        tc::tmem_st16(tbase + TM_VA + lane_addr + c0 / 2, pa);
+        tc::tmem_st16(tbase + TM_VB + lane_addr + c0 / 2, pb);
       }
-      tc::mma_commit(bar_a);
-    }
-    wait_mma();
-    // ---- P8: V_new^T -> bf16 (plain, and decayed by e^{G_L - G_c}) ----------------------------------------
+      tc::tc_wait_st();
+      tc::tc_fence_before();
+      group_sync(2);
+      PROF(20);
+      // ---- (5) S^T += (decayed V_new^T) K^ ;  (4) Do = V_new^T A_qk^T -------------------------------------------
+      if (gt == 0) {
+        tc::tc_fence_after();
 #pragma unroll
-    for (int c0 = 0; c0 < 64; c0 += 32) {
-      uint32_t r[32], pa[16], pb[16];
-      tc::tmem_ld32(tbase + TM_D3 + lane_addr + c0, r);
-      tc::tc_wait_ld();
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint64_t bd = tc::smem_desc(aQK + ks * 2 * RBS, RBS, 128);  // K^ MN-major
+          tc::mma_ts(tbase + TM_S, tbase + TM_VB + ks * 8, bd, id_n128_bmn, 1);
+        }
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const float x0 = __uint_as_float(r[2 * j]), x1 = __uint_as_float(r[2 * j + 1]);
-        pa[j] = tc::pack_bf16(x0, x1);
-        pb[j] = tc::pack_bf16(x0 * sW[c0 + 2 * j], x1 * sW[c0 + 2 * j + 1]);
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint64_t bd = tc::smem_desc(aAqk + ks * 256, 128, A_RBS);
+          tc::mma_ts(tbase + TM_DU + 64 * s, tbase + TM_VA + ks * 8, bd, id_n64, ks > 0);
+        }
+        tc::mma_commit(tc::smem_u32(&ctl.bar2));
       }
-      tc::tmem_st16(tbase + TM_RA + lane_addr + c0 / 2, pa);
-      tc::tmem_st16(tbase + TM_VB + lane_addr + c0 / 2, pb);
-    }
-    tc::tc_wait_st();
-    tc::tc_fence_before();
-    __syncthreads();
-    // ---- P9: D4 = V_new^T A_qk^T ;  S^T += (decayed V_new^T) K^ ----------------------------------------------
-    if (tid == 0) {
+      wait_bar(&ctl.bar2, ph2); ph2 ^= 1;
       tc::tc_fence_after();
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {
-        const uint64_t bd = tc::smem_desc(aAqk + ks * 256, 128, A_RBS);
-        tc::mma_ts(tbase + TM_D3, tbase + TM_RA + ks * 8, bd, id_n64, ks > 0);
-      }
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {
-        // K^ rows (chunk positions) are the contraction axis: MN-major, 16 rows = 2 row blocks per step
-        const uint64_t bd = tc::smem_desc(aQK + ks * 2 * QK_RBS, QK_RBS, 128);
-        tc::mma_ts(tbase + TM_S, tbase + TM_VB + ks * 8, bd, id_n128_mn, 1);
-      }
-      tc::mma_commit(bar_a);
+      PROF(21);
     }
-    wait_mma();
-    // ---- P10: O^T[v][i] = e^{G_i} D2[v][64+i] + D4[v][i]; stage through shared memory ------------------------
+    if (nchunks > 0) final_epilogue(nchunks - 1);
+    // final state: hT[k][v] = S^T[v][k]
+    if (p.hT) {
+      float* hT = p.hT + (int64_t)unit * kD * kD;
 #pragma unroll
-    for (int c0 = 0; c0 < 64; c0 += 32) {
-      uint32_t r2[32], r4[32];
-      tc::tmem_ld32(tbase + TM_D2 + lane_addr + 64 + c0, r2);
-      tc::tmem_ld32(tbase + TM_D3 + lane_addr + c0, r4);
-      tc::tc_wait_ld();
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c0 = 64 * hs + 32 * cc;
+        uint32_t r[32];
+        tc::tmem_ld32(tbase + TM_S + lane_addr + c0, r);
+        tc::tc_wait_ld();
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int i = c0 + j;
-        sV[i * kD + tid] = __float2bfloat16_rn(sEG[i] * __uint_as_float(r2[j]) + __uint_as_float(r4[j]));
+        for (int j = 0; j < 32; ++j) hT[(c0 + j) * kD + l128] = __uint_as_float(r[j]);
       }
-    }
-    tc::tc_fence_before();
-    __syncthreads();
-    {
-      const int r = tid >> 1, half = tid & 1;
-      if (r < rows) {
-        __nv_bfloat16* dst = go + qk_base + (int64_t)(t0 + r) * qk_tok + 64 * half;
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          reinterpret_cast<uint4*>(dst)[j] = reinterpret_cast<const uint4*>(sV + r * kD + 64 * half)[j];
-      }
-    }
-  }
-  // ---- final state: hT[k][v] = S^T[v][k] ---------------------------------------------------------------
-  tc::tc_fence_after();
-  if (p.hT) {
-    float* hT = p.hT + (int64_t)unit * kD * kD;
-    for (int c0 = 0; c0 < kD; c0 += 32) {
-      uint32_t r[32];
-      tc::tmem_ld32(tbase + TM_S + lane_addr + c0, r);
-      tc::tc_wait_ld();
-#pragma unroll
-      for (int j = 0; j < 32; ++j) hT[(c0 + j) * kD + tid] = __uint_as_float(r[j]);
     }
   }
   tc::tc_fence_before();

@@ -39,13 +39,48 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false when the limit ran out; the caller records it and carries on
 // with uniform control flow (no trap, no endless spin).
+// try_wait suspends the thread in hardware until the phase completes or a short system time
+// limit passes, so a waiting warp does not compete for issue slots or shared-memory bandwidth.
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded both in attempts and in time (about a second of SM clock), whichever ends first.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t limit) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t_start = clock64();
   for (uint32_t i = 0; i < limit; ++i) {
-    if (mbar_test(bar, parity)) return true;
-    if (i > 64) __nanosleep(40);
+    if (mbar_try(bar, parity)) return true;
+    if (clock64() - t_start > 2000000000ll) return false;
   }
   return false;
 }
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+// ---- asynchronous copies global -> shared -------------------------------------------------------
+// 1-D bulk copy (TMA engine, no tensor map): size and both addresses multiples of 16 bytes;
+// completion is counted in bytes on the mbarrier.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+// 16-byte per-thread asynchronous copy (scatter into a tiled layout); zero-fills when !valid.
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src, bool valid) {
+  const uint32_t sz = valid ? 16u : 0u;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 // ---- proxies and tcgen05 fences -----------------------------------------------------------
 __device__ __forceinline__ void fence_async_smem() {

@@ -18,24 +18,28 @@ def _rel(a, b):
     return ((a - b).abs().max() / b.abs().max().clamp_min(1e-30)).item()
 
 
-@pytest.mark.parametrize("a_tmem", [0, 1])
+@pytest.mark.parametrize("a_tmem", [0, 1, 2, 5, 6, 8])
 @pytest.mark.parametrize("b_mn", [0, 1])
 @pytest.mark.parametrize("kd,n", [(128, 64), (128, 128), (64, 64), (64, 128)])
 def test_umma_plumbing(a_tmem, b_mn, kd, n):
     g = torch.Generator(device="cpu").manual_seed(kd + n + 2 * a_tmem + b_mn)
+    # a_tmem: 0 A in smem K-major, 1 A in TMEM, 2 A in smem MN-major; +4 sets the negate-A flag;
+    # +8 runs M = 64 (only the first 64 rows of A and D are meaningful)
     A = torch.randn(128, kd, generator=g).bfloat16().cuda()
     B = torch.randn(n, kd, generator=g).bfloat16().cuda()
     Bsrc = B.t().contiguous() if b_mn else B
+    Asrc = A.t().contiguous() if (a_tmem & 3) == 2 else A
     D = torch.full((128, n), float("nan"), device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     vp = lambda t: ctypes.c_void_p(t.data_ptr())
-    st = _lib.load().dr_debug_umma_selftest(vp(A), vp(Bsrc), vp(D), kd, n, a_tmem, b_mn, vp(status),
+    st = _lib.load().dr_debug_umma_selftest(vp(Asrc), vp(Bsrc), vp(D), kd, n, a_tmem, b_mn, vp(status),
                                             ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     _lib.check(st, "dr_debug_umma_selftest")
     torch.cuda.synchronize()
     assert status.item() == 0, "a bounded mbarrier wait ran out"
-    ref = A.float() @ B.float().t()
-    assert (D - ref).abs().max().item() <= 1e-3 * max(1.0, ref.abs().max().item())
+    ref = A.float() @ B.float().t() * (-1.0 if a_tmem & 4 else 1.0)
+    rows = 64 if a_tmem & 8 else 128
+    assert (D[:rows] - ref[:rows]).abs().max().item() <= 1e-3 * max(1.0, ref.abs().max().item())
 
 
 def _truth(variant, inp):
