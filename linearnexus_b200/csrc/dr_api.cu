@@ -54,6 +54,7 @@ dr::FwdParams make_fwd(const DrDesc* d, const void* q, const void* k, const void
   dr::FwdParams p;
   p.q = q; p.k = k; p.v = v; p.g = g; p.beta = beta; p.h0 = h0; p.o = o; p.hT = hT;
   p.status = status;
+  p.ckpt = nullptr;
   p.map.B = d->B; p.map.H = d->H; p.map.T = d->T; p.map.bthd = d->layout == DR_LAYOUT_BTHD;
   p.K = d->K; p.V = d->V; p.C = d->chunk;
   p.variant = d->variant; p.qkv_dt = d->qkv_dtype; p.g_dt = d->g_dtype; p.out_dt = d->out_dtype;

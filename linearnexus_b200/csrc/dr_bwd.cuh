@@ -1,7 +1,555 @@
-// placeholder until the backward lands
+// Backward of the chunkwise delta rule (DeltaNet / Gated DeltaNet / KDA), fp32 on the CUDA cores.
+//
+// The reference has no backward function (its gradients are autodiff through the chunk
+// functions); this is the hand-derived chunk-form adjoint.  Per chunk, with S0 the state at the
+// chunk start, dS1 the incoming state gradient, G the cumulative log decay, E_ij = e^{G_i-G_j}:
+//   forward pieces   X = tril(K^K^^T.E,-1)  A = tril(Q^K^^T.E)  M = I + diag(beta) X
+//                    R = beta V - (beta K^ e^G) S0      Vn = M^-1 R
+//   adjoints         dVn = A^T dO + (K^ e^{G_L-G}) dS1          dR = M^-T dVn
+//                    dV = beta dR                               dA = tril(dO Vn^T)
+//                    dM = -dR Vn^T -> dX = beta dM (strict)     dbeta = dR.V + dM.X + dKg.K^ e^G
+//                    dQg = dO S0^T   dKg = -dR S0^T   dKt = Vn dS1^T
+//                    dQ^ = dQg e^G + (dA.E) K^
+//                    dK^ = [dKg beta e^G + (dX.E) K^]_row + [dKt e^{G_L-G} + (dA.E)^T Q^ + (dX.E)^T K^]_col
+//                    dG  = Q^.dQ^ + K^.(dK^_row - dK^_col);  dG_L += sum_i dKt.Kt + e^{G_L} <dS1,S0>
+//                    dS0 = (Q^ e^G)^T dO + e^{G_L} dS1 - (beta K^ e^G)^T dR
+//   then dg = reverse cumulative sum of dG inside the chunk, and the l2-norm / scale chain rule.
+//
+// Three launches: (1) the fp32 chunk forward with a state checkpoint per chunk, (2) the adjoint
+// kernel, one CTA per (batch, head, slice of value columns) walking the chunks backwards and
+// adding its partial dQ^, dK^, dG into fp32 accumulators (the adjoint is linear in them),
+// (3) a finalize kernel (normalisation chain rule, reverse cumulative sum, casts).
+// Workspace: checkpoints [B*H][N][K][V] | dQ^ acc [B*H][N*C][K] | dK^ acc | dG acc, all fp32.
 #pragma once
+
+#include "dr_chunk_fp32.cuh"
 #include "dr_common.cuh"
+
 namespace dr {
-inline int64_t bwd_workspace_bytes(const DrDesc*) { return DR_ERR_UNSUPPORTED; }
-inline cudaError_t launch_bwd(const DrDesc*, const void*, const void*, const void*, const void*, const float*, const float*, const void*, const float*, void*, void*, void*, float*, float*, float*, void*, cudaStream_t, int*) { return cudaErrorNotSupported; }
+
+constexpr int kBwThreads = 256;
+
+struct BwdParams {
+  const void* q; const void* k; const void* v; const void* g; const float* beta;
+  const void* d_o; const float* d_hT;
+  void* dv; float* dbeta; float* dh0;
+  const float* ckpt; float* dq_acc; float* dk_acc; float* dg_acc;
+  SeqMap map;
+  int K, V, C, N;
+  int variant, qkv_dt, g_dt, l2norm;
+  float scale;
+};
+
+struct BwdSmem {
+  int ldk, lda, ldv;
+  size_t q, k, g, x, a, v, d_o, vn, dr, s0, ds, gs, eg, wd, beta, dbeta, el, total;
+};
+
+__host__ __device__ inline BwdSmem bwd_layout(int C, int K, int VS, bool kda) {
+  BwdSmem L;
+  L.ldk = K + 4; L.lda = C + 1; L.ldv = VS + 1;
+  size_t o = 0;
+  L.q = o; o += (size_t)C * L.ldk;
+  L.k = o; o += (size_t)C * L.ldk;
+  L.g = o; o += kda ? (size_t)C * L.ldk : 0;
+  L.x = o; o += (size_t)C * L.lda;
+  L.a = o; o += (size_t)C * L.lda;
+  L.v = o; o += (size_t)C * L.ldv;
+  L.d_o = o; o += (size_t)C * L.ldv;
+  L.vn = o; o += (size_t)C * L.ldv;
+  L.dr = o; o += (size_t)C * L.ldv;
+  L.s0 = o; o += (size_t)K * L.ldv;
+  L.ds = o; o += (size_t)K * L.ldv;
+  L.gs = o; o += C; L.eg = o; o += C; L.wd = o; o += C; L.beta = o; o += C; L.dbeta = o; o += C;
+  L.el = o; o += K;
+  L.total = (o + 3) & ~(size_t)3;
+  return L;
 }
+
+template <int VS, bool KDA>
+__global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p) {
+  extern __shared__ __align__(16) float smem[];
+  const int K = p.K, V = p.V, C = p.C, T = p.map.T, N = p.N;
+  const bool gated = p.variant == DR_GATED;
+  const BwdSmem L = bwd_layout(C, K, VS, KDA);
+  float* sQ = smem + L.q;      float* sK = smem + L.k;     float* sG = smem + L.g;
+  float* sX = smem + L.x;      float* sA = smem + L.a;
+  float* sV = smem + L.v;      float* sdO = smem + L.d_o;  float* sVn = smem + L.vn;  float* sdR = smem + L.dr;
+  float* sS0 = smem + L.s0;    float* sdS = smem + L.ds;
+  float* sGs = smem + L.gs;    float* sEG = smem + L.eg;   float* sWd = smem + L.wd;
+  float* sBeta = smem + L.beta; float* sdBeta = smem + L.dbeta; float* sEL = smem + L.el;
+  const int ldk = L.ldk, lda = L.lda, ldv = L.ldv;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nvs = (V + VS - 1) / VS;
+  const int unit = blockIdx.x / nvs;
+  const int v0 = (blockIdx.x % nvs) * VS;
+  const int b = unit / p.map.H, h = unit % p.map.H;
+  const int64_t qk_base = p.map.base(b, h, K), qk_tok = p.map.tok(K);
+  const int64_t v_base = p.map.base(b, h, V), v_tok = p.map.tok(V);
+  const int64_t s_base = p.map.base(b, h, 1), s_tok = p.map.tok(1);
+  const int64_t acc_row0 = (int64_t)unit * N * C;  // first row of this unit in the [.., N*C, ..] accumulators
+
+  for (int i = tid; i < K * VS; i += kBwThreads) {
+    const int kk = i / VS, vv = i % VS;
+    sdS[kk * ldv + vv] = (p.d_hT && v0 + vv < V) ? p.d_hT[((int64_t)unit * K + kk) * V + v0 + vv] : 0.f;
+  }
+
+  for (int n = N - 1; n >= 0; --n) {
+    const int t0 = n * C;
+    const int rows = min(C, T - t0);
+    __syncthreads();
+    // ---- stage q^, k^ (fp32, normalised / scaled), g, beta, v, dO, S0 --------------------------------
+    for (int c = warp; c < C; c += kBwThreads / 32) {
+      float nq = 0.f, nk = 0.f;
+      const bool live = c < rows;
+      for (int i = lane; i < K; i += 32) {
+        float qv = 0.f, kv = 0.f, gv = 0.f;
+        if (live) {
+          qv = ld_elem(p.q, qk_base + (t0 + c) * qk_tok + i, p.qkv_dt);
+          kv = ld_elem(p.k, qk_base + (t0 + c) * qk_tok + i, p.qkv_dt);
+          if (KDA) gv = ld_elem(p.g, qk_base + (t0 + c) * qk_tok + i, p.g_dt);
+        }
+        sQ[c * ldk + i] = qv;
+        sK[c * ldk + i] = kv;
+        if (KDA) sG[c * ldk + i] = gv;
+        nq += qv * qv;
+        nk += kv * kv;
+      }
+      float qmul = p.scale, kmul = 1.f;
+      if (p.l2norm) {
+        nq = warp_sum(nq);
+        nk = warp_sum(nk);
+        qmul = p.scale / (sqrtf(nq) + 1e-6f);
+        kmul = 1.f / (sqrtf(nk) + 1e-6f);
+      }
+      __syncwarp();
+      for (int i = lane; i < K; i += 32) {
+        sQ[c * ldk + i] *= qmul;
+        sK[c * ldk + i] *= kmul;
+      }
+      if (lane == 0) {
+        sBeta[c] = live ? p.beta[s_base + (t0 + c) * s_tok] : 0.f;
+        sGs[c] = (live && gated) ? ld_elem(p.g, s_base + (t0 + c) * s_tok, p.g_dt) : 0.f;
+        sdBeta[c] = 0.f;
+      }
+    }
+    for (int i = tid; i < C * VS; i += kBwThreads) {
+      const int c = i / VS, vv = i % VS;
+      float x = 0.f, y = 0.f;
+      if (c < rows && v0 + vv < V) {
+        x = ld_elem(p.v, v_base + (t0 + c) * v_tok + v0 + vv, p.qkv_dt);
+        y = ld_elem(p.d_o, v_base + (t0 + c) * v_tok + v0 + vv, p.qkv_dt);
+      }
+      sV[c * ldv + vv] = x;
+      sdO[c * ldv + vv] = y;
+    }
+    {
+      const float* ck = p.ckpt + ((int64_t)unit * N + n) * K * V;
+      for (int i = tid; i < K * VS; i += kBwThreads) {
+        const int kk = i / VS, vv = i % VS;
+        sS0[kk * ldv + vv] = (v0 + vv < V) ? ck[(int64_t)kk * V + v0 + vv] : 0.f;
+      }
+    }
+    __syncthreads();
+    if (KDA) {
+      for (int i = tid; i < K; i += kBwThreads) {
+        float acc = 0.f;
+        for (int c = 0; c < C; ++c) {
+          acc += sG[c * ldk + i];
+          sG[c * ldk + i] = acc;
+        }
+        sEL[i] = expf(acc);
+      }
+    } else if (tid == 0) {
+      float acc = 0.f;
+      for (int c = 0; c < C; ++c) { acc += sGs[c]; sGs[c] = acc; }
+    }
+    __syncthreads();
+    if (!KDA) {
+      const float gl = sGs[C - 1];
+      for (int i = tid; i < C; i += kBwThreads) {
+        sEG[i] = expf(sGs[i]);
+        sWd[i] = expf(fminf(gl - sGs[i], 0.f));
+      }
+      for (int i = tid; i < K; i += kBwThreads) sEL[i] = expf(gl);
+    }
+    // ---- X = tril(K^K^^T.E,-1) (not yet scaled by beta), A = tril(Q^K^^T.E) ---------------------------
+    for (int pid = tid; pid < C * C; pid += kBwThreads) {
+      const int i = pid / C, j = pid % C;
+      float akk = 0.f, aqk = 0.f;
+      if (j <= i) {
+        const float4* qi = reinterpret_cast<const float4*>(sQ + i * ldk);
+        const float4* ki = reinterpret_cast<const float4*>(sK + i * ldk);
+        const float4* kj = reinterpret_cast<const float4*>(sK + j * ldk);
+        if (KDA) {
+          const float4* gi = reinterpret_cast<const float4*>(sG + i * ldk);
+          const float4* gj = reinterpret_cast<const float4*>(sG + j * ldk);
+          for (int x = 0; x < K / 4; ++x) {
+            const float4 a = qi[x], bq = ki[x], c4 = kj[x], g1 = gi[x], g2 = gj[x];
+            const float e0 = __expf(fminf(g1.x - g2.x, 0.f)), e1 = __expf(fminf(g1.y - g2.y, 0.f));
+            const float e2 = __expf(fminf(g1.z - g2.z, 0.f)), e3 = __expf(fminf(g1.w - g2.w, 0.f));
+            aqk += a.x * c4.x * e0 + a.y * c4.y * e1 + a.z * c4.z * e2 + a.w * c4.w * e3;
+            akk += bq.x * c4.x * e0 + bq.y * c4.y * e1 + bq.z * c4.z * e2 + bq.w * c4.w * e3;
+          }
+        } else {
+          for (int x = 0; x < K / 4; ++x) {
+            const float4 a = qi[x], bq = ki[x], c4 = kj[x];
+            aqk += a.x * c4.x + a.y * c4.y + a.z * c4.z + a.w * c4.w;
+            akk += bq.x * c4.x + bq.y * c4.y + bq.z * c4.z + bq.w * c4.w;
+          }
+        }
+      }
+      sA[i * lda + j] = aqk;   // GDN/DeltaNet: the decay factor is applied where the entry is used
+      sX[i * lda + j] = (j < i) ? akk : 0.f;
+    }
+    __syncthreads();
+    auto Eij = [&](int i, int j) -> float { return KDA ? 1.f : __expf(fminf(sGs[i] - sGs[j], 0.f)); };
+    // ---- R = beta V - (beta K^ e^G) S0  (lane = value column, warp = rows) ----------------------------
+    {
+      constexpr int RPW = 8;  // rows per warp pass
+      const int vv = lane % VS, sub = lane / VS;  // VS = 16: two row streams per warp
+      constexpr int STREAMS = 32 / VS;
+      for (int c = warp * STREAMS + sub; c < C; c += RPW * STREAMS) {
+        float acc = 0.f;
+        const float bc = sBeta[c];
+        for (int kk = 0; kk < K; ++kk) {
+          const float eg = KDA ? __expf(sG[c * ldk + kk]) : 1.f;
+          acc += sK[c * ldk + kk] * eg * sS0[kk * ldv + vv];
+        }
+        if (!KDA) acc *= sEG[c];
+        sVn[c * ldv + vv] = bc * (sV[c * ldv + vv] - acc);
+      }
+    }
+    __syncthreads();
+    // ---- Vn = M^-1 R : forward substitution, 8 lanes per column -----------------------------------------
+    if (tid < 8 * VS) {
+      const int col = tid >> 3, l8 = tid & 7;
+      for (int i = 1; i < C; ++i) {
+        float part = 0.f;
+        for (int j = l8; j < i; j += 8) part += sX[i * lda + j] * Eij(i, j) * sVn[j * ldv + col];
+        part += __shfl_xor_sync(0xffffffffu, part, 1);
+        part += __shfl_xor_sync(0xffffffffu, part, 2);
+        part += __shfl_xor_sync(0xffffffffu, part, 4);
+        if (l8 == 0) sVn[i * ldv + col] -= sBeta[i] * part;
+        __syncwarp();
+      }
+    }
+    __syncthreads();
+    // ---- dVn = A^T dO + (K^ e^{G_L-G}) dS1 -----------------------------------------------------------------
+    {
+      const int vv = lane % VS, sub = lane / VS;
+      constexpr int STREAMS = 32 / VS;
+      for (int c = warp * STREAMS + sub; c < C; c += 8 * STREAMS) {
+        float acc = 0.f;
+        for (int i = c; i < C; ++i) acc += sA[i * lda + c] * Eij(i, c) * sdO[i * ldv + vv];
+        float acc2 = 0.f;
+        for (int kk = 0; kk < K; ++kk) {
+          const float w = KDA ? __expf(fminf(sG[(C - 1) * ldk + kk] - sG[c * ldk + kk], 0.f)) : 1.f;
+          acc2 += sK[c * ldk + kk] * w * sdS[kk * ldv + vv];
+        }
+        if (!KDA) acc2 *= sWd[c];
+        sdR[c * ldv + vv] = acc + acc2;
+      }
+    }
+    __syncthreads();
+    // ---- dR = M^-T dVn : back substitution ---------------------------------------------------------------------
+    if (tid < 8 * VS) {
+      const int col = tid >> 3, l8 = tid & 7;
+      for (int i = C - 2; i >= 0; --i) {
+        float part = 0.f;
+        for (int j = i + 1 + l8; j < C; j += 8) part += sBeta[j] * sX[j * lda + i] * Eij(j, i) * sdR[j * ldv + col];
+        part += __shfl_xor_sync(0xffffffffu, part, 1);
+        part += __shfl_xor_sync(0xffffffffu, part, 2);
+        part += __shfl_xor_sync(0xffffffffu, part, 4);
+        if (l8 == 0) sdR[i * ldv + col] -= part;
+        __syncwarp();
+      }
+    }
+    __syncthreads();
+    // ---- dV = beta dR ; dbeta += dR.V ; dA = tril(dO Vn^T).E ; dX = beta tril(-dR Vn^T).E ; dbeta += dM.X ------
+    for (int i = tid; i < C * VS; i += kBwThreads) {
+      const int c = i / VS, vv = i % VS;
+      if (c < rows && v0 + vv < V)
+        st_elem(p.dv, v_base + (t0 + c) * v_tok + v0 + vv, p.qkv_dt, sBeta[c] * sdR[c * ldv + vv]);
+    }
+    for (int c = warp; c < C; c += 8) {
+      float acc = 0.f;
+      for (int vv = lane; vv < VS; vv += 32) acc += sdR[c * ldv + vv] * sV[c * ldv + vv];
+      acc = warp_sum(acc);
+      if (lane == 0) sdBeta[c] += acc;
+    }
+    __syncthreads();
+    for (int pid = tid; pid < C * C; pid += kBwThreads) {
+      const int i = pid / C, j = pid % C;   // a warp covers 32 consecutive j of one row i
+      float da = 0.f, dm = 0.f;
+      if (j <= i) {
+        for (int vv = 0; vv < VS; ++vv) {
+          const float vn = sVn[j * ldv + vv];
+          da += sdO[i * ldv + vv] * vn;
+          dm -= sdR[i * ldv + vv] * vn;
+        }
+      }
+      const float e = (j <= i) ? Eij(i, j) : 0.f;
+      if (j < i) atomicAdd(&sdBeta[i], dm * sX[i * lda + j] * e);
+      sA[i * lda + j] = (j <= i) ? da * e : 0.f;
+      sX[i * lda + j] = (j < i) ? sBeta[i] * dm * e : 0.f;
+    }
+    __syncthreads();
+    // ---- per (row i, channel k): dQ^, dK^, dG, dbeta; lane = channel, warp = rows ----------------------------------
+    {
+      const int nkk = K / 32 + (K % 32 ? 1 : 0);
+      float extraL[4] = {0.f, 0.f, 0.f, 0.f};  // dG_L contribution, per channel slot of this lane (K <= 128)
+      for (int i = warp; i < C; i += 8) {
+        float dgrow = 0.f, dbrow = 0.f;
+        for (int ks = 0; ks < nkk; ++ks) {
+          const int kk = lane + 32 * ks;
+          if (kk >= K) continue;
+          float dQg = 0.f, dKg = 0.f, dKt = 0.f;
+          for (int vv = 0; vv < VS; ++vv) {
+            const float s0 = sS0[kk * ldv + vv];
+            dQg += sdO[i * ldv + vv] * s0;
+            dKg -= sdR[i * ldv + vv] * s0;
+            dKt += sVn[i * ldv + vv] * sdS[kk * ldv + vv];
+          }
+          float rowA = 0.f, rowX = 0.f, colA = 0.f, colX = 0.f;
+          if (KDA) {
+            const float gi = sG[i * ldk + kk];
+            for (int j = 0; j <= i; ++j) {
+              const float e = __expf(fminf(gi - sG[j * ldk + kk], 0.f)) * sK[j * ldk + kk];
+              rowA += sA[i * lda + j] * e;
+              rowX += sX[i * lda + j] * e;
+            }
+            for (int i2 = i; i2 < C; ++i2) {
+              const float e = __expf(fminf(sG[i2 * ldk + kk] - gi, 0.f));
+              colA += sA[i2 * lda + i] * e * sQ[i2 * ldk + kk];
+              colX += sX[i2 * lda + i] * e * sK[i2 * ldk + kk];
+            }
+          } else {
+            for (int j = 0; j <= i; ++j) {
+              const float kj = sK[j * ldk + kk];
+              rowA += sA[i * lda + j] * kj;
+              rowX += sX[i * lda + j] * kj;
+            }
+            for (int i2 = i; i2 < C; ++i2) {
+              colA += sA[i2 * lda + i] * sQ[i2 * ldk + kk];
+              colX += sX[i2 * lda + i] * sK[i2 * ldk + kk];
+            }
+          }
+          const float eg = KDA ? __expf(sG[i * ldk + kk]) : sEG[i];
+          const float el = KDA ? __expf(fminf(sG[(C - 1) * ldk + kk] - sG[i * ldk + kk], 0.f)) : sWd[i];
+          const float qh = sQ[i * ldk + kk], kh = sK[i * ldk + kk];
+          const float dq = dQg * eg + rowA;
+          const float dk_row = dKg * sBeta[i] * eg + rowX;
+          const float dk_col = dKt * el + colA + colX;
+          dbrow += dKg * kh * eg;
+          const float dG = qh * dq + kh * (dk_row - dk_col);
+          extraL[ks] += dKt * kh * el;
+          const int64_t arow = acc_row0 + t0 + i;
+          atomicAdd(p.dq_acc + arow * K + kk, dq);
+          atomicAdd(p.dk_acc + arow * K + kk, dk_row + dk_col);
+          if (KDA) atomicAdd(p.dg_acc + arow * K + kk, dG);
+          else dgrow += dG;
+        }
+        dbrow = warp_sum(dbrow);
+        if (lane == 0) atomicAdd(&sdBeta[i], dbrow);
+        if (!KDA && p.dg_acc) {
+          dgrow = warp_sum(dgrow);
+          if (lane == 0) atomicAdd(p.dg_acc + acc_row0 + t0 + i, dgrow);
+        }
+      }
+      if (p.dg_acc) {
+        const int64_t lrow = acc_row0 + t0 + C - 1;
+        if (KDA) {
+          for (int ks = 0; ks < nkk; ++ks)
+            if (lane + 32 * ks < K) atomicAdd(p.dg_acc + lrow * K + lane + 32 * ks, extraL[ks]);
+        } else {
+          float e = extraL[0] + extraL[1] + extraL[2] + extraL[3];
+          e = warp_sum(e);
+          if (lane == 0) atomicAdd(p.dg_acc + lrow, e);
+        }
+      }
+    }
+    // ---- dS0 = (Q^ e^G)^T dO + e^{G_L} dS1 - (beta K^ e^G)^T dR ; dG_L += e^{G_L} <dS1, S0> -------------------------
+    float ds_new[16];
+    {
+      const int vv = lane % VS, sub = lane / VS;
+      constexpr int STREAMS = 32 / VS;
+      int slot = 0;
+      for (int kk = warp * STREAMS + sub; kk < K; kk += 8 * STREAMS, ++slot) {
+        float acc = 0.f;
+        for (int i = 0; i < C; ++i) {
+          const float eg = KDA ? __expf(sG[i * ldk + kk]) : sEG[i];
+          acc += eg * (sQ[i * ldk + kk] * sdO[i * ldv + vv] - sBeta[i] * sK[i * ldk + kk] * sdR[i * ldv + vv]);
+        }
+        const float ds1 = sdS[kk * ldv + vv];
+        float t = ds1 * sS0[kk * ldv + vv] * sEL[kk];
+        // reduce over the VS value columns of this row stream
+        for (int o = VS / 2; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (vv == 0 && p.dg_acc) {
+          const int64_t lrow = acc_row0 + t0 + C - 1;
+          if (KDA) atomicAdd(p.dg_acc + lrow * K + kk, t);
+          else atomicAdd(p.dg_acc + lrow, t);
+        }
+        ds_new[slot] = acc + sEL[kk] * ds1;
+      }
+    }
+    __syncthreads();
+    {
+      const int vv = lane % VS, sub = lane / VS;
+      constexpr int STREAMS = 32 / VS;
+      int slot = 0;
+      for (int kk = warp * STREAMS + sub; kk < K; kk += 8 * STREAMS, ++slot) sdS[kk * ldv + vv] = ds_new[slot];
+    }
+    for (int c = tid; c < rows; c += kBwThreads) atomicAdd(p.dbeta + s_base + (t0 + c) * s_tok, sdBeta[c]);
+  }
+  __syncthreads();
+  if (p.dh0) {
+    for (int i = tid; i < K * VS; i += kBwThreads) {
+      const int kk = i / VS, vv = i % VS;
+      if (v0 + vv < V) p.dh0[((int64_t)unit * K + kk) * V + v0 + vv] = sdS[kk * ldv + vv];
+    }
+  }
+}
+
+struct BwdFinalParams {
+  const void* q; const void* k;
+  void* dq; void* dk; float* dg;
+  const float* dq_acc; const float* dk_acc; const float* dg_acc;
+  SeqMap map;
+  int K, C, N, variant, qkv_dt, l2norm;
+  float scale;
+};
+
+// One CTA per (unit, chunk): normalisation/scale chain rule per row, reverse cumulative sum of dG.
+__global__ void __launch_bounds__(256) bwd_finalize_kernel(const BwdFinalParams p) {
+  const int K = p.K, C = p.C, N = p.N, T = p.map.T;
+  const int unit = blockIdx.x / N, n = blockIdx.x % N;
+  const int b = unit / p.map.H, h = unit % p.map.H;
+  const int t0 = n * C, rows = min(C, T - t0);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t qk_base = p.map.base(b, h, K), qk_tok = p.map.tok(K);
+  const int64_t s_base = p.map.base(b, h, 1), s_tok = p.map.tok(1);
+  const int64_t acc_row0 = (int64_t)unit * N * C + t0;
+  for (int c = warp; c < rows; c += 8) {
+    const float* aq = p.dq_acc + (acc_row0 + c) * K;
+    const float* ak = p.dk_acc + (acc_row0 + c) * K;
+    const int64_t grow = qk_base + (t0 + c) * qk_tok;
+    float nq = 0.f, nk = 0.f, dq_q = 0.f, dk_k = 0.f;
+    for (int i = lane; i < K; i += 32) {
+      const float qv = ld_elem(p.q, grow + i, p.qkv_dt), kv = ld_elem(p.k, grow + i, p.qkv_dt);
+      nq += qv * qv; nk += kv * kv;
+      dq_q += qv * aq[i]; dk_k += kv * ak[i];
+    }
+    nq = sqrtf(warp_sum(nq)); nk = sqrtf(warp_sum(nk));
+    dq_q = warp_sum(dq_q); dk_k = warp_sum(dk_k);
+    for (int i = lane; i < K; i += 32) {
+      float dq = p.scale * aq[i], dk = ak[i];
+      if (p.l2norm) {
+        const float qv = ld_elem(p.q, grow + i, p.qkv_dt), kv = ld_elem(p.k, grow + i, p.qkv_dt);
+        const float rq = 1.f / (nq + 1e-6f), rk = 1.f / (nk + 1e-6f);
+        // y = s x / (n + eps):  dx = s [ dy / (n + eps) - x (x.dy) / (n (n + eps)^2) ]
+        dq = p.scale * (aq[i] * rq - (nq > 0.f ? qv * dq_q * rq * rq / nq : 0.f));
+        dk = ak[i] * rk - (nk > 0.f ? kv * dk_k * rk * rk / nk : 0.f);
+      }
+      st_elem(p.dq, grow + i, p.qkv_dt, dq);
+      st_elem(p.dk, grow + i, p.qkv_dt, dk);
+    }
+  }
+  if (p.variant == DR_GATED) {
+    if (threadIdx.x == 0) {
+      float acc = 0.f;
+      for (int c = C - 1; c >= 0; --c) {
+        acc += p.dg_acc[acc_row0 + c];
+        if (c < rows) p.dg[s_base + (t0 + c) * s_tok] = acc;
+      }
+    }
+  } else if (p.variant == DR_KDA) {
+    for (int i = threadIdx.x; i < K; i += blockDim.x) {
+      float acc = 0.f;
+      for (int c = C - 1; c >= 0; --c) {
+        acc += p.dg_acc[(acc_row0 + c) * K + i];
+        if (c < rows) p.dg[qk_base + (t0 + c) * qk_tok + i] = acc;
+      }
+    }
+  }
+}
+
+inline bool bwd_supported(const DrDesc* d) {
+  return d->chunk <= 64 && d->K <= 128 && (d->variant != DR_KDA || d->K % 16 == 0);
+}
+
+inline int64_t bwd_workspace_bytes(const DrDesc* d) {
+  if (!bwd_supported(d)) return DR_ERR_UNSUPPORTED;
+  const int64_t N = (d->T + d->chunk - 1) / d->chunk;
+  const int64_t units = (int64_t)d->B * d->H;
+  const int64_t rows = units * N * d->chunk;
+  int64_t f = units * N * d->K * d->V + 2 * rows * d->K;
+  if (d->variant == DR_GATED) f += rows;
+  if (d->variant == DR_KDA) f += rows * d->K;
+  return f * (int64_t)sizeof(float);
+}
+
+inline cudaError_t launch_bwd(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
+                              const float* beta, const float* h0, const void* d_o, const float* d_hT, void* dq,
+                              void* dk, void* dv, float* dbeta, float* dg, float* dh0, void* workspace,
+                              cudaStream_t stream, int* launches) {
+  const int C = d->chunk, K = d->K, V = d->V;
+  const int64_t N = (d->T + C - 1) / C, units = (int64_t)d->B * d->H, rows = units * N * C;
+  float* ws = reinterpret_cast<float*>(workspace);
+  float* ckpt = ws;
+  float* dq_acc = ckpt + units * N * K * V;
+  float* dk_acc = dq_acc + rows * K;
+  float* dg_acc = d->variant == DR_DELTA ? nullptr : dk_acc + rows * K;
+  const size_t acc_floats = 2 * rows * K + (d->variant == DR_GATED ? rows : d->variant == DR_KDA ? rows * K : 0);
+  cudaError_t e = cudaMemsetAsync(dq_acc, 0, acc_floats * sizeof(float), stream);
+  if (e != cudaSuccess) return e;
+  const size_t nbeta = (size_t)units * d->T;
+  e = cudaMemsetAsync(dbeta, 0, nbeta * sizeof(float), stream);
+  if (e != cudaSuccess) return e;
+  // (1) forward with a state checkpoint per chunk (outputs are not wanted)
+  FwdParams f;
+  f.q = q; f.k = k; f.v = v; f.g = g; f.beta = beta; f.h0 = h0; f.o = nullptr; f.hT = nullptr; f.status = nullptr;
+  f.ckpt = ckpt;
+  f.map.B = d->B; f.map.H = d->H; f.map.T = d->T; f.map.bthd = d->layout == DR_LAYOUT_BTHD;
+  f.K = K; f.V = V; f.C = C;
+  f.variant = d->variant; f.qkv_dt = d->qkv_dtype; f.g_dt = d->g_dtype; f.out_dt = d->qkv_dtype;
+  f.l2norm = d->use_qk_l2norm; f.scale = d->scale;
+  e = launch_chunk_fp32(f, stream);
+  if (e != cudaSuccess) return e;
+  ++*launches;
+  // (2) adjoint
+  BwdParams p;
+  p.q = q; p.k = k; p.v = v; p.g = g; p.beta = beta; p.d_o = d_o; p.d_hT = d_hT;
+  p.dv = dv; p.dbeta = dbeta; p.dh0 = dh0;
+  p.ckpt = ckpt; p.dq_acc = dq_acc; p.dk_acc = dk_acc; p.dg_acc = dg_acc;
+  p.map = f.map; p.K = K; p.V = V; p.C = C; p.N = (int)N;
+  p.variant = d->variant; p.qkv_dt = d->qkv_dtype; p.g_dt = d->g_dtype; p.l2norm = d->use_qk_l2norm; p.scale = d->scale;
+  if (d->variant == DR_KDA) {
+    constexpr int VS = 16;
+    const size_t smem = bwd_layout(C, K, VS, true).total * sizeof(float);
+    e = cudaFuncSetAttribute(bwd_chunk_kernel<VS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    bwd_chunk_kernel<VS, true><<<(unsigned)(units * ((V + VS - 1) / VS)), kBwThreads, smem, stream>>>(p);
+  } else {
+    constexpr int VS = 32;
+    const size_t smem = bwd_layout(C, K, VS, false).total * sizeof(float);
+    e = cudaFuncSetAttribute(bwd_chunk_kernel<VS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    bwd_chunk_kernel<VS, false><<<(unsigned)(units * ((V + VS - 1) / VS)), kBwThreads, smem, stream>>>(p);
+  }
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  ++*launches;
+  // (3) finalize
+  BwdFinalParams fp;
+  fp.q = q; fp.k = k; fp.dq = dq; fp.dk = dk; fp.dg = dg;
+  fp.dq_acc = dq_acc; fp.dk_acc = dk_acc; fp.dg_acc = dg_acc;
+  fp.map = f.map; fp.K = K; fp.C = C; fp.N = (int)N; fp.variant = d->variant; fp.qkv_dt = d->qkv_dtype;
+  fp.l2norm = d->use_qk_l2norm; fp.scale = d->scale;
+  bwd_finalize_kernel<<<(unsigned)(units * N), 256, 0, stream>>>(fp);
+  ++*launches;
+  return cudaGetLastError();
+}
+
+}  // namespace dr

@@ -85,6 +85,13 @@ __global__ void __launch_bounds__(kCfThreads) chunk_fp32_kernel(const FwdParams 
     const int t0 = n * C;
     const int rows = min(C, T - t0);
     __syncthreads();
+    if (p.ckpt) {
+      float* ck = p.ckpt + ((int64_t)unit * nchunks + n) * K * V;
+      for (int i = tid; i < K * kCfCols; i += kCfThreads) {
+        const int kk = i / kCfCols, vv = i % kCfCols;
+        if (v0 + vv < V) ck[(int64_t)kk * V + v0 + vv] = sS[kk * ldv + vv];
+      }
+    }
     // ---- (1) stage q, k (normalised, q scaled), g, beta, beta*v -------------------------
     for (int c = warp; c < C; c += kCfThreads / 32) {
       float nq = 0.f, nk = 0.f;
@@ -244,7 +251,7 @@ __global__ void __launch_bounds__(kCfThreads) chunk_fp32_kernel(const FwdParams 
       if (c < rows) {
         float acc = oacc[r];
         for (int j = 0; j <= c; ++j) acc += sAqk[c * lda + j] * sVn[j * ldv + lane];
-        if (v0 + lane < V) st_elem(p.o, v_base + (t0 + c) * v_tok + v0 + lane, p.out_dt, acc);
+        if (p.o && v0 + lane < V) st_elem(p.o, v_base + (t0 + c) * v_tok + v0 + lane, p.out_dt, acc);
       }
     }
     // ---- (7) S <- e^{G_last} S + K~^T V_new -------------------------------------------------

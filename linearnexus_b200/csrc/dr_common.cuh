@@ -49,6 +49,7 @@ struct FwdParams {
   void* o;
   float* hT;          // null: not wanted
   int32_t* status;    // device status word or null
+  float* ckpt;        // null, or [B*H][N][K][V]: state at the start of every chunk (backward)
   SeqMap map;
   int K, V, C;
   int variant, qkv_dt, g_dt, out_dt, l2norm;

@@ -247,3 +247,107 @@ def kda_chunkwise(q, k, v, g, beta, scale=None, initial_state=None, chunk_size=6
     input dtype, as in the reference (kda.py:416,655); ``out_dtype`` (an extension) overrides it."""
     return _seq_forward("chunk", DR_KDA, q, k, v, g, beta, initial_state, scale, chunk_size, use_qk_l2norm,
                         torch.float32 if out_dtype is None else out_dtype, path)
+
+
+# ------------------------------------------------------------------------------------------
+# Backward.  The reference has no backward function: its gradients are jax.grad through the
+# chunk functions above.  `chunk_backward` is the explicit adjoint; the three `*_chunkwise`
+# ops route through torch.autograd Functions built on it whenever an input requires grad, so
+# `loss.backward()` works as `jax.grad` does on the reference.
+# ------------------------------------------------------------------------------------------
+
+_VARIANTS = {"delta": DR_DELTA, "gated": DR_GATED, "kda": DR_KDA}
+
+
+def chunk_backward(variant, q, k, v, g, beta, d_o, initial_state=None, d_final_state=None, scale=None,
+                   chunk_size=64, use_qk_l2norm=True):
+    """Gradients of sum(o * d_o) + sum(final_state * d_final_state) for ``variant`` in
+    {"delta", "gated", "kda"}.  Returns a dict: dq, dk [like q], dv [like v] in the q/k/v dtype;
+    dbeta float32 [B,H,T]; dg float32 [like g] (None for "delta"); dh0 float32 [B,H,K,V]."""
+    var = _VARIANTS[variant]
+    _require_cuda(q, k, v, g, beta, d_o, initial_state, d_final_state)
+    B, H, T, K = q.shape
+    V = v.shape[-1]
+    if scale is None:
+        scale = K ** -0.5
+    if beta.dim() == 4:
+        beta = beta.squeeze(-1)
+    dev = q.device
+    common = torch.float32 if any(t.dtype not in _NATIVE for t in (q, k, v)) or len({q.dtype, k.dtype, v.dtype}) > 1 else q.dtype
+    qn, kn, vn, don = (t.to(common).contiguous() for t in (q, k, v, d_o))
+    gn = None if g is None else _native(g).contiguous()
+    bn = beta.to(torch.float32).contiguous()
+    h0 = _state(initial_state, B, H, K, V, dev)
+    dhT = _state(d_final_state, B, H, K, V, dev)
+    d = _desc(var, DR_LAYOUT_BHTD, B, H, T, K, V, chunk_size, qn, gn, common, use_qk_l2norm, scale)
+    lib = _lib.load()
+    need = lib.dr_workspace_bytes(ctypes.byref(d), 1)
+    if need == -7:
+        raise ValueError(f"chunk_size (BT={chunk_size}) must be divisible by BC=16.")
+    _lib.check(int(need) if need < 0 else 0, "dr_workspace_bytes")
+    ws = torch.empty(int(need), dtype=torch.uint8, device=dev)
+    dq, dk, dv = torch.empty_like(qn), torch.empty_like(kn), torch.empty_like(vn)
+    dbeta = torch.empty((B, H, T), dtype=torch.float32, device=dev)
+    dg = None if g is None else torch.empty(gn.shape, dtype=torch.float32, device=dev)
+    dh0 = torch.empty((B, H, K, V), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        st = lib.dr_chunk_bwd(ctypes.byref(d), _ptr(qn), _ptr(kn), _ptr(vn), _ptr(gn), _ptr(bn), _ptr(h0), _ptr(don),
+                              _ptr(dhT), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dbeta), _ptr(dg), _ptr(dh0), _ptr(ws),
+                              ws.numel(), None, _stream(dev))
+    _lib.check(st, "dr_chunk_bwd")
+    return dict(dq=dq.to(q.dtype), dk=dk.to(k.dtype), dv=dv.to(v.dtype), dg=dg, dbeta=dbeta, dh0=dh0)
+
+
+class _ChunkFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, variant, q, k, v, g, beta, initial_state, scale, chunk_size, l2norm, out_dtype, path):
+        with torch.no_grad():
+            o, hT = _seq_forward("chunk", _VARIANTS[variant], q, k, v, g, beta, initial_state, scale, chunk_size,
+                                 l2norm, out_dtype, path)
+        ctx.save_for_backward(q, k, v, g if g is not None else q.new_empty(0), beta,
+                              initial_state if initial_state is not None else q.new_empty(0))
+        ctx.meta = (variant, scale, chunk_size, l2norm, g is not None, initial_state is not None)
+        return o, hT
+
+    @staticmethod
+    def backward(ctx, d_o, d_hT):
+        q, k, v, g, beta, h0 = ctx.saved_tensors
+        variant, scale, chunk_size, l2norm, has_g, has_h0 = ctx.meta
+        gr = chunk_backward(variant, q, k, v, g if has_g else None, beta, d_o, h0 if has_h0 else None, d_hT,
+                            scale=scale, chunk_size=chunk_size, use_qk_l2norm=l2norm)
+        dg = gr["dg"].to(g.dtype) if has_g else None
+        return (None, gr["dq"], gr["dk"], gr["dv"], dg, gr["dbeta"].reshape(beta.shape).to(beta.dtype),
+                gr["dh0"].to(h0.dtype) if has_h0 else None, None, None, None, None, None)
+
+
+def _wants_grad(*ts):
+    return torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in ts)
+
+
+_delta_chunk_nograd, _gated_chunk_nograd, _kda_chunk_nograd = delta_rule_chunkwise, gated_delta_rule_chunkwise, kda_chunkwise
+
+
+def delta_rule_chunkwise(q, k, v, beta, initial_state=None, chunk_size=64, scale=None, backend=None, path=None):  # noqa: F811
+    if _wants_grad(q, k, v, beta, initial_state):
+        return _ChunkFn.apply("delta", q, k, v, None, beta, initial_state, scale, chunk_size, False, q.dtype, path)
+    return _delta_chunk_nograd(q, k, v, beta, initial_state, chunk_size, scale, backend, path)
+
+
+def gated_delta_rule_chunkwise(q, k, v, g, beta, scale=None, initial_state=None, chunk_size=64,  # noqa: F811
+                               use_qk_l2norm=True, path=None):
+    if _wants_grad(q, k, v, g, beta, initial_state):
+        return _ChunkFn.apply("gated", q, k, v, g, beta, initial_state, scale, chunk_size, use_qk_l2norm, q.dtype, path)
+    return _gated_chunk_nograd(q, k, v, g, beta, scale, initial_state, chunk_size, use_qk_l2norm, path)
+
+
+def kda_chunkwise(q, k, v, g, beta, scale=None, initial_state=None, chunk_size=64, use_qk_l2norm=True,  # noqa: F811
+                  path=None, out_dtype=None):
+    if _wants_grad(q, k, v, g, beta, initial_state):
+        return _ChunkFn.apply("kda", q, k, v, g, beta, initial_state, scale, chunk_size, use_qk_l2norm,
+                              torch.float32 if out_dtype is None else out_dtype, path)
+    return _kda_chunk_nograd(q, k, v, g, beta, scale, initial_state, chunk_size, use_qk_l2norm, path, out_dtype)
+
+
+delta_rule_chunkwise.__doc__ = _delta_chunk_nograd.__doc__
+gated_delta_rule_chunkwise.__doc__ = _gated_chunk_nograd.__doc__
+kda_chunkwise.__doc__ = _kda_chunk_nograd.__doc__

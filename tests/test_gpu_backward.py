@@ -1,0 +1,77 @@
+"""GPU parity of the backward (dq, dk, dv, dbeta, dg, dh0) against autograd of the float64 oracle,
+which is what jax.grad of the reference functions computes."""
+import pytest
+import torch
+
+import linearnexus_b200 as L
+from linearnexus_b200 import ops
+from oracle import delta_rule_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    a, b = a.double().cpu(), b.double().cpu()
+    return ((a - b).abs().max() / b.abs().max().clamp_min(1e-30)).item()
+
+
+def _check(variant, B, H, T, K, V, C, io=torch.float32, tol=2e-4, h0_std=0.1, with_dhT=True):
+    inp = O.make_inputs(variant, B, H, T, K, V, seed=T + K + C, io_dtype=io, h0_std=h0_std)
+    if io == torch.float32:
+        inp["q"] = inp["q"] * 1.3
+        inp["k"] = inp["k"] * 0.7
+    gen = torch.Generator().manual_seed(5)
+    do = torch.randn(B, H, T, V, generator=gen).to(io)
+    dhT = torch.randn(B, H, K, V, generator=gen) * 0.1 if with_dhT else None
+    l2 = variant != "delta"
+    f = lambda x: None if x is None else x.float() if x.dtype == torch.bfloat16 else x
+    ref = O.delta_rule_grads(variant, f(inp["q"]), f(inp["k"]), f(inp["v"]), inp["g"], inp["beta"], inp["h0"], f(do), dhT,
+                             use_qk_l2norm=l2)
+    cu = lambda x: None if x is None else x.cuda()
+    got = ops.chunk_backward(variant, cu(inp["q"]), cu(inp["k"]), cu(inp["v"]), cu(inp["g"]), cu(inp["beta"]), cu(do),
+                             initial_state=cu(inp["h0"]), d_final_state=cu(dhT), chunk_size=C, use_qk_l2norm=l2)
+    torch.cuda.synchronize()
+    for name in ("dq", "dk", "dv", "dbeta", "dg", "dh0"):
+        if ref[name] is None:
+            assert got[name] is None
+            continue
+        assert got[name].shape == ref[name].shape, name
+        err = _rel(got[name], ref[name])
+        assert err <= tol, f"{variant} {name}: rel err {err}"
+    return got
+
+
+@pytest.mark.parametrize("variant", ["delta", "gated", "kda"])
+@pytest.mark.parametrize("shape", [(1, 2, 64, 32, 32, 64), (2, 2, 100, 16, 48, 32), (1, 1, 130, 64, 64, 64), (1, 2, 40, 128, 128, 16)])
+def test_backward_fp32(variant, shape):
+    _check(variant, *shape)
+
+
+def test_backward_golden_fixture(golden):
+    for name in ("delta", "gated", "kda"):
+        G = lambda key: torch.from_numpy(golden[f"{name}.{key}"]).cuda() if f"{name}.{key}" in golden.files else None
+        got = ops.chunk_backward(name, G("q"), G("k"), G("v"), G("g"), G("beta"), G("do"), initial_state=G("h0"),
+                                 d_final_state=G("dhT"), chunk_size=int(golden[f"{name}.chunk"]), use_qk_l2norm=(name != "delta"))
+        for key in ("dq", "dk", "dv", "dg", "dbeta", "dh0"):
+            if G(key) is not None:
+                assert _rel(got[key], G(key)) <= 2e-4, (name, key)
+
+
+def test_backward_bf16_headline_head_size():
+    """bf16 q,k,v,do with fp32 accumulation at d_k = d_v = 128, chunk 64 (the training configuration's head)."""
+    got = _check("gated", 1, 2, 256, 128, 128, 64, io=torch.bfloat16, tol=2e-2, h0_std=0.02)
+    assert got["dq"].dtype == torch.bfloat16 and got["dg"].dtype == torch.float32
+
+
+def test_autograd_through_the_op():
+    inp = O.make_inputs("gated", 1, 2, 96, 32, 32, seed=9, h0_std=0.1)
+    leaf = {k_: (None if v_ is None else v_.cuda().requires_grad_(True)) for k_, v_ in inp.items()}
+    o, hT = L.gated_delta_rule_chunkwise(leaf["q"], leaf["k"], leaf["v"], leaf["g"], leaf["beta"], initial_state=leaf["h0"],
+                                         chunk_size=32)
+    gen = torch.Generator().manual_seed(1)
+    do = torch.randn(o.shape, generator=gen)
+    dhT = torch.randn(hT.shape, generator=gen) * 0.1
+    ((o * do.cuda()).sum() + (hT * dhT.cuda()).sum()).backward()
+    ref = O.delta_rule_grads("gated", inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], inp["h0"], do, dhT)
+    for name, key in (("q", "dq"), ("k", "dk"), ("v", "dv"), ("g", "dg"), ("beta", "dbeta"), ("h0", "dh0")):
+        assert _rel(leaf[name].grad, ref[key]) <= 2e-4, key
