@@ -46,7 +46,8 @@ typedef enum DrStatus {
   DR_ERR_CHUNK = -7,       /* chunk size not accepted (Gated/KDA: must be a multiple of 16) */
   DR_ERR_CUDA = -8,        /* a CUDA runtime call failed; see dr_last_cuda_error() */
   DR_ERR_UNSUPPORTED = -9, /* valid request that no kernel of this build covers */
-  DR_ERR_DEVICE = -10      /* a kernel reported a problem through the status word */
+  DR_ERR_DEVICE = -10,     /* a kernel reported a problem through the status word */
+  DR_ERR_STATIC_LIMIT = -11 /* dr_chunk_bwd_static: scratch need exceeds DR_STATIC_SCRATCH_BYTES */
 } DrStatus;
 
 /* Which kernel family serves a chunk-forward call. */
@@ -146,6 +147,33 @@ int dr_chunk_bwd(const DrDesc* desc, const void* q, const void* k, const void* v
                  const float* beta, const float* h0, const void* d_o, const float* d_hT, void* dq,
                  void* dk, void* dv, float* dbeta, float* dg, float* dh0, void* workspace,
                  size_t workspace_bytes, int32_t* status_dev, void* stream);
+
+/* Size of the scratch array built into the library for dr_chunk_bwd_static: 32 MiB per GPU. */
+#define DR_STATIC_SCRATCH_BYTES (32u << 20)
+
+/*
+ * dr_chunk_bwd for callers that have no way to hand over a workspace.  It has no counterpart in
+ * the reference.  Same arguments and results as dr_chunk_bwd minus `workspace`/`workspace_bytes`:
+ * the scratch is a fixed DR_STATIC_SCRATCH_BYTES array inside the library's device image, so this
+ * entry point calls neither cudaMalloc/cudaFree nor any allocating routine.  It is meant for hosts
+ * where an allocation at call time is impossible or unwelcome: a runtime that has already claimed
+ * the whole device for its own pool (an XLA/JAX custom call gets only the buffers the compiler
+ * planned), a plug-in that must not touch the allocator of the framework it lives in, or a serving
+ * loop that may not stall on the driver's allocation lock.
+ *   - Limit: dr_workspace_bytes(desc, 1) must not exceed DR_STATIC_SCRATCH_BYTES, otherwise
+ *     DR_ERR_STATIC_LIMIT is returned and nothing is launched (use dr_chunk_bwd then).
+ *     Every GPU that loads the library keeps the 32 MiB array until the process exits.
+ *   - The first call on each device resolves the array's device address (cudaGetSymbolAddress, with
+ *     that device current); make that first call outside any stream capture.
+ *   - All calls on a device share the one array, which still holds the previous call's data when
+ *     the next one starts (everything that must start at zero is cleared by the call itself).
+ *     Two calls that overlap on the GPU -- different streams, or different host threads -- race on
+ *     it: serialise them.
+ */
+int dr_chunk_bwd_static(const DrDesc* desc, const void* q, const void* k, const void* v, const void* g,
+                        const float* beta, const float* h0, const void* d_o, const float* d_hT, void* dq,
+                        void* dk, void* dv, float* dbeta, float* dg, float* dh0, int32_t* status_dev,
+                        void* stream);
 
 /*
  * Debug entry with no counterpart in the reference: runs one 128 x n x kd bf16 product

@@ -3,6 +3,7 @@
 #include <atomic>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "deltarule_sm100.h"
 #include "dr_chunk_fp32.cuh"
@@ -99,6 +100,9 @@ const char* dr_strerror(int s) {
     case DR_ERR_CUDA: return "CUDA runtime error";
     case DR_ERR_UNSUPPORTED: return "no kernel of this build covers the request";
     case DR_ERR_DEVICE: return "a kernel reported a device-side problem";
+    case DR_ERR_STATIC_LIMIT:
+      return "the request needs more scratch than the library's built-in static buffer (DR_STATIC_SCRATCH_BYTES); "
+             "use dr_chunk_bwd with a caller-provided workspace";
     default: return "unknown status";
   }
 }
@@ -217,6 +221,64 @@ int dr_chunk_bwd(const DrDesc* d, const void* q, const void* k, const void* v, c
   int launches = 0;
   cudaError_t e = dr::launch_bwd(d, q, k, v, g, beta, h0, d_o, d_hT, dq, dk, dv, dbeta, dg, dh0,
                                  workspace, reinterpret_cast<cudaStream_t>(stream), &launches);
+  g_launches.fetch_add(launches);
+  return check_cuda(e);
+}
+
+// ---- backward without any allocation by the caller ------------------------------------------------
+// Scratch for dr_chunk_bwd_static lives in the library's own device image: a fixed-size array that
+// every GPU which loads the library carries from module load until the process exits.
+static __device__ __align__(256) unsigned char g_bwd_static_scratch[DR_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+void* g_static_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the static scratch array on the CURRENT device.  The array's name is only a
+// host-side handle; the kernels need the address the runtime resolves for this device's copy.
+int static_scratch_address(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return check_cuda(e);
+  if (dev < 0 || dev >= kMaxDevices) return DR_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (!g_static_ptr[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_bwd_static_scratch);
+    if (e != cudaSuccess) return check_cuda(e);
+    g_static_ptr[dev] = ptr;
+  }
+  *out = g_static_ptr[dev];
+  return DR_OK;
+}
+}  // namespace
+
+int dr_chunk_bwd_static(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
+                        const float* beta, const float* h0, const void* d_o, const float* d_hT, void* dq,
+                        void* dk, void* dv, float* dbeta, float* dg, float* dh0, int32_t* status_dev,
+                        void* stream) {
+  (void)status_dev;
+  int s = validate_common(d, true);
+  if (s != DR_OK) return s;
+  if (!q || !k || !v || !beta || !d_o || !dq || !dk || !dv || !dbeta) return DR_ERR_NULL;
+  if (d->variant == DR_DELTA ? (g != nullptr || dg != nullptr) : (g == nullptr || dg == nullptr))
+    return DR_ERR_VARIANT;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(d_o) || !aligned16(dq) ||
+      !aligned16(dk) || !aligned16(dv))
+    return DR_ERR_ALIGN;
+  const int64_t need = dr::bwd_workspace_bytes(d);
+  if (need < 0) return (int)need;
+  if (need > (int64_t)DR_STATIC_SCRATCH_BYTES) return DR_ERR_STATIC_LIMIT;
+  void* scratch = nullptr;
+  s = static_scratch_address(&scratch);  // first call on a device resolves the symbol; later calls reuse it
+  if (s != DR_OK) return s;
+  tl_path = "bwd_static";
+  int launches = 0;
+  // launch_bwd zeroes the accumulators it adds into and overwrites the checkpoints before reading them,
+  // so whatever an earlier call left in the array is never consumed.
+  cudaError_t e = dr::launch_bwd(d, q, k, v, g, beta, h0, d_o, d_hT, dq, dk, dv, dbeta, dg, dh0, scratch,
+                                 reinterpret_cast<cudaStream_t>(stream), &launches);
   g_launches.fetch_add(launches);
   return check_cuda(e);
 }
