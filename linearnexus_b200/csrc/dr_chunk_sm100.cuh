@@ -90,7 +90,8 @@ __device__ unsigned long long g_prof[64];
 #endif
 
 struct Ctl {
-  uint64_t full[2], empty[2], barP, bar1, bar2, raw;
+  uint64_t full[2], empty[2], late[2], barP, bar1, bar2, raw;
+  float eg_keep[2][64];  // e^G of the chunk whose output epilogue is still pending, per stage
   uint32_t tmem_base;
   int abort;
 };
@@ -194,6 +195,8 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
     tc::mbar_init(tc::smem_u32(&ctl.full[1]), kGroup);
     tc::mbar_init(tc::smem_u32(&ctl.empty[0]), kGroup);
     tc::mbar_init(tc::smem_u32(&ctl.empty[1]), kGroup);
+    tc::mbar_init(tc::smem_u32(&ctl.late[0]), kGroup);
+    tc::mbar_init(tc::smem_u32(&ctl.late[1]), kGroup);
     tc::mbar_init(tc::smem_u32(&ctl.barP), 1);
     tc::mbar_init(tc::smem_u32(&ctl.bar1), 1);
     tc::mbar_init(tc::smem_u32(&ctl.bar2), 1);
@@ -459,6 +462,8 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
       }
       tc::cp_async_wait_all();  // this chunk's V tile has landed
       tc::fence_async_smem();
+      // the stage accumulator and the W / output-staging region are released by the output epilogue
+      if (n >= 2) wait_bar(&ctl.late[s], ((n >> 1) - 1) & 1);
       group_sync(1);
       PROF(5);
       // ---- (2) W^T = K^^T Tw^T -> scratch;  U^T = V^T Tb^T -> stage accumulator ---------------------------
@@ -521,7 +526,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
     auto final_epilogue = [&](int m) {
       const int sm_ = m & 1;
       uint8_t* stm = smem + sm_ * STAGE_BYTES;
-      const float* sEGm = reinterpret_cast<const float*>(stm + ST_SC) + 64;
+      const float* sEGm = ctl.eg_keep[sm_];
       __nv_bfloat16* sO = reinterpret_cast<__nv_bfloat16*>(stm + ST_W);
       const int t0m = m * kC;
       const int rowsm = min(kC, T - t0m);
@@ -546,7 +551,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
         for (int j = 0; j < 4; ++j)
           reinterpret_cast<uint4*>(dst)[j] = reinterpret_cast<const uint4*>(sO + r * kD + 32 * qtr)[j];
       }
-      mbar_arrive(tc::smem_u32(&ctl.empty[sm_]));
+      mbar_arrive(tc::smem_u32(&ctl.late[sm_]));
     };
 
     PROF_DECL
@@ -641,8 +646,13 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
       }
       wait_bar(&ctl.bar2, ph2); ph2 ^= 1;
       tc::tc_fence_after();
+      // every product that reads this stage's tiles is complete: hand [K^;Q^], A_qk and the scalars
+      // back to the producer now; the accumulator and the W region follow after the output epilogue
+      if (gt < 64) ctl.eg_keep[s][gt] = sEG[gt];
+      mbar_arrive(tc::smem_u32(&ctl.empty[s]));
       PROF(21);
     }
+    group_sync(2);  // eg_keep of the last chunk is visible to the whole group
     if (nchunks > 0) final_epilogue(nchunks - 1);
     // final state: hT[k][v] = S^T[v][k]
     if (p.hT) {
