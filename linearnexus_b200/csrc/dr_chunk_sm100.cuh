@@ -69,13 +69,12 @@ constexpr int SM_TW = SM_TB + 64 * 64 * 2;    // T diag(beta e^G)    [64][64] bf
 constexpr int LDT = 68;                       // row stride (floats) of the fp32 64x64 matrices
 constexpr int SM_AKK = SM_TW + 64 * 64 * 2;   // A_kk fp32 [64][68]
 constexpr int SM_T32 = SM_AKK + 64 * LDT * 4; // T fp32 [64][68]
-constexpr int SM_RAW = SM_T32 + 64 * LDT * 4; // raw K rows, raw Q rows [64][128] bf16 row-major  32 KB
-constexpr int SM_TOTAL = SM_RAW + 2 * 64 * 128 * 2;
+constexpr int SM_TOTAL = SM_T32 + 64 * LDT * 4;
 
 // Optional per-phase cycle counters (CTA 0 only), compiled in with -DDR_PROFILE.
 #ifdef DR_PROFILE
-__device__ unsigned long long g_prof[64];
-#define PROF_DECL unsigned long long prof_t0 = clock64();
+__device__ unsigned long long g_prof[128];
+#define PROF_DECL unsigned long long prof_t0 = clock64(); unsigned long long wt0 = 0; (void)wt0;
 #define PROF(idx)                                              \
   do {                                                         \
     if (blockIdx.x == 0 && gt == 0) {                          \
@@ -84,14 +83,32 @@ __device__ unsigned long long g_prof[64];
       prof_t0 = prof_t;                                        \
     }                                                          \
   } while (0)
+#define WSTART wt0 = clock64()
+#define WEND(idx)                                                                   \
+  do {                                                                              \
+    if (blockIdx.x == 0 && lane == 0) atomicAdd(&g_prof[48 + idx * 8 + (warp & 7)], clock64() - wt0); \
+  } while (0)
+#define IPROF_DECL unsigned long long ip0 = clock64();
+#define IPROF(idx)                                                                           \
+  do {                                                                                       \
+    if (blockIdx.x == 0 && gt == 0) { const unsigned long long t_ = clock64(); atomicAdd(&g_prof[idx], t_ - ip0); ip0 = t_; } \
+  } while (0)
 #else
+#define IPROF_DECL
+#define IPROF(idx)
 #define PROF_DECL
 #define PROF(idx)
+#define WSTART
+#define WEND(idx)
 #endif
 
 struct Ctl {
   uint64_t full[2], empty[2], late[2], barP, bar1, bar2, raw;
-  float eg_keep[2][64];  // e^G of the chunk whose output epilogue is still pending, per stage
+  float eg_keep[2][64];  // rq_i e^{G_i} of the chunk whose output epilogue is still pending, per stage
+  float rq_keep[2][64];  // rq_i of that chunk
+  float rq[2][64];       // per stage: scale / (||q_i|| + eps)           (producer -> consumer)
+  float rk[64];          // 1 / (||k_j|| + eps)                           (producer-private)
+  float rs[64];          // beta_i rk_i^2: row factor of the unit-lower system
   uint32_t tmem_base;
   int abort;
 };
@@ -105,22 +122,27 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // substitution with 16x16 diagonal blocks, all 256 threads of the producer group.  sT receives
 // the lower triangle of T; its upper-right 32x32 quadrant is scratch; the upper-right 16x16 blocks
 // of its two diagonal 32x32 quadrants must be zero on entry and stay zero.
-__device__ __forceinline__ void block_inverse_64(const float* __restrict__ sA, float* __restrict__ sT, int gt) {
+// The system is I + diag(rs) A: rs[i] scales row i of A wherever it is read.
+__device__ __forceinline__ void block_inverse_64(const float* __restrict__ sA, const float* __restrict__ rs,
+                                                 float* __restrict__ sT, int gt) {
+  IPROF_DECL
   // diagonal blocks: one thread per column of each 16x16 block
   if (gt < 64) {
     const int o = (gt >> 4) * 16, c = gt & 15;
     float x[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      float acc = (i == c) ? 1.f : 0.f;
+      float acc = 0.f;
 #pragma unroll
-      for (int j = 0; j < i; ++j) acc -= sA[(o + i) * LDT + o + j] * x[j];
-      x[i] = acc;
+      for (int j = 0; j < i; ++j) acc += sA[(o + i) * LDT + o + j] * x[j];
+      x[i] = ((i == c) ? 1.f : 0.f) - rs[o + i] * acc;
     }
 #pragma unroll
     for (int i = 0; i < 16; ++i) sT[(o + i) * LDT + o + c] = x[i];
   }
+  IPROF(100);
   group_sync(1);
+  IPROF(101);
   // level 1: T_10 = -T_11 (A_10 T_00) and T_32 = -T_33 (A_32 T_22); thread -> 1 row x 2 columns
   {
     const int pr = gt >> 7;                     // pair 0: rows 16..31 / cols 0..15;  pair 1: rows 48..63 / cols 32..47
@@ -134,8 +156,11 @@ __device__ __forceinline__ void block_inverse_64(const float* __restrict__ sA, f
       const float2 t = *reinterpret_cast<const float2*>(sT + (c0 + k) * LDT + c0 + c2);
       a0 += a * t.x; a1 += a * t.y;
     }
-    *reinterpret_cast<float2*>(sT + row * LDT + xc + c2) = make_float2(a0, a1);
-    group_sync(1);
+    const float rsr = rs[r0 + row];
+    *reinterpret_cast<float2*>(sT + row * LDT + xc + c2) = make_float2(rsr * a0, rsr * a1);
+    IPROF(102);
+  group_sync(1);
+  IPROF(103);
     a0 = a1 = 0.f;
 #pragma unroll
     for (int k = 0; k < 16; ++k) {
@@ -145,7 +170,9 @@ __device__ __forceinline__ void block_inverse_64(const float* __restrict__ sA, f
     }
     *reinterpret_cast<float2*>(sT + (r0 + row) * LDT + c0 + c2) = make_float2(a0, a1);
   }
+  IPROF(104);
   group_sync(1);
+  IPROF(105);
   // level 2: T[32:64][0:32] = -T[32:64][32:64] (A[32:64][0:32] T[0:32][0:32]); thread -> 1 row x 4 columns
   {
     const int row = gt >> 3, c4 = (gt & 7) * 4;
@@ -157,8 +184,11 @@ __device__ __forceinline__ void block_inverse_64(const float* __restrict__ sA, f
       x0 += a * t.x; x1 += a * t.y; x2 += a * t.z; x3 += a * t.w;
     }
     // (every read of the level-1 scratch finished before the barrier above)
-    *reinterpret_cast<float4*>(sT + row * LDT + 32 + c4) = make_float4(x0, x1, x2, x3);
-    group_sync(1);
+    const float rsr = rs[32 + row];
+    *reinterpret_cast<float4*>(sT + row * LDT + 32 + c4) = make_float4(rsr * x0, rsr * x1, rsr * x2, rsr * x3);
+    IPROF(106);
+  group_sync(1);
+  IPROF(107);
     x0 = x1 = x2 = x3 = 0.f;
 #pragma unroll 8
     for (int k = 0; k < 32; ++k) {
@@ -168,7 +198,9 @@ __device__ __forceinline__ void block_inverse_64(const float* __restrict__ sA, f
     }
     *reinterpret_cast<float4*>(sT + (32 + row) * LDT + c4) = make_float4(x0, x1, x2, x3);
   }
+  IPROF(108);
   group_sync(1);
+  IPROF(109);
 }
 
 __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParams p) {
@@ -237,29 +269,35 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
     uint8_t* sTw = smem + SM_TW;
     float* sAkk = reinterpret_cast<float*>(smem + SM_AKK);
     float* sT32 = reinterpret_cast<float*>(smem + SM_T32);
-    const uint8_t* sRaw = smem + SM_RAW;
-    const uint32_t aRaw = tc::smem_u32(sRaw), rawbar = tc::smem_u32(&ctl.raw);
     uint32_t phP = 0;
 
-    // K,Q rows of chunk m -> raw staging (bulk copies; bytes counted on ctl.raw)
-    auto issue_raw = [&](int m) {
+    // K,Q rows (raw bf16), g and beta of chunk m -> tile / scalars of stage m&1, 16-byte (4-byte)
+    // cp.async per thread; thread -> (row in block, k-block).  The l2 normalisation is NOT applied
+    // to the tiles: it is folded into the epilogue factors rk, rs, rq.
+    auto issue_kq = [&](int m) {
       const int t0m = m * kC, rowsm = min(kC, T - t0m);
-      if (qk_tok == kD) {  // rows of one (batch, head) are contiguous: one copy per matrix
-        if (gt == 0) {
-          tc::mbar_arrive_expect_tx(rawbar, 2u * rowsm * 256u);
-          tc::bulk_g2s(aRaw, gk + qk_base + (int64_t)t0m * qk_tok, rowsm * 256u, rawbar);
-          tc::bulk_g2s(aRaw + 64 * 256, gq + qk_base + (int64_t)t0m * qk_tok, rowsm * 256u, rawbar);
-        }
-      } else if (warp == 0) {  // strided rows: one 256-byte copy per row
-        if (lane == 0) tc::mbar_arrive_expect_tx(rawbar, 2u * rowsm * 256u);
-        __syncwarp();
-        for (int r = lane; r < rowsm; r += 32) {
-          tc::bulk_g2s(aRaw + r * 256, gk + qk_base + (int64_t)(t0m + r) * qk_tok, 256u, rawbar);
-          tc::bulk_g2s(aRaw + 64 * 256 + r * 256, gq + qk_base + (int64_t)(t0m + r) * qk_tok, 256u, rawbar);
-        }
+      uint8_t* stm = smem + (m & 1) * STAGE_BYTES;
+      uint8_t* dQK = stm + ST_QK;
+      float* dG = reinterpret_cast<float*>(stm + ST_SC);
+      const int rin = gt & 7, kb = (gt >> 3) & 15, rbh = gt >> 7;
+#pragma unroll
+      for (int rb2 = 0; rb2 < 4; ++rb2) {
+        const int r = (2 * rb2 + rbh) * 8 + rin;
+        const bool live = r < rowsm;
+        const int64_t off = qk_base + (int64_t)(t0m + (live ? r : 0)) * qk_tok + kb * 8;
+        tc::cp_async16(tc::smem_u32(dQK + tc::core_off(r, kb * 8, RBS)), gk + off, live);
+        tc::cp_async16(tc::smem_u32(dQK + tc::core_off(64 + r, kb * 8, RBS)), gq + off, live);
       }
+      if (gt < 128) {
+        const int r = gt & 63;
+        const bool live = r < rowsm;
+        const int64_t off = s_base + (int64_t)(t0m + (live ? r : 0)) * s_tok;
+        if (gt < 64) tc::cp_async4(tc::smem_u32(dG + 192 + r), p.beta + off, live);          // beta
+        else tc::cp_async4(tc::smem_u32(dG + r), gg ? gg + off : p.beta + off, live && gg);  // g (0 without decay)
+      }
+      tc::cp_async_commit();
     };
-    // V rows of chunk m -> core-matrix tile, 16 bytes per cp.async; thread -> (row in block, k-block)
+    // V rows of chunk m -> core-matrix tile
     auto issue_v = [&](int m) {
       const int t0m = m * kC, rowsm = min(kC, T - t0m);
       const int rin = gt & 7, kb = (gt >> 3) & 15, rbh = gt >> 7;
@@ -274,16 +312,105 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
     };
 
     for (int i = gt; i < 64 * LDT; i += kGroup) sT32[i] = 0.f;
-    float g_next = 0.f, b_next = 0.f;
     if (nchunks > 0) {
-      issue_raw(0);
+      issue_kq(0);
       issue_v(0);
-      if (gt < 64 && gt < min(kC, T)) {
-        b_next = p.beta[s_base + (int64_t)gt * s_tok];
-        g_next = gg ? gg[s_base + (int64_t)gt * s_tok] : 0.f;
-      }
     }
     PROF_DECL
+#ifdef DR_PROFILE
+    {  // fixed costs of the building blocks, measured once per CTA 0 (slots 40..)
+      group_sync(1);
+      PROF(39);
+      for (int i = 0; i < 16; ++i) group_sync(1);
+      PROF(40);
+      for (int i = 0; i < 16; ++i) {
+        uint32_t r[32];
+        tc::tmem_ld32(tbase + TM_D1 + lane_addr, r);
+        tc::tc_wait_ld();
+        if (r[0] == 0x12345u && r[31] == 0x54321u) ctl.rk[0] = 1.f;
+      }
+      PROF(41);
+      for (int i = 0; i < 16; ++i) {
+        tc::fence_async_smem();
+      }
+      PROF(42);
+      for (int i = 0; i < 16; ++i) {
+        tc::tc_fence_before();
+        group_sync(1);
+        tc::tc_fence_after();
+      }
+      PROF(43);
+      float acc = 0.f;
+      for (int i = 0; i < 16; ++i) acc += __expf(sT32[(i * 37 + gt) & 1023]);
+      if (acc == 123.f) ctl.rk[1] = acc;
+      PROF(44);
+      for (int i = gt; i < 64 * LDT; i += kGroup) sAkk[i] = 0.01f;
+      if (gt < 64) ctl.rs[gt] = 0.5f;
+      group_sync(1);
+      PROF(45);
+      for (int i = 0; i < 4; ++i) block_inverse_64(sAkk, ctl.rs, sT32, gt);
+      PROF(46);
+      {  // variants of the level-2 product loop, 8 repetitions each
+        const int row = gt >> 3, c4 = (gt & 7) * 4;
+        float x0 = 0.f, x1 = 0.f, x2 = 0.f, x3 = 0.f;
+        for (int rep = 0; rep < 8; ++rep) {
+#pragma unroll 8
+          for (int k = 0; k < 32; ++k) {
+            const float a = sAkk[(32 + row) * LDT + k];
+            const float4 t = *reinterpret_cast<const float4*>(sT32 + k * LDT + c4);
+            x0 += a * t.x; x1 += a * t.y; x2 += a * t.z; x3 += a * t.w;
+          }
+        }
+        if (x0 + x1 + x2 + x3 == 123.f) ctl.rk[2] = x0;
+        PROF(47);
+        x0 = x1 = x2 = x3 = 0.f;
+        for (int rep = 0; rep < 8; ++rep) {
+          float a[32];
+#pragma unroll
+          for (int k4 = 0; k4 < 8; ++k4) {
+            const float4 v = *reinterpret_cast<const float4*>(sAkk + (32 + row) * LDT + 4 * k4);
+            a[4 * k4] = v.x; a[4 * k4 + 1] = v.y; a[4 * k4 + 2] = v.z; a[4 * k4 + 3] = v.w;
+          }
+#pragma unroll
+          for (int k = 0; k < 32; ++k) {
+            const float4 t = *reinterpret_cast<const float4*>(sT32 + k * LDT + c4);
+            x0 += a[k] * t.x; x1 += a[k] * t.y; x2 += a[k] * t.z; x3 += a[k] * t.w;
+          }
+        }
+        if (x0 + x1 + x2 + x3 == 123.f) ctl.rk[2] = x0;
+        PROF(38);
+        // 64 threads, 4x4 register tiles
+        if (gt < 64) {
+          const int r4 = (gt >> 3) * 4, cc = (gt & 7) * 4;
+          float y[4][4] = {};
+          for (int rep = 0; rep < 8; ++rep) {
+#pragma unroll 4
+            for (int k4 = 0; k4 < 8; ++k4) {
+              float4 av[4];
+#pragma unroll
+              for (int r = 0; r < 4; ++r) av[r] = *reinterpret_cast<const float4*>(sAkk + (32 + r4 + r) * LDT + 4 * k4);
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk) {
+                const float4 t = *reinterpret_cast<const float4*>(sT32 + (4 * k4 + kk) * LDT + cc);
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                  const float a = kk == 0 ? av[r].x : kk == 1 ? av[r].y : kk == 2 ? av[r].z : av[r].w;
+                  y[r][0] += a * t.x; y[r][1] += a * t.y; y[r][2] += a * t.z; y[r][3] += a * t.w;
+                }
+              }
+            }
+          }
+          float sum = 0.f;
+#pragma unroll
+          for (int r = 0; r < 4; ++r) sum += y[r][0] + y[r][1] + y[r][2] + y[r][3];
+          if (sum == 123.f) ctl.rk[3] = sum;
+        }
+        PROF(37);
+      }
+      for (int i = gt; i < 64 * LDT; i += kGroup) sT32[i] = 0.f;
+      group_sync(1);
+    }
+#endif
     for (int n = 0; n < nchunks; ++n) {
       const int s = n & 1;
       uint8_t* st = smem + s * STAGE_BYTES;
@@ -294,71 +421,12 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
       float* sEG = sG + 64;
       float* sWd = sG + 128;
       float* sBeta = sG + 192;
-      const int t0 = n * kC;
-      const int rows = min(kC, T - t0);
-      if (n >= 2) wait_bar(&ctl.empty[s], ((n >> 1) - 1) & 1);
-      PROF(0);
-      if (gt < 64) {
-        sBeta[gt] = b_next;
-        sG[gt] = g_next;
-      }
-      wait_bar(&ctl.raw, n & 1);
-      PROF(1);
-      // ---- fp32 l2norm of the K,Q rows; write the [K^;Q^] core-matrix tile ------------------------------
-      {
-        const int m = hs;  // warps 0-3: K rows, warps 4-7: Q rows
-        const int rin = l128 & 7, kbq = (l128 >> 3) & 3, w4 = l128 >> 5;
-#pragma unroll
-        for (int rbl = 0; rbl < 2; ++rbl) {
-          const int row = 8 * (2 * w4 + rbl) + rin;
-          const bool live = row < rows;
-          uint4 c[4];
-          float ss = 0.f;
-#pragma unroll
-          for (int it = 0; it < 4; ++it) {
-            const int kb = 4 * it + kbq;
-            c[it] = live ? *reinterpret_cast<const uint4*>(sRaw + m * 64 * 256 + row * 256 + kb * 16)
-                         : make_uint4(0, 0, 0, 0);
-            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&c[it]);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float2 f = __bfloat1622float2(h2[e]);
-              ss += f.x * f.x + f.y * f.y;
-            }
-          }
-          float mul = m == 0 ? 1.f : p.scale;
-          if (p.l2norm) {
-            ss += __shfl_xor_sync(0xffffffffu, ss, 8);
-            ss += __shfl_xor_sync(0xffffffffu, ss, 16);
-            mul = mul / (sqrtf(ss) + 1e-6f);
-          }
-#pragma unroll
-          for (int it = 0; it < 4; ++it) {
-            const int kb = 4 * it + kbq;
-            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&c[it]);
-            uint4 out;
-            uint32_t* o32 = reinterpret_cast<uint32_t*>(&out);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float2 f = __bfloat1622float2(h2[e]);
-              o32[e] = tc::pack_bf16(f.x * mul, f.y * mul);
-            }
-            *reinterpret_cast<uint4*>(sQK + tc::core_off(64 * m + row, kb * 8, RBS)) = out;
-          }
-        }
-      }
+      // cp.async groups complete in order; the newest one still in flight here is this chunk's V tile
+      tc::cp_async_wait_1();
       tc::fence_async_smem();
       group_sync(1);
-      // raw staging is free again: prefetch the next chunk's K,Q rows and its g, beta
-      if (n + 1 < nchunks) {
-        issue_raw(n + 1);
-        g_next = 0.f; b_next = 0.f;
-        if (gt < 64 && t0 + kC + gt < T) {
-          b_next = p.beta[s_base + (int64_t)(t0 + kC + gt) * s_tok];
-          g_next = gg ? gg[s_base + (int64_t)(t0 + kC + gt) * s_tok] : 0.f;
-        }
-      }
-      // ---- (1) D1 = [K^;Q^] K^^T ----------------------------------------------------------------------
+      PROF(0);
+      // ---- (1) D1 = [K;Q] K^T on the raw rows ------------------------------------------------------------
       if (gt == 0) {
         tc::tc_fence_after();
         const uint32_t aQK = tc::smem_u32(sQK);
@@ -369,7 +437,8 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
         }
         tc::mma_commit(tc::smem_u32(&ctl.barP));
       }
-      if (warp == 1) {  // inclusive scan of g over the 64 rows (overlaps the product above)
+      // while the product runs: decay scan (one warp) and the query norms (everyone)
+      if (warp == 1) {
         float a = sG[lane], bq = sG[lane + 32];
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -384,18 +453,46 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
         sEG[lane] = __expf(a); sEG[lane + 32] = __expf(bq);
         sWd[lane] = __expf(fminf(last - a, 0.f)); sWd[lane + 32] = __expf(fminf(last - bq, 0.f));
       }
+      {
+        const int row = gt >> 2, part = gt & 3;
+        float ss = 0.f;
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const uint4 c = *reinterpret_cast<const uint4*>(sQK + tc::core_off(64 + row, (4 * part + it) * 8, RBS));
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&c);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h2[e]);
+            ss += f.x * f.x + f.y * f.y;
+          }
+        }
+        ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+        ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+        if (part == 0) ctl.rq[s][row] = p.l2norm ? p.scale / (sqrtf(ss) + 1e-6f) : p.scale;
+      }
       group_sync(1);  // scan results visible to the whole group
       PROF(2);
       wait_bar(&ctl.barP, phP); phP ^= 1;
       tc::tc_fence_after();
       PROF(3);
+      WSTART;
       {
         const int i = l128 & 63, c0 = 32 * hs;
-        const float Gi = sG[i], bi = sBeta[i];
+        const float Gi = sG[i];
         uint32_t r[32];
         tc::tmem_ld32(tbase + TM_D1 + lane_addr + c0, r);
         tc::tc_wait_ld();
         if (l128 < 64) {
+          // X = (K K^T) . E on the raw rows, strictly lower; the row factor beta_i rk_i^2 and the column
+          // factors rk_j are applied later (rs in the solve, rk in the Tb/Tw tiles)
+          if ((i >> 5) == hs) {  // this half holds the diagonal entry ||k_i||^2
+            float d = 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) d = (c0 + j == i) ? __uint_as_float(r[j]) : d;
+            const float rk = p.l2norm ? 1.f / (sqrtf(d) + 1e-6f) : 1.f;
+            ctl.rk[i] = rk;
+            ctl.rs[i] = sBeta[i] * rk * rk;
+          }
 #pragma unroll
           for (int j4 = 0; j4 < 8; ++j4) {
             float4 o4;
@@ -403,7 +500,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const int jj = c0 + 4 * j4 + e;
-              const float x = __uint_as_float(r[4 * j4 + e]) * __expf(fminf(Gi - sG[jj], 0.f)) * bi;
+              const float x = __uint_as_float(r[4 * j4 + e]) * __expf(fminf(Gi - sG[jj], 0.f));
               o[e] = jj < i ? x : 0.f;
             }
             *reinterpret_cast<float4*>(sAkk + i * LDT + c0 + 4 * j4) = o4;
@@ -426,18 +523,36 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
           }
         }
       }
+      WEND(1);
       tc::tc_fence_before();
       group_sync(1);
       PROF(4);
-      // ---- T = (I + A_kk)^-1;  Tb = T diag(beta), Tw = T diag(beta e^G) ----------------------------------
-      block_inverse_64(sAkk, sT32, gt);
+      // prefetch the next chunk's K, Q, g, beta into the other stage (released by the consumer after the
+      // last product of chunk n-1); an empty group keeps the group count uniform on the last chunk
+      if (n + 1 < nchunks) {
+        WSTART;
+        if (n >= 1) wait_bar(&ctl.empty[(n + 1) & 1], (((n + 1) >> 1) - 1) & 1);
+        WEND(3);
+        WSTART;
+        issue_kq(n + 1);
+        WEND(4);
+      } else {
+        tc::cp_async_commit();
+      }
+      PROF(1);
+      // ---- T'' = (I + diag(rs) X)^-1;  Tb = T'' diag(beta rk), Tw = T'' diag(beta e^G rk^2) -----------------
+      WSTART;
+      block_inverse_64(sAkk, ctl.rs, sT32, gt);
+      WEND(5);
+      WSTART;
       {
         const int rin = gt & 7, jb = (gt >> 3) & 7, rbq = gt >> 6;
         float bj[8], bw[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          bj[e] = sBeta[8 * jb + e];
-          bw[e] = bj[e] * sEG[8 * jb + e];
+          const float rkj = ctl.rk[8 * jb + e];
+          bj[e] = sBeta[8 * jb + e] * rkj;
+          bw[e] = bj[e] * sEG[8 * jb + e] * rkj;
         }
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
@@ -460,10 +575,13 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
           *reinterpret_cast<uint4*>(sTw + off) = ow;
         }
       }
-      tc::cp_async_wait_all();  // this chunk's V tile has landed
+      WEND(6);
+      WSTART;
+      tc::cp_async_wait_1();  // this chunk's V tile has landed (the newest group is the next chunk's K,Q)
       tc::fence_async_smem();
       // the stage accumulator and the W / output-staging region are released by the output epilogue
       if (n >= 2) wait_bar(&ctl.late[s], ((n >> 1) - 1) & 1);
+      WEND(7);
       group_sync(1);
       PROF(5);
       // ---- (2) W^T = K^^T Tw^T -> scratch;  U^T = V^T Tb^T -> stage accumulator ---------------------------
@@ -488,6 +606,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
       wait_bar(&ctl.barP, phP); phP ^= 1;
       tc::tc_fence_after();
       PROF(6);
+      WSTART;
       if (n + 1 < nchunks) issue_v(n + 1);  // the V tile is free again
       // ---- W^T[k][c] (lane = k) -> bf16 tile W[c][k] (K-major B operand of (3)) ----------------------------
       {
@@ -500,6 +619,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
           *reinterpret_cast<__nv_bfloat16*>(sWt + tc::core_off(c0 + j, l128, RBS)) = __float2bfloat16_rn(__uint_as_float(r[j]));
       }
       tc::fence_async_smem();
+      WEND(2);
       tc::tc_fence_before();
       mbar_arrive(tc::smem_u32(&ctl.full[s]));
       PROF(7);
@@ -526,7 +646,8 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
     auto final_epilogue = [&](int m) {
       const int sm_ = m & 1;
       uint8_t* stm = smem + sm_ * STAGE_BYTES;
-      const float* sEGm = ctl.eg_keep[sm_];
+      const float* sEGm = ctl.eg_keep[sm_];   // rq_i e^{G_i}
+      const float* sRQm = ctl.rq_keep[sm_];   // rq_i = scale / (||q_i|| + eps)
       __nv_bfloat16* sO = reinterpret_cast<__nv_bfloat16*>(stm + ST_W);
       const int t0m = m * kC;
       const int rowsm = min(kC, T - t0m);
@@ -539,7 +660,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int i = c0 + j;
-          sO[i * kD + l128] = __float2bfloat16_rn(sEGm[i] * __uint_as_float(rq[j]) + __uint_as_float(ro[j]));
+          sO[i * kD + l128] = __float2bfloat16_rn(sEGm[i] * __uint_as_float(rq[j]) + sRQm[i] * __uint_as_float(ro[j]));
         }
       }
       tc::tc_fence_before();
@@ -648,7 +769,11 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
       tc::tc_fence_after();
       // every product that reads this stage's tiles is complete: hand [K^;Q^], A_qk and the scalars
       // back to the producer now; the accumulator and the W region follow after the output epilogue
-      if (gt < 64) ctl.eg_keep[s][gt] = sEG[gt];
+      if (gt < 64) {
+        const float rqi = ctl.rq[s][gt];
+        ctl.eg_keep[s][gt] = sEG[gt] * rqi;
+        ctl.rq_keep[s][gt] = rqi;
+      }
       mbar_arrive(tc::smem_u32(&ctl.empty[s]));
       PROF(21);
     }
