@@ -118,89 +118,105 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-// T = (I + A)^-1 for a strictly lower-triangular 64x64 A (fp32, row stride LDT) by blocked forward
-// substitution with 16x16 diagonal blocks, all 256 threads of the producer group.  sT receives
-// the lower triangle of T; its upper-right 32x32 quadrant is scratch; the upper-right 16x16 blocks
-// of its two diagonal 32x32 quadrants must be zero on entry and stay zero.
-// The system is I + diag(rs) A: rs[i] scales row i of A wherever it is read.
+// T = (I + diag(rs) A)^-1 for a strictly lower-triangular 64x64 A (fp32, row stride LDT).
+// 8x8 diagonal blocks by forward substitution on the CUDA cores, then three merge levels
+// (block size 8, 16, 32):  T_10 = -T_11 (diag(rs) A_10) T_00, each of the two products on the
+// warp-level tensor-core path (mma.sync m16n8k8, tf32 operands, fp32 accumulate) because these
+// tiny products are bound by shared-memory wavefronts, not flops, on the CUDA cores.
+// sT receives the lower triangle of T; entries above the diagonal are scratch (callers mask them).
+__device__ __forceinline__ uint32_t to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+template <int BS>
+__device__ __forceinline__ void inverse_merge_level(const float* __restrict__ sA, const float* __restrict__ rs,
+                                                    float* __restrict__ sT, int warp8, int lane) {
+  constexpr int MT = BS >= 16 ? BS / 16 : 1, NT = BS / 8, KS = BS / 8;
+  constexpr int TPP = MT * NT, NPAIR = 32 / BS, TILES = NPAIR * TPP;
+  const int g = lane >> 2, t = lane & 3;
+  const bool work = warp8 < TILES;
+  const int pr = work ? warp8 / TPP : 0, rem = warp8 % TPP;
+  const int mt = rem / NT, nt = rem % NT;
+  const int r0 = 2 * BS * pr + BS, c0 = 2 * BS * pr;   // block row / column origin of this pair
+  const int m0 = mt * 16 + g, m1 = m0 + 8;              // rows of this lane inside the block
+  const int n0 = nt * 8;
+  // step 1: X = diag(rs) A_10 T_00   -> scratch at the mirrored block (rows c0.., columns r0..)
+  if (work) {
+    float d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      const int k0 = ks * 8 + t, k1 = k0 + 4;
+      uint32_t a[4], b[2];
+      a[0] = to_tf32(m0 < BS ? sA[(r0 + m0) * LDT + c0 + k0] : 0.f);
+      a[1] = to_tf32(m1 < BS ? sA[(r0 + m1) * LDT + c0 + k0] : 0.f);
+      a[2] = to_tf32(m0 < BS ? sA[(r0 + m0) * LDT + c0 + k1] : 0.f);
+      a[3] = to_tf32(m1 < BS ? sA[(r0 + m1) * LDT + c0 + k1] : 0.f);
+      const int n = n0 + g;                              // T_00 is lower triangular: entry (k, n) needs n <= k
+      b[0] = to_tf32(n <= k0 ? sT[(c0 + k0) * LDT + c0 + n] : 0.f);
+      b[1] = to_tf32(n <= k1 ? sT[(c0 + k1) * LDT + c0 + n] : 0.f);
+      mma_tf32(d, a, b);
+    }
+    if (m0 < BS) {
+      const float f = rs[r0 + m0];
+      *reinterpret_cast<float2*>(sT + (c0 + m0) * LDT + r0 + n0 + 2 * t) = make_float2(f * d[0], f * d[1]);
+    }
+    if (m1 < BS) {
+      const float f = rs[r0 + m1];
+      *reinterpret_cast<float2*>(sT + (c0 + m1) * LDT + r0 + n0 + 2 * t) = make_float2(f * d[2], f * d[3]);
+    }
+  }
+  group_sync(1);
+  // step 2: T_10 = -T_11 X
+  if (work) {
+    float d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      const int k0 = ks * 8 + t, k1 = k0 + 4;
+      uint32_t a[4], b[2];
+      // T_11 is lower triangular: entry (m, k) needs k <= m
+      a[0] = to_tf32((m0 < BS && k0 <= m0) ? sT[(r0 + m0) * LDT + r0 + k0] : 0.f);
+      a[1] = to_tf32((m1 < BS && k0 <= m1) ? sT[(r0 + m1) * LDT + r0 + k0] : 0.f);
+      a[2] = to_tf32((m0 < BS && k1 <= m0) ? sT[(r0 + m0) * LDT + r0 + k1] : 0.f);
+      a[3] = to_tf32((m1 < BS && k1 <= m1) ? sT[(r0 + m1) * LDT + r0 + k1] : 0.f);
+      b[0] = to_tf32(sT[(c0 + k0) * LDT + r0 + n0 + g]);
+      b[1] = to_tf32(sT[(c0 + k1) * LDT + r0 + n0 + g]);
+      mma_tf32(d, a, b);
+    }
+    if (m0 < BS) *reinterpret_cast<float2*>(sT + (r0 + m0) * LDT + c0 + n0 + 2 * t) = make_float2(-d[0], -d[1]);
+    if (m1 < BS) *reinterpret_cast<float2*>(sT + (r0 + m1) * LDT + c0 + n0 + 2 * t) = make_float2(-d[2], -d[3]);
+  }
+  group_sync(1);
+}
+
 __device__ __forceinline__ void block_inverse_64(const float* __restrict__ sA, const float* __restrict__ rs,
                                                  float* __restrict__ sT, int gt) {
-  IPROF_DECL
-  // diagonal blocks: one thread per column of each 16x16 block
+  const int warp8 = gt >> 5, lane = gt & 31;
+  // 8x8 diagonal blocks: one thread per column of each block
   if (gt < 64) {
-    const int o = (gt >> 4) * 16, c = gt & 15;
-    float x[16];
+    const int o = (gt >> 3) * 8, c = gt & 7;
+    float x[8];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
+    for (int i = 0; i < 8; ++i) {
       float acc = 0.f;
 #pragma unroll
       for (int j = 0; j < i; ++j) acc += sA[(o + i) * LDT + o + j] * x[j];
       x[i] = ((i == c) ? 1.f : 0.f) - rs[o + i] * acc;
     }
 #pragma unroll
-    for (int i = 0; i < 16; ++i) sT[(o + i) * LDT + o + c] = x[i];
+    for (int i = 0; i < 8; ++i) sT[(o + i) * LDT + o + c] = x[i];
   }
-  IPROF(100);
   group_sync(1);
-  IPROF(101);
-  // level 1: T_10 = -T_11 (A_10 T_00) and T_32 = -T_33 (A_32 T_22); thread -> 1 row x 2 columns
-  {
-    const int pr = gt >> 7;                     // pair 0: rows 16..31 / cols 0..15;  pair 1: rows 48..63 / cols 32..47
-    const int row = (gt & 127) >> 3, c2 = (gt & 7) * 2;
-    const int r0 = 32 * pr + 16, c0 = 32 * pr;  // block row / column origin
-    const int xc = 32 + 16 * pr;                // scratch columns in the upper-right quadrant (rows 0..15)
-    float a0 = 0.f, a1 = 0.f;
-#pragma unroll
-    for (int k = 0; k < 16; ++k) {
-      const float a = sA[(r0 + row) * LDT + c0 + k];
-      const float2 t = *reinterpret_cast<const float2*>(sT + (c0 + k) * LDT + c0 + c2);
-      a0 += a * t.x; a1 += a * t.y;
-    }
-    const float rsr = rs[r0 + row];
-    *reinterpret_cast<float2*>(sT + row * LDT + xc + c2) = make_float2(rsr * a0, rsr * a1);
-    IPROF(102);
-  group_sync(1);
-  IPROF(103);
-    a0 = a1 = 0.f;
-#pragma unroll
-    for (int k = 0; k < 16; ++k) {
-      const float a = sT[(r0 + row) * LDT + r0 + k];
-      const float2 t = *reinterpret_cast<const float2*>(sT + k * LDT + xc + c2);
-      a0 -= a * t.x; a1 -= a * t.y;
-    }
-    *reinterpret_cast<float2*>(sT + (r0 + row) * LDT + c0 + c2) = make_float2(a0, a1);
-  }
-  IPROF(104);
-  group_sync(1);
-  IPROF(105);
-  // level 2: T[32:64][0:32] = -T[32:64][32:64] (A[32:64][0:32] T[0:32][0:32]); thread -> 1 row x 4 columns
-  {
-    const int row = gt >> 3, c4 = (gt & 7) * 4;
-    float x0 = 0.f, x1 = 0.f, x2 = 0.f, x3 = 0.f;
-#pragma unroll 8
-    for (int k = 0; k < 32; ++k) {
-      const float a = sA[(32 + row) * LDT + k];
-      const float4 t = *reinterpret_cast<const float4*>(sT + k * LDT + c4);
-      x0 += a * t.x; x1 += a * t.y; x2 += a * t.z; x3 += a * t.w;
-    }
-    // (every read of the level-1 scratch finished before the barrier above)
-    const float rsr = rs[32 + row];
-    *reinterpret_cast<float4*>(sT + row * LDT + 32 + c4) = make_float4(rsr * x0, rsr * x1, rsr * x2, rsr * x3);
-    IPROF(106);
-  group_sync(1);
-  IPROF(107);
-    x0 = x1 = x2 = x3 = 0.f;
-#pragma unroll 8
-    for (int k = 0; k < 32; ++k) {
-      const float a = sT[(32 + row) * LDT + 32 + k];
-      const float4 t = *reinterpret_cast<const float4*>(sT + k * LDT + 32 + c4);
-      x0 -= a * t.x; x1 -= a * t.y; x2 -= a * t.z; x3 -= a * t.w;
-    }
-    *reinterpret_cast<float4*>(sT + (32 + row) * LDT + c4) = make_float4(x0, x1, x2, x3);
-  }
-  IPROF(108);
-  group_sync(1);
-  IPROF(109);
+  inverse_merge_level<8>(sA, rs, sT, warp8, lane);
+  inverse_merge_level<16>(sA, rs, sT, warp8, lane);
+  inverse_merge_level<32>(sA, rs, sT, warp8, lane);
 }
 
 __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParams p) {
