@@ -32,6 +32,10 @@
 // further waiting.
 #pragma once
 
+#include <cuda.h>
+
+#include <cstring>
+
 #include "dr_common.cuh"
 #include "dr_tcgen05.cuh"
 #include "dr_umma_selftest.cuh"
@@ -103,7 +107,7 @@ __device__ unsigned long long g_prof[128];
 #endif
 
 struct Ctl {
-  uint64_t full[2], empty[2], late[2], barP, bar1, bar2, raw;
+  uint64_t full[2], empty[2], late[2], barP, bar1, bar2, kq[2], vb;
   float eg_keep[2][64];  // rq_i e^{G_i} of the chunk whose output epilogue is still pending, per stage
   float rq_keep[2][64];  // rq_i of that chunk
   float rq[2][64];       // per stage: scale / (||q_i|| + eps)           (producer -> consumer)
@@ -219,8 +223,21 @@ __device__ __forceinline__ void block_inverse_64(const float* __restrict__ sA, c
   inverse_merge_level<32>(sA, rs, sT, warp8, lane);
 }
 
-__global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParams p) {
-  extern __shared__ __align__(128) uint8_t smem[];
+// Kernel parameters: the common forward parameters plus the TMA tensor maps.
+//   tk, tq, tv : 5-d views {8 elements, 8 rows, 16 k-blocks, T/8 row blocks, B*H} of the [B,H,T,128] bf16
+//                inputs; one box {8,8,16,8,1} lands a 64x128 chunk in shared memory already in the
+//                8x8 core-matrix order the tensor cores read (used when use_tma_in).
+//   to         : 4-d view {128, T, H, B} of the output; one box {128,64,1,1} stores a chunk's rows and
+//                clips the ragged tail (used when use_tma_out).
+struct alignas(64) Sm100Params {
+  CUtensorMap tk, tq, tv, to;
+  FwdParams p;
+  int use_tma_in, use_tma_out;
+};
+
+__global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_constant__ Sm100Params P) {
+  const FwdParams& p = P.p;
+  extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ __align__(8) Ctl ctl;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -248,7 +265,9 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
     tc::mbar_init(tc::smem_u32(&ctl.barP), 1);
     tc::mbar_init(tc::smem_u32(&ctl.bar1), 1);
     tc::mbar_init(tc::smem_u32(&ctl.bar2), 1);
-    tc::mbar_init(tc::smem_u32(&ctl.raw), 1);
+    tc::mbar_init(tc::smem_u32(&ctl.kq[0]), 1);
+    tc::mbar_init(tc::smem_u32(&ctl.kq[1]), 1);
+    tc::mbar_init(tc::smem_u32(&ctl.vb), 1);
     tc::fence_mbar_init();
     ctl.abort = 0;
   }
@@ -295,14 +314,23 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
       uint8_t* stm = smem + (m & 1) * STAGE_BYTES;
       uint8_t* dQK = stm + ST_QK;
       float* dG = reinterpret_cast<float*>(stm + ST_SC);
-      const int rin = gt & 7, kb = (gt >> 3) & 15, rbh = gt >> 7;
+      if (P.use_tma_in) {
+        if (gt == 0) {
+          const uint32_t bar = tc::smem_u32(&ctl.kq[m & 1]);
+          tc::mbar_arrive_expect_tx(bar, 2u * 64 * 256);
+          tc::tma_load_5d(tc::smem_u32(dQK), &P.tk, 0, 0, 0, m * 8, unit, bar);
+          tc::tma_load_5d(tc::smem_u32(dQK) + 64 * 256, &P.tq, 0, 0, 0, m * 8, unit, bar);
+        }
+      } else {
+        const int rin = gt & 7, kb = (gt >> 3) & 15, rbh = gt >> 7;
 #pragma unroll
-      for (int rb2 = 0; rb2 < 4; ++rb2) {
-        const int r = (2 * rb2 + rbh) * 8 + rin;
-        const bool live = r < rowsm;
-        const int64_t off = qk_base + (int64_t)(t0m + (live ? r : 0)) * qk_tok + kb * 8;
-        tc::cp_async16(tc::smem_u32(dQK + tc::core_off(r, kb * 8, RBS)), gk + off, live);
-        tc::cp_async16(tc::smem_u32(dQK + tc::core_off(64 + r, kb * 8, RBS)), gq + off, live);
+        for (int rb2 = 0; rb2 < 4; ++rb2) {
+          const int r = (2 * rb2 + rbh) * 8 + rin;
+          const bool live = r < rowsm;
+          const int64_t off = qk_base + (int64_t)(t0m + (live ? r : 0)) * qk_tok + kb * 8;
+          tc::cp_async16(tc::smem_u32(dQK + tc::core_off(r, kb * 8, RBS)), gk + off, live);
+          tc::cp_async16(tc::smem_u32(dQK + tc::core_off(64 + r, kb * 8, RBS)), gq + off, live);
+        }
       }
       if (gt < 128) {
         const int r = gt & 63;
@@ -316,13 +344,21 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
     // V rows of chunk m -> core-matrix tile
     auto issue_v = [&](int m) {
       const int t0m = m * kC, rowsm = min(kC, T - t0m);
-      const int rin = gt & 7, kb = (gt >> 3) & 15, rbh = gt >> 7;
+      if (P.use_tma_in) {
+        if (gt == 0) {
+          const uint32_t bar = tc::smem_u32(&ctl.vb);
+          tc::mbar_arrive_expect_tx(bar, 64u * 256);
+          tc::tma_load_5d(tc::smem_u32(sV), &P.tv, 0, 0, 0, m * 8, unit, bar);
+        }
+      } else {
+        const int rin = gt & 7, kb = (gt >> 3) & 15, rbh = gt >> 7;
 #pragma unroll
-      for (int rb2 = 0; rb2 < 4; ++rb2) {
-        const int r = (2 * rb2 + rbh) * 8 + rin;
-        const bool live = r < rowsm;
-        const __nv_bfloat16* src = gv + qk_base + (int64_t)(t0m + (live ? r : 0)) * qk_tok + kb * 8;
-        tc::cp_async16(tc::smem_u32(sV + tc::core_off(r, kb * 8, RBS)), src, live);
+        for (int rb2 = 0; rb2 < 4; ++rb2) {
+          const int r = (2 * rb2 + rbh) * 8 + rin;
+          const bool live = r < rowsm;
+          const __nv_bfloat16* src = gv + qk_base + (int64_t)(t0m + (live ? r : 0)) * qk_tok + kb * 8;
+          tc::cp_async16(tc::smem_u32(sV + tc::core_off(r, kb * 8, RBS)), src, live);
+        }
       }
       tc::cp_async_commit();
     };
@@ -439,6 +475,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
       float* sBeta = sG + 192;
       // cp.async groups complete in order; the newest one still in flight here is this chunk's V tile
       tc::cp_async_wait_1();
+      if (P.use_tma_in) wait_bar(&ctl.kq[s], (n >> 1) & 1);
       tc::fence_async_smem();
       group_sync(1);
       PROF(0);
@@ -594,6 +631,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
       WEND(6);
       WSTART;
       tc::cp_async_wait_1();  // this chunk's V tile has landed (the newest group is the next chunk's K,Q)
+      if (P.use_tma_in) wait_bar(&ctl.vb, n & 1);
       tc::fence_async_smem();
       // the stage accumulator and the W / output-staging region are released by the output epilogue
       if (n >= 2) wait_bar(&ctl.late[s], ((n >> 1) - 1) & 1);
@@ -680,13 +718,23 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
         }
       }
       tc::tc_fence_before();
-      group_sync(2);
-      const int r = gt >> 2, qtr = gt & 3;
-      if (r < rowsm) {
-        __nv_bfloat16* dst = go + qk_base + (int64_t)(t0m + r) * qk_tok + 32 * qtr;
+      if (P.use_tma_out) {
+        tc::fence_async_smem();
+        group_sync(2);
+        if (gt == 0) {  // one tiled store of the whole chunk; rows past T are clipped by the tensor map
+          tc::tma_store_4d(&P.to, tc::smem_u32(sO), 0, t0m, h, b);
+          tc::bulk_commit();
+          tc::bulk_wait_read_all();  // the staging tile may be overwritten after this
+        }
+      } else {
+        group_sync(2);
+        const int r = gt >> 2, qtr = gt & 3;
+        if (r < rowsm) {
+          __nv_bfloat16* dst = go + qk_base + (int64_t)(t0m + r) * qk_tok + 32 * qtr;
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          reinterpret_cast<uint4*>(dst)[j] = reinterpret_cast<const uint4*>(sO + r * kD + 32 * qtr)[j];
+          for (int j = 0; j < 4; ++j)
+            reinterpret_cast<uint4*>(dst)[j] = reinterpret_cast<const uint4*>(sO + r * kD + 32 * qtr)[j];
+        }
       }
       mbar_arrive(tc::smem_u32(&ctl.late[sm_]));
     };
@@ -795,6 +843,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
     }
     group_sync(2);  // eg_keep of the last chunk is visible to the whole group
     if (nchunks > 0) final_epilogue(nchunks - 1);
+    if (P.use_tma_out && gt == 0) tc::bulk_wait_all();
     // final state: hT[k][v] = S^T[v][k]
     if (p.hT) {
       float* hT = p.hT + (int64_t)unit * kD * kD;
@@ -814,11 +863,63 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const FwdParam
   if (warp == 0) tc::tmem_dealloc(tbase, TM_COLS);
 }
 
+// cuTensorMapEncodeTiled is fetched from the driver at run time (no link dependency on libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      ptr = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+// 5-d input view of a contiguous [B*H][T][128] bf16 tensor (see Sm100Params).
+inline bool make_input_map(CUtensorMap* m, const void* base, int64_t units, int T) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[5] = {8, 8, 16, (cuuint64_t)(T / 8), (cuuint64_t)units};
+  const cuuint64_t strides[4] = {256, 16, 2048, (cuuint64_t)T * 256};  // bytes, dims 1..4
+  const cuuint32_t box[5] = {8, 8, 16, 8, 1};
+  const cuuint32_t es[5] = {1, 1, 1, 1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), dims, strides, box, es,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// 4-d output view {128, T, H, B} of [B,H,T,128] or [B,T,H,128].
+inline bool make_output_map(CUtensorMap* m, void* base, const SeqMap& sm) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[4] = {128, (cuuint64_t)sm.T, (cuuint64_t)sm.H, (cuuint64_t)sm.B};
+  cuuint64_t strides[3];
+  if (sm.bthd) { strides[0] = (cuuint64_t)sm.H * 256; strides[1] = 256; strides[2] = (cuuint64_t)sm.T * sm.H * 256; }
+  else { strides[0] = 256; strides[1] = (cuuint64_t)sm.T * 256; strides[2] = (cuuint64_t)sm.H * sm.T * 256; }
+  const cuuint32_t box[4] = {128, 64, 1, 1};
+  const cuuint32_t es[4] = {1, 1, 1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 inline cudaError_t launch_chunk(const FwdParams& p, cudaStream_t stream) {
   cudaError_t e = cudaFuncSetAttribute(chunk_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_TOTAL);
   if (e != cudaSuccess) return e;
-  const dim3 grid((unsigned)((int64_t)p.map.B * p.map.H)), block(kThreads);
-  chunk_sm100_kernel<<<grid, block, SM_TOTAL, stream>>>(p);
+  Sm100Params P;
+  memset(&P, 0, sizeof(P));
+  P.p = p;
+  const int64_t units = (int64_t)p.map.B * p.map.H;
+  // TMA inputs need the rows of one (batch, head) contiguous and whole 8-row blocks; otherwise the
+  // per-thread cp.async path loads the tiles (same layout, same results).
+  P.use_tma_in = !p.map.bthd && p.map.T % 8 == 0 && make_input_map(&P.tk, p.k, units, p.map.T) &&
+                 make_input_map(&P.tq, p.q, units, p.map.T) && make_input_map(&P.tv, p.v, units, p.map.T);
+  P.use_tma_out = make_output_map(&P.to, p.o, p.map);
+  const dim3 grid((unsigned)units), block(kThreads);
+  chunk_sm100_kernel<<<grid, block, SM_TOTAL, stream>>>(P);
   return cudaGetLastError();
 }
 
