@@ -184,9 +184,9 @@ int dr_step(const DrDesc* d, const void* q, const void* k, const void* v, const 
 #ifdef DR_PROFILE
 // Profiling builds only: copies (and clears) the per-phase cycle counters of the chunk kernel.
 int dr_debug_read_profile(unsigned long long* out64_host) {
-  cudaError_t e = cudaMemcpyFromSymbol(out64_host, dr::sm100::g_prof, sizeof(unsigned long long) * 128);
+  cudaError_t e = cudaMemcpyFromSymbol(out64_host, dr::sm100::g_prof, sizeof(unsigned long long) * 192);
   if (e != cudaSuccess) return check_cuda(e);
-  unsigned long long z[128] = {0};
+  unsigned long long z[192] = {0};
   return check_cuda(cudaMemcpyToSymbol(dr::sm100::g_prof, z, sizeof(z)));
 }
 #endif

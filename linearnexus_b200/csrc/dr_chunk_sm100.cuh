@@ -61,13 +61,15 @@ constexpr uint32_t TM_COLS = 512;
 // shared-memory map (bytes).  Per stage (two stages):
 constexpr int RBS = 16 * 128;                 // row-block stride of the 128-column core-matrix tiles
 constexpr int A_RBS = 8 * 128;                // row-block stride of the 64-column tiles
-constexpr int ST_QK = 0;                      // [K^ (64 rows); Q^ (64 rows)] x 128   32 KB
-constexpr int ST_W = ST_QK + 128 * 128 * 2;   // W [64][128]; reused as the O staging tile  16 KB
+constexpr int QK_TILE = 128 * 128 * 2;        // [K (64 rows); Q (64 rows)] x 128 raw bf16, 32 KB
+constexpr int SM_QKR = 0;                     // ring of 3 such tiles (chunk n uses tile n % 3)
+constexpr int SM_STAGE = 3 * QK_TILE;         // two stages follow
+constexpr int ST_W = 0;                       // W [64][128]; reused as the O staging tile  16 KB
 constexpr int ST_AQK = ST_W + 64 * 128 * 2;   // A_qk [64][64]                           8 KB
 constexpr int ST_SC = ST_AQK + 64 * 64 * 2;   // G, e^G, e^{G_L-G}, beta: 4 x 64 floats  1 KB
 constexpr int STAGE_BYTES = ST_SC + 4 * 64 * 4;
 // Producer-private:
-constexpr int SM_V = 2 * STAGE_BYTES;         // V [64][128] core-matrix tile           16 KB
+constexpr int SM_V = SM_STAGE + 2 * STAGE_BYTES;  // V [64][128] core-matrix tile       16 KB
 constexpr int SM_TB = SM_V + 64 * 128 * 2;    // T diag(beta)        [64][64] bf16
 constexpr int SM_TW = SM_TB + 64 * 64 * 2;    // T diag(beta e^G)    [64][64] bf16
 constexpr int LDT = 68;                       // row stride (floats) of the fp32 64x64 matrices
@@ -77,7 +79,7 @@ constexpr int SM_TOTAL = SM_T32 + 64 * LDT * 4;
 
 // Optional per-phase cycle counters (CTA 0 only), compiled in with -DDR_PROFILE.
 #ifdef DR_PROFILE
-__device__ unsigned long long g_prof[128];
+__device__ unsigned long long g_prof[192];
 #define PROF_DECL unsigned long long prof_t0 = clock64(); unsigned long long wt0 = 0; (void)wt0;
 #define PROF(idx)                                              \
   do {                                                         \
@@ -107,7 +109,8 @@ __device__ unsigned long long g_prof[128];
 #endif
 
 struct Ctl {
-  uint64_t full[2], empty[2], late[2], barP, bar1, bar2, kq[2], vb;
+  uint64_t full[2], empty[2], late[2], barP, bar1, bar2, kq[3], vb;
+  float gb[3][128];      // raw beta (0..63) and g (64..127) of chunk m in slot m % 3
   float eg_keep[2][64];  // rq_i e^{G_i} of the chunk whose output epilogue is still pending, per stage
   float rq_keep[2][64];  // rq_i of that chunk
   float rq[2][64];       // per stage: scale / (||q_i|| + eps)           (producer -> consumer)
@@ -267,6 +270,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
     tc::mbar_init(tc::smem_u32(&ctl.bar2), 1);
     tc::mbar_init(tc::smem_u32(&ctl.kq[0]), 1);
     tc::mbar_init(tc::smem_u32(&ctl.kq[1]), 1);
+    tc::mbar_init(tc::smem_u32(&ctl.kq[2]), 1);
     tc::mbar_init(tc::smem_u32(&ctl.vb), 1);
     tc::fence_mbar_init();
     ctl.abort = 0;
@@ -281,6 +285,18 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
   auto wait_bar = [&](uint64_t* bar, uint32_t parity) {
     if (!*abort_p) {
       if (!tc::mbar_wait_bounded(tc::smem_u32(bar), parity, kWaitLimit)) {
+        *abort_p = 1;
+        if (p.status) atomicOr(p.status, DR_DEV_TIMEOUT);
+      }
+    }
+  };
+
+  // Long waits (a whole group idling until the other group hands a stage over) back off with
+  // nanosleep between polls so that the waiting warps leave the issue slots and the shared-memory
+  // pipe to the working group.
+  auto wait_bar_relaxed = [&](uint64_t* bar, uint32_t parity) {
+    if (!*abort_p) {
+      if (!tc::mbar_wait_sleepy(tc::smem_u32(bar), parity)) {
         *abort_p = 1;
         if (p.status) atomicOr(p.status, DR_DEV_TIMEOUT);
       }
@@ -311,12 +327,11 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
     // to the tiles: it is folded into the epilogue factors rk, rs, rq.
     auto issue_kq = [&](int m) {
       const int t0m = m * kC, rowsm = min(kC, T - t0m);
-      uint8_t* stm = smem + (m & 1) * STAGE_BYTES;
-      uint8_t* dQK = stm + ST_QK;
-      float* dG = reinterpret_cast<float*>(stm + ST_SC);
+      uint8_t* dQK = smem + SM_QKR + (m % 3) * QK_TILE;
+      float* dG = ctl.gb[m % 3];
       if (P.use_tma_in) {
         if (gt == 0) {
-          const uint32_t bar = tc::smem_u32(&ctl.kq[m & 1]);
+          const uint32_t bar = tc::smem_u32(&ctl.kq[m % 3]);
           tc::mbar_arrive_expect_tx(bar, 2u * 64 * 256);
           tc::tma_load_5d(tc::smem_u32(dQK), &P.tk, 0, 0, 0, m * 8, unit, bar);
           tc::tma_load_5d(tc::smem_u32(dQK) + 64 * 256, &P.tq, 0, 0, 0, m * 8, unit, bar);
@@ -336,8 +351,8 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         const int r = gt & 63;
         const bool live = r < rowsm;
         const int64_t off = s_base + (int64_t)(t0m + (live ? r : 0)) * s_tok;
-        if (gt < 64) tc::cp_async4(tc::smem_u32(dG + 192 + r), p.beta + off, live);          // beta
-        else tc::cp_async4(tc::smem_u32(dG + r), gg ? gg + off : p.beta + off, live && gg);  // g (0 without decay)
+        if (gt < 64) tc::cp_async4(tc::smem_u32(dG + r), p.beta + off, live);                     // beta
+        else tc::cp_async4(tc::smem_u32(dG + 64 + r), gg ? gg + off : p.beta + off, live && gg);  // g (0 without decay)
       }
       tc::cp_async_commit();
     };
@@ -363,10 +378,32 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       tc::cp_async_commit();
     };
 
-    for (int i = gt; i < 64 * LDT; i += kGroup) sT32[i] = 0.f;
+    // inclusive scan of the log decay over the 64 rows of a stage (one warp): G, e^G, e^{G_L - G}
+    auto scan_stage = [&](int m) {
+      float* zG = reinterpret_cast<float*>(smem + SM_STAGE + (m & 1) * STAGE_BYTES + ST_SC);
+      const float* raw = ctl.gb[m % 3];
+      zG[192 + lane] = raw[lane]; zG[224 + lane] = raw[32 + lane];   // beta
+      float a = raw[64 + lane], bq = raw[96 + lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float x = __shfl_up_sync(0xffffffffu, a, o);
+        const float y = __shfl_up_sync(0xffffffffu, bq, o);
+        if (lane >= o) { a += x; bq += y; }
+      }
+      const float tot = __shfl_sync(0xffffffffu, a, 31);
+      bq += tot;
+      const float last = __shfl_sync(0xffffffffu, bq, 31);
+      zG[lane] = a; zG[lane + 32] = bq;
+      zG[64 + lane] = __expf(a); zG[96 + lane] = __expf(bq);
+      zG[128 + lane] = __expf(fminf(last - a, 0.f)); zG[160 + lane] = __expf(fminf(last - bq, 0.f));
+    };
+
     if (nchunks > 0) {
       issue_kq(0);
       issue_v(0);
+      tc::cp_async_wait_1();   // g, beta of chunk 0
+      group_sync(1);
+      if (warp == 1) scan_stage(0);
     }
     PROF_DECL
 #ifdef DR_PROFILE
@@ -402,6 +439,21 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       PROF(45);
       for (int i = 0; i < 4; ++i) block_inverse_64(sAkk, ctl.rs, sT32, gt);
       PROF(46);
+      {  // cost of waiting on a phase that has already completed
+        if (gt == 0) {
+          tc::mbar_arrive_expect_tx(tc::smem_u32(&ctl.vb), 0);  // completes phase 0 of vb ...
+        }
+        group_sync(1);
+        PROF(36);
+        bool ok = true;
+        for (int i = 0; i < 16; ++i) ok &= tc::mbar_test(tc::smem_u32(&ctl.vb), 0);
+        if (!ok) ctl.rk[4] = 1.f;
+        PROF(35);
+        for (int i = 0; i < 16; ++i) wait_bar(&ctl.vb, 0);
+        PROF(34);
+        if (gt == 0) tc::mbar_arrive_expect_tx(tc::smem_u32(&ctl.vb), 0);  // ... and phase 1, so that the parity is back
+        group_sync(1);
+      }
       {  // variants of the level-2 product loop, 8 repetitions each
         const int row = gt >> 3, c4 = (gt & 7) * 4;
         float x0 = 0.f, x1 = 0.f, x2 = 0.f, x3 = 0.f;
@@ -465,20 +517,32 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
 #endif
     for (int n = 0; n < nchunks; ++n) {
       const int s = n & 1;
-      uint8_t* st = smem + s * STAGE_BYTES;
-      uint8_t* sQK = st + ST_QK;
+      uint8_t* st = smem + SM_STAGE + s * STAGE_BYTES;
+      uint8_t* sQK = smem + SM_QKR + (n % 3) * QK_TILE;
       uint8_t* sWt = st + ST_W;
       uint8_t* sAqk = st + ST_AQK;
       float* sG = reinterpret_cast<float*>(st + ST_SC);
       float* sEG = sG + 64;
       float* sWd = sG + 128;
       float* sBeta = sG + 192;
-      // cp.async groups complete in order; the newest one still in flight here is this chunk's V tile
-      tc::cp_async_wait_1();
-      if (P.use_tma_in) wait_bar(&ctl.kq[s], (n >> 1) & 1);
+      // The consumer has finished chunk n-2: stage s and tile (n+1) % 3 are free.  Start the next
+      // chunk's loads a whole iteration ahead; an empty group keeps the group count uniform at the end.
+      WSTART;
+      if (n >= 2) wait_bar(&ctl.empty[s], ((n >> 1) - 1) & 1);
+      WEND(3);
+      WSTART;
+      if (n + 1 < nchunks) issue_kq(n + 1);
+      else tc::cp_async_commit();
+      WEND(4);
+      WSTART;
+      // cp.async groups complete in order: the two newest (this chunk's V, the next chunk's K,Q) may fly on
+      tc::cp_async_wait_2();
+      if (P.use_tma_in) wait_bar(&ctl.kq[n % 3], (n / 3) & 1);
+      WEND(11);
       tc::fence_async_smem();
       group_sync(1);
       PROF(0);
+      WSTART;
       // ---- (1) D1 = [K;Q] K^T on the raw rows ------------------------------------------------------------
       if (gt == 0) {
         tc::tc_fence_after();
@@ -490,40 +554,6 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         }
         tc::mma_commit(tc::smem_u32(&ctl.barP));
       }
-      // while the product runs: decay scan (one warp) and the query norms (everyone)
-      if (warp == 1) {
-        float a = sG[lane], bq = sG[lane + 32];
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          const float x = __shfl_up_sync(0xffffffffu, a, o);
-          const float y = __shfl_up_sync(0xffffffffu, bq, o);
-          if (lane >= o) { a += x; bq += y; }
-        }
-        const float tot = __shfl_sync(0xffffffffu, a, 31);
-        bq += tot;
-        const float last = __shfl_sync(0xffffffffu, bq, 31);
-        sG[lane] = a; sG[lane + 32] = bq;
-        sEG[lane] = __expf(a); sEG[lane + 32] = __expf(bq);
-        sWd[lane] = __expf(fminf(last - a, 0.f)); sWd[lane + 32] = __expf(fminf(last - bq, 0.f));
-      }
-      {
-        const int row = gt >> 2, part = gt & 3;
-        float ss = 0.f;
-#pragma unroll
-        for (int it = 0; it < 4; ++it) {
-          const uint4 c = *reinterpret_cast<const uint4*>(sQK + tc::core_off(64 + row, (4 * part + it) * 8, RBS));
-          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&c);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 f = __bfloat1622float2(h2[e]);
-            ss += f.x * f.x + f.y * f.y;
-          }
-        }
-        ss += __shfl_xor_sync(0xffffffffu, ss, 1);
-        ss += __shfl_xor_sync(0xffffffffu, ss, 2);
-        if (part == 0) ctl.rq[s][row] = p.l2norm ? p.scale / (sqrtf(ss) + 1e-6f) : p.scale;
-      }
-      group_sync(1);  // scan results visible to the whole group
       PROF(2);
       wait_bar(&ctl.barP, phP); phP ^= 1;
       tc::tc_fence_after();
@@ -580,18 +610,6 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       tc::tc_fence_before();
       group_sync(1);
       PROF(4);
-      // prefetch the next chunk's K, Q, g, beta into the other stage (released by the consumer after the
-      // last product of chunk n-1); an empty group keeps the group count uniform on the last chunk
-      if (n + 1 < nchunks) {
-        WSTART;
-        if (n >= 1) wait_bar(&ctl.empty[(n + 1) & 1], (((n + 1) >> 1) - 1) & 1);
-        WEND(3);
-        WSTART;
-        issue_kq(n + 1);
-        WEND(4);
-      } else {
-        tc::cp_async_commit();
-      }
       PROF(1);
       // ---- T'' = (I + diag(rs) X)^-1;  Tb = T'' diag(beta rk), Tw = T'' diag(beta e^G rk^2) -----------------
       WSTART;
@@ -657,6 +675,13 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         }
         tc::mma_commit(tc::smem_u32(&ctl.barP));
       }
+      // while the products run: decay scan of the NEXT chunk (its g, beta were prefetched above)
+      if (n + 1 < nchunks) {
+        tc::cp_async_wait_all();
+        group_sync(1);
+        if (n >= 1) wait_bar(&ctl.empty[(n + 1) & 1], (((n + 1) >> 1) - 1) & 1);  // the stage's scalars are free
+        if (warp == 1) scan_stage(n + 1);
+      }
       wait_bar(&ctl.barP, phP); phP ^= 1;
       tc::tc_fence_after();
       PROF(6);
@@ -699,7 +724,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
     // -> coalesced store; then releases stage m&1 to the producer.
     auto final_epilogue = [&](int m) {
       const int sm_ = m & 1;
-      uint8_t* stm = smem + sm_ * STAGE_BYTES;
+      uint8_t* stm = smem + SM_STAGE + sm_ * STAGE_BYTES;
       const float* sEGm = ctl.eg_keep[sm_];   // rq_i e^{G_i}
       const float* sRQm = ctl.rq_keep[sm_];   // rq_i = scale / (||q_i|| + eps)
       __nv_bfloat16* sO = reinterpret_cast<__nv_bfloat16*>(stm + ST_W);
@@ -742,11 +767,12 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
     PROF_DECL
     for (int n = 0; n < nchunks; ++n) {
       const int s = n & 1;
-      uint8_t* st = smem + s * STAGE_BYTES;
-      const uint32_t aQK = tc::smem_u32(st + ST_QK), aW = tc::smem_u32(st + ST_W), aAqk = tc::smem_u32(st + ST_AQK);
+      uint8_t* st = smem + SM_STAGE + s * STAGE_BYTES;
+      const uint8_t* sQKc = smem + SM_QKR + (n % 3) * QK_TILE;
+      const uint32_t aQK = tc::smem_u32(sQKc), aW = tc::smem_u32(st + ST_W), aAqk = tc::smem_u32(st + ST_AQK);
       const float* sEG = reinterpret_cast<const float*>(st + ST_SC) + 64;
       const float* sWd = sEG + 64;
-      wait_bar(&ctl.full[s], (n >> 1) & 1);
+      wait_bar_relaxed(&ctl.full[s], (n >> 1) & 1);
       tc::tc_fence_after();
       PROF(16);
       // ---- state pass: bf16 copy of S^T for the products; fp32 master pre-multiplied by e^{G_L} --------
@@ -779,6 +805,23 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
           tc::mma_ts(tbase + TM_DU + 64 * s, tbase + TM_SB + ks * 8, bd, id_n64_neg, 1);
         }
         tc::mma_commit(tc::smem_u32(&ctl.bar1));
+      }
+      {  // query norms of this chunk (raw rows 64..127 of the tile): rq_i = scale / (||q_i|| + eps)
+        const int row = gt >> 2, part = gt & 3;
+        float ss = 0.f;
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const uint4 c = *reinterpret_cast<const uint4*>(sQKc + tc::core_off(64 + row, (4 * part + it) * 8, RBS));
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&c);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h2[e]);
+            ss += f.x * f.x + f.y * f.y;
+          }
+        }
+        ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+        ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+        if (part == 0) ctl.rq[s][row] = p.l2norm ? p.scale / (sqrtf(ss) + 1e-6f) : p.scale;
       }
       if (n > 0) final_epilogue(n - 1);  // overlaps (3); frees Dq and the other stage
       tc::tc_fence_before();

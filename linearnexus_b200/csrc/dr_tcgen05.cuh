@@ -54,13 +54,26 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 }
 // Bounded both in attempts and in time (about a second of SM clock), whichever ends first.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t limit) {
-  if (mbar_try(bar, parity)) return true;
+  // a completed phase is the common case: test without suspending first
+#pragma unroll 1
+  for (int i = 0; i < 16; ++i)
+    if (mbar_test(bar, parity)) return true;
   const long long t_start = clock64();
   for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try(bar, parity)) return true;
     if (clock64() - t_start > 2000000000ll) return false;
   }
   return false;
+}
+// Polling wait with sleep between polls, bounded to about a second of SM clock.
+__device__ __forceinline__ bool mbar_wait_sleepy(uint32_t bar, uint32_t parity) {
+  if (mbar_test(bar, parity)) return true;
+  const long long t_start = clock64();
+  while (true) {
+    __nanosleep(200);
+    if (mbar_test(bar, parity)) return true;
+    if (clock64() - t_start > 2000000000ll) return false;
+  }
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
@@ -101,6 +114,7 @@ __device__ __forceinline__ void cp_async4(uint32_t dst_smem, const void* src, bo
   const uint32_t sz = valid ? 4u : 0u;
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst_smem), "l"(src), "r"(sz) : "memory");
 }
+__device__ __forceinline__ void cp_async_wait_2() { asm volatile("cp.async.wait_group 2;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_1() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
