@@ -64,8 +64,10 @@ constexpr int A_RBS = 8 * 128;                // row-block stride of the 64-colu
 constexpr int QK_TILE = 128 * 128 * 2;        // [K (64 rows); Q (64 rows)] x 128 raw bf16, 32 KB
 constexpr int SM_QKR = 0;                     // ring of 3 such tiles (chunk n uses tile n % 3)
 constexpr int SM_STAGE = 3 * QK_TILE;         // two stages follow
-constexpr int ST_W = 0;                       // W [64][128]; reused as the O staging tile  16 KB
-constexpr int ST_AQK = ST_W + 64 * 128 * 2;   // A_qk [64][64]                           8 KB
+constexpr int W_KBS = 144;                    // k-block stride of the W tile (padded: conflict-free 2-byte stores)
+constexpr int W_RBS = 16 * W_KBS;             // its row-block stride
+constexpr int ST_W = 0;                       // W [64][128] (18 KB padded); reused as the O staging tile
+constexpr int ST_AQK = ST_W + 8 * W_RBS;       // A_qk [64][64]                           8 KB
 constexpr int ST_SC = ST_AQK + 64 * 64 * 2;   // G, e^G, e^{G_L-G}, beta: 4 x 64 floats  1 KB
 constexpr int STAGE_BYTES = ST_SC + 4 * 64 * 4;
 // Producer-private:
@@ -439,21 +441,6 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       PROF(45);
       for (int i = 0; i < 4; ++i) block_inverse_64(sAkk, ctl.rs, sT32, gt);
       PROF(46);
-      {  // cost of waiting on a phase that has already completed
-        if (gt == 0) {
-          tc::mbar_arrive_expect_tx(tc::smem_u32(&ctl.vb), 0);  // completes phase 0 of vb ...
-        }
-        group_sync(1);
-        PROF(36);
-        bool ok = true;
-        for (int i = 0; i < 16; ++i) ok &= tc::mbar_test(tc::smem_u32(&ctl.vb), 0);
-        if (!ok) ctl.rk[4] = 1.f;
-        PROF(35);
-        for (int i = 0; i < 16; ++i) wait_bar(&ctl.vb, 0);
-        PROF(34);
-        if (gt == 0) tc::mbar_arrive_expect_tx(tc::smem_u32(&ctl.vb), 0);  // ... and phase 1, so that the parity is back
-        group_sync(1);
-      }
       {  // variants of the level-2 product loop, 8 repetitions each
         const int row = gt >> 3, c4 = (gt & 7) * 4;
         float x0 = 0.f, x1 = 0.f, x2 = 0.f, x3 = 0.f;
@@ -695,7 +682,8 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         tc::tc_wait_ld();
 #pragma unroll
         for (int j = 0; j < 32; ++j)
-          *reinterpret_cast<__nv_bfloat16*>(sWt + tc::core_off(c0 + j, l128, RBS)) = __float2bfloat16_rn(__uint_as_float(r[j]));
+          *reinterpret_cast<__nv_bfloat16*>(sWt + ((c0 + j) >> 3) * W_RBS + (l128 >> 3) * W_KBS + ((c0 + j) & 7) * 16 +
+                                            (l128 & 7) * 2) = __float2bfloat16_rn(__uint_as_float(r[j]));
       }
       tc::fence_async_smem();
       WEND(2);
@@ -801,7 +789,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         tc::tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          const uint64_t bd = tc::smem_desc(aW + ks * 256, 128, RBS);
+          const uint64_t bd = tc::smem_desc(aW + ks * 2 * W_KBS, W_KBS, W_RBS);
           tc::mma_ts(tbase + TM_DU + 64 * s, tbase + TM_SB + ks * 8, bd, id_n64_neg, 1);
         }
         tc::mma_commit(tc::smem_u32(&ctl.bar1));
