@@ -332,7 +332,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       uint8_t* dQK = smem + SM_QKR + (m % 3) * QK_TILE;
       float* dG = ctl.gb[m % 3];
       if (P.use_tma_in) {
-        if (gt == 0) {
+        if (gt == 64) {  // a warp other than the one that issues the products
           const uint32_t bar = tc::smem_u32(&ctl.kq[m % 3]);
           tc::mbar_arrive_expect_tx(bar, 2u * 64 * 256);
           tc::tma_load_5d(tc::smem_u32(dQK), &P.tk, 0, 0, 0, m * 8, unit, bar);
@@ -349,11 +349,11 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
           tc::cp_async16(tc::smem_u32(dQK + tc::core_off(64 + r, kb * 8, RBS)), gq + off, live);
         }
       }
-      if (gt < 128) {
+      if (gt >= 128) {
         const int r = gt & 63;
         const bool live = r < rowsm;
         const int64_t off = s_base + (int64_t)(t0m + (live ? r : 0)) * s_tok;
-        if (gt < 64) tc::cp_async4(tc::smem_u32(dG + r), p.beta + off, live);                     // beta
+        if (gt < 192) tc::cp_async4(tc::smem_u32(dG + r), p.beta + off, live);                     // beta
         else tc::cp_async4(tc::smem_u32(dG + 64 + r), gg ? gg + off : p.beta + off, live && gg);  // g (0 without decay)
       }
       tc::cp_async_commit();
@@ -362,7 +362,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
     auto issue_v = [&](int m) {
       const int t0m = m * kC, rowsm = min(kC, T - t0m);
       if (P.use_tma_in) {
-        if (gt == 0) {
+        if (gt == 64) {
           const uint32_t bar = tc::smem_u32(&ctl.vb);
           tc::mbar_arrive_expect_tx(bar, 64u * 256);
           tc::tma_load_5d(tc::smem_u32(sV), &P.tv, 0, 0, 0, m * 8, unit, bar);
@@ -512,26 +512,18 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       float* sEG = sG + 64;
       float* sWd = sG + 128;
       float* sBeta = sG + 192;
-      // The consumer has finished chunk n-2: stage s and tile (n+1) % 3 are free.  Start the next
-      // chunk's loads a whole iteration ahead; an empty group keeps the group count uniform at the end.
-      WSTART;
-      if (n >= 2) wait_bar(&ctl.empty[s], ((n >> 1) - 1) & 1);
-      WEND(3);
-      WSTART;
-      if (n + 1 < nchunks) issue_kq(n + 1);
-      else tc::cp_async_commit();
-      WEND(4);
-      WSTART;
-      // cp.async groups complete in order: the two newest (this chunk's V, the next chunk's K,Q) may fly on
-      tc::cp_async_wait_2();
-      if (P.use_tma_in) wait_bar(&ctl.kq[n % 3], (n / 3) & 1);
-      WEND(11);
-      tc::fence_async_smem();
-      group_sync(1);
+      // this chunk's K,Q tile: TMA completion is awaited by the issuing thread alone; tiles filled by
+      // per-thread cp.async need everyone's copies (the two newest groups -- this chunk's V and the
+      // next chunk's K,Q -- may stay in flight) and a proxy fence
+      if (!P.use_tma_in) {
+        tc::cp_async_wait_1();
+        tc::fence_async_smem();
+      }
+      group_sync(1);  // also: every read of the producer scratch columns by the previous chunk is done
       PROF(0);
-      WSTART;
       // ---- (1) D1 = [K;Q] K^T on the raw rows ------------------------------------------------------------
       if (gt == 0) {
+        if (P.use_tma_in) wait_bar(&ctl.kq[n % 3], (n / 3) & 1);
         tc::tc_fence_after();
         const uint32_t aQK = tc::smem_u32(sQK);
 #pragma unroll
@@ -541,6 +533,12 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         }
         tc::mma_commit(tc::smem_u32(&ctl.barP));
       }
+      // while the product runs: the consumer has finished chunk n-2, so stage s and tile (n+1) % 3 are
+      // free -- start the next chunk's loads a whole iteration ahead (an empty group keeps the cp.async
+      // group count uniform on the last chunk)
+      if (n >= 2 && (!P.use_tma_in || gt == 64)) wait_bar(&ctl.empty[s], ((n >> 1) - 1) & 1);
+      if (n + 1 < nchunks) issue_kq(n + 1);
+      else tc::cp_async_commit();
       PROF(2);
       wait_bar(&ctl.barP, phP); phP ^= 1;
       tc::tc_fence_after();
