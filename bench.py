@@ -42,6 +42,10 @@ WORKLOADS = {
     "deltanet_fwd_fp32": dict(variant="delta", B=2, T=512, H=4, K=64, V=64, chunk=64, kind="chunk_fwd", cfg_id=1),
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel (ncu, see profiles/*.md)
+NCU_TRAFFIC = {
+    "gdn_fwd:chunk_tcgen05": 504.4e6,   # profiles/chunk_sm100_kernel_gdn_fwd.md (B=4 capture scaled by sequences)
+}
 
 
 def alg_flops_per_token_head(C, K, V):
@@ -354,12 +358,8 @@ def main():
         roof["peak_source"] = peaks["source"]
         roof["kernel"] = res["path"]
         roof["alg_bytes_per_launch"] = alg_b
-        roof["traffic"] = None
-        tfile = ROOT / "profiles" / "traffic.json"
-        if tfile.exists():
-            t = json.loads(tfile.read_text()).get(f"{args.workload}:{res['path']}")
-            if t:
-                roof["traffic"] = t["dram_bytes_per_launch"]
+        # DRAM bytes per launch from the ncu captures summarised under profiles/ (per workload and kernel)
+        roof["traffic"] = NCU_TRAFFIC.get(f"{args.workload}:{res['path']}") if not args.batch else None
         cpu = None
         if not args.no_cpu_baseline:
             c = cpu_oracle_sample(w, target_s=args.cpu_seconds)
