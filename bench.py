@@ -242,8 +242,8 @@ def cpu_oracle_sample(w, target_s=12.0, threads=None):
     """Times the CPU oracle (torch fp32 restatement of the reference op) on a bounded sample of
     the workload: a (batch x head) slice at the full sequence length, scaled linearly."""
     from oracle import delta_rule_oracle as O
-    if threads:
-        torch.set_num_threads(threads)
+    # torchrun exports OMP_NUM_THREADS=1: the CPU arm is meant to use every host core it can
+    torch.set_num_threads(threads or os.cpu_count() or 1)
     cores = torch.get_num_threads()
     heads = 8 if w["kind"] != "decode" else w["H"]
     batch = 1 if w["kind"] != "decode" else 8
