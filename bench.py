@@ -39,6 +39,8 @@ WORKLOADS = {
     "gdn_fwd": dict(variant="gated", B=8, T=4096, H=16, K=128, V=128, chunk=64, kind="chunk_fwd", cfg_id=2),
     "kda_fwd": dict(variant="kda", B=4, T=8192, H=32, K=128, V=128, chunk=64, kind="chunk_fwd", cfg_id=3),
     "gdn_decode": dict(variant="gated", B=256, T=1, H=32, K=128, V=128, chunk=0, kind="decode", cfg_id=4),
+    # training configuration: B=16 over 8 GPUs = 2 batch rows per GPU; forward + backward
+    "gdn_fwd_bwd": dict(variant="gated", B=2, T=4096, H=16, K=128, V=128, chunk=64, kind="fwd_bwd", cfg_id=5),
     "deltanet_fwd_fp32": dict(variant="delta", B=2, T=512, H=4, K=64, V=64, chunk=64, kind="chunk_fwd", cfg_id=1),
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
@@ -148,6 +150,15 @@ def run_ours(args, w, rank, world, dev):
 
         def step():
             return L.gated_delta_rule_step(q, k, v, g, beta, state, inplace=True)
+    elif w["kind"] == "fwd_bwd":
+        from linearnexus_b200 import ops as _ops
+        gen = torch.Generator().manual_seed(7)
+        d_o = torch.randn(w["B"], w["H"], w["T"], w["V"], generator=gen).to(torch.bfloat16).to(dev)
+
+        def step():
+            o, hT = L.gated_delta_rule_chunkwise(devt["q"], devt["k"], devt["v"], devt["g"], devt["beta"], chunk_size=w["chunk"])
+            gr = _ops.chunk_backward("gated", devt["q"], devt["k"], devt["v"], devt["g"], devt["beta"], d_o, chunk_size=w["chunk"])
+            return o, gr["dq"]
     elif w["variant"] == "gated":
         def step():
             return L.gated_delta_rule_chunkwise(devt["q"], devt["k"], devt["v"], devt["g"], devt["beta"], chunk_size=w["chunk"])
@@ -297,7 +308,8 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    metric = "decode_tokens_per_sec" if w["kind"] == "decode" else "delta_rule_fwd_tokens_per_sec"
+    metric = ("decode_tokens_per_sec" if w["kind"] == "decode" else
+              "delta_rule_fwd_bwd_tokens_per_sec" if w["kind"] == "fwd_bwd" else "delta_rule_fwd_tokens_per_sec")
     config = {"workload": f"{args.workload}: {w['variant']} {'decode step' if w['kind'] == 'decode' else 'chunkwise forward'} "
                           f"B={w['B']} T={w['T']} H={w['H']} d_k={w['K']} d_v={w['V']} chunk={w['chunk']} per GPU",
               "per_gpu_batch": w["B"], "global_batch": w["B"] * world, "seq_len": w["T"], "heads": w["H"],
@@ -344,7 +356,7 @@ def main():
             alg_b = alg_bytes_per_token_head(w) * units
             roof = {"bound": "hbm", "achieved": alg_b / ktime / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s"}
         else:
-            flops = alg_flops_per_token_head(C, w["K"], w["V"]) * units
+            flops = alg_flops_per_token_head(C, w["K"], w["V"]) * units * (3 if w["kind"] == "fwd_bwd" else 1)
             alg_b = alg_bytes_per_token_head(w, 4 if w["cfg_id"] == 1 else 2) * units
             tf = flops / ktime / 1e12
             hb = alg_b / ktime / 1e9

@@ -23,6 +23,7 @@
 #pragma once
 
 #include "dr_chunk_fp32.cuh"
+#include "dr_chunk_sm100.cuh"
 #include "dr_common.cuh"
 
 namespace dr {
@@ -515,7 +516,10 @@ inline cudaError_t launch_bwd(const DrDesc* d, const void* q, const void* k, con
   f.K = K; f.V = V; f.C = C;
   f.variant = d->variant; f.qkv_dt = d->qkv_dtype; f.g_dt = d->g_dtype; f.out_dt = d->qkv_dtype;
   f.l2norm = d->use_qk_l2norm; f.scale = d->scale;
-  e = launch_chunk_fp32(f, stream);
+  // the tensor-core forward writes the same checkpoints when the shape qualifies (bf16, K=V=128, C=64)
+  const bool tc_fwd = sm100::kAvailable && K == 128 && V == 128 && C == 64 && d->qkv_dtype == DR_BF16 &&
+                      (d->variant == DR_DELTA || (d->variant == DR_GATED && d->g_dtype == DR_F32));
+  e = tc_fwd ? sm100::launch_chunk(f, stream) : launch_chunk_fp32(f, stream);
   if (e != cudaSuccess) return e;
   ++*launches;
   // (2) adjoint

@@ -729,7 +729,9 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         }
       }
       tc::tc_fence_before();
-      if (P.use_tma_out) {
+      if (!p.o) {
+        group_sync(2);  // output not wanted (checkpoint-only forward of the backward)
+      } else if (P.use_tma_out) {
         tc::fence_async_smem();
         group_sync(2);
         if (gt == 0) {  // one tiled store of the whole chunk; rows past T are clipped by the tensor map
@@ -772,6 +774,11 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
           tc::tc_wait_ld();
 #pragma unroll
           for (int j = 0; j < 16; ++j) pk[j] = tc::pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+          if (p.ckpt) {  // state at the start of this chunk, [K][V] row-major, for the backward
+            float* ck = p.ckpt + ((int64_t)unit * nchunks + n) * kD * kD;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) ck[(c0 + j) * kD + l128] = __uint_as_float(r[j]);
+          }
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * gl);
           tc::tmem_st16(tbase + TM_SB + lane_addr + c0 / 2, pk);
@@ -946,7 +953,7 @@ inline cudaError_t launch_chunk(const FwdParams& p, cudaStream_t stream) {
   // per-thread cp.async path loads the tiles (same layout, same results).
   P.use_tma_in = !p.map.bthd && p.map.T % 8 == 0 && make_input_map(&P.tk, p.k, units, p.map.T) &&
                  make_input_map(&P.tq, p.q, units, p.map.T) && make_input_map(&P.tv, p.v, units, p.map.T);
-  P.use_tma_out = make_output_map(&P.to, p.o, p.map);
+  P.use_tma_out = p.o != nullptr && make_output_map(&P.to, p.o, p.map);
   const dim3 grid((unsigned)units), block(kThreads);
   chunk_sm100_kernel<<<grid, block, SM_TOTAL, stream>>>(P);
   return cudaGetLastError();
