@@ -30,6 +30,25 @@ namespace dr {
 
 constexpr int kBwThreads = 256;
 
+// One 16x8 output tile of D (+)= A B on the warp-level tensor-core path (tf32 operands, fp32
+// accumulate): a(m, k), b(k, n) are element accessors into fp32 shared memory.  Lane (g = lane/4,
+// t = lane%4) ends up with D[m0+g][n0+2t], D[m0+g][n0+2t+1], D[m0+g+8][n0+2t], D[m0+g+8][n0+2t+1].
+// The CUDA-core loops these replace are bound by shared-memory wavefronts, not by flops.
+template <class AF, class BF>
+__device__ __forceinline__ void tile_gemm_tf32(float (&d)[4], int m0, int n0, int kdim, AF a, BF b, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  for (int k0 = 0; k0 < kdim; k0 += 8) {
+    uint32_t af[4], bf[2];
+    af[0] = sm100::to_tf32(a(m0 + g, k0 + t));
+    af[1] = sm100::to_tf32(a(m0 + g + 8, k0 + t));
+    af[2] = sm100::to_tf32(a(m0 + g, k0 + t + 4));
+    af[3] = sm100::to_tf32(a(m0 + g + 8, k0 + t + 4));
+    bf[0] = sm100::to_tf32(b(k0 + t, n0 + g));
+    bf[1] = sm100::to_tf32(b(k0 + t + 4, n0 + g));
+    sm100::mma_tf32(d, af, bf);
+  }
+}
+
 struct BwdParams {
   const void* q; const void* k; const void* v; const void* g; const float* beta;
   const void* d_o; const float* d_hT;
@@ -67,7 +86,8 @@ __host__ __device__ inline BwdSmem bwd_layout(int C, int K, int VS, bool kda) {
   return L;
 }
 
-template <int VS, bool KDA>
+// TC: the products run on mma.sync tf32 (bf16 inputs: well inside their 2e-2 tolerance); otherwise exact fp32.
+template <int VS, bool KDA, bool TC>
 __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p) {
   extern __shared__ __align__(16) float smem[];
   const int K = p.K, V = p.V, C = p.C, T = p.map.T, N = p.N;
@@ -90,6 +110,9 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
   const int64_t v_base = p.map.base(b, h, V), v_tok = p.map.tok(V);
   const int64_t s_base = p.map.base(b, h, 1), s_tok = p.map.tok(1);
   const int64_t acc_row0 = (int64_t)unit * N * C;  // first row of this unit in the [.., N*C, ..] accumulators
+  // dq^, dk^ partials of this value slice go to the slice's own copy of the accumulator (plain stores;
+  // the finalize kernel adds the slices), dG and dbeta are few enough for atomics
+  const int64_t slice_off = (int64_t)(blockIdx.x % nvs) * ((int64_t)p.map.B * p.map.H * N * C) * K;
 
   for (int i = tid; i < K * VS; i += kBwThreads) {
     const int kk = i / VS, vv = i % VS;
@@ -176,6 +199,28 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
       for (int i = tid; i < K; i += kBwThreads) sEL[i] = expf(gl);
     }
     // ---- X = tril(K^K^^T.E,-1) (not yet scaled by beta), A = tril(Q^K^^T.E) ---------------------------
+    if constexpr (TC) {
+      // rows 0..63 of the stacked product are K^ (-> X), rows 64..127 are Q^ (-> A); the decay factor is
+      // folded in here (the exact path applies it where an entry is used)
+      for (int tile = warp; tile < 64; tile += 8) {
+        const int m0 = (tile >> 3) * 16, n0 = (tile & 7) * 8;
+        const int i0 = m0 & 63;
+        float d[4] = {0.f, 0.f, 0.f, 0.f};
+        if (n0 <= i0 + 15)
+          tile_gemm_tf32(d, m0, n0, K,
+                         [&](int m, int k) { return m < 64 ? sK[m * ldk + k] : sQ[(m - 64) * ldk + k]; },
+                         [&](int k, int n) { return sK[n * ldk + k]; }, lane);
+        const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int m = m0 + g + (e >> 1) * 8, j = n0 + 2 * t + (e & 1);
+          const int i = m & 63;
+          const float v = d[e] * __expf(fminf(sGs[i] - sGs[j], 0.f));
+          if (m < 64) sX[i * lda + j] = (j < i) ? v : 0.f;
+          else sA[i * lda + j] = (j <= i) ? v : 0.f;
+        }
+      }
+    } else {
     for (int pid = tid; pid < C * C; pid += kBwThreads) {
       const int i = pid / C, j = pid % C;
       float akk = 0.f, aqk = 0.f;
@@ -204,9 +249,24 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
       sA[i * lda + j] = aqk;   // GDN/DeltaNet: the decay factor is applied where the entry is used
       sX[i * lda + j] = (j < i) ? akk : 0.f;
     }
+    }
     __syncthreads();
-    auto Eij = [&](int i, int j) -> float { return KDA ? 1.f : __expf(fminf(sGs[i] - sGs[j], 0.f)); };
+    auto Eij = [&](int i, int j) -> float { return (KDA || TC) ? 1.f : __expf(fminf(sGs[i] - sGs[j], 0.f)); };
     // ---- R = beta V - (beta K^ e^G) S0  (lane = value column, warp = rows) ----------------------------
+    if constexpr (TC) {
+      for (int tile = warp; tile < 4 * (VS / 8); tile += 8) {
+        const int m0 = (tile / (VS / 8)) * 16, n0 = (tile % (VS / 8)) * 8;
+        float d[4] = {0.f, 0.f, 0.f, 0.f};
+        tile_gemm_tf32(d, m0, n0, K, [&](int m, int k) { return sK[m * ldk + k]; },
+                       [&](int k, int n) { return sS0[k * ldv + n]; }, lane);
+        const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int c = m0 + g + (e >> 1) * 8, vv = n0 + 2 * t + (e & 1);
+          sVn[c * ldv + vv] = sBeta[c] * (sV[c * ldv + vv] - sEG[c] * d[e]);
+        }
+      }
+    } else {
     {
       constexpr int RPW = 8;  // rows per warp pass
       const int vv = lane % VS, sub = lane / VS;  // VS = 16: two row streams per warp
@@ -221,6 +281,7 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
         if (!KDA) acc *= sEG[c];
         sVn[c * ldv + vv] = bc * (sV[c * ldv + vv] - acc);
       }
+    }
     }
     __syncthreads();
     // ---- Vn = M^-1 R : forward substitution, 8 lanes per column -----------------------------------------
@@ -238,6 +299,22 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
     }
     __syncthreads();
     // ---- dVn = A^T dO + (K^ e^{G_L-G}) dS1 -----------------------------------------------------------------
+    if constexpr (TC) {
+      for (int tile = warp; tile < 4 * (VS / 8); tile += 8) {
+        const int m0 = (tile / (VS / 8)) * 16, n0 = (tile % (VS / 8)) * 8;
+        float d1[4] = {0.f, 0.f, 0.f, 0.f}, d2[4] = {0.f, 0.f, 0.f, 0.f};
+        tile_gemm_tf32(d1, m0, n0, C, [&](int m, int k) { return sA[k * lda + m]; },   // A^T (already lower, decayed)
+                       [&](int k, int n) { return sdO[k * ldv + n]; }, lane);
+        tile_gemm_tf32(d2, m0, n0, K, [&](int m, int k) { return sK[m * ldk + k]; },
+                       [&](int k, int n) { return sdS[k * ldv + n]; }, lane);
+        const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int c = m0 + g + (e >> 1) * 8, vv = n0 + 2 * t + (e & 1);
+          sdR[c * ldv + vv] = d1[e] + sWd[c] * d2[e];
+        }
+      }
+    } else {
     {
       const int vv = lane % VS, sub = lane / VS;
       constexpr int STREAMS = 32 / VS;
@@ -252,6 +329,7 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
         if (!KDA) acc2 *= sWd[c];
         sdR[c * ldv + vv] = acc + acc2;
       }
+    }
     }
     __syncthreads();
     // ---- dR = M^-T dVn : back substitution ---------------------------------------------------------------------
@@ -281,6 +359,28 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
       if (lane == 0) sdBeta[c] += acc;
     }
     __syncthreads();
+    if constexpr (TC) {
+      for (int tile = warp; tile < 32; tile += 8) {
+        const int m0 = (tile >> 3) * 16, n0 = (tile & 7) * 8;
+        float da[4] = {0.f, 0.f, 0.f, 0.f}, dm[4] = {0.f, 0.f, 0.f, 0.f};
+        if (n0 <= m0 + 15) {
+          tile_gemm_tf32(da, m0, n0, VS, [&](int m, int k) { return sdO[m * ldv + k]; },
+                         [&](int k, int n) { return sVn[n * ldv + k]; }, lane);
+          tile_gemm_tf32(dm, m0, n0, VS, [&](int m, int k) { return sdR[m * ldv + k]; },
+                         [&](int k, int n) { return sVn[n * ldv + k]; }, lane);
+        }
+        const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = m0 + g + (e >> 1) * 8, j = n0 + 2 * t + (e & 1);
+          const float ee = (j <= i) ? __expf(fminf(sGs[i] - sGs[j], 0.f)) : 0.f;
+          const float dmv = -dm[e];
+          if (j < i) atomicAdd(&sdBeta[i], dmv * sX[i * lda + j]);   // sX already carries the decay factor
+          sA[i * lda + j] = (j <= i) ? da[e] * ee : 0.f;
+          sX[i * lda + j] = (j < i) ? sBeta[i] * dmv * ee : 0.f;
+        }
+      }
+    } else {
     for (int pid = tid; pid < C * C; pid += kBwThreads) {
       const int i = pid / C, j = pid % C;   // a warp covers 32 consecutive j of one row i
       float da = 0.f, dm = 0.f;
@@ -296,8 +396,61 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
       sA[i * lda + j] = (j <= i) ? da * e : 0.f;
       sX[i * lda + j] = (j < i) ? sBeta[i] * dm * e : 0.f;
     }
+    }
     __syncthreads();
     // ---- per (row i, channel k): dQ^, dK^, dG, dbeta; lane = channel, warp = rows ----------------------------------
+    if constexpr (TC) {
+      // warp w owns rows 16*(w/2).. and channels 64*(w%2)..: 8 tiles of 16x8, seven products per tile
+      const int g = lane >> 2, t = lane & 3;
+      const int m0 = (warp >> 1) * 16;
+      float dgrow[2] = {0.f, 0.f}, dbrow[2] = {0.f, 0.f}, extra = 0.f;
+      for (int tn = 0; tn < 8; ++tn) {
+        const int n0 = (warp & 1) * 64 + tn * 8;
+        if (n0 >= K) break;
+        float dQg[4] = {0.f, 0.f, 0.f, 0.f}, dKg[4] = {0.f, 0.f, 0.f, 0.f}, dKt[4] = {0.f, 0.f, 0.f, 0.f};
+        float rowA[4] = {0.f, 0.f, 0.f, 0.f}, rowX[4] = {0.f, 0.f, 0.f, 0.f};
+        float colA[4] = {0.f, 0.f, 0.f, 0.f}, colX[4] = {0.f, 0.f, 0.f, 0.f};
+        auto bS0 = [&](int k, int n) { return sS0[n * ldv + k]; };
+        tile_gemm_tf32(dQg, m0, n0, VS, [&](int m, int k) { return sdO[m * ldv + k]; }, bS0, lane);
+        tile_gemm_tf32(dKg, m0, n0, VS, [&](int m, int k) { return sdR[m * ldv + k]; }, bS0, lane);
+        tile_gemm_tf32(dKt, m0, n0, VS, [&](int m, int k) { return sVn[m * ldv + k]; },
+                       [&](int k, int n) { return sdS[n * ldv + k]; }, lane);
+        auto bK = [&](int k, int n) { return sK[k * ldk + n]; };
+        tile_gemm_tf32(rowA, m0, n0, C, [&](int m, int k) { return sA[m * lda + k]; }, bK, lane);
+        tile_gemm_tf32(rowX, m0, n0, C, [&](int m, int k) { return sX[m * lda + k]; }, bK, lane);
+        tile_gemm_tf32(colA, m0, n0, C, [&](int m, int k) { return sA[k * lda + m]; },
+                       [&](int k, int n) { return sQ[k * ldk + n]; }, lane);
+        tile_gemm_tf32(colX, m0, n0, C, [&](int m, int k) { return sX[k * lda + m]; }, bK, lane);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = m0 + g + (e >> 1) * 8, kk = n0 + 2 * t + (e & 1);
+          const float eg = sEG[i], el = sWd[i];
+          const float qh = sQ[i * ldk + kk], kh = sK[i * ldk + kk];
+          const float dq = dQg[e] * eg + rowA[e];
+          const float dk_row = -dKg[e] * sBeta[i] * eg + rowX[e];
+          const float dk_col = dKt[e] * el + colA[e] + colX[e];
+          dbrow[e >> 1] += -dKg[e] * kh * eg;
+          dgrow[e >> 1] += qh * dq + kh * (dk_row - dk_col);
+          extra += dKt[e] * kh * el;
+          const int64_t arow = acc_row0 + t0 + i;
+          p.dq_acc[slice_off + arow * K + kk] = dq;
+          p.dk_acc[slice_off + arow * K + kk] = dk_row + dk_col;
+        }
+      }
+#pragma unroll
+      for (int hrow = 0; hrow < 2; ++hrow) {
+        float db = dbrow[hrow], dg = dgrow[hrow];
+        db += __shfl_xor_sync(0xffffffffu, db, 1); db += __shfl_xor_sync(0xffffffffu, db, 2);
+        dg += __shfl_xor_sync(0xffffffffu, dg, 1); dg += __shfl_xor_sync(0xffffffffu, dg, 2);
+        if (t == 0) {
+          const int i = m0 + g + hrow * 8;
+          atomicAdd(&sdBeta[i], db);
+          if (p.dg_acc) atomicAdd(p.dg_acc + acc_row0 + t0 + i, dg);
+        }
+      }
+      extra = warp_sum(extra);
+      if (lane == 0 && p.dg_acc) atomicAdd(p.dg_acc + acc_row0 + t0 + C - 1, extra);
+    } else {
     {
       const int nkk = K / 32 + (K % 32 ? 1 : 0);
       float extraL[4] = {0.f, 0.f, 0.f, 0.f};  // dG_L contribution, per channel slot of this lane (K <= 128)
@@ -347,8 +500,8 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
           const float dG = qh * dq + kh * (dk_row - dk_col);
           extraL[ks] += dKt * kh * el;
           const int64_t arow = acc_row0 + t0 + i;
-          atomicAdd(p.dq_acc + arow * K + kk, dq);
-          atomicAdd(p.dk_acc + arow * K + kk, dk_row + dk_col);
+          p.dq_acc[slice_off + arow * K + kk] = dq;
+          p.dk_acc[slice_off + arow * K + kk] = dk_row + dk_col;
           if (KDA) atomicAdd(p.dg_acc + arow * K + kk, dG);
           else dgrow += dG;
         }
@@ -371,7 +524,40 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
         }
       }
     }
+    }
     // ---- dS0 = (Q^ e^G)^T dO + e^{G_L} dS1 - (beta K^ e^G)^T dR ; dG_L += e^{G_L} <dS1, S0> -------------------------
+    if constexpr (TC) {
+      // rows = channels k (tiles 16*mt), columns = value columns (8*nt); warp w takes tiles w, w+8, ...
+      constexpr int NT = VS / 8;
+      float keep[4][4];
+      const int g = lane >> 2, t = lane & 3;
+      float tsum = 0.f;
+      int slot = 0;
+      for (int tile = warp; tile < (K / 16) * NT; tile += 8, ++slot) {
+        const int m0 = (tile / NT) * 16, n0 = (tile % NT) * 8;
+        float d[4] = {0.f, 0.f, 0.f, 0.f};
+        tile_gemm_tf32(d, m0, n0, C, [&](int m, int k) { return sEG[k] * sQ[k * ldk + m]; },
+                       [&](int k, int n) { return sdO[k * ldv + n]; }, lane);
+        tile_gemm_tf32(d, m0, n0, C, [&](int m, int k) { return -sEG[k] * sBeta[k] * sK[k * ldk + m]; },
+                       [&](int k, int n) { return sdR[k * ldv + n]; }, lane);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int kk = m0 + g + (e >> 1) * 8, vv = n0 + 2 * t + (e & 1);
+          const float ds1 = sdS[kk * ldv + vv];
+          tsum += ds1 * sS0[kk * ldv + vv] * sEL[kk];
+          keep[slot][e] = d[e] + sEL[kk] * ds1;
+        }
+      }
+      tsum = warp_sum(tsum);
+      if (lane == 0 && p.dg_acc) atomicAdd(p.dg_acc + acc_row0 + t0 + C - 1, tsum);
+      __syncthreads();
+      slot = 0;
+      for (int tile = warp; tile < (K / 16) * NT; tile += 8, ++slot) {
+        const int m0 = (tile / NT) * 16, n0 = (tile % NT) * 8;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sdS[(m0 + g + (e >> 1) * 8) * ldv + n0 + 2 * t + (e & 1)] = keep[slot][e];
+      }
+    } else {
     float ds_new[16];
     {
       const int vv = lane % VS, sub = lane / VS;
@@ -402,6 +588,7 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
       int slot = 0;
       for (int kk = warp * STREAMS + sub; kk < K; kk += 8 * STREAMS, ++slot) sdS[kk * ldv + vv] = ds_new[slot];
     }
+    }
     for (int c = tid; c < rows; c += kBwThreads) atomicAdd(p.dbeta + s_base + (t0 + c) * s_tok, sdBeta[c]);
   }
   __syncthreads();
@@ -418,7 +605,8 @@ struct BwdFinalParams {
   void* dq; void* dk; float* dg;
   const float* dq_acc; const float* dk_acc; const float* dg_acc;
   SeqMap map;
-  int K, C, N, variant, qkv_dt, l2norm;
+  int K, C, N, variant, qkv_dt, l2norm, nvs;
+  int64_t slice_stride;  // floats between the per-slice copies of dq_acc / dk_acc
   float scale;
 };
 
@@ -433,25 +621,38 @@ __global__ void __launch_bounds__(256) bwd_finalize_kernel(const BwdFinalParams 
   const int64_t s_base = p.map.base(b, h, 1), s_tok = p.map.tok(1);
   const int64_t acc_row0 = (int64_t)unit * N * C + t0;
   for (int c = warp; c < rows; c += 8) {
-    const float* aq = p.dq_acc + (acc_row0 + c) * K;
-    const float* ak = p.dk_acc + (acc_row0 + c) * K;
+    const float* aq0 = p.dq_acc + (acc_row0 + c) * K;
+    const float* ak0 = p.dk_acc + (acc_row0 + c) * K;
     const int64_t grow = qk_base + (t0 + c) * qk_tok;
     float nq = 0.f, nk = 0.f, dq_q = 0.f, dk_k = 0.f;
-    for (int i = lane; i < K; i += 32) {
-      const float qv = ld_elem(p.q, grow + i, p.qkv_dt), kv = ld_elem(p.k, grow + i, p.qkv_dt);
-      nq += qv * qv; nk += kv * kv;
-      dq_q += qv * aq[i]; dk_k += kv * ak[i];
+    float aq[8], ak[8];  // this lane's channels (K <= 256), summed over the value slices
+#pragma unroll
+    for (int s8 = 0; s8 < 8; ++s8) {
+      const int i = lane + 32 * s8;
+      aq[s8] = 0.f; ak[s8] = 0.f;
+      if (i < K) {
+        for (int sl = 0; sl < p.nvs; ++sl) {
+          aq[s8] += aq0[sl * p.slice_stride + i];
+          ak[s8] += ak0[sl * p.slice_stride + i];
+        }
+        const float qv = ld_elem(p.q, grow + i, p.qkv_dt), kv = ld_elem(p.k, grow + i, p.qkv_dt);
+        nq += qv * qv; nk += kv * kv;
+        dq_q += qv * aq[s8]; dk_k += kv * ak[s8];
+      }
     }
     nq = sqrtf(warp_sum(nq)); nk = sqrtf(warp_sum(nk));
     dq_q = warp_sum(dq_q); dk_k = warp_sum(dk_k);
-    for (int i = lane; i < K; i += 32) {
-      float dq = p.scale * aq[i], dk = ak[i];
+#pragma unroll
+    for (int s8 = 0; s8 < 8; ++s8) {
+      const int i = lane + 32 * s8;
+      if (i >= K) continue;
+      float dq = p.scale * aq[s8], dk = ak[s8];
       if (p.l2norm) {
         const float qv = ld_elem(p.q, grow + i, p.qkv_dt), kv = ld_elem(p.k, grow + i, p.qkv_dt);
         const float rq = 1.f / (nq + 1e-6f), rk = 1.f / (nk + 1e-6f);
         // y = s x / (n + eps):  dx = s [ dy / (n + eps) - x (x.dy) / (n (n + eps)^2) ]
-        dq = p.scale * (aq[i] * rq - (nq > 0.f ? qv * dq_q * rq * rq / nq : 0.f));
-        dk = ak[i] * rk - (nk > 0.f ? kv * dk_k * rk * rk / nk : 0.f);
+        dq = p.scale * (aq[s8] * rq - (nq > 0.f ? qv * dq_q * rq * rq / nq : 0.f));
+        dk = ak[s8] * rk - (nk > 0.f ? kv * dk_k * rk * rk / nk : 0.f);
       }
       st_elem(p.dq, grow + i, p.qkv_dt, dq);
       st_elem(p.dk, grow + i, p.qkv_dt, dk);
@@ -485,7 +686,8 @@ inline int64_t bwd_workspace_bytes(const DrDesc* d) {
   const int64_t N = (d->T + d->chunk - 1) / d->chunk;
   const int64_t units = (int64_t)d->B * d->H;
   const int64_t rows = units * N * d->chunk;
-  int64_t f = units * N * d->K * d->V + 2 * rows * d->K;
+  const int64_t nvs = (d->V + (d->variant == DR_KDA ? 16 : 32) - 1) / (d->variant == DR_KDA ? 16 : 32);
+  int64_t f = units * N * d->K * d->V + 2 * rows * d->K * nvs;
   if (d->variant == DR_GATED) f += rows;
   if (d->variant == DR_KDA) f += rows * d->K;
   return f * (int64_t)sizeof(float);
@@ -499,11 +701,14 @@ inline cudaError_t launch_bwd(const DrDesc* d, const void* q, const void* k, con
   const int64_t N = (d->T + C - 1) / C, units = (int64_t)d->B * d->H, rows = units * N * C;
   float* ws = reinterpret_cast<float*>(workspace);
   float* ckpt = ws;
-  float* dq_acc = ckpt + units * N * K * V;
-  float* dk_acc = dq_acc + rows * K;
-  float* dg_acc = d->variant == DR_DELTA ? nullptr : dk_acc + rows * K;
-  const size_t acc_floats = 2 * rows * K + (d->variant == DR_GATED ? rows : d->variant == DR_KDA ? rows * K : 0);
-  cudaError_t e = cudaMemsetAsync(dq_acc, 0, acc_floats * sizeof(float), stream);
+  const int VSl = d->variant == DR_KDA ? 16 : 32;
+  const int64_t nvs = (V + VSl - 1) / VSl;
+  float* dq_acc = ckpt + units * N * K * V;      // [nvs][rows][K], one copy per value slice (fully overwritten)
+  float* dk_acc = dq_acc + nvs * rows * K;
+  float* dg_acc = d->variant == DR_DELTA ? nullptr : dk_acc + nvs * rows * K;
+  const size_t dg_floats = d->variant == DR_GATED ? rows : d->variant == DR_KDA ? rows * K : 0;
+  cudaError_t e = cudaSuccess;
+  if (dg_floats) e = cudaMemsetAsync(dg_acc, 0, dg_floats * sizeof(float), stream);
   if (e != cudaSuccess) return e;
   const size_t nbeta = (size_t)units * d->T;
   e = cudaMemsetAsync(dbeta, 0, nbeta * sizeof(float), stream);
@@ -532,15 +737,23 @@ inline cudaError_t launch_bwd(const DrDesc* d, const void* q, const void* k, con
   if (d->variant == DR_KDA) {
     constexpr int VS = 16;
     const size_t smem = bwd_layout(C, K, VS, true).total * sizeof(float);
-    e = cudaFuncSetAttribute(bwd_chunk_kernel<VS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = cudaFuncSetAttribute(bwd_chunk_kernel<VS, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    bwd_chunk_kernel<VS, true><<<(unsigned)(units * ((V + VS - 1) / VS)), kBwThreads, smem, stream>>>(p);
+    bwd_chunk_kernel<VS, true, false><<<(unsigned)(units * ((V + VS - 1) / VS)), kBwThreads, smem, stream>>>(p);
   } else {
     constexpr int VS = 32;
     const size_t smem = bwd_layout(C, K, VS, false).total * sizeof(float);
-    e = cudaFuncSetAttribute(bwd_chunk_kernel<VS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    bwd_chunk_kernel<VS, false><<<(unsigned)(units * ((V + VS - 1) / VS)), kBwThreads, smem, stream>>>(p);
+    // bf16 inputs with whole 16x8 tiles: the products run on the tensor cores (tf32); fp32 inputs stay exact
+    const bool tc = d->qkv_dtype == DR_BF16 && C == 64 && K % 16 == 0;
+    if (tc) {
+      e = cudaFuncSetAttribute(bwd_chunk_kernel<VS, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+      bwd_chunk_kernel<VS, false, true><<<(unsigned)(units * ((V + VS - 1) / VS)), kBwThreads, smem, stream>>>(p);
+    } else {
+      e = cudaFuncSetAttribute(bwd_chunk_kernel<VS, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+      bwd_chunk_kernel<VS, false, false><<<(unsigned)(units * ((V + VS - 1) / VS)), kBwThreads, smem, stream>>>(p);
+    }
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
@@ -551,6 +764,7 @@ inline cudaError_t launch_bwd(const DrDesc* d, const void* q, const void* k, con
   fp.dq_acc = dq_acc; fp.dk_acc = dk_acc; fp.dg_acc = dg_acc;
   fp.map = f.map; fp.K = K; fp.C = C; fp.N = (int)N; fp.variant = d->variant; fp.qkv_dt = d->qkv_dtype;
   fp.l2norm = d->use_qk_l2norm; fp.scale = d->scale;
+  fp.nvs = (int)nvs; fp.slice_stride = rows * K;
   bwd_finalize_kernel<<<(unsigned)(units * N), 256, 0, stream>>>(fp);
   ++*launches;
   return cudaGetLastError();
