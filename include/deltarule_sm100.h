@@ -54,7 +54,10 @@ typedef enum DrStatus {
 typedef enum DrChunkPath {
   DR_PATH_AUTO = 0,   /* tensor-core kernel when the shape qualifies, else the fp32 kernel */
   DR_PATH_FP32 = 1,   /* CUDA-core fp32 chunk kernel (any K,V multiple of 16 up to 256) */
-  DR_PATH_TCGEN05 = 2 /* tcgen05/TMEM bf16-operand kernel (K=V=128, chunk 64, bf16 q,k,v) */
+  DR_PATH_TCGEN05 = 2, /* tcgen05/TMEM bf16-operand kernel (K=V=128, chunk 64, bf16 q,k,v) */
+  DR_PATH_SPLIT = 3    /* two kernels: chunk-parallel intra-chunk pass + tcgen05 state pass over a caller
+                          workspace (dr_workspace_bytes(desc, 0)); every variant, K=V=128, chunk 64, bf16
+                          q,k,v.  AUTO picks it for KDA when the workspace is given. */
 } DrChunkPath;
 
 /* Values the device status word can take (written by kernels, never trapped). */
@@ -95,7 +98,10 @@ uint64_t dr_launch_count(void);
 const char* dr_last_path(void);
 
 /* Bytes of caller-provided scratch that dr_chunk_fwd (op=0) or dr_chunk_bwd (op=1)
- * needs for `desc`; 0 when none is needed.  Negative DrStatus (cast) on a bad desc. */
+ * needs for `desc`; 0 when none is needed.  Negative DrStatus (cast) on a bad desc.
+ * For op=0 the figure is what the path desc->path resolves to would use; a forward that is
+ * given less falls back to a kernel that needs none when path is DR_PATH_AUTO and returns
+ * DR_ERR_WORKSPACE when the path was requested explicitly. */
 int64_t dr_workspace_bytes(const DrDesc* desc, int op);
 
 /*

@@ -25,7 +25,7 @@ _HEADERS = ["dr_common.cuh", "dr_step.cuh", "dr_recurrent.cuh", "dr_chunk_fp32.c
 DR_DELTA, DR_GATED, DR_KDA = 0, 1, 2
 DR_F32, DR_BF16 = 0, 1
 DR_LAYOUT_BHTD, DR_LAYOUT_BTHD = 0, 1
-DR_PATH_AUTO, DR_PATH_FP32, DR_PATH_TCGEN05 = 0, 1, 2
+DR_PATH_AUTO, DR_PATH_FP32, DR_PATH_TCGEN05, DR_PATH_SPLIT = 0, 1, 2, 3
 
 EXPORTS = ["dr_version", "dr_strerror", "dr_last_cuda_error", "dr_launch_count", "dr_last_path",
            "dr_workspace_bytes", "dr_chunk_fwd", "dr_recurrent_fwd", "dr_step", "dr_chunk_bwd",

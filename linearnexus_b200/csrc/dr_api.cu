@@ -8,6 +8,7 @@
 #include "deltarule_sm100.h"
 #include "dr_chunk_fp32.cuh"
 #include "dr_chunk_sm100.cuh"
+#include "dr_kda_sm100.cuh"
 #include "dr_bwd.cuh"
 #include "dr_common.cuh"
 #include "dr_recurrent.cuh"
@@ -45,7 +46,7 @@ int validate_common(const DrDesc* d, bool need_chunk) {
     // The reference raises ValueError when chunk_size % 16 != 0 for Gated DeltaNet and KDA
     // (gated_deltanet.py:318-321, kda.py:438-441); DeltaNet has no such rule.
     if (d->variant != DR_DELTA && d->chunk % 16) return DR_ERR_CHUNK;
-    if (d->path < DR_PATH_AUTO || d->path > DR_PATH_TCGEN05) return DR_ERR_UNSUPPORTED;
+    if (d->path < DR_PATH_AUTO || d->path > DR_PATH_SPLIT) return DR_ERR_UNSUPPORTED;
   }
   return DR_OK;
 }
@@ -77,6 +78,17 @@ bool tcgen05_eligible(const DrDesc* d) {
   return dr::sm100::kAvailable && d->K == 128 && d->V == 128 && d->chunk == 64 &&
          d->qkv_dtype == DR_BF16 && (d->variant == DR_GATED || d->variant == DR_DELTA) &&
          (d->variant == DR_DELTA || d->g_dtype == DR_F32);
+}
+
+// the two-kernel form (chunk-parallel intra pass + tcgen05 state pass over a workspace)
+bool split_eligible(const DrDesc* d) {
+  return dr::sm100::kAvailable && d->K == 128 && d->V == 128 && d->chunk == 64 && d->qkv_dtype == DR_BF16;
+}
+int resolve_chunk_path(const DrDesc* d) {
+  if (d->path != DR_PATH_AUTO) return d->path;
+  if (tcgen05_eligible(d)) return DR_PATH_TCGEN05;
+  if (d->variant == DR_KDA && split_eligible(d)) return DR_PATH_SPLIT;
+  return DR_PATH_FP32;
 }
 
 bool fp32_chunk_eligible(const DrDesc* d) { return d->chunk <= 64 && d->K <= 128; }
@@ -114,7 +126,9 @@ const char* dr_last_path(void) { return tl_path; }
 int64_t dr_workspace_bytes(const DrDesc* d, int op) {
   int s = validate_common(d, true);
   if (s != DR_OK) return s;
-  if (op == 0) return 0;
+  if (op == 0)
+    return (resolve_chunk_path(d) == DR_PATH_SPLIT && split_eligible(d))
+               ? dr::kda::workspace_bytes((int64_t)d->B * d->H, d->T) : 0;
   if (op == 1) return dr::bwd_workspace_bytes(d);
   return DR_ERR_UNSUPPORTED;
 }
@@ -122,15 +136,27 @@ int64_t dr_workspace_bytes(const DrDesc* d, int op) {
 int dr_chunk_fwd(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
                  const float* beta, const float* h0, void* o, float* hT, void* workspace,
                  size_t workspace_bytes, int32_t* status_dev, void* stream) {
-  (void)workspace; (void)workspace_bytes;
   int s = validate_common(d, true);
   if (s != DR_OK) return s;
   s = validate_fwd_ptrs(d, q, k, v, g, beta, h0, o, hT);
   if (s != DR_OK) return s;
   const dr::FwdParams p = make_fwd(d, q, k, v, g, beta, h0, o, hT, status_dev);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  int path = d->path;
-  if (path == DR_PATH_AUTO) path = tcgen05_eligible(d) ? DR_PATH_TCGEN05 : DR_PATH_FP32;
+  int path = resolve_chunk_path(d);
+  if (path == DR_PATH_SPLIT) {
+    if (!split_eligible(d)) return DR_ERR_UNSUPPORTED;
+    const int64_t need = dr::kda::workspace_bytes((int64_t)d->B * d->H, d->T);
+    if (!workspace || (int64_t)workspace_bytes < need || !aligned16(workspace)) {
+      if (d->path != DR_PATH_AUTO) return workspace && !aligned16(workspace) ? DR_ERR_ALIGN : DR_ERR_WORKSPACE;
+      path = DR_PATH_FP32;   // no scratch given: the kernel that needs none
+    } else {
+      tl_path = "chunk_split_tcgen05";
+      int launches = 0;
+      cudaError_t e = dr::kda::launch_chunk(p, workspace, st, &launches);
+      g_launches.fetch_add(launches);
+      return check_cuda(e);
+    }
+  }
   if (path == DR_PATH_TCGEN05) {
     if (!tcgen05_eligible(d)) return DR_ERR_UNSUPPORTED;
     tl_path = "chunk_tcgen05";

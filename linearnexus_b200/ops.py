@@ -20,11 +20,12 @@ import torch
 
 from . import _lib
 from ._lib import (DR_BF16, DR_DELTA, DR_F32, DR_GATED, DR_KDA, DR_LAYOUT_BHTD, DR_LAYOUT_BTHD,
-                   DR_PATH_AUTO, DR_PATH_FP32, DR_PATH_TCGEN05, DrDesc)
+                   DR_PATH_AUTO, DR_PATH_FP32, DR_PATH_TCGEN05, DR_PATH_SPLIT, DrDesc)
 
 Tensor = torch.Tensor
 _NATIVE = {torch.float32: DR_F32, torch.bfloat16: DR_BF16}
-_PATHS = {None: DR_PATH_AUTO, "auto": DR_PATH_AUTO, "fp32": DR_PATH_FP32, "tcgen05": DR_PATH_TCGEN05}
+_PATHS = {None: DR_PATH_AUTO, "auto": DR_PATH_AUTO, "fp32": DR_PATH_FP32, "tcgen05": DR_PATH_TCGEN05,
+          "split": DR_PATH_SPLIT}
 
 # Kernel family used by the chunk entry point when a call does not say; tests set it to
 # force one family ("fp32" / "tcgen05").
@@ -120,8 +121,10 @@ def _seq_forward(kind, variant, q, k, v, g, beta, initial_state, scale, chunk_si
     lib = _lib.load()
     with torch.cuda.device(dev):
         if kind == "chunk":
+            need = int(lib.dr_workspace_bytes(ctypes.byref(d), 0))
+            ws = torch.empty(need, dtype=torch.uint8, device=dev) if need > 0 else None
             st = lib.dr_chunk_fwd(ctypes.byref(d), _ptr(qn), _ptr(kn), _ptr(vn), _ptr(gn), _ptr(bn),
-                                  _ptr(h0), _ptr(o), _ptr(hT), None, 0, None, _stream(dev))
+                                  _ptr(h0), _ptr(o), _ptr(hT), _ptr(ws), max(need, 0), None, _stream(dev))
         else:
             st = lib.dr_recurrent_fwd(ctypes.byref(d), _ptr(qn), _ptr(kn), _ptr(vn), _ptr(gn), _ptr(bn),
                                       _ptr(h0), _ptr(o), _ptr(hT), _stream(dev))
