@@ -50,19 +50,23 @@ constexpr int WS_REC = WS_EGL + 512;       // 82432
 inline int64_t workspace_bytes(int64_t units, int T) { return units * ((T + kC - 1) / kC) * (int64_t)WS_REC; }
 
 // ---- intra-chunk kernel ------------------------------------------------------------------------------------
-constexpr int LDF = 132;   // row stride (floats) of the [64][128] fp32 arrays
-constexpr int LDH = 136;   // row stride (bf16) of the [..][128] bf16 operand arrays (conflict-free fragments)
-constexpr int IN_G = 0;                          // G      fp32 [64][132]
-constexpr int IN_K = IN_G + 64 * LDF * 4;        // k^ (later k^ e^G)
-constexpr int IN_Q = IN_K + 64 * LDF * 4;        // scale q^ (later W staging)
-constexpr int IN_QP = IN_Q + 64 * LDF * 4;       // q+ bf16 [64][136]
-constexpr int IN_KP = IN_QP + 64 * LDH * 2;      // k+ bf16 [64][136]
-constexpr int IN_KM = IN_KP + 64 * LDH * 2;      // k- bf16 [96][136]: versions for sub-blocks 1,2,3 (16,32,48 rows)
-constexpr int IN_AKK = IN_KM + 96 * LDH * 2;     // A_kk fp32 [64][68]
-constexpr int IN_AQK = IN_AKK + 64 * LDT * 4;    // A_qk fp32 [64][68]
-constexpr int IN_T = IN_AQK + 64 * LDT * 4;      // T    fp32 [64][68]
-constexpr int IN_BETA = IN_T + 64 * LDT * 4;     // beta[64]
-constexpr int IN_TOTAL = IN_BETA + 64 * 4;
+// Shared memory is kept under half an SM's worth so that two CTAs are resident and one chunk's latency
+// (global loads, the serial prefix sum, the barriers between phases) hides behind the other's work.  The
+// inputs stay as raw bf16 with their l2-norm factors on the side, and the decayed bf16 operands of the
+// tensor-core products are formed in registers from them (no scaled copies in shared memory).
+constexpr int LDF = 132;   // row stride (floats) of G
+constexpr int LDH = 136;   // row stride (bf16) of the raw q, k rows and of the W staging tile
+constexpr int LDQ = 72;    // row stride (bf16) of A_qk
+constexpr int IN_G = 0;                          // log2(e) G   fp32 [64][132]
+constexpr int IN_K = IN_G + 64 * LDF * 4;        // raw k       bf16 [64][136]
+constexpr int IN_Q = IN_K + 64 * LDH * 2;        // raw q       bf16 [64][136]
+constexpr int IN_AKK = IN_Q + 64 * LDH * 2;      // A_kk fp32 [64][68]; later the W staging tile bf16 [64][136]
+constexpr int IN_T = IN_AKK + 64 * LDT * 4;      // T    fp32 [64][68]
+constexpr int IN_AQK = IN_T + 64 * LDT * 4;      // A_qk bf16 [64][72]
+constexpr int IN_BETA = IN_AQK + 64 * LDQ * 2;   // beta[64], rk[64], rq[64]
+constexpr int IN_TOTAL = IN_BETA + 3 * 64 * 4;
+static_assert(64 * LDT * 4 == 64 * LDH * 2, "the W staging tile reuses the A_kk array");
+static_assert(2 * (IN_TOTAL + 1024) <= 233472, "two CTAs per SM");
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
   asm volatile(
@@ -70,13 +74,20 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float2 bf2(uint32_t u) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u));
+}
 
 // four consecutive elements starting at element index i (a multiple of 4)
 __device__ __forceinline__ void ld4(const void* p, int64_t i, int dt, float (&x)[4]) {
   if (dt == DR_BF16) {
     const uint2 u = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p) + i);
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
-    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+    const float2 a = bf2(u.x), b = bf2(u.y);
     x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
   } else {
     const float4 f = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i);
@@ -101,18 +112,27 @@ __device__ __forceinline__ uint4 pack8(const float (&x)[8]) {
   return u;
 }
 
-__global__ void __launch_bounds__(kThreads, 1) intra_kernel(const FwdParams p, uint8_t* __restrict__ ws) {
+#ifdef DR_PROFILE
+#define KPROF(idx)                                                                                   \
+  do {                                                                                               \
+    if (blockIdx.x == gridDim.x / 2 && tid == 0) { const unsigned long long t_ = clock64(); sm100::g_prof[idx] += t_ - kp0; kp0 = t_; } \
+  } while (0)
+#else
+#define KPROF(idx)
+#endif
+
+__global__ void __launch_bounds__(kThreads, 2) intra_kernel(const FwdParams p, uint8_t* __restrict__ ws) {
   extern __shared__ __align__(1024) uint8_t smem[];
   float* sG = reinterpret_cast<float*>(smem + IN_G);
-  float* sK = reinterpret_cast<float*>(smem + IN_K);
-  float* sQ = reinterpret_cast<float*>(smem + IN_Q);
-  __nv_bfloat16* sQp = reinterpret_cast<__nv_bfloat16*>(smem + IN_QP);
-  __nv_bfloat16* sKp = reinterpret_cast<__nv_bfloat16*>(smem + IN_KP);
-  __nv_bfloat16* sKm = reinterpret_cast<__nv_bfloat16*>(smem + IN_KM);
+  __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem + IN_K);
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem + IN_Q);
   float* sAkk = reinterpret_cast<float*>(smem + IN_AKK);
-  float* sAqk = reinterpret_cast<float*>(smem + IN_AQK);
+  __nv_bfloat16* sWst = reinterpret_cast<__nv_bfloat16*>(smem + IN_AKK);
   float* sT = reinterpret_cast<float*>(smem + IN_T);
+  __nv_bfloat16* sAqk = reinterpret_cast<__nv_bfloat16*>(smem + IN_AQK);
   float* sBeta = reinterpret_cast<float*>(smem + IN_BETA);
+  float* sRk = sBeta + 64;
+  float* sRq = sBeta + 128;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -124,35 +144,57 @@ __global__ void __launch_bounds__(kThreads, 1) intra_kernel(const FwdParams p, u
   const int64_t qk_base = p.map.base(b, h, kD), qk_tok = p.map.tok(kD);
   const int64_t s_base = p.map.base(b, h, 1), s_tok = p.map.tok(1);
   uint8_t* rec = ws + ((int64_t)unit * nchunks + n) * WS_REC;
+  constexpr float kLog2e = 1.4426950408889634f;
+#ifdef DR_PROFILE
+  unsigned long long kp0 = clock64();
+#endif
 
-  // ---- load: k^ = k / (|k| + eps), scale q^, raw log decay; lane = four channels, warp = rows ------------
-  for (int c = warp; c < kC; c += 8) {
-    const bool live = c < rows;
-    float qv[4] = {0.f, 0.f, 0.f, 0.f}, kv[4] = {0.f, 0.f, 0.f, 0.f}, gv[4] = {0.f, 0.f, 0.f, 0.f};
-    if (live) {
-      const int64_t at = qk_base + (t0 + c) * qk_tok + 4 * lane;
-      ld4(p.q, at, DR_BF16, qv);
-      ld4(p.k, at, DR_BF16, kv);
-      if (p.variant == DR_KDA) {
-        ld4(p.g, at, p.g_dt, gv);
-      } else if (p.variant == DR_GATED) {
-        const float gs = ld_elem(p.g, s_base + (t0 + c) * s_tok, p.g_dt);
-        gv[0] = gv[1] = gv[2] = gv[3] = gs;
+  // ---- load: raw k, q rows, their norm factors, the log decay (in log2 units); lane = four channels ---------
+  // (all global loads of the warp's eight rows are issued before the first is used)
+  {
+    uint2 qraw[8], kraw[8];
+    float gv[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int c = warp + 8 * i;
+      qraw[i] = make_uint2(0u, 0u); kraw[i] = make_uint2(0u, 0u);
+      gv[i][0] = gv[i][1] = gv[i][2] = gv[i][3] = 0.f;
+      if (c < rows) {
+        const int64_t at = qk_base + (t0 + c) * qk_tok + 4 * lane;
+        qraw[i] = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.q) + at);
+        kraw[i] = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.k) + at);
+        if (p.variant == DR_KDA) {
+          ld4(p.g, at, p.g_dt, gv[i]);
+        } else if (p.variant == DR_GATED) {
+          const float gs = ld_elem(p.g, s_base + (t0 + c) * s_tok, p.g_dt);
+          gv[i][0] = gv[i][1] = gv[i][2] = gv[i][3] = gs;
+        }
       }
     }
-    float qmul = p.scale, kmul = 1.f;
-    if (p.l2norm) {
-      const float nq = warp_sum(qv[0] * qv[0] + qv[1] * qv[1] + qv[2] * qv[2] + qv[3] * qv[3]);
-      const float nk = warp_sum(kv[0] * kv[0] + kv[1] * kv[1] + kv[2] * kv[2] + kv[3] * kv[3]);
-      qmul = p.scale / (sqrtf(nq) + 1e-6f);
-      kmul = 1.f / (sqrtf(nk) + 1e-6f);
+    float bt = 0.f;
+    if (lane < 8 && warp + 8 * lane < rows) bt = p.beta[s_base + (t0 + warp + 8 * lane) * s_tok];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int c = warp + 8 * i;
+      *reinterpret_cast<uint2*>(sQ + c * LDH + 4 * lane) = qraw[i];
+      *reinterpret_cast<uint2*>(sK + c * LDH + 4 * lane) = kraw[i];
+      *reinterpret_cast<float4*>(sG + c * LDF + 4 * lane) =
+          make_float4(gv[i][0] * kLog2e, gv[i][1] * kLog2e, gv[i][2] * kLog2e, gv[i][3] * kLog2e);
+      float qmul = p.scale, kmul = 1.f;
+      if (p.l2norm) {
+        const float2 q0 = bf2(qraw[i].x), q1 = bf2(qraw[i].y), k0 = bf2(kraw[i].x), k1 = bf2(kraw[i].y);
+        const float nq = warp_sum(q0.x * q0.x + q0.y * q0.y + q1.x * q1.x + q1.y * q1.y);
+        const float nk = warp_sum(k0.x * k0.x + k0.y * k0.y + k1.x * k1.x + k1.y * k1.y);
+        qmul = p.scale / (sqrtf(nq) + 1e-6f);
+        kmul = 1.f / (sqrtf(nk) + 1e-6f);
+      }
+      if (lane == i) {
+        sBeta[c] = bt;
+        sRk[c] = kmul;
+        sRq[c] = qmul;
+      }
     }
-    *reinterpret_cast<float4*>(sQ + c * LDF + 4 * lane) = make_float4(qv[0] * qmul, qv[1] * qmul, qv[2] * qmul, qv[3] * qmul);
-    *reinterpret_cast<float4*>(sK + c * LDF + 4 * lane) = make_float4(kv[0] * kmul, kv[1] * kmul, kv[2] * kmul, kv[3] * kmul);
-    *reinterpret_cast<float4*>(sG + c * LDF + 4 * lane) = make_float4(gv[0], gv[1], gv[2], gv[3]);
-    if (lane == 0) sBeta[c] = live ? p.beta[s_base + (t0 + c) * s_tok] : 0.f;
   }
-  for (int i = tid; i < 64 * LDT; i += kThreads) { sAkk[i] = 0.f; sAqk[i] = 0.f; }
   // V rows -> the record's tile, 16 bytes per piece (coalesced writes)
   {
     const __nv_bfloat16* gv = reinterpret_cast<const __nv_bfloat16*>(p.v);
@@ -168,91 +210,157 @@ __global__ void __launch_bounds__(kThreads, 1) intra_kernel(const FwdParams p, u
     }
   }
   __syncthreads();
+  KPROF(140);
   // ---- G = inclusive prefix sum of the log decay over the rows of the chunk, per channel ---------------------
+  // thread = (8-row segment, four channels): local scan, then the totals of the earlier segments are added;
+  // the segment totals live in the first rows of the (still unused) T array
   {
-    const int ch = tid & 127, half = tid >> 7;
-    float acc = 0.f;
-    for (int r = 0; r < 32; ++r) {
-      acc += sG[(32 * half + r) * LDF + ch];
-      sG[(32 * half + r) * LDF + ch] = acc;
-    }
-    __syncthreads();
-    if (half) {
-      const float add = sG[31 * LDF + ch];
-      for (int r = 32; r < 64; ++r) sG[r * LDF + ch] += add;
-    }
-    __syncthreads();
-  }
-  // ---- bf16 operands of the off-diagonal sub-blocks -----------------------------------------------------------
-  //   q+_i = scale q^_i e^{G_i - G_n(i)},  k+_i = k^_i e^{G_i - G_n(i)},  n(i) = first row of i's sub-block
-  //   k-_{bi,j} = k^_j e^{G_{16 bi} - G_j}  for j < 16 bi
-  for (int idx = tid; idx < 64 * 64; idx += kThreads) {
-    const int i = idx >> 6, c2 = (idx & 63) * 2, nrow = i & ~15;
-    const float e0 = __expf(sG[i * LDF + c2] - sG[nrow * LDF + c2]);
-    const float e1 = __expf(sG[i * LDF + c2 + 1] - sG[nrow * LDF + c2 + 1]);
-    *reinterpret_cast<uint32_t*>(sQp + i * LDH + c2) = tc::pack_bf16(sQ[i * LDF + c2] * e0, sQ[i * LDF + c2 + 1] * e1);
-    *reinterpret_cast<uint32_t*>(sKp + i * LDH + c2) = tc::pack_bf16(sK[i * LDF + c2] * e0, sK[i * LDF + c2 + 1] * e1);
-  }
-  for (int idx = tid; idx < 96 * 64; idx += kThreads) {
-    const int r = idx >> 6, c2 = (idx & 63) * 2;
-    const int bi = r < 16 ? 1 : r < 48 ? 2 : 3;
-    const int j = r - (bi == 1 ? 0 : bi == 2 ? 16 : 48);
-    const float e0 = __expf(sG[16 * bi * LDF + c2] - sG[j * LDF + c2]);
-    const float e1 = __expf(sG[16 * bi * LDF + c2 + 1] - sG[j * LDF + c2 + 1]);
-    *reinterpret_cast<uint32_t*>(sKm + r * LDH + c2) = tc::pack_bf16(sK[j * LDF + c2] * e0, sK[j * LDF + c2 + 1] * e1);
-  }
-  __syncthreads();
-  // ---- off-diagonal 16x16 blocks on mma.sync (bf16): 6 blocks x {k,q} x two 8-column halves = 24 tiles --------
-  for (int x = 0; x < 3; ++x) {
-    const int task = warp * 3 + x;
-    const int bp = task >> 2, isq = (task >> 1) & 1, nt = task & 1;
-    const int bi = bp == 0 ? 1 : bp < 3 ? 2 : 3;
-    const int jb = bp == 0 ? 0 : bp < 3 ? bp - 1 : bp - 3;
-    const __nv_bfloat16* arow = (isq ? sQp : sKp) + (16 * bi + g) * LDH;
-    const __nv_bfloat16* brow = sKm + ((bi == 1 ? 0 : bi == 2 ? 16 : 48) + 16 * jb + 8 * nt + g) * LDH;
-    float d[4] = {0.f, 0.f, 0.f, 0.f};
+    const int seg = tid >> 5, c4 = 4 * (tid & 31);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 loc[8];
 #pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const float4 x = *reinterpret_cast<const float4*>(sG + (8 * seg + r) * LDF + c4);
+      acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+      loc[r] = acc;
+    }
+    *reinterpret_cast<float4*>(sT + seg * 128 + c4) = acc;
+    __syncthreads();
+    float4 pre = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s2 = 0; s2 < seg; ++s2) {
+      const float4 x = *reinterpret_cast<const float4*>(sT + s2 * 128 + c4);
+      pre.x += x.x; pre.y += x.y; pre.z += x.z; pre.w += x.w;
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+      *reinterpret_cast<float4*>(sG + (8 * seg + r) * LDF + c4) =
+          make_float4(loc[r].x + pre.x, loc[r].y + pre.y, loc[r].z + pre.z, loc[r].w + pre.w);
+    __syncthreads();
+  }
+  KPROF(141);
+  // ---- chunk-local products on mma.sync (bf16) -------------------------------------------------------------------
+  // Rows of sub-block bi against the columns of blocks 0..bi; operands  x_i e^{G_i - G_n}  and  k_j e^{G_n - G_j}
+  // (n = first row of bi) are formed in registers; the k and q rows share their decay factors and the column
+  // operand.  For columns of EARLIER blocks both exponents are <= 0.  For the columns of bi itself the second
+  // exponent is positive, at most the decay accumulated over the block; when that exceeds 2^64 in some channel
+  // (never with trained gates, but legal input) the block is redone exactly below.
+  // Eight warp tasks: (bi; 8-column tiles)  3;0-2  3;3-5  3;6-7  2;0-2  2;3-5  1;0-1  1;2-3  0;0-1
+  auto block_unsafe = [&](int blk) -> bool {   // warp-uniform
+    const float4 ga = *reinterpret_cast<const float4*>(sG + (16 * blk) * LDF + 4 * lane);
+    const float4 gb = *reinterpret_cast<const float4*>(sG + (16 * blk + 15) * LDF + 4 * lane);
+    float m = fmaxf(fmaxf(ga.x - gb.x, ga.y - gb.y), fmaxf(ga.z - gb.z, ga.w - gb.w));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    return !(m <= 64.f);
+  };
+  {
+    const int bi = warp < 3 ? 3 : warp < 5 ? 2 : warp < 7 ? 1 : 0;
+    const int nt0 = warp < 3 ? 3 * warp : warp < 5 ? 3 * (warp - 3) : warp < 7 ? 2 * (warp - 5) : 0;
+    const int ntn = (warp == 2 || warp >= 5) ? 2 : 3;
+    const bool skip_diag = block_unsafe(bi);
+    const int r0 = 16 * bi + g, r1 = r0 + 8, nrow = 16 * bi;
+    float dk[3][4], dq[3][4];
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      dk[i][0] = dk[i][1] = dk[i][2] = dk[i][3] = 0.f;
+      dq[i][0] = dq[i][1] = dq[i][2] = dq[i][3] = 0.f;
+    }
+#pragma unroll 2
     for (int ks = 0; ks < 8; ++ks) {
       const int k0 = ks * 16 + 2 * t;
-      uint32_t a[4], bb[2];
-      a[0] = *reinterpret_cast<const uint32_t*>(arow + k0);
-      a[1] = *reinterpret_cast<const uint32_t*>(arow + 8 * LDH + k0);
-      a[2] = *reinterpret_cast<const uint32_t*>(arow + k0 + 8);
-      a[3] = *reinterpret_cast<const uint32_t*>(arow + 8 * LDH + k0 + 8);
-      bb[0] = *reinterpret_cast<const uint32_t*>(brow + k0);
-      bb[1] = *reinterpret_cast<const uint32_t*>(brow + k0 + 8);
-      mma_bf16(d, a, bb);
+      const float2 gn0 = *reinterpret_cast<const float2*>(sG + nrow * LDF + k0);
+      const float2 gn1 = *reinterpret_cast<const float2*>(sG + nrow * LDF + k0 + 8);
+      uint32_t ak[4], aq[4];
+      {
+        const float2 ga = *reinterpret_cast<const float2*>(sG + r0 * LDF + k0);
+        const float2 gb = *reinterpret_cast<const float2*>(sG + r1 * LDF + k0);
+        const float2 gc = *reinterpret_cast<const float2*>(sG + r0 * LDF + k0 + 8);
+        const float2 gd = *reinterpret_cast<const float2*>(sG + r1 * LDF + k0 + 8);
+        const float ea0 = ex2(ga.x - gn0.x), ea1 = ex2(ga.y - gn0.y), eb0 = ex2(gb.x - gn0.x), eb1 = ex2(gb.y - gn0.y);
+        const float ec0 = ex2(gc.x - gn1.x), ec1 = ex2(gc.y - gn1.y), ed0 = ex2(gd.x - gn1.x), ed1 = ex2(gd.y - gn1.y);
+        float2 x;
+        x = bf2(*reinterpret_cast<const uint32_t*>(sK + r0 * LDH + k0));     ak[0] = tc::pack_bf16(x.x * ea0, x.y * ea1);
+        x = bf2(*reinterpret_cast<const uint32_t*>(sK + r1 * LDH + k0));     ak[1] = tc::pack_bf16(x.x * eb0, x.y * eb1);
+        x = bf2(*reinterpret_cast<const uint32_t*>(sK + r0 * LDH + k0 + 8)); ak[2] = tc::pack_bf16(x.x * ec0, x.y * ec1);
+        x = bf2(*reinterpret_cast<const uint32_t*>(sK + r1 * LDH + k0 + 8)); ak[3] = tc::pack_bf16(x.x * ed0, x.y * ed1);
+        x = bf2(*reinterpret_cast<const uint32_t*>(sQ + r0 * LDH + k0));     aq[0] = tc::pack_bf16(x.x * ea0, x.y * ea1);
+        x = bf2(*reinterpret_cast<const uint32_t*>(sQ + r1 * LDH + k0));     aq[1] = tc::pack_bf16(x.x * eb0, x.y * eb1);
+        x = bf2(*reinterpret_cast<const uint32_t*>(sQ + r0 * LDH + k0 + 8)); aq[2] = tc::pack_bf16(x.x * ec0, x.y * ec1);
+        x = bf2(*reinterpret_cast<const uint32_t*>(sQ + r1 * LDH + k0 + 8)); aq[3] = tc::pack_bf16(x.x * ed0, x.y * ed1);
+      }
+#pragma unroll
+      for (int i = 0; i < 3; ++i) {
+        if (i < ntn && !(skip_diag && nt0 + i >= 2 * bi)) {
+          const int j = 8 * (nt0 + i) + g;
+          const float2 gj0 = *reinterpret_cast<const float2*>(sG + j * LDF + k0);
+          const float2 gj1 = *reinterpret_cast<const float2*>(sG + j * LDF + k0 + 8);
+          const float2 y0 = bf2(*reinterpret_cast<const uint32_t*>(sK + j * LDH + k0));
+          const float2 y1 = bf2(*reinterpret_cast<const uint32_t*>(sK + j * LDH + k0 + 8));
+          uint32_t bb[2];
+          bb[0] = tc::pack_bf16(y0.x * ex2(gn0.x - gj0.x), y0.y * ex2(gn0.y - gj0.y));
+          bb[1] = tc::pack_bf16(y1.x * ex2(gn1.x - gj1.x), y1.y * ex2(gn1.y - gj1.y));
+          mma_bf16(dk[i], ak, bb);
+          mma_bf16(dq[i], aq, bb);
+        }
+      }
     }
-    float* out = (isq ? sAqk : sAkk) + (16 * bi + g) * LDT + 16 * jb + 8 * nt + 2 * t;
-    *reinterpret_cast<float2*>(out) = make_float2(d[0], d[1]);
-    *reinterpret_cast<float2*>(out + 8 * LDT) = make_float2(d[2], d[3]);
+    const float fk0 = sRk[r0], fk1 = sRk[r1], fq0 = sRq[r0], fq1 = sRq[r1];
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      if (i < ntn) {
+        const int c = 8 * (nt0 + i) + 2 * t;
+        const float c0 = sRk[c], c1 = sRk[c + 1];
+        *reinterpret_cast<uint32_t*>(sAqk + r0 * LDQ + c) = tc::pack_bf16(dq[i][0] * fq0 * c0, dq[i][1] * fq0 * c1);
+        *reinterpret_cast<uint32_t*>(sAqk + r1 * LDQ + c) = tc::pack_bf16(dq[i][2] * fq1 * c0, dq[i][3] * fq1 * c1);
+        *reinterpret_cast<float2*>(sAkk + r0 * LDT + c) = make_float2(dk[i][0] * fk0 * c0, dk[i][1] * fk0 * c1);
+        *reinterpret_cast<float2*>(sAkk + r1 * LDT + c) = make_float2(dk[i][2] * fk1 * c0, dk[i][3] * fk1 * c1);
+      }
+    }
   }
-  // ---- diagonal 16x16 blocks exactly (fp32): warp = two rows of every block, lane = four channels -------------
-  for (int blk = 0; blk < 4; ++blk) {
-#pragma unroll 1
-    for (int sel = 0; sel < 2; ++sel) {
-      const int rr = sel ? 15 - warp : warp;
-      const int i = 16 * blk + rr;
-      const float4 qi = *reinterpret_cast<const float4*>(sQ + i * LDF + 4 * lane);
-      const float4 ki = *reinterpret_cast<const float4*>(sK + i * LDF + 4 * lane);
-      const float4 gi = *reinterpret_cast<const float4*>(sG + i * LDF + 4 * lane);
-      for (int jg = 0; jg <= rr; jg += 4) {
+  KPROF(142);
+  // ---- diagonal 16x16 blocks exactly (fp32), only for blocks whose decay range is too wide for the product form ----
+  // Two warps per block, 64 channels each, two channels per lane; the 16 rows of k and the per-row decay
+  // d_r = e^{G_r - G_{r-1}} stay in registers, so e^{G_i - G_j} is a running product (no exponentials per pair).
+  // Partial sums of the two channel halves meet in a scratch array (the T array, not yet in use).
+  __syncthreads();   // the tensor-core tasks have written their (possibly non-finite) entries of these blocks
+  if (block_unsafe(warp >> 1)) {
+    const int blk = warp >> 1, half = warp & 1, ch0 = 64 * half + 2 * lane;
+    float2 kr[16], dd[16];
+    {
+      float2 gprev = make_float2(0.f, 0.f);
+#pragma unroll
+      for (int r = 0; r < 16; ++r) {
+        const int row = 16 * blk + r;
+        kr[r] = bf2(*reinterpret_cast<const uint32_t*>(sK + row * LDH + ch0));
+        const float2 gg = *reinterpret_cast<const float2*>(sG + row * LDF + ch0);
+        dd[r] = make_float2(ex2(gg.x - gprev.x), ex2(gg.y - gprev.y));   // dd[0] is never used
+        gprev = gg;
+      }
+    }
+    float* part = sT + (half * 4 + blk) * 512;   // [i][j][kk,qk]
+    const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4;
+    const int idx = (b4 ? 4 : 0) + (b3 ? 2 : 0) + (b2 ? 1 : 0);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float2 qi = bf2(*reinterpret_cast<const uint32_t*>(sQ + (16 * blk + i) * LDH + ch0));
+      const float2 ki = kr[i];
+      float2 P = make_float2(1.f, 1.f);
+#pragma unroll
+      for (int jg = (i & ~3); jg >= 0; jg -= 4) {
         float v[8];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          v[u] = 0.f; v[u + 4] = 0.f;
-          if (jg + u <= rr) {
-            const int j = 16 * blk + jg + u;
-            const float4 kj = *reinterpret_cast<const float4*>(sK + j * LDF + 4 * lane);
-            const float4 gj = *reinterpret_cast<const float4*>(sG + j * LDF + 4 * lane);
-            const float w0 = kj.x * __expf(gi.x - gj.x), w1 = kj.y * __expf(gi.y - gj.y);
-            const float w2 = kj.z * __expf(gi.z - gj.z), w3 = kj.w * __expf(gi.w - gj.w);
-            v[u] = ki.x * w0 + ki.y * w1 + ki.z * w2 + ki.w * w3;
-            v[u + 4] = qi.x * w0 + qi.y * w1 + qi.z * w2 + qi.w * w3;
+        for (int u = 3; u >= 0; --u) {
+          const int j = jg + u;
+          if (j <= i) {
+            const float w0 = kr[j].x * P.x, w1 = kr[j].y * P.y;
+            v[u] = ki.x * w0 + ki.y * w1;
+            v[u + 4] = qi.x * w0 + qi.y * w1;
+            if (j > 0) { P.x *= dd[j].x; P.y *= dd[j].y; }
+          } else {
+            v[u] = 0.f; v[u + 4] = 0.f;
           }
         }
         // eight sums over the 32 lanes in nine shuffles: each level halves the number of live values
-        const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4;
         float x4[4], y2[2];
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4) {
@@ -268,56 +376,84 @@ __global__ void __launch_bounds__(kThreads, 1) intra_kernel(const FwdParams p, u
         z += __shfl_xor_sync(0xffffffffu, z, 2);
         z += __shfl_xor_sync(0xffffffffu, z, 1);
         if (t == 0) {
-          const int idx = (b4 ? 4 : 0) + (b3 ? 2 : 0) + (b2 ? 1 : 0);
-          const int jj = jg + (idx & 3);
-          if (idx >= 4) { if (jj <= rr) sAqk[i * LDT + 16 * blk + jj] = z; }
-          else if (jj < rr) sAkk[i * LDT + 16 * blk + jj] = z;
+          const int j = jg + (idx & 3);
+          if (j <= i) part[(i * 16 + j) * 2 + (idx >> 2)] = z;
         }
+      }
+    }
+    asm volatile("bar.sync %0, 64;" ::"r"(2 + blk) : "memory");   // the two warps of this block
+    const float* p0 = sT + blk * 512;
+    const float* p1 = sT + (4 + blk) * 512;
+    for (int e = lane; e < 256; e += 32) {
+      const int i = e >> 4, j = e & 15, gi = 16 * blk + i, gj = 16 * blk + j;
+      if (half == 0) {
+        if (j < i) sAkk[gi * LDT + gj] = (p0[2 * e] + p1[2 * e]) * sRk[gi] * sRk[gj];
+      } else if (j <= i) {
+        sAqk[gi * LDQ + gj] = __float2bfloat16_rn((p0[2 * e + 1] + p1[2 * e + 1]) * sRq[gi] * sRk[gj]);
       }
     }
   }
   __syncthreads();
+  KPROF(143);
   // ---- T = (I + diag(beta) A_kk)^-1 -----------------------------------------------------------------------------
   sm100::block_inverse_64(sAkk, sBeta, sT, tid);
+  KPROF(144);
   // ---- record tiles: T diag(beta), A_qk, Qg = scale q^ e^G, Kd = k^ e^{G_L - G}, e^{G_L} ------------------------
 #pragma unroll
   for (int it = 0; it < 2; ++it) {
     const int piece = tid + kThreads * it;
     int row, col;
     piece64(piece, row, col);
-    float a[8], c[8];
+    float a[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       const int j = col + e;
       a[e] = j <= row ? sT[row * LDT + j] * sBeta[j] : 0.f;
-      c[e] = j <= row ? sAqk[row * LDT + j] : 0.f;
     }
     *reinterpret_cast<uint4*>(rec + WS_TB + piece * 16) = pack8(a);
-    *reinterpret_cast<uint4*>(rec + WS_AQK + piece * 16) = pack8(c);
+    uint4 q = *reinterpret_cast<const uint4*>(sAqk + row * LDQ + col);
+    uint32_t* qw = reinterpret_cast<uint32_t*>(&q);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {   // keep j <= row
+      const int j = col + 2 * e;
+      if (j > row) qw[e] = 0u;
+      else if (j + 1 > row) qw[e] &= 0x0000ffffu;
+    }
+    *reinterpret_cast<uint4*>(rec + WS_AQK + piece * 16) = q;
   }
 #pragma unroll
   for (int it = 0; it < 4; ++it) {
     const int piece = tid + kThreads * it;
     int row, col;
     piece128(piece, row, col);
-    float a[8], c[8];
+    const uint4 uq = *reinterpret_cast<const uint4*>(sQ + row * LDH + col);
+    const uint4 uk = *reinterpret_cast<const uint4*>(sK + row * LDH + col);
+    const uint32_t* wq = reinterpret_cast<const uint32_t*>(&uq);
+    const uint32_t* wk = reinterpret_cast<const uint32_t*>(&uk);
+    const float rq = sRq[row], rk = sRk[row];
+    float a[8], c[8], kg[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const float gg = sG[row * LDF + col + e];
-      a[e] = sQ[row * LDF + col + e] * __expf(gg);
-      c[e] = sK[row * LDF + col + e] * __expf(sG[63 * LDF + col + e] - gg);
+    for (int e = 0; e < 4; ++e) {
+      const float2 gg = *reinterpret_cast<const float2*>(sG + row * LDF + col + 2 * e);
+      const float2 gl = *reinterpret_cast<const float2*>(sG + 63 * LDF + col + 2 * e);
+      const float2 qq = bf2(wq[e]), kk = bf2(wk[e]);
+      const float e0 = ex2(gg.x), e1 = ex2(gg.y);
+      a[2 * e] = qq.x * rq * e0;
+      a[2 * e + 1] = qq.y * rq * e1;
+      c[2 * e] = kk.x * rk * ex2(gl.x - gg.x);
+      c[2 * e + 1] = kk.y * rk * ex2(gl.y - gg.y);
+      kg[2 * e] = kk.x * rk * e0;
+      kg[2 * e + 1] = kk.y * rk * e1;
     }
     *reinterpret_cast<uint4*>(rec + WS_QG + piece * 16) = pack8(a);
     *reinterpret_cast<uint4*>(rec + WS_KD + piece * 16) = pack8(c);
+    *reinterpret_cast<uint4*>(sQ + row * LDH + col) = pack8(kg);   // k^ e^G for the W product (q is dead)
   }
-  if (tid < kD) reinterpret_cast<float*>(rec + WS_EGL)[tid] = __expf(sG[63 * LDF + tid]);
+  if (tid < kD) reinterpret_cast<float*>(rec + WS_EGL)[tid] = ex2(sG[63 * LDF + tid]);
   __syncthreads();
-  for (int idx = tid; idx < 64 * 128; idx += kThreads) {
-    const int r = idx >> 7, c = idx & 127;
-    sK[r * LDF + c] *= __expf(sG[r * LDF + c]);
-  }
-  __syncthreads();
-  // ---- W = (T diag(beta)) (k^ e^G): 64x128x64 on mma.sync (tf32); warp = 16 rows x 64 channels -------------------
+  KPROF(145);
+  // ---- W = (T diag(beta)) (k^ e^G): 64x128x64 on mma.sync (tf32); warp = 16 rows x 64 channels ----------------------
+  // (A_kk is dead after the inverse: its array takes the bf16 staging tile of W; bf16 -> tf32 is exact)
   {
     const int m0 = (warp >> 1) * 16, nb = (warp & 1) * 64;
     float d[8][4];
@@ -326,23 +462,25 @@ __global__ void __launch_bounds__(kThreads, 1) intra_kernel(const FwdParams p, u
     const int r0 = m0 + g, r1 = r0 + 8;
     for (int ks = 0; ks * 8 <= m0 + 15; ++ks) {
       const int k0 = ks * 8 + t, k1 = k0 + 4;
+      const float s0 = sBeta[k0], s1 = sBeta[k1];
       uint32_t a[4];
-      a[0] = sm100::to_tf32(k0 <= r0 ? sT[r0 * LDT + k0] * sBeta[k0] : 0.f);
-      a[1] = sm100::to_tf32(k0 <= r1 ? sT[r1 * LDT + k0] * sBeta[k0] : 0.f);
-      a[2] = sm100::to_tf32(k1 <= r0 ? sT[r0 * LDT + k1] * sBeta[k1] : 0.f);
-      a[3] = sm100::to_tf32(k1 <= r1 ? sT[r1 * LDT + k1] * sBeta[k1] : 0.f);
+      a[0] = sm100::to_tf32(k0 <= r0 ? sT[r0 * LDT + k0] * s0 : 0.f);
+      a[1] = sm100::to_tf32(k0 <= r1 ? sT[r1 * LDT + k0] * s0 : 0.f);
+      a[2] = sm100::to_tf32(k1 <= r0 ? sT[r0 * LDT + k1] * s1 : 0.f);
+      a[3] = sm100::to_tf32(k1 <= r1 ? sT[r1 * LDT + k1] * s1 : 0.f);
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
+        const int ch = nb + nt * 8 + g;
         uint32_t bb[2];
-        bb[0] = sm100::to_tf32(sK[k0 * LDF + nb + nt * 8 + g]);
-        bb[1] = sm100::to_tf32(sK[k1 * LDF + nb + nt * 8 + g]);
+        bb[0] = (uint32_t)reinterpret_cast<const uint16_t*>(sQ)[k0 * LDH + ch] << 16;
+        bb[1] = (uint32_t)reinterpret_cast<const uint16_t*>(sQ)[k1 * LDH + ch] << 16;
         sm100::mma_tf32(d[nt], a, bb);
       }
     }
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
-      *reinterpret_cast<float2*>(sQ + r0 * LDF + nb + nt * 8 + 2 * t) = make_float2(d[nt][0], d[nt][1]);
-      *reinterpret_cast<float2*>(sQ + r1 * LDF + nb + nt * 8 + 2 * t) = make_float2(d[nt][2], d[nt][3]);
+      *reinterpret_cast<uint32_t*>(sWst + r0 * LDH + nb + nt * 8 + 2 * t) = tc::pack_bf16(d[nt][0], d[nt][1]);
+      *reinterpret_cast<uint32_t*>(sWst + r1 * LDH + nb + nt * 8 + 2 * t) = tc::pack_bf16(d[nt][2], d[nt][3]);
     }
   }
   __syncthreads();
@@ -351,11 +489,9 @@ __global__ void __launch_bounds__(kThreads, 1) intra_kernel(const FwdParams p, u
     const int piece = tid + kThreads * it;
     int row, col;
     piece128(piece, row, col);
-    float a[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) a[e] = sQ[row * LDF + col + e];
-    *reinterpret_cast<uint4*>(rec + WS_W + piece * 16) = pack8(a);
+    *reinterpret_cast<uint4*>(rec + WS_W + piece * 16) = *reinterpret_cast<const uint4*>(sWst + row * LDH + col);
   }
+  KPROF(146);
 }
 
 // ---- state kernel ----------------------------------------------------------------------------------------------

@@ -60,12 +60,15 @@ def test_kda_split_parity(B, H, T, h0, g_dtype):
     assert _rel(o, o3) <= BF16_TOL and _rel(hT, hT3) <= BF16_TOL
 
 
-def test_kda_split_strong_decay():
-    """Log decay of -3 per token and channel: e^{-G} over a chunk would overflow fp32 (e^{192}); the
-    sub-block form keeps every exponent <= 0."""
+@pytest.mark.parametrize("decay", [-2.0, -3.0, -8.0, -40.0])
+def test_kda_split_strong_decay(decay):
+    """Strong log decay per token and channel: e^{-G} over a chunk would overflow fp32.  Off-diagonal
+    sub-blocks keep every exponent <= 0; a diagonal sub-block whose decay range passes 2^64 in some
+    channel (here: -3 and below) is recomputed exactly, the others use the product form."""
     inp = O.make_inputs("kda", 1, 2, 192, 128, 128, seed=5, io_dtype=torch.bfloat16, h0_std=0.02)
-    inp["g"] = torch.full_like(inp["g"], -3.0)
+    inp["g"] = torch.full_like(inp["g"], decay)
     inp["g"][:, :, ::7] = -0.01
+    inp["g"][:, :, 64:96, :64] = -0.05   # one sub-block pair mild in half of the channels
     o, hT = _run("kda", inp, "split")
     torch.cuda.synchronize()
     ro, rS = _truth("kda", inp)
