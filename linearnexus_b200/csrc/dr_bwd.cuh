@@ -49,6 +49,73 @@ __device__ __forceinline__ void tile_gemm_tf32(float (&d)[4], int m0, int n0, in
   }
 }
 
+// Row-panel products on the same path: the warp owns 16 rows (m0..) and NT consecutive 8-column tiles
+// (n0..); the A fragment is fetched once per k-step and reused for every tile, and products that share
+// their B operand share its fetch too.  Operands are passed as raw fp32 bits (the tensor core ignores the
+// low mantissa bits: truncation to tf32).  k runs over [kb, ke) in steps of 8.
+template <int NT, class AF, class BF>
+__device__ __forceinline__ void rgemm(float (&d)[NT][4], int m0, int n0, int kb, int ke, AF a, BF b, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  for (int k0 = kb; k0 < ke; k0 += 8) {
+    uint32_t af[4];
+    af[0] = __float_as_uint(a(m0 + g, k0 + t));
+    af[1] = __float_as_uint(a(m0 + g + 8, k0 + t));
+    af[2] = __float_as_uint(a(m0 + g, k0 + t + 4));
+    af[3] = __float_as_uint(a(m0 + g + 8, k0 + t + 4));
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      uint32_t bf[2];
+      bf[0] = __float_as_uint(b(k0 + t, n0 + 8 * nt + g));
+      bf[1] = __float_as_uint(b(k0 + t + 4, n0 + 8 * nt + g));
+      sm100::mma_tf32(d[nt], af, bf);
+    }
+  }
+}
+template <int NT, class AF1, class AF2, class BF>
+__device__ __forceinline__ void rgemm2(float (&d1)[NT][4], float (&d2)[NT][4], int m0, int n0, int kb, int ke, AF1 a1,
+                                       AF2 a2, BF b, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  for (int k0 = kb; k0 < ke; k0 += 8) {
+    uint32_t af1[4], af2[4];
+    af1[0] = __float_as_uint(a1(m0 + g, k0 + t));     af2[0] = __float_as_uint(a2(m0 + g, k0 + t));
+    af1[1] = __float_as_uint(a1(m0 + g + 8, k0 + t)); af2[1] = __float_as_uint(a2(m0 + g + 8, k0 + t));
+    af1[2] = __float_as_uint(a1(m0 + g, k0 + t + 4)); af2[2] = __float_as_uint(a2(m0 + g, k0 + t + 4));
+    af1[3] = __float_as_uint(a1(m0 + g + 8, k0 + t + 4)); af2[3] = __float_as_uint(a2(m0 + g + 8, k0 + t + 4));
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      uint32_t bf[2];
+      bf[0] = __float_as_uint(b(k0 + t, n0 + 8 * nt + g));
+      bf[1] = __float_as_uint(b(k0 + t + 4, n0 + 8 * nt + g));
+      sm100::mma_tf32(d1[nt], af1, bf);
+      sm100::mma_tf32(d2[nt], af2, bf);
+    }
+  }
+}
+template <int NT, class AF1, class AF2, class AF3, class BF>
+__device__ __forceinline__ void rgemm3(float (&d1)[NT][4], float (&d2)[NT][4], float (&d3)[NT][4], int m0, int n0, int kb,
+                                       int ke, AF1 a1, AF2 a2, AF3 a3, BF b, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  for (int k0 = kb; k0 < ke; k0 += 8) {
+    uint32_t af1[4], af2[4], af3[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int m = m0 + g + (e & 1) * 8, k = k0 + t + (e >> 1) * 4;
+      af1[e] = __float_as_uint(a1(m, k));
+      af2[e] = __float_as_uint(a2(m, k));
+      af3[e] = __float_as_uint(a3(m, k));
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      uint32_t bf[2];
+      bf[0] = __float_as_uint(b(k0 + t, n0 + 8 * nt + g));
+      bf[1] = __float_as_uint(b(k0 + t + 4, n0 + 8 * nt + g));
+      sm100::mma_tf32(d1[nt], af1, bf);
+      sm100::mma_tf32(d2[nt], af2, bf);
+      sm100::mma_tf32(d3[nt], af3, bf);
+    }
+  }
+}
+
 struct BwdParams {
   const void* q; const void* k; const void* v; const void* g; const float* beta;
   const void* d_o; const float* d_hT;
@@ -62,18 +129,21 @@ struct BwdParams {
 
 struct BwdSmem {
   int ldk, lda, ldv;
-  size_t q, k, g, x, a, v, d_o, vn, dr, s0, ds, gs, eg, wd, beta, dbeta, el, total;
+  size_t q, k, g, x, a, t, v, d_o, vn, dr, s0, ds, gs, eg, wd, beta, dbeta, el, total;
 };
 
-__host__ __device__ inline BwdSmem bwd_layout(int C, int K, int VS, bool kda) {
+// tc: strides that keep tensor-core fragment fetches (row = lane/4, column = lane%4) conflict-free and 16-byte
+// aligned, plus the array of the explicit inverse T = M^-1 (row stride sm100::LDT)
+__host__ __device__ inline BwdSmem bwd_layout(int C, int K, int VS, bool kda, bool tc = false) {
   BwdSmem L;
-  L.ldk = K + 4; L.lda = C + 1; L.ldv = VS + 1;
+  L.ldk = K + 4; L.lda = tc ? sm100::LDT : C + 1; L.ldv = tc ? VS + 4 : VS + 1;
   size_t o = 0;
   L.q = o; o += (size_t)C * L.ldk;
   L.k = o; o += (size_t)C * L.ldk;
   L.g = o; o += kda ? (size_t)C * L.ldk : 0;
   L.x = o; o += (size_t)C * L.lda;
   L.a = o; o += (size_t)C * L.lda;
+  L.t = o; o += tc ? (size_t)C * L.lda : 0;
   L.v = o; o += (size_t)C * L.ldv;
   L.d_o = o; o += (size_t)C * L.ldv;
   L.vn = o; o += (size_t)C * L.ldv;
@@ -86,15 +156,24 @@ __host__ __device__ inline BwdSmem bwd_layout(int C, int K, int VS, bool kda) {
   return L;
 }
 
+#ifdef DR_PROFILE
+#define BPROF(idx)                                                                                  \
+  do {                                                                                              \
+    if (blockIdx.x == gridDim.x / 2 && tid == 0) { const unsigned long long t_ = clock64(); sm100::g_prof[idx] += t_ - bp0; bp0 = t_; } \
+  } while (0)
+#else
+#define BPROF(idx)
+#endif
+
 // TC: the products run on mma.sync tf32 (bf16 inputs: well inside their 2e-2 tolerance); otherwise exact fp32.
 template <int VS, bool KDA, bool TC>
 __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p) {
   extern __shared__ __align__(16) float smem[];
   const int K = p.K, V = p.V, C = p.C, T = p.map.T, N = p.N;
   const bool gated = p.variant == DR_GATED;
-  const BwdSmem L = bwd_layout(C, K, VS, KDA);
+  const BwdSmem L = bwd_layout(C, K, VS, KDA, TC);
   float* sQ = smem + L.q;      float* sK = smem + L.k;     float* sG = smem + L.g;
-  float* sX = smem + L.x;      float* sA = smem + L.a;
+  float* sX = smem + L.x;      float* sA = smem + L.a;      float* sT = smem + L.t;
   float* sV = smem + L.v;      float* sdO = smem + L.d_o;  float* sVn = smem + L.vn;  float* sdR = smem + L.dr;
   float* sS0 = smem + L.s0;    float* sdS = smem + L.ds;
   float* sGs = smem + L.gs;    float* sEG = smem + L.eg;   float* sWd = smem + L.wd;
@@ -119,11 +198,112 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
     sdS[kk * ldv + vv] = (p.d_hT && v0 + vv < V) ? p.d_hT[((int64_t)unit * K + kk) * V + v0 + vv] : 0.f;
   }
 
+#ifdef DR_PROFILE
+  unsigned long long bp0 = clock64();
+#endif
   for (int n = N - 1; n >= 0; --n) {
     const int t0 = n * C;
     const int rows = min(C, T - t0);
     __syncthreads();
+    BPROF(150);
     // ---- stage q^, k^ (fp32, normalised / scaled), g, beta, v, dO, S0 --------------------------------
+    if constexpr (TC) {
+      // bf16 inputs: 8-byte (q, k) and 16-byte (v, dO, S0) accesses, every global load of the warp's eight rows
+      // issued before the first is used (C = 64: rows warp, warp + 8, ...)
+      const __nv_bfloat16* gq = reinterpret_cast<const __nv_bfloat16*>(p.q);
+      const __nv_bfloat16* gk = reinterpret_cast<const __nv_bfloat16*>(p.k);
+      uint2 qr[8][2], kr[8][2];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int c = warp + 8 * i;
+#pragma unroll
+        for (int ps = 0; ps < 2; ++ps) {
+          const int ch = 128 * ps + 4 * lane;
+          qr[i][ps] = make_uint2(0u, 0u); kr[i][ps] = make_uint2(0u, 0u);
+          if (c < rows && ch < K) {
+            qr[i][ps] = *reinterpret_cast<const uint2*>(gq + qk_base + (t0 + c) * qk_tok + ch);
+            kr[i][ps] = *reinterpret_cast<const uint2*>(gk + qk_base + (t0 + c) * qk_tok + ch);
+          }
+        }
+      }
+      float bt = 0.f, gt_ = 0.f;
+      if (lane < 8 && warp + 8 * lane < rows) {
+        bt = p.beta[s_base + (t0 + warp + 8 * lane) * s_tok];
+        if (gated) gt_ = ld_elem(p.g, s_base + (t0 + warp + 8 * lane) * s_tok, p.g_dt);
+      }
+      uint4 vr = make_uint4(0u, 0u, 0u, 0u), dor = make_uint4(0u, 0u, 0u, 0u);
+      const int vrow = tid / (VS / 8), vpc = tid % (VS / 8);
+      if (tid < C * (VS / 8) && vrow < rows && v0 + 8 * vpc < V) {
+        vr = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.v) + v_base + (t0 + vrow) * v_tok + v0 + 8 * vpc);
+        dor = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.d_o) + v_base + (t0 + vrow) * v_tok + v0 + 8 * vpc);
+      }
+      float4 s0r[8];   // K <= 256, VS = 32: at most eight 16-byte pieces of the checkpoint slice per thread
+      {
+        const float* ck = p.ckpt + ((int64_t)unit * N + n) * K * V;
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int i = tid + it * kBwThreads;
+          const int kk = i / (VS / 4), j4 = 4 * (i % (VS / 4));
+          s0r[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (i < K * (VS / 4) && v0 + j4 < V) s0r[it] = *reinterpret_cast<const float4*>(ck + (int64_t)kk * V + v0 + j4);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int c = warp + 8 * i;
+        float qf[2][4], kf[2][4];
+        float nq = 0.f, nk = 0.f;
+#pragma unroll
+        for (int ps = 0; ps < 2; ++ps) {
+          const float2 a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qr[i][ps].x));
+          const float2 a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qr[i][ps].y));
+          const float2 b0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr[i][ps].x));
+          const float2 b1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr[i][ps].y));
+          qf[ps][0] = a0.x; qf[ps][1] = a0.y; qf[ps][2] = a1.x; qf[ps][3] = a1.y;
+          kf[ps][0] = b0.x; kf[ps][1] = b0.y; kf[ps][2] = b1.x; kf[ps][3] = b1.y;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { nq += qf[ps][e] * qf[ps][e]; nk += kf[ps][e] * kf[ps][e]; }
+        }
+        float qmul = p.scale, kmul = 1.f;
+        if (p.l2norm) {
+          nq = warp_sum(nq);
+          nk = warp_sum(nk);
+          qmul = p.scale / (sqrtf(nq) + 1e-6f);
+          kmul = 1.f / (sqrtf(nk) + 1e-6f);
+        }
+#pragma unroll
+        for (int ps = 0; ps < 2; ++ps) {
+          const int ch = 128 * ps + 4 * lane;
+          if (ch < K) {
+            *reinterpret_cast<float4*>(sQ + c * ldk + ch) =
+                make_float4(qf[ps][0] * qmul, qf[ps][1] * qmul, qf[ps][2] * qmul, qf[ps][3] * qmul);
+            *reinterpret_cast<float4*>(sK + c * ldk + ch) =
+                make_float4(kf[ps][0] * kmul, kf[ps][1] * kmul, kf[ps][2] * kmul, kf[ps][3] * kmul);
+          }
+        }
+        if (lane == i) {
+          sBeta[c] = bt;
+          sGs[c] = gt_;
+          sdBeta[c] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int i = tid + it * kBwThreads;
+        if (i < K * (VS / 4)) *reinterpret_cast<float4*>(sS0 + (i / (VS / 4)) * ldv + 4 * (i % (VS / 4))) = s0r[it];
+      }
+      if (tid < C * (VS / 8)) {
+        const uint32_t* wv = reinterpret_cast<const uint32_t*>(&vr);
+        const uint32_t* wo = reinterpret_cast<const uint32_t*>(&dor);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wv[e]));
+          const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wo[e]));
+          *reinterpret_cast<float2*>(sV + vrow * ldv + 8 * vpc + 2 * e) = x;
+          *reinterpret_cast<float2*>(sdO + vrow * ldv + 8 * vpc + 2 * e) = y;
+        }
+      }
+    } else {
     for (int c = warp; c < C; c += kBwThreads / 32) {
       float nq = 0.f, nk = 0.f;
       const bool live = c < rows;
@@ -175,7 +355,9 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
         sS0[kk * ldv + vv] = (v0 + vv < V) ? ck[(int64_t)kk * V + v0 + vv] : 0.f;
       }
     }
+    }
     __syncthreads();
+    BPROF(151);
     if (KDA) {
       for (int i = tid; i < K; i += kBwThreads) {
         float acc = 0.f;
@@ -198,26 +380,60 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
       }
       for (int i = tid; i < K; i += kBwThreads) sEL[i] = expf(gl);
     }
+    BPROF(152);
     // ---- X = tril(K^K^^T.E,-1) (not yet scaled by beta), A = tril(Q^K^^T.E) ---------------------------
     if constexpr (TC) {
       // rows 0..63 of the stacked product are K^ (-> X), rows 64..127 are Q^ (-> A); the decay factor is
       // folded in here (the exact path applies it where an entry is used)
-      for (int tile = warp; tile < 64; tile += 8) {
-        const int m0 = (tile >> 3) * 16, n0 = (tile & 7) * 8;
-        const int i0 = m0 & 63;
-        float d[4] = {0.f, 0.f, 0.f, 0.f};
-        if (n0 <= i0 + 15)
-          tile_gemm_tf32(d, m0, n0, K,
-                         [&](int m, int k) { return m < 64 ? sK[m * ldk + k] : sQ[(m - 64) * ldk + k]; },
-                         [&](int k, int n) { return sK[n * ldk + k]; }, lane);
+      {
+        // Lower-triangular 16-row panels cut into tasks of at most three 8-column tiles:
+        //   task 0..2: rows 48.., tiles 0-2 / 3-5 / 6-7    3,4: rows 32.., tiles 0-2 / 3-5
+        //   5,6: rows 16.., tiles 0-1 / 2-3                7: rows 0.., tiles 0-1
+        // warp w runs task w on K^ (-> X) and task 7-w on Q^ (-> A): five or six tiles per warp.
         const int g = lane >> 2, t = lane & 3;
+#pragma unroll 1
+        for (int pass = 0; pass < 2; ++pass) {
+          const int task = pass ? 7 - warp : warp;
+          const int i0 = task < 3 ? 48 : task < 5 ? 32 : task < 7 ? 16 : 0;
+          const int nt0 = task < 3 ? 3 * task : task < 5 ? 3 * (task - 3) : task < 7 ? 2 * (task - 5) : 0;
+          const int ntn = (task == 2 || task >= 5) ? 2 : 3;
+          const float* arows = pass ? sQ : sK;
+          float d[3][4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int m = m0 + g + (e >> 1) * 8, j = n0 + 2 * t + (e & 1);
-          const int i = m & 63;
-          const float v = d[e] * __expf(fminf(sGs[i] - sGs[j], 0.f));
-          if (m < 64) sX[i * lda + j] = (j < i) ? v : 0.f;
-          else sA[i * lda + j] = (j <= i) ? v : 0.f;
+          for (int nt = 0; nt < 3; ++nt) d[nt][0] = d[nt][1] = d[nt][2] = d[nt][3] = 0.f;
+          for (int k0 = 0; k0 < K; k0 += 8) {
+            uint32_t af[4];
+            af[0] = __float_as_uint(arows[(i0 + g) * ldk + k0 + t]);
+            af[1] = __float_as_uint(arows[(i0 + g + 8) * ldk + k0 + t]);
+            af[2] = __float_as_uint(arows[(i0 + g) * ldk + k0 + t + 4]);
+            af[3] = __float_as_uint(arows[(i0 + g + 8) * ldk + k0 + t + 4]);
+#pragma unroll
+            for (int nt = 0; nt < 3; ++nt) {
+              if (nt < ntn) {
+                uint32_t bf[2];
+                bf[0] = __float_as_uint(sK[(8 * (nt0 + nt) + g) * ldk + k0 + t]);
+                bf[1] = __float_as_uint(sK[(8 * (nt0 + nt) + g) * ldk + k0 + t + 4]);
+                sm100::mma_tf32(d[nt], af, bf);
+              }
+            }
+          }
+#pragma unroll
+          for (int nt = 0; nt < 3; ++nt) {
+            if (nt < ntn) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int i = i0 + g + (e >> 1) * 8, j = 8 * (nt0 + nt) + 2 * t + (e & 1);
+                const float v = d[nt][e] * __expf(fminf(sGs[i] - sGs[j], 0.f));
+                if (pass) sA[i * lda + j] = (j <= i) ? v : 0.f;
+                else sX[i * lda + j] = (j < i) ? v : 0.f;
+              }
+            }
+          }
+        }
+        // the tiles above the diagonal blocks are zero
+        for (int e = tid; e < 64 * 64; e += kBwThreads) {
+          const int i = e >> 6, j = e & 63;
+          if ((j >> 3) > (i >> 4) * 2 + 1) { sX[i * lda + j] = 0.f; sA[i * lda + j] = 0.f; }
         }
       }
     } else {
@@ -251,20 +467,26 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
     }
     }
     __syncthreads();
+    BPROF(153);
     auto Eij = [&](int i, int j) -> float { return (KDA || TC) ? 1.f : __expf(fminf(sGs[i] - sGs[j], 0.f)); };
     // ---- R = beta V - (beta K^ e^G) S0  (lane = value column, warp = rows) ----------------------------
     if constexpr (TC) {
-      for (int tile = warp; tile < 4 * (VS / 8); tile += 8) {
-        const int m0 = (tile / (VS / 8)) * 16, n0 = (tile % (VS / 8)) * 8;
-        float d[4] = {0.f, 0.f, 0.f, 0.f};
-        tile_gemm_tf32(d, m0, n0, K, [&](int m, int k) { return sK[m * ldk + k]; },
-                       [&](int k, int n) { return sS0[k * ldv + n]; }, lane);
+      {
+        constexpr int NT = VS / 16;
+        const int m0 = (warp >> 1) * 16, n0 = (warp & 1) * 8 * NT;
+        float d[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) d[nt][0] = d[nt][1] = d[nt][2] = d[nt][3] = 0.f;
+        rgemm<NT>(d, m0, n0, 0, K, [&](int m, int k) { return sK[m * ldk + k]; },
+                  [&](int k, int nn) { return sS0[k * ldv + nn]; }, lane);
         const int g = lane >> 2, t = lane & 3;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int c = m0 + g + (e >> 1) * 8, vv = n0 + 2 * t + (e & 1);
-          sVn[c * ldv + vv] = sBeta[c] * (sV[c * ldv + vv] - sEG[c] * d[e]);
-        }
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int c = m0 + g + (e >> 1) * 8, vv = n0 + 8 * nt + 2 * t + (e & 1);
+            sVn[c * ldv + vv] = sBeta[c] * (sV[c * ldv + vv] - sEG[c] * d[nt][e]);
+          }
       }
     } else {
     {
@@ -284,7 +506,26 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
     }
     }
     __syncthreads();
+    BPROF(154);
     // ---- Vn = M^-1 R : forward substitution, 8 lanes per column -----------------------------------------
+    if constexpr (TC) {
+      // explicit inverse T = (I + diag(beta) X)^-1 (X carries the decay), then Vn = T R on the tensor cores
+      sm100::block_inverse_64(sX, sBeta, sT, tid);
+      constexpr int NT = VS / 16;
+      const int m0 = (warp >> 1) * 16, n0 = (warp & 1) * 8 * NT;
+      float d[NT][4];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) d[nt][0] = d[nt][1] = d[nt][2] = d[nt][3] = 0.f;
+      rgemm<NT>(d, m0, n0, 0, m0 + 16, [&](int m, int k) { return k <= m ? sT[m * lda + k] : 0.f; },
+                [&](int k, int nn) { return sVn[k * ldv + nn]; }, lane);
+      __syncthreads();
+      const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          sVn[(m0 + g + (e >> 1) * 8) * ldv + n0 + 8 * nt + 2 * t + (e & 1)] = d[nt][e];
+    } else
     if (tid < 8 * VS) {
       const int col = tid >> 3, l8 = tid & 7;
       for (int i = 1; i < C; ++i) {
@@ -298,21 +539,30 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
       }
     }
     __syncthreads();
+    BPROF(155);
     // ---- dVn = A^T dO + (K^ e^{G_L-G}) dS1 -----------------------------------------------------------------
     if constexpr (TC) {
-      for (int tile = warp; tile < 4 * (VS / 8); tile += 8) {
-        const int m0 = (tile / (VS / 8)) * 16, n0 = (tile % (VS / 8)) * 8;
-        float d1[4] = {0.f, 0.f, 0.f, 0.f}, d2[4] = {0.f, 0.f, 0.f, 0.f};
-        tile_gemm_tf32(d1, m0, n0, C, [&](int m, int k) { return sA[k * lda + m]; },   // A^T (already lower, decayed)
-                       [&](int k, int n) { return sdO[k * ldv + n]; }, lane);
-        tile_gemm_tf32(d2, m0, n0, K, [&](int m, int k) { return sK[m * ldk + k]; },
-                       [&](int k, int n) { return sdS[k * ldv + n]; }, lane);
+      {
+        constexpr int NT = VS / 16;
+        const int m0 = (warp >> 1) * 16, n0 = (warp & 1) * 8 * NT;
+        float d1[NT][4], d2[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          d1[nt][0] = d1[nt][1] = d1[nt][2] = d1[nt][3] = 0.f;
+          d2[nt][0] = d2[nt][1] = d2[nt][2] = d2[nt][3] = 0.f;
+        }
+        rgemm<NT>(d1, m0, n0, m0, C, [&](int m, int k) { return sA[k * lda + m]; },   // A^T (lower A, decayed)
+                  [&](int k, int nn) { return sdO[k * ldv + nn]; }, lane);
+        rgemm<NT>(d2, m0, n0, 0, K, [&](int m, int k) { return sK[m * ldk + k]; },
+                  [&](int k, int nn) { return sdS[k * ldv + nn]; }, lane);
         const int g = lane >> 2, t = lane & 3;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int c = m0 + g + (e >> 1) * 8, vv = n0 + 2 * t + (e & 1);
-          sdR[c * ldv + vv] = d1[e] + sWd[c] * d2[e];
-        }
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int c = m0 + g + (e >> 1) * 8, vv = n0 + 8 * nt + 2 * t + (e & 1);
+            sdR[c * ldv + vv] = d1[nt][e] + sWd[c] * d2[nt][e];
+          }
       }
     } else {
     {
@@ -332,7 +582,24 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
     }
     }
     __syncthreads();
+    BPROF(156);
     // ---- dR = M^-T dVn : back substitution ---------------------------------------------------------------------
+    if constexpr (TC) {
+      constexpr int NT = VS / 16;
+      const int m0 = (warp >> 1) * 16, n0 = (warp & 1) * 8 * NT;
+      float d[NT][4];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) d[nt][0] = d[nt][1] = d[nt][2] = d[nt][3] = 0.f;
+      rgemm<NT>(d, m0, n0, m0, C, [&](int m, int k) { return k >= m ? sT[k * lda + m] : 0.f; },
+                [&](int k, int nn) { return sdR[k * ldv + nn]; }, lane);
+      __syncthreads();
+      const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          sdR[(m0 + g + (e >> 1) * 8) * ldv + n0 + 8 * nt + 2 * t + (e & 1)] = d[nt][e];
+    } else
     if (tid < 8 * VS) {
       const int col = tid >> 3, l8 = tid & 7;
       for (int i = C - 2; i >= 0; --i) {
@@ -346,6 +613,7 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
       }
     }
     __syncthreads();
+    BPROF(157);
     // ---- dV = beta dR ; dbeta += dR.V ; dA = tril(dO Vn^T).E ; dX = beta tril(-dR Vn^T).E ; dbeta += dM.X ------
     for (int i = tid; i < C * VS; i += kBwThreads) {
       const int c = i / VS, vv = i % VS;
@@ -360,24 +628,37 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
     }
     __syncthreads();
     if constexpr (TC) {
-      for (int tile = warp; tile < 32; tile += 8) {
-        const int m0 = (tile >> 3) * 16, n0 = (tile & 7) * 8;
-        float da[4] = {0.f, 0.f, 0.f, 0.f}, dm[4] = {0.f, 0.f, 0.f, 0.f};
-        if (n0 <= m0 + 15) {
-          tile_gemm_tf32(da, m0, n0, VS, [&](int m, int k) { return sdO[m * ldv + k]; },
-                         [&](int k, int n) { return sVn[n * ldv + k]; }, lane);
-          tile_gemm_tf32(dm, m0, n0, VS, [&](int m, int k) { return sdR[m * ldv + k]; },
-                         [&](int k, int n) { return sVn[n * ldv + k]; }, lane);
-        }
-        const int g = lane >> 2, t = lane & 3;
+      {
+        // warp = 16 rows x 32 columns; both products share the B operand Vn^T
+        const int m0 = (warp >> 1) * 16, n0 = (warp & 1) * 32;
+        float da[4][4], dm[4][4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int i = m0 + g + (e >> 1) * 8, j = n0 + 2 * t + (e & 1);
-          const float ee = (j <= i) ? __expf(fminf(sGs[i] - sGs[j], 0.f)) : 0.f;
-          const float dmv = -dm[e];
-          if (j < i) atomicAdd(&sdBeta[i], dmv * sX[i * lda + j]);   // sX already carries the decay factor
-          sA[i * lda + j] = (j <= i) ? da[e] * ee : 0.f;
-          sX[i * lda + j] = (j < i) ? sBeta[i] * dmv * ee : 0.f;
+        for (int nt = 0; nt < 4; ++nt) {
+          da[nt][0] = da[nt][1] = da[nt][2] = da[nt][3] = 0.f;
+          dm[nt][0] = dm[nt][1] = dm[nt][2] = dm[nt][3] = 0.f;
+        }
+        if (n0 <= m0 + 15)
+          rgemm2<4>(da, dm, m0, n0, 0, VS, [&](int m, int k) { return sdO[m * ldv + k]; },
+                    [&](int m, int k) { return sdR[m * ldv + k]; }, [&](int k, int nn) { return sVn[nn * ldv + k]; }, lane);
+        const int g = lane >> 2, t = lane & 3;
+        float dbacc[2] = {0.f, 0.f};
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = m0 + g + (e >> 1) * 8, j = n0 + 8 * nt + 2 * t + (e & 1);
+            const float ee = (j <= i) ? __expf(fminf(sGs[i] - sGs[j], 0.f)) : 0.f;
+            const float dmv = -dm[nt][e];
+            if (j < i) dbacc[e >> 1] += dmv * sX[i * lda + j];   // sX already carries the decay factor
+            sA[i * lda + j] = (j <= i) ? da[nt][e] * ee : 0.f;
+            sX[i * lda + j] = (j < i) ? sBeta[i] * dmv * ee : 0.f;
+          }
+#pragma unroll
+        for (int hr = 0; hr < 2; ++hr) {
+          float x = dbacc[hr];
+          x += __shfl_xor_sync(0xffffffffu, x, 1);
+          x += __shfl_xor_sync(0xffffffffu, x, 2);
+          if (t == 0) atomicAdd(&sdBeta[m0 + g + hr * 8], x);
         }
       }
     } else {
@@ -398,44 +679,51 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
     }
     }
     __syncthreads();
+    BPROF(158);
     // ---- per (row i, channel k): dQ^, dK^, dG, dbeta; lane = channel, warp = rows ----------------------------------
     if constexpr (TC) {
-      // warp w owns rows 16*(w/2).. and channels 64*(w%2)..: 8 tiles of 16x8, seven products per tile
+      // warp w owns rows 16*(w/2)..; the channel tiles are dealt to the two warps of a row panel in pairs.
+      // Seven products per tile; products with the same B operand share its fetch, the A fragments are
+      // fetched once per pair of tiles.
       const int g = lane >> 2, t = lane & 3;
       const int m0 = (warp >> 1) * 16;
       float dgrow[2] = {0.f, 0.f}, dbrow[2] = {0.f, 0.f}, extra = 0.f;
-      for (int tn = 0; tn < 8; ++tn) {
-        const int n0 = (warp & 1) * 64 + tn * 8;
-        if (n0 >= K) break;
-        float dQg[4] = {0.f, 0.f, 0.f, 0.f}, dKg[4] = {0.f, 0.f, 0.f, 0.f}, dKt[4] = {0.f, 0.f, 0.f, 0.f};
-        float rowA[4] = {0.f, 0.f, 0.f, 0.f}, rowX[4] = {0.f, 0.f, 0.f, 0.f};
-        float colA[4] = {0.f, 0.f, 0.f, 0.f}, colX[4] = {0.f, 0.f, 0.f, 0.f};
-        auto bS0 = [&](int k, int n) { return sS0[n * ldv + k]; };
-        tile_gemm_tf32(dQg, m0, n0, VS, [&](int m, int k) { return sdO[m * ldv + k]; }, bS0, lane);
-        tile_gemm_tf32(dKg, m0, n0, VS, [&](int m, int k) { return sdR[m * ldv + k]; }, bS0, lane);
-        tile_gemm_tf32(dKt, m0, n0, VS, [&](int m, int k) { return sVn[m * ldv + k]; },
-                       [&](int k, int n) { return sdS[n * ldv + k]; }, lane);
-        auto bK = [&](int k, int n) { return sK[k * ldk + n]; };
-        tile_gemm_tf32(rowA, m0, n0, C, [&](int m, int k) { return sA[m * lda + k]; }, bK, lane);
-        tile_gemm_tf32(rowX, m0, n0, C, [&](int m, int k) { return sX[m * lda + k]; }, bK, lane);
-        tile_gemm_tf32(colA, m0, n0, C, [&](int m, int k) { return sA[k * lda + m]; },
-                       [&](int k, int n) { return sQ[k * ldk + n]; }, lane);
-        tile_gemm_tf32(colX, m0, n0, C, [&](int m, int k) { return sX[k * lda + m]; }, bK, lane);
+      for (int n0 = (warp & 1) * 16; n0 < K; n0 += 32) {
+        float dQg[2][4], dKg[2][4], dKt[2][4], rowA[2][4], rowX[2][4], colA[2][4], colX[2][4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int i = m0 + g + (e >> 1) * 8, kk = n0 + 2 * t + (e & 1);
-          const float eg = sEG[i], el = sWd[i];
-          const float qh = sQ[i * ldk + kk], kh = sK[i * ldk + kk];
-          const float dq = dQg[e] * eg + rowA[e];
-          const float dk_row = -dKg[e] * sBeta[i] * eg + rowX[e];
-          const float dk_col = dKt[e] * el + colA[e] + colX[e];
-          dbrow[e >> 1] += -dKg[e] * kh * eg;
-          dgrow[e >> 1] += qh * dq + kh * (dk_row - dk_col);
-          extra += dKt[e] * kh * el;
-          const int64_t arow = acc_row0 + t0 + i;
-          p.dq_acc[slice_off + arow * K + kk] = dq;
-          p.dk_acc[slice_off + arow * K + kk] = dk_row + dk_col;
-        }
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            dQg[nt][e] = dKg[nt][e] = dKt[nt][e] = rowA[nt][e] = rowX[nt][e] = colA[nt][e] = colX[nt][e] = 0.f;
+        rgemm2<2>(dQg, dKg, m0, n0, 0, VS, [&](int m, int k) { return sdO[m * ldv + k]; },
+                  [&](int m, int k) { return sdR[m * ldv + k]; }, [&](int k, int nn) { return sS0[nn * ldv + k]; }, lane);
+        rgemm<2>(dKt, m0, n0, 0, VS, [&](int m, int k) { return sVn[m * ldv + k]; },
+                 [&](int k, int nn) { return sdS[nn * ldv + k]; }, lane);
+        auto bK = [&](int k, int nn) { return sK[k * ldk + nn]; };
+        // rows of dA, dX (lower: k <= m) ...
+        rgemm2<2>(rowA, rowX, m0, n0, 0, m0 + 16, [&](int m, int k) { return sA[m * lda + k]; },
+                  [&](int m, int k) { return sX[m * lda + k]; }, bK, lane);
+        // ... and their columns (k >= m)
+        rgemm<2>(colX, m0, n0, m0, C, [&](int m, int k) { return sX[k * lda + m]; }, bK, lane);
+        rgemm<2>(colA, m0, n0, m0, C, [&](int m, int k) { return sA[k * lda + m]; },
+                 [&](int k, int nn) { return sQ[k * ldk + nn]; }, lane);
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = m0 + g + (e >> 1) * 8, kk = n0 + 8 * nt + 2 * t + (e & 1);
+            const float eg = sEG[i], el = sWd[i];
+            const float qh = sQ[i * ldk + kk], kh = sK[i * ldk + kk];
+            const float dq = dQg[nt][e] * eg + rowA[nt][e];
+            const float dk_row = -dKg[nt][e] * sBeta[i] * eg + rowX[nt][e];
+            const float dk_col = dKt[nt][e] * el + colA[nt][e] + colX[nt][e];
+            dbrow[e >> 1] += -dKg[nt][e] * kh * eg;
+            dgrow[e >> 1] += qh * dq + kh * (dk_row - dk_col);
+            extra += dKt[nt][e] * kh * el;
+            const int64_t arow = acc_row0 + t0 + i;
+            p.dq_acc[slice_off + arow * K + kk] = dq;
+            p.dk_acc[slice_off + arow * K + kk] = dk_row + dk_col;
+          }
       }
 #pragma unroll
       for (int hrow = 0; hrow < 2; ++hrow) {
@@ -525,37 +813,49 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
       }
     }
     }
+    BPROF(159);
     // ---- dS0 = (Q^ e^G)^T dO + e^{G_L} dS1 - (beta K^ e^G)^T dR ; dG_L += e^{G_L} <dS1, S0> -------------------------
     if constexpr (TC) {
-      // rows = channels k (tiles 16*mt), columns = value columns (8*nt); warp w takes tiles w, w+8, ...
+      // rows = channels k (panels of 16), columns = the VS value columns; warp w takes panels w, w+8 (K <= 256)
       constexpr int NT = VS / 8;
-      float keep[4][4];
+      float keep[2][NT][4];
       const int g = lane >> 2, t = lane & 3;
       float tsum = 0.f;
-      int slot = 0;
-      for (int tile = warp; tile < (K / 16) * NT; tile += 8, ++slot) {
-        const int m0 = (tile / NT) * 16, n0 = (tile % NT) * 8;
-        float d[4] = {0.f, 0.f, 0.f, 0.f};
-        tile_gemm_tf32(d, m0, n0, C, [&](int m, int k) { return sEG[k] * sQ[k * ldk + m]; },
-                       [&](int k, int n) { return sdO[k * ldv + n]; }, lane);
-        tile_gemm_tf32(d, m0, n0, C, [&](int m, int k) { return -sEG[k] * sBeta[k] * sK[k * ldk + m]; },
-                       [&](int k, int n) { return sdR[k * ldv + n]; }, lane);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int kk = m0 + g + (e >> 1) * 8, vv = n0 + 2 * t + (e & 1);
-          const float ds1 = sdS[kk * ldv + vv];
-          tsum += ds1 * sS0[kk * ldv + vv] * sEL[kk];
-          keep[slot][e] = d[e] + sEL[kk] * ds1;
+      for (int slot = 0; slot < 2; ++slot) {
+        const int m0 = (warp + 8 * slot) * 16;
+        if (m0 < K) {
+          float d[NT][4];
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) d[nt][0] = d[nt][1] = d[nt][2] = d[nt][3] = 0.f;
+          rgemm<NT>(d, m0, 0, 0, C, [&](int m, int k) { return sEG[k] * sQ[k * ldk + m]; },
+                    [&](int k, int nn) { return sdO[k * ldv + nn]; }, lane);
+          rgemm<NT>(d, m0, 0, 0, C, [&](int m, int k) { return -sEG[k] * sBeta[k] * sK[k * ldk + m]; },
+                    [&](int k, int nn) { return sdR[k * ldv + nn]; }, lane);
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int kk = m0 + g + (e >> 1) * 8, vv = 8 * nt + 2 * t + (e & 1);
+              const float ds1 = sdS[kk * ldv + vv];
+              tsum += ds1 * sS0[kk * ldv + vv] * sEL[kk];
+              keep[slot][nt][e] = d[nt][e] + sEL[kk] * ds1;
+            }
         }
       }
       tsum = warp_sum(tsum);
       if (lane == 0 && p.dg_acc) atomicAdd(p.dg_acc + acc_row0 + t0 + C - 1, tsum);
       __syncthreads();
-      slot = 0;
-      for (int tile = warp; tile < (K / 16) * NT; tile += 8, ++slot) {
-        const int m0 = (tile / NT) * 16, n0 = (tile % NT) * 8;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) sdS[(m0 + g + (e >> 1) * 8) * ldv + n0 + 2 * t + (e & 1)] = keep[slot][e];
+      for (int slot = 0; slot < 2; ++slot) {
+        const int m0 = (warp + 8 * slot) * 16;
+        if (m0 < K) {
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              sdS[(m0 + g + (e >> 1) * 8) * ldv + 8 * nt + 2 * t + (e & 1)] = keep[slot][nt][e];
+        }
       }
     } else {
     float ds_new[16];
@@ -589,6 +889,7 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
       for (int kk = warp * STREAMS + sub; kk < K; kk += 8 * STREAMS, ++slot) sdS[kk * ldv + vv] = ds_new[slot];
     }
     }
+    BPROF(160);
     for (int c = tid; c < rows; c += kBwThreads) atomicAdd(p.dbeta + s_base + (t0 + c) * s_tok, sdBeta[c]);
   }
   __syncthreads();
@@ -742,9 +1043,9 @@ inline cudaError_t launch_bwd(const DrDesc* d, const void* q, const void* k, con
     bwd_chunk_kernel<VS, true, false><<<(unsigned)(units * ((V + VS - 1) / VS)), kBwThreads, smem, stream>>>(p);
   } else {
     constexpr int VS = 32;
-    const size_t smem = bwd_layout(C, K, VS, false).total * sizeof(float);
     // bf16 inputs with whole 16x8 tiles: the products run on the tensor cores (tf32); fp32 inputs stay exact
     const bool tc = d->qkv_dtype == DR_BF16 && C == 64 && K % 16 == 0;
+    const size_t smem = bwd_layout(C, K, VS, false, tc).total * sizeof(float);
     if (tc) {
       e = cudaFuncSetAttribute(bwd_chunk_kernel<VS, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return e;

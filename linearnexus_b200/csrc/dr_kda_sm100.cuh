@@ -195,6 +195,7 @@ __global__ void __launch_bounds__(kThreads, 2) intra_kernel(const FwdParams p, u
       }
     }
   }
+  KPROF(147);
   // V rows -> the record's tile, 16 bytes per piece (coalesced writes)
   {
     const __nv_bfloat16* gv = reinterpret_cast<const __nv_bfloat16*>(p.v);
@@ -209,6 +210,7 @@ __global__ void __launch_bounds__(kThreads, 2) intra_kernel(const FwdParams p, u
       *reinterpret_cast<uint4*>(rec + WS_V + piece * 16) = u;
     }
   }
+  KPROF(148);
   __syncthreads();
   KPROF(140);
   // ---- G = inclusive prefix sum of the log decay over the rows of the chunk, per channel ---------------------
