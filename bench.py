@@ -47,6 +47,9 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel (ncu, see profiles/*.md)
 NCU_TRAFFIC = {
     "gdn_fwd:chunk_tcgen05": 504.4e6,   # profiles/chunk_sm100_kernel_gdn_fwd.md (B=4 capture scaled by sequences)
+    "kda_fwd:chunk_split_tcgen05": 4.305e9,   # profiles/kda_split_kernels.md: both kernels, B=1 capture x 4 sequences-wise
+    "gdn_decode:step": 1026.8e6,        # profiles/step_kernel_gdn_decode.md (full size)
+    "gdn_fwd_bwd:bwd": 792.8e6,         # profiles/bwd_chunk_kernel_phases.md: the adjoint kernel only (full size)
 }
 
 

@@ -84,3 +84,23 @@ def test_state_factories_cpu():
     assert s.conv_state_q is None
     s = L.DeltaNetState.zeros(2, 4, 16, 32, conv_channels=64, device="cpu")
     assert s.conv_state.shape == (2, 3, 64)
+
+
+def test_forward_workspace_sizes_need_no_gpu():
+    """dr_workspace_bytes(desc, 0): one 82 432-byte record per (sequence, 64-token chunk) for the two-kernel
+    forward (KDA by default, any variant when asked for), nothing for the kernels that need no scratch."""
+    import ctypes
+    import torch
+    from linearnexus_b200 import ops
+    lib = _lib.load()
+    q = torch.empty(0, dtype=torch.bfloat16)
+    g = torch.empty(0, dtype=torch.float32)
+    def need(variant, path, B=2, H=3, T=130, K=128, V=128, qkv=q):
+        d = ops._desc(variant, _lib.DR_LAYOUT_BHTD, B, H, T, K, V, 64, qkv, g, torch.float32, True, 0.1, path)
+        return int(lib.dr_workspace_bytes(ctypes.byref(d), 0))
+    assert need(_lib.DR_KDA, None) == 2 * 3 * 3 * 82432
+    assert need(_lib.DR_KDA, "fp32") == 0
+    assert need(_lib.DR_GATED, None) == 0
+    assert need(_lib.DR_GATED, "split") == 2 * 3 * 3 * 82432
+    assert need(_lib.DR_KDA, None, K=64) == 0                      # not the tensor-core shape: fp32 kernel
+    assert need(_lib.DR_KDA, None, qkv=torch.empty(0)) == 0        # fp32 inputs stay on the exact kernel
