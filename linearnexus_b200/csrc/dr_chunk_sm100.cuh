@@ -111,8 +111,9 @@ __device__ unsigned long long g_prof[192];
 #endif
 
 struct Ctl {
-  uint64_t full[2], empty[2], late[2], barP, bar1, bar2, kq[3], vb;
+  uint64_t full[2], empty[2], barP, barUW, uwfree, bar1, bar2, kq[3], vb;
   float gb[3][128];      // raw beta (0..63) and g (64..127) of chunk m in slot m % 3
+  float sc[3][256];      // G, e^G, e^{G_L-G}, beta (64 each) of chunk m in slot m % 3
   float eg_keep[2][64];  // rq_i e^{G_i} of the chunk whose output epilogue is still pending, per stage
   float rq_keep[2][64];  // rq_i of that chunk
   float rq[2][64];       // per stage: scale / (||q_i|| + eps)           (producer -> consumer)
@@ -145,9 +146,13 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-template <int BS>
+struct SyncGroup256 { __device__ __forceinline__ void operator()() const { group_sync(1); } };
+// the first four warps of a group only (barrier 3): the 8- and 16-wide merge levels have work for four warps
+struct SyncHalf128 { __device__ __forceinline__ void operator()() const { asm volatile("bar.sync 3, 128;" ::: "memory"); } };
+
+template <int BS, class Sync>
 __device__ __forceinline__ void inverse_merge_level(const float* __restrict__ sA, const float* __restrict__ rs,
-                                                    float* __restrict__ sT, int warp8, int lane) {
+                                                    float* __restrict__ sT, int warp8, int lane, Sync sync) {
   constexpr int MT = BS >= 16 ? BS / 16 : 1, NT = BS / 8, KS = BS / 8;
   constexpr int TPP = MT * NT, NPAIR = 32 / BS, TILES = NPAIR * TPP;
   const int g = lane >> 2, t = lane & 3;
@@ -182,7 +187,7 @@ __device__ __forceinline__ void inverse_merge_level(const float* __restrict__ sA
       *reinterpret_cast<float2*>(sT + (c0 + m1) * LDT + r0 + n0 + 2 * t) = make_float2(f * d[2], f * d[3]);
     }
   }
-  group_sync(1);
+  sync();
   // step 2: T_10 = -T_11 X
   if (work) {
     float d[4] = {0.f, 0.f, 0.f, 0.f};
@@ -202,7 +207,7 @@ __device__ __forceinline__ void inverse_merge_level(const float* __restrict__ sA
     if (m0 < BS) *reinterpret_cast<float2*>(sT + (r0 + m0) * LDT + c0 + n0 + 2 * t) = make_float2(-d[0], -d[1]);
     if (m1 < BS) *reinterpret_cast<float2*>(sT + (r0 + m1) * LDT + c0 + n0 + 2 * t) = make_float2(-d[2], -d[3]);
   }
-  group_sync(1);
+  sync();
 }
 
 __device__ __forceinline__ void block_inverse_64(const float* __restrict__ sA, const float* __restrict__ rs,
@@ -223,9 +228,40 @@ __device__ __forceinline__ void block_inverse_64(const float* __restrict__ sA, c
     for (int i = 0; i < 8; ++i) sT[(o + i) * LDT + o + c] = x[i];
   }
   group_sync(1);
-  inverse_merge_level<8>(sA, rs, sT, warp8, lane);
-  inverse_merge_level<16>(sA, rs, sT, warp8, lane);
-  inverse_merge_level<32>(sA, rs, sT, warp8, lane);
+  inverse_merge_level<8>(sA, rs, sT, warp8, lane, SyncGroup256());
+  inverse_merge_level<16>(sA, rs, sT, warp8, lane, SyncGroup256());
+  inverse_merge_level<32>(sA, rs, sT, warp8, lane, SyncGroup256());
+}
+
+// The same inverse with the group split for its first part: warps 0-3 run the diagonal blocks and the 8- and
+// 16-wide merge levels (which have work for four warps only) while warps 4-7 run `side()`; all eight warps
+// join for the 32-wide level.  Every thread of the group must call it.
+template <class Side>
+__device__ __forceinline__ void block_inverse_64_split(const float* __restrict__ sA, const float* __restrict__ rs,
+                                                       float* __restrict__ sT, int gt, Side side) {
+  const int warp8 = gt >> 5, lane = gt & 31;
+  if (gt < 128) {
+    if (gt < 64) {
+      const int o = (gt >> 3) * 8, c = gt & 7;
+      float x[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < i; ++j) acc += sA[(o + i) * LDT + o + j] * x[j];
+        x[i] = ((i == c) ? 1.f : 0.f) - rs[o + i] * acc;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sT[(o + i) * LDT + o + c] = x[i];
+    }
+    SyncHalf128()();
+    inverse_merge_level<8>(sA, rs, sT, warp8, lane, SyncHalf128());
+    inverse_merge_level<16>(sA, rs, sT, warp8, lane, SyncHalf128());
+  } else {
+    side();
+  }
+  group_sync(1);
+  inverse_merge_level<32>(sA, rs, sT, warp8, lane, SyncGroup256());
 }
 
 // Kernel parameters: the common forward parameters plus the TMA tensor maps.
@@ -265,8 +301,8 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
     tc::mbar_init(tc::smem_u32(&ctl.full[1]), kGroup);
     tc::mbar_init(tc::smem_u32(&ctl.empty[0]), kGroup);
     tc::mbar_init(tc::smem_u32(&ctl.empty[1]), kGroup);
-    tc::mbar_init(tc::smem_u32(&ctl.late[0]), kGroup);
-    tc::mbar_init(tc::smem_u32(&ctl.late[1]), kGroup);
+    tc::mbar_init(tc::smem_u32(&ctl.barUW), 1);
+    tc::mbar_init(tc::smem_u32(&ctl.uwfree), 1);
     tc::mbar_init(tc::smem_u32(&ctl.barP), 1);
     tc::mbar_init(tc::smem_u32(&ctl.bar1), 1);
     tc::mbar_init(tc::smem_u32(&ctl.bar2), 1);
@@ -359,6 +395,8 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       tc::cp_async_commit();
     };
     // V rows of chunk m -> core-matrix tile
+    // (with TMA only chunk 0 is fetched here; the consumer fetches V of chunk m+1 the moment its U^T product
+    // of chunk m has completed)
     auto issue_v = [&](int m) {
       const int t0m = m * kC, rowsm = min(kC, T - t0m);
       if (P.use_tma_in) {
@@ -382,7 +420,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
 
     // inclusive scan of the log decay over the 64 rows of a stage (one warp): G, e^G, e^{G_L - G}
     auto scan_stage = [&](int m) {
-      float* zG = reinterpret_cast<float*>(smem + SM_STAGE + (m & 1) * STAGE_BYTES + ST_SC);
+      float* zG = ctl.sc[m % 3];
       const float* raw = ctl.gb[m % 3];
       zG[192 + lane] = raw[lane]; zG[224 + lane] = raw[32 + lane];   // beta
       float a = raw[64 + lane], bq = raw[96 + lane];
@@ -400,146 +438,46 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       zG[128 + lane] = __expf(fminf(last - a, 0.f)); zG[160 + lane] = __expf(fminf(last - bq, 0.f));
     };
 
+    // first product of chunk m: D1 = [K;Q] K^T on the raw rows (B = first 64 rows of the same tile)
+    auto issue_d1 = [&](int m) {
+      if (P.use_tma_in) wait_bar(&ctl.kq[m % 3], (m / 3) & 1);
+      tc::tc_fence_after();
+      const uint32_t aQK = tc::smem_u32(smem + SM_QKR + (m % 3) * QK_TILE);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint64_t ad = tc::smem_desc(aQK + ks * 256, 128, RBS);
+        tc::mma_ss(tbase + TM_D1, ad, ad, id_n64, ks > 0);
+      }
+      tc::mma_commit(tc::smem_u32(&ctl.barP));
+    };
+
     if (nchunks > 0) {
       issue_kq(0);
       issue_v(0);
-      tc::cp_async_wait_1();   // g, beta of chunk 0
+      tc::cp_async_wait_all();
+      if (!P.use_tma_in) tc::fence_async_smem();
       group_sync(1);
       if (warp == 1) scan_stage(0);
+      if (gt == 0) issue_d1(0);
     }
     PROF_DECL
-#ifdef DR_PROFILE
-    {  // fixed costs of the building blocks, measured once per CTA 0 (slots 40..)
-      group_sync(1);
-      PROF(39);
-      for (int i = 0; i < 16; ++i) group_sync(1);
-      PROF(40);
-      for (int i = 0; i < 16; ++i) {
-        uint32_t r[32];
-        tc::tmem_ld32(tbase + TM_D1 + lane_addr, r);
-        tc::tc_wait_ld();
-        if (r[0] == 0x12345u && r[31] == 0x54321u) ctl.rk[0] = 1.f;
-      }
-      PROF(41);
-      for (int i = 0; i < 16; ++i) {
-        tc::fence_async_smem();
-      }
-      PROF(42);
-      for (int i = 0; i < 16; ++i) {
-        tc::tc_fence_before();
-        group_sync(1);
-        tc::tc_fence_after();
-      }
-      PROF(43);
-      float acc = 0.f;
-      for (int i = 0; i < 16; ++i) acc += __expf(sT32[(i * 37 + gt) & 1023]);
-      if (acc == 123.f) ctl.rk[1] = acc;
-      PROF(44);
-      for (int i = gt; i < 64 * LDT; i += kGroup) sAkk[i] = 0.01f;
-      if (gt < 64) ctl.rs[gt] = 0.5f;
-      group_sync(1);
-      PROF(45);
-      for (int i = 0; i < 4; ++i) block_inverse_64(sAkk, ctl.rs, sT32, gt);
-      PROF(46);
-      {  // variants of the level-2 product loop, 8 repetitions each
-        const int row = gt >> 3, c4 = (gt & 7) * 4;
-        float x0 = 0.f, x1 = 0.f, x2 = 0.f, x3 = 0.f;
-        for (int rep = 0; rep < 8; ++rep) {
-#pragma unroll 8
-          for (int k = 0; k < 32; ++k) {
-            const float a = sAkk[(32 + row) * LDT + k];
-            const float4 t = *reinterpret_cast<const float4*>(sT32 + k * LDT + c4);
-            x0 += a * t.x; x1 += a * t.y; x2 += a * t.z; x3 += a * t.w;
-          }
-        }
-        if (x0 + x1 + x2 + x3 == 123.f) ctl.rk[2] = x0;
-        PROF(47);
-        x0 = x1 = x2 = x3 = 0.f;
-        for (int rep = 0; rep < 8; ++rep) {
-          float a[32];
-#pragma unroll
-          for (int k4 = 0; k4 < 8; ++k4) {
-            const float4 v = *reinterpret_cast<const float4*>(sAkk + (32 + row) * LDT + 4 * k4);
-            a[4 * k4] = v.x; a[4 * k4 + 1] = v.y; a[4 * k4 + 2] = v.z; a[4 * k4 + 3] = v.w;
-          }
-#pragma unroll
-          for (int k = 0; k < 32; ++k) {
-            const float4 t = *reinterpret_cast<const float4*>(sT32 + k * LDT + c4);
-            x0 += a[k] * t.x; x1 += a[k] * t.y; x2 += a[k] * t.z; x3 += a[k] * t.w;
-          }
-        }
-        if (x0 + x1 + x2 + x3 == 123.f) ctl.rk[2] = x0;
-        PROF(38);
-        // 64 threads, 4x4 register tiles
-        if (gt < 64) {
-          const int r4 = (gt >> 3) * 4, cc = (gt & 7) * 4;
-          float y[4][4] = {};
-          for (int rep = 0; rep < 8; ++rep) {
-#pragma unroll 4
-            for (int k4 = 0; k4 < 8; ++k4) {
-              float4 av[4];
-#pragma unroll
-              for (int r = 0; r < 4; ++r) av[r] = *reinterpret_cast<const float4*>(sAkk + (32 + r4 + r) * LDT + 4 * k4);
-#pragma unroll
-              for (int kk = 0; kk < 4; ++kk) {
-                const float4 t = *reinterpret_cast<const float4*>(sT32 + (4 * k4 + kk) * LDT + cc);
-#pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                  const float a = kk == 0 ? av[r].x : kk == 1 ? av[r].y : kk == 2 ? av[r].z : av[r].w;
-                  y[r][0] += a * t.x; y[r][1] += a * t.y; y[r][2] += a * t.z; y[r][3] += a * t.w;
-                }
-              }
-            }
-          }
-          float sum = 0.f;
-#pragma unroll
-          for (int r = 0; r < 4; ++r) sum += y[r][0] + y[r][1] + y[r][2] + y[r][3];
-          if (sum == 123.f) ctl.rk[3] = sum;
-        }
-        PROF(37);
-      }
-      for (int i = gt; i < 64 * LDT; i += kGroup) sT32[i] = 0.f;
-      group_sync(1);
-    }
-#endif
     for (int n = 0; n < nchunks; ++n) {
       const int s = n & 1;
       uint8_t* st = smem + SM_STAGE + s * STAGE_BYTES;
-      uint8_t* sQK = smem + SM_QKR + (n % 3) * QK_TILE;
-      uint8_t* sWt = st + ST_W;
       uint8_t* sAqk = st + ST_AQK;
-      float* sG = reinterpret_cast<float*>(st + ST_SC);
-      float* sEG = sG + 64;
-      float* sWd = sG + 128;
-      float* sBeta = sG + 192;
-      // this chunk's K,Q tile: TMA completion is awaited by the issuing thread alone; tiles filled by
-      // per-thread cp.async need everyone's copies (the two newest groups -- this chunk's V and the
-      // next chunk's K,Q -- may stay in flight) and a proxy fence
-      if (!P.use_tma_in) {
-        tc::cp_async_wait_1();
-        tc::fence_async_smem();
-      }
-      group_sync(1);  // also: every read of the producer scratch columns by the previous chunk is done
+      const uint8_t* sQKp = smem + SM_QKR + (n % 3) * QK_TILE;
+      const float* sG = ctl.sc[n % 3];
+      const float* sEG = sG + 64;
+      const float* sBeta = sG + 192;
+      group_sync(1);  // the scalars of this chunk (scan) are visible
       PROF(0);
-      // ---- (1) D1 = [K;Q] K^T on the raw rows ------------------------------------------------------------
-      if (gt == 0) {
-        if (P.use_tma_in) wait_bar(&ctl.kq[n % 3], (n / 3) & 1);
-        tc::tc_fence_after();
-        const uint32_t aQK = tc::smem_u32(sQK);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint64_t ad = tc::smem_desc(aQK + ks * 256, 128, RBS);
-          tc::mma_ss(tbase + TM_D1, ad, ad, id_n64, ks > 0);  // B = first 64 rows of the same tile
-        }
-        tc::mma_commit(tc::smem_u32(&ctl.barP));
-      }
-      // while the product runs: the consumer has finished chunk n-2, so stage s and tile (n+1) % 3 are
-      // free -- start the next chunk's loads a whole iteration ahead (an empty group keeps the cp.async
-      // group count uniform on the last chunk)
-      if (n >= 2 && (!P.use_tma_in || gt == 64)) wait_bar(&ctl.empty[s], ((n >> 1) - 1) & 1);
+      // the consumer has finished chunk n-2, so tile (n+1) % 3 and stage s are free: fetch the next chunk's
+      // K,Q (and beta, g) a whole iteration before their first use
+      // (every thread waits: the first epilogue below overwrites the stage's A_qk tile)
+      if (n >= 2) wait_bar(&ctl.empty[s], ((n >> 1) - 1) & 1);
       if (n + 1 < nchunks) issue_kq(n + 1);
-      else tc::cp_async_commit();
       PROF(2);
+      // ---- D1 of this chunk was issued during the previous iteration ----------------------------------------
       wait_bar(&ctl.barP, phP); phP ^= 1;
       tc::tc_fence_after();
       PROF(3);
@@ -592,15 +530,42 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         }
       }
       WEND(1);
+      tc::cp_async_wait_all();   // the next chunk's beta, g (and, without TMA, its K,Q rows) have landed
+      if (!P.use_tma_in) tc::fence_async_smem();
       tc::tc_fence_before();
       group_sync(1);
       PROF(4);
-      PROF(1);
-      // ---- T'' = (I + diag(rs) X)^-1;  Tb = T'' diag(beta rk), Tw = T'' diag(beta e^G rk^2) -----------------
+      // ---- T'' = (I + diag(rs) X)^-1 on warps 0-3 (+ all eight for the last level).  Meanwhile warps 4-7:
+      //      D1 of the NEXT chunk (its scratch columns are free now, so it completes behind the inverse), the
+      //      decay scan of the next chunk, and this chunk's query norms for the consumer -----------------------
       WSTART;
-      block_inverse_64(sAkk, ctl.rs, sT32, gt);
+      block_inverse_64_split(sAkk, ctl.rs, sT32, gt, [&]() {
+        if (n + 1 < nchunks) {
+          if (gt == 128) issue_d1(n + 1);
+          if (warp == 5) scan_stage(n + 1);
+        }
+        if (gt >= 192) {  // rq_i = scale / (||q_i|| + eps) from the raw rows 64..127 of the tile, one thread per row
+          const int row = gt - 192;
+          float ss = 0.f;
+#pragma unroll
+          for (int it = 0; it < 16; ++it) {
+            const uint4 c = *reinterpret_cast<const uint4*>(sQKp + tc::core_off(64 + row, it * 8, RBS));
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&c);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = __bfloat1622float2(h2[e]);
+              ss += f.x * f.x + f.y * f.y;
+            }
+          }
+          ctl.rq[s][row] = p.l2norm ? p.scale / (sqrtf(ss) + 1e-6f) : p.scale;
+        }
+      });
       WEND(5);
+      PROF(1);
       WSTART;
+      // the consumer's U^T, W^T products of the previous chunk have read Tb, Tw (and V)
+      if (n >= 1) wait_bar(&ctl.uwfree, (n - 1) & 1);
+      if (!P.use_tma_in && n >= 1) issue_v(n);   // (with TMA the consumer fetched it)
       {
         const int rin = gt & 7, jb = (gt >> 3) & 7, rbq = gt >> 6;
         float bj[8], bw[8];
@@ -632,62 +597,10 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         }
       }
       WEND(6);
-      WSTART;
-      tc::cp_async_wait_1();  // this chunk's V tile has landed (the newest group is the next chunk's K,Q)
-      if (P.use_tma_in) wait_bar(&ctl.vb, n & 1);
+      if (!P.use_tma_in) tc::cp_async_wait_all();   // this chunk's V rows
       tc::fence_async_smem();
-      // the stage accumulator and the W / output-staging region are released by the output epilogue
-      if (n >= 2) wait_bar(&ctl.late[s], ((n >> 1) - 1) & 1);
-      WEND(7);
-      group_sync(1);
+      mbar_arrive(tc::smem_u32(&ctl.full[s]));   // A_qk, Tb, Tw, the scalars (and V) of chunk n are ready
       PROF(5);
-      // ---- (2) W^T = K^^T Tw^T -> scratch;  U^T = V^T Tb^T -> stage accumulator ---------------------------
-      if (gt == 0) {
-        tc::tc_fence_after();
-        const uint32_t aV = tc::smem_u32(sV), aK = tc::smem_u32(sQK);
-        const uint32_t aTb = tc::smem_u32(sTb), aTw = tc::smem_u32(sTw);
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          const uint64_t ad = tc::smem_desc(aK + ks * 2 * RBS, RBS, 128);   // MN-major, 16 chunk rows per step
-          const uint64_t bd = tc::smem_desc(aTw + ks * 256, 128, A_RBS);
-          tc::mma_ss(tbase + TM_D1, ad, bd, id_n64_amn, ks > 0);
-        }
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          const uint64_t ad = tc::smem_desc(aV + ks * 2 * RBS, RBS, 128);
-          const uint64_t bd = tc::smem_desc(aTb + ks * 256, 128, A_RBS);
-          tc::mma_ss(tbase + TM_DU + 64 * s, ad, bd, id_n64_amn, ks > 0);
-        }
-        tc::mma_commit(tc::smem_u32(&ctl.barP));
-      }
-      // while the products run: decay scan of the NEXT chunk (its g, beta were prefetched above)
-      if (n + 1 < nchunks) {
-        tc::cp_async_wait_all();
-        group_sync(1);
-        if (n >= 1) wait_bar(&ctl.empty[(n + 1) & 1], (((n + 1) >> 1) - 1) & 1);  // the stage's scalars are free
-        if (warp == 1) scan_stage(n + 1);
-      }
-      wait_bar(&ctl.barP, phP); phP ^= 1;
-      tc::tc_fence_after();
-      PROF(6);
-      WSTART;
-      if (n + 1 < nchunks) issue_v(n + 1);  // the V tile is free again
-      // ---- W^T[k][c] (lane = k) -> bf16 tile W[c][k] (K-major B operand of (3)) ----------------------------
-      {
-        const int c0 = 32 * hs;
-        uint32_t r[32];
-        tc::tmem_ld32(tbase + TM_D1 + lane_addr + c0, r);
-        tc::tc_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          *reinterpret_cast<__nv_bfloat16*>(sWt + ((c0 + j) >> 3) * W_RBS + (l128 >> 3) * W_KBS + ((c0 + j) & 7) * 16 +
-                                            (l128 & 7) * 2) = __float2bfloat16_rn(__uint_as_float(r[j]));
-      }
-      tc::fence_async_smem();
-      WEND(2);
-      tc::tc_fence_before();
-      mbar_arrive(tc::smem_u32(&ctl.full[s]));
-      PROF(7);
     }
   } else {
     // =========================== CONSUMER ===========================================================
@@ -736,8 +649,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         group_sync(2);
         if (gt == 0) {  // one tiled store of the whole chunk; rows past T are clipped by the tensor map
           tc::tma_store_4d(&P.to, tc::smem_u32(sO), 0, t0m, h, b);
-          tc::bulk_commit();
-          tc::bulk_wait_read_all();  // the staging tile may be overwritten after this
+          tc::bulk_commit();   // its shared-memory reads are awaited before the tile is written again
         }
       } else {
         group_sync(2);
@@ -749,7 +661,6 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
             reinterpret_cast<uint4*>(dst)[j] = reinterpret_cast<const uint4*>(sO + r * kD + 32 * qtr)[j];
         }
       }
-      mbar_arrive(tc::smem_u32(&ctl.late[sm_]));
     };
 
     PROF_DECL
@@ -758,11 +669,33 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       uint8_t* st = smem + SM_STAGE + s * STAGE_BYTES;
       const uint8_t* sQKc = smem + SM_QKR + (n % 3) * QK_TILE;
       const uint32_t aQK = tc::smem_u32(sQKc), aW = tc::smem_u32(st + ST_W), aAqk = tc::smem_u32(st + ST_AQK);
-      const float* sEG = reinterpret_cast<const float*>(st + ST_SC) + 64;
+      const float* sEG = ctl.sc[n % 3] + 64;
       const float* sWd = sEG + 64;
+      uint8_t* sWt = st + ST_W;
       wait_bar_relaxed(&ctl.full[s], (n >> 1) & 1);
       tc::tc_fence_after();
       PROF(16);
+      // ---- (2) W^T = K^T Tw^T -> the (idle) bf16 V_new columns;  U^T = V^T Tb^T -> stage accumulator ----------
+      if (gt == 0) {
+        // the output store that read this stage's staging tile (chunk n-2) has finished reading it; every
+        // other thread learns that through the completion barrier of the products issued next
+        if (P.use_tma_out) tc::bulk_wait_read_all();
+        if (P.use_tma_in) wait_bar(&ctl.vb, n & 1);
+        const uint32_t aV = tc::smem_u32(smem + SM_V), aTb = tc::smem_u32(smem + SM_TB), aTw = tc::smem_u32(smem + SM_TW);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint64_t ad = tc::smem_desc(aQK + ks * 2 * RBS, RBS, 128);   // K MN-major, 16 chunk rows per step
+          const uint64_t bd = tc::smem_desc(aTw + ks * 256, 128, A_RBS);
+          tc::mma_ss(tbase + TM_VA, ad, bd, id_n64_amn, ks > 0);
+        }
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint64_t ad = tc::smem_desc(aV + ks * 2 * RBS, RBS, 128);
+          const uint64_t bd = tc::smem_desc(aTb + ks * 256, 128, A_RBS);
+          tc::mma_ss(tbase + TM_DU + 64 * s, ad, bd, id_n64_amn, ks > 0);
+        }
+        tc::mma_commit(tc::smem_u32(&ctl.barUW));
+      }
       // ---- state pass: bf16 copy of S^T for the products; fp32 master pre-multiplied by e^{G_L} --------
       {
         const float gl = sEG[63];
@@ -786,9 +719,33 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         }
         tc::tc_wait_st();
       }
+      PROF(17);
+      // ---- W^T[k][c] (lane = k) -> bf16 tile W[c][k] (K-major B operand of (3)) ----------------------------
+      wait_bar(&ctl.barUW, n & 1);
+      tc::tc_fence_after();
+      if (gt == 0) {
+        // Tb, Tw and the V tile are free again: tell the producer, and fetch the next chunk's V rows
+        mbar_arrive(tc::smem_u32(&ctl.uwfree));
+        if (P.use_tma_in && n + 1 < nchunks) {
+          const uint32_t bar = tc::smem_u32(&ctl.vb);
+          tc::mbar_arrive_expect_tx(bar, 64u * 256);
+          tc::tma_load_5d(tc::smem_u32(smem + SM_V), &P.tv, 0, 0, 0, (n + 1) * 8, unit, bar);
+        }
+      }
+      {
+        const int c0 = 32 * hs;
+        uint32_t r[32];
+        tc::tmem_ld32(tbase + TM_VA + lane_addr + c0, r);
+        tc::tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          *reinterpret_cast<__nv_bfloat16*>(sWt + ((c0 + j) >> 3) * W_RBS + (l128 >> 3) * W_KBS + ((c0 + j) & 7) * 16 +
+                                            (l128 & 7) * 2) = __float2bfloat16_rn(__uint_as_float(r[j]));
+      }
+      tc::fence_async_smem();
       tc::tc_fence_before();
       group_sync(2);
-      PROF(17);
+      PROF(22);
       // ---- (3) V_new^T = U^T - S^T W^T --------------------------------------------------------------------
       if (gt == 0) {
         tc::tc_fence_after();
@@ -798,23 +755,6 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
           tc::mma_ts(tbase + TM_DU + 64 * s, tbase + TM_SB + ks * 8, bd, id_n64_neg, 1);
         }
         tc::mma_commit(tc::smem_u32(&ctl.bar1));
-      }
-      {  // query norms of this chunk (raw rows 64..127 of the tile): rq_i = scale / (||q_i|| + eps)
-        const int row = gt >> 2, part = gt & 3;
-        float ss = 0.f;
-#pragma unroll
-        for (int it = 0; it < 4; ++it) {
-          const uint4 c = *reinterpret_cast<const uint4*>(sQKc + tc::core_off(64 + row, (4 * part + it) * 8, RBS));
-          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&c);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 f = __bfloat1622float2(h2[e]);
-            ss += f.x * f.x + f.y * f.y;
-          }
-        }
-        ss += __shfl_xor_sync(0xffffffffu, ss, 1);
-        ss += __shfl_xor_sync(0xffffffffu, ss, 2);
-        if (part == 0) ctl.rq[s][row] = p.l2norm ? p.scale / (sqrtf(ss) + 1e-6f) : p.scale;
       }
       if (n > 0) final_epilogue(n - 1);  // overlaps (3); frees Dq and the other stage
       tc::tc_fence_before();
