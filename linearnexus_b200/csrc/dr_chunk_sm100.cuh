@@ -9,24 +9,27 @@
 // warps share each 32-lane quarter of tensor memory and split the columns of every epilogue):
 //
 //   PRODUCER (warps 0-7): everything that does not depend on the state.
-//     K,Q rows arrive by 1-D bulk copies (cp.async.bulk + mbarrier) one chunk ahead; V rows are
-//     scattered straight into their core-matrix tile by 16-byte cp.async.
-//     l2-normalise K^,Q^ (fp32) -> core-matrix tile [K^;Q^]
-//     (1) D1 = [K^;Q^] K^^T                          128x64x128  smem x smem
-//         A_kk = beta_i D1[i][j] e^{G_i-G_j} (i>j);  A_qk = D1[64+i][j] e^{G_i-G_j} (i>=j) -> bf16 tile
-//         T = (I + A_kk)^-1: blocked forward substitution on the CUDA cores (fp32)
-//         -> Tb = T diag(beta), Tw = T diag(beta e^G)   bf16 tiles
-//     (2) U^T = V^T Tb^T  -> TMEM (stage accumulator)  128x64x64   smem(MN-major) x smem
-//         W^T = K^^T Tw^T -> TMEM -> bf16 tile W       128x64x64   smem(MN-major) x smem
+//     Raw K,Q rows of a chunk land by TMA as one [K;Q] tile already in core-matrix order, two chunks
+//     ahead (3-deep ring).  The l2 norms are not applied to the tiles: they are folded into row and
+//     column factors (rk from the diagonal of (1), rq from the raw Q rows).
+//     (1) D1 = [K;Q] K^T                             128x64x128  smem x smem, issued one chunk ahead
+//         X = D1[i][j] e^{G_i-G_j} (i>j, fp32);  A_qk = D1[64+i][j] e^{G_i-G_j} (i>=j) -> bf16 tile
+//         T = (I + diag(beta rk^2) X)^-1: 8x8 blocks by substitution, three merge levels on mma.sync tf32;
+//         the first two levels occupy warps 0-3 while warps 4-7 issue (1) of the next chunk, scan its
+//         decay and take the query norms
+//         -> Tb = T diag(beta rk), Tw = T diag(beta e^G rk^2)   bf16 tiles
 //   CONSUMER (warps 8-15): the serial chain over the state.
+//     (2) U^T = V^T Tb^T  -> TMEM (stage accumulator)  128x64x64   smem(MN-major) x smem
+//         W^T = K^T Tw^T  -> idle TMEM columns -> bf16 tile W      smem(MN-major) x smem
+//         (issued the moment the chunk is handed over; the next chunk's V rows are fetched when they complete)
 //         bf16 copy of S^T for the products; fp32 S^T pre-multiplied by e^{G_L}
-//     (3) V_new^T = U^T - S^T W^T  (accumulated onto the producer's U^T with negate-A)   128x64x128
-//         Dq = S^T Q^^T                                                                   128x64x128
-//     (4) Do = V_new^T A_qk^T                                                             128x64x64
-//     (5) S^T += (V_new^T e^{G_L-G_c}) K^   (K^ read MN-major)                             128x128x64
-//         O^T[v][i] = e^{G_i} Dq[v][i] + Do[v][i], written one chunk late so that it overlaps (3)
+//     (3) V_new^T = U^T - S^T W^T  (accumulated onto U^T with negate-A)                    128x64x128
+//         Dq = S^T Q^T                                                                     128x64x128
+//     (4) Do = V_new^T A_qk^T                                                              128x64x64
+//     (5) S^T += (V_new^T e^{G_L-G_c}) K   (K read MN-major)                                128x128x64
+//         O^T[v][i] = rq_i e^{G_i} Dq[v][i] + rq_i Do[v][i], written one chunk late so that it overlaps (3)
 //
-// The [K^;Q^] tile is stored once as 8x8 core matrices and serves as A and B of (1), MN-major
+// The [K;Q] tile is stored once as 8x8 core matrices and serves as A and B of (1), MN-major
 // A of (2), K-major B of (3) and MN-major B of (5).  Every wait on an mbarrier is bounded; a
 // wait that runs out sets DR_DEV_TIMEOUT in the status word and the kernel finishes without
 // further waiting.
