@@ -759,6 +759,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         }
         tc::mma_commit(tc::smem_u32(&ctl.bar1));
       }
+      PROF(23);
       if (n > 0) final_epilogue(n - 1);  // overlaps (3); frees Dq and the other stage
       tc::tc_fence_before();
       group_sync(2);
