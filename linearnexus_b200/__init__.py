@@ -10,6 +10,7 @@ from .ops import (delta_rule_chunkwise, delta_rule_recurrent, delta_rule_recurre
                   delta_rule_step, gated_delta_rule_chunkwise, gated_delta_rule_recurrent,
                   gated_delta_rule_step, kda_chunkwise, kda_recurrent, kda_step)
 from .state import DeltaNetState, GatedDeltaNetState, KDAState
+from .host_pipeline import HostPipeline, chunkwise_from_host
 
 __all__ = [
     "delta_rule_recurrent", "delta_rule_chunkwise", "delta_rule_step", "delta_rule_recurrent_pallas",
@@ -17,4 +18,5 @@ __all__ = [
     "kda_recurrent", "kda_chunkwise", "kda_step",
     "DeltaNetState", "GatedDeltaNetState", "KDAState",
     "KernelBackend", "backend_availability", "select_kernel_backend",
+    "HostPipeline", "chunkwise_from_host",
 ]
