@@ -872,18 +872,20 @@ inline bool make_input_map(CUtensorMap* m, const void* base, int64_t units, int 
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// 4-d output view {128, T, H, B} of [B,H,T,128] or [B,T,H,128].
-inline bool make_output_map(CUtensorMap* m, void* base, const SeqMap& sm) {
+// 4-d output view {128, T, H, B} of [B,H,T,128] or [B,T,H,128], bf16 (elem_bytes 2) or fp32 (4).
+inline bool make_output_map(CUtensorMap* m, void* base, const SeqMap& sm, int elem_bytes = 2) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return false;
+  const cuuint64_t row = 128ull * elem_bytes;
   const cuuint64_t dims[4] = {128, (cuuint64_t)sm.T, (cuuint64_t)sm.H, (cuuint64_t)sm.B};
   cuuint64_t strides[3];
-  if (sm.bthd) { strides[0] = (cuuint64_t)sm.H * 256; strides[1] = 256; strides[2] = (cuuint64_t)sm.T * sm.H * 256; }
-  else { strides[0] = 256; strides[1] = (cuuint64_t)sm.T * 256; strides[2] = (cuuint64_t)sm.H * sm.T * 256; }
+  if (sm.bthd) { strides[0] = (cuuint64_t)sm.H * row; strides[1] = row; strides[2] = (cuuint64_t)sm.T * sm.H * row; }
+  else { strides[0] = row; strides[1] = (cuuint64_t)sm.T * row; strides[2] = (cuuint64_t)sm.H * sm.T * row; }
   const cuuint32_t box[4] = {128, 64, 1, 1};
   const cuuint32_t es[4] = {1, 1, 1, 1};
-  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return fn(m, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, dims,
+            strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 inline cudaError_t launch_chunk(const FwdParams& p, cudaStream_t stream) {

@@ -509,16 +509,35 @@ constexpr int ST_O = 2 * WS_REC;
 constexpr int ST_TOTAL = ST_O + 64 * 128 * 4;
 
 struct StateCtl {
-  uint64_t full[2], bar1, bar2;
+  uint64_t full[2], go1, go2, go3, bar1, bar2;
   uint32_t tmem_base;
   int abort;
 };
 
-__global__ void __launch_bounds__(kThreads, 1) state_kernel(const FwdParams p, const uint8_t* __restrict__ ws) {
+// Nine warps.  Warps 0-7 (256 threads; two warps per 32-lane quarter of tensor memory, each taking half of the
+// columns) do everything that touches data; warp 8 only issues: the bulk copies of the records and every
+// tcgen05.mma.  Issuing one product costs its thread ~100 cycles, 28 products per chunk: on a worker warp that
+// time would sit on the serial chain of the chunk, on the issuing warp it overlaps the workers' epilogues.
+// Hand-offs are mbarriers: go1 (bf16 state copy written), go2 (the previous chunk's Dq has been read),
+// go3 (bf16 V_new written) from the workers; bar1, bar2 (products complete) from tcgen05.commit.
+constexpr int kStateThreads = kThreads + 32;
+
+// Kernel parameters of the state pass: the forward parameters plus the output tensor map ({128, T, H, B} view of
+// o in its own dtype; one box {128, 64, 1, 1} stores a chunk's rows and clips the ragged tail).
+struct StateParams {
+  CUtensorMap to;
+  FwdParams p;
+  const uint8_t* ws;
+  int use_tma_out;
+};
+
+__global__ void __launch_bounds__(kStateThreads, 1) state_kernel(const __grid_constant__ StateParams P) {
+  const FwdParams& p = P.p;
+  const uint8_t* __restrict__ ws = P.ws;
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ __align__(8) StateCtl ctl;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int hs = tid >> 7, l128 = tid & 127;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int hs = (tid >> 7) & 1, l128 = tid & 127;
   const int T = p.map.T, nchunks = (T + kC - 1) / kC;
   const int unit = blockIdx.x;
   const int b = unit / p.map.H, h = unit % p.map.H;
@@ -532,6 +551,9 @@ __global__ void __launch_bounds__(kThreads, 1) state_kernel(const FwdParams p, c
   if (tid == 0) {
     tc::mbar_init(tc::smem_u32(&ctl.full[0]), 1);
     tc::mbar_init(tc::smem_u32(&ctl.full[1]), 1);
+    tc::mbar_init(tc::smem_u32(&ctl.go1), kThreads);
+    tc::mbar_init(tc::smem_u32(&ctl.go2), kThreads);
+    tc::mbar_init(tc::smem_u32(&ctl.go3), kThreads);
     tc::mbar_init(tc::smem_u32(&ctl.bar1), 1);
     tc::mbar_init(tc::smem_u32(&ctl.bar2), 1);
     tc::fence_mbar_init();
@@ -551,187 +573,224 @@ __global__ void __launch_bounds__(kThreads, 1) state_kernel(const FwdParams p, c
       }
     }
   };
-  // the whole record of chunk m -> buffer m & 1, one bulk copy (the record is contiguous)
-  auto issue_load = [&](int m) {
-    const uint32_t bar = tc::smem_u32(&ctl.full[m & 1]);
-    tc::mbar_arrive_expect_tx(bar, WS_REC);
-    const uint32_t dst = tc::smem_u32(smem + (m & 1) * WS_REC);
-    const uint8_t* src = recs + (int64_t)m * WS_REC;
-    // four copies so that several are in flight
-    constexpr int Q4 = WS_REC / 4;   // 20608, a multiple of 16
-#pragma unroll
-    for (int i = 0; i < 4; ++i) tc::bulk_g2s(dst + i * Q4, src + i * Q4, Q4, bar);
-  };
-  if (tid == 0) {
-    if (nchunks > 0) issue_load(0);
-    if (nchunks > 1) issue_load(1);
-  }
+  auto arrive = [&](uint64_t* bar) { sm100::mbar_arrive(tc::smem_u32(bar)); };
+  auto workers_sync = [&]() { asm volatile("bar.sync 1, 256;" ::: "memory"); };
 
-  const uint32_t id_n64 = tc::idesc_bf16(128, 64, 0, 0);
-  const uint32_t id_n64_amn = tc::idesc_bf16(128, 64, 1, 0);
-  const uint32_t id_n64_neg = id_n64 | (1u << 13);
-  const uint32_t id_n128_bmn = tc::idesc_bf16(128, 128, 0, 1);
-
-  // initial state: S^T[v][k] = h0[k][v]
-  {
-    const float* h0 = p.h0 ? p.h0 + (int64_t)unit * kD * kD : nullptr;
+  if (warp == 8) {
+    // =========================== ISSUING WARP (one thread) ======================================================
+    if (tid == kThreads) {
+      // the whole record of chunk m -> buffer m & 1 (the record is contiguous; four copies in flight)
+      auto issue_load = [&](int m) {
+        const uint32_t bar = tc::smem_u32(&ctl.full[m & 1]);
+        tc::mbar_arrive_expect_tx(bar, WS_REC);
+        const uint32_t dst = tc::smem_u32(smem + (m & 1) * WS_REC);
+        const uint8_t* src = recs + (int64_t)m * WS_REC;
+        constexpr int Q4 = WS_REC / 4;   // 20608, a multiple of 16
 #pragma unroll
-    for (int cc = 0; cc < 2; ++cc) {
-      const int c0 = 64 * hs + 32 * cc;
-      uint32_t r[32];
+        for (int i = 0; i < 4; ++i) tc::bulk_g2s(dst + i * Q4, src + i * Q4, Q4, bar);
+      };
+      if (nchunks > 0) issue_load(0);
+      if (nchunks > 1) issue_load(1);
+      const uint32_t id_n64 = tc::idesc_bf16(128, 64, 0, 0);
+      const uint32_t id_n64_amn = tc::idesc_bf16(128, 64, 1, 0);
+      const uint32_t id_n64_neg = id_n64 | (1u << 13);
+      const uint32_t id_n128_bmn = tc::idesc_bf16(128, 128, 0, 1);
+      for (int n = 0; n < nchunks; ++n) {
+        const int s = n & 1;
+        const uint8_t* st = smem + s * WS_REC;
+        const uint32_t aW = tc::smem_u32(st + WS_W), aQg = tc::smem_u32(st + WS_QG), aKd = tc::smem_u32(st + WS_KD);
+        const uint32_t aV = tc::smem_u32(st + WS_V), aTb = tc::smem_u32(st + WS_TB), aAqk = tc::smem_u32(st + WS_AQK);
+        wait_bar(&ctl.full[s], (n >> 1) & 1);
+        // U^T = V^T Tb^T needs no state: issue it before the workers' state pass has finished
+        tc::tc_fence_after();
 #pragma unroll
-      for (int j = 0; j < 32; ++j) r[j] = h0 ? __float_as_uint(h0[(c0 + j) * kD + l128]) : 0u;
-      tc::tmem_st32(tbase + TM_S + lane_addr + c0, r);
-    }
-    tc::tc_wait_st();
-  }
-  float* sO = reinterpret_cast<float*>(smem + ST_O);
-  // O^T of chunk m = Dq + Do -> staging tile -> rows of the output
-  auto output_epilogue = [&](int m) {
-    const int t0m = m * kC, rowsm = min(kC, T - t0m);
-    {
-      const int c0 = 32 * hs;
-      uint32_t rq[32], ro[32];
-      tc::tmem_ld32(tbase + TM_DQ + lane_addr + c0, rq);
-      tc::tmem_ld32(tbase + TM_DU + 64 * (m & 1) + lane_addr + c0, ro);
-      tc::tc_wait_ld();
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint64_t ad = tc::smem_desc(aV + ks * 2 * RBS, RBS, 128);   // MN-major, 16 chunk rows per step
+          const uint64_t bd = tc::smem_desc(aTb + ks * 256, 128, A_RBS);
+          tc::mma_ss(tbase + TM_DU + 64 * s, ad, bd, id_n64_amn, ks > 0);
+        }
+        wait_bar(&ctl.go1, n & 1);
+        tc::tc_fence_after();
 #pragma unroll
-      for (int j = 0; j < 32; ++j) sO[(c0 + j) * kD + l128] = __uint_as_float(rq[j]) + __uint_as_float(ro[j]);
-    }
-    tc::tc_fence_before();
-    __syncthreads();
-    if (p.o) {
-      const int r = tid >> 2, qtr = tid & 3;
-      if (r < rowsm) {
-        const float* src = sO + r * kD + 32 * qtr;
-        const int64_t at = o_base + (int64_t)(t0m + r) * o_tok + 32 * qtr;
-        if (p.out_dt == DR_BF16) {
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.o) + at;
+        for (int ks = 0; ks < 8; ++ks) {   // Vn^T = U^T - S^T W^T
+          const uint64_t bd = tc::smem_desc(aW + ks * 256, 128, RBS);
+          tc::mma_ts(tbase + TM_DU + 64 * s, tbase + TM_SB + ks * 8, bd, id_n64_neg, 1);
+        }
+        tc::mma_commit(tc::smem_u32(&ctl.bar1));
+        if (n > 0) wait_bar(&ctl.go2, (n - 1) & 1);   // the previous chunk's Dq has been read
+        tc::tc_fence_after();
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float x[8];
+        for (int ks = 0; ks < 8; ++ks) {   // Dq = S^T Qg^T
+          const uint64_t bd = tc::smem_desc(aQg + ks * 256, 128, RBS);
+          tc::mma_ts(tbase + TM_DQ, tbase + TM_SB + ks * 8, bd, id_n64, ks > 0);
+        }
+        wait_bar(&ctl.go3, n & 1);
+        tc::tc_fence_after();
 #pragma unroll
-            for (int e = 0; e < 8; ++e) x[e] = src[8 * j + e];
-            reinterpret_cast<uint4*>(dst)[j] = pack8(x);
-          }
-        } else {
-          float* dst = reinterpret_cast<float*>(p.o) + at;
+        for (int ks = 0; ks < 4; ++ks) {   // S^T += Vn^T Kd   (Kd MN-major)
+          const uint64_t bd = tc::smem_desc(aKd + ks * 2 * RBS, RBS, 128);
+          tc::mma_ts(tbase + TM_S, tbase + TM_VA + ks * 8, bd, id_n128_bmn, 1);
+        }
 #pragma unroll
-          for (int j = 0; j < 8; ++j) reinterpret_cast<float4*>(dst)[j] = reinterpret_cast<const float4*>(src)[j];
+        for (int ks = 0; ks < 4; ++ks) {   // Do = Vn^T A_qk^T
+          const uint64_t bd = tc::smem_desc(aAqk + ks * 256, 128, A_RBS);
+          tc::mma_ts(tbase + TM_DU + 64 * s, tbase + TM_VA + ks * 8, bd, id_n64, ks > 0);
+        }
+        tc::mma_commit(tc::smem_u32(&ctl.bar2));
+        // every product that reads this buffer has completed once bar2 flips: fetch the record of chunk n + 2
+        if (n + 2 < nchunks) {
+          wait_bar(&ctl.bar2, n & 1);
+          tc::fence_async_smem();
+          issue_load(n + 2);
         }
       }
     }
-  };
-
-  uint32_t ph1 = 0, ph2 = 0;
-  for (int n = 0; n < nchunks; ++n) {
-    const int s = n & 1;
-    const uint8_t* st = smem + s * WS_REC;
-    const uint32_t aW = tc::smem_u32(st + WS_W), aQg = tc::smem_u32(st + WS_QG), aKd = tc::smem_u32(st + WS_KD);
-    const uint32_t aV = tc::smem_u32(st + WS_V), aTb = tc::smem_u32(st + WS_TB), aAqk = tc::smem_u32(st + WS_AQK);
-    const float* sEGL = reinterpret_cast<const float*>(st + WS_EGL);
-    wait_bar(&ctl.full[s], (n >> 1) & 1);
-    tc::tc_fence_after();
-    // ---- state pass: bf16 copy of S^T for the products; fp32 master decayed per key channel -------------------
+  } else {
+    // =========================== WORKERS ===========================================================================
+    // initial state: S^T[v][k] = h0[k][v]
     {
+      const float* h0 = p.h0 ? p.h0 + (int64_t)unit * kD * kD : nullptr;
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int c0 = 64 * hs + 32 * cc;
-        uint32_t r[32], pk[16];
-        tc::tmem_ld32(tbase + TM_S + lane_addr + c0, r);
-        tc::tc_wait_ld();
+        uint32_t r[32];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) pk[j] = tc::pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-        if (p.ckpt) {
-          float* ck = p.ckpt + ((int64_t)unit * nchunks + n) * kD * kD;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) ck[(c0 + j) * kD + l128] = __uint_as_float(r[j]);
-        }
-#pragma unroll
-        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * sEGL[c0 + j]);
-        tc::tmem_st16(tbase + TM_SB + lane_addr + c0 / 2, pk);
+        for (int j = 0; j < 32; ++j) r[j] = h0 ? __float_as_uint(h0[(c0 + j) * kD + l128]) : 0u;
         tc::tmem_st32(tbase + TM_S + lane_addr + c0, r);
       }
       tc::tc_wait_st();
     }
-    tc::tc_fence_before();
-    __syncthreads();
-    // ---- U^T = V^T Tb^T, then Vn^T = U^T - S^T W^T ---------------------------------------------------------------
-    if (tid == 0) {
+    float* sO = reinterpret_cast<float*>(smem + ST_O);
+    __nv_bfloat16* sOh = reinterpret_cast<__nv_bfloat16*>(smem + ST_O);
+    // O^T of chunk m = Dq + Do -> staging tile [64][128] in the output dtype -> one tiled TMA store (or, without a
+    // tensor map, row copies by the threads)
+    auto output_epilogue = [&](int m) {
+      const int t0m = m * kC, rowsm = min(kC, T - t0m);
+      if (P.use_tma_out && tid == 0) tc::bulk_wait_read_all();   // the previous store has read the staging tile
+      workers_sync();
+      {
+        const int c0 = 32 * hs;
+        uint32_t rq[32], ro[32];
+        tc::tmem_ld32(tbase + TM_DQ + lane_addr + c0, rq);
+        tc::tmem_ld32(tbase + TM_DU + 64 * (m & 1) + lane_addr + c0, ro);
+        tc::tc_wait_ld();
+        tc::tc_fence_before();
+        arrive(&ctl.go2);   // Dq (and this accumulator) may be overwritten
+        if (p.out_dt == DR_BF16) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            sOh[(c0 + j) * kD + l128] = __float2bfloat16_rn(__uint_as_float(rq[j]) + __uint_as_float(ro[j]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) sO[(c0 + j) * kD + l128] = __uint_as_float(rq[j]) + __uint_as_float(ro[j]);
+        }
+      }
+      if (!p.o) return;
+      if (P.use_tma_out) {
+        tc::fence_async_smem();
+        workers_sync();
+        if (tid == 0) {
+          tc::tma_store_4d(&P.to, tc::smem_u32(sO), 0, t0m, h, b);
+          tc::bulk_commit();
+        }
+        return;
+      }
+      workers_sync();
+      const int r = tid >> 2, qtr = tid & 3;
+      if (r < rowsm) {
+        const int64_t at = o_base + (int64_t)(t0m + r) * o_tok + 32 * qtr;
+        if (p.out_dt == DR_BF16) {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.o) + at;
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            reinterpret_cast<uint4*>(dst)[j] = reinterpret_cast<const uint4*>(sOh + r * kD + 32 * qtr)[j];
+        } else {
+          float* dst = reinterpret_cast<float*>(p.o) + at;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            reinterpret_cast<float4*>(dst)[j] = reinterpret_cast<const float4*>(sO + r * kD + 32 * qtr)[j];
+        }
+      }
+    };
+
+#ifdef DR_PROFILE
+    unsigned long long sp0 = clock64();
+#define SPROF(idx) do { if (blockIdx.x == 0 && tid == 0) { const unsigned long long t_ = clock64(); sm100::g_prof[idx] += t_ - sp0; sp0 = t_; } } while (0)
+#else
+#define SPROF(idx)
+#endif
+    for (int n = 0; n < nchunks; ++n) {
+      const int s = n & 1;
+      const float* sEGL = reinterpret_cast<const float*>(smem + s * WS_REC + WS_EGL);
+      wait_bar(&ctl.full[s], (n >> 1) & 1);
+      SPROF(170);
+      if (n > 0) {
+        wait_bar(&ctl.bar2, (n - 1) & 1);   // the previous chunk's state update and Do have completed
+        tc::tc_fence_after();
+      }
+      SPROF(171);
+      // ---- state pass: bf16 copy of S^T for the products; fp32 master decayed per key channel -------------------
+      {
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c0 = 64 * hs + 32 * cc;
+          uint32_t r[32], pk[16];
+          tc::tmem_ld32(tbase + TM_S + lane_addr + c0, r);
+          tc::tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) pk[j] = tc::pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+          if (p.ckpt) {
+            float* ck = p.ckpt + ((int64_t)unit * nchunks + n) * kD * kD;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) ck[(c0 + j) * kD + l128] = __uint_as_float(r[j]);
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * sEGL[c0 + j]);
+          tc::tmem_st16(tbase + TM_SB + lane_addr + c0 / 2, pk);
+          tc::tmem_st32(tbase + TM_S + lane_addr + c0, r);
+        }
+        tc::tc_wait_st();
+      }
+      tc::tc_fence_before();
+      arrive(&ctl.go1);
+      SPROF(172);
+      if (n > 0) output_epilogue(n - 1);   // overlaps the products of this chunk
+      SPROF(173);
+      wait_bar(&ctl.bar1, n & 1);
       tc::tc_fence_after();
+      SPROF(174);
+      // ---- Vn^T -> bf16 -------------------------------------------------------------------------------------------
+      {
+        const int c0 = 32 * hs;
+        uint32_t r[32], pa[16];
+        tc::tmem_ld32(tbase + TM_DU + 64 * s + lane_addr + c0, r);
+        tc::tc_wait_ld();
 #pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {
-        const uint64_t ad = tc::smem_desc(aV + ks * 2 * RBS, RBS, 128);   // MN-major, 16 chunk rows per step
-        const uint64_t bd = tc::smem_desc(aTb + ks * 256, 128, A_RBS);
-        tc::mma_ss(tbase + TM_DU + 64 * s, ad, bd, id_n64_amn, ks > 0);
+        for (int j = 0; j < 16; ++j) pa[j] = tc::pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+        tc::tmem_st16(tbase + TM_VA + lane_addr + c0 / 2, pa);
       }
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const uint64_t bd = tc::smem_desc(aW + ks * 256, 128, RBS);
-        tc::mma_ts(tbase + TM_DU + 64 * s, tbase + TM_SB + ks * 8, bd, id_n64_neg, 1);
-      }
-      tc::mma_commit(tc::smem_u32(&ctl.bar1));
+      tc::tc_wait_st();
+      tc::tc_fence_before();
+      arrive(&ctl.go3);
+      SPROF(175);
     }
-    if (n > 0) output_epilogue(n - 1);   // overlaps the products; frees Dq
-    tc::tc_fence_before();
-    __syncthreads();
-    if (tid == 0) {  // Dq = S^T Qg^T
+    if (nchunks > 0) {
+      wait_bar(&ctl.bar2, (nchunks - 1) & 1);
       tc::tc_fence_after();
+      output_epilogue(nchunks - 1);
+      if (P.use_tma_out && tid == 0) tc::bulk_wait_all();
+    }
+    if (p.hT) {
+      float* hT = p.hT + (int64_t)unit * kD * kD;
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const uint64_t bd = tc::smem_desc(aQg + ks * 256, 128, RBS);
-        tc::mma_ts(tbase + TM_DQ, tbase + TM_SB + ks * 8, bd, id_n64, ks > 0);
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c0 = 64 * hs + 32 * cc;
+        uint32_t r[32];
+        tc::tmem_ld32(tbase + TM_S + lane_addr + c0, r);
+        tc::tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) hT[(c0 + j) * kD + l128] = __uint_as_float(r[j]);
       }
-    }
-    wait_bar(&ctl.bar1, ph1); ph1 ^= 1;
-    tc::tc_fence_after();
-    // ---- Vn^T -> bf16 -----------------------------------------------------------------------------------------------
-    {
-      const int c0 = 32 * hs;
-      uint32_t r[32], pa[16];
-      tc::tmem_ld32(tbase + TM_DU + 64 * s + lane_addr + c0, r);
-      tc::tc_wait_ld();
-#pragma unroll
-      for (int j = 0; j < 16; ++j) pa[j] = tc::pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-      tc::tmem_st16(tbase + TM_VA + lane_addr + c0 / 2, pa);
-    }
-    tc::tc_wait_st();
-    tc::tc_fence_before();
-    __syncthreads();
-    // ---- S^T += Vn^T Kd ;  Do = Vn^T A_qk^T ---------------------------------------------------------------------------
-    if (tid == 0) {
-      tc::tc_fence_after();
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {
-        const uint64_t bd = tc::smem_desc(aKd + ks * 2 * RBS, RBS, 128);  // Kd MN-major
-        tc::mma_ts(tbase + TM_S, tbase + TM_VA + ks * 8, bd, id_n128_bmn, 1);
-      }
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {
-        const uint64_t bd = tc::smem_desc(aAqk + ks * 256, 128, A_RBS);
-        tc::mma_ts(tbase + TM_DU + 64 * s, tbase + TM_VA + ks * 8, bd, id_n64, ks > 0);
-      }
-      tc::mma_commit(tc::smem_u32(&ctl.bar2));
-    }
-    wait_bar(&ctl.bar2, ph2); ph2 ^= 1;
-    tc::tc_fence_after();
-    // every product that reads this buffer is complete: fetch the record of chunk n + 2 into it
-    if (tid == 0 && n + 2 < nchunks) {
-      tc::fence_async_smem();
-      issue_load(n + 2);
-    }
-  }
-  if (nchunks > 0) output_epilogue(nchunks - 1);
-  if (p.hT) {
-    float* hT = p.hT + (int64_t)unit * kD * kD;
-#pragma unroll
-    for (int cc = 0; cc < 2; ++cc) {
-      const int c0 = 64 * hs + 32 * cc;
-      uint32_t r[32];
-      tc::tmem_ld32(tbase + TM_S + lane_addr + c0, r);
-      tc::tc_wait_ld();
-#pragma unroll
-      for (int j = 0; j < 32; ++j) hT[(c0 + j) * kD + l128] = __uint_as_float(r[j]);
     }
   }
   tc::tc_fence_before();
@@ -750,7 +809,12 @@ inline cudaError_t launch_chunk(const FwdParams& p, void* workspace, cudaStream_
   intra_kernel<<<(unsigned)(units * nchunks), kThreads, IN_TOTAL, stream>>>(p, ws);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  state_kernel<<<(unsigned)units, kThreads, ST_TOTAL, stream>>>(p, ws);
+  StateParams SP;
+  memset(&SP, 0, sizeof(SP));
+  SP.p = p;
+  SP.ws = ws;
+  SP.use_tma_out = p.o != nullptr && sm100::make_output_map(&SP.to, p.o, p.map, p.out_dt == DR_BF16 ? 2 : 4);
+  state_kernel<<<(unsigned)units, kStateThreads, ST_TOTAL, stream>>>(SP);
   *launches = 2;
   return cudaGetLastError();
 }

@@ -25,6 +25,8 @@ GDN = {0: "P barrier (scalars visible)", 2: "P wait stage + issue next K,Q", 3: 
 KDA = {147: "global loads q,k,g -> smem", 148: "V copy to the record", 140: "barrier", 141: "prefix sum of the decay",
        142: "A_kk, A_qk on mma.sync", 143: "exact diagonal blocks (if any) + barrier", 144: "inverse",
        145: "record tiles (Tb, A_qk, Qg, Kd)", 146: "W product + tile"}
+KDA_STATE = {170: "wait record", 171: "wait state update of previous chunk", 172: "state pass", 173: "output epilogue of previous chunk",
+             174: "wait Vn", 175: "Vn -> bf16"}
 BWD = {150: "loop barrier", 151: "stage q,k,v,dO,S0", 152: "decay scan", 153: "X, A build", 154: "R (+ barrier)",
        155: "inverse, Vn = T R", 156: "dVn", 157: "dR = T^T dVn", 158: "dV, dbeta, dA, dM", 159: "per (row, channel) products",
        160: "dS0"}
@@ -87,6 +89,10 @@ def main(which):
         print(f"  {nm:44s} {buf[i] / per:10.0f}")
         total += buf[i] / per
     print(f"  {'sum':44s} {total:10.0f}")
+    if which == "kda":
+        print("state kernel (workers, thread 0 of CTA 0), cycles per chunk")
+        for i, nm in KDA_STATE.items():
+            print(f"  {nm:44s} {buf[i] / (T // 64):10.0f}")
 
 
 if __name__ == "__main__":
