@@ -121,7 +121,7 @@ __device__ __forceinline__ uint4 pack8(const float (&x)[8]) {
 #define KPROF(idx)
 #endif
 
-__global__ void __launch_bounds__(kThreads, 2) intra_kernel(const FwdParams p, uint8_t* __restrict__ ws) {
+__global__ void __launch_bounds__(kThreads, 2) intra_kernel(const FwdParams p, uint8_t* __restrict__ ws, const int copy_v) {
   extern __shared__ __align__(1024) uint8_t smem[];
   float* sG = reinterpret_cast<float*>(smem + IN_G);
   __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem + IN_K);
@@ -196,8 +196,9 @@ __global__ void __launch_bounds__(kThreads, 2) intra_kernel(const FwdParams p, u
     }
   }
   KPROF(147);
-  // V rows -> the record's tile, 16 bytes per piece (coalesced writes)
-  {
+  // V rows -> the record's tile, 16 bytes per piece (coalesced writes); skipped when the state kernel can fetch
+  // the rows itself through a tensor map
+  if (copy_v) {
     const __nv_bfloat16* gv = reinterpret_cast<const __nv_bfloat16*>(p.v);
     const int64_t v_base = p.map.base(b, h, kD), v_tok = p.map.tok(kD);
 #pragma unroll
@@ -526,9 +527,10 @@ constexpr int kStateThreads = kThreads + 32;
 // o in its own dtype; one box {128, 64, 1, 1} stores a chunk's rows and clips the ragged tail).
 struct StateParams {
   CUtensorMap to;
+  CUtensorMap tv;   // 5-d view of v whose box is one 64x128 tile in core-matrix order (see sm100::make_input_map)
   FwdParams p;
   const uint8_t* ws;
-  int use_tma_out;
+  int use_tma_out, use_tma_v;
 };
 
 __global__ void __launch_bounds__(kStateThreads, 1) state_kernel(const __grid_constant__ StateParams P) {
@@ -585,9 +587,17 @@ __global__ void __launch_bounds__(kStateThreads, 1) state_kernel(const __grid_co
         tc::mbar_arrive_expect_tx(bar, WS_REC);
         const uint32_t dst = tc::smem_u32(smem + (m & 1) * WS_REC);
         const uint8_t* src = recs + (int64_t)m * WS_REC;
-        constexpr int Q4 = WS_REC / 4;   // 20608, a multiple of 16
+        if (P.use_tma_v) {
+          // the V rows straight from the input tensor; the record carries the other tiles
+          tc::tma_load_5d(dst + WS_V, &P.tv, 0, 0, 0, m * 8, unit, bar);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) tc::bulk_g2s(dst + i * Q4, src + i * Q4, Q4, bar);
+          for (int i = 0; i < 3; ++i) tc::bulk_g2s(dst + i * 16384, src + i * 16384, 16384, bar);   // W, Qg, Kd
+          tc::bulk_g2s(dst + WS_TB, src + WS_TB, WS_REC - WS_TB, bar);                                   // Tb, A_qk, e^{G_L}
+        } else {
+          constexpr int Q4 = WS_REC / 4;   // 20608, a multiple of 16
+#pragma unroll
+          for (int i = 0; i < 4; ++i) tc::bulk_g2s(dst + i * Q4, src + i * Q4, Q4, bar);
+        }
       };
       if (nchunks > 0) issue_load(0);
       if (nchunks > 1) issue_load(1);
@@ -806,13 +816,15 @@ inline cudaError_t launch_chunk(const FwdParams& p, void* workspace, cudaStream_
   const int64_t units = (int64_t)p.map.B * p.map.H;
   const int nchunks = (p.map.T + kC - 1) / kC;
   uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
-  intra_kernel<<<(unsigned)(units * nchunks), kThreads, IN_TOTAL, stream>>>(p, ws);
-  e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
   StateParams SP;
   memset(&SP, 0, sizeof(SP));
   SP.p = p;
   SP.ws = ws;
+  // V rows by TMA need the rows of one sequence contiguous and whole 8-row blocks
+  SP.use_tma_v = !p.map.bthd && p.map.T % 8 == 0 && sm100::make_input_map(&SP.tv, p.v, units, p.map.T);
+  intra_kernel<<<(unsigned)(units * nchunks), kThreads, IN_TOTAL, stream>>>(p, ws, SP.use_tma_v ? 0 : 1);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
   SP.use_tma_out = p.o != nullptr && sm100::make_output_map(&SP.to, p.o, p.map, p.out_dt == DR_BF16 ? 2 : 4);
   state_kernel<<<(unsigned)units, kStateThreads, ST_TOTAL, stream>>>(SP);
   *launches = 2;
