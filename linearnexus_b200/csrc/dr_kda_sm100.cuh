@@ -171,6 +171,7 @@ __global__ void __launch_bounds__(kThreads, 2) intra_kernel(const FwdParams p, u
         }
       }
     }
+    KPROF(149);
     float bt = 0.f;
     if (lane < 8 && warp + 8 * lane < rows) bt = p.beta[s_base + (t0 + warp + 8 * lane) * s_tok];
 #pragma unroll

@@ -22,7 +22,7 @@ GDN = {0: "P barrier (scalars visible)", 2: "P wait stage + issue next K,Q", 3: 
        1: "P issue next D1 / decay scan", 5: "P inverse, Tb/Tw, q norms, arrive",
        16: "C wait for the producer", 17: "C issue U^T,W^T + state pass", 22: "C wait U^T,W^T; W tile", 23: "C issue Vn (8 products, thread 0)", 18: "C output epilogue + barrier",
        19: "C wait Vn (+ issue Dq)", 20: "C Vn -> bf16", 21: "C Do, state update + wait"}
-KDA = {147: "global loads q,k,g -> smem", 148: "V copy to the record", 140: "barrier", 141: "prefix sum of the decay",
+KDA = {149: "issue global loads q,k,g", 147: "first use -> smem, norms", 148: "V copy to the record", 140: "barrier", 141: "prefix sum of the decay",
        142: "A_kk, A_qk on mma.sync", 143: "exact diagonal blocks (if any) + barrier", 144: "inverse",
        145: "record tiles (Tb, A_qk, Qg, Kd)", 146: "W product + tile"}
 KDA_STATE = {170: "wait record", 171: "wait state update of previous chunk", 172: "state pass", 173: "output epilogue of previous chunk",
