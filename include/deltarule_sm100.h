@@ -76,7 +76,11 @@ typedef struct DrDesc {
   int32_t use_qk_l2norm; /* 1: normalise q,k rows as x/(||x||+1e-6) inside the kernel */
   float scale;           /* multiplies q after normalisation */
   int32_t path;          /* DrChunkPath, chunk entry points only */
-  int32_t reserved[2];   /* must be zero */
+  int32_t qk_heads;      /* heads of q and k when fewer than H (grouped value attention: head h of v, o, g, beta,
+                            state uses q/k head h / (H / qk_heads)); 0 or H: one q/k head per head.  Replaces the
+                            jnp.repeat of q, k before the op (gated_deltanet.py:798-801, kda.py:917-922).
+                            Forward entry points only. */
+  int32_t reserved;      /* must be zero */
 } DrDesc;
 
 /* Library / build identification, e.g. "deltarule_sm100 0.1 (sm_100a)". */

@@ -39,7 +39,7 @@ class DrDesc(ctypes.Structure):
         ("K", ctypes.c_int32), ("V", ctypes.c_int32), ("chunk", ctypes.c_int32),
         ("qkv_dtype", ctypes.c_int32), ("g_dtype", ctypes.c_int32), ("out_dtype", ctypes.c_int32),
         ("use_qk_l2norm", ctypes.c_int32), ("scale", ctypes.c_float), ("path", ctypes.c_int32),
-        ("reserved", ctypes.c_int32 * 2),
+        ("qk_heads", ctypes.c_int32), ("reserved", ctypes.c_int32),
     ]
 
 

@@ -9,6 +9,7 @@
 #include "dr_chunk_fp32.cuh"
 #include "dr_chunk_sm100.cuh"
 #include "dr_kda_sm100.cuh"
+#include "dr_step_stream.cuh"
 #include "dr_bwd.cuh"
 #include "dr_common.cuh"
 #include "dr_recurrent.cuh"
@@ -40,7 +41,8 @@ int validate_common(const DrDesc* d, bool need_chunk) {
   if (d->V < 4 || d->V > 256 || d->V % 4) return DR_ERR_SHAPE;
   if (!dtype_ok(d->qkv_dtype) || !dtype_ok(d->out_dtype)) return DR_ERR_DTYPE;
   if (d->variant != DR_DELTA && !dtype_ok(d->g_dtype)) return DR_ERR_DTYPE;
-  if (d->reserved[0] || d->reserved[1]) return DR_ERR_SHAPE;
+  if (d->qk_heads < 0 || (d->qk_heads > 0 && (d->qk_heads > d->H || d->H % d->qk_heads))) return DR_ERR_SHAPE;
+  if (d->reserved) return DR_ERR_SHAPE;
   if (need_chunk) {
     if (d->chunk < 1) return DR_ERR_CHUNK;
     // The reference raises ValueError when chunk_size % 16 != 0 for Gated DeltaNet and KDA
@@ -58,6 +60,7 @@ dr::FwdParams make_fwd(const DrDesc* d, const void* q, const void* k, const void
   p.status = status;
   p.ckpt = nullptr;
   p.map.B = d->B; p.map.H = d->H; p.map.T = d->T; p.map.bthd = d->layout == DR_LAYOUT_BTHD;
+  p.map.Hq = d->qk_heads > 0 ? d->qk_heads : d->H;
   p.K = d->K; p.V = d->V; p.C = d->chunk;
   p.variant = d->variant; p.qkv_dt = d->qkv_dtype; p.g_dt = d->g_dtype; p.out_dt = d->out_dtype;
   p.l2norm = d->use_qk_l2norm; p.scale = d->scale;
@@ -72,6 +75,18 @@ int validate_fwd_ptrs(const DrDesc* d, const void* q, const void* k, const void*
       (g && !aligned16(g)) || (h0 && !aligned16(h0)) || (hT && !aligned16(hT)))
     return DR_ERR_ALIGN;
   return DR_OK;
+}
+
+// SM count of the current device (cached per host thread and device)
+int sm_count() {
+  thread_local int cached_dev = -1, cached = 0;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (dev != cached_dev) {
+    if (cudaDeviceGetAttribute(&cached, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    cached_dev = dev;
+  }
+  return cached;
 }
 
 bool tcgen05_eligible(const DrDesc* d) {
@@ -200,11 +215,18 @@ int dr_step(const DrDesc* d, const void* q, const void* k, const void* v, const 
   dr::StepParams p;
   p.q = q; p.k = k; p.v = v; p.g = g; p.beta = beta; p.s_in = state_in; p.s_out = state_out; p.o = o;
   p.K = d->K; p.V = d->V;
+  p.H = d->H; p.Hq = d->qk_heads > 0 ? d->qk_heads : d->H;
   p.variant = d->variant; p.qkv_dt = d->qkv_dtype; p.g_dt = d->g_dtype; p.out_dt = d->out_dtype;
   p.l2norm = d->use_qk_l2norm; p.scale = d->scale;
-  tl_path = "step";
   g_launches.fetch_add(1);
-  return check_cuda(dr::launch_step(p, (int64_t)d->B * d->H, reinterpret_cast<cudaStream_t>(stream)));
+  const int64_t units = (int64_t)d->B * d->H;
+  const int sms = sm_count();
+  if (sms > 0 && dr::step_stream_eligible(p, units, sms)) {
+    tl_path = "step_stream";
+    return check_cuda(dr::launch_step_stream(p, units, sms, reinterpret_cast<cudaStream_t>(stream)));
+  }
+  tl_path = "step";
+  return check_cuda(dr::launch_step(p, units, reinterpret_cast<cudaStream_t>(stream)));
 }
 
 #ifdef DR_PROFILE
@@ -235,6 +257,7 @@ int dr_chunk_bwd(const DrDesc* d, const void* q, const void* k, const void* v, c
   int s = validate_common(d, true);
   if (s != DR_OK) return s;
   if (!q || !k || !v || !beta || !d_o || !dq || !dk || !dv || !dbeta) return DR_ERR_NULL;
+  if (d->qk_heads > 0 && d->qk_heads != d->H) return DR_ERR_UNSUPPORTED;   // the backward wants q,k per value head
   if (d->variant == DR_DELTA ? (g != nullptr || dg != nullptr) : (g == nullptr || dg == nullptr))
     return DR_ERR_VARIANT;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(d_o) || !aligned16(dq) ||
@@ -288,6 +311,7 @@ int dr_chunk_bwd_static(const DrDesc* d, const void* q, const void* k, const voi
   int s = validate_common(d, true);
   if (s != DR_OK) return s;
   if (!q || !k || !v || !beta || !d_o || !dq || !dk || !dv || !dbeta) return DR_ERR_NULL;
+  if (d->qk_heads > 0 && d->qk_heads != d->H) return DR_ERR_UNSUPPORTED;   // the backward wants q,k per value head
   if (d->variant == DR_DELTA ? (g != nullptr || dg != nullptr) : (g == nullptr || dg == nullptr))
     return DR_ERR_VARIANT;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(d_o) || !aligned16(dq) ||

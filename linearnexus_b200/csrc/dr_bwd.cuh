@@ -1019,6 +1019,7 @@ inline cudaError_t launch_bwd(const DrDesc* d, const void* q, const void* k, con
   f.q = q; f.k = k; f.v = v; f.g = g; f.beta = beta; f.h0 = h0; f.o = nullptr; f.hT = nullptr; f.status = nullptr;
   f.ckpt = ckpt;
   f.map.B = d->B; f.map.H = d->H; f.map.T = d->T; f.map.bthd = d->layout == DR_LAYOUT_BTHD;
+  f.map.Hq = d->H;
   f.K = K; f.V = V; f.C = C;
   f.variant = d->variant; f.qkv_dt = d->qkv_dtype; f.g_dt = d->g_dtype; f.out_dt = d->qkv_dtype;
   f.l2norm = d->use_qk_l2norm; f.scale = d->scale;

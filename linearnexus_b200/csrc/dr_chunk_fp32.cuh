@@ -71,7 +71,8 @@ __global__ void __launch_bounds__(kCfThreads) chunk_fp32_kernel(const FwdParams 
   const int unit = blockIdx.x / nvs;
   const int v0 = (blockIdx.x % nvs) * kCfCols;
   const int b = unit / p.map.H, h = unit % p.map.H;
-  const int64_t qk_base = p.map.base(b, h, K), qk_tok = p.map.tok(K);
+  const int64_t qk_base = p.map.base_qk(b, h, K), qk_tok = p.map.tok_qk(K);
+  const int64_t gk_base = p.map.base(b, h, K), gk_tok = p.map.tok(K);   // per-channel decay: one row per value head
   const int64_t v_base = p.map.base(b, h, V), v_tok = p.map.tok(V);
   const int64_t s_base = p.map.base(b, h, 1), s_tok = p.map.tok(1);
 
@@ -101,7 +102,7 @@ __global__ void __launch_bounds__(kCfThreads) chunk_fp32_kernel(const FwdParams 
         if (live) {
           qv = ld_elem(p.q, qk_base + (t0 + c) * qk_tok + i, p.qkv_dt);
           kv = ld_elem(p.k, qk_base + (t0 + c) * qk_tok + i, p.qkv_dt);
-          if (kda) gv = ld_elem(p.g, qk_base + (t0 + c) * qk_tok + i, p.g_dt);
+          if (kda) gv = ld_elem(p.g, gk_base + (t0 + c) * gk_tok + i, p.g_dt);
         }
         sQ[c * ldk + i] = qv;
         sK[c * ldk + i] = kv;

@@ -292,7 +292,9 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
   const int T = p.map.T;
   const int unit = blockIdx.x;
   const int b = unit / p.map.H, h = unit % p.map.H;
-  const int64_t qk_base = p.map.base(b, h, kD), qk_tok = p.map.tok(kD);
+  const int64_t qk_base = p.map.base_qk(b, h, kD), qk_tok = p.map.tok_qk(kD);   // q, k (possibly fewer heads)
+  const int64_t vo_base = p.map.base(b, h, kD), vo_tok = p.map.tok(kD);         // v, o
+  const int unit_qk = b * p.map.Hq + p.map.hq(h);
   const int64_t s_base = p.map.base(b, h, 1), s_tok = p.map.tok(1);
 
   if (warp == 0) {
@@ -374,8 +376,8 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         if (gt == 64) {  // a warp other than the one that issues the products
           const uint32_t bar = tc::smem_u32(&ctl.kq[m % 3]);
           tc::mbar_arrive_expect_tx(bar, 2u * 64 * 256);
-          tc::tma_load_5d(tc::smem_u32(dQK), &P.tk, 0, 0, 0, m * 8, unit, bar);
-          tc::tma_load_5d(tc::smem_u32(dQK) + 64 * 256, &P.tq, 0, 0, 0, m * 8, unit, bar);
+          tc::tma_load_5d(tc::smem_u32(dQK), &P.tk, 0, 0, 0, m * 8, unit_qk, bar);
+          tc::tma_load_5d(tc::smem_u32(dQK) + 64 * 256, &P.tq, 0, 0, 0, m * 8, unit_qk, bar);
         }
       } else {
         const int rin = gt & 7, kb = (gt >> 3) & 15, rbh = gt >> 7;
@@ -414,7 +416,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         for (int rb2 = 0; rb2 < 4; ++rb2) {
           const int r = (2 * rb2 + rbh) * 8 + rin;
           const bool live = r < rowsm;
-          const __nv_bfloat16* src = gv + qk_base + (int64_t)(t0m + (live ? r : 0)) * qk_tok + kb * 8;
+          const __nv_bfloat16* src = gv + vo_base + (int64_t)(t0m + (live ? r : 0)) * vo_tok + kb * 8;
           tc::cp_async16(tc::smem_u32(sV + tc::core_off(r, kb * 8, RBS)), src, live);
         }
       }
@@ -658,7 +660,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         group_sync(2);
         const int r = gt >> 2, qtr = gt & 3;
         if (r < rowsm) {
-          __nv_bfloat16* dst = go + qk_base + (int64_t)(t0m + r) * qk_tok + 32 * qtr;
+          __nv_bfloat16* dst = go + vo_base + (int64_t)(t0m + r) * vo_tok + 32 * qtr;
 #pragma unroll
           for (int j = 0; j < 4; ++j)
             reinterpret_cast<uint4*>(dst)[j] = reinterpret_cast<const uint4*>(sO + r * kD + 32 * qtr)[j];
@@ -897,8 +899,9 @@ inline cudaError_t launch_chunk(const FwdParams& p, cudaStream_t stream) {
   const int64_t units = (int64_t)p.map.B * p.map.H;
   // TMA inputs need the rows of one (batch, head) contiguous and whole 8-row blocks; otherwise the
   // per-thread cp.async path loads the tiles (same layout, same results).
-  P.use_tma_in = !p.map.bthd && p.map.T % 8 == 0 && make_input_map(&P.tk, p.k, units, p.map.T) &&
-                 make_input_map(&P.tq, p.q, units, p.map.T) && make_input_map(&P.tv, p.v, units, p.map.T);
+  const int64_t units_qk = (int64_t)p.map.B * p.map.Hq;
+  P.use_tma_in = !p.map.bthd && p.map.T % 8 == 0 && make_input_map(&P.tk, p.k, units_qk, p.map.T) &&
+                 make_input_map(&P.tq, p.q, units_qk, p.map.T) && make_input_map(&P.tv, p.v, units, p.map.T);
   P.use_tma_out = p.o != nullptr && make_output_map(&P.to, p.o, p.map);
   const dim3 grid((unsigned)units), block(kThreads);
   chunk_sm100_kernel<<<grid, block, SM_TOTAL, stream>>>(P);

@@ -14,10 +14,17 @@ namespace dr {
 struct SeqMap {
   int B, H, T;
   int bthd;  // 0: [B,H,T,D]   1: [B,T,H,D]
+  int Hq;    // heads of q and k (grouped value attention: head h of v, o reads q/k head h / (H / Hq)); Hq == H: none
   __host__ __device__ inline int64_t base(int b, int h, int D) const {
     return bthd ? ((int64_t)b * T * H + h) * D : ((int64_t)b * H + h) * (int64_t)T * D;
   }
   __host__ __device__ inline int64_t tok(int D) const { return bthd ? (int64_t)H * D : D; }
+  // the same for q and k
+  __host__ __device__ inline int hq(int h) const { return h / (H / Hq); }
+  __host__ __device__ inline int64_t base_qk(int b, int h, int D) const {
+    return bthd ? ((int64_t)b * T * Hq + hq(h)) * D : ((int64_t)b * Hq + hq(h)) * (int64_t)T * D;
+  }
+  __host__ __device__ inline int64_t tok_qk(int D) const { return bthd ? (int64_t)Hq * D : D; }
 };
 
 __device__ __forceinline__ float ld_elem(const void* p, int64_t i, int dt) {

@@ -141,7 +141,8 @@ __global__ void __launch_bounds__(kThreads, 2) intra_kernel(const FwdParams p, u
   const int unit = blockIdx.x / nchunks, n = blockIdx.x % nchunks;
   const int b = unit / p.map.H, h = unit % p.map.H;
   const int t0 = n * kC, rows = min(kC, T - t0);
-  const int64_t qk_base = p.map.base(b, h, kD), qk_tok = p.map.tok(kD);
+  const int64_t qk_base = p.map.base_qk(b, h, kD), qk_tok = p.map.tok_qk(kD);   // q, k (possibly fewer heads)
+  const int64_t gk_base = p.map.base(b, h, kD), gk_tok = p.map.tok(kD);         // per-channel decay: per value head
   const int64_t s_base = p.map.base(b, h, 1), s_tok = p.map.tok(1);
   uint8_t* rec = ws + ((int64_t)unit * nchunks + n) * WS_REC;
   constexpr float kLog2e = 1.4426950408889634f;
@@ -164,7 +165,7 @@ __global__ void __launch_bounds__(kThreads, 2) intra_kernel(const FwdParams p, u
         qraw[i] = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.q) + at);
         kraw[i] = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.k) + at);
         if (p.variant == DR_KDA) {
-          ld4(p.g, at, p.g_dt, gv[i]);
+          ld4(p.g, gk_base + (t0 + c) * gk_tok + 4 * lane, p.g_dt, gv[i]);
         } else if (p.variant == DR_GATED) {
           const float gs = ld_elem(p.g, s_base + (t0 + c) * s_tok, p.g_dt);
           gv[i][0] = gv[i][1] = gv[i][2] = gv[i][3] = gs;

@@ -32,7 +32,8 @@ __global__ void __launch_bounds__(kRecThreads) recurrent_kernel(const FwdParams 
   const int vcol = v0 + col;
   const bool vok = vcol < V;
 
-  const int64_t qk_base = p.map.base(b, h, K), qk_tok = p.map.tok(K);
+  const int64_t qk_base = p.map.base_qk(b, h, K), qk_tok = p.map.tok_qk(K);
+  const int64_t gk_base = p.map.base(b, h, K), gk_tok = p.map.tok(K);   // per-channel decay: one row per value head
   const int64_t v_base = p.map.base(b, h, V), v_tok = p.map.tok(V);
   const int64_t s_base = p.map.base(b, h, 1), s_tok = p.map.tok(1);
 
@@ -56,7 +57,7 @@ __global__ void __launch_bounds__(kRecThreads) recurrent_kernel(const FwdParams 
       if (i < K) {
         f_q[s] = ld_elem(p.q, qk_base + t * qk_tok + i, p.qkv_dt);
         f_k[s] = ld_elem(p.k, qk_base + t * qk_tok + i, p.qkv_dt);
-        if (p.variant == DR_KDA) f_g[s] = ld_elem(p.g, qk_base + t * qk_tok + i, p.g_dt);
+        if (p.variant == DR_KDA) f_g[s] = ld_elem(p.g, gk_base + t * gk_tok + i, p.g_dt);
       }
     }
     if (tid < kRecCols)

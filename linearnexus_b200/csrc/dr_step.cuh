@@ -23,8 +23,13 @@ struct StepParams {
   float* s_out;
   void* o;
   int K, V;
+  int H, Hq;   // heads of v/o/state and of q/k (grouped value attention when Hq < H)
   int variant, qkv_dt, g_dt, out_dt, l2norm;
   float scale;
+  // unit (b * H + h) -> row of q and k
+  __host__ __device__ inline int64_t unit_qk(int64_t unit) const {
+    return (unit / H) * Hq + (unit % H) / (H / Hq);
+  }
 };
 
 constexpr int kStepThreads = 256;
@@ -66,8 +71,8 @@ __global__ void __launch_bounds__(kStepThreads) step_kernel(const StepParams p) 
   // q, k -> fp32, optional l2 normalisation; q.k after normalisation.
   float qq = 0.f, kq = 0.f, kk2 = 0.f;
   for (int i = tid; i < K; i += kStepThreads) {
-    const float qv = ld_elem(p.q, unit * K + i, p.qkv_dt);
-    const float kv = ld_elem(p.k, unit * K + i, p.qkv_dt);
+    const float qv = ld_elem(p.q, p.unit_qk(unit) * K + i, p.qkv_dt);
+    const float kv = ld_elem(p.k, p.unit_qk(unit) * K + i, p.qkv_dt);
     s_q[i] = qv;
     s_k[i] = kv;
     qq += qv * qv;

@@ -89,10 +89,12 @@ def _desc(variant, layout, B, H, T, K, V, chunk, qkv, g, out_dtype, l2norm, scal
 def _seq_forward(kind, variant, q, k, v, g, beta, initial_state, scale, chunk_size, l2norm,
                  out_dtype, path=None):
     _require_cuda(q, k, v, g, beta, initial_state)
-    if q.dim() != 4 or k.shape != q.shape or v.dim() != 4 or v.shape[:3] != q.shape[:3]:
-        raise ValueError(f"expected q,k [B,H,T,K] and v [B,H,T,V]; got {tuple(q.shape)}, {tuple(k.shape)}, {tuple(v.shape)}")
-    B, H, T, K = q.shape
-    V = v.shape[-1]
+    if (q.dim() != 4 or k.shape != q.shape or v.dim() != 4 or v.shape[0] != q.shape[0] or v.shape[2] != q.shape[2]
+            or v.shape[1] % q.shape[1]):
+        raise ValueError("expected q,k [B,Hq,T,K] and v [B,H,T,V] with H a multiple of Hq; got "
+                         f"{tuple(q.shape)}, {tuple(k.shape)}, {tuple(v.shape)}")
+    B, Hq, T, K = q.shape
+    H, V = v.shape[1], v.shape[-1]   # Hq < H: grouped value attention, q/k head h // (H // Hq) serves head h
     if scale is None:
         scale = K ** -0.5
     if beta.dim() == 4:
@@ -118,6 +120,7 @@ def _seq_forward(kind, variant, q, k, v, g, beta, initial_state, scale, chunk_si
     hT = torch.empty((B, H, K, V), dtype=torch.float32, device=dev)
     d = _desc(variant, layout, B, H, T, K, V, chunk_size, qn, gn, native_out, l2norm, scale,
               path if path is not None else default_chunk_path)
+    d.qk_heads = Hq
     lib = _lib.load()
     with torch.cuda.device(dev):
         if kind == "chunk":
@@ -136,10 +139,10 @@ def _seq_forward(kind, variant, q, k, v, g, beta, initial_state, scale, chunk_si
 
 def _step(variant, q, k, v, g, beta, state, scale, l2norm, out_dtype, inplace=False):
     _require_cuda(q, k, v, g, beta, state)
-    if q.dim() != 3 or k.shape != q.shape or v.dim() != 3:
-        raise ValueError("expected q,k [B,H,K] and v [B,H,V]")
-    B, H, K = q.shape
-    V = v.shape[-1]
+    if q.dim() != 3 or k.shape != q.shape or v.dim() != 3 or v.shape[0] != q.shape[0] or v.shape[1] % q.shape[1]:
+        raise ValueError("expected q,k [B,Hq,K] and v [B,H,V] with H a multiple of Hq")
+    B, Hq, K = q.shape
+    H, V = v.shape[1], v.shape[-1]
     if scale is None:
         scale = K ** -0.5
     if tuple(state.shape) != (B, H, K, V):
@@ -159,6 +162,7 @@ def _step(variant, q, k, v, g, beta, state, scale, l2norm, out_dtype, inplace=Fa
     native_out = out_dtype if out_dtype in _NATIVE else torch.float32
     o = torch.empty((B, H, V), dtype=native_out, device=dev)
     d = _desc(variant, DR_LAYOUT_BHTD, B, H, 1, K, V, 0, qn, gn, native_out, l2norm, scale)
+    d.qk_heads = Hq
     with torch.cuda.device(dev):
         st = _lib.load().dr_step(ctypes.byref(d), _ptr(qn), _ptr(kn), _ptr(vn), _ptr(gn), _ptr(bn),
                                  _ptr(s_in), _ptr(s_out), _ptr(o), _stream(dev))

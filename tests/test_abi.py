@@ -104,3 +104,28 @@ def test_forward_workspace_sizes_need_no_gpu():
     assert need(_lib.DR_GATED, "split") == 2 * 3 * 3 * 82432
     assert need(_lib.DR_KDA, None, K=64) == 0                      # not the tensor-core shape: fp32 kernel
     assert need(_lib.DR_KDA, None, qkv=torch.empty(0)) == 0        # fp32 inputs stay on the exact kernel
+
+
+def test_grouped_head_count_is_validated_on_the_host():
+    """DrDesc.qk_heads: 0 or a divisor of H; anything else is a shape error before any launch."""
+    import ctypes
+    import torch
+    from linearnexus_b200 import ops
+    lib = _lib.load()
+    q = torch.empty(0, dtype=torch.bfloat16)
+    g = torch.empty(0, dtype=torch.float32)
+    def status(qk_heads):
+        d = ops._desc(_lib.DR_GATED, _lib.DR_LAYOUT_BHTD, 2, 6, 64, 128, 128, 64, q, g, torch.bfloat16, True, 0.1, None)
+        d.qk_heads = qk_heads
+        return int(lib.dr_workspace_bytes(ctypes.byref(d), 0))
+    assert status(0) == 0 and status(6) == 0 and status(2) == 0 and status(1) == 0
+    assert status(4) == -2 and status(12) == -2 and status(-1) == -2
+
+
+def test_host_pipeline_argument_checks_need_no_gpu():
+    import pytest
+    import torch
+    from linearnexus_b200 import host_pipeline
+    host_pipeline._pinned(None, "g")
+    with pytest.raises(ValueError):
+        host_pipeline._pinned(torch.zeros(4), "q")          # pageable host memory

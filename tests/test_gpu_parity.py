@@ -211,3 +211,29 @@ def test_step_bf16_io_decode_config_shape():
         assert o.dtype == torch.bfloat16
         assert _rel(o, ro) <= BF16_TOL
     assert _rel(S_gpu, S_ref) <= 1e-4
+
+
+@pytest.mark.parametrize("variant", ["delta", "gated", "kda"])
+def test_step_streamed_kernel_many_units(variant):
+    """More than two (batch, head) units per SM at d_k = d_v = 128: the persistent, TMA-pipelined decode kernel.
+    Three steps, in place and out of place, against the float64 step."""
+    from linearnexus_b200 import _lib
+    B, H, K, V = 41, 8, 128, 128
+    inp = O.make_inputs(variant, B, H, 3, K, V, seed=77, io_dtype=torch.bfloat16, h0_std=0.02)
+    S_ref = inp["h0"].double()
+    S_gpu = inp["h0"].cuda().clone()
+    for t in range(3):
+        sl = lambda x: None if x is None else x[:, :, t]
+        q, k, v, g, beta = (sl(inp[x]) for x in ("q", "k", "v", "g", "beta"))
+        if variant == "delta":
+            ro, S_ref = O.delta_rule_step(q.double(), k.double(), v.double(), beta.double(), S_ref, compute_dtype=F64)
+            o, S_gpu = L.delta_rule_step(_cuda(q), _cuda(k), _cuda(v), _cuda(beta), S_gpu)
+        elif variant == "gated":
+            ro, S_ref = O.gated_delta_rule_step(q.double(), k.double(), v.double(), g.double(), beta.double(), S_ref, compute_dtype=F64)
+            o, _ = L.gated_delta_rule_step(_cuda(q), _cuda(k), _cuda(v), _cuda(g), _cuda(beta), S_gpu, inplace=True)
+        else:
+            ro, S_ref = O.kda_step(q.double(), k.double(), v.double(), g.double(), beta.double(), S_ref, compute_dtype=F64)
+            o, _ = L.kda_step(_cuda(q), _cuda(k), _cuda(v), _cuda(g), _cuda(beta), S_gpu, inplace=True)
+        assert _lib.last_path() == "step_stream"
+        assert _rel(o, ro) <= BF16_TOL
+        assert _rel(S_gpu, S_ref) <= 1e-4
