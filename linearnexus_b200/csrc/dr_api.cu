@@ -221,10 +221,14 @@ int dr_step(const DrDesc* d, const void* q, const void* k, const void* v, const 
   g_launches.fetch_add(1);
   const int64_t units = (int64_t)d->B * d->H;
   const int sms = sm_count();
+#ifndef DR_NO_STEP_STREAM   // (A/B builds of the benchmark compare against the one-CTA-per-unit kernel)
   if (sms > 0 && dr::step_stream_eligible(p, units, sms)) {
     tl_path = "step_stream";
     return check_cuda(dr::launch_step_stream(p, units, sms, reinterpret_cast<cudaStream_t>(stream)));
   }
+#else
+  (void)sms;
+#endif
   tl_path = "step";
   return check_cuda(dr::launch_step(p, units, reinterpret_cast<cudaStream_t>(stream)));
 }

@@ -20,7 +20,7 @@ struct SeqMap {
   }
   __host__ __device__ inline int64_t tok(int D) const { return bthd ? (int64_t)H * D : D; }
   // the same for q and k
-  __host__ __device__ inline int hq(int h) const { return h / (H / Hq); }
+  __host__ __device__ inline int hq(int h) const { return Hq == H ? h : h / (H / Hq); }
   __host__ __device__ inline int64_t base_qk(int b, int h, int D) const {
     return bthd ? ((int64_t)b * T * Hq + hq(h)) * D : ((int64_t)b * Hq + hq(h)) * (int64_t)T * D;
   }

@@ -28,7 +28,9 @@ struct StepParams {
   float scale;
   // unit (b * H + h) -> row of q and k
   __host__ __device__ inline int64_t unit_qk(int64_t unit) const {
-    return (unit / H) * Hq + (unit % H) / (H / Hq);
+    if (Hq == H) return unit;
+    const int u = (int)unit, b = u / H, h = u - b * H;   // B * H < 2^24: 32-bit arithmetic
+    return b * Hq + h / (H / Hq);
   }
 };
 

@@ -1,10 +1,10 @@
 // Decode step for K = V = 128 as a persistent, software-pipelined stream over the state cache.
 //
-// One CTA per SM walks its share of the (batch, head) units.  The 64 KB state of a unit arrives by the TMA
-// engine (cp.async.bulk global -> shared, completion on an mbarrier) up to three units ahead: a buffer is handed
-// back to the loader as soon as every thread has taken its rows into registers, and the updated rows leave from
-// the registers with streaming 128-bit stores.  The memory system therefore always has two to three 64 KB
-// loads in flight per SM besides the stores, with no phase in which a CTA's loads have drained and its stores
+// One CTA per SM walks its share of the (batch, head) units.  The 64 KB state of a unit travels by the TMA
+// engine in both directions: cp.async.bulk global -> shared one unit ahead (three 64 KB buffers: one being
+// loaded, one being worked on, one being written back), cp.async.bulk shared -> global after the update.
+// The threads only ever touch shared memory and registers, so the memory system always has a full load and
+// a full store of 64 KB in flight per SM, with no phase in which a CTA's loads have drained and its stores
 // have not started (what limits the one-CTA-per-unit kernel to two such CTAs per SM).
 // Same arithmetic as step_kernel:
 //     S~ = gamma * S ; d = beta * (v - S~^T k) ; S' = S~ + k d^T ; o = S~^T q + (q.k) d
@@ -54,9 +54,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) step_stream_kernel(const Step
 #pragma unroll
     for (int c = 0; c < 4; ++c) tc::bulk_g2s(dst + c * 16384, src + c * 16384, 16384, bar);
   };
-  if (tid == 0) {
-    for (int64_t i = 0; i < kStreamStages && i < nmine; ++i) issue_load(i);
-  }
+  if (tid == 0) issue_load(0);
 
   // raw per-unit vectors of the NEXT unit, fetched one iteration ahead (thread t < 128: channel t)
   float nq = 0.f, nk = 0.f, ng = 0.f, nv = 0.f, nbeta = 0.f, ngs = 0.f;
@@ -88,7 +86,13 @@ __global__ void __launch_bounds__(kStepThreads, 1) step_stream_kernel(const Step
       qq = warp_sum(qq); kk2 = warp_sum(kk2); kq = warp_sum(kq);
       if ((tid & 31) == 0) { s_part[0][tid >> 5] = qq; s_part[1][tid >> 5] = kk2; s_part[2][tid >> 5] = kq; }
     }
-    if (i + 1 < nmine) fetch_small(unit + stride);
+    if (i + 1 < nmine) {
+      if (tid == 0) {
+        tc::bulk_wait_read_1();   // the write-back that last used the target buffer (two units ago) has read it
+        issue_load(i + 1);
+      }
+      fetch_small(unit + stride);
+    }
     __syncthreads();
     float qmul = p.scale, kmul = 1.f;
     const float sq = s_part[0][0] + s_part[0][1] + s_part[0][2] + s_part[0][3];
@@ -123,11 +127,6 @@ __global__ void __launch_bounds__(kStepThreads, 1) step_stream_kernel(const Step
     reinterpret_cast<float4*>(s_red + ks * V)[vg] = a_k;
     reinterpret_cast<float4*>(s_red + (8 + ks) * V)[vg] = a_q;
     __syncthreads();
-    // every thread holds its part of the state in registers: the buffer takes the unit three ahead
-    if (tid == 0 && i + kStreamStages < nmine) {
-      tc::fence_async_smem();
-      issue_load(i + kStreamStages);
-    }
     float4 vo = make_float4(0.f, 0.f, 0.f, 0.f), oq = vo;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -146,19 +145,25 @@ __global__ void __launch_bounds__(kStepThreads, 1) step_stream_kernel(const Step
       st_elem(p.o, vi + 2, p.out_dt, oq.z + qk * d.z);
       st_elem(p.o, vi + 3, p.out_dt, oq.w + qk * d.w);
     }
-    {
-      float* S_out = p.s_out + unit * (int64_t)K * V;
 #pragma unroll
-      for (int r = 0; r < 16; ++r) {
-        const int kk = ks + 8 * r;
-        const float kn = s_k[kk] * kmul;
-        float4 s = st[r];
-        s.x += kn * d.x; s.y += kn * d.y; s.z += kn * d.z; s.w += kn * d.w;
-        __stcs(reinterpret_cast<float4*>(S_out + (int64_t)kk * V) + vg, s);
-      }
+    for (int r = 0; r < 16; ++r) {
+      const int kk = ks + 8 * r;
+      const float kn = s_k[kk] * kmul;
+      float4 s = st[r];
+      s.x += kn * d.x; s.y += kn * d.y; s.z += kn * d.z; s.w += kn * d.w;
+      reinterpret_cast<float4*>(S + kk * V)[vg] = s;
     }
-    __syncthreads();   // the per-unit vectors in shared memory are rewritten by the next iteration
+    tc::fence_async_smem();   // the updated state is read by the TMA engine next
+    __syncthreads();
+    if (tid == 0) {
+      uint8_t* dst = reinterpret_cast<uint8_t*>(p.s_out + unit * (int64_t)K * V);
+      const uint32_t src = tc::smem_u32(S);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tc::bulk_s2g(dst + c * 16384, src + c * 16384, 16384);
+      tc::bulk_commit();
+    }
   }
+  if (tid == 0) tc::bulk_wait_all();
 }
 
 // the streamed kernel serves K = V = 128 once there is more than one unit per SM to pipeline
