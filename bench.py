@@ -47,8 +47,9 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel (ncu, see profiles/*.md)
 NCU_TRAFFIC = {
     "gdn_fwd:chunk_tcgen05": 504.4e6,   # profiles/chunk_sm100_kernel_gdn_fwd.md (B=4 capture scaled by sequences)
-    "kda_fwd:chunk_split_tcgen05": 4.305e9,   # profiles/kda_split_kernels.md: both kernels, B=1 capture x 4 sequences-wise
+    "kda_fwd:chunk_split_tcgen05": 3.78e9,    # profiles/kda_split_kernels.md: both kernels, B=1 capture x 4 sequences-wise
     "gdn_decode:step": 1026.8e6,        # profiles/step_kernel_gdn_decode.md (full size)
+    "gdn_decode:step_stream": 1023.5e6, # same file, second capture
     "gdn_fwd_bwd:bwd": 792.8e6,         # profiles/bwd_chunk_kernel_phases.md: the adjoint kernel only (full size)
 }
 
@@ -183,7 +184,7 @@ def run_ours(args, w, rank, world, dev):
     # their steady state when the timed region starts (untimed, on top of the W warm-up steps)
     torch.cuda.synchronize(dev)
     t_spin = time.perf_counter()
-    while time.perf_counter() - t_spin < 0.05:
+    while not args.no_steady_warmup and time.perf_counter() - t_spin < 0.05:
         step()
         torch.cuda.synchronize(dev)
     barrier()
@@ -333,6 +334,8 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU time budget of the cpu_baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (profiling captures of a small case)")
+    ap.add_argument("--no-steady-warmup", action="store_true",
+                    help="skip the ~50 ms of extra untimed launches (profiler captures: keeps the launch count small)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     w = dict(WORKLOADS[args.workload])
