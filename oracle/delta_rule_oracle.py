@@ -19,7 +19,7 @@ float64 token recurrence as the mathematical truth.
 
 ``compute_dtype`` selects the arithmetic type: ``torch.float32`` follows the
 reference (which computes everything in fp32), ``torch.float64`` gives the
-mathematical truth used to judge both the fp32 restatement and the kernels.
+mathematical truth against which both the fp32 restatement and the kernels are checked.
 """
 
 from __future__ import annotations
