@@ -86,3 +86,29 @@ def test_tcgen05_is_default_for_headline_shape():
     assert _lib.last_path() == "chunk_tcgen05"
     L.gated_delta_rule_chunkwise(cu["q"].float(), cu["k"].float(), cu["v"].float(), cu["g"], cu["beta"])
     assert _lib.last_path() == "chunk_fp32"
+
+
+@pytest.mark.parametrize("variant", ["gated", "delta"])
+@pytest.mark.parametrize("T", [100, 320])
+def test_tcgen05_without_tma_inputs(variant, T):
+    """Inputs the tensor maps cannot describe -- [B,T,H,D] storage (rows of a sequence not contiguous) or a
+    length that is not a multiple of 8 -- take the per-thread copy path of the same kernel: same results."""
+    inp = O.make_inputs(variant, 2, 3, T, 128, 128, seed=T, io_dtype=torch.bfloat16, h0_std=0.02)
+    o, hT = _run(variant, inp, "tcgen05")
+    ro, rS = _truth(variant, inp)
+    assert _rel(o, ro) <= BF16_TOL and _rel(hT, rS) <= BF16_TOL
+    cu = {k: (None if v is None else v.cuda()) for k, v in inp.items()}
+    tr = lambda x: None if x is None else x.transpose(1, 2).contiguous().transpose(1, 2)
+    if variant == "delta":
+        o2, hT2 = L.delta_rule_chunkwise(tr(cu["q"]), tr(cu["k"]), tr(cu["v"]), tr(cu["beta"]), cu["h0"], chunk_size=64,
+                                         path="tcgen05")
+    else:
+        o2, hT2 = L.gated_delta_rule_chunkwise(tr(cu["q"]), tr(cu["k"]), tr(cu["v"]), tr(cu["g"]), tr(cu["beta"]),
+                                               initial_state=cu["h0"], chunk_size=64, path="tcgen05")
+    assert _lib.last_path() == "chunk_tcgen05"
+    assert o2.transpose(1, 2).is_contiguous()
+    # the two load paths feed identical tiles to identical products
+    if T % 8 == 0:
+        assert _rel(o2, ro) <= BF16_TOL and _rel(hT2, rS) <= BF16_TOL
+    else:
+        assert torch.equal(o2, o) and torch.equal(hT2, hT)
