@@ -159,9 +159,11 @@ def run_ours(args, w, rank, world, dev):
         gen = torch.Generator().manual_seed(7)
         d_o = torch.randn(w["B"], w["H"], w["T"], w["V"], generator=gen).to(torch.bfloat16).to(dev)
 
-        def step():
-            o, hT = L.gated_delta_rule_chunkwise(devt["q"], devt["k"], devt["v"], devt["g"], devt["beta"], chunk_size=w["chunk"])
-            gr = _ops.chunk_backward("gated", devt["q"], devt["k"], devt["v"], devt["g"], devt["beta"], d_o, chunk_size=w["chunk"])
+        def step():   # one forward (which keeps the per-chunk states) + the backward that uses them
+            o, hT, saved = _ops.chunk_forward_saving("gated", devt["q"], devt["k"], devt["v"], devt["g"], devt["beta"],
+                                                     chunk_size=w["chunk"])
+            gr = _ops.chunk_backward("gated", devt["q"], devt["k"], devt["v"], devt["g"], devt["beta"], d_o,
+                                     chunk_size=w["chunk"], saved=saved)
             return o, gr["dq"]
     elif w["variant"] == "gated":
         def step():
@@ -236,9 +238,10 @@ def run_ours(args, w, rank, world, dev):
             ins = {x: (None if pin[x] is None else pin[x].to(dev, non_blocking=True)) for x in names}
             if fwd_bwd:
                 do_dev = pin_do.to(dev, non_blocking=True)
-                o, hT = L.gated_delta_rule_chunkwise(ins["q"], ins["k"], ins["v"], ins["g"], ins["beta"], chunk_size=w["chunk"])
+                o, hT, saved = _ops.chunk_forward_saving("gated", ins["q"], ins["k"], ins["v"], ins["g"], ins["beta"],
+                                                         chunk_size=w["chunk"])
                 gr = _ops.chunk_backward("gated", ins["q"], ins["k"], ins["v"], ins["g"], ins["beta"], do_dev,
-                                         chunk_size=w["chunk"])
+                                         chunk_size=w["chunk"], saved=saved)
             elif w["variant"] == "gated":
                 o, hT = L.gated_delta_rule_chunkwise(ins["q"], ins["k"], ins["v"], ins["g"], ins["beta"], chunk_size=w["chunk"])
             elif w["variant"] == "kda":

@@ -147,6 +147,23 @@ int dr_step(const DrDesc* desc, const void* q, const void* k, const void* v, con
             const float* beta, const float* state_in, float* state_out, void* o, void* stream);
 
 /*
+ * Training-step pair: ONE forward per step instead of two.  dr_chunk_bwd recomputes the forward to get the
+ * state at the start of every chunk; a caller that is about to differentiate can instead run
+ * dr_chunk_fwd_saving, which is dr_chunk_fwd (same o, hT) that also leaves those states at the head of the
+ * BACKWARD workspace (dr_workspace_bytes(desc, 1) bytes, kept by the caller until the backward), and later
+ * dr_chunk_bwd_saved, which is dr_chunk_bwd without the recomputation.  Under jax this is the fwd / bwd pair of a
+ * jax.custom_vjp around the three *_chunkwise functions, the workspace being the residual.
+ * desc->path is ignored (the forward kernel is chosen by shape as in dr_chunk_bwd); out_dtype as in dr_chunk_fwd.
+ */
+int dr_chunk_fwd_saving(const DrDesc* desc, const void* q, const void* k, const void* v, const void* g,
+                        const float* beta, const float* h0, void* o, float* hT, void* bwd_workspace,
+                        size_t bwd_workspace_bytes, int32_t* status_dev, void* stream);
+int dr_chunk_bwd_saved(const DrDesc* desc, const void* q, const void* k, const void* v, const void* g,
+                       const float* beta, const void* d_o, const float* d_hT, void* dq, void* dk, void* dv,
+                       float* dbeta, float* dg, float* dh0, void* bwd_workspace, size_t bwd_workspace_bytes,
+                       int32_t* status_dev, void* stream);
+
+/*
  * Backward of the chunkwise/recurrent forward (the reference has no backward function:
  * its gradients are jax.grad through the three *_chunkwise functions cited above).
  * Inputs: the forward inputs, d_o [like o, desc->qkv_dtype] and d_hT (float32 [B,H,K,V] or

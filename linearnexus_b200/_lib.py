@@ -29,7 +29,7 @@ DR_PATH_AUTO, DR_PATH_FP32, DR_PATH_TCGEN05, DR_PATH_SPLIT = 0, 1, 2, 3
 
 EXPORTS = ["dr_version", "dr_strerror", "dr_last_cuda_error", "dr_launch_count", "dr_last_path",
            "dr_workspace_bytes", "dr_chunk_fwd", "dr_recurrent_fwd", "dr_step", "dr_chunk_bwd",
-           "dr_debug_umma_selftest", "dr_chunk_bwd_static"]
+           "dr_debug_umma_selftest", "dr_chunk_bwd_static", "dr_chunk_fwd_saving", "dr_chunk_bwd_saved"]
 
 
 class DrDesc(ctypes.Structure):
@@ -119,6 +119,11 @@ def load() -> ctypes.CDLL:
                                      ctypes.c_size_t, ip, vp]
         lib.dr_chunk_bwd_static.restype = ctypes.c_int
         lib.dr_chunk_bwd_static.argtypes = [dp, vp, vp, vp, vp, fp, fp, vp, fp, vp, vp, vp, fp, fp, fp, ip, vp]
+        lib.dr_chunk_fwd_saving.restype = ctypes.c_int
+        lib.dr_chunk_fwd_saving.argtypes = [dp, vp, vp, vp, vp, fp, fp, vp, fp, vp, ctypes.c_size_t, ip, vp]
+        lib.dr_chunk_bwd_saved.restype = ctypes.c_int
+        lib.dr_chunk_bwd_saved.argtypes = [dp, vp, vp, vp, vp, fp, vp, fp, vp, vp, vp, fp, fp, fp, vp,
+                                           ctypes.c_size_t, ip, vp]
         lib.dr_debug_umma_selftest.restype = ctypes.c_int
         lib.dr_debug_umma_selftest.argtypes = [vp, vp, fp, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ip, vp]
         _lib = lib

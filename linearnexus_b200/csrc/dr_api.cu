@@ -278,6 +278,52 @@ int dr_chunk_bwd(const DrDesc* d, const void* q, const void* k, const void* v, c
   return check_cuda(e);
 }
 
+int dr_chunk_fwd_saving(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
+                        const float* beta, const float* h0, void* o, float* hT, void* workspace,
+                        size_t workspace_bytes, int32_t* status_dev, void* stream) {
+  (void)status_dev;
+  int s = validate_common(d, true);
+  if (s != DR_OK) return s;
+  s = validate_fwd_ptrs(d, q, k, v, g, beta, h0, o, hT);
+  if (s != DR_OK) return s;
+  if (d->qk_heads > 0 && d->qk_heads != d->H) return DR_ERR_UNSUPPORTED;
+  const int64_t need = dr::bwd_workspace_bytes(d);
+  if (need < 0) return (int)need;
+  if (!workspace || (int64_t)workspace_bytes < need) return DR_ERR_WORKSPACE;
+  if (!aligned16(workspace)) return DR_ERR_ALIGN;
+  tl_path = "fwd_saving";
+  int launches = 0;
+  cudaError_t e = dr::launch_bwd_forward(d, q, k, v, g, beta, h0, o, hT, workspace,
+                                         reinterpret_cast<cudaStream_t>(stream), &launches);
+  g_launches.fetch_add(launches);
+  return check_cuda(e);
+}
+
+int dr_chunk_bwd_saved(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
+                       const float* beta, const void* d_o, const float* d_hT, void* dq, void* dk, void* dv,
+                       float* dbeta, float* dg, float* dh0, void* workspace, size_t workspace_bytes,
+                       int32_t* status_dev, void* stream) {
+  (void)status_dev;
+  int s = validate_common(d, true);
+  if (s != DR_OK) return s;
+  if (!q || !k || !v || !beta || !d_o || !dq || !dk || !dv || !dbeta) return DR_ERR_NULL;
+  if (d->qk_heads > 0 && d->qk_heads != d->H) return DR_ERR_UNSUPPORTED;
+  if (d->variant == DR_DELTA ? (g != nullptr || dg != nullptr) : (g == nullptr || dg == nullptr))
+    return DR_ERR_VARIANT;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(d_o) || !aligned16(dq) ||
+      !aligned16(dk) || !aligned16(dv) || !aligned16(workspace))
+    return DR_ERR_ALIGN;
+  const int64_t need = dr::bwd_workspace_bytes(d);
+  if (need < 0) return (int)need;
+  if ((int64_t)workspace_bytes < need || !workspace) return DR_ERR_WORKSPACE;
+  tl_path = "bwd_saved";
+  int launches = 0;
+  cudaError_t e = dr::launch_bwd_adjoint(d, q, k, v, g, beta, d_o, d_hT, dq, dk, dv, dbeta, dg, dh0, workspace,
+                                         reinterpret_cast<cudaStream_t>(stream), &launches);
+  g_launches.fetch_add(launches);
+  return check_cuda(e);
+}
+
 // ---- backward without any allocation by the caller ------------------------------------------------
 // Scratch for dr_chunk_bwd_static lives in the library's own device image: a fixed-size array that
 // every GPU which loads the library carries from module load until the process exits.

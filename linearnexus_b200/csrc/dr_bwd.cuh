@@ -24,6 +24,7 @@
 
 #include "dr_chunk_fp32.cuh"
 #include "dr_chunk_sm100.cuh"
+#include "dr_kda_sm100.cuh"
 #include "dr_common.cuh"
 
 namespace dr {
@@ -994,10 +995,48 @@ inline int64_t bwd_workspace_bytes(const DrDesc* d) {
   return f * (int64_t)sizeof(float);
 }
 
-inline cudaError_t launch_bwd(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
-                              const float* beta, const float* h0, const void* d_o, const float* d_hT, void* dq,
-                              void* dk, void* dv, float* dbeta, float* dg, float* dh0, void* workspace,
-                              cudaStream_t stream, int* launches) {
+// The checkpointing forward of the backward: state at the start of every chunk -> the head of the workspace.
+// With o / hT given it is also the forward a training step needs (dr_chunk_fwd_saving), so that step runs one
+// forward instead of two.  KDA at the tensor-core shape uses the two-kernel forward with its records parked in the
+// accumulator part of the workspace (524 KB per chunk there against 82 KB of records; the adjoint overwrites it).
+inline cudaError_t launch_bwd_forward(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
+                                      const float* beta, const float* h0, void* o, float* hT, void* workspace,
+                                      cudaStream_t stream, int* launches) {
+  const int C = d->chunk, K = d->K, V = d->V;
+  const int64_t N = (d->T + C - 1) / C, units = (int64_t)d->B * d->H;
+  float* ckpt = reinterpret_cast<float*>(workspace);
+  FwdParams f;
+  f.q = q; f.k = k; f.v = v; f.g = g; f.beta = beta; f.h0 = h0; f.o = o; f.hT = hT; f.status = nullptr;
+  f.ckpt = ckpt;
+  f.map.B = d->B; f.map.H = d->H; f.map.T = d->T; f.map.bthd = d->layout == DR_LAYOUT_BTHD;
+  f.map.Hq = d->H;
+  f.K = K; f.V = V; f.C = C;
+  f.variant = d->variant; f.qkv_dt = d->qkv_dtype; f.g_dt = d->g_dtype; f.out_dt = o ? d->out_dtype : d->qkv_dtype;
+  f.l2norm = d->use_qk_l2norm; f.scale = d->scale;
+  const bool tc_shape = sm100::kAvailable && K == 128 && V == 128 && C == 64 && d->qkv_dtype == DR_BF16;
+  // the tensor-core forwards write the same checkpoints when the shape qualifies
+  const bool fused = tc_shape && (d->variant == DR_DELTA || (d->variant == DR_GATED && d->g_dtype == DR_F32)) &&
+                     (!o || d->out_dtype == DR_BF16);
+  const bool split = tc_shape && !fused && d->variant == DR_KDA;
+  cudaError_t e;
+  if (fused) {
+    e = sm100::launch_chunk(f, stream);
+    ++*launches;
+  } else if (split) {
+    int n2 = 0;
+    e = kda::launch_chunk(f, ckpt + units * N * K * V, stream, &n2);
+    *launches += n2;
+  } else {
+    e = launch_chunk_fp32(f, stream);
+    ++*launches;
+  }
+  return e;
+}
+
+inline cudaError_t launch_bwd_adjoint(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
+                                      const float* beta, const void* d_o, const float* d_hT, void* dq, void* dk,
+                                      void* dv, float* dbeta, float* dg, float* dh0, void* workspace,
+                                      cudaStream_t stream, int* launches) {
   const int C = d->chunk, K = d->K, V = d->V;
   const int64_t N = (d->T + C - 1) / C, units = (int64_t)d->B * d->H, rows = units * N * C;
   float* ws = reinterpret_cast<float*>(workspace);
@@ -1014,27 +1053,14 @@ inline cudaError_t launch_bwd(const DrDesc* d, const void* q, const void* k, con
   const size_t nbeta = (size_t)units * d->T;
   e = cudaMemsetAsync(dbeta, 0, nbeta * sizeof(float), stream);
   if (e != cudaSuccess) return e;
-  // (1) forward with a state checkpoint per chunk (outputs are not wanted)
-  FwdParams f;
-  f.q = q; f.k = k; f.v = v; f.g = g; f.beta = beta; f.h0 = h0; f.o = nullptr; f.hT = nullptr; f.status = nullptr;
-  f.ckpt = ckpt;
-  f.map.B = d->B; f.map.H = d->H; f.map.T = d->T; f.map.bthd = d->layout == DR_LAYOUT_BTHD;
-  f.map.Hq = d->H;
-  f.K = K; f.V = V; f.C = C;
-  f.variant = d->variant; f.qkv_dt = d->qkv_dtype; f.g_dt = d->g_dtype; f.out_dt = d->qkv_dtype;
-  f.l2norm = d->use_qk_l2norm; f.scale = d->scale;
-  // the tensor-core forward writes the same checkpoints when the shape qualifies (bf16, K=V=128, C=64)
-  const bool tc_fwd = sm100::kAvailable && K == 128 && V == 128 && C == 64 && d->qkv_dtype == DR_BF16 &&
-                      (d->variant == DR_DELTA || (d->variant == DR_GATED && d->g_dtype == DR_F32));
-  e = tc_fwd ? sm100::launch_chunk(f, stream) : launch_chunk_fp32(f, stream);
-  if (e != cudaSuccess) return e;
-  ++*launches;
+  SeqMap map;
+  map.B = d->B; map.H = d->H; map.T = d->T; map.bthd = d->layout == DR_LAYOUT_BTHD; map.Hq = d->H;
   // (2) adjoint
   BwdParams p;
   p.q = q; p.k = k; p.v = v; p.g = g; p.beta = beta; p.d_o = d_o; p.d_hT = d_hT;
   p.dv = dv; p.dbeta = dbeta; p.dh0 = dh0;
   p.ckpt = ckpt; p.dq_acc = dq_acc; p.dk_acc = dk_acc; p.dg_acc = dg_acc;
-  p.map = f.map; p.K = K; p.V = V; p.C = C; p.N = (int)N;
+  p.map = map; p.K = K; p.V = V; p.C = C; p.N = (int)N;
   p.variant = d->variant; p.qkv_dt = d->qkv_dtype; p.g_dt = d->g_dtype; p.l2norm = d->use_qk_l2norm; p.scale = d->scale;
   if (d->variant == DR_KDA) {
     constexpr int VS = 16;
@@ -1064,12 +1090,22 @@ inline cudaError_t launch_bwd(const DrDesc* d, const void* q, const void* k, con
   BwdFinalParams fp;
   fp.q = q; fp.k = k; fp.dq = dq; fp.dk = dk; fp.dg = dg;
   fp.dq_acc = dq_acc; fp.dk_acc = dk_acc; fp.dg_acc = dg_acc;
-  fp.map = f.map; fp.K = K; fp.C = C; fp.N = (int)N; fp.variant = d->variant; fp.qkv_dt = d->qkv_dtype;
+  fp.map = map; fp.K = K; fp.C = C; fp.N = (int)N; fp.variant = d->variant; fp.qkv_dt = d->qkv_dtype;
   fp.l2norm = d->use_qk_l2norm; fp.scale = d->scale;
   fp.nvs = (int)nvs; fp.slice_stride = rows * K;
   bwd_finalize_kernel<<<(unsigned)(units * N), 256, 0, stream>>>(fp);
   ++*launches;
   return cudaGetLastError();
+}
+
+// forward recomputation + adjoint (dr_chunk_bwd)
+inline cudaError_t launch_bwd(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
+                              const float* beta, const float* h0, const void* d_o, const float* d_hT, void* dq,
+                              void* dk, void* dv, float* dbeta, float* dg, float* dh0, void* workspace,
+                              cudaStream_t stream, int* launches) {
+  cudaError_t e = launch_bwd_forward(d, q, k, v, g, beta, h0, nullptr, nullptr, workspace, stream, launches);
+  if (e != cudaSuccess) return e;
+  return launch_bwd_adjoint(d, q, k, v, g, beta, d_o, d_hT, dq, dk, dv, dbeta, dg, dh0, workspace, stream, launches);
 }
 
 }  // namespace dr

@@ -266,13 +266,9 @@ def kda_chunkwise(q, k, v, g, beta, scale=None, initial_state=None, chunk_size=6
 _VARIANTS = {"delta": DR_DELTA, "gated": DR_GATED, "kda": DR_KDA}
 
 
-def chunk_backward(variant, q, k, v, g, beta, d_o, initial_state=None, d_final_state=None, scale=None,
-                   chunk_size=64, use_qk_l2norm=True):
-    """Gradients of sum(o * d_o) + sum(final_state * d_final_state) for ``variant`` in
-    {"delta", "gated", "kda"}.  Returns a dict: dq, dk [like q], dv [like v] in the q/k/v dtype;
-    dbeta float32 [B,H,T]; dg float32 [like g] (None for "delta"); dh0 float32 [B,H,K,V]."""
+def _train_prep(variant, q, k, v, g, beta, initial_state, scale, chunk_size, use_qk_l2norm, out_dtype=None):
+    """Common argument handling of the backward-related entry points ([B,H,T,D] contiguous copies)."""
     var = _VARIANTS[variant]
-    _require_cuda(q, k, v, g, beta, d_o, initial_state, d_final_state)
     B, H, T, K = q.shape
     V = v.shape[-1]
     if scale is None:
@@ -281,38 +277,90 @@ def chunk_backward(variant, q, k, v, g, beta, d_o, initial_state=None, d_final_s
         beta = beta.squeeze(-1)
     dev = q.device
     common = torch.float32 if any(t.dtype not in _NATIVE for t in (q, k, v)) or len({q.dtype, k.dtype, v.dtype}) > 1 else q.dtype
-    qn, kn, vn, don = (t.to(common).contiguous() for t in (q, k, v, d_o))
+    qn, kn, vn = (t.to(common).contiguous() for t in (q, k, v))
     gn = None if g is None else _native(g).contiguous()
     bn = beta.to(torch.float32).contiguous()
     h0 = _state(initial_state, B, H, K, V, dev)
-    dhT = _state(d_final_state, B, H, K, V, dev)
-    d = _desc(var, DR_LAYOUT_BHTD, B, H, T, K, V, chunk_size, qn, gn, common, use_qk_l2norm, scale)
+    d = _desc(var, DR_LAYOUT_BHTD, B, H, T, K, V, chunk_size, qn, gn, common if out_dtype is None else out_dtype,
+              use_qk_l2norm, scale)
     lib = _lib.load()
     need = lib.dr_workspace_bytes(ctypes.byref(d), 1)
     if need == -7:
         raise ValueError(f"chunk_size (BT={chunk_size}) must be divisible by BC=16.")
     _lib.check(int(need) if need < 0 else 0, "dr_workspace_bytes")
-    ws = torch.empty(int(need), dtype=torch.uint8, device=dev)
+    return d, lib, int(need), (qn, kn, vn, gn, bn, h0), (B, H, T, K, V, dev, common)
+
+
+def chunk_forward_saving(variant, q, k, v, g, beta, initial_state=None, scale=None, chunk_size=64,
+                         use_qk_l2norm=True, out_dtype=None):
+    """The chunkwise forward of a training step: returns ``(o, final_state, saved)`` where ``saved`` is the
+    backward workspace holding the state at the start of every chunk; pass it to ``chunk_backward(..., saved=)``
+    so that the backward does not recompute the forward."""
+    _require_cuda(q, k, v, g, beta, initial_state)
+    if out_dtype is None:
+        out_dtype = torch.float32 if variant == "kda" else q.dtype
+    native_out = out_dtype if out_dtype in _NATIVE else torch.float32
+    d, lib, need, (qn, kn, vn, gn, bn, h0), (B, H, T, K, V, dev, common) = _train_prep(
+        variant, q, k, v, g, beta, initial_state, scale, chunk_size, use_qk_l2norm, native_out)
+    ws = torch.empty(need, dtype=torch.uint8, device=dev)
+    o = torch.empty((B, H, T, V), dtype=native_out, device=dev)
+    hT = torch.empty((B, H, K, V), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        st = lib.dr_chunk_fwd_saving(ctypes.byref(d), _ptr(qn), _ptr(kn), _ptr(vn), _ptr(gn), _ptr(bn), _ptr(h0),
+                                     _ptr(o), _ptr(hT), _ptr(ws), ws.numel(), None, _stream(dev))
+    _lib.check(st, "dr_chunk_fwd_saving")
+    return (o if o.dtype == out_dtype else o.to(out_dtype)), hT, ws
+
+
+def chunk_backward(variant, q, k, v, g, beta, d_o, initial_state=None, d_final_state=None, scale=None,
+                   chunk_size=64, use_qk_l2norm=True, saved=None):
+    """Gradients of sum(o * d_o) + sum(final_state * d_final_state) for ``variant`` in
+    {"delta", "gated", "kda"}.  Returns a dict: dq, dk [like q], dv [like v] in the q/k/v dtype;
+    dbeta float32 [B,H,T]; dg float32 [like g] (None for "delta"); dh0 float32 [B,H,K,V].
+    ``saved``: the third result of ``chunk_forward_saving`` on the same inputs (skips the forward recomputation;
+    the buffer is consumed)."""
+    _require_cuda(q, k, v, g, beta, d_o, initial_state, d_final_state)
+    d, lib, need, (qn, kn, vn, gn, bn, h0), (B, H, T, K, V, dev, common) = _train_prep(
+        variant, q, k, v, g, beta, initial_state, scale, chunk_size, use_qk_l2norm)
+    don = d_o.to(common).contiguous()
+    dhT = _state(d_final_state, B, H, K, V, dev)
+    if saved is not None and (saved.numel() < need or saved.device != dev or saved.dtype != torch.uint8):
+        raise ValueError("saved must be the workspace returned by chunk_forward_saving for the same shapes")
+    ws = torch.empty(need, dtype=torch.uint8, device=dev) if saved is None else saved
     dq, dk, dv = torch.empty_like(qn), torch.empty_like(kn), torch.empty_like(vn)
     dbeta = torch.empty((B, H, T), dtype=torch.float32, device=dev)
     dg = None if g is None else torch.empty(gn.shape, dtype=torch.float32, device=dev)
     dh0 = torch.empty((B, H, K, V), dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
-        st = lib.dr_chunk_bwd(ctypes.byref(d), _ptr(qn), _ptr(kn), _ptr(vn), _ptr(gn), _ptr(bn), _ptr(h0), _ptr(don),
-                              _ptr(dhT), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dbeta), _ptr(dg), _ptr(dh0), _ptr(ws),
-                              ws.numel(), None, _stream(dev))
+        if saved is None:
+            st = lib.dr_chunk_bwd(ctypes.byref(d), _ptr(qn), _ptr(kn), _ptr(vn), _ptr(gn), _ptr(bn), _ptr(h0), _ptr(don),
+                                  _ptr(dhT), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dbeta), _ptr(dg), _ptr(dh0), _ptr(ws),
+                                  ws.numel(), None, _stream(dev))
+        else:
+            st = lib.dr_chunk_bwd_saved(ctypes.byref(d), _ptr(qn), _ptr(kn), _ptr(vn), _ptr(gn), _ptr(bn), _ptr(don),
+                                        _ptr(dhT), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dbeta), _ptr(dg), _ptr(dh0),
+                                        _ptr(ws), ws.numel(), None, _stream(dev))
     _lib.check(st, "dr_chunk_bwd")
     return dict(dq=dq.to(q.dtype), dk=dk.to(k.dtype), dv=dv.to(v.dtype), dg=dg, dbeta=dbeta, dh0=dh0)
 
 
 class _ChunkFn(torch.autograd.Function):
+    """Forward that keeps the per-chunk states for its backward (one forward per training step).  Inputs the
+    saving forward does not take (grouped q/k heads, an explicit kernel path) fall back to forward + recomputation."""
+
     @staticmethod
     def forward(ctx, variant, q, k, v, g, beta, initial_state, scale, chunk_size, l2norm, out_dtype, path):
+        saved = None
         with torch.no_grad():
-            o, hT = _seq_forward("chunk", _VARIANTS[variant], q, k, v, g, beta, initial_state, scale, chunk_size,
-                                 l2norm, out_dtype, path)
+            if path is None and q.shape[1] == v.shape[1]:
+                o, hT, saved = chunk_forward_saving(variant, q, k, v, g, beta, initial_state, scale, chunk_size,
+                                                    l2norm, out_dtype)
+            else:
+                o, hT = _seq_forward("chunk", _VARIANTS[variant], q, k, v, g, beta, initial_state, scale, chunk_size,
+                                     l2norm, out_dtype, path)
         ctx.save_for_backward(q, k, v, g if g is not None else q.new_empty(0), beta,
                               initial_state if initial_state is not None else q.new_empty(0))
+        ctx.saved_ws = saved
         ctx.meta = (variant, scale, chunk_size, l2norm, g is not None, initial_state is not None)
         return o, hT
 
@@ -320,8 +368,9 @@ class _ChunkFn(torch.autograd.Function):
     def backward(ctx, d_o, d_hT):
         q, k, v, g, beta, h0 = ctx.saved_tensors
         variant, scale, chunk_size, l2norm, has_g, has_h0 = ctx.meta
+        saved, ctx.saved_ws = ctx.saved_ws, None   # consumed: a second backward recomputes
         gr = chunk_backward(variant, q, k, v, g if has_g else None, beta, d_o, h0 if has_h0 else None, d_hT,
-                            scale=scale, chunk_size=chunk_size, use_qk_l2norm=l2norm)
+                            scale=scale, chunk_size=chunk_size, use_qk_l2norm=l2norm, saved=saved)
         dg = gr["dg"].to(g.dtype) if has_g else None
         return (None, gr["dq"], gr["dk"], gr["dv"], dg, gr["dbeta"].reshape(beta.shape).to(beta.dtype),
                 gr["dh0"].to(h0.dtype) if has_h0 else None, None, None, None, None, None)
