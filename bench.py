@@ -38,6 +38,9 @@ WORKLOADS = {
     # name: variant, B, T, H, K, V, chunk, io dtype, kind
     "gdn_fwd": dict(variant="gated", B=8, T=4096, H=16, K=128, V=128, chunk=64, kind="chunk_fwd", cfg_id=2),
     "kda_fwd": dict(variant="kda", B=4, T=8192, H=32, K=128, V=128, chunk=64, kind="chunk_fwd", cfg_id=3),
+    # same shape with the decay and the output in bf16 (the block's activation dtype; opt-in output dtype)
+    "kda_fwd_bf16": dict(variant="kda", B=4, T=8192, H=32, K=128, V=128, chunk=64, kind="chunk_fwd", cfg_id=3,
+                         g_bf16=True, out_bf16=True),
     "gdn_decode": dict(variant="gated", B=256, T=1, H=32, K=128, V=128, chunk=0, kind="decode", cfg_id=4),
     # training configuration: B=16 over 8 GPUs = 2 batch rows per GPU; forward + backward
     "gdn_fwd_bwd": dict(variant="gated", B=2, T=4096, H=16, K=128, V=128, chunk=64, kind="fwd_bwd", cfg_id=5),
@@ -63,8 +66,8 @@ def alg_bytes_per_token_head(w, io_bytes=2):
     K, V = w["K"], w["V"]
     if w["kind"] == "decode":
         return 2 * 4 * K * V + io_bytes * (2 * K + V) + 8 + io_bytes * V
-    g_bytes = 4 * K if w["variant"] == "kda" else 4
-    o_bytes = 4 if w["variant"] == "kda" else io_bytes
+    g_bytes = (2 if w.get("g_bf16") else 4) * K if w["variant"] == "kda" else 4
+    o_bytes = 4 if w["variant"] == "kda" and not w.get("out_bf16") else io_bytes
     return io_bytes * (2 * K + V) + o_bytes * V + g_bytes + 4
 
 
@@ -132,7 +135,8 @@ def make_host_inputs(w, seed, n_sets=1):
     sets = []
     for s in range(n_sets):
         h0 = 0.02 if w["kind"] == "decode" or w["variant"] == "kda" else None
-        sets.append(make_inputs(w["variant"], w["B"], w["H"], w["T"], w["K"], w["V"], seed + s, io_dtype=io, h0_std=h0))
+        sets.append(make_inputs(w["variant"], w["B"], w["H"], w["T"], w["K"], w["V"], seed + s, io_dtype=io, h0_std=h0,
+                                g_dtype=torch.bfloat16 if w.get("g_bf16") else torch.float32))
     return sets
 
 
@@ -147,6 +151,7 @@ def run_ours(args, w, rank, world, dev):
     torch.cuda.synchronize(dev)
     decode = w["kind"] == "decode"
     tokens_per_step = w["B"] * w["T"]
+    kda_kw = dict(out_dtype=torch.bfloat16) if w.get("out_bf16") else {}
 
     if decode:
         q, k, v, g, beta = (devt[x][:, :, 0].contiguous() if devt[x] is not None else None for x in ("q", "k", "v", "g", "beta"))
@@ -170,7 +175,8 @@ def run_ours(args, w, rank, world, dev):
             return L.gated_delta_rule_chunkwise(devt["q"], devt["k"], devt["v"], devt["g"], devt["beta"], chunk_size=w["chunk"])
     elif w["variant"] == "kda":
         def step():
-            return L.kda_chunkwise(devt["q"], devt["k"], devt["v"], devt["g"], devt["beta"], initial_state=devt["h0"], chunk_size=w["chunk"])
+            return L.kda_chunkwise(devt["q"], devt["k"], devt["v"], devt["g"], devt["beta"], initial_state=devt["h0"],
+                                   chunk_size=w["chunk"], **kda_kw)
     else:
         def step():
             return L.delta_rule_chunkwise(devt["q"], devt["k"], devt["v"], devt["beta"], chunk_size=w["chunk"])
@@ -226,10 +232,10 @@ def run_ours(args, w, rank, world, dev):
             if not fwd_bwd:
                 # the public host-memory entry point: batch slices, H2D / kernel / D2H overlapped on three streams
                 if out_host is None:
-                    o_dt = torch.float32 if w["variant"] == "kda" else pin["q"].dtype
+                    o_dt = torch.float32 if w["variant"] == "kda" and not w.get("out_bf16") else pin["q"].dtype
                     out_host = [torch.empty((w["B"], w["H"], w["T"], w["V"]), dtype=o_dt).pin_memory(),
                                 torch.empty((w["B"], w["H"], w["K"], w["V"]), dtype=torch.float32).pin_memory()]
-                kw = dict(chunk_size=w["chunk"])
+                kw = dict(chunk_size=w["chunk"], **kda_kw)
                 if pin.get("h0") is not None:
                     kw["initial_state"] = pin["h0"]
                 L.chunkwise_from_host(w["variant"], pin["q"], pin["k"], pin["v"], pin["g"], pin["beta"],
