@@ -122,6 +122,7 @@ struct BwdParams {
   const void* d_o; const float* d_hT;
   void* dv; float* dbeta; float* dh0;
   const float* ckpt; float* dq_acc; float* dk_acc; float* dg_acc;
+  float* pre;   // per chunk [3][64][64] X, A, T then [2][64][K] q^, k^ from bwd_pre_kernel (tensor-core path), or null
   SeqMap map;
   int K, V, C, N;
   int variant, qkv_dt, g_dt, l2norm;
@@ -209,6 +210,24 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
     BPROF(150);
     // ---- stage q^, k^ (fp32, normalised / scaled), g, beta, v, dO, S0 --------------------------------
     if constexpr (TC) {
+      if (p.pre) {
+        // X, A, T of this chunk were computed once for all value slices: 16-byte async copies into their arrays
+        // (and so were the normalised fp32 rows q^, k^)
+        const float* src = p.pre + ((int64_t)unit * N + n) * (3 * 64 * 64 + 2 * 64 * K);
+        for (int i = tid; i < 3 * 64 * 16; i += kBwThreads) {
+          const int m = i >> 10, r = (i >> 4) & 63, c4 = (i & 15) * 4;
+          float* dst = (m == 0 ? sX : m == 1 ? sA : sT) + r * lda + c4;
+          tc::cp_async16(tc::smem_u32(dst), src + m * 4096 + r * 64 + c4, true);
+        }
+        const float* qsrc = src + 3 * 4096;
+        const int k4 = K >> 2;
+        for (int i = tid; i < 2 * 64 * k4; i += kBwThreads) {
+          const int m = i / (64 * k4), r = (i / k4) & 63, c4 = (i % k4) * 4;
+          tc::cp_async16(tc::smem_u32((m ? sK : sQ) + r * ldk + c4), qsrc + (m * 64 + r) * K + c4, true);
+        }
+        tc::cp_async_commit();
+      }
+      const bool have_qk = p.pre != nullptr;
       // bf16 inputs: 8-byte (q, k) and 16-byte (v, dO, S0) accesses, every global load of the warp's eight rows
       // issued before the first is used (C = 64: rows warp, warp + 8, ...)
       const __nv_bfloat16* gq = reinterpret_cast<const __nv_bfloat16*>(p.q);
@@ -221,7 +240,7 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
         for (int ps = 0; ps < 2; ++ps) {
           const int ch = 128 * ps + 4 * lane;
           qr[i][ps] = make_uint2(0u, 0u); kr[i][ps] = make_uint2(0u, 0u);
-          if (c < rows && ch < K) {
+          if (!have_qk && c < rows && ch < K) {
             qr[i][ps] = *reinterpret_cast<const uint2*>(gq + qk_base + (t0 + c) * qk_tok + ch);
             kr[i][ps] = *reinterpret_cast<const uint2*>(gk + qk_base + (t0 + c) * qk_tok + ch);
           }
@@ -252,6 +271,7 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int c = warp + 8 * i;
+        if (!have_qk) {
         float qf[2][4], kf[2][4];
         float nq = 0.f, nk = 0.f;
 #pragma unroll
@@ -281,6 +301,7 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
             *reinterpret_cast<float4*>(sK + c * ldk + ch) =
                 make_float4(kf[ps][0] * kmul, kf[ps][1] * kmul, kf[ps][2] * kmul, kf[ps][3] * kmul);
           }
+        }
         }
         if (lane == i) {
           sBeta[c] = bt;
@@ -357,6 +378,9 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
       }
     }
     }
+    if constexpr (TC) {
+      if (p.pre) tc::cp_async_wait_all();
+    }
     __syncthreads();
     BPROF(151);
     if (KDA) {
@@ -386,7 +410,7 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
     if constexpr (TC) {
       // rows 0..63 of the stacked product are K^ (-> X), rows 64..127 are Q^ (-> A); the decay factor is
       // folded in here (the exact path applies it where an entry is used)
-      {
+      if (!p.pre) {
         // Lower-triangular 16-row panels cut into tasks of at most three 8-column tiles:
         //   task 0..2: rows 48.., tiles 0-2 / 3-5 / 6-7    3,4: rows 32.., tiles 0-2 / 3-5
         //   5,6: rows 16.., tiles 0-1 / 2-3                7: rows 0.., tiles 0-1
@@ -511,7 +535,7 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
     // ---- Vn = M^-1 R : forward substitution, 8 lanes per column -----------------------------------------
     if constexpr (TC) {
       // explicit inverse T = (I + diag(beta) X)^-1 (X carries the decay), then Vn = T R on the tensor cores
-      sm100::block_inverse_64(sX, sBeta, sT, tid);
+      if (!p.pre) sm100::block_inverse_64(sX, sBeta, sT, tid);
       constexpr int NT = VS / 16;
       const int m0 = (warp >> 1) * 16, n0 = (warp & 1) * 8 * NT;
       float d[NT][4];
@@ -902,6 +926,169 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
   }
 }
 
+// Chunk-parallel pre-pass of the tensor-core adjoint (bf16 inputs, C = 64): the pieces of a chunk that do not
+// depend on the value slice -- X = tril(K^K^^T.E,-1), A = tril(Q^K^^T.E) and T = (I + diag(beta) X)^-1 -- computed
+// once per chunk instead of once per slice, one CTA per (sequence, chunk), together with the normalised fp32
+// rows q^, k^ themselves.  Output per chunk: [3][64][64] then [2][64][K] fp32.
+inline size_t bwd_pre_smem_bytes(int K) { return sizeof(float) * (2 * 64 * (size_t)(K + 4) + 3 * 64 * sm100::LDT + 128); }
+
+__global__ void __launch_bounds__(kBwThreads) bwd_pre_kernel(const BwdParams p) {
+  extern __shared__ __align__(16) float smem[];
+  const int K = p.K, T = p.map.T, N = p.N;
+  constexpr int C = 64;
+  const int ldk = K + 4, lda = sm100::LDT;
+  float* sQ = smem;
+  float* sK = sQ + C * ldk;
+  float* sX = sK + C * ldk;
+  float* sA = sX + C * lda;
+  float* sT = sA + C * lda;
+  float* sGs = sT + C * lda;
+  float* sBeta = sGs + 64;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int unit = blockIdx.x / N, n = blockIdx.x % N;
+  const int b = unit / p.map.H, h = unit % p.map.H;
+  const int64_t qk_base = p.map.base(b, h, K), qk_tok = p.map.tok(K);
+  const int64_t s_base = p.map.base(b, h, 1), s_tok = p.map.tok(1);
+  const bool gated = p.variant == DR_GATED;
+  const int t0 = n * C, rows = min(C, T - t0);
+  // ---- stage q^, k^ (fp32, normalised / scaled), g, beta: all global loads of the warp's eight rows first --------
+  {
+    const __nv_bfloat16* gq = reinterpret_cast<const __nv_bfloat16*>(p.q);
+    const __nv_bfloat16* gk = reinterpret_cast<const __nv_bfloat16*>(p.k);
+    uint2 qr[8][2], kr[8][2];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int c = warp + 8 * i;
+#pragma unroll
+      for (int ps = 0; ps < 2; ++ps) {
+        const int ch = 128 * ps + 4 * lane;
+        qr[i][ps] = make_uint2(0u, 0u); kr[i][ps] = make_uint2(0u, 0u);
+        if (c < rows && ch < K) {
+          qr[i][ps] = *reinterpret_cast<const uint2*>(gq + qk_base + (t0 + c) * qk_tok + ch);
+          kr[i][ps] = *reinterpret_cast<const uint2*>(gk + qk_base + (t0 + c) * qk_tok + ch);
+        }
+      }
+    }
+    float bt = 0.f, gt_ = 0.f;
+    if (lane < 8 && warp + 8 * lane < rows) {
+      bt = p.beta[s_base + (t0 + warp + 8 * lane) * s_tok];
+      if (gated) gt_ = ld_elem(p.g, s_base + (t0 + warp + 8 * lane) * s_tok, p.g_dt);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int c = warp + 8 * i;
+      float qf[2][4], kf[2][4];
+      float nq = 0.f, nk = 0.f;
+#pragma unroll
+      for (int ps = 0; ps < 2; ++ps) {
+        const float2 a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qr[i][ps].x));
+        const float2 a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qr[i][ps].y));
+        const float2 b0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr[i][ps].x));
+        const float2 b1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr[i][ps].y));
+        qf[ps][0] = a0.x; qf[ps][1] = a0.y; qf[ps][2] = a1.x; qf[ps][3] = a1.y;
+        kf[ps][0] = b0.x; kf[ps][1] = b0.y; kf[ps][2] = b1.x; kf[ps][3] = b1.y;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { nq += qf[ps][e] * qf[ps][e]; nk += kf[ps][e] * kf[ps][e]; }
+      }
+      float qmul = p.scale, kmul = 1.f;
+      if (p.l2norm) {
+        nq = warp_sum(nq);
+        nk = warp_sum(nk);
+        qmul = p.scale / (sqrtf(nq) + 1e-6f);
+        kmul = 1.f / (sqrtf(nk) + 1e-6f);
+      }
+#pragma unroll
+      for (int ps = 0; ps < 2; ++ps) {
+        const int ch = 128 * ps + 4 * lane;
+        if (ch < K) {
+          *reinterpret_cast<float4*>(sQ + c * ldk + ch) =
+              make_float4(qf[ps][0] * qmul, qf[ps][1] * qmul, qf[ps][2] * qmul, qf[ps][3] * qmul);
+          *reinterpret_cast<float4*>(sK + c * ldk + ch) =
+              make_float4(kf[ps][0] * kmul, kf[ps][1] * kmul, kf[ps][2] * kmul, kf[ps][3] * kmul);
+        }
+      }
+      if (lane == i) { sBeta[c] = bt; sGs[c] = gt_; }
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    float acc = 0.f;
+    for (int c = 0; c < C; ++c) { acc += sGs[c]; sGs[c] = acc; }
+  }
+  __syncthreads();
+  // ---- X, A: the adjoint kernel's balanced triangular tasks (warp w: task w on K^, task 7-w on Q^) ---------------
+  {
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll 1
+    for (int pass = 0; pass < 2; ++pass) {
+      const int task = pass ? 7 - warp : warp;
+      const int i0 = task < 3 ? 48 : task < 5 ? 32 : task < 7 ? 16 : 0;
+      const int nt0 = task < 3 ? 3 * task : task < 5 ? 3 * (task - 3) : task < 7 ? 2 * (task - 5) : 0;
+      const int ntn = (task == 2 || task >= 5) ? 2 : 3;
+      const float* arows = pass ? sQ : sK;
+      float d[3][4];
+#pragma unroll
+      for (int nt = 0; nt < 3; ++nt) d[nt][0] = d[nt][1] = d[nt][2] = d[nt][3] = 0.f;
+      for (int k0 = 0; k0 < K; k0 += 8) {
+        uint32_t af[4];
+        af[0] = __float_as_uint(arows[(i0 + g) * ldk + k0 + t]);
+        af[1] = __float_as_uint(arows[(i0 + g + 8) * ldk + k0 + t]);
+        af[2] = __float_as_uint(arows[(i0 + g) * ldk + k0 + t + 4]);
+        af[3] = __float_as_uint(arows[(i0 + g + 8) * ldk + k0 + t + 4]);
+#pragma unroll
+        for (int nt = 0; nt < 3; ++nt) {
+          if (nt < ntn) {
+            uint32_t bf[2];
+            bf[0] = __float_as_uint(sK[(8 * (nt0 + nt) + g) * ldk + k0 + t]);
+            bf[1] = __float_as_uint(sK[(8 * (nt0 + nt) + g) * ldk + k0 + t + 4]);
+            sm100::mma_tf32(d[nt], af, bf);
+          }
+        }
+      }
+#pragma unroll
+      for (int nt = 0; nt < 3; ++nt) {
+        if (nt < ntn) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = i0 + g + (e >> 1) * 8, j = 8 * (nt0 + nt) + 2 * t + (e & 1);
+            const float v = d[nt][e] * __expf(fminf(sGs[i] - sGs[j], 0.f));
+            if (pass) sA[i * lda + j] = (j <= i) ? v : 0.f;
+            else sX[i * lda + j] = (j < i) ? v : 0.f;
+          }
+        }
+      }
+    }
+    for (int e = tid; e < 64 * 64; e += kBwThreads) {
+      const int i = e >> 6, j = e & 63;
+      if ((j >> 3) > (i >> 4) * 2 + 1) { sX[i * lda + j] = 0.f; sA[i * lda + j] = 0.f; }
+    }
+  }
+  __syncthreads();
+  sm100::block_inverse_64(sX, sBeta, sT, tid);   // ends with a barrier of all 256 threads
+  // ---- X, A, T -> [3][64][64] ---------------------------------------------------------------------------------------
+  float* dst = p.pre + ((int64_t)unit * N + n) * (3 * 64 * 64 + 2 * 64 * K);
+  for (int i = tid; i < 3 * 64 * 16; i += kBwThreads) {
+    const int m = i >> 10, r = (i >> 4) & 63, c4 = (i & 15) * 4;
+    const float* src = (m == 0 ? sX : m == 1 ? sA : sT) + r * lda + c4;
+    float4 v = *reinterpret_cast<const float4*>(src);
+    if (m == 2) {   // the inverse leaves scratch above the diagonal: store zeros there
+      if (c4 + 0 > r) v.x = 0.f;
+      if (c4 + 1 > r) v.y = 0.f;
+      if (c4 + 2 > r) v.z = 0.f;
+      if (c4 + 3 > r) v.w = 0.f;
+    }
+    *reinterpret_cast<float4*>(dst + m * 4096 + r * 64 + c4) = v;
+  }
+  {
+    float* qdst = dst + 3 * 4096;
+    const int k4 = K >> 2;
+    for (int i = tid; i < 2 * 64 * k4; i += kBwThreads) {
+      const int m = i / (64 * k4), r = (i / k4) & 63, c4 = (i % k4) * 4;
+      *reinterpret_cast<float4*>(qdst + (m * 64 + r) * K + c4) = *reinterpret_cast<const float4*>((m ? sK : sQ) + r * ldk + c4);
+    }
+  }
+}
+
 struct BwdFinalParams {
   const void* q; const void* k;
   void* dq; void* dk; float* dg;
@@ -983,6 +1170,12 @@ inline bool bwd_supported(const DrDesc* d) {
   return d->chunk <= 64 && d->K <= 128 && (d->variant != DR_KDA || d->K % 16 == 0);
 }
 
+// bf16 inputs with whole 16x8 tiles: the products of the adjoint run on the tensor cores (tf32); fp32 inputs
+// stay on the exact CUDA-core path
+inline bool bwd_tensor_core_path(const DrDesc* d) {
+  return d->variant != DR_KDA && d->qkv_dtype == DR_BF16 && d->chunk == 64 && d->K % 16 == 0 && d->V % 8 == 0;
+}
+
 inline int64_t bwd_workspace_bytes(const DrDesc* d) {
   if (!bwd_supported(d)) return DR_ERR_UNSUPPORTED;
   const int64_t N = (d->T + d->chunk - 1) / d->chunk;
@@ -992,6 +1185,7 @@ inline int64_t bwd_workspace_bytes(const DrDesc* d) {
   int64_t f = units * N * d->K * d->V + 2 * rows * d->K * nvs;
   if (d->variant == DR_GATED) f += rows;
   if (d->variant == DR_KDA) f += rows * d->K;
+  if (bwd_tensor_core_path(d)) f += units * N * (3 * 64 * 64 + 2 * 64 * d->K);   // X, A, T, q^, k^ of every chunk
   return f * (int64_t)sizeof(float);
 }
 
@@ -1047,6 +1241,7 @@ inline cudaError_t launch_bwd_adjoint(const DrDesc* d, const void* q, const void
   float* dk_acc = dq_acc + nvs * rows * K;
   float* dg_acc = d->variant == DR_DELTA ? nullptr : dk_acc + nvs * rows * K;
   const size_t dg_floats = d->variant == DR_GATED ? rows : d->variant == DR_KDA ? rows * K : 0;
+  float* pre = dk_acc + nvs * rows * K + dg_floats;   // [units][N][3][64][64], tensor-core path only
   cudaError_t e = cudaSuccess;
   if (dg_floats) e = cudaMemsetAsync(dg_acc, 0, dg_floats * sizeof(float), stream);
   if (e != cudaSuccess) return e;
@@ -1059,7 +1254,7 @@ inline cudaError_t launch_bwd_adjoint(const DrDesc* d, const void* q, const void
   BwdParams p;
   p.q = q; p.k = k; p.v = v; p.g = g; p.beta = beta; p.d_o = d_o; p.d_hT = d_hT;
   p.dv = dv; p.dbeta = dbeta; p.dh0 = dh0;
-  p.ckpt = ckpt; p.dq_acc = dq_acc; p.dk_acc = dk_acc; p.dg_acc = dg_acc;
+  p.ckpt = ckpt; p.dq_acc = dq_acc; p.dk_acc = dk_acc; p.dg_acc = dg_acc; p.pre = nullptr;
   p.map = map; p.K = K; p.V = V; p.C = C; p.N = (int)N;
   p.variant = d->variant; p.qkv_dt = d->qkv_dtype; p.g_dt = d->g_dtype; p.l2norm = d->use_qk_l2norm; p.scale = d->scale;
   if (d->variant == DR_KDA) {
@@ -1071,9 +1266,18 @@ inline cudaError_t launch_bwd_adjoint(const DrDesc* d, const void* q, const void
   } else {
     constexpr int VS = 32;
     // bf16 inputs with whole 16x8 tiles: the products run on the tensor cores (tf32); fp32 inputs stay exact
-    const bool tc = d->qkv_dtype == DR_BF16 && C == 64 && K % 16 == 0;
+    const bool tc = bwd_tensor_core_path(d);
     const size_t smem = bwd_layout(C, K, VS, false, tc).total * sizeof(float);
     if (tc) {
+      // slice-independent pieces (X, A, T) once per chunk, all chunks in parallel
+      p.pre = pre;
+      const size_t psmem = bwd_pre_smem_bytes(K);
+      e = cudaFuncSetAttribute(bwd_pre_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)psmem);
+      if (e != cudaSuccess) return e;
+      bwd_pre_kernel<<<(unsigned)(units * N), kBwThreads, psmem, stream>>>(p);
+      e = cudaGetLastError();
+      if (e != cudaSuccess) return e;
+      ++*launches;
       e = cudaFuncSetAttribute(bwd_chunk_kernel<VS, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return e;
       bwd_chunk_kernel<VS, false, true><<<(unsigned)(units * ((V + VS - 1) / VS)), kBwThreads, smem, stream>>>(p);
