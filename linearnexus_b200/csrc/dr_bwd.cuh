@@ -1109,51 +1109,88 @@ __global__ void __launch_bounds__(256) bwd_finalize_kernel(const BwdFinalParams 
   const int64_t qk_base = p.map.base(b, h, K), qk_tok = p.map.tok(K);
   const int64_t s_base = p.map.base(b, h, 1), s_tok = p.map.tok(1);
   const int64_t acc_row0 = (int64_t)unit * N * C + t0;
+  // lane = four consecutive channels (two groups of 128 channels for K > 128): 16-byte loads of the slice
+  // partials, all of a row's loads issued before the first sum
   for (int c = warp; c < rows; c += 8) {
     const float* aq0 = p.dq_acc + (acc_row0 + c) * K;
     const float* ak0 = p.dk_acc + (acc_row0 + c) * K;
     const int64_t grow = qk_base + (t0 + c) * qk_tok;
     float nq = 0.f, nk = 0.f, dq_q = 0.f, dk_k = 0.f;
-    float aq[8], ak[8];  // this lane's channels (K <= 256), summed over the value slices
+    float aq[2][4], ak[2][4], qv[2][4], kv[2][4];
 #pragma unroll
-    for (int s8 = 0; s8 < 8; ++s8) {
-      const int i = lane + 32 * s8;
-      aq[s8] = 0.f; ak[s8] = 0.f;
+    for (int s2 = 0; s2 < 2; ++s2) {
+      const int i = 4 * lane + 128 * s2;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { aq[s2][e] = 0.f; ak[s2][e] = 0.f; qv[s2][e] = 0.f; kv[s2][e] = 0.f; }
       if (i < K) {
-        for (int sl = 0; sl < p.nvs; ++sl) {
-          aq[s8] += aq0[sl * p.slice_stride + i];
-          ak[s8] += ak0[sl * p.slice_stride + i];
+        float4 xq[8], xk[8];   // up to eight value slices (V <= 256 in 32-column slices)
+#pragma unroll
+        for (int sl = 0; sl < 8; ++sl) {
+          if (sl < p.nvs) {
+            xq[sl] = *reinterpret_cast<const float4*>(aq0 + sl * p.slice_stride + i);
+            xk[sl] = *reinterpret_cast<const float4*>(ak0 + sl * p.slice_stride + i);
+          }
         }
-        const float qv = ld_elem(p.q, grow + i, p.qkv_dt), kv = ld_elem(p.k, grow + i, p.qkv_dt);
-        nq += qv * qv; nk += kv * kv;
-        dq_q += qv * aq[s8]; dk_k += kv * ak[s8];
+        for (int sl = 8; sl < p.nvs; ++sl) {   // (16-column slices of the per-channel-decay variant)
+          const float4 a = *reinterpret_cast<const float4*>(aq0 + sl * p.slice_stride + i);
+          const float4 bq = *reinterpret_cast<const float4*>(ak0 + sl * p.slice_stride + i);
+          aq[s2][0] += a.x; aq[s2][1] += a.y; aq[s2][2] += a.z; aq[s2][3] += a.w;
+          ak[s2][0] += bq.x; ak[s2][1] += bq.y; ak[s2][2] += bq.z; ak[s2][3] += bq.w;
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          qv[s2][e] = ld_elem(p.q, grow + i + e, p.qkv_dt);
+          kv[s2][e] = ld_elem(p.k, grow + i + e, p.qkv_dt);
+        }
+#pragma unroll
+        for (int sl = 0; sl < 8; ++sl) {
+          if (sl < p.nvs) {
+            aq[s2][0] += xq[sl].x; aq[s2][1] += xq[sl].y; aq[s2][2] += xq[sl].z; aq[s2][3] += xq[sl].w;
+            ak[s2][0] += xk[sl].x; ak[s2][1] += xk[sl].y; ak[s2][2] += xk[sl].z; ak[s2][3] += xk[sl].w;
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          nq += qv[s2][e] * qv[s2][e]; nk += kv[s2][e] * kv[s2][e];
+          dq_q += qv[s2][e] * aq[s2][e]; dk_k += kv[s2][e] * ak[s2][e];
+        }
       }
     }
     nq = sqrtf(warp_sum(nq)); nk = sqrtf(warp_sum(nk));
     dq_q = warp_sum(dq_q); dk_k = warp_sum(dk_k);
 #pragma unroll
-    for (int s8 = 0; s8 < 8; ++s8) {
-      const int i = lane + 32 * s8;
+    for (int s2 = 0; s2 < 2; ++s2) {
+      const int i = 4 * lane + 128 * s2;
       if (i >= K) continue;
-      float dq = p.scale * aq[s8], dk = ak[s8];
-      if (p.l2norm) {
-        const float qv = ld_elem(p.q, grow + i, p.qkv_dt), kv = ld_elem(p.k, grow + i, p.qkv_dt);
-        const float rq = 1.f / (nq + 1e-6f), rk = 1.f / (nk + 1e-6f);
-        // y = s x / (n + eps):  dx = s [ dy / (n + eps) - x (x.dy) / (n (n + eps)^2) ]
-        dq = p.scale * (aq[s8] * rq - (nq > 0.f ? qv * dq_q * rq * rq / nq : 0.f));
-        dk = ak[s8] * rk - (nk > 0.f ? kv * dk_k * rk * rk / nk : 0.f);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float dq = p.scale * aq[s2][e], dk = ak[s2][e];
+        if (p.l2norm) {
+          const float rq = 1.f / (nq + 1e-6f), rk = 1.f / (nk + 1e-6f);
+          // y = s x / (n + eps):  dx = s [ dy / (n + eps) - x (x.dy) / (n (n + eps)^2) ]
+          dq = p.scale * (aq[s2][e] * rq - (nq > 0.f ? qv[s2][e] * dq_q * rq * rq / nq : 0.f));
+          dk = ak[s2][e] * rk - (nk > 0.f ? kv[s2][e] * dk_k * rk * rk / nk : 0.f);
+        }
+        st_elem(p.dq, grow + i + e, p.qkv_dt, dq);
+        st_elem(p.dk, grow + i + e, p.qkv_dt, dk);
       }
-      st_elem(p.dq, grow + i, p.qkv_dt, dq);
-      st_elem(p.dk, grow + i, p.qkv_dt, dk);
     }
   }
   if (p.variant == DR_GATED) {
-    if (threadIdx.x == 0) {
-      float acc = 0.f;
-      for (int c = C - 1; c >= 0; --c) {
-        acc += p.dg_acc[acc_row0 + c];
-        if (c < rows) p.dg[s_base + (t0 + c) * s_tok] = acc;
+    // dg = reverse cumulative sum of dG inside the chunk: one warp, two rows per lane
+    if (warp == 0) {
+      float a = lane < C ? p.dg_acc[acc_row0 + lane] : 0.f;
+      float bq = lane + 32 < C ? p.dg_acc[acc_row0 + 32 + lane] : 0.f;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {   // inclusive suffix sums within each half
+        const float ya = __shfl_down_sync(0xffffffffu, a, o);
+        const float yb = __shfl_down_sync(0xffffffffu, bq, o);
+        if (lane + o < 32) { a += ya; bq += yb; }
       }
+      const float upper = __shfl_sync(0xffffffffu, bq, 0);   // total of rows 32..63
+      a += upper;
+      if (lane < rows) p.dg[s_base + (t0 + lane) * s_tok] = a;
+      if (lane + 32 < rows) p.dg[s_base + (t0 + 32 + lane) * s_tok] = bq;
     }
   } else if (p.variant == DR_KDA) {
     for (int i = threadIdx.x; i < K; i += blockDim.x) {
