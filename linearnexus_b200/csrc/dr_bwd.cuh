@@ -930,9 +930,10 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
 // depend on the value slice -- X = tril(K^K^^T.E,-1), A = tril(Q^K^^T.E) and T = (I + diag(beta) X)^-1 -- computed
 // once per chunk instead of once per slice, one CTA per (sequence, chunk), together with the normalised fp32
 // rows q^, k^ themselves.  Output per chunk: [3][64][64] then [2][64][K] fp32.
-inline size_t bwd_pre_smem_bytes(int K) { return sizeof(float) * (2 * 64 * (size_t)(K + 4) + 3 * 64 * sm100::LDT + 128); }
+// (T takes the place of A, which is written out before the inverse starts: two CTAs per SM at K = 128)
+inline size_t bwd_pre_smem_bytes(int K) { return sizeof(float) * (2 * 64 * (size_t)(K + 4) + 2 * 64 * sm100::LDT + 128); }
 
-__global__ void __launch_bounds__(kBwThreads) bwd_pre_kernel(const BwdParams p) {
+__global__ void __launch_bounds__(kBwThreads, 2) bwd_pre_kernel(const BwdParams p) {
   extern __shared__ __align__(16) float smem[];
   const int K = p.K, T = p.map.T, N = p.N;
   constexpr int C = 64;
@@ -941,8 +942,8 @@ __global__ void __launch_bounds__(kBwThreads) bwd_pre_kernel(const BwdParams p) 
   float* sK = sQ + C * ldk;
   float* sX = sK + C * ldk;
   float* sA = sX + C * lda;
-  float* sT = sA + C * lda;
-  float* sGs = sT + C * lda;
+  float* sT = sA;   // A leaves for global memory before the inverse writes T
+  float* sGs = sA + C * lda;
   float* sBeta = sGs + 64;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int unit = blockIdx.x / N, n = blockIdx.x % N;
@@ -1064,12 +1065,18 @@ __global__ void __launch_bounds__(kBwThreads) bwd_pre_kernel(const BwdParams p) 
     }
   }
   __syncthreads();
-  sm100::block_inverse_64(sX, sBeta, sT, tid);   // ends with a barrier of all 256 threads
-  // ---- X, A, T -> [3][64][64] ---------------------------------------------------------------------------------------
+  // ---- X, A, T -> [3][64][64]: A first (its array is reused for T), then the inverse, then X and T -----------------
   float* dst = p.pre + ((int64_t)unit * N + n) * (3 * 64 * 64 + 2 * 64 * K);
+  for (int i = tid; i < 64 * 16; i += kBwThreads) {
+    const int r = i >> 4, c4 = (i & 15) * 4;
+    *reinterpret_cast<float4*>(dst + 4096 + r * 64 + c4) = *reinterpret_cast<const float4*>(sA + r * lda + c4);
+  }
+  __syncthreads();
+  sm100::block_inverse_64(sX, sBeta, sT, tid);   // ends with a barrier of all 256 threads
   for (int i = tid; i < 3 * 64 * 16; i += kBwThreads) {
     const int m = i >> 10, r = (i >> 4) & 63, c4 = (i & 15) * 4;
-    const float* src = (m == 0 ? sX : m == 1 ? sA : sT) + r * lda + c4;
+    if (m == 1) continue;
+    const float* src = (m == 0 ? sX : sT) + r * lda + c4;
     float4 v = *reinterpret_cast<const float4*>(src);
     if (m == 2) {   // the inverse leaves scratch above the diagonal: store zeros there
       if (c4 + 0 > r) v.x = 0.f;
