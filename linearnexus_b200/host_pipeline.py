@@ -2,8 +2,8 @@
 
 The ops in ``ops.py`` take device tensors.  A caller whose q, k, v (and g, beta) sit in pinned host memory
 -- a data loader, an offloaded activation store, a benchmark that times end to end -- pays two PCIe transfers
-around a kernel that is ~30x shorter than they are.  Every (batch row) of the op is independent, so this helper
-cuts the batch into slices and runs
+around a kernel that is ~30x shorter than they are.  Every (batch, head) unit of the op is independent, so this
+helper cuts the work into slices and runs
 
     copy stream   : H2D slice i+1        compute stream : op(slice i)        return stream : D2H slice i-1
 
@@ -51,8 +51,10 @@ class HostPipeline:
                             **op_kwargs) -> Tuple[Tensor, Tensor]:
         """``variant`` in {"delta", "gated", "kda"}; q, k, v, g, beta as for the chunkwise op but in pinned host
         memory, ``[B,H,T,D]``.  Returns ``(o, final_state)`` as pinned host tensors (``out`` / ``final_state`` when
-        given).  ``slices`` batch slices (default: one per batch row).  The call returns when the results are in
-        host memory."""
+        given).  ``slices``: number of pieces the work is cut into (default 8 pieces of the flattened batch x head
+        axis -- every piece costs one kernel's latency, measured best at 4-8 -- or one per batch row when the
+        tensors are not plain contiguous [B,H,T,D]).  The call returns when
+        the results are in host memory."""
         if variant not in _FWD:
             raise ValueError(f"unknown variant {variant!r}")
         if (g is None) != (variant == "delta"):
@@ -62,14 +64,34 @@ class HostPipeline:
             _pinned(t, name)
         B, H, T, K = q.shape
         V = v.shape[-1]
-        n = B if slices is None else max(1, min(int(slices), B))
-        bounds = [(B * i // n, B * (i + 1) // n) for i in range(n)]
+        # Every (batch, head) unit is independent: slice the flattened unit axis (B*H) so that the first copy and
+        # the last kernel / copy-back -- the parts of the pipeline that cannot overlap -- are short.  That needs
+        # [B,H,T,D]-contiguous tensors with one q/k head per head; otherwise slice whole batch rows.
+        flat = (q.shape[1] == v.shape[1] and beta.dim() == 3 and
+                all(t is None or t.is_contiguous() for t in (q, k, v, g, beta, initial_state, out, final_state)))
+        if flat:
+            U = B * H
+            q, k, v = q.view(1, U, T, K), k.view(1, U, T, K), v.view(1, U, T, V)
+            g = None if g is None else g.view(1, U, *g.shape[2:])
+            beta = beta.reshape(1, U, T)
+            initial_state = None if initial_state is None else initial_state.view(1, U, K, V)
+            n = max(1, min(U, 8 if slices is None else int(slices)))
+            bounds = [(U * i // n, U * (i + 1) // n) for i in range(n)]
+            ax = 1
+        else:
+            U = B
+            n = B if slices is None else max(1, min(int(slices), B))
+            bounds = [(B * i // n, B * (i + 1) // n) for i in range(n)]
+            ax = 0
         dev = self.device
         o_dtype = torch.float32 if variant == "kda" and "out_dtype" not in op_kwargs else op_kwargs.get("out_dtype", q.dtype)
         if out is None:
             out = torch.empty((B, H, T, V), dtype=o_dtype).pin_memory()
         if final_state is None:
             final_state = torch.empty((B, H, K, V), dtype=torch.float32).pin_memory()
+        out_v = out.view(1, B * H, T, V) if flat else out
+        fs_v = final_state.view(1, B * H, K, V) if flat else final_state
+        cut = (lambda t, lo, hi: t[:, lo:hi]) if ax == 1 else (lambda t, lo, hi: t[lo:hi])
         caller = torch.cuda.current_stream(dev)
         start = torch.cuda.Event()
         start.record(caller)
@@ -78,7 +100,7 @@ class HostPipeline:
         keep = []   # device tensors stay referenced until the final synchronisation
         for lo, hi in bounds:
             with torch.cuda.stream(self.h2d):
-                ins = [None if t is None else t[lo:hi].to(dev, non_blocking=True)
+                ins = [None if t is None else cut(t, lo, hi).to(dev, non_blocking=True)
                        for t in (q, k, v, g, beta, initial_state)]
                 ready = torch.cuda.Event()
                 ready.record(self.h2d)
@@ -89,8 +111,8 @@ class HostPipeline:
                 done.record(self.compute)
             with torch.cuda.stream(self.d2h):
                 self.d2h.wait_event(done)
-                out[lo:hi].copy_(o_d, non_blocking=True)
-                final_state[lo:hi].copy_(s_d, non_blocking=True)
+                cut(out_v, lo, hi).copy_(o_d, non_blocking=True)
+                cut(fs_v, lo, hi).copy_(s_d, non_blocking=True)
             for t in ins + [o_d, s_d]:
                 if t is not None:
                     t.record_stream(self.compute)
