@@ -30,6 +30,9 @@
 namespace dr {
 
 constexpr int kBwThreads = 256;
+// the tensor-core adjoint runs 16 warps: its phases are short dependent chains of mma.sync and shared-memory
+// fetches, and four warps per scheduler hide them where two did not
+__host__ __device__ constexpr int bwd_threads(bool tc) { return tc ? 512 : 256; }
 
 // One 16x8 output tile of D (+)= A B on the warp-level tensor-core path (tf32 operands, fp32
 // accumulate): a(m, k), b(k, n) are element accessors into fp32 shared memory.  Lane (g = lane/4,
@@ -117,6 +120,42 @@ __device__ __forceinline__ void rgemm3(float (&d1)[NT][4], float (&d2)[NT][4], f
   }
 }
 
+// The same row-panel products with the contraction index taken in pairs: lane (g, t) supplies k0 + 2t and
+// k0 + 2t + 1 where the natural order has k0 + t and k0 + t + 4 (a sum over k does not care).  The accessors
+// return both values at once, a2(m, k) = {A[m][k], A[m][k+1]} and b2(k, n) = {B[k][n], B[k+1][n]}.
+template <int NT, class AF, class BF>
+__device__ __forceinline__ void rgemm_p(float (&d)[NT][4], int m0, int n0, int kb, int ke, AF a2, BF b2, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  for (int k0 = kb; k0 < ke; k0 += 8) {
+    const float2 x0 = a2(m0 + g, k0 + 2 * t), x1 = a2(m0 + g + 8, k0 + 2 * t);
+    const uint32_t af[4] = {__float_as_uint(x0.x), __float_as_uint(x1.x), __float_as_uint(x0.y), __float_as_uint(x1.y)};
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const float2 y = b2(k0 + 2 * t, n0 + 8 * nt + g);
+      const uint32_t bf[2] = {__float_as_uint(y.x), __float_as_uint(y.y)};
+      sm100::mma_tf32(d[nt], af, bf);
+    }
+  }
+}
+template <int NT, class AF1, class AF2, class BF>
+__device__ __forceinline__ void rgemm2_p(float (&d1)[NT][4], float (&d2)[NT][4], int m0, int n0, int kb, int ke, AF1 a1,
+                                         AF2 a2, BF b2, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  for (int k0 = kb; k0 < ke; k0 += 8) {
+    const float2 x0 = a1(m0 + g, k0 + 2 * t), x1 = a1(m0 + g + 8, k0 + 2 * t);
+    const float2 z0 = a2(m0 + g, k0 + 2 * t), z1 = a2(m0 + g + 8, k0 + 2 * t);
+    const uint32_t af1[4] = {__float_as_uint(x0.x), __float_as_uint(x1.x), __float_as_uint(x0.y), __float_as_uint(x1.y)};
+    const uint32_t af2[4] = {__float_as_uint(z0.x), __float_as_uint(z1.x), __float_as_uint(z0.y), __float_as_uint(z1.y)};
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const float2 y = b2(k0 + 2 * t, n0 + 8 * nt + g);
+      const uint32_t bf[2] = {__float_as_uint(y.x), __float_as_uint(y.y)};
+      sm100::mma_tf32(d1[nt], af1, bf);
+      sm100::mma_tf32(d2[nt], af2, bf);
+    }
+  }
+}
+
 struct BwdParams {
   const void* q; const void* k; const void* v; const void* g; const float* beta;
   const void* d_o; const float* d_hT;
@@ -130,22 +169,29 @@ struct BwdParams {
 };
 
 struct BwdSmem {
-  int ldk, lda, ldv;
+  int ldk, ldq, lda, ldt, ldv;
   size_t q, k, g, x, a, t, v, d_o, vn, dr, s0, ds, gs, eg, wd, beta, dbeta, el, total;
 };
 
-// tc: strides that keep tensor-core fragment fetches (row = lane/4, column = lane%4) conflict-free and 16-byte
-// aligned, plus the array of the explicit inverse T = M^-1 (row stride sm100::LDT)
+// tc: the strides decide which tensor-core fragment fetches are free of bank conflicts.  A fragment is read either
+// along the rows of its array (array row <- lane / 4, the contraction index k <- lane % 4 along the row) or
+// across them (array row <- k <- lane % 4, consecutive words <- lane / 4).  With k in the natural order (lane % 4
+// and lane % 4 + 4) a read along the rows wants a stride of 4 mod 32 words and a read across them 8 mod 32; with
+// k taken in pairs (2 (lane % 4) and the word after it: one 8-byte load along a row) it is the other way round.
+// Every product of the kernel picks the order that suits both of its operands: k^ and T sit at 4 mod 32,
+// everything else at 8 mod 32.  Three products keep a two-way conflict on one operand (T^T in dR; k^ in dS0 and
+// in the column sums of dX).
 __host__ __device__ inline BwdSmem bwd_layout(int C, int K, int VS, bool kda, bool tc = false) {
   BwdSmem L;
-  L.ldk = K + 4; L.lda = tc ? sm100::LDT : C + 1; L.ldv = tc ? VS + 4 : VS + 1;
+  L.ldk = K + 4; L.ldq = tc ? K + 8 : K + 4;
+  L.lda = tc ? 72 : C + 1; L.ldt = sm100::LDT; L.ldv = tc ? VS + 8 : VS + 1;
   size_t o = 0;
-  L.q = o; o += (size_t)C * L.ldk;
+  L.q = o; o += (size_t)C * L.ldq;
   L.k = o; o += (size_t)C * L.ldk;
   L.g = o; o += kda ? (size_t)C * L.ldk : 0;
   L.x = o; o += (size_t)C * L.lda;
   L.a = o; o += (size_t)C * L.lda;
-  L.t = o; o += tc ? (size_t)C * L.lda : 0;
+  L.t = o; o += tc ? (size_t)C * L.ldt : 0;
   L.v = o; o += (size_t)C * L.ldv;
   L.d_o = o; o += (size_t)C * L.ldv;
   L.vn = o; o += (size_t)C * L.ldv;
@@ -169,7 +215,9 @@ __host__ __device__ inline BwdSmem bwd_layout(int C, int K, int VS, bool kda, bo
 
 // TC: the products run on mma.sync tf32 (bf16 inputs: well inside their 2e-2 tolerance); otherwise exact fp32.
 template <int VS, bool KDA, bool TC>
-__global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p) {
+__global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdParams p) {
+  constexpr int NTHR = bwd_threads(TC), NW = NTHR / 32;
+  constexpr int NTW = NW / 4;   // tensor-core phases: warps that share one 16-row panel of the chunk
   extern __shared__ __align__(16) float smem[];
   const int K = p.K, V = p.V, C = p.C, T = p.map.T, N = p.N;
   const bool gated = p.variant == DR_GATED;
@@ -180,7 +228,7 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
   float* sS0 = smem + L.s0;    float* sdS = smem + L.ds;
   float* sGs = smem + L.gs;    float* sEG = smem + L.eg;   float* sWd = smem + L.wd;
   float* sBeta = smem + L.beta; float* sdBeta = smem + L.dbeta; float* sEL = smem + L.el;
-  const int ldk = L.ldk, lda = L.lda, ldv = L.ldv;
+  const int ldk = L.ldk, ldq = L.ldq, lda = L.lda, ldt = L.ldt, ldv = L.ldv;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nvs = (V + VS - 1) / VS;
@@ -195,7 +243,7 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
   // the finalize kernel adds the slices), dG and dbeta are few enough for atomics
   const int64_t slice_off = (int64_t)(blockIdx.x % nvs) * ((int64_t)p.map.B * p.map.H * N * C) * K;
 
-  for (int i = tid; i < K * VS; i += kBwThreads) {
+  for (int i = tid; i < K * VS; i += NTHR) {
     const int kk = i / VS, vv = i % VS;
     sdS[kk * ldv + vv] = (p.d_hT && v0 + vv < V) ? p.d_hT[((int64_t)unit * K + kk) * V + v0 + vv] : 0.f;
   }
@@ -210,108 +258,58 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
     BPROF(150);
     // ---- stage q^, k^ (fp32, normalised / scaled), g, beta, v, dO, S0 --------------------------------
     if constexpr (TC) {
-      if (p.pre) {
-        // X, A, T of this chunk were computed once for all value slices: 16-byte async copies into their arrays
-        // (and so were the normalised fp32 rows q^, k^)
+      {
+        // X, A, T of this chunk were computed once for all value slices by bwd_pre_kernel: 16-byte async copies
+        // into their arrays (and so were the normalised fp32 rows q^, k^)
         const float* src = p.pre + ((int64_t)unit * N + n) * (3 * 64 * 64 + 2 * 64 * K);
-        for (int i = tid; i < 3 * 64 * 16; i += kBwThreads) {
+        for (int i = tid; i < 3 * 64 * 16; i += NTHR) {
           const int m = i >> 10, r = (i >> 4) & 63, c4 = (i & 15) * 4;
-          float* dst = (m == 0 ? sX : m == 1 ? sA : sT) + r * lda + c4;
+          float* dst = (m == 0 ? sX + r * lda : m == 1 ? sA + r * lda : sT + r * ldt) + c4;
           tc::cp_async16(tc::smem_u32(dst), src + m * 4096 + r * 64 + c4, true);
         }
         const float* qsrc = src + 3 * 4096;
         const int k4 = K >> 2;
-        for (int i = tid; i < 2 * 64 * k4; i += kBwThreads) {
+        for (int i = tid; i < 2 * 64 * k4; i += NTHR) {
           const int m = i / (64 * k4), r = (i / k4) & 63, c4 = (i % k4) * 4;
-          tc::cp_async16(tc::smem_u32((m ? sK : sQ) + r * ldk + c4), qsrc + (m * 64 + r) * K + c4, true);
+          tc::cp_async16(tc::smem_u32((m ? sK + r * ldk : sQ + r * ldq) + c4), qsrc + (m * 64 + r) * K + c4, true);
         }
         tc::cp_async_commit();
       }
-      const bool have_qk = p.pre != nullptr;
-      // bf16 inputs: 8-byte (q, k) and 16-byte (v, dO, S0) accesses, every global load of the warp's eight rows
-      // issued before the first is used (C = 64: rows warp, warp + 8, ...)
-      const __nv_bfloat16* gq = reinterpret_cast<const __nv_bfloat16*>(p.q);
-      const __nv_bfloat16* gk = reinterpret_cast<const __nv_bfloat16*>(p.k);
-      uint2 qr[8][2], kr[8][2];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int c = warp + 8 * i;
-#pragma unroll
-        for (int ps = 0; ps < 2; ++ps) {
-          const int ch = 128 * ps + 4 * lane;
-          qr[i][ps] = make_uint2(0u, 0u); kr[i][ps] = make_uint2(0u, 0u);
-          if (!have_qk && c < rows && ch < K) {
-            qr[i][ps] = *reinterpret_cast<const uint2*>(gq + qk_base + (t0 + c) * qk_tok + ch);
-            kr[i][ps] = *reinterpret_cast<const uint2*>(gk + qk_base + (t0 + c) * qk_tok + ch);
-          }
-        }
-      }
+      // beta, g: row warp + NW * lane of the chunk (C = 64)
+      constexpr int RPW = 64 / NW;
       float bt = 0.f, gt_ = 0.f;
-      if (lane < 8 && warp + 8 * lane < rows) {
-        bt = p.beta[s_base + (t0 + warp + 8 * lane) * s_tok];
-        if (gated) gt_ = ld_elem(p.g, s_base + (t0 + warp + 8 * lane) * s_tok, p.g_dt);
+      if (lane < RPW && warp + NW * lane < rows) {
+        bt = p.beta[s_base + (t0 + warp + NW * lane) * s_tok];
+        if (gated) gt_ = ld_elem(p.g, s_base + (t0 + warp + NW * lane) * s_tok, p.g_dt);
       }
+      // bf16 v, dO and the fp32 checkpoint slice: 16-byte accesses, every global load issued before the first is used
       uint4 vr = make_uint4(0u, 0u, 0u, 0u), dor = make_uint4(0u, 0u, 0u, 0u);
       const int vrow = tid / (VS / 8), vpc = tid % (VS / 8);
       if (tid < C * (VS / 8) && vrow < rows && v0 + 8 * vpc < V) {
         vr = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.v) + v_base + (t0 + vrow) * v_tok + v0 + 8 * vpc);
         dor = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.d_o) + v_base + (t0 + vrow) * v_tok + v0 + 8 * vpc);
       }
-      float4 s0r[8];   // K <= 256, VS = 32: at most eight 16-byte pieces of the checkpoint slice per thread
+      constexpr int SIT = 2048 / NTHR;   // K <= 256, VS = 32: at most 2048 16-byte pieces of the checkpoint slice
+      float4 s0r[SIT];
       {
         const float* ck = p.ckpt + ((int64_t)unit * N + n) * K * V;
 #pragma unroll
-        for (int it = 0; it < 8; ++it) {
-          const int i = tid + it * kBwThreads;
+        for (int it = 0; it < SIT; ++it) {
+          const int i = tid + it * NTHR;
           const int kk = i / (VS / 4), j4 = 4 * (i % (VS / 4));
           s0r[it] = make_float4(0.f, 0.f, 0.f, 0.f);
           if (i < K * (VS / 4) && v0 + j4 < V) s0r[it] = *reinterpret_cast<const float4*>(ck + (int64_t)kk * V + v0 + j4);
         }
       }
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int c = warp + 8 * i;
-        if (!have_qk) {
-        float qf[2][4], kf[2][4];
-        float nq = 0.f, nk = 0.f;
-#pragma unroll
-        for (int ps = 0; ps < 2; ++ps) {
-          const float2 a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qr[i][ps].x));
-          const float2 a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qr[i][ps].y));
-          const float2 b0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr[i][ps].x));
-          const float2 b1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr[i][ps].y));
-          qf[ps][0] = a0.x; qf[ps][1] = a0.y; qf[ps][2] = a1.x; qf[ps][3] = a1.y;
-          kf[ps][0] = b0.x; kf[ps][1] = b0.y; kf[ps][2] = b1.x; kf[ps][3] = b1.y;
-#pragma unroll
-          for (int e = 0; e < 4; ++e) { nq += qf[ps][e] * qf[ps][e]; nk += kf[ps][e] * kf[ps][e]; }
-        }
-        float qmul = p.scale, kmul = 1.f;
-        if (p.l2norm) {
-          nq = warp_sum(nq);
-          nk = warp_sum(nk);
-          qmul = p.scale / (sqrtf(nq) + 1e-6f);
-          kmul = 1.f / (sqrtf(nk) + 1e-6f);
-        }
-#pragma unroll
-        for (int ps = 0; ps < 2; ++ps) {
-          const int ch = 128 * ps + 4 * lane;
-          if (ch < K) {
-            *reinterpret_cast<float4*>(sQ + c * ldk + ch) =
-                make_float4(qf[ps][0] * qmul, qf[ps][1] * qmul, qf[ps][2] * qmul, qf[ps][3] * qmul);
-            *reinterpret_cast<float4*>(sK + c * ldk + ch) =
-                make_float4(kf[ps][0] * kmul, kf[ps][1] * kmul, kf[ps][2] * kmul, kf[ps][3] * kmul);
-          }
-        }
-        }
-        if (lane == i) {
-          sBeta[c] = bt;
-          sGs[c] = gt_;
-          sdBeta[c] = 0.f;
-        }
+      if (lane < RPW) {
+        const int c = warp + NW * lane;
+        sBeta[c] = bt;
+        sGs[c] = gt_;
+        sdBeta[c] = 0.f;
       }
 #pragma unroll
-      for (int it = 0; it < 8; ++it) {
-        const int i = tid + it * kBwThreads;
+      for (int it = 0; it < SIT; ++it) {
+        const int i = tid + it * NTHR;
         if (i < K * (VS / 4)) *reinterpret_cast<float4*>(sS0 + (i / (VS / 4)) * ldv + 4 * (i % (VS / 4))) = s0r[it];
       }
       if (tid < C * (VS / 8)) {
@@ -326,7 +324,7 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
         }
       }
     } else {
-    for (int c = warp; c < C; c += kBwThreads / 32) {
+    for (int c = warp; c < C; c += NTHR / 32) {
       float nq = 0.f, nk = 0.f;
       const bool live = c < rows;
       for (int i = lane; i < K; i += 32) {
@@ -336,7 +334,7 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
           kv = ld_elem(p.k, qk_base + (t0 + c) * qk_tok + i, p.qkv_dt);
           if (KDA) gv = ld_elem(p.g, qk_base + (t0 + c) * qk_tok + i, p.g_dt);
         }
-        sQ[c * ldk + i] = qv;
+        sQ[c * ldq + i] = qv;
         sK[c * ldk + i] = kv;
         if (KDA) sG[c * ldk + i] = gv;
         nq += qv * qv;
@@ -351,7 +349,7 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
       }
       __syncwarp();
       for (int i = lane; i < K; i += 32) {
-        sQ[c * ldk + i] *= qmul;
+        sQ[c * ldq + i] *= qmul;
         sK[c * ldk + i] *= kmul;
       }
       if (lane == 0) {
@@ -360,7 +358,7 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
         sdBeta[c] = 0.f;
       }
     }
-    for (int i = tid; i < C * VS; i += kBwThreads) {
+    for (int i = tid; i < C * VS; i += NTHR) {
       const int c = i / VS, vv = i % VS;
       float x = 0.f, y = 0.f;
       if (c < rows && v0 + vv < V) {
@@ -372,19 +370,17 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
     }
     {
       const float* ck = p.ckpt + ((int64_t)unit * N + n) * K * V;
-      for (int i = tid; i < K * VS; i += kBwThreads) {
+      for (int i = tid; i < K * VS; i += NTHR) {
         const int kk = i / VS, vv = i % VS;
         sS0[kk * ldv + vv] = (v0 + vv < V) ? ck[(int64_t)kk * V + v0 + vv] : 0.f;
       }
     }
     }
-    if constexpr (TC) {
-      if (p.pre) tc::cp_async_wait_all();
-    }
+    if constexpr (TC) tc::cp_async_wait_all();
     __syncthreads();
     BPROF(151);
     if (KDA) {
-      for (int i = tid; i < K; i += kBwThreads) {
+      for (int i = tid; i < K; i += NTHR) {
         float acc = 0.f;
         for (int c = 0; c < C; ++c) {
           acc += sG[c * ldk + i];
@@ -399,74 +395,22 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
     __syncthreads();
     if (!KDA) {
       const float gl = sGs[C - 1];
-      for (int i = tid; i < C; i += kBwThreads) {
+      for (int i = tid; i < C; i += NTHR) {
         sEG[i] = expf(sGs[i]);
         sWd[i] = expf(fminf(gl - sGs[i], 0.f));
       }
-      for (int i = tid; i < K; i += kBwThreads) sEL[i] = expf(gl);
+      for (int i = tid; i < K; i += NTHR) sEL[i] = expf(gl);
     }
     BPROF(152);
     // ---- X = tril(K^K^^T.E,-1) (not yet scaled by beta), A = tril(Q^K^^T.E) ---------------------------
     if constexpr (TC) {
-      // rows 0..63 of the stacked product are K^ (-> X), rows 64..127 are Q^ (-> A); the decay factor is
-      // folded in here (the exact path applies it where an entry is used)
-      if (!p.pre) {
-        // Lower-triangular 16-row panels cut into tasks of at most three 8-column tiles:
-        //   task 0..2: rows 48.., tiles 0-2 / 3-5 / 6-7    3,4: rows 32.., tiles 0-2 / 3-5
-        //   5,6: rows 16.., tiles 0-1 / 2-3                7: rows 0.., tiles 0-1
-        // warp w runs task w on K^ (-> X) and task 7-w on Q^ (-> A): five or six tiles per warp.
-        const int g = lane >> 2, t = lane & 3;
-#pragma unroll 1
-        for (int pass = 0; pass < 2; ++pass) {
-          const int task = pass ? 7 - warp : warp;
-          const int i0 = task < 3 ? 48 : task < 5 ? 32 : task < 7 ? 16 : 0;
-          const int nt0 = task < 3 ? 3 * task : task < 5 ? 3 * (task - 3) : task < 7 ? 2 * (task - 5) : 0;
-          const int ntn = (task == 2 || task >= 5) ? 2 : 3;
-          const float* arows = pass ? sQ : sK;
-          float d[3][4];
-#pragma unroll
-          for (int nt = 0; nt < 3; ++nt) d[nt][0] = d[nt][1] = d[nt][2] = d[nt][3] = 0.f;
-          for (int k0 = 0; k0 < K; k0 += 8) {
-            uint32_t af[4];
-            af[0] = __float_as_uint(arows[(i0 + g) * ldk + k0 + t]);
-            af[1] = __float_as_uint(arows[(i0 + g + 8) * ldk + k0 + t]);
-            af[2] = __float_as_uint(arows[(i0 + g) * ldk + k0 + t + 4]);
-            af[3] = __float_as_uint(arows[(i0 + g + 8) * ldk + k0 + t + 4]);
-#pragma unroll
-            for (int nt = 0; nt < 3; ++nt) {
-              if (nt < ntn) {
-                uint32_t bf[2];
-                bf[0] = __float_as_uint(sK[(8 * (nt0 + nt) + g) * ldk + k0 + t]);
-                bf[1] = __float_as_uint(sK[(8 * (nt0 + nt) + g) * ldk + k0 + t + 4]);
-                sm100::mma_tf32(d[nt], af, bf);
-              }
-            }
-          }
-#pragma unroll
-          for (int nt = 0; nt < 3; ++nt) {
-            if (nt < ntn) {
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const int i = i0 + g + (e >> 1) * 8, j = 8 * (nt0 + nt) + 2 * t + (e & 1);
-                const float v = d[nt][e] * __expf(fminf(sGs[i] - sGs[j], 0.f));
-                if (pass) sA[i * lda + j] = (j <= i) ? v : 0.f;
-                else sX[i * lda + j] = (j < i) ? v : 0.f;
-              }
-            }
-          }
-        }
-        // the tiles above the diagonal blocks are zero
-        for (int e = tid; e < 64 * 64; e += kBwThreads) {
-          const int i = e >> 6, j = e & 63;
-          if ((j >> 3) > (i >> 4) * 2 + 1) { sX[i * lda + j] = 0.f; sA[i * lda + j] = 0.f; }
-        }
-      }
+      // X and A (decay folded in) came from the pre-pass
     } else {
-    for (int pid = tid; pid < C * C; pid += kBwThreads) {
+    for (int pid = tid; pid < C * C; pid += NTHR) {
       const int i = pid / C, j = pid % C;
       float akk = 0.f, aqk = 0.f;
       if (j <= i) {
-        const float4* qi = reinterpret_cast<const float4*>(sQ + i * ldk);
+        const float4* qi = reinterpret_cast<const float4*>(sQ + i * ldq);
         const float4* ki = reinterpret_cast<const float4*>(sK + i * ldk);
         const float4* kj = reinterpret_cast<const float4*>(sK + j * ldk);
         if (KDA) {
@@ -493,12 +437,13 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
     }
     __syncthreads();
     BPROF(153);
+    auto ld2 = [](const float* ptr) { return *reinterpret_cast<const float2*>(ptr); };
     auto Eij = [&](int i, int j) -> float { return (KDA || TC) ? 1.f : __expf(fminf(sGs[i] - sGs[j], 0.f)); };
     // ---- R = beta V - (beta K^ e^G) S0  (lane = value column, warp = rows) ----------------------------
     if constexpr (TC) {
       {
-        constexpr int NT = VS / 16;
-        const int m0 = (warp >> 1) * 16, n0 = (warp & 1) * 8 * NT;
+        constexpr int NT = VS / 8 / NTW;
+        const int m0 = (warp / NTW) * 16, n0 = (warp % NTW) * 8 * NT;
         float d[NT][4];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) d[nt][0] = d[nt][1] = d[nt][2] = d[nt][3] = 0.f;
@@ -534,14 +479,13 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
     BPROF(154);
     // ---- Vn = M^-1 R : forward substitution, 8 lanes per column -----------------------------------------
     if constexpr (TC) {
-      // explicit inverse T = (I + diag(beta) X)^-1 (X carries the decay), then Vn = T R on the tensor cores
-      if (!p.pre) sm100::block_inverse_64(sX, sBeta, sT, tid);
-      constexpr int NT = VS / 16;
-      const int m0 = (warp >> 1) * 16, n0 = (warp & 1) * 8 * NT;
+      // with the explicit inverse T = (I + diag(beta) X)^-1 of the pre-pass, Vn = T R on the tensor cores
+      constexpr int NT = VS / 8 / NTW;
+      const int m0 = (warp / NTW) * 16, n0 = (warp % NTW) * 8 * NT;
       float d[NT][4];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) d[nt][0] = d[nt][1] = d[nt][2] = d[nt][3] = 0.f;
-      rgemm<NT>(d, m0, n0, 0, m0 + 16, [&](int m, int k) { return k <= m ? sT[m * lda + k] : 0.f; },
+      rgemm<NT>(d, m0, n0, 0, m0 + 16, [&](int m, int k) { return k <= m ? sT[m * ldt + k] : 0.f; },
                 [&](int k, int nn) { return sVn[k * ldv + nn]; }, lane);
       __syncthreads();
       const int g = lane >> 2, t = lane & 3;
@@ -568,8 +512,8 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
     // ---- dVn = A^T dO + (K^ e^{G_L-G}) dS1 -----------------------------------------------------------------
     if constexpr (TC) {
       {
-        constexpr int NT = VS / 16;
-        const int m0 = (warp >> 1) * 16, n0 = (warp & 1) * 8 * NT;
+        constexpr int NT = VS / 8 / NTW;
+        const int m0 = (warp / NTW) * 16, n0 = (warp % NTW) * 8 * NT;
         float d1[NT][4], d2[NT][4];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
@@ -610,12 +554,12 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
     BPROF(156);
     // ---- dR = M^-T dVn : back substitution ---------------------------------------------------------------------
     if constexpr (TC) {
-      constexpr int NT = VS / 16;
-      const int m0 = (warp >> 1) * 16, n0 = (warp & 1) * 8 * NT;
+      constexpr int NT = VS / 8 / NTW;
+      const int m0 = (warp / NTW) * 16, n0 = (warp % NTW) * 8 * NT;
       float d[NT][4];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) d[nt][0] = d[nt][1] = d[nt][2] = d[nt][3] = 0.f;
-      rgemm<NT>(d, m0, n0, m0, C, [&](int m, int k) { return k >= m ? sT[k * lda + m] : 0.f; },
+      rgemm<NT>(d, m0, n0, m0, C, [&](int m, int k) { return k >= m ? sT[k * ldt + m] : 0.f; },
                 [&](int k, int nn) { return sdR[k * ldv + nn]; }, lane);
       __syncthreads();
       const int g = lane >> 2, t = lane & 3;
@@ -640,12 +584,12 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
     __syncthreads();
     BPROF(157);
     // ---- dV = beta dR ; dbeta += dR.V ; dA = tril(dO Vn^T).E ; dX = beta tril(-dR Vn^T).E ; dbeta += dM.X ------
-    for (int i = tid; i < C * VS; i += kBwThreads) {
+    for (int i = tid; i < C * VS; i += NTHR) {
       const int c = i / VS, vv = i % VS;
       if (c < rows && v0 + vv < V)
         st_elem(p.dv, v_base + (t0 + c) * v_tok + v0 + vv, p.qkv_dt, sBeta[c] * sdR[c * ldv + vv]);
     }
-    for (int c = warp; c < C; c += 8) {
+    for (int c = warp; c < C; c += NW) {
       float acc = 0.f;
       for (int vv = lane; vv < VS; vv += 32) acc += sdR[c * ldv + vv] * sV[c * ldv + vv];
       acc = warp_sum(acc);
@@ -654,21 +598,23 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
     __syncthreads();
     if constexpr (TC) {
       {
-        // warp = 16 rows x 32 columns; both products share the B operand Vn^T
-        const int m0 = (warp >> 1) * 16, n0 = (warp & 1) * 32;
-        float da[4][4], dm[4][4];
+        // warp = 16 rows x 64 / NTW columns; both products share the B operand Vn^T
+        constexpr int NA = 8 / NTW;
+        const int m0 = (warp / NTW) * 16, n0 = (warp % NTW) * 8 * NA;
+        float da[NA][4], dm[NA][4];
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
+        for (int nt = 0; nt < NA; ++nt) {
           da[nt][0] = da[nt][1] = da[nt][2] = da[nt][3] = 0.f;
           dm[nt][0] = dm[nt][1] = dm[nt][2] = dm[nt][3] = 0.f;
         }
         if (n0 <= m0 + 15)
-          rgemm2<4>(da, dm, m0, n0, 0, VS, [&](int m, int k) { return sdO[m * ldv + k]; },
-                    [&](int m, int k) { return sdR[m * ldv + k]; }, [&](int k, int nn) { return sVn[nn * ldv + k]; }, lane);
+          rgemm2_p<NA>(da, dm, m0, n0, 0, VS, [&](int m, int k) { return ld2(sdO + m * ldv + k); },
+                       [&](int m, int k) { return ld2(sdR + m * ldv + k); },
+                       [&](int k, int nn) { return ld2(sVn + nn * ldv + k); }, lane);
         const int g = lane >> 2, t = lane & 3;
         float dbacc[2] = {0.f, 0.f};
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt)
+        for (int nt = 0; nt < NA; ++nt)
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int i = m0 + g + (e >> 1) * 8, j = n0 + 8 * nt + 2 * t + (e & 1);
@@ -687,7 +633,7 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
         }
       }
     } else {
-    for (int pid = tid; pid < C * C; pid += kBwThreads) {
+    for (int pid = tid; pid < C * C; pid += NTHR) {
       const int i = pid / C, j = pid % C;   // a warp covers 32 consecutive j of one row i
       float da = 0.f, dm = 0.f;
       if (j <= i) {
@@ -707,38 +653,40 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
     BPROF(158);
     // ---- per (row i, channel k): dQ^, dK^, dG, dbeta; lane = channel, warp = rows ----------------------------------
     if constexpr (TC) {
-      // warp w owns rows 16*(w/2)..; the channel tiles are dealt to the two warps of a row panel in pairs.
+      // warp w owns rows 16*(w/NTW)..; the channel tiles are dealt to the NTW warps of a row panel in pairs.
       // Seven products per tile; products with the same B operand share its fetch, the A fragments are
       // fetched once per pair of tiles.
       const int g = lane >> 2, t = lane & 3;
-      const int m0 = (warp >> 1) * 16;
+      const int m0 = (warp / NTW) * 16;
       float dgrow[2] = {0.f, 0.f}, dbrow[2] = {0.f, 0.f}, extra = 0.f;
-      for (int n0 = (warp & 1) * 16; n0 < K; n0 += 32) {
+      for (int n0 = (warp % NTW) * 16; n0 < K; n0 += 16 * NTW) {
         float dQg[2][4], dKg[2][4], dKt[2][4], rowA[2][4], rowX[2][4], colA[2][4], colX[2][4];
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
           for (int e = 0; e < 4; ++e)
             dQg[nt][e] = dKg[nt][e] = dKt[nt][e] = rowA[nt][e] = rowX[nt][e] = colA[nt][e] = colX[nt][e] = 0.f;
-        rgemm2<2>(dQg, dKg, m0, n0, 0, VS, [&](int m, int k) { return sdO[m * ldv + k]; },
-                  [&](int m, int k) { return sdR[m * ldv + k]; }, [&](int k, int nn) { return sS0[nn * ldv + k]; }, lane);
-        rgemm<2>(dKt, m0, n0, 0, VS, [&](int m, int k) { return sVn[m * ldv + k]; },
-                 [&](int k, int nn) { return sdS[nn * ldv + k]; }, lane);
+        rgemm2_p<2>(dQg, dKg, m0, n0, 0, VS, [&](int m, int k) { return ld2(sdO + m * ldv + k); },
+                    [&](int m, int k) { return ld2(sdR + m * ldv + k); },
+                    [&](int k, int nn) { return ld2(sS0 + nn * ldv + k); }, lane);
+        rgemm_p<2>(dKt, m0, n0, 0, VS, [&](int m, int k) { return ld2(sVn + m * ldv + k); },
+                   [&](int k, int nn) { return ld2(sdS + nn * ldv + k); }, lane);
         auto bK = [&](int k, int nn) { return sK[k * ldk + nn]; };
         // rows of dA, dX (lower: k <= m) ...
-        rgemm2<2>(rowA, rowX, m0, n0, 0, m0 + 16, [&](int m, int k) { return sA[m * lda + k]; },
-                  [&](int m, int k) { return sX[m * lda + k]; }, bK, lane);
+        rgemm2_p<2>(rowA, rowX, m0, n0, 0, m0 + 16, [&](int m, int k) { return ld2(sA + m * lda + k); },
+                    [&](int m, int k) { return ld2(sX + m * lda + k); },
+                    [&](int k, int nn) { return make_float2(sK[k * ldk + nn], sK[(k + 1) * ldk + nn]); }, lane);
         // ... and their columns (k >= m)
         rgemm<2>(colX, m0, n0, m0, C, [&](int m, int k) { return sX[k * lda + m]; }, bK, lane);
         rgemm<2>(colA, m0, n0, m0, C, [&](int m, int k) { return sA[k * lda + m]; },
-                 [&](int k, int nn) { return sQ[k * ldk + nn]; }, lane);
+                 [&](int k, int nn) { return sQ[k * ldq + nn]; }, lane);
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int i = m0 + g + (e >> 1) * 8, kk = n0 + 8 * nt + 2 * t + (e & 1);
             const float eg = sEG[i], el = sWd[i];
-            const float qh = sQ[i * ldk + kk], kh = sK[i * ldk + kk];
+            const float qh = sQ[i * ldq + kk], kh = sK[i * ldk + kk];
             const float dq = dQg[nt][e] * eg + rowA[nt][e];
             const float dk_row = -dKg[nt][e] * sBeta[i] * eg + rowX[nt][e];
             const float dk_col = dKt[nt][e] * el + colA[nt][e] + colX[nt][e];
@@ -789,7 +737,7 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
             }
             for (int i2 = i; i2 < C; ++i2) {
               const float e = __expf(fminf(sG[i2 * ldk + kk] - gi, 0.f));
-              colA += sA[i2 * lda + i] * e * sQ[i2 * ldk + kk];
+              colA += sA[i2 * lda + i] * e * sQ[i2 * ldq + kk];
               colX += sX[i2 * lda + i] * e * sK[i2 * ldk + kk];
             }
           } else {
@@ -799,13 +747,13 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
               rowX += sX[i * lda + j] * kj;
             }
             for (int i2 = i; i2 < C; ++i2) {
-              colA += sA[i2 * lda + i] * sQ[i2 * ldk + kk];
+              colA += sA[i2 * lda + i] * sQ[i2 * ldq + kk];
               colX += sX[i2 * lda + i] * sK[i2 * ldk + kk];
             }
           }
           const float eg = KDA ? __expf(sG[i * ldk + kk]) : sEG[i];
           const float el = KDA ? __expf(fminf(sG[(C - 1) * ldk + kk] - sG[i * ldk + kk], 0.f)) : sWd[i];
-          const float qh = sQ[i * ldk + kk], kh = sK[i * ldk + kk];
+          const float qh = sQ[i * ldq + kk], kh = sK[i * ldk + kk];
           const float dq = dQg * eg + rowA;
           const float dk_row = dKg * sBeta[i] * eg + rowX;
           const float dk_col = dKt * el + colA + colX;
@@ -841,27 +789,30 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
     BPROF(159);
     // ---- dS0 = (Q^ e^G)^T dO + e^{G_L} dS1 - (beta K^ e^G)^T dR ; dG_L += e^{G_L} <dS1, S0> -------------------------
     if constexpr (TC) {
-      // rows = channels k (panels of 16), columns = the VS value columns; warp w takes panels w, w+8 (K <= 256)
-      constexpr int NT = VS / 8;
+      // rows = channels k (panels of 16), columns = the VS value columns cut into NTW / 2 parts; the warps of one
+      // column part take panels j, j + 8 (K <= 256)
+      constexpr int CP = NTW / 2;            // column parts
+      constexpr int NT = VS / 8 / CP;
+      const int panel = warp / CP, n0 = (warp % CP) * 8 * NT;
       float keep[2][NT][4];
       const int g = lane >> 2, t = lane & 3;
       float tsum = 0.f;
 #pragma unroll
       for (int slot = 0; slot < 2; ++slot) {
-        const int m0 = (warp + 8 * slot) * 16;
+        const int m0 = (panel + 8 * slot) * 16;
         if (m0 < K) {
           float d[NT][4];
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) d[nt][0] = d[nt][1] = d[nt][2] = d[nt][3] = 0.f;
-          rgemm<NT>(d, m0, 0, 0, C, [&](int m, int k) { return sEG[k] * sQ[k * ldk + m]; },
+          rgemm<NT>(d, m0, n0, 0, C, [&](int m, int k) { return sEG[k] * sQ[k * ldq + m]; },
                     [&](int k, int nn) { return sdO[k * ldv + nn]; }, lane);
-          rgemm<NT>(d, m0, 0, 0, C, [&](int m, int k) { return -sEG[k] * sBeta[k] * sK[k * ldk + m]; },
+          rgemm<NT>(d, m0, n0, 0, C, [&](int m, int k) { return -sEG[k] * sBeta[k] * sK[k * ldk + m]; },
                     [&](int k, int nn) { return sdR[k * ldv + nn]; }, lane);
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const int kk = m0 + g + (e >> 1) * 8, vv = 8 * nt + 2 * t + (e & 1);
+              const int kk = m0 + g + (e >> 1) * 8, vv = n0 + 8 * nt + 2 * t + (e & 1);
               const float ds1 = sdS[kk * ldv + vv];
               tsum += ds1 * sS0[kk * ldv + vv] * sEL[kk];
               keep[slot][nt][e] = d[nt][e] + sEL[kk] * ds1;
@@ -873,13 +824,13 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
       __syncthreads();
 #pragma unroll
       for (int slot = 0; slot < 2; ++slot) {
-        const int m0 = (warp + 8 * slot) * 16;
+        const int m0 = (panel + 8 * slot) * 16;
         if (m0 < K) {
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e)
-              sdS[(m0 + g + (e >> 1) * 8) * ldv + 8 * nt + 2 * t + (e & 1)] = keep[slot][nt][e];
+              sdS[(m0 + g + (e >> 1) * 8) * ldv + n0 + 8 * nt + 2 * t + (e & 1)] = keep[slot][nt][e];
         }
       }
     } else {
@@ -892,7 +843,7 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
         float acc = 0.f;
         for (int i = 0; i < C; ++i) {
           const float eg = KDA ? __expf(sG[i * ldk + kk]) : sEG[i];
-          acc += eg * (sQ[i * ldk + kk] * sdO[i * ldv + vv] - sBeta[i] * sK[i * ldk + kk] * sdR[i * ldv + vv]);
+          acc += eg * (sQ[i * ldq + kk] * sdO[i * ldv + vv] - sBeta[i] * sK[i * ldk + kk] * sdR[i * ldv + vv]);
         }
         const float ds1 = sdS[kk * ldv + vv];
         float t = ds1 * sS0[kk * ldv + vv] * sEL[kk];
@@ -915,11 +866,11 @@ __global__ void __launch_bounds__(kBwThreads) bwd_chunk_kernel(const BwdParams p
     }
     }
     BPROF(160);
-    for (int c = tid; c < rows; c += kBwThreads) atomicAdd(p.dbeta + s_base + (t0 + c) * s_tok, sdBeta[c]);
+    for (int c = tid; c < rows; c += NTHR) atomicAdd(p.dbeta + s_base + (t0 + c) * s_tok, sdBeta[c]);
   }
   __syncthreads();
   if (p.dh0) {
-    for (int i = tid; i < K * VS; i += kBwThreads) {
+    for (int i = tid; i < K * VS; i += NTHR) {
       const int kk = i / VS, vv = i % VS;
       if (v0 + vv < V) p.dh0[((int64_t)unit * K + kk) * V + v0 + vv] = sdS[kk * ldv + vv];
     }
@@ -1324,7 +1275,7 @@ inline cudaError_t launch_bwd_adjoint(const DrDesc* d, const void* q, const void
       ++*launches;
       e = cudaFuncSetAttribute(bwd_chunk_kernel<VS, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return e;
-      bwd_chunk_kernel<VS, false, true><<<(unsigned)(units * ((V + VS - 1) / VS)), kBwThreads, smem, stream>>>(p);
+      bwd_chunk_kernel<VS, false, true><<<(unsigned)(units * ((V + VS - 1) / VS)), bwd_threads(true), smem, stream>>>(p);
     } else {
       e = cudaFuncSetAttribute(bwd_chunk_kernel<VS, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return e;
