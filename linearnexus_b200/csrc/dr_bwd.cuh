@@ -275,12 +275,14 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
         }
         tc::cp_async_commit();
       }
-      // beta, g: row warp + NW * lane of the chunk (C = 64)
+      // beta: row warp + NW * lane of the chunk (C = 64); the last warp takes the decay of all 64 rows (two per
+      // lane) and scans it in registers while the other loads are in flight
       constexpr int RPW = 64 / NW;
-      float bt = 0.f, gt_ = 0.f;
-      if (lane < RPW && warp + NW * lane < rows) {
-        bt = p.beta[s_base + (t0 + warp + NW * lane) * s_tok];
-        if (gated) gt_ = ld_elem(p.g, s_base + (t0 + warp + NW * lane) * s_tok, p.g_dt);
+      float bt = 0.f, g_lo = 0.f, g_hi = 0.f;
+      if (lane < RPW && warp + NW * lane < rows) bt = p.beta[s_base + (t0 + warp + NW * lane) * s_tok];
+      if (warp == NW - 1 && gated) {
+        if (lane < rows) g_lo = ld_elem(p.g, s_base + (t0 + lane) * s_tok, p.g_dt);
+        if (lane + 32 < rows) g_hi = ld_elem(p.g, s_base + (t0 + lane + 32) * s_tok, p.g_dt);
       }
       // bf16 v, dO and the fp32 checkpoint slice: 16-byte accesses, every global load issued before the first is used
       uint4 vr = make_uint4(0u, 0u, 0u, 0u), dor = make_uint4(0u, 0u, 0u, 0u);
@@ -304,8 +306,22 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
       if (lane < RPW) {
         const int c = warp + NW * lane;
         sBeta[c] = bt;
-        sGs[c] = gt_;
         sdBeta[c] = 0.f;
+      }
+      if (warp == NW - 1) {
+        // inclusive prefix sums G of the 64 log-decays, then e^G, e^{G_L - G} and e^{G_L}
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const float a = __shfl_up_sync(0xffffffffu, g_lo, o), b2 = __shfl_up_sync(0xffffffffu, g_hi, o);
+          if (lane >= o) { g_lo += a; g_hi += b2; }
+        }
+        g_hi += __shfl_sync(0xffffffffu, g_lo, 31);
+        const float gl = __shfl_sync(0xffffffffu, g_hi, 31);
+        sGs[lane] = g_lo; sGs[lane + 32] = g_hi;
+        sEG[lane] = expf(g_lo); sEG[lane + 32] = expf(g_hi);
+        sWd[lane] = expf(fminf(gl - g_lo, 0.f)); sWd[lane + 32] = expf(fminf(gl - g_hi, 0.f));
+        const float egl = expf(gl);
+        for (int i = lane; i < K; i += 32) sEL[i] = egl;
       }
 #pragma unroll
       for (int it = 0; it < SIT; ++it) {
@@ -388,12 +404,12 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
         }
         sEL[i] = expf(acc);
       }
-    } else if (tid == 0) {
+    } else if (!TC && tid == 0) {
       float acc = 0.f;
       for (int c = 0; c < C; ++c) { acc += sGs[c]; sGs[c] = acc; }
     }
-    __syncthreads();
-    if (!KDA) {
+    if (!TC) __syncthreads();
+    if (!KDA && !TC) {
       const float gl = sGs[C - 1];
       for (int i = tid; i < C; i += NTHR) {
         sEG[i] = expf(sGs[i]);
@@ -659,6 +675,8 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
       const int g = lane >> 2, t = lane & 3;
       const int m0 = (warp / NTW) * 16;
       float dgrow[2] = {0.f, 0.f}, dbrow[2] = {0.f, 0.f}, extra = 0.f;
+      const float row_eg[2] = {sEG[m0 + g], sEG[m0 + g + 8]}, row_el[2] = {sWd[m0 + g], sWd[m0 + g + 8]};
+      const float row_beta[2] = {sBeta[m0 + g], sBeta[m0 + g + 8]};
       for (int n0 = (warp % NTW) * 16; n0 < K; n0 += 16 * NTW) {
         float dQg[2][4], dKg[2][4], dKt[2][4], rowA[2][4], rowX[2][4], colA[2][4], colX[2][4];
 #pragma unroll
@@ -683,19 +701,35 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int i = m0 + g + (e >> 1) * 8, kk = n0 + 8 * nt + 2 * t + (e & 1);
-            const float eg = sEG[i], el = sWd[i];
-            const float qh = sQ[i * ldq + kk], kh = sK[i * ldk + kk];
-            const float dq = dQg[nt][e] * eg + rowA[nt][e];
-            const float dk_row = -dKg[nt][e] * sBeta[i] * eg + rowX[nt][e];
-            const float dk_col = dKt[nt][e] * el + colA[nt][e] + colX[nt][e];
-            dbrow[e >> 1] += -dKg[nt][e] * kh * eg;
-            dgrow[e >> 1] += qh * dq + kh * (dk_row - dk_col);
-            extra += dKt[nt][e] * kh * el;
-            const int64_t arow = acc_row0 + t0 + i;
-            p.dq_acc[slice_off + arow * K + kk] = dq;
-            p.dk_acc[slice_off + arow * K + kk] = dk_row + dk_col;
+          for (int hr = 0; hr < 2; ++hr) {
+            // two adjacent channels of one row: 8-byte accesses
+            const int i = m0 + g + hr * 8, kk = n0 + 8 * nt + 2 * t;
+            const float eg = row_eg[hr], el = row_el[hr], bi = row_beta[hr];
+            const float2 qh = ld2(sQ + i * ldq + kk), kh = ld2(sK + i * ldk + kk);
+            float2 dq, dk;
+            {
+              const int e = 2 * hr;
+              dq.x = dQg[nt][e] * eg + rowA[nt][e];
+              const float dk_row = -dKg[nt][e] * bi * eg + rowX[nt][e];
+              const float dk_col = dKt[nt][e] * el + colA[nt][e] + colX[nt][e];
+              dbrow[hr] += -dKg[nt][e] * kh.x * eg;
+              dgrow[hr] += qh.x * dq.x + kh.x * (dk_row - dk_col);
+              extra += dKt[nt][e] * kh.x * el;
+              dk.x = dk_row + dk_col;
+            }
+            {
+              const int e = 2 * hr + 1;
+              dq.y = dQg[nt][e] * eg + rowA[nt][e];
+              const float dk_row = -dKg[nt][e] * bi * eg + rowX[nt][e];
+              const float dk_col = dKt[nt][e] * el + colA[nt][e] + colX[nt][e];
+              dbrow[hr] += -dKg[nt][e] * kh.y * eg;
+              dgrow[hr] += qh.y * dq.y + kh.y * (dk_row - dk_col);
+              extra += dKt[nt][e] * kh.y * el;
+              dk.y = dk_row + dk_col;
+            }
+            const int64_t at = slice_off + (acc_row0 + t0 + i) * K + kk;
+            *reinterpret_cast<float2*>(p.dq_acc + at) = dq;
+            *reinterpret_cast<float2*>(p.dk_acc + at) = dk;
           }
       }
 #pragma unroll
