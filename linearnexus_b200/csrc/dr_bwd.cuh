@@ -248,6 +248,13 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
     sdS[kk * ldv + vv] = (p.d_hT && v0 + vv < V) ? p.d_hT[((int64_t)unit * K + kk) * V + v0 + vv] : 0.f;
   }
 
+  if constexpr (TC) {
+    // blocks above the diagonal of X, A, T: zero once (the copies below skip them, the dA / dX tiles rewrite zeros)
+    for (int i = tid; i < 64 * 64; i += NTHR) {
+      const int r = i >> 6, c = i & 63;
+      if ((c >> 4) > (r >> 4)) { sX[r * lda + c] = 0.f; sA[r * lda + c] = 0.f; sT[r * ldt + c] = 0.f; }
+    }
+  }
 #ifdef DR_PROFILE
   unsigned long long bp0 = clock64();
 #endif
@@ -261,17 +268,18 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
       {
         // X, A, T of this chunk were computed once for all value slices by bwd_pre_kernel: 16-byte async copies
         // into their arrays (and so were the normalised fp32 rows q^, k^)
+        // (only the 16x16 blocks on and below the diagonal: the others are zero in all three and stay zero here)
         const float* src = p.pre + ((int64_t)unit * N + n) * (3 * 64 * 64 + 2 * 64 * K);
         for (int i = tid; i < 3 * 64 * 16; i += NTHR) {
           const int m = i >> 10, r = (i >> 4) & 63, c4 = (i & 15) * 4;
           float* dst = (m == 0 ? sX + r * lda : m == 1 ? sA + r * lda : sT + r * ldt) + c4;
-          tc::cp_async16(tc::smem_u32(dst), src + m * 4096 + r * 64 + c4, true);
+          if ((c4 >> 4) <= (r >> 4)) tc::cp_async16(tc::smem_u32(dst), src + m * 4096 + r * 64 + c4, true);
         }
-        const float* qsrc = src + 3 * 4096;
-        const int k4 = K >> 2;
-        for (int i = tid; i < 2 * 64 * k4; i += NTHR) {
-          const int m = i / (64 * k4), r = (i / k4) & 63, c4 = (i % k4) * 4;
-          tc::cp_async16(tc::smem_u32((m ? sK + r * ldk : sQ + r * ldq) + c4), qsrc + (m * 64 + r) * K + c4, true);
+        const float* qsrc = src + 3 * 4096;   // a warp per row, 512 bytes per instruction
+        for (int rr = warp; rr < 128; rr += NW) {
+          const int r = rr & 63;
+          float* drow = rr >> 6 ? sK + r * ldk : sQ + r * ldq;
+          for (int c4 = 4 * lane; c4 < K; c4 += 128) tc::cp_async16(tc::smem_u32(drow + c4), qsrc + rr * K + c4, true);
         }
         tc::cp_async_commit();
       }
