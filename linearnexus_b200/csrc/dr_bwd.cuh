@@ -269,18 +269,24 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
         // X, A, T of this chunk were computed once for all value slices by bwd_pre_kernel: 16-byte async copies
         // into their arrays (and so were the normalised fp32 rows q^, k^)
         // (only the 16x16 blocks on and below the diagonal: the others are zero in all three and stay zero here)
+        // Two groups: A, T, k^ are needed from the first product on; X and q^ only by the dA / dX tiles and the
+        // per-channel products, so their copies keep running under the phases before those.
         const float* src = p.pre + ((int64_t)unit * N + n) * (3 * 64 * 64 + 2 * 64 * K);
-        for (int i = tid; i < 3 * 64 * 16; i += NTHR) {
-          const int m = i >> 10, r = (i >> 4) & 63, c4 = (i & 15) * 4;
-          float* dst = (m == 0 ? sX + r * lda : m == 1 ? sA + r * lda : sT + r * ldt) + c4;
+        const float* qsrc = src + 3 * 4096;   // q^, k^: a warp per row, 512 bytes per instruction
+        for (int i = tid; i < 2 * 64 * 16; i += NTHR) {
+          const int m = 1 + (i >> 10), r = (i >> 4) & 63, c4 = (i & 15) * 4;
+          float* dst = (m == 1 ? sA + r * lda : sT + r * ldt) + c4;
           if ((c4 >> 4) <= (r >> 4)) tc::cp_async16(tc::smem_u32(dst), src + m * 4096 + r * 64 + c4, true);
         }
-        const float* qsrc = src + 3 * 4096;   // a warp per row, 512 bytes per instruction
-        for (int rr = warp; rr < 128; rr += NW) {
-          const int r = rr & 63;
-          float* drow = rr >> 6 ? sK + r * ldk : sQ + r * ldq;
-          for (int c4 = 4 * lane; c4 < K; c4 += 128) tc::cp_async16(tc::smem_u32(drow + c4), qsrc + rr * K + c4, true);
+        for (int r = warp; r < 64; r += NW)
+          for (int c4 = 4 * lane; c4 < K; c4 += 128) tc::cp_async16(tc::smem_u32(sK + r * ldk + c4), qsrc + (64 + r) * K + c4, true);
+        tc::cp_async_commit();
+        for (int i = tid; i < 64 * 16; i += NTHR) {
+          const int r = i >> 4, c4 = (i & 15) * 4;
+          if ((c4 >> 4) <= (r >> 4)) tc::cp_async16(tc::smem_u32(sX + r * lda + c4), src + r * 64 + c4, true);
         }
+        for (int r = warp; r < 64; r += NW)
+          for (int c4 = 4 * lane; c4 < K; c4 += 128) tc::cp_async16(tc::smem_u32(sQ + r * ldq + c4), qsrc + r * K + c4, true);
         tc::cp_async_commit();
       }
       // beta: row warp + NW * lane of the chunk (C = 64); the last warp takes the decay of all 64 rows (two per
@@ -400,7 +406,7 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
       }
     }
     }
-    if constexpr (TC) tc::cp_async_wait_all();
+    if constexpr (TC) tc::cp_async_wait_1();   // A, T, k^ have landed; X, q^ may still be in flight
     __syncthreads();
     BPROF(151);
     if (KDA) {
@@ -619,6 +625,7 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
       acc = warp_sum(acc);
       if (lane == 0) sdBeta[c] += acc;
     }
+    if constexpr (TC) tc::cp_async_wait_all();   // X, q^
     __syncthreads();
     if constexpr (TC) {
       {
