@@ -79,7 +79,8 @@ typedef struct DrDesc {
   int32_t qk_heads;      /* heads of q and k when fewer than H (grouped value attention: head h of v, o, g, beta,
                             state uses q/k head h / (H / qk_heads)); 0 or H: one q/k head per head.  Replaces the
                             jnp.repeat of q, k before the op (gated_deltanet.py:798-801, kda.py:917-922).
-                            Forward entry points only. */
+                            Backward entry points: dq, dk have qk_heads heads and hold the sum over each group
+                            (the transpose of that repeat). */
   int32_t reserved;      /* must be zero */
 } DrDesc;
 

@@ -261,7 +261,6 @@ int dr_chunk_bwd(const DrDesc* d, const void* q, const void* k, const void* v, c
   int s = validate_common(d, true);
   if (s != DR_OK) return s;
   if (!q || !k || !v || !beta || !d_o || !dq || !dk || !dv || !dbeta) return DR_ERR_NULL;
-  if (d->qk_heads > 0 && d->qk_heads != d->H) return DR_ERR_UNSUPPORTED;   // the backward wants q,k per value head
   if (d->variant == DR_DELTA ? (g != nullptr || dg != nullptr) : (g == nullptr || dg == nullptr))
     return DR_ERR_VARIANT;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(d_o) || !aligned16(dq) ||
@@ -286,7 +285,6 @@ int dr_chunk_fwd_saving(const DrDesc* d, const void* q, const void* k, const voi
   if (s != DR_OK) return s;
   s = validate_fwd_ptrs(d, q, k, v, g, beta, h0, o, hT);
   if (s != DR_OK) return s;
-  if (d->qk_heads > 0 && d->qk_heads != d->H) return DR_ERR_UNSUPPORTED;
   const int64_t need = dr::bwd_workspace_bytes(d);
   if (need < 0) return (int)need;
   if (!workspace || (int64_t)workspace_bytes < need) return DR_ERR_WORKSPACE;
@@ -307,7 +305,6 @@ int dr_chunk_bwd_saved(const DrDesc* d, const void* q, const void* k, const void
   int s = validate_common(d, true);
   if (s != DR_OK) return s;
   if (!q || !k || !v || !beta || !d_o || !dq || !dk || !dv || !dbeta) return DR_ERR_NULL;
-  if (d->qk_heads > 0 && d->qk_heads != d->H) return DR_ERR_UNSUPPORTED;
   if (d->variant == DR_DELTA ? (g != nullptr || dg != nullptr) : (g == nullptr || dg == nullptr))
     return DR_ERR_VARIANT;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(d_o) || !aligned16(dq) ||
@@ -361,7 +358,6 @@ int dr_chunk_bwd_static(const DrDesc* d, const void* q, const void* k, const voi
   int s = validate_common(d, true);
   if (s != DR_OK) return s;
   if (!q || !k || !v || !beta || !d_o || !dq || !dk || !dv || !dbeta) return DR_ERR_NULL;
-  if (d->qk_heads > 0 && d->qk_heads != d->H) return DR_ERR_UNSUPPORTED;   // the backward wants q,k per value head
   if (d->variant == DR_DELTA ? (g != nullptr || dg != nullptr) : (g == nullptr || dg == nullptr))
     return DR_ERR_VARIANT;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(d_o) || !aligned16(dq) ||

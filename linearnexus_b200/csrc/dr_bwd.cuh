@@ -235,7 +235,8 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
   const int unit = blockIdx.x / nvs;
   const int v0 = (blockIdx.x % nvs) * VS;
   const int b = unit / p.map.H, h = unit % p.map.H;
-  const int64_t qk_base = p.map.base(b, h, K), qk_tok = p.map.tok(K);
+  const int64_t qk_base = p.map.base_qk(b, h, K), qk_tok = p.map.tok_qk(K);   // q, k: head h / (H / Hq)
+  const int64_t gk_base = p.map.base(b, h, K), gk_tok = p.map.tok(K);          // per-channel decay: per value head
   const int64_t v_base = p.map.base(b, h, V), v_tok = p.map.tok(V);
   const int64_t s_base = p.map.base(b, h, 1), s_tok = p.map.tok(1);
   const int64_t acc_row0 = (int64_t)unit * N * C;  // first row of this unit in the [.., N*C, ..] accumulators
@@ -362,7 +363,7 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
         if (live) {
           qv = ld_elem(p.q, qk_base + (t0 + c) * qk_tok + i, p.qkv_dt);
           kv = ld_elem(p.k, qk_base + (t0 + c) * qk_tok + i, p.qkv_dt);
-          if (KDA) gv = ld_elem(p.g, qk_base + (t0 + c) * qk_tok + i, p.g_dt);
+          if (KDA) gv = ld_elem(p.g, gk_base + (t0 + c) * gk_tok + i, p.g_dt);
         }
         sQ[c * ldq + i] = qv;
         sK[c * ldk + i] = kv;
@@ -948,7 +949,7 @@ __global__ void __launch_bounds__(kBwThreads, 2) bwd_pre_kernel(const BwdParams 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int unit = blockIdx.x / N, n = blockIdx.x % N;
   const int b = unit / p.map.H, h = unit % p.map.H;
-  const int64_t qk_base = p.map.base(b, h, K), qk_tok = p.map.tok(K);
+  const int64_t qk_base = p.map.base_qk(b, h, K), qk_tok = p.map.tok_qk(K);
   const int64_t s_base = p.map.base(b, h, 1), s_tok = p.map.tok(1);
   const bool gated = p.variant == DR_GATED;
   const int t0 = n * C, rows = min(C, T - t0);
@@ -1106,19 +1107,28 @@ struct BwdFinalParams {
   float scale;
 };
 
-// One CTA per (unit, chunk): normalisation/scale chain rule per row, reverse cumulative sum of dG.
+// One CTA per (unit, chunk): sum of the partial copies, normalisation/scale chain rule per row, reverse
+// cumulative sum of dG.
 __global__ void __launch_bounds__(256) bwd_finalize_kernel(const BwdFinalParams p) {
   const int K = p.K, C = p.C, N = p.N, T = p.map.T;
   const int unit = blockIdx.x / N, n = blockIdx.x % N;
   const int b = unit / p.map.H, h = unit % p.map.H;
   const int t0 = n * C, rows = min(C, T - t0);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t qk_base = p.map.base(b, h, K), qk_tok = p.map.tok(K);
+  const int64_t qk_base = p.map.base_qk(b, h, K), qk_tok = p.map.tok_qk(K);
+  const int64_t gk_base = p.map.base(b, h, K), gk_tok = p.map.tok(K);
   const int64_t s_base = p.map.base(b, h, 1), s_tok = p.map.tok(1);
   const int64_t acc_row0 = (int64_t)unit * N * C + t0;
+  // Grouped value attention: the G = H / Hq value heads of a group share one q/k head, whose gradient is the sum
+  // over the group.  The CTA of the group's first head adds all G x nvs partial copies (the chain rule of the
+  // normalisation is linear in them); the others only have their dg to do.
+  const int G = p.map.H / p.map.Hq;
+  const int ncopies = G * p.nvs;
+  const int64_t head_stride = (int64_t)N * C * K;   // floats between the accumulator rows of consecutive heads
+  auto copy_off = [&](int ci) -> int64_t { return (int64_t)(ci / p.nvs) * head_stride + (int64_t)(ci % p.nvs) * p.slice_stride; };
   // lane = four consecutive channels (two groups of 128 channels for K > 128): 16-byte loads of the slice
   // partials, all of a row's loads issued before the first sum
-  for (int c = warp; c < rows; c += 8) {
+  for (int c = warp; c < ((h % G) == 0 ? rows : 0); c += 8) {
     const float* aq0 = p.dq_acc + (acc_row0 + c) * K;
     const float* ak0 = p.dk_acc + (acc_row0 + c) * K;
     const int64_t grow = qk_base + (t0 + c) * qk_tok;
@@ -1130,17 +1140,17 @@ __global__ void __launch_bounds__(256) bwd_finalize_kernel(const BwdFinalParams 
 #pragma unroll
       for (int e = 0; e < 4; ++e) { aq[s2][e] = 0.f; ak[s2][e] = 0.f; qv[s2][e] = 0.f; kv[s2][e] = 0.f; }
       if (i < K) {
-        float4 xq[8], xk[8];   // up to eight value slices (V <= 256 in 32-column slices)
+        float4 xq[8], xk[8];   // the first eight copies in flight together (V <= 256 in 32-column slices, one head)
 #pragma unroll
         for (int sl = 0; sl < 8; ++sl) {
-          if (sl < p.nvs) {
-            xq[sl] = *reinterpret_cast<const float4*>(aq0 + sl * p.slice_stride + i);
-            xk[sl] = *reinterpret_cast<const float4*>(ak0 + sl * p.slice_stride + i);
+          if (sl < ncopies) {
+            xq[sl] = *reinterpret_cast<const float4*>(aq0 + copy_off(sl) + i);
+            xk[sl] = *reinterpret_cast<const float4*>(ak0 + copy_off(sl) + i);
           }
         }
-        for (int sl = 8; sl < p.nvs; ++sl) {   // (16-column slices of the per-channel-decay variant)
-          const float4 a = *reinterpret_cast<const float4*>(aq0 + sl * p.slice_stride + i);
-          const float4 bq = *reinterpret_cast<const float4*>(ak0 + sl * p.slice_stride + i);
+        for (int sl = 8; sl < ncopies; ++sl) {   // (16-column slices of the per-channel-decay variant; head groups)
+          const float4 a = *reinterpret_cast<const float4*>(aq0 + copy_off(sl) + i);
+          const float4 bq = *reinterpret_cast<const float4*>(ak0 + copy_off(sl) + i);
           aq[s2][0] += a.x; aq[s2][1] += a.y; aq[s2][2] += a.z; aq[s2][3] += a.w;
           ak[s2][0] += bq.x; ak[s2][1] += bq.y; ak[s2][2] += bq.z; ak[s2][3] += bq.w;
         }
@@ -1151,7 +1161,7 @@ __global__ void __launch_bounds__(256) bwd_finalize_kernel(const BwdFinalParams 
         }
 #pragma unroll
         for (int sl = 0; sl < 8; ++sl) {
-          if (sl < p.nvs) {
+          if (sl < ncopies) {
             aq[s2][0] += xq[sl].x; aq[s2][1] += xq[sl].y; aq[s2][2] += xq[sl].z; aq[s2][3] += xq[sl].w;
             ak[s2][0] += xk[sl].x; ak[s2][1] += xk[sl].y; ak[s2][2] += xk[sl].z; ak[s2][3] += xk[sl].w;
           }
@@ -1204,7 +1214,7 @@ __global__ void __launch_bounds__(256) bwd_finalize_kernel(const BwdFinalParams 
       float acc = 0.f;
       for (int c = C - 1; c >= 0; --c) {
         acc += p.dg_acc[(acc_row0 + c) * K + i];
-        if (c < rows) p.dg[qk_base + (t0 + c) * qk_tok + i] = acc;
+        if (c < rows) p.dg[gk_base + (t0 + c) * gk_tok + i] = acc;
       }
     }
   }
@@ -1247,7 +1257,7 @@ inline cudaError_t launch_bwd_forward(const DrDesc* d, const void* q, const void
   f.q = q; f.k = k; f.v = v; f.g = g; f.beta = beta; f.h0 = h0; f.o = o; f.hT = hT; f.status = nullptr;
   f.ckpt = ckpt;
   f.map.B = d->B; f.map.H = d->H; f.map.T = d->T; f.map.bthd = d->layout == DR_LAYOUT_BTHD;
-  f.map.Hq = d->H;
+  f.map.Hq = d->qk_heads > 0 ? d->qk_heads : d->H;
   f.K = K; f.V = V; f.C = C;
   f.variant = d->variant; f.qkv_dt = d->qkv_dtype; f.g_dt = d->g_dtype; f.out_dt = o ? d->out_dtype : d->qkv_dtype;
   f.l2norm = d->use_qk_l2norm; f.scale = d->scale;
@@ -1293,7 +1303,8 @@ inline cudaError_t launch_bwd_adjoint(const DrDesc* d, const void* q, const void
   e = cudaMemsetAsync(dbeta, 0, nbeta * sizeof(float), stream);
   if (e != cudaSuccess) return e;
   SeqMap map;
-  map.B = d->B; map.H = d->H; map.T = d->T; map.bthd = d->layout == DR_LAYOUT_BTHD; map.Hq = d->H;
+  map.B = d->B; map.H = d->H; map.T = d->T; map.bthd = d->layout == DR_LAYOUT_BTHD;
+  map.Hq = d->qk_heads > 0 ? d->qk_heads : d->H;
   // (2) adjoint
   BwdParams p;
   p.q = q; p.k = k; p.v = v; p.g = g; p.beta = beta; p.d_o = d_o; p.d_hT = d_hT;

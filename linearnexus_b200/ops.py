@@ -269,8 +269,11 @@ _VARIANTS = {"delta": DR_DELTA, "gated": DR_GATED, "kda": DR_KDA}
 def _train_prep(variant, q, k, v, g, beta, initial_state, scale, chunk_size, use_qk_l2norm, out_dtype=None):
     """Common argument handling of the backward-related entry points ([B,H,T,D] contiguous copies)."""
     var = _VARIANTS[variant]
-    B, H, T, K = q.shape
-    V = v.shape[-1]
+    B, Hq, T, K = q.shape
+    H, V = v.shape[1], v.shape[-1]   # Hq < H: grouped value attention (dq, dk come back summed over each group)
+    if k.shape != q.shape or H % Hq:
+        raise ValueError("expected q,k [B,Hq,T,K] and v [B,H,T,V] with H a multiple of Hq; got "
+                         f"{tuple(q.shape)}, {tuple(k.shape)}, {tuple(v.shape)}")
     if scale is None:
         scale = K ** -0.5
     if beta.dim() == 4:
@@ -283,6 +286,7 @@ def _train_prep(variant, q, k, v, g, beta, initial_state, scale, chunk_size, use
     h0 = _state(initial_state, B, H, K, V, dev)
     d = _desc(var, DR_LAYOUT_BHTD, B, H, T, K, V, chunk_size, qn, gn, common if out_dtype is None else out_dtype,
               use_qk_l2norm, scale)
+    d.qk_heads = Hq
     lib = _lib.load()
     need = lib.dr_workspace_bytes(ctypes.byref(d), 1)
     if need == -7:
@@ -315,7 +319,8 @@ def chunk_forward_saving(variant, q, k, v, g, beta, initial_state=None, scale=No
 def chunk_backward(variant, q, k, v, g, beta, d_o, initial_state=None, d_final_state=None, scale=None,
                    chunk_size=64, use_qk_l2norm=True, saved=None):
     """Gradients of sum(o * d_o) + sum(final_state * d_final_state) for ``variant`` in
-    {"delta", "gated", "kda"}.  Returns a dict: dq, dk [like q], dv [like v] in the q/k/v dtype;
+    {"delta", "gated", "kda"}.  Returns a dict: dq, dk [like q: with grouped q/k heads, summed over each
+    group's value heads], dv [like v] in the q/k/v dtype;
     dbeta float32 [B,H,T]; dg float32 [like g] (None for "delta"); dh0 float32 [B,H,K,V].
     ``saved``: the third result of ``chunk_forward_saving`` on the same inputs (skips the forward recomputation;
     the buffer is consumed)."""
@@ -352,7 +357,7 @@ class _ChunkFn(torch.autograd.Function):
     def forward(ctx, variant, q, k, v, g, beta, initial_state, scale, chunk_size, l2norm, out_dtype, path):
         saved = None
         with torch.no_grad():
-            if path is None and q.shape[1] == v.shape[1]:
+            if path is None:
                 o, hT, saved = chunk_forward_saving(variant, q, k, v, g, beta, initial_state, scale, chunk_size,
                                                     l2norm, out_dtype)
             else:

@@ -81,3 +81,52 @@ def test_grouped_heads_rejected_where_unsupported():
     cu, q, k, qr, kr = _inputs("gated", 1, 1, 2, 64, 128, 128, torch.bfloat16)
     with pytest.raises(ValueError):
         L.gated_delta_rule_chunkwise(torch.cat([q, q, q], 1), torch.cat([k, k, k], 1), cu["v"], cu["g"], cu["beta"])  # 2 % 3
+
+
+@pytest.mark.parametrize("variant,dtype,K", [
+    ("gated", torch.bfloat16, 128), ("delta", torch.bfloat16, 128), ("kda", torch.bfloat16, 128),
+    ("gated", torch.float32, 64), ("kda", torch.float32, 32), ("delta", torch.float32, 64)])
+@pytest.mark.parametrize("saving", [False, True])
+def test_chunk_backward_grouped_heads(variant, dtype, K, saving):
+    """dq, dk of a shared q/k head are the sums over its group of the gradients the op gives on repeated
+    tensors; dv, dbeta, dg, dh0 (per value head) are those gradients themselves."""
+    B, Hq, H, T = 2, 2, 6, 200
+    rep = H // Hq
+    cu, q, k, qr, kr = _inputs(variant, B, Hq, H, T, K, K, dtype)
+    gen = torch.Generator().manual_seed(11)
+    d_o = (torch.randn(B, H, T, K, generator=gen) * 0.1).to(dtype).cuda()
+    d_hT = (torch.randn(B, H, K, K, generator=gen) * 0.1).cuda()
+    g = cu["g"]
+
+    def run(qq, kk):
+        saved = None
+        if saving:
+            *_, saved = L.ops.chunk_forward_saving(variant, qq, kk, cu["v"], g, cu["beta"], cu["h0"])
+        return L.ops.chunk_backward(variant, qq, kk, cu["v"], g, cu["beta"], d_o, cu["h0"], d_hT, saved=saved)
+    a, b = run(q, k), run(qr, kr)
+    assert a["dq"].shape == q.shape and a["dk"].shape == k.shape
+    # bf16 results are rounded per head before the reference sum and after it in the grouped call
+    tol = 1e-5 if dtype == torch.float32 else 1.5e-2
+    for name in ("dq", "dk"):
+        ref = b[name].float().view(B, Hq, rep, T, K).sum(2)
+        err = (a[name].float() - ref).abs().max() / ref.abs().max()
+        assert err <= tol, (name, float(err))
+    for name in ("dv", "dbeta", "dg", "dh0"):
+        if a[name] is None:
+            assert b[name] is None
+            continue
+        ref = b[name].float()
+        err = (a[name].float() - ref).abs().max() / ref.abs().max().clamp_min(1e-30)
+        assert err <= 1e-5, (name, float(err))
+
+
+def test_autograd_grouped_heads():
+    """loss.backward() through the op with Hq < H: one saving forward, gradients of the shape of q and k."""
+    B, Hq, H, T, K = 1, 2, 4, 192, 128
+    cu, q, k, qr, kr = _inputs("gated", B, Hq, H, T, K, K, torch.bfloat16)
+    q.requires_grad_(True); k.requires_grad_(True)
+    v = cu["v"].clone().requires_grad_(True)
+    o, hT = L.gated_delta_rule_chunkwise(q, k, v, cu["g"], cu["beta"], initial_state=cu["h0"])
+    (o.float().square().mean() + hT.square().mean()).backward()
+    assert q.grad.shape == q.shape and k.grad.shape == k.shape and v.grad.shape == v.shape
+    assert torch.isfinite(q.grad.float()).all() and q.grad.float().abs().max() > 0
