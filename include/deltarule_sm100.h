@@ -204,6 +204,35 @@ int dr_chunk_bwd_static(const DrDesc* desc, const void* q, const void* k, const 
                         void* stream);
 
 /*
+ * The element-wise steps of a block next to the op, one HBM pass each, in the token-major layout the op reads
+ * with DR_LAYOUT_BTHD (so the block needs no transposes around it).  dtype tags are DrDtype.
+ *
+ * dr_short_conv_silu -- depthwise_conv1d_causal (core/conv.py:13-68) followed by jax.nn.silu
+ *   (gated_deltanet.py:764-783).  x, y [B,T,C]; weight float32 [W,C] (w[W-1] meets the current step); bias
+ *   float32 [C] or null; cache_in [B,W-1,C] (null: zeros); cache_out [B,W-1,C] (null: not wanted) = the last W-1
+ *   rows of concat(cache_in, x).  W in 1..8; W == 1 returns x (+ bias) as the reference does, weight unused.
+ *   C a multiple of 16 bytes of elements.  y must not be x; cache_out may be cache_in only for T <= 32 (decode).
+ *   apply_silu 0 leaves the convolution output as is.
+ *
+ * dr_gate_activations -- mode 0: g = -exp(A_log[h]) softplus(a + bias[h]), beta = beta_scale sigmoid(b) with
+ *   a, b [B,T,H] (gated_deltanet.py:804-815; beta_scale 2 for allow_neg_eigval), K = 1.  mode 1 (kda_gate,
+ *   kda.py:120-172): a [B,T,H,K] (+ bias [H*K] or null), g = -exp(A_log[h]) (x > threshold ? x : softplus(x)),
+ *   beta = beta_scale sigmoid(b), b [B,T,H].  b and beta may both be null.  g, beta float32, token-major.
+ *
+ * dr_gated_rmsnorm -- y[b,t,h,:] = o / sqrt(mean(o^2) + eps) * weight * sigmoid(gate[b,t,h,:]) (RMSNorm
+ *   common.py:42-53 with the gate of gated_deltanet.py:853-865; FusedRMSNormGated kda.py:664-700).  o in
+ *   o_layout ([B,H,T,V] as the op writes it, or [B,T,H,V]); gate [B,T,H,V] or null (plain o_norm); weight
+ *   float32 [V]; y [B,T,H,V].  V a multiple of 4, at most 512.
+ */
+int dr_short_conv_silu(const void* x, const float* weight, const float* bias, const void* cache_in, void* y,
+                       void* cache_out, int B, int T, int C, int W, int dtype, int apply_silu, void* stream);
+int dr_gate_activations(int mode, const void* a, const void* b, const float* A_log, const float* bias, float* g,
+                        float* beta, int B, int T, int H, int K, int a_dtype, int b_dtype, float beta_scale,
+                        float threshold, void* stream);
+int dr_gated_rmsnorm(const void* o, const void* gate, const float* weight, void* y, int B, int H, int T, int V,
+                     int o_layout, int o_dtype, int gate_dtype, int y_dtype, float eps, void* stream);
+
+/*
  * Debug entry with no counterpart in the reference: runs one 128 x n x kd bf16 product
  * D = A * B^T through the tcgen05/TMEM plumbing the chunk kernel uses (A [128][kd] row-major
  * read from shared memory or staged in tensor memory; B given as [n][kd] (K-major) or as

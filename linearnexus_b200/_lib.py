@@ -18,8 +18,7 @@ _ROOT = _PKG.parent
 # DELTARULE_SM100_LIB points the loader at another build of the same library (profiling builds).
 LIB_PATH = Path(os.environ.get("DELTARULE_SM100_LIB", _PKG / "libdeltarule_sm100.so"))
 _SOURCES = ["dr_api.cu"]
-_HEADERS = ["dr_common.cuh", "dr_step.cuh", "dr_recurrent.cuh", "dr_chunk_fp32.cuh",
-            "dr_chunk_sm100.cuh", "dr_bwd.cuh", "dr_tcgen05.cuh", "dr_umma_selftest.cuh"]
+_HEADERS = sorted(f.name for f in (_PKG / "csrc").glob("*.cuh"))
 
 # DrVariant / DrDtype / DrLayout / DrChunkPath (include/deltarule_sm100.h)
 DR_DELTA, DR_GATED, DR_KDA = 0, 1, 2
@@ -29,7 +28,8 @@ DR_PATH_AUTO, DR_PATH_FP32, DR_PATH_TCGEN05, DR_PATH_SPLIT = 0, 1, 2, 3
 
 EXPORTS = ["dr_version", "dr_strerror", "dr_last_cuda_error", "dr_launch_count", "dr_last_path",
            "dr_workspace_bytes", "dr_chunk_fwd", "dr_recurrent_fwd", "dr_step", "dr_chunk_bwd",
-           "dr_debug_umma_selftest", "dr_chunk_bwd_static", "dr_chunk_fwd_saving", "dr_chunk_bwd_saved"]
+           "dr_debug_umma_selftest", "dr_chunk_bwd_static", "dr_chunk_fwd_saving", "dr_chunk_bwd_saved",
+           "dr_short_conv_silu", "dr_gate_activations", "dr_gated_rmsnorm"]
 
 
 class DrDesc(ctypes.Structure):
@@ -124,6 +124,13 @@ def load() -> ctypes.CDLL:
         lib.dr_chunk_bwd_saved.restype = ctypes.c_int
         lib.dr_chunk_bwd_saved.argtypes = [dp, vp, vp, vp, vp, fp, vp, fp, vp, vp, vp, fp, fp, fp, vp,
                                            ctypes.c_size_t, ip, vp]
+        ci, cf = ctypes.c_int, ctypes.c_float
+        lib.dr_short_conv_silu.restype = ctypes.c_int
+        lib.dr_short_conv_silu.argtypes = [vp, fp, fp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp]
+        lib.dr_gate_activations.restype = ctypes.c_int
+        lib.dr_gate_activations.argtypes = [ci, vp, vp, fp, fp, fp, fp, ci, ci, ci, ci, ci, ci, cf, cf, vp]
+        lib.dr_gated_rmsnorm.restype = ctypes.c_int
+        lib.dr_gated_rmsnorm.argtypes = [vp, vp, fp, vp, ci, ci, ci, ci, ci, ci, ci, ci, cf, vp]
         lib.dr_debug_umma_selftest.restype = ctypes.c_int
         lib.dr_debug_umma_selftest.argtypes = [vp, vp, fp, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ip, vp]
         _lib = lib

@@ -11,6 +11,7 @@
 #include "dr_kda_sm100.cuh"
 #include "dr_step_stream.cuh"
 #include "dr_bwd.cuh"
+#include "dr_block_ops.cuh"
 #include "dr_common.cuh"
 #include "dr_recurrent.cuh"
 #include "dr_step.cuh"
@@ -376,6 +377,67 @@ int dr_chunk_bwd_static(const DrDesc* d, const void* q, const void* k, const voi
   cudaError_t e = dr::launch_bwd(d, q, k, v, g, beta, h0, d_o, d_hT, dq, dk, dv, dbeta, dg, dh0, scratch,
                                  reinterpret_cast<cudaStream_t>(stream), &launches);
   g_launches.fetch_add(launches);
+  return check_cuda(e);
+}
+
+int dr_short_conv_silu(const void* x, const float* weight, const float* bias, const void* cache_in, void* y,
+                       void* cache_out, int B, int T, int C, int W, int dtype, int apply_silu, void* stream) {
+  if (!x || !y || (W > 1 && !weight)) return DR_ERR_NULL;
+  if (dtype != DR_F32 && dtype != DR_BF16) return DR_ERR_DTYPE;
+  const int n = dtype == DR_BF16 ? 8 : 4;
+  if (B < 1 || T < 1 || C < 1 || W < 1 || W > dr::blk::kConvMaxW || C % n) return DR_ERR_SHAPE;
+  if (B > 65535) return DR_ERR_SHAPE;
+  if (!aligned16(x) || !aligned16(y) || (cache_in && !aligned16(cache_in)) || (cache_out && !aligned16(cache_out)))
+    return DR_ERR_ALIGN;
+  if (x == y) return DR_ERR_UNSUPPORTED;   // a tile reads the rows before it: not in place
+  if (cache_out && cache_out == cache_in && T > dr::blk::kConvTile) return DR_ERR_UNSUPPORTED;
+  dr::blk::ConvParams p;
+  p.x = x; p.w = weight; p.bias = bias; p.cache_in = W > 1 ? cache_in : nullptr; p.y = y;
+  p.cache_out = W > 1 ? cache_out : nullptr;
+  p.B = B; p.T = T; p.C = C; p.W = W; p.apply_silu = apply_silu;
+  tl_path = "short_conv";
+  cudaError_t e = dr::blk::launch_short_conv(p, dtype, reinterpret_cast<cudaStream_t>(stream));
+  g_launches.fetch_add(1);
+  return check_cuda(e);
+}
+
+int dr_gate_activations(int mode, const void* a, const void* b, const float* A_log, const float* bias, float* g,
+                        float* beta, int B, int T, int H, int K, int a_dtype, int b_dtype, float beta_scale,
+                        float threshold, void* stream) {
+  if (!a || !A_log || !g || ((b == nullptr) != (beta == nullptr))) return DR_ERR_NULL;
+  if (mode != 0 && mode != 1) return DR_ERR_VARIANT;
+  if ((a_dtype != DR_F32 && a_dtype != DR_BF16) || (b && b_dtype != DR_F32 && b_dtype != DR_BF16)) return DR_ERR_DTYPE;
+  if (B < 1 || T < 1 || H < 1 || K < 1 || (mode == 0 && K != 1)) return DR_ERR_SHAPE;
+  dr::blk::GateParams p;
+  p.a = a; p.b = b; p.A_log = A_log; p.bias = bias; p.g = g; p.beta = beta;
+  p.n_beta = b ? (int64_t)B * T * H : 0;
+  p.n_g = (int64_t)B * T * H * K;
+  p.H = H; p.K = K; p.a_dt = a_dtype; p.b_dt = b_dtype; p.mode = mode;
+  p.beta_scale = beta_scale; p.threshold = threshold;
+  tl_path = "gate_activations";
+  cudaError_t e = dr::blk::launch_gate_act(p, reinterpret_cast<cudaStream_t>(stream));
+  g_launches.fetch_add(1);
+  return check_cuda(e);
+}
+
+int dr_gated_rmsnorm(const void* o, const void* gate, const float* weight, void* y, int B, int H, int T, int V,
+                     int o_layout, int o_dtype, int gate_dtype, int y_dtype, float eps, void* stream) {
+  if (!o || !weight || !y) return DR_ERR_NULL;
+  if (o_layout != DR_LAYOUT_BHTD && o_layout != DR_LAYOUT_BTHD) return DR_ERR_SHAPE;
+  if ((o_dtype != DR_F32 && o_dtype != DR_BF16) || (y_dtype != DR_F32 && y_dtype != DR_BF16) ||
+      (gate && gate_dtype != DR_F32 && gate_dtype != DR_BF16))
+    return DR_ERR_DTYPE;
+  if (B < 1 || H < 1 || T < 1 || V < 4 || V > 512 || V % 4) return DR_ERR_SHAPE;
+  if (!aligned16(o) || !aligned16(y) || !aligned16(weight) || (gate && !aligned16(gate))) return DR_ERR_ALIGN;
+  if (o == y && o_layout != DR_LAYOUT_BTHD) return DR_ERR_UNSUPPORTED;
+  dr::blk::NormParams p;
+  p.o = o; p.gate = gate; p.w = weight; p.y = y;
+  p.map.B = B; p.map.H = H; p.map.T = T; p.map.bthd = o_layout == DR_LAYOUT_BTHD; p.map.Hq = H;
+  p.V = V; p.eps = eps;
+  tl_path = "gated_rmsnorm";
+  cudaError_t e = dr::blk::launch_gated_rmsnorm(p, o_dtype, gate ? gate_dtype : o_dtype, y_dtype,
+                                                reinterpret_cast<cudaStream_t>(stream));
+  g_launches.fetch_add(1);
   return check_cuda(e);
 }
 

@@ -129,3 +129,22 @@ def test_host_pipeline_argument_checks_need_no_gpu():
     host_pipeline._pinned(None, "g")
     with pytest.raises(ValueError):
         host_pipeline._pinned(torch.zeros(4), "q")          # pageable host memory
+
+
+def test_block_op_entry_points_validate_on_the_host():
+    """Bad arguments of the conv / gate / norm entry points are refused before any CUDA call."""
+    lib = _lib.load()
+    buf = ctypes.create_string_buffer(256)
+    p = ctypes.cast(buf, ctypes.c_void_p)
+    al = ctypes.c_void_p((p.value + 15) & ~15)
+    assert lib.dr_short_conv_silu(None, al, None, None, al, None, 1, 1, 8, 4, 1, 1, None) == -1
+    assert lib.dr_short_conv_silu(al, al, None, None, ctypes.c_void_p(al.value + 16), None, 1, 1, 12, 4, 1, 1, None) == -2
+    assert lib.dr_short_conv_silu(al, al, None, None, ctypes.c_void_p(al.value + 16), None, 1, 1, 8, 9, 1, 1, None) == -2
+    assert lib.dr_short_conv_silu(al, al, None, None, al, None, 1, 1, 8, 4, 1, 1, None) == -9      # in place
+    assert lib.dr_short_conv_silu(al, al, None, None, ctypes.c_void_p(al.value + 8), None, 1, 1, 8, 4, 1, 1, None) == -4
+    assert lib.dr_gate_activations(2, al, None, al, None, al, None, 1, 1, 1, 1, 0, 0, 1.0, 20.0, None) == -6
+    assert lib.dr_gate_activations(0, al, None, al, None, al, None, 1, 1, 1, 4, 0, 0, 1.0, 20.0, None) == -2
+    assert lib.dr_gate_activations(0, al, al, al, None, al, None, 1, 1, 1, 1, 0, 0, 1.0, 20.0, None) == -1
+    assert lib.dr_gated_rmsnorm(al, None, al, al, 1, 1, 1, 6, 0, 0, 0, 0, 1e-6, None) == -2
+    assert lib.dr_gated_rmsnorm(al, None, al, al, 1, 1, 1, 8, 0, 7, 0, 0, 1e-6, None) == -3
+    assert lib.dr_gated_rmsnorm(al, None, al, al, 1, 1, 1, 8, 0, 0, 0, 0, 1e-6, None) == -9        # in place, transposing

@@ -151,3 +151,31 @@ def test_oracle_grads_against_golden(golden, name):
     for key in ("dq", "dk", "dv", "dg", "dbeta", "dh0"):
         if G(key) is not None:
             assert (gr[key] - G(key)).abs().max() < 1e-9, key
+
+
+def test_block_ops_oracle_against_torch_primitives():
+    """The restated conv / norm against torch's own conv1d and a direct formula; kernel_size 1 returns the input."""
+    import torch.nn.functional as F
+    from oracle import block_ops_oracle as BO
+    g = torch.Generator().manual_seed(0)
+    B, T, C, W = 2, 19, 8, 4
+    x, w = torch.randn(B, T, C, generator=g), torch.randn(W, C, generator=g)
+    cache, bias = torch.randn(B, W - 1, C, generator=g), torch.randn(C, generator=g)
+    y, nc = BO.short_conv_silu(x, w, bias, cache, apply_silu=False)
+    xx = torch.cat([cache, x], 1).transpose(1, 2)                       # [B,C,W-1+T]
+    ref = F.conv1d(xx, w.t().unsqueeze(1), bias, groups=C).transpose(1, 2)
+    assert torch.allclose(y, ref, atol=1e-5) and torch.equal(nc, torch.cat([cache, x], 1)[:, -(W - 1):])
+    y1, nc1 = BO.short_conv_silu(x, torch.randn(1, C, generator=g), None, None, apply_silu=False)
+    assert torch.equal(y1, x) and nc1.shape == (B, 0, C)
+    # prefill == step-by-step decode through the cache
+    c = torch.zeros(B, W - 1, C)
+    rows = []
+    for t in range(T):
+        r, c = BO.short_conv_silu(x[:, t:t + 1], w, None, c)
+        rows.append(r)
+    assert torch.allclose(torch.cat(rows, 1), BO.short_conv_silu(x, w)[0], atol=1e-6)
+    o, wt, gate = torch.randn(3, 5, 16, generator=g), torch.rand(16, generator=g), torch.randn(3, 5, 16, generator=g)
+    yn = BO.gated_rmsnorm(o, wt, gate, eps=1e-5)
+    assert torch.allclose(yn, o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + 1e-5) * wt * torch.sigmoid(gate), atol=1e-6)
+    gk, bk = BO.kda_gate(torch.full((1, 1, 4), 30.0), torch.zeros(2), 2, None, torch.zeros(1, 1, 2))
+    assert torch.allclose(gk, torch.full((1, 1, 2, 2), -30.0)) and torch.allclose(bk, torch.full((1, 1, 2), 0.5))
