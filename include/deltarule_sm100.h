@@ -211,7 +211,7 @@ int dr_chunk_bwd_static(const DrDesc* desc, const void* q, const void* k, const 
  *   (gated_deltanet.py:764-783).  x, y [B,T,C]; weight float32 [W,C] (w[W-1] meets the current step); bias
  *   float32 [C] or null; cache_in [B,W-1,C] (null: zeros); cache_out [B,W-1,C] (null: not wanted) = the last W-1
  *   rows of concat(cache_in, x).  W in 1..8; W == 1 returns x (+ bias) as the reference does, weight unused.
- *   C a multiple of 16 bytes of elements.  y must not be x; cache_out may be cache_in only for T <= 32 (decode).
+ *   C a multiple of 8.  y must not be x; cache_out may be cache_in only for T <= 4 (decode).
  *   apply_silu 0 leaves the convolution output as is.
  *
  * dr_gate_activations -- mode 0: g = -exp(A_log[h]) softplus(a + bias[h]), beta = beta_scale sigmoid(b) with

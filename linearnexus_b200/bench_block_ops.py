@@ -13,7 +13,6 @@ from pathlib import Path
 
 import torch
 
-from . import block_ops as BO
 
 
 def _time(fn, steps, warmup):
@@ -46,12 +45,33 @@ def main():
     wn = torch.rand(D, device="cuda", generator=g) + 0.5
     a, b = torch.randn(B, T, H, device="cuda", generator=g), torch.randn(B, T, H, device="cuda", generator=g)
     A_log, dt_bias = torch.zeros(H, device="cuda"), torch.zeros(H, device="cuda")
+    # the C entry points on preallocated outputs: a launch costs the host a few microseconds, so back-to-back
+    # launches keep the GPU busy and the event time is kernel time
+    import ctypes
+    from . import _lib
+    lib = _lib.load()
+    ptr = lambda t: None if t is None else ctypes.c_void_p(t.data_ptr())
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    y = torch.empty_like(x)
+    cache = torch.empty(B, W - 1, C, device="cuda", dtype=torch.bfloat16)
+    yn = torch.empty(B, T, H, D, device="cuda", dtype=torch.bfloat16)
+    go, bo = torch.empty_like(a), torch.empty_like(b)
+    BF, F32 = _lib.DR_BF16, _lib.DR_F32
+
+    def chk(status):
+        _lib.check(status, "bench_block_ops")
     cases = [
-        ("short_conv_silu", lambda: BO.short_conv_silu(x, w), 2 * x.numel() * 2 + w.numel() * 4 + B * (W - 1) * C * 2),
-        ("gated_rmsnorm", lambda: BO.rmsnorm_gated(o, wn, gate), 3 * o.numel() * 2),
-        ("gated_rmsnorm_token_major", lambda: BO.rmsnorm_gated(o.view(B, T, H, D), wn, gate, o_layout="bthd"),
+        ("short_conv_silu", lambda: chk(lib.dr_short_conv_silu(ptr(x), ptr(w), None, None, ptr(y), ptr(cache), B, T, C, W,
+                                                               BF, 1, st)),
+         2 * x.numel() * 2 + w.numel() * 4 + B * (W - 1) * C * 2),
+        ("gated_rmsnorm", lambda: chk(lib.dr_gated_rmsnorm(ptr(o), ptr(gate), ptr(wn), ptr(yn), B, H, T, D,
+                                                           _lib.DR_LAYOUT_BHTD, BF, BF, BF, 1e-6, st)), 3 * o.numel() * 2),
+        ("gated_rmsnorm_token_major", lambda: chk(lib.dr_gated_rmsnorm(ptr(o), ptr(gate), ptr(wn), ptr(yn), B, H, T, D,
+                                                                       _lib.DR_LAYOUT_BTHD, BF, BF, BF, 1e-6, st)),
          3 * o.numel() * 2),
-        ("gate_activations", lambda: BO.gated_deltanet_gates(a, b, A_log, dt_bias), 4 * a.numel() * 4),
+        ("gate_activations", lambda: chk(lib.dr_gate_activations(0, ptr(a), ptr(b), ptr(A_log), ptr(dt_bias), ptr(go),
+                                                                 ptr(bo), B, T, H, 1, F32, F32, 1.0, 0.0, st)),
+         4 * a.numel() * 4),
     ]
     for name, fn, nbytes in cases:
         ms = _time(fn, args.steps, args.warmup)

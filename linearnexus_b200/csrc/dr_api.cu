@@ -384,13 +384,12 @@ int dr_short_conv_silu(const void* x, const float* weight, const float* bias, co
                        void* cache_out, int B, int T, int C, int W, int dtype, int apply_silu, void* stream) {
   if (!x || !y || (W > 1 && !weight)) return DR_ERR_NULL;
   if (dtype != DR_F32 && dtype != DR_BF16) return DR_ERR_DTYPE;
-  const int n = dtype == DR_BF16 ? 8 : 4;
-  if (B < 1 || T < 1 || C < 1 || W < 1 || W > dr::blk::kConvMaxW || C % n) return DR_ERR_SHAPE;
-  if (B > 65535) return DR_ERR_SHAPE;
+  if (B < 1 || T < 1 || C < 1 || W < 1 || W > dr::blk::kConvMaxW || C % 8) return DR_ERR_SHAPE;
+  if (B > 65535 || (T + 15) / 16 > 65535) return DR_ERR_SHAPE;
   if (!aligned16(x) || !aligned16(y) || (cache_in && !aligned16(cache_in)) || (cache_out && !aligned16(cache_out)))
     return DR_ERR_ALIGN;
   if (x == y) return DR_ERR_UNSUPPORTED;   // a tile reads the rows before it: not in place
-  if (cache_out && cache_out == cache_in && T > dr::blk::kConvTile) return DR_ERR_UNSUPPORTED;
+  if (cache_out && cache_out == cache_in && T > dr::blk::kConvSteps) return DR_ERR_UNSUPPORTED;
   dr::blk::ConvParams p;
   p.x = x; p.w = weight; p.bias = bias; p.cache_in = W > 1 ? cache_in : nullptr; p.y = y;
   p.cache_out = W > 1 ? cache_out : nullptr;
@@ -428,6 +427,7 @@ int dr_gated_rmsnorm(const void* o, const void* gate, const float* weight, void*
       (gate && gate_dtype != DR_F32 && gate_dtype != DR_BF16))
     return DR_ERR_DTYPE;
   if (B < 1 || H < 1 || T < 1 || V < 4 || V > 512 || V % 4) return DR_ERR_SHAPE;
+  if ((int64_t)B * H * T >= ((int64_t)1 << 31)) return DR_ERR_SHAPE;
   if (!aligned16(o) || !aligned16(y) || !aligned16(weight) || (gate && !aligned16(gate))) return DR_ERR_ALIGN;
   if (o == y && o_layout != DR_LAYOUT_BTHD) return DR_ERR_UNSUPPORTED;
   dr::blk::NormParams p;
@@ -435,7 +435,7 @@ int dr_gated_rmsnorm(const void* o, const void* gate, const float* weight, void*
   p.map.B = B; p.map.H = H; p.map.T = T; p.map.bthd = o_layout == DR_LAYOUT_BTHD; p.map.Hq = H;
   p.V = V; p.eps = eps;
   tl_path = "gated_rmsnorm";
-  cudaError_t e = dr::blk::launch_gated_rmsnorm(p, o_dtype, gate ? gate_dtype : o_dtype, y_dtype,
+  cudaError_t e = dr::blk::launch_gated_rmsnorm(p, o_dtype, gate ? gate_dtype : o_dtype, y_dtype, sm_count(),
                                                 reinterpret_cast<cudaStream_t>(stream));
   g_launches.fetch_add(1);
   return check_cuda(e);

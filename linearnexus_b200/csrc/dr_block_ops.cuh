@@ -24,8 +24,11 @@ namespace blk {
 template <int DT> struct Vec;
 template <> struct Vec<DR_BF16> {
   static constexpr int N = 8;
-  __device__ static void load(const void* base, int64_t idx, float (&f)[8]) {
-    const uint4 r = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(base) + idx);
+  __device__ static uint4 raw(const void* base, int64_t idx) {
+    return *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(base) + idx);
+  }
+  __device__ static void load(const void* base, int64_t idx, float (&f)[8]) { cvt(raw(base, idx), f); }
+  __device__ static void cvt(const uint4 r, float (&f)[8]) {
     const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -45,17 +48,20 @@ template <> struct Vec<DR_BF16> {
 };
 template <> struct Vec<DR_F32> {
   static constexpr int N = 4;
-  __device__ static void load(const void* base, int64_t idx, float (&f)[4]) {
-    const float4 r = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + idx);
-    f[0] = r.x; f[1] = r.y; f[2] = r.z; f[3] = r.w;
+  __device__ static uint4 raw(const void* base, int64_t idx) {
+    return *reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(base) + idx);
+  }
+  __device__ static void load(const void* base, int64_t idx, float (&f)[4]) { cvt(raw(base, idx), f); }
+  __device__ static void cvt(const uint4 r, float (&f)[4]) {
+    f[0] = __uint_as_float(r.x); f[1] = __uint_as_float(r.y); f[2] = __uint_as_float(r.z); f[3] = __uint_as_float(r.w);
   }
   __device__ static void store(void* base, int64_t idx, const float (&f)[4]) {
     *reinterpret_cast<float4*>(reinterpret_cast<float*>(base) + idx) = make_float4(f[0], f[1], f[2], f[3]);
   }
 };
 
-__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
-__device__ __forceinline__ float sigmoidf(float x) { return 1.f / (1.f + __expf(-x)); }
+__device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.f + __expf(-x)); }
+__device__ __forceinline__ float sigmoidf(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
 // log(1 + e^x) without overflow
 __device__ __forceinline__ float softplusf(float x) { return fmaxf(x, 0.f) + log1pf(__expf(-fabsf(x))); }
 
@@ -63,10 +69,11 @@ __device__ __forceinline__ float softplusf(float x) { return fmaxf(x, 0.f) + log
 // Causal depthwise convolution over time, then SiLU.
 //   xx = concat(cache [B,W-1,C], x [B,T,C]);  y[t] = bias + sum_j w[j] xx[t + j]  (w[W-1] meets x[t]);
 //   new cache = the last W-1 rows of xx.  W == 1: y = x + bias, as the reference (its weight is not applied).
-// A thread owns 16 bytes of channels and walks kConvTile time steps with the window in registers; consecutive
-// threads own consecutive channels, so every access of a warp is one 512-byte row segment.
+// A thread produces kConvSteps consecutive time steps of four consecutive channels: it fetches the
+// kConvSteps + W - 1 rows it needs (all loads issued before the first use; the W - 1 rows shared with the thread
+// before it come from L1/L2), so there is no serial walk and the SM holds many small independent threads.
 // ---------------------------------------------------------------------------------------------------------
-constexpr int kConvTile = 32;
+constexpr int kConvSteps = 4;   // time steps per thread; also the longest T whose cache may be updated in place
 constexpr int kConvMaxW = 8;
 
 struct ConvParams {
@@ -75,107 +82,115 @@ struct ConvParams {
   int B, T, C, W, apply_silu;
 };
 
-template <int DT, int MW>   // MW: compiled window bound (4 covers the blocks' kernel size, 8 the rest)
+// four consecutive channels: 8 bytes of bf16 or 16 bytes of fp32
+template <int DT> struct Quad;
+template <> struct Quad<DR_BF16> {
+  using Raw = uint2;
+  __device__ static Raw raw(const void* base, int64_t idx) {
+    return *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(base) + idx);
+  }
+  __device__ static void cvt(const Raw r, float (&f)[4]) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+  }
+  __device__ static void store(void* base, int64_t idx, const float (&f)[4]) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+    uint2 r;
+    r.x = *reinterpret_cast<const uint32_t*>(&a); r.y = *reinterpret_cast<const uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(base) + idx) = r;
+  }
+};
+template <> struct Quad<DR_F32> {
+  using Raw = uint4;
+  __device__ static Raw raw(const void* base, int64_t idx) {
+    return *reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(base) + idx);
+  }
+  __device__ static void cvt(const Raw r, float (&f)[4]) {
+    f[0] = __uint_as_float(r.x); f[1] = __uint_as_float(r.y); f[2] = __uint_as_float(r.z); f[3] = __uint_as_float(r.w);
+  }
+  __device__ static void store(void* base, int64_t idx, const float (&f)[4]) {
+    *reinterpret_cast<float4*>(reinterpret_cast<float*>(base) + idx) = make_float4(f[0], f[1], f[2], f[3]);
+  }
+};
+
+template <int DT, int MW, bool EXACT>   // EXACT: the window is MW (compiled for 1..4); else any window up to MW
 __global__ void __launch_bounds__(128) short_conv_kernel(const ConvParams p) {
-  using VT = Vec<DT>;
-  constexpr int N = VT::N;
-  const int cvecs = p.C / N;
-  const int cv = blockIdx.x * blockDim.x + threadIdx.x;
-  if (cv >= cvecs) return;
+  using Q = Quad<DT>;
+  using Raw = typename Q::Raw;
+  constexpr int N = 4, HW = MW - 1, ROWS = kConvSteps + HW;
+  const int cv = blockIdx.x * 32 + (threadIdx.x & 31);
+  const int t0 = (blockIdx.y * 4 + (threadIdx.x >> 5)) * kConvSteps;
+  if (cv >= p.C / N || t0 >= p.T) return;
   const int c0 = cv * N;
   const int b = blockIdx.z;
-  const int t_begin = blockIdx.y * kConvTile, t_end = min(p.T, t_begin + kConvTile);
-  const int W = p.W, H = W - 1;   // H: rows of history
-  const int64_t xb = (int64_t)b * p.T * p.C, cb = (int64_t)b * H * p.C;
+  const int W = EXACT ? MW : p.W, H = W - 1;   // H: rows of history
+  const int64_t xb = (int64_t)b * p.T * p.C + c0, cb = (int64_t)b * H * p.C + c0;
 
-  float wt[MW][N], bias[N], win[MW][N];   // win[j] = xx[t + j] for the current t
+  // rows t0 .. t0 + kConvSteps - 1 + H of xx = concat(cache, x): cache (zeros if absent) for r < H, else x[r - H]
+  Raw raw[ROWS];
+#pragma unroll
+  for (int w = 0; w < ROWS; ++w) {
+    const int r = t0 + w;
+    raw[w] = Raw{};
+    if (w < kConvSteps + H) {
+      if (r >= H) { if (r - H < p.T) raw[w] = Q::raw(p.x, xb + (int64_t)(r - H) * p.C); }
+      else if (p.cache_in) raw[w] = Q::raw(p.cache_in, cb + (int64_t)r * p.C);
+    }
+  }
+  float wt[MW][N], bias[N];
 #pragma unroll
   for (int i = 0; i < N; ++i) bias[i] = p.bias ? p.bias[c0 + i] : 0.f;
 #pragma unroll
   for (int j = 0; j < MW; ++j)
 #pragma unroll
     for (int i = 0; i < N; ++i) wt[j][i] = (j < W && W > 1) ? p.w[(int64_t)j * p.C + c0 + i] : (j == 0 ? 1.f : 0.f);
-
-  // row r of xx (r = 0 .. H + T - 1): cache for r < H, else x[r - H]; missing cache = zeros
-  auto load_row = [&](int r, float (&f)[N]) {
-    if (r >= H) VT::load(p.x, xb + (int64_t)(r - H) * p.C + c0, f);
-    else if (p.cache_in) VT::load(p.cache_in, cb + (int64_t)r * p.C + c0, f);
-    else {
+  float row[ROWS][N];
 #pragma unroll
-      for (int i = 0; i < N; ++i) f[i] = 0.f;
-    }
-  };
-  // history of the first step of the tile
+  for (int w = 0; w < ROWS; ++w) Q::cvt(raw[w], row[w]);
 #pragma unroll
-  for (int j = 0; j < MW - 1; ++j)
-    if (j < H) load_row(t_begin + j, win[j]);
-  // the last tile also owns the new cache: rows T .. T + H - 1 of xx, read before anything is written so that
-  // a one-tile call (decode) may update its cache in place
-  float keep[MW - 1][N];
-  const bool last = t_end == p.T;
-  if (last && p.cache_out) {
+  for (int u = 0; u < kConvSteps; ++u) {
+    if (t0 + u < p.T) {
+      float acc[N];
 #pragma unroll
-    for (int j = 0; j < MW - 1; ++j)
-      if (j < H) load_row(p.T + j, keep[j]);
-  }
-  for (int t = t_begin; t < t_end; ++t) {
-    float cur[N], acc[N];
-    VT::load(p.x, xb + (int64_t)t * p.C + c0, cur);
+      for (int i = 0; i < N; ++i) acc[i] = bias[i];
 #pragma unroll
-    for (int i = 0; i < N; ++i) acc[i] = bias[i];
+      for (int j = 0; j < MW; ++j) {
+        if (j < W) {
 #pragma unroll
-    for (int j = 0; j < MW - 1; ++j) {
-      if (j < H) {
-#pragma unroll
-        for (int i = 0; i < N; ++i) acc[i] += wt[j][i] * win[j][i];
+          for (int i = 0; i < N; ++i) acc[i] += wt[j][i] * row[u + j][i];
+        }
       }
-    }
+      if (p.apply_silu) {
 #pragma unroll
-    for (int j = 0; j < MW; ++j) {   // the current step meets w[W-1]
-      if (j == H) {
-#pragma unroll
-        for (int i = 0; i < N; ++i) acc[i] += wt[j][i] * cur[i];
+        for (int i = 0; i < N; ++i) acc[i] = silu(acc[i]);
       }
-    }
-    if (p.apply_silu) {
-#pragma unroll
-      for (int i = 0; i < N; ++i) acc[i] = silu(acc[i]);
-    }
-    VT::store(p.y, xb + (int64_t)t * p.C + c0, acc);
-    // slide the window
-#pragma unroll
-    for (int j = 0; j < MW - 2; ++j) {
-      if (j + 1 < H) {
-#pragma unroll
-        for (int i = 0; i < N; ++i) win[j][i] = win[j + 1][i];
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < MW - 1; ++j) {
-      if (j == H - 1) {
-#pragma unroll
-        for (int i = 0; i < N; ++i) win[j][i] = cur[i];
-      }
+      Q::store(p.y, xb + (int64_t)(t0 + u) * p.C, acc);
     }
   }
-  if (last && p.cache_out) {
+  // the thread that holds the end of the sequence also holds the new cache: rows T .. T + H - 1 of xx
+  if (p.cache_out && t0 + kConvSteps >= p.T) {
 #pragma unroll
-    for (int j = 0; j < MW - 1; ++j)
-      if (j < H) VT::store(p.cache_out, cb + (int64_t)j * p.C + c0, keep[j]);
+    for (int w = 0; w < ROWS; ++w) {
+      const int j = t0 + w - p.T;
+      if (j >= 0 && j < H) Q::store(p.cache_out, cb + (int64_t)j * p.C, row[w]);
+    }
   }
 }
 
 inline cudaError_t launch_short_conv(const ConvParams& p, int dt, cudaStream_t stream) {
-  const int n = dt == DR_BF16 ? 8 : 4;
-  const int cvecs = p.C / n;
-  dim3 grid((cvecs + 127) / 128, (p.T + kConvTile - 1) / kConvTile, p.B);
-  if (dt == DR_BF16) {
-    if (p.W <= 4) short_conv_kernel<DR_BF16, 4><<<grid, 128, 0, stream>>>(p);
-    else short_conv_kernel<DR_BF16, kConvMaxW><<<grid, 128, 0, stream>>>(p);
-  } else {
-    if (p.W <= 4) short_conv_kernel<DR_F32, 4><<<grid, 128, 0, stream>>>(p);
-    else short_conv_kernel<DR_F32, kConvMaxW><<<grid, 128, 0, stream>>>(p);
+  const int cvecs = p.C / 4;
+  dim3 grid((cvecs + 31) / 32, (p.T + 4 * kConvSteps - 1) / (4 * kConvSteps), p.B);
+#define DR_CONV_CASE(DT)                                                                        \
+  switch (p.W) {                                                                                \
+    case 1: short_conv_kernel<DT, 1, true><<<grid, 128, 0, stream>>>(p); break;                 \
+    case 2: short_conv_kernel<DT, 2, true><<<grid, 128, 0, stream>>>(p); break;                 \
+    case 3: short_conv_kernel<DT, 3, true><<<grid, 128, 0, stream>>>(p); break;                 \
+    case 4: short_conv_kernel<DT, 4, true><<<grid, 128, 0, stream>>>(p); break;                 \
+    default: short_conv_kernel<DT, kConvMaxW, false><<<grid, 128, 0, stream>>>(p); break;       \
   }
+  if (dt == DR_BF16) { DR_CONV_CASE(DR_BF16) } else { DR_CONV_CASE(DR_F32) }
+#undef DR_CONV_CASE
   return cudaGetLastError();
 }
 
@@ -295,11 +310,94 @@ __global__ void __launch_bounds__(256) gated_rmsnorm_kernel(const NormParams p) 
   }
 }
 
-inline cudaError_t launch_gated_rmsnorm(const NormParams& p, int odt, int gdt, int ydt, cudaStream_t stream) {
+// V = 128 (the blocks' head size): 16 lanes x 8 columns per row, two rows per warp and pass, two passes with every
+// load of both issued before the first reduction (one 16-lane butterfly per row).
+template <int DT>
+__device__ __forceinline__ void ld8(const void* base, int64_t idx, float (&f)[8]) {
+  if constexpr (DT == DR_BF16) {
+    Vec<DR_BF16>::load(base, idx, f);
+  } else {
+    float a[4], b[4];
+    Vec<DR_F32>::load(base, idx, a); Vec<DR_F32>::load(base, idx + 4, b);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { f[i] = a[i]; f[4 + i] = b[i]; }
+  }
+}
+template <int DT>
+__device__ __forceinline__ void st8(void* base, int64_t idx, const float (&f)[8]) {
+  if constexpr (DT == DR_BF16) {
+    Vec<DR_BF16>::store(base, idx, f);
+  } else {
+    const float a[4] = {f[0], f[1], f[2], f[3]}, b[4] = {f[4], f[5], f[6], f[7]};
+    Vec<DR_F32>::store(base, idx, a); Vec<DR_F32>::store(base, idx + 4, b);
+  }
+}
+
+constexpr int kNormRowsPerWarp = 4;
+
+template <int ODT, int GDT, int YDT>
+__global__ void __launch_bounds__(256) gated_rmsnorm_v128_kernel(const NormParams p) {
+  constexpr int V = 128, P = kNormRowsPerWarp / 2;
+  const int lane = threadIdx.x & 31, sub = lane >> 4, c = (lane & 15) * 8;
+  const int64_t nrows = (int64_t)p.map.B * p.map.T * p.map.H;
+  const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const float4 w0 = *reinterpret_cast<const float4*>(p.w + c), w1 = *reinterpret_cast<const float4*>(p.w + c + 4);
+  const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+  // a few resident CTAs per SM walk the rows: no CTA start-up per 32 rows
+  for (int64_t warp_id = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+       warp_id * kNormRowsPerWarp < nrows; warp_id += nwarps) {
+  float x[P][8], gt[P][8];
+  int64_t dst[P];
+  bool live[P];
+#pragma unroll
+  for (int i = 0; i < P; ++i) {
+    const int64_t row = warp_id * kNormRowsPerWarp + 2 * i + sub;
+    live[i] = row < nrows;
+    dst[i] = row * V + c;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { x[i][e] = 0.f; gt[i][e] = 0.f; }
+    if (live[i]) {
+      int64_t src = dst[i];   // token-major o: the same place as y
+      if (!p.map.bthd) {      // (rows < 2^31, checked by the caller: 32-bit divisions)
+        const uint32_t r32 = (uint32_t)row, H32 = (uint32_t)p.map.H, T32 = (uint32_t)p.map.T;
+        const uint32_t h = r32 % H32, bt = r32 / H32;
+        const uint32_t t = bt % T32, b = bt / T32;
+        src = (((int64_t)b * H32 + h) * T32 + t) * V + c;
+      }
+      ld8<ODT>(p.o, src, x[i]);
+      if (p.gate) ld8<GDT>(p.gate, dst[i], gt[i]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < P; ++i) {
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += x[i][e] * x[i][e];
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float r = 1.f / sqrtf(ss * (1.f / V) + p.eps);
+    float y[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      y[e] = x[i][e] * r * wv[e];
+      if (p.gate) y[e] *= sigmoidf(gt[i][e]);
+    }
+    if (live[i]) st8<YDT>(p.y, dst[i], y);
+  }
+  }
+}
+
+inline cudaError_t launch_gated_rmsnorm(const NormParams& p, int odt, int gdt, int ydt, int sms, cudaStream_t stream) {
   const int64_t nrows = (int64_t)p.map.B * p.map.T * p.map.H;
   const unsigned grid = (unsigned)((nrows + 7) / 8);
-#define DR_NORM_CASE(O, G, Y) \
-  if (odt == O && gdt == G && ydt == Y) { gated_rmsnorm_kernel<O, G, Y><<<grid, 256, 0, stream>>>(p); return cudaGetLastError(); }
+  const int64_t want128 = (nrows + 8 * kNormRowsPerWarp - 1) / (8 * kNormRowsPerWarp);
+  const unsigned grid128 = (unsigned)(want128 < (int64_t)sms * 8 ? want128 : (int64_t)sms * 8);
+#define DR_NORM_CASE(O, G, Y)                                                              \
+  if (odt == O && gdt == G && ydt == Y) {                                                  \
+    if (p.V == 128) gated_rmsnorm_v128_kernel<O, G, Y><<<grid128, 256, 0, stream>>>(p);    \
+    else gated_rmsnorm_kernel<O, G, Y><<<grid, 256, 0, stream>>>(p);                       \
+    return cudaGetLastError();                                                             \
+  }
   DR_NORM_CASE(DR_BF16, DR_BF16, DR_BF16)
   DR_NORM_CASE(DR_F32, DR_F32, DR_F32)
   DR_NORM_CASE(DR_F32, DR_BF16, DR_BF16)
