@@ -11,6 +11,8 @@ from .ops import (delta_rule_chunkwise, delta_rule_recurrent, delta_rule_recurre
                   gated_delta_rule_step, kda_chunkwise, kda_recurrent, kda_step)
 from .state import DeltaNetState, GatedDeltaNetState, KDAState
 from .host_pipeline import HostPipeline, chunkwise_from_host
+from .block_ops import (depthwise_conv1d_causal, gated_deltanet_gates, kda_gate, rmsnorm_gated,
+                        short_conv_silu)
 
 __all__ = [
     "delta_rule_recurrent", "delta_rule_chunkwise", "delta_rule_step", "delta_rule_recurrent_pallas",
@@ -19,4 +21,5 @@ __all__ = [
     "DeltaNetState", "GatedDeltaNetState", "KDAState",
     "KernelBackend", "backend_availability", "select_kernel_backend",
     "HostPipeline", "chunkwise_from_host",
+    "depthwise_conv1d_causal", "short_conv_silu", "gated_deltanet_gates", "kda_gate", "rmsnorm_gated",
 ]

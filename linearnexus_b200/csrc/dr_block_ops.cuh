@@ -73,7 +73,7 @@ __device__ __forceinline__ float softplusf(float x) { return fmaxf(x, 0.f) + log
 // kConvSteps + W - 1 rows it needs (all loads issued before the first use; the W - 1 rows shared with the thread
 // before it come from L1/L2), so there is no serial walk and the SM holds many small independent threads.
 // ---------------------------------------------------------------------------------------------------------
-constexpr int kConvSteps = 4;   // time steps per thread; also the longest T whose cache may be updated in place
+constexpr int kConvSteps = 4;   // time steps per thread (measured best of 2, 3, 4, 8); also the longest T whose cache may be updated in place
 constexpr int kConvMaxW = 8;
 
 struct ConvParams {
@@ -139,12 +139,16 @@ __global__ void __launch_bounds__(128) short_conv_kernel(const ConvParams p) {
     }
   }
   float wt[MW][N], bias[N];
+  {
+    const float4 b4 = p.bias ? *reinterpret_cast<const float4*>(p.bias + c0) : make_float4(0.f, 0.f, 0.f, 0.f);
+    bias[0] = b4.x; bias[1] = b4.y; bias[2] = b4.z; bias[3] = b4.w;
+  }
 #pragma unroll
-  for (int i = 0; i < N; ++i) bias[i] = p.bias ? p.bias[c0 + i] : 0.f;
-#pragma unroll
-  for (int j = 0; j < MW; ++j)
-#pragma unroll
-    for (int i = 0; i < N; ++i) wt[j][i] = (j < W && W > 1) ? p.w[(int64_t)j * p.C + c0 + i] : (j == 0 ? 1.f : 0.f);
+  for (int j = 0; j < MW; ++j) {
+    float4 w4 = make_float4(j == 0 ? 1.f : 0.f, j == 0 ? 1.f : 0.f, j == 0 ? 1.f : 0.f, j == 0 ? 1.f : 0.f);
+    if (j < W && W > 1) w4 = *reinterpret_cast<const float4*>(p.w + (int64_t)j * p.C + c0);
+    wt[j][0] = w4.x; wt[j][1] = w4.y; wt[j][2] = w4.z; wt[j][3] = w4.w;
+  }
   float row[ROWS][N];
 #pragma unroll
   for (int w = 0; w < ROWS; ++w) Q::cvt(raw[w], row[w]);
@@ -349,6 +353,11 @@ __global__ void __launch_bounds__(256) gated_rmsnorm_v128_kernel(const NormParam
   float x[P][8], gt[P][8];
   int64_t dst[P];
   bool live[P];
+  uint32_t h0 = 0, tt0 = 0, b0 = 0;   // (b, t, h) of the warp's first row
+  if (!p.map.bthd) {
+    const uint32_t r32 = (uint32_t)(warp_id * kNormRowsPerWarp), bt = r32 / (uint32_t)p.map.H;
+    h0 = r32 % (uint32_t)p.map.H; tt0 = bt % (uint32_t)p.map.T; b0 = bt / (uint32_t)p.map.T;
+  }
 #pragma unroll
   for (int i = 0; i < P; ++i) {
     const int64_t row = warp_id * kNormRowsPerWarp + 2 * i + sub;
@@ -358,10 +367,11 @@ __global__ void __launch_bounds__(256) gated_rmsnorm_v128_kernel(const NormParam
     for (int e = 0; e < 8; ++e) { x[i][e] = 0.f; gt[i][e] = 0.f; }
     if (live[i]) {
       int64_t src = dst[i];   // token-major o: the same place as y
-      if (!p.map.bthd) {      // (rows < 2^31, checked by the caller: 32-bit divisions)
-        const uint32_t r32 = (uint32_t)row, H32 = (uint32_t)p.map.H, T32 = (uint32_t)p.map.T;
-        const uint32_t h = r32 % H32, bt = r32 / H32;
-        const uint32_t t = bt % T32, b = bt / T32;
+      if (!p.map.bthd) {      // (rows < 2^31, checked by the caller: 32-bit divisions, once per warp and pass)
+        const uint32_t H32 = (uint32_t)p.map.H, T32 = (uint32_t)p.map.T;
+        uint32_t h = h0 + 2 * i + sub, t = tt0, b = b0;
+        while (h >= H32) { h -= H32; ++t; }
+        while (t >= T32) { t -= T32; ++b; }
         src = (((int64_t)b * H32 + h) * T32 + t) * V + c;
       }
       ld8<ODT>(p.o, src, x[i]);
