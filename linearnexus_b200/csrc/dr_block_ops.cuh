@@ -69,7 +69,7 @@ __device__ __forceinline__ float softplusf(float x) { return fmaxf(x, 0.f) + log
 // Causal depthwise convolution over time, then SiLU.
 //   xx = concat(cache [B,W-1,C], x [B,T,C]);  y[t] = bias + sum_j w[j] xx[t + j]  (w[W-1] meets x[t]);
 //   new cache = the last W-1 rows of xx.  W == 1: y = x + bias, as the reference (its weight is not applied).
-// A thread produces kConvSteps consecutive time steps of four consecutive channels: it fetches the
+// A thread produces kConvSteps consecutive time steps of 16 bytes of channels (8 bf16 / 4 fp32): it fetches the
 // kConvSteps + W - 1 rows it needs (all loads issued before the first use; the W - 1 rows shared with the thread
 // before it come from L1/L2), so there is no serial walk and the SM holds many small independent threads.
 // ---------------------------------------------------------------------------------------------------------
@@ -82,43 +82,14 @@ struct ConvParams {
   int B, T, C, W, apply_silu;
 };
 
-// four consecutive channels: 8 bytes of bf16 or 16 bytes of fp32
-template <int DT> struct Quad;
-template <> struct Quad<DR_BF16> {
-  using Raw = uint2;
-  __device__ static Raw raw(const void* base, int64_t idx) {
-    return *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(base) + idx);
-  }
-  __device__ static void cvt(const Raw r, float (&f)[4]) {
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
-    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
-    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
-  }
-  __device__ static void store(void* base, int64_t idx, const float (&f)[4]) {
-    const __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
-    uint2 r;
-    r.x = *reinterpret_cast<const uint32_t*>(&a); r.y = *reinterpret_cast<const uint32_t*>(&b);
-    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(base) + idx) = r;
-  }
-};
-template <> struct Quad<DR_F32> {
-  using Raw = uint4;
-  __device__ static Raw raw(const void* base, int64_t idx) {
-    return *reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(base) + idx);
-  }
-  __device__ static void cvt(const Raw r, float (&f)[4]) {
-    f[0] = __uint_as_float(r.x); f[1] = __uint_as_float(r.y); f[2] = __uint_as_float(r.z); f[3] = __uint_as_float(r.w);
-  }
-  __device__ static void store(void* base, int64_t idx, const float (&f)[4]) {
-    *reinterpret_cast<float4*>(reinterpret_cast<float*>(base) + idx) = make_float4(f[0], f[1], f[2], f[3]);
-  }
-};
+// 16 bytes of channels per thread: 8 bf16 or 4 fp32
+template <int DT> using ConvVec = Vec<DT>;
 
 template <int DT, int MW, bool EXACT>   // EXACT: the window is MW (compiled for 1..4); else any window up to MW
 __global__ void __launch_bounds__(128) short_conv_kernel(const ConvParams p) {
-  using Q = Quad<DT>;
-  using Raw = typename Q::Raw;
-  constexpr int N = 4, HW = MW - 1, ROWS = kConvSteps + HW;
+  using Q = ConvVec<DT>;
+  using Raw = uint4;
+  constexpr int N = Q::N, HW = MW - 1, ROWS = kConvSteps + HW;
   const int cv = blockIdx.x * 32 + (threadIdx.x & 31);
   const int t0 = (blockIdx.y * 4 + (threadIdx.x >> 5)) * kConvSteps;
   if (cv >= p.C / N || t0 >= p.T) return;
@@ -140,14 +111,20 @@ __global__ void __launch_bounds__(128) short_conv_kernel(const ConvParams p) {
   }
   float wt[MW][N], bias[N];
   {
-    const float4 b4 = p.bias ? *reinterpret_cast<const float4*>(p.bias + c0) : make_float4(0.f, 0.f, 0.f, 0.f);
-    bias[0] = b4.x; bias[1] = b4.y; bias[2] = b4.z; bias[3] = b4.w;
+#pragma unroll
+    for (int q4 = 0; q4 < N; q4 += 4) {
+      const float4 b4 = p.bias ? *reinterpret_cast<const float4*>(p.bias + c0 + q4) : make_float4(0.f, 0.f, 0.f, 0.f);
+      bias[q4] = b4.x; bias[q4 + 1] = b4.y; bias[q4 + 2] = b4.z; bias[q4 + 3] = b4.w;
+    }
   }
 #pragma unroll
   for (int j = 0; j < MW; ++j) {
-    float4 w4 = make_float4(j == 0 ? 1.f : 0.f, j == 0 ? 1.f : 0.f, j == 0 ? 1.f : 0.f, j == 0 ? 1.f : 0.f);
-    if (j < W && W > 1) w4 = *reinterpret_cast<const float4*>(p.w + (int64_t)j * p.C + c0);
-    wt[j][0] = w4.x; wt[j][1] = w4.y; wt[j][2] = w4.z; wt[j][3] = w4.w;
+#pragma unroll
+    for (int q4 = 0; q4 < N; q4 += 4) {
+      float4 w4 = make_float4(j == 0 ? 1.f : 0.f, j == 0 ? 1.f : 0.f, j == 0 ? 1.f : 0.f, j == 0 ? 1.f : 0.f);
+      if (j < W && W > 1) w4 = *reinterpret_cast<const float4*>(p.w + (int64_t)j * p.C + c0 + q4);
+      wt[j][q4] = w4.x; wt[j][q4 + 1] = w4.y; wt[j][q4 + 2] = w4.z; wt[j][q4 + 3] = w4.w;
+    }
   }
   float row[ROWS][N];
 #pragma unroll
@@ -183,7 +160,7 @@ __global__ void __launch_bounds__(128) short_conv_kernel(const ConvParams p) {
 }
 
 inline cudaError_t launch_short_conv(const ConvParams& p, int dt, cudaStream_t stream) {
-  const int cvecs = p.C / 4;
+  const int cvecs = p.C / (dt == DR_BF16 ? 8 : 4);
   dim3 grid((cvecs + 31) / 32, (p.T + 4 * kConvSteps - 1) / (4 * kConvSteps), p.B);
 #define DR_CONV_CASE(DT)                                                                        \
   switch (p.W) {                                                                                \
