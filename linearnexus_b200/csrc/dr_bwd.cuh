@@ -1,4 +1,5 @@
-// Backward of the chunkwise delta rule (DeltaNet / Gated DeltaNet / KDA), fp32 on the CUDA cores.
+// Backward of the chunkwise delta rule (DeltaNet / Gated DeltaNet / KDA): exact fp32 on the CUDA cores, and for
+// bf16 inputs of DeltaNet / Gated DeltaNet the same phases as tf32 mma.sync products (16 warps per CTA).
 //
 // The reference has no backward function (its gradients are autodiff through the chunk
 // functions); this is the hand-derived chunk-form adjoint.  Per chunk, with S0 the state at the
@@ -15,11 +16,15 @@
 //                    dS0 = (Q^ e^G)^T dO + e^{G_L} dS1 - (beta K^ e^G)^T dR
 //   then dg = reverse cumulative sum of dG inside the chunk, and the l2-norm / scale chain rule.
 //
-// Three launches: (1) the fp32 chunk forward with a state checkpoint per chunk, (2) the adjoint
-// kernel, one CTA per (batch, head, slice of value columns) walking the chunks backwards and
-// adding its partial dQ^, dK^, dG into fp32 accumulators (the adjoint is linear in them),
-// (3) a finalize kernel (normalisation chain rule, reverse cumulative sum, casts).
-// Workspace: checkpoints [B*H][N][K][V] | dQ^ acc [B*H][N*C][K] | dK^ acc | dG acc, all fp32.
+// Launches: (1) a chunk forward that leaves the state at every chunk start (the fused tcgen05 kernel, the
+// two-kernel KDA forward or the fp32 kernel, by shape; skipped when the caller ran the saving forward),
+// (1b, tensor-core path) a chunk-parallel pre-pass with what does not depend on the value slice (X, A,
+// T = M^-1, q^, k^), (2) the adjoint kernel, one CTA per (batch, head, slice of value columns) walking the
+// chunks backwards and storing its partial dQ^, dK^ to the slice's own copy (dG, dbeta by atomics; the adjoint
+// is linear in them), (3) a finalize kernel (sum of the copies -- over the value heads of a group too when q, k
+// have fewer heads --, normalisation chain rule, reverse cumulative sum, casts).
+// Workspace: checkpoints [B*H][N][K][V] | dQ^ copies [slices][B*H][N*C][K] | dK^ copies | dG acc | pre-pass
+// records [B*H][N][3*64*64 + 2*64*K], all fp32.
 #pragma once
 
 #include "dr_chunk_fp32.cuh"
@@ -34,26 +39,10 @@ constexpr int kBwThreads = 256;
 // fetches, and four warps per scheduler hide them where two did not
 __host__ __device__ constexpr int bwd_threads(bool tc) { return tc ? 512 : 256; }
 
-// One 16x8 output tile of D (+)= A B on the warp-level tensor-core path (tf32 operands, fp32
-// accumulate): a(m, k), b(k, n) are element accessors into fp32 shared memory.  Lane (g = lane/4,
-// t = lane%4) ends up with D[m0+g][n0+2t], D[m0+g][n0+2t+1], D[m0+g+8][n0+2t], D[m0+g+8][n0+2t+1].
-// The CUDA-core loops these replace are bound by shared-memory wavefronts, not by flops.
-template <class AF, class BF>
-__device__ __forceinline__ void tile_gemm_tf32(float (&d)[4], int m0, int n0, int kdim, AF a, BF b, int lane) {
-  const int g = lane >> 2, t = lane & 3;
-  for (int k0 = 0; k0 < kdim; k0 += 8) {
-    uint32_t af[4], bf[2];
-    af[0] = sm100::to_tf32(a(m0 + g, k0 + t));
-    af[1] = sm100::to_tf32(a(m0 + g + 8, k0 + t));
-    af[2] = sm100::to_tf32(a(m0 + g, k0 + t + 4));
-    af[3] = sm100::to_tf32(a(m0 + g + 8, k0 + t + 4));
-    bf[0] = sm100::to_tf32(b(k0 + t, n0 + g));
-    bf[1] = sm100::to_tf32(b(k0 + t + 4, n0 + g));
-    sm100::mma_tf32(d, af, bf);
-  }
-}
-
-// Row-panel products on the same path: the warp owns 16 rows (m0..) and NT consecutive 8-column tiles
+// Row-panel products on the warp-level tensor-core path (mma.sync m16n8k8, tf32 operands, fp32 accumulate);
+// a(m, k), b(k, n) are element accessors into fp32 shared memory.  Lane (g = lane/4, t = lane%4) ends up with
+// D[m0+g][n0+2t], D[m0+g][n0+2t+1], D[m0+g+8][n0+2t], D[m0+g+8][n0+2t+1] of every tile.
+// The warp owns 16 rows (m0..) and NT consecutive 8-column tiles
 // (n0..); the A fragment is fetched once per k-step and reused for every tile, and products that share
 // their B operand share its fetch too.  Operands are passed as raw fp32 bits (the tensor core ignores the
 // low mantissa bits: truncation to tf32).  k runs over [kb, ke) in steps of 8.
@@ -95,31 +84,6 @@ __device__ __forceinline__ void rgemm2(float (&d1)[NT][4], float (&d2)[NT][4], i
     }
   }
 }
-template <int NT, class AF1, class AF2, class AF3, class BF>
-__device__ __forceinline__ void rgemm3(float (&d1)[NT][4], float (&d2)[NT][4], float (&d3)[NT][4], int m0, int n0, int kb,
-                                       int ke, AF1 a1, AF2 a2, AF3 a3, BF b, int lane) {
-  const int g = lane >> 2, t = lane & 3;
-  for (int k0 = kb; k0 < ke; k0 += 8) {
-    uint32_t af1[4], af2[4], af3[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int m = m0 + g + (e & 1) * 8, k = k0 + t + (e >> 1) * 4;
-      af1[e] = __float_as_uint(a1(m, k));
-      af2[e] = __float_as_uint(a2(m, k));
-      af3[e] = __float_as_uint(a3(m, k));
-    }
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      uint32_t bf[2];
-      bf[0] = __float_as_uint(b(k0 + t, n0 + 8 * nt + g));
-      bf[1] = __float_as_uint(b(k0 + t + 4, n0 + 8 * nt + g));
-      sm100::mma_tf32(d1[nt], af1, bf);
-      sm100::mma_tf32(d2[nt], af2, bf);
-      sm100::mma_tf32(d3[nt], af3, bf);
-    }
-  }
-}
-
 // The same row-panel products with the contraction index taken in pairs: lane (g, t) supplies k0 + 2t and
 // k0 + 2t + 1 where the natural order has k0 + t and k0 + t + 4 (a sum over k does not care).  The accessors
 // return both values at once, a2(m, k) = {A[m][k], A[m][k+1]} and b2(k, n) = {B[k][n], B[k+1][n]}.

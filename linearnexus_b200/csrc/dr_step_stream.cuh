@@ -32,7 +32,6 @@ __global__ void __launch_bounds__(kStepThreads, 1) step_stream_kernel(const Step
   float* s_red = s_v + kStreamD;   // [2][8][128]
   __shared__ __align__(8) uint64_t full[kStreamStages];
   __shared__ float s_part[3][4];
-  __shared__ float s_scal[3];
   constexpr int K = kStreamD, V = kStreamD;
 
   const int tid = threadIdx.x;
