@@ -53,7 +53,7 @@ NCU_TRAFFIC = {
     "kda_fwd:chunk_split_tcgen05": 3.78e9,    # profiles/kda_split_kernels.md: both kernels, B=1 capture x 4 sequences-wise
     "gdn_decode:step": 1026.8e6,        # profiles/step_kernel_gdn_decode.md (full size)
     "gdn_decode:step_stream": 1023.5e6, # same file, second capture
-    "gdn_fwd_bwd:bwd_saved": 1944.8e6,  # profiles/bwd_chunk_kernel_phases.md: pre-pass + adjoint + finalize (full size)
+    "gdn_fwd_bwd:bwd_saved": 2123.1e6,  # profiles/bwd_chunk_kernel_phases.md: saving forward + pre-pass + adjoint + finalize (full size)
 }
 
 
