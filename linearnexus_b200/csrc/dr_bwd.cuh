@@ -35,6 +35,7 @@
 namespace dr {
 
 constexpr int kBwThreads = 256;
+constexpr int kBwSlice = 32;   // value columns per adjoint CTA, every variant (KDA at K = 128: 204 KB of shared memory)
 // the tensor-core adjoint runs 16 warps: its phases are short dependent chains of mma.sync and shared-memory
 // fetches, and four warps per scheduler hide them where two did not
 __host__ __device__ constexpr int bwd_threads(bool tc) { return tc ? 512 : 256; }
@@ -1112,7 +1113,7 @@ __global__ void __launch_bounds__(256) bwd_finalize_kernel(const BwdFinalParams 
             xk[sl] = *reinterpret_cast<const float4*>(ak0 + copy_off(sl) + i);
           }
         }
-        for (int sl = 8; sl < ncopies; ++sl) {   // (16-column slices of the per-channel-decay variant; head groups)
+        for (int sl = 8; sl < ncopies; ++sl) {   // (head groups)
           const float4 a = *reinterpret_cast<const float4*>(aq0 + copy_off(sl) + i);
           const float4 bq = *reinterpret_cast<const float4*>(ak0 + copy_off(sl) + i);
           aq[s2][0] += a.x; aq[s2][1] += a.y; aq[s2][2] += a.z; aq[s2][3] += a.w;
@@ -1199,7 +1200,7 @@ inline int64_t bwd_workspace_bytes(const DrDesc* d) {
   const int64_t N = (d->T + d->chunk - 1) / d->chunk;
   const int64_t units = (int64_t)d->B * d->H;
   const int64_t rows = units * N * d->chunk;
-  const int64_t nvs = (d->V + (d->variant == DR_KDA ? 16 : 32) - 1) / (d->variant == DR_KDA ? 16 : 32);
+  const int64_t nvs = (d->V + kBwSlice - 1) / kBwSlice;
   int64_t f = units * N * d->K * d->V + 2 * rows * d->K * nvs;
   if (d->variant == DR_GATED) f += rows;
   if (d->variant == DR_KDA) f += rows * d->K;
@@ -1210,7 +1211,7 @@ inline int64_t bwd_workspace_bytes(const DrDesc* d) {
 // The checkpointing forward of the backward: state at the start of every chunk -> the head of the workspace.
 // With o / hT given it is also the forward a training step needs (dr_chunk_fwd_saving), so that step runs one
 // forward instead of two.  KDA at the tensor-core shape uses the two-kernel forward with its records parked in the
-// accumulator part of the workspace (524 KB per chunk there against 82 KB of records; the adjoint overwrites it).
+// accumulator part of the workspace (262 KB per chunk there against 82 KB of records; the adjoint overwrites it).
 inline cudaError_t launch_bwd_forward(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
                                       const float* beta, const float* h0, void* o, float* hT, void* workspace,
                                       cudaStream_t stream, int* launches) {
@@ -1253,7 +1254,7 @@ inline cudaError_t launch_bwd_adjoint(const DrDesc* d, const void* q, const void
   const int64_t N = (d->T + C - 1) / C, units = (int64_t)d->B * d->H, rows = units * N * C;
   float* ws = reinterpret_cast<float*>(workspace);
   float* ckpt = ws;
-  const int VSl = d->variant == DR_KDA ? 16 : 32;
+  const int VSl = kBwSlice;
   const int64_t nvs = (V + VSl - 1) / VSl;
   float* dq_acc = ckpt + units * N * K * V;      // [nvs][rows][K], one copy per value slice (fully overwritten)
   float* dk_acc = dq_acc + nvs * rows * K;
@@ -1277,7 +1278,7 @@ inline cudaError_t launch_bwd_adjoint(const DrDesc* d, const void* q, const void
   p.map = map; p.K = K; p.V = V; p.C = C; p.N = (int)N;
   p.variant = d->variant; p.qkv_dt = d->qkv_dtype; p.g_dt = d->g_dtype; p.l2norm = d->use_qk_l2norm; p.scale = d->scale;
   if (d->variant == DR_KDA) {
-    constexpr int VS = 16;
+    constexpr int VS = kBwSlice;
     const size_t smem = bwd_layout(C, K, VS, true).total * sizeof(float);
     e = cudaFuncSetAttribute(bwd_chunk_kernel<VS, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
