@@ -9,6 +9,7 @@ figures always come from the normal build.
     python -m linearnexus_b200.profile_phases gdn      # fused tcgen05 forward, B=8 T=4096 H=16
     python -m linearnexus_b200.profile_phases kda      # intra-chunk pass of the two-kernel forward
     python -m linearnexus_b200.profile_phases bwd      # adjoint kernel, bf16 inputs
+    python -m linearnexus_b200.profile_phases bwd_kda  # adjoint kernel of the per-channel-decay variant (CUDA cores)
 """
 import ctypes
 import os
@@ -75,9 +76,10 @@ def main(which):
         per = 1          # the profiled CTA handles one chunk
     else:
         B, H, T, names = 2, 16, 1024, BWD
-        q, k, v, g, beta = _inputs(torch, "gated", B, H, T)
+        variant = "kda" if which == "bwd_kda" else "gated"
+        q, k, v, g, beta = _inputs(torch, variant, B, H, T)
         d_o = torch.randn(B, H, T, 128, device="cuda").bfloat16()
-        run = lambda: ops.chunk_backward("gated", q, k, v, g, beta, d_o, chunk_size=64)
+        run = lambda: ops.chunk_backward(variant, q, k, v, g, beta, d_o, chunk_size=64)
         per = T // 64
     for _ in range(3):   # the counters are cleared by every read: the last launch is reported
         run()
