@@ -121,6 +121,27 @@ __device__ __forceinline__ void rgemm2_p(float (&d1)[NT][4], float (&d2)[NT][4],
   }
 }
 
+// sum over j < n (n <= 128) of a(j) b(j) where a(j) is the same for all lanes of the warp and costly: lane l
+// evaluates a(l), a(l + 32), ... once and a shuffle hands the values round; b(j) is the lane's own operand.
+template <class AF, class BF>
+__device__ __forceinline__ float bcast_dot(AF a, BF b, int n, int lane) {
+  float av[4], acc = 0.f;
+#pragma unroll
+  for (int ii = 0; ii < 4; ++ii) av[ii] = (lane + 32 * ii < n) ? a(lane + 32 * ii) : 0.f;
+#pragma unroll
+  for (int ii = 0; ii < 4; ++ii) {
+    if (32 * ii < n) {
+      const int lim = min(32, n - 32 * ii);
+#pragma unroll 8
+      for (int l = 0; l < 32; ++l) {
+        const float x = __shfl_sync(0xffffffffu, av[ii], l);
+        if (l < lim) acc += x * b(32 * ii + l);
+      }
+    }
+  }
+  return acc;
+}
+
 struct BwdParams {
   const void* q; const void* k; const void* v; const void* g; const float* beta;
   const void* d_o; const float* d_hT;
@@ -320,38 +341,56 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
         }
       }
     } else {
-    for (int c = warp; c < C; c += NTHR / 32) {
-      float nq = 0.f, nk = 0.f;
-      const bool live = c < rows;
-      for (int i = lane; i < K; i += 32) {
-        float qv = 0.f, kv = 0.f, gv = 0.f;
-        if (live) {
-          qv = ld_elem(p.q, qk_base + (t0 + c) * qk_tok + i, p.qkv_dt);
-          kv = ld_elem(p.k, qk_base + (t0 + c) * qk_tok + i, p.qkv_dt);
-          if (KDA) gv = ld_elem(p.g, gk_base + (t0 + c) * gk_tok + i, p.g_dt);
+    // rows warp, warp + NW, ... of the chunk, four at a time: every global load of the four rows is issued before
+    // the first norm (K <= 128: at most four elements per lane, row and array)
+    for (int cb = warp; cb < C; cb += 4 * NW) {
+      float qv[4][4], kv[4][4], gv[4][4], bt[4], gs[4];
+#pragma unroll
+      for (int rr = 0; rr < 4; ++rr) {
+        const int c = cb + rr * NW;
+        const bool live = c < rows;
+#pragma unroll
+        for (int ii = 0; ii < 4; ++ii) {
+          const int i = lane + 32 * ii;
+          qv[rr][ii] = kv[rr][ii] = gv[rr][ii] = 0.f;
+          if (live && i < K) {
+            qv[rr][ii] = ld_elem(p.q, qk_base + (t0 + c) * qk_tok + i, p.qkv_dt);
+            kv[rr][ii] = ld_elem(p.k, qk_base + (t0 + c) * qk_tok + i, p.qkv_dt);
+            if (KDA) gv[rr][ii] = ld_elem(p.g, gk_base + (t0 + c) * gk_tok + i, p.g_dt);
+          }
         }
-        sQ[c * ldq + i] = qv;
-        sK[c * ldk + i] = kv;
-        if (KDA) sG[c * ldk + i] = gv;
-        nq += qv * qv;
-        nk += kv * kv;
+        bt[rr] = (live && lane == 0) ? p.beta[s_base + (t0 + c) * s_tok] : 0.f;
+        gs[rr] = (live && gated && lane == 0) ? ld_elem(p.g, s_base + (t0 + c) * s_tok, p.g_dt) : 0.f;
       }
-      float qmul = p.scale, kmul = 1.f;
-      if (p.l2norm) {
-        nq = warp_sum(nq);
-        nk = warp_sum(nk);
-        qmul = p.scale / (sqrtf(nq) + 1e-6f);
-        kmul = 1.f / (sqrtf(nk) + 1e-6f);
-      }
-      __syncwarp();
-      for (int i = lane; i < K; i += 32) {
-        sQ[c * ldq + i] *= qmul;
-        sK[c * ldk + i] *= kmul;
-      }
-      if (lane == 0) {
-        sBeta[c] = live ? p.beta[s_base + (t0 + c) * s_tok] : 0.f;
-        sGs[c] = (live && gated) ? ld_elem(p.g, s_base + (t0 + c) * s_tok, p.g_dt) : 0.f;
-        sdBeta[c] = 0.f;
+#pragma unroll
+      for (int rr = 0; rr < 4; ++rr) {
+        const int c = cb + rr * NW;
+        if (c < C) {
+          float nq = 0.f, nk = 0.f;
+#pragma unroll
+          for (int ii = 0; ii < 4; ++ii) { nq += qv[rr][ii] * qv[rr][ii]; nk += kv[rr][ii] * kv[rr][ii]; }
+          float qmul = p.scale, kmul = 1.f;
+          if (p.l2norm) {
+            nq = warp_sum(nq);
+            nk = warp_sum(nk);
+            qmul = p.scale / (sqrtf(nq) + 1e-6f);
+            kmul = 1.f / (sqrtf(nk) + 1e-6f);
+          }
+#pragma unroll
+          for (int ii = 0; ii < 4; ++ii) {
+            const int i = lane + 32 * ii;
+            if (i < K) {
+              sQ[c * ldq + i] = qv[rr][ii] * qmul;
+              sK[c * ldk + i] = kv[rr][ii] * kmul;
+              if (KDA) sG[c * ldk + i] = gv[rr][ii];
+            }
+          }
+          if (lane == 0) {
+            sBeta[c] = bt[rr];
+            sGs[c] = gs[rr];
+            sdBeta[c] = 0.f;
+          }
+        }
       }
     }
     for (int i = tid; i < C * VS; i += NTHR) {
@@ -462,9 +501,15 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
       for (int c = warp * STREAMS + sub; c < C; c += RPW * STREAMS) {
         float acc = 0.f;
         const float bc = sBeta[c];
+        if constexpr (KDA && VS == 32) {
+          // the 32 lanes of a row need the same k^ e^G: each lane forms four of them once, a shuffle hands them round
+          acc = bcast_dot([&](int kk) { return sK[c * ldk + kk] * __expf(sG[c * ldk + kk]); },
+                          [&](int kk) { return sS0[kk * ldv + vv]; }, K, lane);
+        } else {
         for (int kk = 0; kk < K; ++kk) {
           const float eg = KDA ? __expf(sG[c * ldk + kk]) : 1.f;
           acc += sK[c * ldk + kk] * eg * sS0[kk * ldv + vv];
+        }
         }
         if (!KDA) acc *= sEG[c];
         sVn[c * ldv + vv] = bc * (sV[c * ldv + vv] - acc);
@@ -537,9 +582,14 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
         float acc = 0.f;
         for (int i = c; i < C; ++i) acc += sA[i * lda + c] * Eij(i, c) * sdO[i * ldv + vv];
         float acc2 = 0.f;
+        if constexpr (KDA && VS == 32) {
+          acc2 = bcast_dot([&](int kk) { return sK[c * ldk + kk] * __expf(fminf(sG[(C - 1) * ldk + kk] - sG[c * ldk + kk], 0.f)); },
+                           [&](int kk) { return sdS[kk * ldv + vv]; }, K, lane);
+        } else {
         for (int kk = 0; kk < K; ++kk) {
           const float w = KDA ? __expf(fminf(sG[(C - 1) * ldk + kk] - sG[c * ldk + kk], 0.f)) : 1.f;
           acc2 += sK[c * ldk + kk] * w * sdS[kk * ldv + vv];
+        }
         }
         if (!KDA) acc2 *= sWd[c];
         sdR[c * ldv + vv] = acc + acc2;
@@ -856,9 +906,16 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
       int slot = 0;
       for (int kk = warp * STREAMS + sub; kk < K; kk += 8 * STREAMS, ++slot) {
         float acc = 0.f;
+        if constexpr (KDA && VS == 32) {
+          acc = bcast_dot([&](int i) { return __expf(sG[i * ldk + kk]) * sQ[i * ldq + kk]; },
+                          [&](int i) { return sdO[i * ldv + vv]; }, C, lane) -
+                bcast_dot([&](int i) { return __expf(sG[i * ldk + kk]) * sBeta[i] * sK[i * ldk + kk]; },
+                          [&](int i) { return sdR[i * ldv + vv]; }, C, lane);
+        } else {
         for (int i = 0; i < C; ++i) {
           const float eg = KDA ? __expf(sG[i * ldk + kk]) : sEG[i];
           acc += eg * (sQ[i * ldq + kk] * sdO[i * ldv + vv] - sBeta[i] * sK[i * ldk + kk] * sdR[i * ldv + vv]);
+        }
         }
         const float ds1 = sdS[kk * ldv + vv];
         float t = ds1 * sS0[kk * ldv + vv] * sEL[kk];
