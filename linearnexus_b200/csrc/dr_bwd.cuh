@@ -35,10 +35,13 @@
 namespace dr {
 
 constexpr int kBwThreads = 256;
+#ifndef DR_BWD_EXACT_THREADS
+#define DR_BWD_EXACT_THREADS 512
+#endif
 constexpr int kBwSlice = 32;   // value columns per adjoint CTA, every variant (KDA at K = 128: 204 KB of shared memory)
 // the tensor-core adjoint runs 16 warps: its phases are short dependent chains of mma.sync and shared-memory
 // fetches, and four warps per scheduler hide them where two did not
-__host__ __device__ constexpr int bwd_threads(bool tc) { return tc ? 512 : 256; }
+__host__ __device__ constexpr int bwd_threads(bool tc) { return tc ? 512 : DR_BWD_EXACT_THREADS; }
 
 // Row-panel products on the warp-level tensor-core path (mma.sync m16n8k8, tf32 operands, fp32 accumulate);
 // a(m, k), b(k, n) are element accessors into fp32 shared memory.  Lane (g = lane/4, t = lane%4) ends up with
@@ -495,7 +498,7 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
       }
     } else {
     {
-      constexpr int RPW = 8;  // rows per warp pass
+      constexpr int RPW = NW;  // rows per warp pass
       const int vv = lane % VS, sub = lane / VS;  // VS = 16: two row streams per warp
       constexpr int STREAMS = 32 / VS;
       for (int c = warp * STREAMS + sub; c < C; c += RPW * STREAMS) {
@@ -578,7 +581,7 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
     {
       const int vv = lane % VS, sub = lane / VS;
       constexpr int STREAMS = 32 / VS;
-      for (int c = warp * STREAMS + sub; c < C; c += 8 * STREAMS) {
+      for (int c = warp * STREAMS + sub; c < C; c += NW * STREAMS) {
         float acc = 0.f;
         for (int i = c; i < C; ++i) acc += sA[i * lda + c] * Eij(i, c) * sdO[i * ldv + vv];
         float acc2 = 0.f;
@@ -780,7 +783,7 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
     {
       const int nkk = K / 32 + (K % 32 ? 1 : 0);
       float extraL[4] = {0.f, 0.f, 0.f, 0.f};  // dG_L contribution, per channel slot of this lane (K <= 128)
-      for (int i = warp; i < C; i += 8) {
+      for (int i = warp; i < C; i += NW) {
         float dgrow = 0.f, dbrow = 0.f;
         for (int ks = 0; ks < nkk; ++ks) {
           const int kk = lane + 32 * ks;
@@ -904,7 +907,7 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
       const int vv = lane % VS, sub = lane / VS;
       constexpr int STREAMS = 32 / VS;
       int slot = 0;
-      for (int kk = warp * STREAMS + sub; kk < K; kk += 8 * STREAMS, ++slot) {
+      for (int kk = warp * STREAMS + sub; kk < K; kk += NW * STREAMS, ++slot) {
         float acc = 0.f;
         if constexpr (KDA && VS == 32) {
           acc = bcast_dot([&](int i) { return __expf(sG[i * ldk + kk]) * sQ[i * ldq + kk]; },
@@ -934,7 +937,7 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
       const int vv = lane % VS, sub = lane / VS;
       constexpr int STREAMS = 32 / VS;
       int slot = 0;
-      for (int kk = warp * STREAMS + sub; kk < K; kk += 8 * STREAMS, ++slot) sdS[kk * ldv + vv] = ds_new[slot];
+      for (int kk = warp * STREAMS + sub; kk < K; kk += NW * STREAMS, ++slot) sdS[kk * ldv + vv] = ds_new[slot];
     }
     }
     BPROF(160);
@@ -1339,7 +1342,7 @@ inline cudaError_t launch_bwd_adjoint(const DrDesc* d, const void* q, const void
     const size_t smem = bwd_layout(C, K, VS, true).total * sizeof(float);
     e = cudaFuncSetAttribute(bwd_chunk_kernel<VS, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    bwd_chunk_kernel<VS, true, false><<<(unsigned)(units * ((V + VS - 1) / VS)), kBwThreads, smem, stream>>>(p);
+    bwd_chunk_kernel<VS, true, false><<<(unsigned)(units * ((V + VS - 1) / VS)), bwd_threads(false), smem, stream>>>(p);
   } else {
     constexpr int VS = 32;
     // bf16 inputs with whole 16x8 tiles: the products run on the tensor cores (tf32); fp32 inputs stay exact
@@ -1361,7 +1364,7 @@ inline cudaError_t launch_bwd_adjoint(const DrDesc* d, const void* q, const void
     } else {
       e = cudaFuncSetAttribute(bwd_chunk_kernel<VS, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return e;
-      bwd_chunk_kernel<VS, false, false><<<(unsigned)(units * ((V + VS - 1) / VS)), kBwThreads, smem, stream>>>(p);
+      bwd_chunk_kernel<VS, false, false><<<(unsigned)(units * ((V + VS - 1) / VS)), bwd_threads(false), smem, stream>>>(p);
     }
   }
   e = cudaGetLastError();
