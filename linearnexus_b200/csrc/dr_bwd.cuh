@@ -173,14 +173,14 @@ struct BwdSmem {
 __host__ __device__ inline BwdSmem bwd_layout(int C, int K, int VS, bool kda, bool tc = false) {
   BwdSmem L;
   L.ldk = K + 4; L.ldq = tc ? K + 8 : K + 4;
-  L.lda = tc ? 72 : C + 1; L.ldt = sm100::LDT; L.ldv = tc ? VS + 8 : VS + 1;
+  L.lda = tc ? 72 : kda ? sm100::LDT : C + 1; L.ldt = sm100::LDT; L.ldv = tc ? VS + 8 : VS + 1;
   size_t o = 0;
   L.q = o; o += (size_t)C * L.ldq;
   L.k = o; o += (size_t)C * L.ldk;
   L.g = o; o += kda ? (size_t)C * L.ldk : 0;
   L.x = o; o += (size_t)C * L.lda;
   L.a = o; o += (size_t)C * L.lda;
-  L.t = o; o += tc ? (size_t)C * L.ldt : 0;
+  L.t = o; o += (tc || kda) ? (size_t)C * L.ldt : 0;
   L.v = o; o += (size_t)C * L.ldv;
   L.d_o = o; o += (size_t)C * L.ldv;
   L.vn = o; o += (size_t)C * L.ldv;
@@ -476,6 +476,8 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
     __syncthreads();
     BPROF(153);
     auto ld2 = [](const float* ptr) { return *reinterpret_cast<const float2*>(ptr); };
+    // explicit inverse (tf32 merge products) instead of the substitutions: exact-path kernel, bf16 inputs only
+    const bool use_inv = KDA && !TC && NW == 16 && C == 64 && p.qkv_dt == DR_BF16;
     auto Eij = [&](int i, int j) -> float { return (KDA || TC) ? 1.f : __expf(fminf(sGs[i] - sGs[j], 0.f)); };
     // ---- R = beta V - (beta K^ e^G) S0  (lane = value column, warp = rows) ----------------------------
     if constexpr (TC) {
@@ -538,6 +540,27 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
 #pragma unroll
         for (int e = 0; e < 4; ++e)
           sVn[(m0 + g + (e >> 1) * 8) * ldv + n0 + 8 * nt + 2 * t + (e & 1)] = d[nt][e];
+    } else if (use_inv) {
+      // (bf16 inputs of the per-channel variant) the blocked inverse of the forward kernels instead of 63 dependent
+      // steps, then Vn = T R with four rows per thread
+      if (tid < 256) sm100::block_inverse_64(sX, sBeta, sT, tid);
+      __syncthreads();
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      if (lane < VS) {
+        for (int j = 0; j < 64; ++j) {
+          const float x = sVn[j * ldv + lane];
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            const int i = warp + 16 * r;
+            acc[r] += (j <= i ? sT[i * ldt + j] : 0.f) * x;
+          }
+        }
+      }
+      __syncthreads();
+      if (lane < VS) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) sVn[(warp + 16 * r) * ldv + lane] = acc[r];
+      }
     } else
     if (tid < 8 * VS) {
       const int col = tid >> 3, l8 = tid & 7;
@@ -617,6 +640,23 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
 #pragma unroll
         for (int e = 0; e < 4; ++e)
           sdR[(m0 + g + (e >> 1) * 8) * ldv + n0 + 8 * nt + 2 * t + (e & 1)] = d[nt][e];
+    } else if (use_inv) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};   // dR = T^T dVn
+      if (lane < VS) {
+        for (int j = 0; j < 64; ++j) {
+          const float x = sdR[j * ldv + lane];
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            const int i = warp + 16 * r;
+            acc[r] += (j >= i ? sT[j * ldt + i] : 0.f) * x;
+          }
+        }
+      }
+      __syncthreads();
+      if (lane < VS) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) sdR[(warp + 16 * r) * ldv + lane] = acc[r];
+      }
     } else
     if (tid < 8 * VS) {
       const int col = tid >> 3, l8 = tid & 7;
