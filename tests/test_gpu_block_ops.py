@@ -148,3 +148,22 @@ def test_block_ops_full_size_properties():
     y1 = BO.rmsnorm_gated(o, wn, eps=0.0)
     y2 = BO.rmsnorm_gated(o * 4, wn, eps=0.0)
     assert torch.isfinite(y1.float()).all() and torch.equal(y1, y2)
+
+
+def test_block_ops_against_golden_vectors():
+    """The kernels on the committed fixtures (float64 oracle outputs, tests/golden/make_block_ops_golden.py)."""
+    import numpy as np
+    from pathlib import Path
+    G = np.load(Path(__file__).parent / "golden" / "block_ops_golden.npz")
+    c = lambda k: torch.from_numpy(G[k]).cuda()
+    y, nc = BO.short_conv_silu(c("conv.x"), c("conv.w"), c("conv.bias"), cache=c("conv.cache"))
+    _close(y, torch.from_numpy(G["conv.y"]), torch.float32)
+    assert torch.equal(nc.cpu(), torch.from_numpy(G["conv.new_cache"]))
+    g, beta = BO.gated_deltanet_gates(c("gdn_gate.a"), c("gdn_gate.b"), c("gdn_gate.A_log"), c("gdn_gate.dt_bias"), True)
+    _close(g, torch.from_numpy(G["gdn_gate.g"]), torch.float32)
+    _close(beta, torch.from_numpy(G["gdn_gate.beta"]), torch.float32)
+    gk, bk = BO.kda_gate(c("kda_gate.g"), c("kda_gate.A_log"), 8, c("kda_gate.g_bias"), c("kda_gate.beta"))
+    _close(gk, torch.from_numpy(G["kda_gate.g_out"]), torch.float32)
+    _close(bk, torch.from_numpy(G["kda_gate.beta_out"]), torch.float32)
+    yn = BO.rmsnorm_gated(c("norm.o"), c("norm.w"), c("norm.gate"), eps=1e-5)
+    _close(yn, torch.from_numpy(G["norm.y"]), torch.float32)

@@ -179,3 +179,20 @@ def test_block_ops_oracle_against_torch_primitives():
     assert torch.allclose(yn, o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + 1e-5) * wt * torch.sigmoid(gate), atol=1e-6)
     gk, bk = BO.kda_gate(torch.full((1, 1, 4), 30.0), torch.zeros(2), 2, None, torch.zeros(1, 1, 2))
     assert torch.allclose(gk, torch.full((1, 1, 2, 2), -30.0)) and torch.allclose(bk, torch.full((1, 1, 2), 0.5))
+
+
+def test_block_ops_oracle_fp32_against_golden():
+    """The fp32 restatement of the block steps against the committed float64 vectors."""
+    import numpy as np
+    from pathlib import Path
+    from oracle import block_ops_oracle as BO
+    G = np.load(Path(__file__).parent / "golden" / "block_ops_golden.npz")
+    T_ = lambda k: torch.from_numpy(G[k])
+    y, nc = BO.short_conv_silu(T_("conv.x"), T_("conv.w"), T_("conv.bias"), T_("conv.cache"))
+    assert (y.double() - T_("conv.y")).abs().max() < 1e-5 and torch.equal(nc, T_("conv.new_cache"))
+    g, beta = BO.gdn_gate_activations(T_("gdn_gate.a"), T_("gdn_gate.b"), T_("gdn_gate.A_log"), T_("gdn_gate.dt_bias"), True)
+    assert (g.double() - T_("gdn_gate.g")).abs().max() < 1e-5 and (beta.double() - T_("gdn_gate.beta")).abs().max() < 1e-6
+    gk, bk = BO.kda_gate(T_("kda_gate.g"), T_("kda_gate.A_log"), 8, T_("kda_gate.g_bias"), T_("kda_gate.beta"))
+    assert (gk.double() - T_("kda_gate.g_out")).abs().max() < 1e-4 and (bk.double() - T_("kda_gate.beta_out")).abs().max() < 1e-6
+    yn = BO.gated_rmsnorm(T_("norm.o").transpose(1, 2), T_("norm.w"), T_("norm.gate"), eps=1e-5)
+    assert (yn.double() - T_("norm.y")).abs().max() < 1e-5
