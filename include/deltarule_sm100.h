@@ -98,6 +98,19 @@ int dr_last_cuda_error(void);
  * benchmark reports the difference across its timed region. */
 uint64_t dr_launch_count(void);
 
+/*
+ * Device status word.  Kernels never trap and never wait without a limit; a wait that runs out ORs
+ * DR_DEV_TIMEOUT into the int32 the caller passed as `status_dev` and the kernel finishes (its results are
+ * then meaningless).  Entry points do not synchronise, so they cannot return that outcome themselves:
+ * dr_check_status copies the word back on `stream`, WAITS for the stream, and returns DR_ERR_DEVICE if any
+ * kernel enqueued before it reported a problem (the word is cleared so that the next check starts clean;
+ * dr_last_device_status() then gives the DR_DEV_* bits that were found), DR_OK otherwise.  Call it where the
+ * host synchronises anyway (end of a step, before results are consumed).  The reference has no counterpart:
+ * its one GPU kernel falls back silently (modules/linear_attn/delta_net.py:150-156).
+ */
+int dr_check_status(int32_t* status_dev, void* stream);
+int dr_last_device_status(void);
+
 /* Name of the kernel family the most recent call on this thread dispatched to
  * ("step", "recurrent", "chunk_fp32", "chunk_tcgen05", "bwd", ...). */
 const char* dr_last_path(void);
@@ -105,8 +118,10 @@ const char* dr_last_path(void);
 /* Bytes of caller-provided scratch that dr_chunk_fwd (op=0) or dr_chunk_bwd (op=1)
  * needs for `desc`; 0 when none is needed.  Negative DrStatus (cast) on a bad desc.
  * For op=0 the figure is what the path desc->path resolves to would use; a forward that is
- * given less falls back to a kernel that needs none when path is DR_PATH_AUTO and returns
- * DR_ERR_WORKSPACE when the path was requested explicitly. */
+ * given less returns DR_ERR_WORKSPACE (there is no silent downgrade to a slower kernel: ask for
+ * DR_PATH_FP32 to run without scratch).
+ * op=1 returns DR_ERR_UNSUPPORTED for shapes the backward does not cover: chunk > 64, K > 128,
+ * or DR_KDA with K % 16 != 0 (the forward entry points accept those shapes). */
 int64_t dr_workspace_bytes(const DrDesc* desc, int op);
 
 /*
@@ -143,9 +158,12 @@ int dr_recurrent_fwd(const DrDesc* desc, const void* q, const void* k, const voi
  * q,k [B,H,K]  v [B,H,V]  g [B,H] or [B,H,K]  beta [B,H] float32.
  * state_in/state_out: float32 [B,H,K,V]; they may be the same pointer (in-place update of
  * the decode cache, the case the kernel is tuned for).  o [B,H,V] in desc->out_dtype.
+ * status_dev as in dr_chunk_fwd; a unit whose state never arrived in shared memory (bounded wait ran out)
+ * is NOT written back, so a reported time-out leaves the cache entries it touched as they were.
  */
 int dr_step(const DrDesc* desc, const void* q, const void* k, const void* v, const void* g,
-            const float* beta, const float* state_in, float* state_out, void* o, void* stream);
+            const float* beta, const float* state_in, float* state_out, void* o, int32_t* status_dev,
+            void* stream);
 
 /*
  * Training-step pair: ONE forward per step instead of two.  dr_chunk_bwd recomputes the forward to get the
@@ -231,16 +249,6 @@ int dr_gate_activations(int mode, const void* a, const void* b, const float* A_l
                         float threshold, void* stream);
 int dr_gated_rmsnorm(const void* o, const void* gate, const float* weight, void* y, int B, int H, int T, int V,
                      int o_layout, int o_dtype, int gate_dtype, int y_dtype, float eps, void* stream);
-
-/*
- * Debug entry with no counterpart in the reference: runs one 128 x n x kd bf16 product
- * D = A * B^T through the tcgen05/TMEM plumbing the chunk kernel uses (A [128][kd] row-major
- * read from shared memory or staged in tensor memory; B given as [n][kd] (K-major) or as
- * [kd][n] (MN-major)), so the GPU tests can pin the descriptor encodings against a plain
- * matmul.  n in {64,128}; kd in {32,64,96,128}.  d_out: float32 [128][n].
- */
-int dr_debug_umma_selftest(const void* a, const void* b, float* d_out, int kd, int n, int a_in_tmem,
-                           int b_mn_major, int32_t* status_dev, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,34 @@
+/*
+ * deltarule_sm100 -- test and bring-up entry points of the library.  None has a counterpart in the
+ * reference; production callers need only deltarule_sm100.h.
+ */
+#ifndef DELTARULE_SM100_DEBUG_H_
+#define DELTARULE_SM100_DEBUG_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/*
+ * Runs one 128 x n x kd bf16 product D = A * B^T through the tcgen05/TMEM plumbing the chunk kernels
+ * use (A [128][kd] row-major read from shared memory or staged in tensor memory; B given as [n][kd]
+ * (K-major) or as [kd][n] (MN-major)), so the GPU tests can pin the descriptor encodings against a
+ * plain matmul.  n in {64,128}; kd in {32,64,96,128}.  d_out: float32 [128][n].
+ */
+int dr_debug_umma_selftest(const void* a, const void* b, float* d_out, int kd, int n, int a_in_tmem,
+                           int b_mn_major, int32_t* status_dev, void* stream);
+
+/*
+ * Exercises the error path of the bounded waits without faulting anything: one warp waits, with the
+ * kernels' own wait routine limited to `attempts` tries (1..4096), on an mbarrier that nothing arrives
+ * on.  The wait gives up, DR_DEV_TIMEOUT is ORed into *status_dev and the kernel returns normally; the
+ * CUDA context stays usable.
+ */
+int dr_debug_wait_timeout(int32_t* status_dev, uint32_t attempts, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DELTARULE_SM100_DEBUG_H_ */

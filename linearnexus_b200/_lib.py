@@ -26,10 +26,14 @@ DR_F32, DR_BF16 = 0, 1
 DR_LAYOUT_BHTD, DR_LAYOUT_BTHD = 0, 1
 DR_PATH_AUTO, DR_PATH_FP32, DR_PATH_TCGEN05, DR_PATH_SPLIT = 0, 1, 2, 3
 
+# bits of the device status word (DR_DEV_* in include/deltarule_sm100.h)
+DEVICE_STATUS_BITS = {1: "a bounded wait on an mbarrier ran out", 2: "an index check failed"}
+
 EXPORTS = ["dr_version", "dr_strerror", "dr_last_cuda_error", "dr_launch_count", "dr_last_path",
            "dr_workspace_bytes", "dr_chunk_fwd", "dr_recurrent_fwd", "dr_step", "dr_chunk_bwd",
            "dr_debug_umma_selftest", "dr_chunk_bwd_static", "dr_chunk_fwd_saving", "dr_chunk_bwd_saved",
-           "dr_short_conv_silu", "dr_gate_activations", "dr_gated_rmsnorm"]
+           "dr_short_conv_silu", "dr_gate_activations", "dr_gated_rmsnorm", "dr_check_status",
+           "dr_last_device_status", "dr_debug_wait_timeout"]
 
 
 class DrDesc(ctypes.Structure):
@@ -113,7 +117,12 @@ def load() -> ctypes.CDLL:
         lib.dr_recurrent_fwd.restype = ctypes.c_int
         lib.dr_recurrent_fwd.argtypes = [dp, vp, vp, vp, vp, fp, fp, vp, fp, vp]
         lib.dr_step.restype = ctypes.c_int
-        lib.dr_step.argtypes = [dp, vp, vp, vp, vp, fp, fp, fp, vp, vp]
+        lib.dr_step.argtypes = [dp, vp, vp, vp, vp, fp, fp, fp, vp, ip, vp]
+        lib.dr_check_status.restype = ctypes.c_int
+        lib.dr_check_status.argtypes = [ip, vp]
+        lib.dr_last_device_status.restype = ctypes.c_int
+        lib.dr_debug_wait_timeout.restype = ctypes.c_int
+        lib.dr_debug_wait_timeout.argtypes = [ip, ctypes.c_uint32, vp]
         lib.dr_chunk_bwd.restype = ctypes.c_int
         lib.dr_chunk_bwd.argtypes = [dp, vp, vp, vp, vp, fp, fp, vp, fp, vp, vp, vp, fp, fp, fp, vp,
                                      ctypes.c_size_t, ip, vp]
@@ -143,6 +152,9 @@ def check(status: int, where: str) -> None:
         text = lib.dr_strerror(status).decode()
         if status == -8:
             text += f" (cudaError {lib.dr_last_cuda_error()})"
+        if status == -10:
+            bits = lib.dr_last_device_status()
+            text += " (" + ", ".join(n for b, n in DEVICE_STATUS_BITS.items() if bits & b) + ")"
         raise DeltaRuleError(status, text, where)
 
 

@@ -6,6 +6,7 @@
 #include <mutex>
 
 #include "deltarule_sm100.h"
+#include "deltarule_sm100_debug.h"
 #include "dr_chunk_fp32.cuh"
 #include "dr_chunk_sm100.cuh"
 #include "dr_kda_sm100.cuh"
@@ -20,6 +21,7 @@ namespace {
 
 std::atomic<uint64_t> g_launches{0};
 thread_local int tl_cuda_error = 0;
+thread_local int tl_device_status = 0;
 thread_local const char* tl_path = "none";
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -162,16 +164,15 @@ int dr_chunk_fwd(const DrDesc* d, const void* q, const void* k, const void* v, c
   if (path == DR_PATH_SPLIT) {
     if (!split_eligible(d)) return DR_ERR_UNSUPPORTED;
     const int64_t need = dr::kda::workspace_bytes((int64_t)d->B * d->H, d->T);
-    if (!workspace || (int64_t)workspace_bytes < need || !aligned16(workspace)) {
-      if (d->path != DR_PATH_AUTO) return workspace && !aligned16(workspace) ? DR_ERR_ALIGN : DR_ERR_WORKSPACE;
-      path = DR_PATH_FP32;   // no scratch given: the kernel that needs none
-    } else {
-      tl_path = "chunk_split_tcgen05";
-      int launches = 0;
-      cudaError_t e = dr::kda::launch_chunk(p, workspace, st, &launches);
-      g_launches.fetch_add(launches);
-      return check_cuda(e);
-    }
+    // no silent downgrade to the (much slower) kernel that needs no scratch: the caller asks for that one
+    // with DR_PATH_FP32
+    if (workspace && !aligned16(workspace)) return DR_ERR_ALIGN;
+    if (!workspace || (int64_t)workspace_bytes < need) return DR_ERR_WORKSPACE;
+    tl_path = "chunk_split_tcgen05";
+    int launches = 0;
+    cudaError_t e = dr::kda::launch_chunk(p, workspace, st, &launches);
+    g_launches.fetch_add(launches);
+    return check_cuda(e);
   }
   if (path == DR_PATH_TCGEN05) {
     if (!tcgen05_eligible(d)) return DR_ERR_UNSUPPORTED;
@@ -204,7 +205,7 @@ int dr_recurrent_fwd(const DrDesc* d, const void* q, const void* k, const void* 
 }
 
 int dr_step(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
-            const float* beta, const float* state_in, float* state_out, void* o, void* stream) {
+            const float* beta, const float* state_in, float* state_out, void* o, int32_t* status_dev, void* stream) {
   int s = validate_common(d, false);
   if (s != DR_OK) return s;
   if (d->T != 1) return DR_ERR_SHAPE;
@@ -222,27 +223,38 @@ int dr_step(const DrDesc* d, const void* q, const void* k, const void* v, const 
   g_launches.fetch_add(1);
   const int64_t units = (int64_t)d->B * d->H;
   const int sms = sm_count();
-#ifndef DR_NO_STEP_STREAM   // (A/B builds of the benchmark compare against the one-CTA-per-unit kernel)
   if (sms > 0 && dr::step_stream_eligible(p, units, sms)) {
     tl_path = "step_stream";
-    return check_cuda(dr::launch_step_stream(p, units, sms, reinterpret_cast<cudaStream_t>(stream)));
+    return check_cuda(dr::launch_step_stream(p, units, sms, status_dev, reinterpret_cast<cudaStream_t>(stream)));
   }
-#else
-  (void)sms;
-#endif
   tl_path = "step";
   return check_cuda(dr::launch_step(p, units, reinterpret_cast<cudaStream_t>(stream)));
 }
 
-#ifdef DR_PROFILE
-// Profiling builds only: copies (and clears) the per-phase cycle counters of the chunk kernel.
-int dr_debug_read_profile(unsigned long long* out64_host) {
-  cudaError_t e = cudaMemcpyFromSymbol(out64_host, dr::sm100::g_prof, sizeof(unsigned long long) * 192);
+int dr_check_status(int32_t* status_dev, void* stream) {
+  if (!status_dev) return DR_ERR_NULL;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int32_t host = 0;
+  cudaError_t e = cudaMemcpyAsync(&host, status_dev, sizeof(host), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
   if (e != cudaSuccess) return check_cuda(e);
-  unsigned long long z[192] = {0};
-  return check_cuda(cudaMemcpyToSymbol(dr::sm100::g_prof, z, sizeof(z)));
+  if (host == DR_DEV_OK) return DR_OK;
+  e = cudaMemsetAsync(status_dev, 0, sizeof(host), st);   // reported once: the next check starts clean
+  if (e != cudaSuccess) return check_cuda(e);
+  tl_device_status = host;
+  return DR_ERR_DEVICE;
 }
-#endif
+
+int dr_last_device_status(void) { return tl_device_status; }
+
+int dr_debug_wait_timeout(int32_t* status_dev, uint32_t attempts, void* stream) {
+  if (!status_dev) return DR_ERR_NULL;
+  if (attempts < 1 || attempts > 4096) return DR_ERR_SHAPE;
+  tl_path = "wait_timeout";
+  g_launches.fetch_add(1);
+  dr::sm100::wait_timeout_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(status_dev, attempts);
+  return check_cuda(cudaGetLastError());
+}
 
 int dr_debug_umma_selftest(const void* a, const void* b, float* d_out, int kd, int n, int a_in_tmem,
                             int b_mn_major, int32_t* status_dev, void* stream) {
@@ -258,7 +270,6 @@ int dr_chunk_bwd(const DrDesc* d, const void* q, const void* k, const void* v, c
                  const float* beta, const float* h0, const void* d_o, const float* d_hT, void* dq,
                  void* dk, void* dv, float* dbeta, float* dg, float* dh0, void* workspace,
                  size_t workspace_bytes, int32_t* status_dev, void* stream) {
-  (void)status_dev;
   int s = validate_common(d, true);
   if (s != DR_OK) return s;
   if (!q || !k || !v || !beta || !d_o || !dq || !dk || !dv || !dbeta) return DR_ERR_NULL;
@@ -273,7 +284,7 @@ int dr_chunk_bwd(const DrDesc* d, const void* q, const void* k, const void* v, c
   tl_path = "bwd";
   int launches = 0;
   cudaError_t e = dr::launch_bwd(d, q, k, v, g, beta, h0, d_o, d_hT, dq, dk, dv, dbeta, dg, dh0,
-                                 workspace, reinterpret_cast<cudaStream_t>(stream), &launches);
+                                 workspace, status_dev, reinterpret_cast<cudaStream_t>(stream), &launches);
   g_launches.fetch_add(launches);
   return check_cuda(e);
 }
@@ -281,7 +292,6 @@ int dr_chunk_bwd(const DrDesc* d, const void* q, const void* k, const void* v, c
 int dr_chunk_fwd_saving(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
                         const float* beta, const float* h0, void* o, float* hT, void* workspace,
                         size_t workspace_bytes, int32_t* status_dev, void* stream) {
-  (void)status_dev;
   int s = validate_common(d, true);
   if (s != DR_OK) return s;
   s = validate_fwd_ptrs(d, q, k, v, g, beta, h0, o, hT);
@@ -292,7 +302,7 @@ int dr_chunk_fwd_saving(const DrDesc* d, const void* q, const void* k, const voi
   if (!aligned16(workspace)) return DR_ERR_ALIGN;
   tl_path = "fwd_saving";
   int launches = 0;
-  cudaError_t e = dr::launch_bwd_forward(d, q, k, v, g, beta, h0, o, hT, workspace,
+  cudaError_t e = dr::launch_bwd_forward(d, q, k, v, g, beta, h0, o, hT, workspace, status_dev,
                                          reinterpret_cast<cudaStream_t>(stream), &launches);
   g_launches.fetch_add(launches);
   return check_cuda(e);
@@ -302,7 +312,7 @@ int dr_chunk_bwd_saved(const DrDesc* d, const void* q, const void* k, const void
                        const float* beta, const void* d_o, const float* d_hT, void* dq, void* dk, void* dv,
                        float* dbeta, float* dg, float* dh0, void* workspace, size_t workspace_bytes,
                        int32_t* status_dev, void* stream) {
-  (void)status_dev;
+  (void)status_dev;   // the adjoint kernels have no bounded waits: nothing can be reported here
   int s = validate_common(d, true);
   if (s != DR_OK) return s;
   if (!q || !k || !v || !beta || !d_o || !dq || !dk || !dv || !dbeta) return DR_ERR_NULL;
@@ -355,7 +365,6 @@ int dr_chunk_bwd_static(const DrDesc* d, const void* q, const void* k, const voi
                         const float* beta, const float* h0, const void* d_o, const float* d_hT, void* dq,
                         void* dk, void* dv, float* dbeta, float* dg, float* dh0, int32_t* status_dev,
                         void* stream) {
-  (void)status_dev;
   int s = validate_common(d, true);
   if (s != DR_OK) return s;
   if (!q || !k || !v || !beta || !d_o || !dq || !dk || !dv || !dbeta) return DR_ERR_NULL;
@@ -374,7 +383,7 @@ int dr_chunk_bwd_static(const DrDesc* d, const void* q, const void* k, const voi
   int launches = 0;
   // launch_bwd zeroes the accumulators it adds into and overwrites the checkpoints before reading them,
   // so whatever an earlier call left in the array is never consumed.
-  cudaError_t e = dr::launch_bwd(d, q, k, v, g, beta, h0, d_o, d_hT, dq, dk, dv, dbeta, dg, dh0, scratch,
+  cudaError_t e = dr::launch_bwd(d, q, k, v, g, beta, h0, d_o, d_hT, dq, dk, dv, dbeta, dg, dh0, scratch, status_dev,
                                  reinterpret_cast<cudaStream_t>(stream), &launches);
   g_launches.fetch_add(launches);
   return check_cuda(e);
@@ -386,7 +395,8 @@ int dr_short_conv_silu(const void* x, const float* weight, const float* bias, co
   if (dtype != DR_F32 && dtype != DR_BF16) return DR_ERR_DTYPE;
   if (B < 1 || T < 1 || C < 1 || W < 1 || W > dr::blk::kConvMaxW || C % 8) return DR_ERR_SHAPE;
   if (B > 65535 || (T + 15) / 16 > 65535) return DR_ERR_SHAPE;
-  if (!aligned16(x) || !aligned16(y) || (cache_in && !aligned16(cache_in)) || (cache_out && !aligned16(cache_out)))
+  if (!aligned16(x) || !aligned16(y) || (cache_in && !aligned16(cache_in)) || (cache_out && !aligned16(cache_out)) ||
+      (W > 1 && !aligned16(weight)) || (bias && !aligned16(bias)))   // the kernel reads taps and bias as float4
     return DR_ERR_ALIGN;
   if (x == y) return DR_ERR_UNSUPPORTED;   // a tile reads the rows before it: not in place
   if (cache_out && cache_out == cache_in && T > dr::blk::kConvSteps) return DR_ERR_UNSUPPORTED;

@@ -1314,12 +1314,12 @@ inline int64_t bwd_workspace_bytes(const DrDesc* d) {
 // accumulator part of the workspace (262 KB per chunk there against 82 KB of records; the adjoint overwrites it).
 inline cudaError_t launch_bwd_forward(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
                                       const float* beta, const float* h0, void* o, float* hT, void* workspace,
-                                      cudaStream_t stream, int* launches) {
+                                      int32_t* status, cudaStream_t stream, int* launches) {
   const int C = d->chunk, K = d->K, V = d->V;
   const int64_t N = (d->T + C - 1) / C, units = (int64_t)d->B * d->H;
   float* ckpt = reinterpret_cast<float*>(workspace);
   FwdParams f;
-  f.q = q; f.k = k; f.v = v; f.g = g; f.beta = beta; f.h0 = h0; f.o = o; f.hT = hT; f.status = nullptr;
+  f.q = q; f.k = k; f.v = v; f.g = g; f.beta = beta; f.h0 = h0; f.o = o; f.hT = hT; f.status = status;
   f.ckpt = ckpt;
   f.map.B = d->B; f.map.H = d->H; f.map.T = d->T; f.map.bthd = d->layout == DR_LAYOUT_BTHD;
   f.map.Hq = d->qk_heads > 0 ? d->qk_heads : d->H;
@@ -1426,8 +1426,9 @@ inline cudaError_t launch_bwd_adjoint(const DrDesc* d, const void* q, const void
 inline cudaError_t launch_bwd(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
                               const float* beta, const float* h0, const void* d_o, const float* d_hT, void* dq,
                               void* dk, void* dv, float* dbeta, float* dg, float* dh0, void* workspace,
-                              cudaStream_t stream, int* launches) {
-  cudaError_t e = launch_bwd_forward(d, q, k, v, g, beta, h0, nullptr, nullptr, workspace, stream, launches);
+                              int32_t* status, cudaStream_t stream, int* launches) {
+  // only the forward has bounded waits that can report; the adjoint kernels synchronise with block barriers
+  cudaError_t e = launch_bwd_forward(d, q, k, v, g, beta, h0, nullptr, nullptr, workspace, status, stream, launches);
   if (e != cudaSuccess) return e;
   return launch_bwd_adjoint(d, q, k, v, g, beta, d_o, d_hT, dq, dk, dv, dbeta, dg, dh0, workspace, stream, launches);
 }

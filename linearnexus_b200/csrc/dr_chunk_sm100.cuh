@@ -5,34 +5,35 @@
 // whole sequence (S^T: lane = value column v, column = key row k), so every product has
 // M = 128 and each epilogue thread owns one value column.
 //
-// Two groups of eight warps run as a two-stage pipeline over the chunks of the sequence (two
-// warps share each 32-lane quarter of tensor memory and split the columns of every epilogue):
+// Four groups of four warps (one warp per 32-lane quarter of tensor memory in each group) form a
+// pipeline over the chunks of the sequence.  Each group has its own instruction stream, so the short
+// dependent phases of one group fill the issue slots the others leave idle:
 //
-//   PRODUCER (warps 0-7): everything that does not depend on the state.
-//     Raw K,Q rows of a chunk land by TMA as one [K;Q] tile already in core-matrix order, two chunks
-//     ahead (3-deep ring).  The l2 norms are not applied to the tiles: they are folded into row and
-//     column factors (rk from the diagonal of (1), rq from the raw Q rows).
+//   PA (warps 0-3)   state-independent, chunk n:
+//     K,Q rows land by TMA as one [K;Q] tile already in core-matrix order (3-deep ring, one chunk ahead).
+//     The l2 norms are not applied to the tiles: they are folded into row and column factors (rk from the
+//     diagonal of D1, rq from the raw Q rows).
 //     (1) D1 = [K;Q] K^T                             128x64x128  smem x smem, issued one chunk ahead
-//         X = D1[i][j] e^{G_i-G_j} (i>j, fp32);  A_qk = D1[64+i][j] e^{G_i-G_j} (i>=j) -> bf16 tile
-//         T = (I + diag(beta rk^2) X)^-1: 8x8 blocks by substitution, three merge levels on mma.sync tf32;
-//         the first two levels occupy warps 0-3 while warps 4-7 issue (1) of the next chunk, scan its
-//         decay and take the query norms
+//         X = D1[i][j] e^{G_i-G_j} (i>j, fp32) -> fp32 matrix;  A_qk = D1[64+i][j] e^{G_i-G_j} (i>=j) -> bf16 tile
+//   PB (warps 4-7)   chunk n, one hand-over behind PA:
+//         T = (I + diag(beta rk^2) X)^-1 in place: 8x8 blocks by substitution, three merge levels on mma.sync tf32
 //         -> Tb = T diag(beta rk), Tw = T diag(beta e^G rk^2)   bf16 tiles
-//   CONSUMER (warps 8-15): the serial chain over the state.
+//   CB (warps 12-15) the products and copies that feed or drain the chain:
 //     (2) U^T = V^T Tb^T  -> TMEM (stage accumulator)  128x64x64   smem(MN-major) x smem
-//         W^T = K^T Tw^T  -> idle TMEM columns -> bf16 tile W      smem(MN-major) x smem
-//         (issued the moment the chunk is handed over; the next chunk's V rows are fetched when they complete)
+//         W^T = K^T Tw^T  -> idle TMEM columns -> bf16 tile W (MN-major B operand: 16-byte stores)
+//         output of the previous chunk: O^T[v][i] = rq_i (e^{G_i} Dq[v][i] + Do[v][i]) -> staging tile -> TMA store
+//   CA (warps 8-11)  the serial chain over the state:
 //         bf16 copy of S^T for the products; fp32 S^T pre-multiplied by e^{G_L}
 //     (3) V_new^T = U^T - S^T W^T  (accumulated onto U^T with negate-A)                    128x64x128
 //         Dq = S^T Q^T                                                                     128x64x128
-//     (4) Do = V_new^T A_qk^T                                                              128x64x64
+//         V_new^T -> bf16, plain and decayed by e^{G_L-G_c}
 //     (5) S^T += (V_new^T e^{G_L-G_c}) K   (K read MN-major)                                128x128x64
-//         O^T[v][i] = rq_i e^{G_i} Dq[v][i] + rq_i Do[v][i], written one chunk late so that it overlaps (3)
+//     (4) Do = V_new^T A_qk^T                                                              128x64x64
 //
 // The [K;Q] tile is stored once as 8x8 core matrices and serves as A and B of (1), MN-major
-// A of (2), K-major B of (3) and MN-major B of (5).  Every wait on an mbarrier is bounded; a
-// wait that runs out sets DR_DEV_TIMEOUT in the status word and the kernel finishes without
-// further waiting.
+// A of (2), K-major B of (3) and MN-major B of (5).  Hand-overs are mbarriers (arrive counts of a whole
+// group, or tcgen05.commit for product completion); every wait is bounded: a wait that runs out sets
+// DR_DEV_TIMEOUT in the status word and the kernel finishes without further waiting.
 #pragma once
 
 #include <cuda.h>
@@ -40,6 +41,7 @@
 #include <cstring>
 
 #include "dr_common.cuh"
+#include "dr_sm100_common.cuh"
 #include "dr_tcgen05.cuh"
 #include "dr_umma_selftest.cuh"
 
@@ -48,44 +50,57 @@ namespace sm100 {
 
 constexpr bool kAvailable = true;
 constexpr int kThreads = 512;
-constexpr int kGroup = 256;
-constexpr int kC = 64, kD = 128;
+constexpr int kGrp = 128;
 
 // tensor-memory columns (32-bit x 128 lanes each): 512 in total
 constexpr uint32_t TM_S = 0;      // S^T fp32                                   128
 constexpr uint32_t TM_SB = 128;   // bf16 copy of S^T (A operand)                 64
-constexpr uint32_t TM_D1 = 192;   // producer scratch: D1, then W^T               64
+constexpr uint32_t TM_D1 = 192;   // D1                                           64
 constexpr uint32_t TM_DU = 256;   // 2 stages x 64: U^T -> V_new^T -> Do          128
 constexpr uint32_t TM_DQ = 384;   // S^T Q^^T                                     64
-constexpr uint32_t TM_VA = 448;   // V_new^T bf16                                 32
+constexpr uint32_t TM_VA = 448;   // V_new^T bf16 (before that: W^T fp32, 64 columns from here)   32
 constexpr uint32_t TM_VB = 480;   // decayed V_new^T bf16                         32
 constexpr uint32_t TM_COLS = 512;
 
-// shared-memory map (bytes).  Per stage (two stages):
-constexpr int RBS = 16 * 128;                 // row-block stride of the 128-column core-matrix tiles
-constexpr int A_RBS = 8 * 128;                // row-block stride of the 64-column tiles
+// shared-memory map (bytes)
 constexpr int QK_TILE = 128 * 128 * 2;        // [K (64 rows); Q (64 rows)] x 128 raw bf16, 32 KB
 constexpr int SM_QKR = 0;                     // ring of 3 such tiles (chunk n uses tile n % 3)
 constexpr int SM_STAGE = 3 * QK_TILE;         // two stages follow
-constexpr int W_KBS = 144;                    // k-block stride of the W tile (padded: conflict-free 2-byte stores)
-constexpr int W_RBS = 16 * W_KBS;             // its row-block stride
-constexpr int ST_W = 0;                       // W [64][128] (18 KB padded); reused as the O staging tile
-constexpr int ST_AQK = ST_W + 8 * W_RBS;       // A_qk [64][64]                           8 KB
-constexpr int ST_SC = ST_AQK + 64 * 64 * 2;   // G, e^G, e^{G_L-G}, beta: 4 x 64 floats  1 KB
-constexpr int STAGE_BYTES = ST_SC + 4 * 64 * 4;
-// Producer-private:
+constexpr int ST_W = 0;                       // W as [128 k][64 c] core matrices (16 KB); reused as the O staging tile
+constexpr int ST_AQK = ST_W + 128 * 64 * 2;   // A_qk [64][64]                           8 KB
+constexpr int STAGE_BYTES = ST_AQK + 64 * 64 * 2;
 constexpr int SM_V = SM_STAGE + 2 * STAGE_BYTES;  // V [64][128] core-matrix tile       16 KB
 constexpr int SM_TB = SM_V + 64 * 128 * 2;    // T diag(beta)        [64][64] bf16
 constexpr int SM_TW = SM_TB + 64 * 64 * 2;    // T diag(beta e^G)    [64][64] bf16
-constexpr int LDT = 68;                       // row stride (floats) of the fp32 64x64 matrices
-constexpr int SM_AKK = SM_TW + 64 * 64 * 2;   // A_kk fp32 [64][68]
-constexpr int SM_T32 = SM_AKK + 64 * LDT * 4; // T fp32 [64][68]
-constexpr int SM_TOTAL = SM_T32 + 64 * LDT * 4;
+constexpr int AKK_BYTES = 64 * LDT * 4;       // X, then T in place: fp32 [64][68]
+constexpr int SM_AKK = SM_TW + 64 * 64 * 2;   // two such matrices (chunk n uses n & 1)
+constexpr int SM_TOTAL = SM_AKK + 2 * AKK_BYTES;
 
-// Optional per-phase cycle counters (CTA 0 only), compiled in with -DDR_PROFILE.
+struct alignas(16) Ctl {
+  uint64_t full[2], empty[2], akk[2], akkfree[2], kq[3], vb, barP, barW, barUW, uwfree, wrdy, bar1, bar2s, bar2, oload;
+  alignas(16) float gb[3][128];      // raw beta (0..63) and g (64..127) of chunk m in slot m % 3
+  alignas(16) float sc[3][384];      // of chunk m in slot m % 3: G, e^G, e^{G_L-G}, beta (64 each); G log2(e) (64);
+                         // 2^{G2_32 - G2_j}, j < 32 (32); 2^{G2_i - G2_32}, i >= 32 (32)
+  alignas(16) float rq[2][64];       // per stage: scale / (||q_i|| + eps)
+  alignas(16) float keep[2][128];    // per stage, CB-private: rq_i e^{G_i} (0..63) and rq_i (64..127) of the chunk whose output is pending
+  alignas(16) float rk[2][64];       // per X buffer: 1 / (||k_j|| + eps)
+  alignas(16) float rs[2][64];       // per X buffer: beta_i rk_i^2, row factor of the unit-lower system
+  uint32_t tmem_base;
+  int abort;
+};
+
+// Kernel parameters: the common forward parameters plus the TMA tensor maps (see make_input_map /
+// make_output_map).  qc2/qc4 (vc2/vc4) are the fixed coordinates of this layout: the column-block origin
+// and the outermost index are derived from (b, h) in the kernel.
+struct alignas(64) Sm100Params {
+  CUtensorMap tk, tq, tv, to;
+  FwdParams p;
+  int use_tma_out;
+};
+
 #ifdef DR_PROFILE
 __device__ unsigned long long g_prof[192];
-#define PROF_DECL unsigned long long prof_t0 = clock64(); unsigned long long wt0 = 0; (void)wt0;
+#define PROF_DECL unsigned long long prof_t0 = clock64();
 #define PROF(idx)                                              \
   do {                                                         \
     if (blockIdx.x == 0 && gt == 0) {                          \
@@ -94,227 +109,59 @@ __device__ unsigned long long g_prof[192];
       prof_t0 = prof_t;                                        \
     }                                                          \
   } while (0)
-#define WSTART wt0 = clock64()
-#define WEND(idx)                                                                   \
-  do {                                                                              \
-    if (blockIdx.x == 0 && lane == 0) atomicAdd(&g_prof[48 + idx * 8 + (warp & 7)], clock64() - wt0); \
-  } while (0)
-#define IPROF_DECL unsigned long long ip0 = clock64();
-#define IPROF(idx)                                                                           \
-  do {                                                                                       \
-    if (blockIdx.x == 0 && gt == 0) { const unsigned long long t_ = clock64(); atomicAdd(&g_prof[idx], t_ - ip0); ip0 = t_; } \
-  } while (0)
 #else
-#define IPROF_DECL
-#define IPROF(idx)
 #define PROF_DECL
 #define PROF(idx)
-#define WSTART
-#define WEND(idx)
 #endif
 
-struct Ctl {
-  uint64_t full[2], empty[2], barP, barUW, uwfree, bar1, bar2, kq[3], vb;
-  float gb[3][128];      // raw beta (0..63) and g (64..127) of chunk m in slot m % 3
-  float sc[3][256];      // G, e^G, e^{G_L-G}, beta (64 each) of chunk m in slot m % 3
-  float eg_keep[2][64];  // rq_i e^{G_i} of the chunk whose output epilogue is still pending, per stage
-  float rq_keep[2][64];  // rq_i of that chunk
-  float rq[2][64];       // per stage: scale / (||q_i|| + eps)           (producer -> consumer)
-  float rk[64];          // 1 / (||k_j|| + eps)                           (producer-private)
-  float rs[64];          // beta_i rk_i^2: row factor of the unit-lower system
-  uint32_t tmem_base;
-  int abort;
-};
+// A shared-memory descriptor whose start address is `bytes` further on (the address field holds bytes / 16 and
+// cannot carry out of its 14 bits for addresses inside one CTA's shared memory).
+__device__ __forceinline__ uint64_t desc_adv(uint64_t d, uint32_t bytes) { return d + (uint64_t)(bytes >> 4); }
 
-__device__ __forceinline__ void group_sync(int id) { asm volatile("bar.sync %0, 256;" ::"r"(id) : "memory"); }
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
+struct SyncPB { __device__ __forceinline__ void operator()() const { group_sync128(2); } };
 
-// T = (I + diag(rs) A)^-1 for a strictly lower-triangular 64x64 A (fp32, row stride LDT).
-// 8x8 diagonal blocks by forward substitution on the CUDA cores, then three merge levels
-// (block size 8, 16, 32):  T_10 = -T_11 (diag(rs) A_10) T_00, each of the two products on the
-// warp-level tensor-core path (mma.sync m16n8k8, tf32 operands, fp32 accumulate) because these
-// tiny products are bound by shared-memory wavefronts, not flops, on the CUDA cores.
-// sT receives the lower triangle of T; entries above the diagonal are scratch (callers mask them).
-__device__ __forceinline__ uint32_t to_tf32(float x) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-  return r;
-}
-__device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
-}
-
-struct SyncGroup256 { __device__ __forceinline__ void operator()() const { group_sync(1); } };
-// the first four warps of a group only (barrier 3): the 8- and 16-wide merge levels have work for four warps
-struct SyncHalf128 { __device__ __forceinline__ void operator()() const { asm volatile("bar.sync 3, 128;" ::: "memory"); } };
-
-template <int BS, class Sync>
-__device__ __forceinline__ void inverse_merge_level(const float* __restrict__ sA, const float* __restrict__ rs,
-                                                    float* __restrict__ sT, int warp8, int lane, Sync sync) {
-  constexpr int MT = BS >= 16 ? BS / 16 : 1, NT = BS / 8, KS = BS / 8;
-  constexpr int TPP = MT * NT, NPAIR = 32 / BS, TILES = NPAIR * TPP;
-  const int g = lane >> 2, t = lane & 3;
-  const bool work = warp8 < TILES;
-  const int pr = work ? warp8 / TPP : 0, rem = warp8 % TPP;
-  const int mt = rem / NT, nt = rem % NT;
-  const int r0 = 2 * BS * pr + BS, c0 = 2 * BS * pr;   // block row / column origin of this pair
-  const int m0 = mt * 16 + g, m1 = m0 + 8;              // rows of this lane inside the block
-  const int n0 = nt * 8;
-  // step 1: X = diag(rs) A_10 T_00   -> scratch at the mirrored block (rows c0.., columns r0..)
-  if (work) {
-    float d[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int ks = 0; ks < KS; ++ks) {
-      const int k0 = ks * 8 + t, k1 = k0 + 4;
-      uint32_t a[4], b[2];
-      a[0] = to_tf32(m0 < BS ? sA[(r0 + m0) * LDT + c0 + k0] : 0.f);
-      a[1] = to_tf32(m1 < BS ? sA[(r0 + m1) * LDT + c0 + k0] : 0.f);
-      a[2] = to_tf32(m0 < BS ? sA[(r0 + m0) * LDT + c0 + k1] : 0.f);
-      a[3] = to_tf32(m1 < BS ? sA[(r0 + m1) * LDT + c0 + k1] : 0.f);
-      const int n = n0 + g;                              // T_00 is lower triangular: entry (k, n) needs n <= k
-      b[0] = to_tf32(n <= k0 ? sT[(c0 + k0) * LDT + c0 + n] : 0.f);
-      b[1] = to_tf32(n <= k1 ? sT[(c0 + k1) * LDT + c0 + n] : 0.f);
-      mma_tf32(d, a, b);
-    }
-    if (m0 < BS) {
-      const float f = rs[r0 + m0];
-      *reinterpret_cast<float2*>(sT + (c0 + m0) * LDT + r0 + n0 + 2 * t) = make_float2(f * d[0], f * d[1]);
-    }
-    if (m1 < BS) {
-      const float f = rs[r0 + m1];
-      *reinterpret_cast<float2*>(sT + (c0 + m1) * LDT + r0 + n0 + 2 * t) = make_float2(f * d[2], f * d[3]);
-    }
-  }
-  sync();
-  // step 2: T_10 = -T_11 X
-  if (work) {
-    float d[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int ks = 0; ks < KS; ++ks) {
-      const int k0 = ks * 8 + t, k1 = k0 + 4;
-      uint32_t a[4], b[2];
-      // T_11 is lower triangular: entry (m, k) needs k <= m
-      a[0] = to_tf32((m0 < BS && k0 <= m0) ? sT[(r0 + m0) * LDT + r0 + k0] : 0.f);
-      a[1] = to_tf32((m1 < BS && k0 <= m1) ? sT[(r0 + m1) * LDT + r0 + k0] : 0.f);
-      a[2] = to_tf32((m0 < BS && k1 <= m0) ? sT[(r0 + m0) * LDT + r0 + k1] : 0.f);
-      a[3] = to_tf32((m1 < BS && k1 <= m1) ? sT[(r0 + m1) * LDT + r0 + k1] : 0.f);
-      b[0] = to_tf32(sT[(c0 + k0) * LDT + r0 + n0 + g]);
-      b[1] = to_tf32(sT[(c0 + k1) * LDT + r0 + n0 + g]);
-      mma_tf32(d, a, b);
-    }
-    if (m0 < BS) *reinterpret_cast<float2*>(sT + (r0 + m0) * LDT + c0 + n0 + 2 * t) = make_float2(-d[0], -d[1]);
-    if (m1 < BS) *reinterpret_cast<float2*>(sT + (r0 + m1) * LDT + c0 + n0 + 2 * t) = make_float2(-d[2], -d[3]);
-  }
-  sync();
-}
-
-__device__ __forceinline__ void block_inverse_64(const float* __restrict__ sA, const float* __restrict__ rs,
-                                                 float* __restrict__ sT, int gt) {
-  const int warp8 = gt >> 5, lane = gt & 31;
-  // 8x8 diagonal blocks: one thread per column of each block
-  if (gt < 64) {
-    const int o = (gt >> 3) * 8, c = gt & 7;
-    float x[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float acc = 0.f;
-#pragma unroll
-      for (int j = 0; j < i; ++j) acc += sA[(o + i) * LDT + o + j] * x[j];
-      x[i] = ((i == c) ? 1.f : 0.f) - rs[o + i] * acc;
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) sT[(o + i) * LDT + o + c] = x[i];
-  }
-  group_sync(1);
-  inverse_merge_level<8>(sA, rs, sT, warp8, lane, SyncGroup256());
-  inverse_merge_level<16>(sA, rs, sT, warp8, lane, SyncGroup256());
-  inverse_merge_level<32>(sA, rs, sT, warp8, lane, SyncGroup256());
-}
-
-// The same inverse with the group split for its first part: warps 0-3 run the diagonal blocks and the 8- and
-// 16-wide merge levels (which have work for four warps only) while warps 4-7 run `side()`; all eight warps
-// join for the 32-wide level.  Every thread of the group must call it.
-template <class Side>
-__device__ __forceinline__ void block_inverse_64_split(const float* __restrict__ sA, const float* __restrict__ rs,
-                                                       float* __restrict__ sT, int gt, Side side) {
-  const int warp8 = gt >> 5, lane = gt & 31;
-  if (gt < 128) {
-    if (gt < 64) {
-      const int o = (gt >> 3) * 8, c = gt & 7;
-      float x[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        float acc = 0.f;
-#pragma unroll
-        for (int j = 0; j < i; ++j) acc += sA[(o + i) * LDT + o + j] * x[j];
-        x[i] = ((i == c) ? 1.f : 0.f) - rs[o + i] * acc;
-      }
-#pragma unroll
-      for (int i = 0; i < 8; ++i) sT[(o + i) * LDT + o + c] = x[i];
-    }
-    SyncHalf128()();
-    inverse_merge_level<8>(sA, rs, sT, warp8, lane, SyncHalf128());
-    inverse_merge_level<16>(sA, rs, sT, warp8, lane, SyncHalf128());
-  } else {
-    side();
-  }
-  group_sync(1);
-  inverse_merge_level<32>(sA, rs, sT, warp8, lane, SyncGroup256());
-}
-
-// Kernel parameters: the common forward parameters plus the TMA tensor maps.
-//   tk, tq, tv : 5-d views {8 elements, 8 rows, 16 k-blocks, T/8 row blocks, B*H} of the [B,H,T,128] bf16
-//                inputs; one box {8,8,16,8,1} lands a 64x128 chunk in shared memory already in the
-//                8x8 core-matrix order the tensor cores read (used when use_tma_in).
-//   to         : 4-d view {128, T, H, B} of the output; one box {128,64,1,1} stores a chunk's rows and
-//                clips the ragged tail (used when use_tma_out).
-struct alignas(64) Sm100Params {
-  CUtensorMap tk, tq, tv, to;
-  FwdParams p;
-  int use_tma_in, use_tma_out;
-};
-
+template <bool kTma>
 __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_constant__ Sm100Params P) {
   const FwdParams& p = P.p;
   extern __shared__ __align__(1024) uint8_t smem[];
-  __shared__ __align__(8) Ctl ctl;
+  __shared__ __align__(16) Ctl ctl;   // its float arrays are read with 16-byte loads
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int gt = tid & (kGroup - 1);     // thread index inside its group of eight warps
-  const int hs = gt >> 7;                // which of the two warps sharing a tensor-memory lane quarter
-  const int l128 = gt & 127;             // tensor-memory lane owned by this thread
-  const bool producer = tid < kGroup;
+  const int grp = warp >> 2;             // 0 PA, 1 PB, 2 CA, 3 CB
+  const int gt = tid & (kGrp - 1);       // thread index inside its group = tensor-memory lane it owns
   const int T = p.map.T;
   const int unit = blockIdx.x;
   const int b = unit / p.map.H, h = unit % p.map.H;
+  const int hq = p.map.hq(h);
   const int64_t qk_base = p.map.base_qk(b, h, kD), qk_tok = p.map.tok_qk(kD);   // q, k (possibly fewer heads)
   const int64_t vo_base = p.map.base(b, h, kD), vo_tok = p.map.tok(kD);         // v, o
-  const int unit_qk = b * p.map.Hq + p.map.hq(h);
   const int64_t s_base = p.map.base(b, h, 1), s_tok = p.map.tok(1);
+  // tensor-map coordinates of this sequence (column-block origin, outermost index)
+  const int qc2 = p.map.bthd ? 16 * hq : 0, qc4 = p.map.bthd ? b : b * p.map.Hq + hq;
+  const int vc2 = p.map.bthd ? 16 * h : 0, vc4 = p.map.bthd ? b : unit;
 
   if (warp == 0) {
     tc::tmem_alloc(tc::smem_u32(&ctl.tmem_base), TM_COLS);
     tc::tmem_relinquish();
   }
   if (tid == 0) {
-    tc::mbar_init(tc::smem_u32(&ctl.full[0]), kGroup);
-    tc::mbar_init(tc::smem_u32(&ctl.full[1]), kGroup);
-    tc::mbar_init(tc::smem_u32(&ctl.empty[0]), kGroup);
-    tc::mbar_init(tc::smem_u32(&ctl.empty[1]), kGroup);
+    for (int i = 0; i < 2; ++i) {
+      tc::mbar_init(tc::smem_u32(&ctl.full[i]), kGrp);
+      tc::mbar_init(tc::smem_u32(&ctl.empty[i]), 2 * kGrp);
+      tc::mbar_init(tc::smem_u32(&ctl.akk[i]), kGrp);
+      tc::mbar_init(tc::smem_u32(&ctl.akkfree[i]), kGrp);
+    }
+    for (int i = 0; i < 3; ++i) tc::mbar_init(tc::smem_u32(&ctl.kq[i]), kTma ? 1 : kGrp);
+    tc::mbar_init(tc::smem_u32(&ctl.vb), kTma ? 1 : kGrp);
+    tc::mbar_init(tc::smem_u32(&ctl.barP), 1);
+    tc::mbar_init(tc::smem_u32(&ctl.barW), 1);
     tc::mbar_init(tc::smem_u32(&ctl.barUW), 1);
     tc::mbar_init(tc::smem_u32(&ctl.uwfree), 1);
-    tc::mbar_init(tc::smem_u32(&ctl.barP), 1);
+    tc::mbar_init(tc::smem_u32(&ctl.wrdy), kGrp);
     tc::mbar_init(tc::smem_u32(&ctl.bar1), 1);
+    tc::mbar_init(tc::smem_u32(&ctl.bar2s), 1);
     tc::mbar_init(tc::smem_u32(&ctl.bar2), 1);
-    tc::mbar_init(tc::smem_u32(&ctl.kq[0]), 1);
-    tc::mbar_init(tc::smem_u32(&ctl.kq[1]), 1);
-    tc::mbar_init(tc::smem_u32(&ctl.kq[2]), 1);
-    tc::mbar_init(tc::smem_u32(&ctl.vb), 1);
+    tc::mbar_init(tc::smem_u32(&ctl.oload), kGrp);
     tc::fence_mbar_init();
     ctl.abort = 0;
   }
@@ -327,104 +174,75 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
 
   auto wait_bar = [&](uint64_t* bar, uint32_t parity) {
     if (!*abort_p) {
-      if (!tc::mbar_wait_bounded(tc::smem_u32(bar), parity, kWaitLimit)) {
+      if (!tc::mbar_wait_compact(tc::smem_u32(bar), parity, kWaitLimit)) {
         *abort_p = 1;
         if (p.status) atomicOr(p.status, DR_DEV_TIMEOUT);
       }
     }
   };
-
-  // Long waits (a whole group idling until the other group hands a stage over) back off with
-  // nanosleep between polls so that the waiting warps leave the issue slots and the shared-memory
-  // pipe to the working group.
-  auto wait_bar_relaxed = [&](uint64_t* bar, uint32_t parity) {
-    if (!*abort_p) {
-      if (!tc::mbar_wait_sleepy(tc::smem_u32(bar), parity)) {
-        *abort_p = 1;
-        if (p.status) atomicOr(p.status, DR_DEV_TIMEOUT);
-      }
-    }
-  };
+  auto arrive = [&](uint64_t* bar) { mbar_arrive(tc::smem_u32(bar)); };
 
   const uint32_t id_n64 = tc::idesc_bf16(128, 64, 0, 0);
   const uint32_t id_n64_amn = tc::idesc_bf16(128, 64, 1, 0);
-  const uint32_t id_n64_neg = id_n64 | (1u << 13);
+  const uint32_t id_n64_bmn_neg = tc::idesc_bf16(128, 64, 0, 1) | (1u << 13);
   const uint32_t id_n128_bmn = tc::idesc_bf16(128, 128, 0, 1);
   const int nchunks = (T + kC - 1) / kC;
+  float* const sAkk0 = reinterpret_cast<float*>(smem + SM_AKK);
 
-  if (producer) {
-    // =========================== PRODUCER ===========================================================
+  if (grp == 0) {
+    // =========================== PA: K,Q tiles, D1, decay masks ======================================
     const __nv_bfloat16* gq = reinterpret_cast<const __nv_bfloat16*>(p.q);
     const __nv_bfloat16* gk = reinterpret_cast<const __nv_bfloat16*>(p.k);
-    const __nv_bfloat16* gv = reinterpret_cast<const __nv_bfloat16*>(p.v);
     const float* gg = reinterpret_cast<const float*>(p.g);
-    uint8_t* sV = smem + SM_V;
-    uint8_t* sTb = smem + SM_TB;
-    uint8_t* sTw = smem + SM_TW;
-    float* sAkk = reinterpret_cast<float*>(smem + SM_AKK);
-    float* sT32 = reinterpret_cast<float*>(smem + SM_T32);
-    uint32_t phP = 0;
+    const int wq = warp & 3;
 
-    // K,Q rows (raw bf16), g and beta of chunk m -> tile / scalars of stage m&1, 16-byte (4-byte)
-    // cp.async per thread; thread -> (row in block, k-block).  The l2 normalisation is NOT applied
-    // to the tiles: it is folded into the epilogue factors rk, rs, rq.
+    // K,Q rows (raw bf16), g and beta of chunk m -> ring tile m % 3 / raw scalars.  The l2 normalisation is
+    // NOT applied to the tiles: it is folded into the factors rk, rs, rq.
     auto issue_kq = [&](int m) {
       const int t0m = m * kC, rowsm = min(kC, T - t0m);
       uint8_t* dQK = smem + SM_QKR + (m % 3) * QK_TILE;
-      float* dG = ctl.gb[m % 3];
-      if (P.use_tma_in) {
-        if (gt == 64) {  // a warp other than the one that issues the products
+      if (kTma) {
+        if (gt == 32) {  // a warp other than the one that issues the products
           const uint32_t bar = tc::smem_u32(&ctl.kq[m % 3]);
           tc::mbar_arrive_expect_tx(bar, 2u * 64 * 256);
-          tc::tma_load_5d(tc::smem_u32(dQK), &P.tk, 0, 0, 0, m * 8, unit_qk, bar);
-          tc::tma_load_5d(tc::smem_u32(dQK) + 64 * 256, &P.tq, 0, 0, 0, m * 8, unit_qk, bar);
+          tc::tma_load_5d(tc::smem_u32(dQK), &P.tk, 0, 0, qc2, m * 8, qc4, bar);
+          tc::tma_load_5d(tc::smem_u32(dQK) + 64 * 256, &P.tq, 0, 0, qc2, m * 8, qc4, bar);
         }
       } else {
-        const int rin = gt & 7, kb = (gt >> 3) & 15, rbh = gt >> 7;
+        const int rin = gt & 7, kb = gt >> 3;
 #pragma unroll
-        for (int rb2 = 0; rb2 < 4; ++rb2) {
-          const int r = (2 * rb2 + rbh) * 8 + rin;
+        for (int rb = 0; rb < 8; ++rb) {
+          const int r = rb * 8 + rin;
           const bool live = r < rowsm;
           const int64_t off = qk_base + (int64_t)(t0m + (live ? r : 0)) * qk_tok + kb * 8;
           tc::cp_async16(tc::smem_u32(dQK + tc::core_off(r, kb * 8, RBS)), gk + off, live);
           tc::cp_async16(tc::smem_u32(dQK + tc::core_off(64 + r, kb * 8, RBS)), gq + off, live);
         }
       }
-      if (gt >= 128) {
+      {
+        float* dG = ctl.gb[m % 3];
         const int r = gt & 63;
         const bool live = r < rowsm;
         const int64_t off = s_base + (int64_t)(t0m + (live ? r : 0)) * s_tok;
-        if (gt < 192) tc::cp_async4(tc::smem_u32(dG + r), p.beta + off, live);                     // beta
+        if (gt < 64) tc::cp_async4(tc::smem_u32(dG + r), p.beta + off, live);                    // beta
         else tc::cp_async4(tc::smem_u32(dG + 64 + r), gg ? gg + off : p.beta + off, live && gg);  // g (0 without decay)
       }
       tc::cp_async_commit();
     };
-    // V rows of chunk m -> core-matrix tile
-    // (with TMA only chunk 0 is fetched here; the consumer fetches V of chunk m+1 the moment its U^T product
-    // of chunk m has completed)
-    auto issue_v = [&](int m) {
-      const int t0m = m * kC, rowsm = min(kC, T - t0m);
-      if (P.use_tma_in) {
-        if (gt == 64) {
-          const uint32_t bar = tc::smem_u32(&ctl.vb);
-          tc::mbar_arrive_expect_tx(bar, 64u * 256);
-          tc::tma_load_5d(tc::smem_u32(sV), &P.tv, 0, 0, 0, m * 8, unit, bar);
-        }
-      } else {
-        const int rin = gt & 7, kb = (gt >> 3) & 15, rbh = gt >> 7;
-#pragma unroll
-        for (int rb2 = 0; rb2 < 4; ++rb2) {
-          const int r = (2 * rb2 + rbh) * 8 + rin;
-          const bool live = r < rowsm;
-          const __nv_bfloat16* src = gv + vo_base + (int64_t)(t0m + (live ? r : 0)) * vo_tok + kb * 8;
-          tc::cp_async16(tc::smem_u32(sV + tc::core_off(r, kb * 8, RBS)), src, live);
-        }
+    // every thread: its copies of chunk m have landed (and, without TMA, are published on the tile's barrier)
+    auto land_kq = [&](int m) {
+      tc::cp_async_wait_all();
+      if (!kTma) {
+        tc::fence_async_smem();
+        arrive(&ctl.kq[m % 3]);
       }
-      tc::cp_async_commit();
     };
 
-    // inclusive scan of the log decay over the 64 rows of a stage (one warp): G, e^G, e^{G_L - G}
+    // inclusive scan of the log decay over the 64 rows of a chunk (one warp): G, e^G, e^{G_L - G}, beta, and
+    // the factors of the decay mask: for a row i >= 32 and a column j < 32,
+    // e^{G_i - G_j} = 2^{G2_i - G2_32} 2^{G2_32 - G2_j} with both exponents <= 0 (G2 = G log2 e)
     auto scan_stage = [&](int m) {
+      constexpr float kLog2e = 1.4426950408889634f;
       float* zG = ctl.sc[m % 3];
       const float* raw = ctl.gb[m % 3];
       zG[192 + lane] = raw[lane]; zG[224 + lane] = raw[32 + lane];   // beta
@@ -438,153 +256,207 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       const float tot = __shfl_sync(0xffffffffu, a, 31);
       bq += tot;
       const float last = __shfl_sync(0xffffffffu, bq, 31);
+      const float g32 = __shfl_sync(0xffffffffu, bq, 0);     // G of row 32
       zG[lane] = a; zG[lane + 32] = bq;
-      zG[64 + lane] = __expf(a); zG[96 + lane] = __expf(bq);
-      zG[128 + lane] = __expf(fminf(last - a, 0.f)); zG[160 + lane] = __expf(fminf(last - bq, 0.f));
+      zG[64 + lane] = tc::fast_exp2(a * kLog2e); zG[96 + lane] = tc::fast_exp2(bq * kLog2e);
+      zG[128 + lane] = tc::fast_exp2(fminf(last - a, 0.f) * kLog2e);
+      zG[160 + lane] = tc::fast_exp2(fminf(last - bq, 0.f) * kLog2e);
+      zG[256 + lane] = a * kLog2e; zG[288 + lane] = bq * kLog2e;
+      zG[320 + lane] = tc::fast_exp2(fminf(g32 - a, 0.f) * kLog2e);
+      zG[352 + lane] = tc::fast_exp2(fminf(bq - g32, 0.f) * kLog2e);
     };
 
     // first product of chunk m: D1 = [K;Q] K^T on the raw rows (B = first 64 rows of the same tile)
     auto issue_d1 = [&](int m) {
-      if (P.use_tma_in) wait_bar(&ctl.kq[m % 3], (m / 3) & 1);
+      wait_bar(&ctl.kq[m % 3], (m / 3) & 1);
       tc::tc_fence_after();
-      const uint32_t aQK = tc::smem_u32(smem + SM_QKR + (m % 3) * QK_TILE);
+      const uint64_t ad0 = tc::smem_desc(tc::smem_u32(smem + SM_QKR + (m % 3) * QK_TILE), 128, RBS);
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
-        const uint64_t ad = tc::smem_desc(aQK + ks * 256, 128, RBS);
+        const uint64_t ad = desc_adv(ad0, ks * 256);
         tc::mma_ss(tbase + TM_D1, ad, ad, id_n64, ks > 0);
       }
       tc::mma_commit(tc::smem_u32(&ctl.barP));
     };
 
-    if (nchunks > 0) {
-      issue_kq(0);
-      issue_v(0);
-      tc::cp_async_wait_all();
-      if (!P.use_tma_in) tc::fence_async_smem();
-      group_sync(1);
-      if (warp == 1) scan_stage(0);
-      if (gt == 0) issue_d1(0);
-    }
+    issue_kq(0);
+    land_kq(0);
+    group_sync128(1);
+    if (warp == 1) scan_stage(0);
+    if (gt == 0) issue_d1(0);
+    uint32_t phP = 0;
     PROF_DECL
     for (int n = 0; n < nchunks; ++n) {
       const int s = n & 1;
-      uint8_t* st = smem + SM_STAGE + s * STAGE_BYTES;
-      uint8_t* sAqk = st + ST_AQK;
-      const uint8_t* sQKp = smem + SM_QKR + (n % 3) * QK_TILE;
+      uint8_t* sAqk = smem + SM_STAGE + s * STAGE_BYTES + ST_AQK;
+      float* sX = sAkk0 + s * (64 * LDT);
       const float* sG = ctl.sc[n % 3];
-      const float* sEG = sG + 64;
       const float* sBeta = sG + 192;
-      group_sync(1);  // the scalars of this chunk (scan) are visible
+      group_sync128(1);  // the scalars of this chunk (scan) are visible
       PROF(0);
-      // the consumer has finished chunk n-2, so tile (n+1) % 3 and stage s are free: fetch the next chunk's
-      // K,Q (and beta, g) a whole iteration before their first use
-      // (every thread waits: the first epilogue below overwrites the stage's A_qk tile)
-      if (n >= 2) wait_bar(&ctl.empty[s], ((n >> 1) - 1) & 1);
+      // chunk n-2 has left the consumers and PB: tile (n+1) % 3, stage s and X buffer s are free
+      if (n >= 2) {
+        wait_bar(&ctl.empty[s], ((n >> 1) - 1) & 1);
+        wait_bar(&ctl.akkfree[s], ((n >> 1) - 1) & 1);
+      }
+      PROF(1);
       if (n + 1 < nchunks) issue_kq(n + 1);
       PROF(2);
-      // ---- D1 of this chunk was issued during the previous iteration ----------------------------------------
-      wait_bar(&ctl.barP, phP); phP ^= 1;
+      wait_bar(&ctl.barP, phP); phP ^= 1;   // D1 of this chunk was issued during the previous iteration
       tc::tc_fence_after();
       PROF(3);
-      WSTART;
       {
-        const int i = l128 & 63, c0 = 32 * hs;
-        const float Gi = sG[i];
-        uint32_t r[32];
-        tc::tmem_ld32(tbase + TM_D1 + lane_addr + c0, r);
-        tc::tc_wait_ld();
-        if (l128 < 64) {
-          // X = (K K^T) . E on the raw rows, strictly lower; the row factor beta_i rk_i^2 and the column
-          // factors rk_j are applied later (rs in the solve, rk in the Tb/Tw tiles)
-          if ((i >> 5) == hs) {  // this half holds the diagonal entry ||k_i||^2
-            float d = 0.f;
+        const int i = gt & 63;
+        const bool qrow = gt >= 64;        // warps 2,3 hold the Q rows (A_qk); warps 0,1 the K rows (X)
+        const int hown = wq & 1;           // the 32-column half that holds this warp's diagonal
+        const float* sG2 = sG + 256;
+        if (hown) {
+          // rows 32..63 x columns 0..31 lie wholly below the diagonal: factorised decay, no exponentials here
+          const float ai = sG[352 + (i - 32)];
+          uint32_t r[32];
+          tc::tmem_ld32(tbase + TM_D1 + lane_addr, r);
+          tc::tc_wait_ld();
+          if (!qrow) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) d = (c0 + j == i) ? __uint_as_float(r[j]) : d;
+            for (int j4 = 0; j4 < 8; ++j4) {
+              const float4 c4 = *reinterpret_cast<const float4*>(sG + 320 + 4 * j4);
+              float4 o4;
+              o4.x = __uint_as_float(r[4 * j4 + 0]) * ai * c4.x; o4.y = __uint_as_float(r[4 * j4 + 1]) * ai * c4.y;
+              o4.z = __uint_as_float(r[4 * j4 + 2]) * ai * c4.z; o4.w = __uint_as_float(r[4 * j4 + 3]) * ai * c4.w;
+              *reinterpret_cast<float4*>(sX + i * LDT + 4 * j4) = o4;
+            }
+          } else {
+#pragma unroll
+            for (int j8 = 0; j8 < 4; ++j8) {
+              const float4 ca = *reinterpret_cast<const float4*>(sG + 320 + 8 * j8);
+              const float4 cb = *reinterpret_cast<const float4*>(sG + 320 + 8 * j8 + 4);
+              uint4 out;
+              out.x = tc::pack_bf16(__uint_as_float(r[8 * j8 + 0]) * ai * ca.x, __uint_as_float(r[8 * j8 + 1]) * ai * ca.y);
+              out.y = tc::pack_bf16(__uint_as_float(r[8 * j8 + 2]) * ai * ca.z, __uint_as_float(r[8 * j8 + 3]) * ai * ca.w);
+              out.z = tc::pack_bf16(__uint_as_float(r[8 * j8 + 4]) * ai * cb.x, __uint_as_float(r[8 * j8 + 5]) * ai * cb.y);
+              out.w = tc::pack_bf16(__uint_as_float(r[8 * j8 + 6]) * ai * cb.z, __uint_as_float(r[8 * j8 + 7]) * ai * cb.w);
+              *reinterpret_cast<uint4*>(sAqk + tc::core_off(i, 8 * j8, A_RBS)) = out;
+            }
+          }
+        }
+        {
+          // the half with the diagonal: exact pairwise decay 2^{min(G2_i - G2_j, 0)}, masked to the lower triangle
+          const int c0 = 32 * hown;
+          const float Gi = sG2[i];
+          uint32_t r[32];
+          tc::tmem_ld32(tbase + TM_D1 + lane_addr + c0, r);
+          tc::tc_wait_ld();
+          if (!qrow) {
+            // X = (K K^T) . E on the raw rows, lower triangle INCLUDING the diagonal (= ||k_i||^2, which the inverse
+            // never reads and overwrites); the row factor beta_i rk_i^2 and the column factors rk_j are applied
+            // later (rs in the solve, rk in the Tb/Tw tiles)
+#pragma unroll
+            for (int j4 = 0; j4 < 8; ++j4) {
+              const float4 g4 = *reinterpret_cast<const float4*>(sG2 + c0 + 4 * j4);
+              const float gj[4] = {g4.x, g4.y, g4.z, g4.w};
+              float4 o4;
+              float* o = reinterpret_cast<float*>(&o4);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int jj = c0 + 4 * j4 + e;
+                const float x = __uint_as_float(r[4 * j4 + e]) * tc::fast_exp2(fminf(Gi - gj[e], 0.f));
+                o[e] = jj <= i ? x : 0.f;
+              }
+              *reinterpret_cast<float4*>(sX + i * LDT + c0 + 4 * j4) = o4;
+            }
+            const float d = sX[i * LDT + i];   // this thread's own store
             const float rk = p.l2norm ? 1.f / (sqrtf(d) + 1e-6f) : 1.f;
-            ctl.rk[i] = rk;
-            ctl.rs[i] = sBeta[i] * rk * rk;
-          }
+            ctl.rk[s][i] = rk;
+            ctl.rs[s][i] = sBeta[i] * rk * rk;
+          } else {
 #pragma unroll
-          for (int j4 = 0; j4 < 8; ++j4) {
-            float4 o4;
-            float* o = reinterpret_cast<float*>(&o4);
+            for (int j8 = 0; j8 < 4; ++j8) {
+              const float4 ga = *reinterpret_cast<const float4*>(sG2 + c0 + 8 * j8);
+              const float4 gb4 = *reinterpret_cast<const float4*>(sG2 + c0 + 8 * j8 + 4);
+              const float gj[8] = {ga.x, ga.y, ga.z, ga.w, gb4.x, gb4.y, gb4.z, gb4.w};
+              uint4 out;
+              uint32_t* o32 = reinterpret_cast<uint32_t*>(&out);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int jj = c0 + 4 * j4 + e;
-              const float x = __uint_as_float(r[4 * j4 + e]) * __expf(fminf(Gi - sG[jj], 0.f));
-              o[e] = jj < i ? x : 0.f;
+              for (int e = 0; e < 4; ++e) {
+                const int j0 = c0 + 8 * j8 + 2 * e;
+                float x0 = __uint_as_float(r[8 * j8 + 2 * e]) * tc::fast_exp2(fminf(Gi - gj[2 * e], 0.f));
+                float x1 = __uint_as_float(r[8 * j8 + 2 * e + 1]) * tc::fast_exp2(fminf(Gi - gj[2 * e + 1], 0.f));
+                x0 = j0 <= i ? x0 : 0.f;
+                x1 = j0 + 1 <= i ? x1 : 0.f;
+                o32[e] = tc::pack_bf16(x0, x1);
+              }
+              *reinterpret_cast<uint4*>(sAqk + tc::core_off(i, c0 + 8 * j8, A_RBS)) = out;
             }
-            *reinterpret_cast<float4*>(sAkk + i * LDT + c0 + 4 * j4) = o4;
-          }
-        } else {
+            if (!hown) {   // rows 0..31: columns 32..63 lie above the diagonal
 #pragma unroll
-          for (int j8 = 0; j8 < 4; ++j8) {
-            uint4 out;
-            uint32_t* o32 = reinterpret_cast<uint32_t*>(&out);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int j0 = c0 + 8 * j8 + 2 * e;
-              float x0 = __uint_as_float(r[8 * j8 + 2 * e]) * __expf(fminf(Gi - sG[j0], 0.f));
-              float x1 = __uint_as_float(r[8 * j8 + 2 * e + 1]) * __expf(fminf(Gi - sG[j0 + 1], 0.f));
-              x0 = j0 <= i ? x0 : 0.f;
-              x1 = j0 + 1 <= i ? x1 : 0.f;
-              o32[e] = tc::pack_bf16(x0, x1);
+              for (int j8 = 0; j8 < 4; ++j8)
+                *reinterpret_cast<uint4*>(sAqk + tc::core_off(i, 32 + 8 * j8, A_RBS)) = make_uint4(0u, 0u, 0u, 0u);
             }
-            *reinterpret_cast<uint4*>(sAqk + tc::core_off(i, c0 + 8 * j8, A_RBS)) = out;
           }
         }
       }
-      WEND(1);
-      tc::cp_async_wait_all();   // the next chunk's beta, g (and, without TMA, its K,Q rows) have landed
-      if (!P.use_tma_in) tc::fence_async_smem();
-      tc::tc_fence_before();
-      group_sync(1);
       PROF(4);
-      // ---- T'' = (I + diag(rs) X)^-1 on warps 0-3 (+ all eight for the last level).  Meanwhile warps 4-7:
-      //      D1 of the NEXT chunk (its scratch columns are free now, so it completes behind the inverse), the
-      //      decay scan of the next chunk, and this chunk's query norms for the consumer -----------------------
-      WSTART;
-      block_inverse_64_split(sAkk, ctl.rs, sT32, gt, [&]() {
-        if (n + 1 < nchunks) {
-          if (gt == 128) issue_d1(n + 1);
-          if (warp == 5) scan_stage(n + 1);
-        }
-        if (gt >= 192) {  // rq_i = scale / (||q_i|| + eps) from the raw rows 64..127 of the tile, one thread per row
-          const int row = gt - 192;
-          float ss = 0.f;
+      if (n + 1 < nchunks) land_kq(n + 1);   // the next chunk's beta, g (and, without TMA, its K,Q rows)
+      tc::fence_async_smem();                // the A_qk tile is read by the tensor cores
+      tc::tc_fence_before();
+      group_sync128(1);                      // every warp has drained D1 from tensor memory
+      PROF(5);
+      if (n + 1 < nchunks) {
+        if (gt == 0) issue_d1(n + 1);        // completes behind PB's inverse of this chunk
+        if (warp == 1) scan_stage(n + 1);
+      }
+      arrive(&ctl.akk[s]);   // X, A_qk, rk, rs and the scalars of chunk n are ready
+      PROF(6);
+    }
+  } else if (grp == 1) {
+    // =========================== PB: inverse, Tb / Tw tiles ==========================================
+    uint8_t* sTb = smem + SM_TB;
+    uint8_t* sTw = smem + SM_TW;
+    PROF_DECL
+    for (int n = 0; n < nchunks; ++n) {
+      const int s = n & 1;
+      float* sT = sAkk0 + s * (64 * LDT);
+      const float* sEG = ctl.sc[n % 3] + 64;
+      const float* sBeta = ctl.sc[n % 3] + 192;
+      wait_bar(&ctl.akk[s], (n >> 1) & 1);
+      PROF(10);
+      {  // rq_i = scale / (||q_i|| + eps) from the raw rows 64..127 of the tile (it has landed: D1 has read it),
+         // two threads per row
+        const uint8_t* sQKp = smem + SM_QKR + (n % 3) * QK_TILE;
+        const int row = gt >> 1, hf = gt & 1;
+        float ss = 0.f;
+#pragma unroll 2
+        for (int it = 0; it < 8; ++it) {
+          const uint4 c = *reinterpret_cast<const uint4*>(sQKp + tc::core_off(64 + row, (8 * hf + it) * 8, RBS));
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&c);
 #pragma unroll
-          for (int it = 0; it < 16; ++it) {
-            const uint4 c = *reinterpret_cast<const uint4*>(sQKp + tc::core_off(64 + row, it * 8, RBS));
-            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&c);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float2 f = __bfloat1622float2(h2[e]);
-              ss += f.x * f.x + f.y * f.y;
-            }
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h2[e]);
+            ss += f.x * f.x + f.y * f.y;
           }
-          ctl.rq[s][row] = p.l2norm ? p.scale / (sqrtf(ss) + 1e-6f) : p.scale;
         }
-      });
-      WEND(5);
-      PROF(1);
-      WSTART;
-      // the consumer's U^T, W^T products of the previous chunk have read Tb, Tw (and V)
+        ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+        if (hf == 0) ctl.rq[s][row] = p.l2norm ? p.scale / (sqrtf(ss) + 1e-6f) : p.scale;
+      }
+      block_inverse_64_inplace(sT, ctl.rs[s], gt, SyncPB());
+      PROF(11);
+      // the U^T, W^T products of the previous chunk have read Tb, Tw
       if (n >= 1) wait_bar(&ctl.uwfree, (n - 1) & 1);
-      if (!P.use_tma_in && n >= 1) issue_v(n);   // (with TMA the consumer fetched it)
+      PROF(12);
       {
         const int rin = gt & 7, jb = (gt >> 3) & 7, rbq = gt >> 6;
         float bj[8], bw[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          const float rkj = ctl.rk[8 * jb + e];
+          const float rkj = ctl.rk[s][8 * jb + e];
           bj[e] = sBeta[8 * jb + e] * rkj;
           bw[e] = bj[e] * sEG[8 * jb + e] * rkj;
         }
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const int i = 8 * (4 * j + rbq) + rin;
-          const float4 t0v = *reinterpret_cast<const float4*>(sT32 + i * LDT + 8 * jb);
-          const float4 t1v = *reinterpret_cast<const float4*>(sT32 + i * LDT + 8 * jb + 4);
+#pragma unroll 1
+        for (int j = 0; j < 4; ++j) {
+          const int i = 8 * (2 * j + rbq) + rin;
+          const float4 t0v = *reinterpret_cast<const float4*>(sT + i * LDT + 8 * jb);
+          const float4 t1v = *reinterpret_cast<const float4*>(sT + i * LDT + 8 * jb + 4);
           float t[8] = {t0v.x, t0v.y, t0v.z, t0v.w, t1v.x, t1v.y, t1v.z, t1v.w};
 #pragma unroll
           for (int e = 0; e < 8; ++e) t[e] = (8 * jb + e <= i) ? t[e] : 0.f;
@@ -601,112 +473,49 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
           *reinterpret_cast<uint4*>(sTw + off) = ow;
         }
       }
-      WEND(6);
-      if (!P.use_tma_in) tc::cp_async_wait_all();   // this chunk's V rows
       tc::fence_async_smem();
-      mbar_arrive(tc::smem_u32(&ctl.full[s]));   // A_qk, Tb, Tw, the scalars (and V) of chunk n are ready
-      PROF(5);
+      arrive(&ctl.full[s]);      // A_qk, Tb, Tw and the scalars of chunk n are ready
+      arrive(&ctl.akkfree[s]);   // the X/T buffer may be overwritten
+      PROF(13);
     }
-  } else {
-    // =========================== CONSUMER ===========================================================
-    __nv_bfloat16* go = reinterpret_cast<__nv_bfloat16*>(p.o);
-    uint32_t ph1 = 0, ph2 = 0;
-    // initial state: S^T[v][k] = h0[k][v] (thread = value column v, half of the key columns)
+  } else if (grp == 2) {
+    // =========================== CA: the serial chain over the state =================================
+    // initial state: S^T[v][k] = h0[k][v] (thread = value column v)
     {
       const float* h0 = p.h0 ? p.h0 + (int64_t)unit * kD * kD : nullptr;
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c0 = 64 * hs + 32 * cc;
+      for (int cc = 0; cc < 4; ++cc) {
+        const int c0 = 32 * cc;
         uint32_t r[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) r[j] = h0 ? __float_as_uint(h0[(c0 + j) * kD + l128]) : 0u;
+        for (int j = 0; j < 32; ++j) r[j] = h0 ? __float_as_uint(h0[(c0 + j) * kD + gt]) : 0u;
         tc::tmem_st32(tbase + TM_S + lane_addr + c0, r);
       }
       tc::tc_wait_st();
     }
-    // O^T of chunk m: e^{G_i} Dq + Do -> staging tile (the stage's W region, no longer needed)
-    // -> coalesced store; then releases stage m&1 to the producer.
-    auto final_epilogue = [&](int m) {
-      const int sm_ = m & 1;
-      uint8_t* stm = smem + SM_STAGE + sm_ * STAGE_BYTES;
-      const float* sEGm = ctl.eg_keep[sm_];   // rq_i e^{G_i}
-      const float* sRQm = ctl.rq_keep[sm_];   // rq_i = scale / (||q_i|| + eps)
-      __nv_bfloat16* sO = reinterpret_cast<__nv_bfloat16*>(stm + ST_W);
-      const int t0m = m * kC;
-      const int rowsm = min(kC, T - t0m);
-      {
-        const int c0 = 32 * hs;
-        uint32_t rq[32], ro[32];
-        tc::tmem_ld32(tbase + TM_DQ + lane_addr + c0, rq);
-        tc::tmem_ld32(tbase + TM_DU + 64 * sm_ + lane_addr + c0, ro);
-        tc::tc_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int i = c0 + j;
-          sO[i * kD + l128] = __float2bfloat16_rn(sEGm[i] * __uint_as_float(rq[j]) + sRQm[i] * __uint_as_float(ro[j]));
-        }
-      }
-      tc::tc_fence_before();
-      if (!p.o) {
-        group_sync(2);  // output not wanted (checkpoint-only forward of the backward)
-      } else if (P.use_tma_out) {
-        tc::fence_async_smem();
-        group_sync(2);
-        if (gt == 0) {  // one tiled store of the whole chunk; rows past T are clipped by the tensor map
-          tc::tma_store_4d(&P.to, tc::smem_u32(sO), 0, t0m, h, b);
-          tc::bulk_commit();   // its shared-memory reads are awaited before the tile is written again
-        }
-      } else {
-        group_sync(2);
-        const int r = gt >> 2, qtr = gt & 3;
-        if (r < rowsm) {
-          __nv_bfloat16* dst = go + vo_base + (int64_t)(t0m + r) * vo_tok + 32 * qtr;
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            reinterpret_cast<uint4*>(dst)[j] = reinterpret_cast<const uint4*>(sO + r * kD + 32 * qtr)[j];
-        }
-      }
-    };
-
+    uint32_t ph1 = 0;
     PROF_DECL
     for (int n = 0; n < nchunks; ++n) {
       const int s = n & 1;
-      uint8_t* st = smem + SM_STAGE + s * STAGE_BYTES;
       const uint8_t* sQKc = smem + SM_QKR + (n % 3) * QK_TILE;
+      uint8_t* st = smem + SM_STAGE + s * STAGE_BYTES;
       const uint32_t aQK = tc::smem_u32(sQKc), aW = tc::smem_u32(st + ST_W), aAqk = tc::smem_u32(st + ST_AQK);
       const float* sEG = ctl.sc[n % 3] + 64;
       const float* sWd = sEG + 64;
-      uint8_t* sWt = st + ST_W;
-      wait_bar_relaxed(&ctl.full[s], (n >> 1) & 1);
-      tc::tc_fence_after();
-      PROF(16);
-      // ---- (2) W^T = K^T Tw^T -> the (idle) bf16 V_new columns;  U^T = V^T Tb^T -> stage accumulator ----------
-      if (gt == 0) {
-        // the output store that read this stage's staging tile (chunk n-2) has finished reading it; every
-        // other thread learns that through the completion barrier of the products issued next
-        if (P.use_tma_out) tc::bulk_wait_read_all();
-        if (P.use_tma_in) wait_bar(&ctl.vb, n & 1);
-        const uint32_t aV = tc::smem_u32(smem + SM_V), aTb = tc::smem_u32(smem + SM_TB), aTw = tc::smem_u32(smem + SM_TW);
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          const uint64_t ad = tc::smem_desc(aQK + ks * 2 * RBS, RBS, 128);   // K MN-major, 16 chunk rows per step
-          const uint64_t bd = tc::smem_desc(aTw + ks * 256, 128, A_RBS);
-          tc::mma_ss(tbase + TM_VA, ad, bd, id_n64_amn, ks > 0);
-        }
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          const uint64_t ad = tc::smem_desc(aV + ks * 2 * RBS, RBS, 128);
-          const uint64_t bd = tc::smem_desc(aTb + ks * 256, 128, A_RBS);
-          tc::mma_ss(tbase + TM_DU + 64 * s, ad, bd, id_n64_amn, ks > 0);
-        }
-        tc::mma_commit(tc::smem_u32(&ctl.barUW));
+      wait_bar(&ctl.full[s], (n >> 1) & 1);
+      PROF(20);
+      if (n >= 1) {
+        wait_bar(&ctl.bar2s, (n - 1) & 1);   // the state update of the previous chunk is complete
+        arrive(&ctl.empty[s ^ 1]);           // ... and so is every earlier product that read its K,Q tile
       }
+      tc::tc_fence_after();
+      PROF(21);
       // ---- state pass: bf16 copy of S^T for the products; fp32 master pre-multiplied by e^{G_L} --------
       {
         const float gl = sEG[63];
-#pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          const int c0 = 64 * hs + 32 * cc;
+#pragma unroll 1
+        for (int cc = 0; cc < 4; ++cc) {
+          const int c0 = 32 * cc;
           uint32_t r[32], pk[16];
           tc::tmem_ld32(tbase + TM_S + lane_addr + c0, r);
           tc::tc_wait_ld();
@@ -715,7 +524,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
           if (p.ckpt) {  // state at the start of this chunk, [K][V] row-major, for the backward
             float* ck = p.ckpt + ((int64_t)unit * nchunks + n) * kD * kD;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) ck[(c0 + j) * kD + l128] = __uint_as_float(r[j]);
+            for (int j = 0; j < 32; ++j) ck[(c0 + j) * kD + gt] = __uint_as_float(r[j]);
           }
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * gl);
@@ -724,62 +533,37 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         }
         tc::tc_wait_st();
       }
-      PROF(17);
-      // ---- W^T[k][c] (lane = k) -> bf16 tile W[c][k] (K-major B operand of (3)) ----------------------------
-      wait_bar(&ctl.barUW, n & 1);
-      tc::tc_fence_after();
-      if (gt == 0) {
-        // Tb, Tw and the V tile are free again: tell the producer, and fetch the next chunk's V rows
-        mbar_arrive(tc::smem_u32(&ctl.uwfree));
-        if (P.use_tma_in && n + 1 < nchunks) {
-          const uint32_t bar = tc::smem_u32(&ctl.vb);
-          tc::mbar_arrive_expect_tx(bar, 64u * 256);
-          tc::tma_load_5d(tc::smem_u32(smem + SM_V), &P.tv, 0, 0, 0, (n + 1) * 8, unit, bar);
-        }
-      }
-      {
-        const int c0 = 32 * hs;
-        uint32_t r[32];
-        tc::tmem_ld32(tbase + TM_VA + lane_addr + c0, r);
-        tc::tc_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          *reinterpret_cast<__nv_bfloat16*>(sWt + ((c0 + j) >> 3) * W_RBS + (l128 >> 3) * W_KBS + ((c0 + j) & 7) * 16 +
-                                            (l128 & 7) * 2) = __float2bfloat16_rn(__uint_as_float(r[j]));
-      }
-      tc::fence_async_smem();
       tc::tc_fence_before();
-      group_sync(2);
+      group_sync128(3);
       PROF(22);
-      // ---- (3) V_new^T = U^T - S^T W^T --------------------------------------------------------------------
+      // ---- (3) V_new^T = U^T - S^T W^T ;  Dq = S^T Q^T --------------------------------------------------
       if (gt == 0) {
+        wait_bar(&ctl.wrdy, n & 1);          // W tile written by CB
+        wait_bar(&ctl.barUW, n & 1);         // U^T complete
         tc::tc_fence_after();
+        PROF(23);
+        const uint64_t wd0 = tc::smem_desc(aW, A_RBS, 128);   // W MN-major: 16 key rows per step
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint64_t bd = tc::smem_desc(aW + ks * 2 * W_KBS, W_KBS, W_RBS);
-          tc::mma_ts(tbase + TM_DU + 64 * s, tbase + TM_SB + ks * 8, bd, id_n64_neg, 1);
-        }
+        for (int ks = 0; ks < 8; ++ks)
+          tc::mma_ts(tbase + TM_DU + 64 * s, tbase + TM_SB + ks * 8, desc_adv(wd0, ks * 2 * A_RBS), id_n64_bmn_neg, 1);
         tc::mma_commit(tc::smem_u32(&ctl.bar1));
-      }
-      PROF(23);
-      if (n > 0) final_epilogue(n - 1);  // overlaps (3); frees Dq and the other stage
-      tc::tc_fence_before();
-      group_sync(2);
-      PROF(18);
-      if (gt == 0) {  // Dq = S^T Q^^T   (Q^ = rows 64..127 of the tile)
+        PROF(24);
+        if (n >= 1) wait_bar(&ctl.oload, (n - 1) & 1);   // the output epilogue of chunk n-1 has read Dq
         tc::tc_fence_after();
+        PROF(25);
+        const uint64_t qd0 = tc::smem_desc(aQK + 8 * RBS, 128, RBS);   // Q^ = rows 64..127 of the tile
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint64_t bd = tc::smem_desc(aQK + 8 * RBS + ks * 256, 128, RBS);
-          tc::mma_ts(tbase + TM_DQ, tbase + TM_SB + ks * 8, bd, id_n64, ks > 0);
-        }
+        for (int ks = 0; ks < 8; ++ks)
+          tc::mma_ts(tbase + TM_DQ, tbase + TM_SB + ks * 8, desc_adv(qd0, ks * 256), id_n64, ks > 0);
       }
+      PROF(26);
       wait_bar(&ctl.bar1, ph1); ph1 ^= 1;
       tc::tc_fence_after();
-      PROF(19);
+      PROF(27);
       // ---- V_new^T -> bf16 (plain, and decayed by e^{G_L - G_c}) ---------------------------------------------
-      {
-        const int c0 = 32 * hs;
+#pragma unroll 1
+      for (int hh = 0; hh < 2; ++hh) {
+        const int c0 = 32 * hh;
         uint32_t r[32], pa[16], pb[16];
         tc::tmem_ld32(tbase + TM_DU + 64 * s + lane_addr + c0, r);
         tc::tc_wait_ld();
@@ -794,117 +578,250 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       }
       tc::tc_wait_st();
       tc::tc_fence_before();
-      group_sync(2);
-      PROF(20);
+      group_sync128(3);
+      PROF(28);
       // ---- (5) S^T += (decayed V_new^T) K^ ;  (4) Do = V_new^T A_qk^T -------------------------------------------
       if (gt == 0) {
         tc::tc_fence_after();
+        const uint64_t kd0 = tc::smem_desc(aQK, RBS, 128);  // K^ MN-major
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          const uint64_t bd = tc::smem_desc(aQK + ks * 2 * RBS, RBS, 128);  // K^ MN-major
-          tc::mma_ts(tbase + TM_S, tbase + TM_VB + ks * 8, bd, id_n128_bmn, 1);
-        }
+        for (int ks = 0; ks < 4; ++ks)
+          tc::mma_ts(tbase + TM_S, tbase + TM_VB + ks * 8, desc_adv(kd0, ks * 2 * RBS), id_n128_bmn, 1);
+        tc::mma_commit(tc::smem_u32(&ctl.bar2s));
+        const uint64_t ad0 = tc::smem_desc(aAqk, 128, A_RBS);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          const uint64_t bd = tc::smem_desc(aAqk + ks * 256, 128, A_RBS);
-          tc::mma_ts(tbase + TM_DU + 64 * s, tbase + TM_VA + ks * 8, bd, id_n64, ks > 0);
-        }
+        for (int ks = 0; ks < 4; ++ks)
+          tc::mma_ts(tbase + TM_DU + 64 * s, tbase + TM_VA + ks * 8, desc_adv(ad0, ks * 256), id_n64, ks > 0);
         tc::mma_commit(tc::smem_u32(&ctl.bar2));
       }
-      wait_bar(&ctl.bar2, ph2); ph2 ^= 1;
-      tc::tc_fence_after();
-      // every product that reads this stage's tiles is complete: hand [K^;Q^], A_qk and the scalars
-      // back to the producer now; the accumulator and the W region follow after the output epilogue
-      if (gt < 64) {
-        const float rqi = ctl.rq[s][gt];
-        ctl.eg_keep[s][gt] = sEG[gt] * rqi;
-        ctl.rq_keep[s][gt] = rqi;
-      }
-      mbar_arrive(tc::smem_u32(&ctl.empty[s]));
-      PROF(21);
+      PROF(29);
     }
-    group_sync(2);  // eg_keep of the last chunk is visible to the whole group
-    if (nchunks > 0) final_epilogue(nchunks - 1);
-    if (P.use_tma_out && gt == 0) tc::bulk_wait_all();
     // final state: hT[k][v] = S^T[v][k]
+    wait_bar(&ctl.bar2s, (nchunks - 1) & 1);
+    tc::tc_fence_after();
     if (p.hT) {
       float* hT = p.hT + (int64_t)unit * kD * kD;
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c0 = 64 * hs + 32 * cc;
+      for (int cc = 0; cc < 4; ++cc) {
+        const int c0 = 32 * cc;
         uint32_t r[32];
         tc::tmem_ld32(tbase + TM_S + lane_addr + c0, r);
         tc::tc_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) hT[(c0 + j) * kD + l128] = __uint_as_float(r[j]);
+        for (int j = 0; j < 32; ++j) hT[(c0 + j) * kD + gt] = __uint_as_float(r[j]);
       }
     }
+    wait_bar(&ctl.bar2, (nchunks - 1) & 1);   // every product has completed before tensor memory is released
+  } else {
+    // =========================== CB: U^T / W^T products, W tile, output =================================
+    const __nv_bfloat16* gv = reinterpret_cast<const __nv_bfloat16*>(p.v);
+    __nv_bfloat16* go = reinterpret_cast<__nv_bfloat16*>(p.o);
+    uint8_t* sV = smem + SM_V;
+    // V rows of chunk m -> core-matrix tile
+    auto issue_v = [&](int m) {
+      if (kTma) {
+        if (gt == 0) {
+          const uint32_t bar = tc::smem_u32(&ctl.vb);
+          tc::mbar_arrive_expect_tx(bar, 64u * 256);
+          tc::tma_load_5d(tc::smem_u32(sV), &P.tv, 0, 0, vc2, m * 8, vc4, bar);
+        }
+      } else {
+        const int t0m = m * kC, rowsm = min(kC, T - t0m);
+        const int rin = gt & 7, kb = gt >> 3;
+#pragma unroll
+        for (int rb = 0; rb < 8; ++rb) {
+          const int r = rb * 8 + rin;
+          const bool live = r < rowsm;
+          const __nv_bfloat16* src = gv + vo_base + (int64_t)(t0m + (live ? r : 0)) * vo_tok + kb * 8;
+          tc::cp_async16(tc::smem_u32(sV + tc::core_off(r, kb * 8, RBS)), src, live);
+        }
+        tc::cp_async_commit();
+      }
+    };
+    auto land_v = [&]() {
+      if (!kTma) {
+        tc::cp_async_wait_all();
+        tc::fence_async_smem();
+        arrive(&ctl.vb);
+      }
+    };
+    // O^T of chunk m: rq_i (e^{G_i} Dq + Do) -> staging tile (the stage's W region, no longer needed)
+    // -> one tiled store; releases the accumulators and stage m & 1.
+    auto out_epilogue = [&](int m) {
+      const int sm_ = m & 1;
+      uint8_t* stm = smem + SM_STAGE + sm_ * STAGE_BYTES;
+      const float* sEGm = ctl.keep[sm_];        // rq_i e^{G_i}
+      const float* sRQm = ctl.keep[sm_] + 64;   // rq_i
+      __nv_bfloat16* sO = reinterpret_cast<__nv_bfloat16*>(stm + ST_W);
+      const int t0m = m * kC;
+      const int rowsm = min(kC, T - t0m);
+#pragma unroll 1
+      for (int hh = 0; hh < 2; ++hh) {
+        const int c0 = 32 * hh;
+        uint32_t rq[32], ro[32];
+        tc::tmem_ld32(tbase + TM_DQ + lane_addr + c0, rq);
+        tc::tmem_ld32(tbase + TM_DU + 64 * sm_ + lane_addr + c0, ro);
+        tc::tc_wait_ld();
+        if (hh == 1) {
+          tc::tc_fence_before();
+          arrive(&ctl.oload);   // Dq and this stage's accumulator are in registers
+        }
+        if (p.o) {
+          // each thread owns one value column v and 32 tokens; neighbouring lanes swap halves of token pairs so
+          // that every lane stores two adjacent columns of one token with one 32-bit store
+          const bool odd = gt & 1;
+#pragma unroll
+          for (int j4 = 0; j4 < 8; ++j4) {
+            const float4 e4 = *reinterpret_cast<const float4*>(sEGm + c0 + 4 * j4);
+            const float4 q4 = *reinterpret_cast<const float4*>(sRQm + c0 + 4 * j4);
+            const float ee[4] = {e4.x, e4.y, e4.z, e4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+            for (int e2 = 0; e2 < 2; ++e2) {
+              const int j = 4 * j4 + 2 * e2;
+              const float o0 = ee[2 * e2] * __uint_as_float(rq[j]) + qq[2 * e2] * __uint_as_float(ro[j]);
+              const float o1 = ee[2 * e2 + 1] * __uint_as_float(rq[j + 1]) + qq[2 * e2 + 1] * __uint_as_float(ro[j + 1]);
+              const uint32_t mine = tc::pack_bf16(o0, o1);               // (token j, token j+1) of column v
+              const uint32_t other = __shfl_xor_sync(0xffffffffu, mine, 1);   // the same of column v ^ 1
+              // even lane: token j, columns (v, v+1); odd lane: token j+1, columns (v-1, v)
+              const uint32_t word = odd ? __byte_perm(other, mine, 0x7632) : __byte_perm(mine, other, 0x5410);
+              *reinterpret_cast<uint32_t*>(sO + (c0 + j + (odd ? 1 : 0)) * kD + (gt & ~1)) = word;
+            }
+          }
+        }
+      }
+      if (!p.o) return;          // output not wanted (checkpoint-only forward of the backward)
+      if (P.use_tma_out) {
+        tc::fence_async_smem();
+        group_sync128(4);
+        if (gt == 0) {  // one tiled store of the whole chunk; rows past T are clipped by the tensor map
+          tc::tma_store_4d(&P.to, tc::smem_u32(sO), 0, t0m, h, b);
+          tc::bulk_commit();   // its shared-memory reads are awaited before the tile is written again
+        }
+      } else {
+        group_sync128(4);
+        const int r = gt >> 1, hf = gt & 1;
+        if (r < rowsm) {
+          __nv_bfloat16* dst = go + vo_base + (int64_t)(t0m + r) * vo_tok + 64 * hf;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            reinterpret_cast<uint4*>(dst)[j] = reinterpret_cast<const uint4*>(sO + r * kD + 64 * hf)[j];
+        }
+        group_sync128(4);
+      }
+    };
+
+    issue_v(0);
+    land_v();
+    PROF_DECL
+    for (int n = 0; n < nchunks; ++n) {
+      const int s = n & 1;
+      uint8_t* st = smem + SM_STAGE + s * STAGE_BYTES;
+      const uint32_t aQK = tc::smem_u32(smem + SM_QKR + (n % 3) * QK_TILE);
+      uint8_t* sWt = st + ST_W;
+      if (n >= 1) {
+        wait_bar(&ctl.bar2, (n - 1) & 1);   // chunk n-1 is complete: its V_new operands, W tile and A_qk tile are dead
+        arrive(&ctl.empty[s ^ 1]);
+      }
+      PROF(30);
+      wait_bar(&ctl.full[s], (n >> 1) & 1);
+      tc::tc_fence_after();
+      PROF(31);
+      // the scalars the output epilogue of this chunk will need, kept where PA cannot overwrite them
+      if (gt < 64) {
+        const float rqi = ctl.rq[s][gt];
+        ctl.keep[s][gt] = ctl.sc[n % 3][64 + gt] * rqi;
+        ctl.keep[s][64 + gt] = rqi;
+      }
+      // ---- (2) W^T = K^T Tw^T -> the (idle) bf16 V_new columns;  U^T = V^T Tb^T -> stage accumulator ----------
+      if (gt == 0) {
+        // the output store that read this stage's staging tile has finished reading it; every other thread
+        // learns that through the completion barrier of the products issued next
+        if (P.use_tma_out) tc::bulk_wait_read_all();
+        wait_bar(&ctl.vb, n & 1);
+        tc::tc_fence_after();
+        const uint32_t aV = tc::smem_u32(sV), aTb = tc::smem_u32(smem + SM_TB), aTw = tc::smem_u32(smem + SM_TW);
+        const uint64_t kd0 = tc::smem_desc(aQK, RBS, 128);   // K MN-major, 16 chunk rows per step
+        const uint64_t twd0 = tc::smem_desc(aTw, 128, A_RBS);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          tc::mma_ss(tbase + TM_VA, desc_adv(kd0, ks * 2 * RBS), desc_adv(twd0, ks * 256), id_n64_amn, ks > 0);
+        tc::mma_commit(tc::smem_u32(&ctl.barW));   // the W tile is on the chain's path: it does not wait for U^T
+        const uint64_t vd0 = tc::smem_desc(aV, RBS, 128);
+        const uint64_t tbd0 = tc::smem_desc(aTb, 128, A_RBS);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          tc::mma_ss(tbase + TM_DU + 64 * s, desc_adv(vd0, ks * 2 * RBS), desc_adv(tbd0, ks * 256), id_n64_amn, ks > 0);
+        tc::mma_commit(tc::smem_u32(&ctl.barUW));
+      }
+      PROF(32);
+      wait_bar(&ctl.barW, n & 1);
+      tc::tc_fence_after();
+      PROF(33);
+      // ---- W^T[k][c] (lane = k) -> bf16 tile, key rows x chunk rows in core-matrix order (MN-major B of (3)) ---
+#pragma unroll 1
+      for (int hh = 0; hh < 2; ++hh) {
+        const int c0 = 32 * hh;
+        uint32_t r[32];
+        tc::tmem_ld32(tbase + TM_VA + lane_addr + c0, r);
+        tc::tc_wait_ld();
+#pragma unroll
+        for (int cb = 0; cb < 4; ++cb) {
+          uint4 out;
+          out.x = tc::pack_bf16(__uint_as_float(r[8 * cb + 0]), __uint_as_float(r[8 * cb + 1]));
+          out.y = tc::pack_bf16(__uint_as_float(r[8 * cb + 2]), __uint_as_float(r[8 * cb + 3]));
+          out.z = tc::pack_bf16(__uint_as_float(r[8 * cb + 4]), __uint_as_float(r[8 * cb + 5]));
+          out.w = tc::pack_bf16(__uint_as_float(r[8 * cb + 6]), __uint_as_float(r[8 * cb + 7]));
+          *reinterpret_cast<uint4*>(sWt + tc::core_off(gt, c0 + 8 * cb, A_RBS)) = out;
+        }
+      }
+      tc::fence_async_smem();
+      tc::tc_fence_before();
+      arrive(&ctl.wrdy);
+      // Tb, Tw and the V tile are free once U^T has completed too: tell PB, and fetch the next chunk's V rows
+      wait_bar(&ctl.barUW, n & 1);
+      if (gt == 0) arrive(&ctl.uwfree);
+      if (n + 1 < nchunks) issue_v(n + 1);
+      PROF(34);
+      if (n + 1 < nchunks) land_v();
+      group_sync128(4);   // the kept scalars of this chunk are visible to the whole group (read one iteration later)
+      PROF(35);
+      if (n >= 1) out_epilogue(n - 1);
+      PROF(36);
+    }
+    wait_bar(&ctl.bar2, (nchunks - 1) & 1);
+    tc::tc_fence_after();
+    group_sync128(4);
+    out_epilogue(nchunks - 1);
+    if (P.use_tma_out && gt == 0) tc::bulk_wait_all();
   }
   tc::tc_fence_before();
   __syncthreads();
   if (warp == 0) tc::tmem_dealloc(tbase, TM_COLS);
 }
 
-// cuTensorMapEncodeTiled is fetched from the driver at run time (no link dependency on libcuda).
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-inline EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = [] {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      ptr = nullptr;
-    return reinterpret_cast<EncodeTiledFn>(ptr);
-  }();
-  return fn;
-}
-
-// 5-d input view of a contiguous [B*H][T][128] bf16 tensor (see Sm100Params).
-inline bool make_input_map(CUtensorMap* m, const void* base, int64_t units, int T) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (!fn) return false;
-  const cuuint64_t dims[5] = {8, 8, 16, (cuuint64_t)(T / 8), (cuuint64_t)units};
-  const cuuint64_t strides[4] = {256, 16, 2048, (cuuint64_t)T * 256};  // bytes, dims 1..4
-  const cuuint32_t box[5] = {8, 8, 16, 8, 1};
-  const cuuint32_t es[5] = {1, 1, 1, 1, 1};
-  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), dims, strides, box, es,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-// 4-d output view {128, T, H, B} of [B,H,T,128] or [B,T,H,128], bf16 (elem_bytes 2) or fp32 (4).
-inline bool make_output_map(CUtensorMap* m, void* base, const SeqMap& sm, int elem_bytes = 2) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (!fn) return false;
-  const cuuint64_t row = 128ull * elem_bytes;
-  const cuuint64_t dims[4] = {128, (cuuint64_t)sm.T, (cuuint64_t)sm.H, (cuuint64_t)sm.B};
-  cuuint64_t strides[3];
-  if (sm.bthd) { strides[0] = (cuuint64_t)sm.H * row; strides[1] = row; strides[2] = (cuuint64_t)sm.T * sm.H * row; }
-  else { strides[0] = row; strides[1] = (cuuint64_t)sm.T * row; strides[2] = (cuuint64_t)sm.H * sm.T * row; }
-  const cuuint32_t box[4] = {128, 64, 1, 1};
-  const cuuint32_t es[4] = {1, 1, 1, 1};
-  return fn(m, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, dims,
-            strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 inline cudaError_t launch_chunk(const FwdParams& p, cudaStream_t stream) {
-  cudaError_t e = cudaFuncSetAttribute(chunk_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_TOTAL);
-  if (e != cudaSuccess) return e;
+  // TMA inputs need whole 8-row blocks; otherwise the per-thread cp.async instantiation loads the tiles
+  // (same layout, same results).
   Sm100Params P;
   memset(&P, 0, sizeof(P));
   P.p = p;
-  const int64_t units = (int64_t)p.map.B * p.map.H;
-  // TMA inputs need the rows of one (batch, head) contiguous and whole 8-row blocks; otherwise the
-  // per-thread cp.async path loads the tiles (same layout, same results).
-  const int64_t units_qk = (int64_t)p.map.B * p.map.Hq;
-  P.use_tma_in = !p.map.bthd && p.map.T % 8 == 0 && make_input_map(&P.tk, p.k, units_qk, p.map.T) &&
-                 make_input_map(&P.tq, p.q, units_qk, p.map.T) && make_input_map(&P.tv, p.v, units, p.map.T);
+  const bool bthd = p.map.bthd != 0;
+  const bool tma_in = p.map.T % 8 == 0 && make_input_map(&P.tk, p.k, p.map.B, p.map.Hq, p.map.T, bthd) &&
+                      make_input_map(&P.tq, p.q, p.map.B, p.map.Hq, p.map.T, bthd) &&
+                      make_input_map(&P.tv, p.v, p.map.B, p.map.H, p.map.T, bthd);
   P.use_tma_out = p.o != nullptr && make_output_map(&P.to, p.o, p.map);
-  const dim3 grid((unsigned)units), block(kThreads);
-  chunk_sm100_kernel<<<grid, block, SM_TOTAL, stream>>>(P);
+  auto kern = tma_in ? chunk_sm100_kernel<true> : chunk_sm100_kernel<false>;
+  thread_local int attr_dev[2] = {-1, -1};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (attr_dev[tma_in] != dev) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_TOTAL);
+    if (e != cudaSuccess) return e;
+    attr_dev[tma_in] = dev;
+  }
+  const dim3 grid((unsigned)((int64_t)p.map.B * p.map.H)), block(kThreads);
+  kern<<<grid, block, SM_TOTAL, stream>>>(P);
   return cudaGetLastError();
 }
 

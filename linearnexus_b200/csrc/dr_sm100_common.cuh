@@ -1,0 +1,275 @@
+// Pieces shared by the tcgen05 kernels (fused chunk forward, two-kernel forward, backward pre-pass):
+// tile geometry, the blocked 64x64 unit-lower-triangular inverse on mma.sync tf32, and the TMA tensor
+// maps (encoded once per distinct tensor and kept in a small host-side cache).
+#pragma once
+
+#include <cuda.h>
+
+#include <cstring>
+#include <mutex>
+
+#include "dr_common.cuh"
+#include "dr_tcgen05.cuh"
+
+namespace dr {
+namespace sm100 {
+
+constexpr int kC = 64, kD = 128;
+constexpr int RBS = 16 * 128;    // row-block stride (bytes) of the 128-column bf16 core-matrix tiles
+constexpr int A_RBS = 8 * 128;   // row-block stride of the 64-column tiles
+constexpr int LDT = 68;          // row stride (floats) of the fp32 64x64 matrices
+constexpr uint32_t kWaitLimit = 4u << 20;
+
+__device__ __forceinline__ void group_sync(int id) { asm volatile("bar.sync %0, 256;" ::"r"(id) : "memory"); }
+__device__ __forceinline__ void group_sync128(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ uint32_t to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+// ---------------------------------------------------------------------------------------------------
+// T = (I + diag(rs) A)^-1 for a strictly lower-triangular 64x64 A (fp32, row stride LDT).
+// 8x8 diagonal blocks by forward substitution on the CUDA cores, then three merge levels
+// (block size 8, 16, 32):  T_10 = -T_11 (diag(rs) A_10) T_00, each of the two products on the
+// warp-level tensor-core path (mma.sync m16n8k8, tf32 operands, fp32 accumulate): these tiny
+// products are bound by shared-memory wavefronts, not flops, on the CUDA cores.
+// sT receives the lower triangle of T; entries above the diagonal are scratch (callers mask them).
+// sA and sT may be the SAME array: every block of A is consumed before the block of T that takes
+// its place is written.
+// ---------------------------------------------------------------------------------------------------
+struct SyncGroup256 { __device__ __forceinline__ void operator()() const { group_sync(1); } };
+
+// One merge level on NW warps (w = index of the calling warp inside its group).
+template <int BS, int NW, class Sync>
+__device__ __forceinline__ void inverse_merge_level(const float* __restrict__ sA, const float* __restrict__ rs,
+                                                    float* __restrict__ sT, int w, int lane, Sync sync) {
+  constexpr int MT = BS >= 16 ? BS / 16 : 1, NT = BS / 8, KS = BS / 8;
+  constexpr int TPP = MT * NT, NPAIR = 32 / BS, TILES = NPAIR * TPP;
+  const int g = lane >> 2, t = lane & 3;
+  // step 1: X = diag(rs) A_10 T_00   -> scratch at the mirrored block (rows c0.., columns r0..)
+#pragma unroll 1
+  for (int tile = w; tile < TILES; tile += NW) {
+    const int pr = tile / TPP, rem = tile % TPP;
+    const int mt = rem / NT, nt = rem % NT;
+    const int r0 = 2 * BS * pr + BS, c0 = 2 * BS * pr;   // block row / column origin of this pair
+    const int m0 = mt * 16 + g, m1 = m0 + 8;              // rows of this lane inside the block
+    const int n0 = nt * 8;
+    float d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      const int k0 = ks * 8 + t, k1 = k0 + 4;
+      uint32_t a[4], b[2];
+      a[0] = to_tf32(m0 < BS ? sA[(r0 + m0) * LDT + c0 + k0] : 0.f);
+      a[1] = to_tf32(m1 < BS ? sA[(r0 + m1) * LDT + c0 + k0] : 0.f);
+      a[2] = to_tf32(m0 < BS ? sA[(r0 + m0) * LDT + c0 + k1] : 0.f);
+      a[3] = to_tf32(m1 < BS ? sA[(r0 + m1) * LDT + c0 + k1] : 0.f);
+      const int n = n0 + g;                              // T_00 is lower triangular: entry (k, n) needs n <= k
+      b[0] = to_tf32(n <= k0 ? sT[(c0 + k0) * LDT + c0 + n] : 0.f);
+      b[1] = to_tf32(n <= k1 ? sT[(c0 + k1) * LDT + c0 + n] : 0.f);
+      mma_tf32(d, a, b);
+    }
+    if (m0 < BS) {
+      const float f = rs[r0 + m0];
+      *reinterpret_cast<float2*>(sT + (c0 + m0) * LDT + r0 + n0 + 2 * t) = make_float2(f * d[0], f * d[1]);
+    }
+    if (m1 < BS) {
+      const float f = rs[r0 + m1];
+      *reinterpret_cast<float2*>(sT + (c0 + m1) * LDT + r0 + n0 + 2 * t) = make_float2(f * d[2], f * d[3]);
+    }
+  }
+  sync();
+  // step 2: T_10 = -T_11 X
+#pragma unroll 1
+  for (int tile = w; tile < TILES; tile += NW) {
+    const int pr = tile / TPP, rem = tile % TPP;
+    const int mt = rem / NT, nt = rem % NT;
+    const int r0 = 2 * BS * pr + BS, c0 = 2 * BS * pr;
+    const int m0 = mt * 16 + g, m1 = m0 + 8;
+    const int n0 = nt * 8;
+    float d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      const int k0 = ks * 8 + t, k1 = k0 + 4;
+      uint32_t a[4], b[2];
+      // T_11 is lower triangular: entry (m, k) needs k <= m
+      a[0] = to_tf32((m0 < BS && k0 <= m0) ? sT[(r0 + m0) * LDT + r0 + k0] : 0.f);
+      a[1] = to_tf32((m1 < BS && k0 <= m1) ? sT[(r0 + m1) * LDT + r0 + k0] : 0.f);
+      a[2] = to_tf32((m0 < BS && k1 <= m0) ? sT[(r0 + m0) * LDT + r0 + k1] : 0.f);
+      a[3] = to_tf32((m1 < BS && k1 <= m1) ? sT[(r0 + m1) * LDT + r0 + k1] : 0.f);
+      b[0] = to_tf32(sT[(c0 + k0) * LDT + r0 + n0 + g]);
+      b[1] = to_tf32(sT[(c0 + k1) * LDT + r0 + n0 + g]);
+      mma_tf32(d, a, b);
+    }
+    if (m0 < BS) *reinterpret_cast<float2*>(sT + (r0 + m0) * LDT + c0 + n0 + 2 * t) = make_float2(-d[0], -d[1]);
+    if (m1 < BS) *reinterpret_cast<float2*>(sT + (r0 + m1) * LDT + c0 + n0 + 2 * t) = make_float2(-d[2], -d[3]);
+  }
+  sync();
+}
+
+// 8x8 diagonal blocks: one thread per column of each block (threads 0..63 of the group, i.e. two full
+// warps).  All entries of A's block are read before the first entry of T is written (in-place use).
+__device__ __forceinline__ void inverse_diag_blocks(const float* __restrict__ sA, const float* __restrict__ rs,
+                                                    float* __restrict__ sT, int gt) {
+  if (gt < 64) {
+    const int o = (gt >> 3) * 8, c = gt & 7;
+    float a[8][8];
+#pragma unroll
+    for (int i = 1; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < i; ++j) a[i][j] = sA[(o + i) * LDT + o + j];
+    float f[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = rs[o + i];
+    __syncwarp();
+    float x[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < i; ++j) acc += a[i][j] * x[j];
+      x[i] = ((i == c) ? 1.f : 0.f) - f[i] * acc;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sT[(o + i) * LDT + o + c] = x[i];
+  }
+}
+
+// The inverse on a group of 256 threads synchronised by named barrier 1.
+__device__ __forceinline__ void block_inverse_64(const float* __restrict__ sA, const float* __restrict__ rs,
+                                                 float* __restrict__ sT, int gt) {
+  const int warp8 = gt >> 5, lane = gt & 31;
+  inverse_diag_blocks(sA, rs, sT, gt);
+  group_sync(1);
+  inverse_merge_level<8, 8>(sA, rs, sT, warp8, lane, SyncGroup256());
+  inverse_merge_level<16, 8>(sA, rs, sT, warp8, lane, SyncGroup256());
+  inverse_merge_level<32, 8>(sA, rs, sT, warp8, lane, SyncGroup256());
+}
+
+// The inverse IN PLACE (sT holds A on entry, T on return) on a group of 128 threads synchronised by `sync`.
+template <class Sync>
+__device__ __forceinline__ void block_inverse_64_inplace(float* __restrict__ sT, const float* __restrict__ rs, int gt,
+                                                         Sync sync) {
+  const int w = gt >> 5, lane = gt & 31;
+  inverse_diag_blocks(sT, rs, sT, gt);
+  sync();
+  inverse_merge_level<8, 4>(sT, rs, sT, w, lane, sync);
+  inverse_merge_level<16, 4>(sT, rs, sT, w, lane, sync);
+  inverse_merge_level<32, 4>(sT, rs, sT, w, lane, sync);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// TMA tensor maps.  cuTensorMapEncodeTiled is fetched from the driver at run time (no link dependency
+// on libcuda).  Encoded maps are kept in a small cache keyed by (pointer, geometry): a serving or
+// training loop calls with the same buffers over and over.
+// ---------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      ptr = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+struct MapKey {
+  const void* base;
+  int64_t a, b, c;   // geometry (meaning depends on kind)
+  int kind;          // 0: [units][T][128] input, 1: [B][T][heads][128] input, 2: output
+  bool operator==(const MapKey& o) const { return base == o.base && a == o.a && b == o.b && c == o.c && kind == o.kind; }
+};
+struct MapCache {
+  static constexpr int kSlots = 32;
+  std::mutex mu;
+  MapKey key[kSlots];
+  CUtensorMap map[kSlots];
+  int used = 0, next = 0;
+  bool find(const MapKey& k, CUtensorMap* out) {
+    std::lock_guard<std::mutex> lock(mu);
+    for (int i = 0; i < used; ++i)
+      if (key[i] == k) { *out = map[i]; return true; }
+    return false;
+  }
+  void put(const MapKey& k, const CUtensorMap& m) {
+    std::lock_guard<std::mutex> lock(mu);
+    const int i = used < kSlots ? used++ : (next++ % kSlots);
+    key[i] = k; map[i] = m;
+  }
+};
+inline MapCache& map_cache() { static MapCache c; return c; }
+
+// 5-d input view whose box {8,8,16,8,1} lands one 64x128 bf16 chunk in shared memory already in the
+// 8x8 core-matrix order the tensor cores read (needs T % 8 == 0).
+//   [B*heads, T, 128] storage ([B,H,T,D]): dims {8 elems, 8 rows, 16 column blocks, T/8 row blocks, B*heads};
+//     the chunk m of sequence u is at coordinates (0, 0, 0, 8m, u).
+//   [B, T, heads, 128] storage ([B,T,H,D]): dims {8 elems, 8 rows (stride heads*256 B), 16*heads column
+//     blocks, T/8 row blocks, B}; the chunk m of (b, h) is at coordinates (0, 0, 16h, 8m, b).
+// The maps cover this GPU's memory only and are used without multicast.
+inline bool make_input_map(CUtensorMap* m, const void* base, int64_t B, int64_t heads, int T, bool bthd) {
+  const MapKey key{base, B, heads, T, bthd ? 1 : 0};
+  if (map_cache().find(key, m)) return true;
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  cuuint64_t dims[5], strides[4];
+  if (bthd) {
+    dims[0] = 8; dims[1] = 8; dims[2] = 16 * (cuuint64_t)heads; dims[3] = (cuuint64_t)(T / 8); dims[4] = (cuuint64_t)B;
+    strides[0] = (cuuint64_t)heads * 256; strides[1] = 16; strides[2] = 8 * (cuuint64_t)heads * 256;
+    strides[3] = (cuuint64_t)T * heads * 256;
+  } else {
+    dims[0] = 8; dims[1] = 8; dims[2] = 16; dims[3] = (cuuint64_t)(T / 8); dims[4] = (cuuint64_t)(B * heads);
+    strides[0] = 256; strides[1] = 16; strides[2] = 2048; strides[3] = (cuuint64_t)T * 256;
+  }
+  const cuuint32_t box[5] = {8, 8, 16, 8, 1};
+  const cuuint32_t es[5] = {1, 1, 1, 1, 1};
+  if (fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), dims, strides, box, es,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  map_cache().put(key, *m);
+  return true;
+}
+// the [B*heads][T][128] form with the units already flattened
+inline bool make_input_map(CUtensorMap* m, const void* base, int64_t units, int T) {
+  return make_input_map(m, base, units, 1, T, false);
+}
+
+// 4-d output view {128, T, H, B} of [B,H,T,128] or [B,T,H,128], bf16 (elem_bytes 2) or fp32 (4); one box
+// {128,64,1,1} stores a chunk's rows and clips the ragged tail.
+inline bool make_output_map(CUtensorMap* m, void* base, const SeqMap& sm, int elem_bytes = 2) {
+  const MapKey key{base, ((int64_t)sm.B << 32) | (uint32_t)sm.H, sm.T, (sm.bthd ? 1 : 0) | (elem_bytes << 1), 2};
+  if (map_cache().find(key, m)) return true;
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint64_t row = 128ull * elem_bytes;
+  const cuuint64_t dims[4] = {128, (cuuint64_t)sm.T, (cuuint64_t)sm.H, (cuuint64_t)sm.B};
+  cuuint64_t strides[3];
+  if (sm.bthd) { strides[0] = (cuuint64_t)sm.H * row; strides[1] = row; strides[2] = (cuuint64_t)sm.T * sm.H * row; }
+  else { strides[0] = row; strides[1] = (cuuint64_t)sm.T * row; strides[2] = (cuuint64_t)sm.H * sm.T * row; }
+  const cuuint32_t box[4] = {128, 64, 1, 1};
+  const cuuint32_t es[4] = {1, 1, 1, 1};
+  if (fn(m, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, dims,
+         strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  map_cache().put(key, *m);
+  return true;
+}
+
+}  // namespace sm100
+}  // namespace dr

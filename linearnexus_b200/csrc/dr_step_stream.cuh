@@ -32,6 +32,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) step_stream_kernel(const Step
   float* s_red = s_v + kStreamD;   // [2][8][128]
   __shared__ __align__(8) uint64_t full[kStreamStages];
   __shared__ float s_part[3][4];
+  __shared__ int s_abort;   // set once a bounded wait has run out: from then on nothing is written back
   constexpr int K = kStreamD, V = kStreamD;
 
   const int tid = threadIdx.x;
@@ -43,6 +44,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) step_stream_kernel(const Step
   if (tid == 0) {
     for (int i = 0; i < kStreamStages; ++i) tc::mbar_init(tc::smem_u32(&full[i]), 1);
     tc::fence_mbar_init();
+    s_abort = 0;
   }
   __syncthreads();
   auto issue_load = [&](int64_t i) {   // thread 0
@@ -108,6 +110,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) step_stream_kernel(const Step
       const uint32_t bar = tc::smem_u32(&full[i % kStreamStages]);
       const uint32_t parity = (uint32_t)((i / kStreamStages) & 1);
       if (!tc::mbar_wait_bounded(bar, parity, 4u << 20)) {
+        s_abort = 1;   // the state of this unit never arrived: its stale buffer must not reach the cache
         if (status) atomicOr(status, DR_DEV_TIMEOUT);
       }
     }
@@ -154,7 +157,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) step_stream_kernel(const Step
     }
     tc::fence_async_smem();   // the updated state is read by the TMA engine next
     __syncthreads();
-    if (tid == 0) {
+    if (tid == 0 && !s_abort) {
       uint8_t* dst = reinterpret_cast<uint8_t*>(p.s_out + unit * (int64_t)K * V);
       const uint32_t src = tc::smem_u32(S);
 #pragma unroll
@@ -170,10 +173,11 @@ inline bool step_stream_eligible(const StepParams& p, int64_t units, int sms) {
   return p.K == kStreamD && p.V == kStreamD && units >= 2 * (int64_t)sms;
 }
 
-inline cudaError_t launch_step_stream(const StepParams& p, int64_t units, int sms, cudaStream_t stream) {
+inline cudaError_t launch_step_stream(const StepParams& p, int64_t units, int sms, int32_t* status,
+                                      cudaStream_t stream) {
   cudaError_t e = cudaFuncSetAttribute(step_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem);
   if (e != cudaSuccess) return e;
-  step_stream_kernel<<<(unsigned)sms, kStepThreads, kStreamSmem, stream>>>(p, units, nullptr);
+  step_stream_kernel<<<(unsigned)sms, kStepThreads, kStreamSmem, stream>>>(p, units, status);
   return cudaGetLastError();
 }
 

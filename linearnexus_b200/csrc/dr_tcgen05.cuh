@@ -65,6 +65,20 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   }
   return false;
 }
+// The same bound with the loop kept out of line: call sites inline one try_wait (the common case: the phase
+// has completed or completes within the hardware's own suspend window) and share this function for the rest.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, uint32_t limit) {
+  const long long t_start = clock64();
+  for (uint32_t i = 0; i < limit; ++i) {
+    if (mbar_try(bar, parity)) return true;
+    if (clock64() - t_start > 2000000000ll) return false;
+  }
+  return false;
+}
+__device__ __forceinline__ bool mbar_wait_compact(uint32_t bar, uint32_t parity, uint32_t limit) {
+  if (mbar_try(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, limit);
+}
 // Polling wait with sleep between polls, bounded to about a second of SM clock.
 __device__ __forceinline__ bool mbar_wait_sleepy(uint32_t bar, uint32_t parity) {
   if (mbar_test(bar, parity)) return true;
@@ -229,6 +243,14 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
         "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
+}
+
+// 2^x on the special-function unit, results below the normal range flushed to zero (one MUFU instruction;
+// __expf adds range fix-ups for denormal results that the decay factors do not need)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {

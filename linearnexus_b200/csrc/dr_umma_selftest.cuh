@@ -6,12 +6,11 @@
 #pragma once
 
 #include "dr_common.cuh"
+#include "dr_sm100_common.cuh"
 #include "dr_tcgen05.cuh"
 
 namespace dr {
 namespace sm100 {
-
-constexpr uint32_t kWaitLimit = 4u << 20;
 
 __global__ void __launch_bounds__(128) umma_selftest_kernel(const __nv_bfloat16* __restrict__ A,
                                                             const __nv_bfloat16* __restrict__ B,
@@ -122,6 +121,18 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const __nv_bfloat16*
   tc::tc_fence_before();
   __syncthreads();
   if (warp == 0) tc::tmem_dealloc(tbase, 512);
+}
+
+// One warp waits on an mbarrier that nothing ever arrives on, with the bounded wait the kernels use and a
+// small attempt limit: the wait gives up, the status word gets DR_DEV_TIMEOUT, the kernel returns normally.
+__global__ void wait_timeout_kernel(int32_t* status, uint32_t attempts) {
+  __shared__ __align__(8) uint64_t bar;
+  if (threadIdx.x == 0) {
+    tc::mbar_init(tc::smem_u32(&bar), 1);
+    tc::fence_mbar_init();
+  }
+  __syncwarp();
+  if (!tc::mbar_wait_bounded(tc::smem_u32(&bar), 0, attempts) && threadIdx.x == 0) atomicOr(status, DR_DEV_TIMEOUT);
 }
 
 inline cudaError_t launch_umma_selftest(const void* A, const void* B, float* D, int Kd, int N, int a_tmem,

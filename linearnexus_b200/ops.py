@@ -40,6 +40,31 @@ def _stream(dev) -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
 
 
+# One status word per device, handed to every kernel launch; kernels OR problems into it (a bounded wait
+# that ran out) and never trap.  Nothing here synchronises to look at it: `check_device_status` does, and is
+# meant to be called where the host synchronises anyway.
+_status_words: dict = {}
+
+
+def _status(dev) -> Tensor:
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    t = _status_words.get(idx)
+    if t is None:
+        t = _status_words[idx] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+    return t
+
+
+def check_device_status(device=None) -> None:
+    """Synchronise the current stream of ``device`` and raise :class:`DeltaRuleError` (DR_ERR_DEVICE) if any
+    kernel launched by this package since the last check reported a problem through the device status word;
+    the word is cleared, so the next check starts clean.  The reference has nothing to mirror here: its GPU
+    kernel falls back silently (delta_net.py:150-156)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        st = _lib.load().dr_check_status(_ptr(_status(dev)), _stream(dev))
+    _lib.check(st, "dr_check_status")
+
+
 def _require_cuda(*ts):
     for t in ts:
         if t is not None and not t.is_cuda:
@@ -127,7 +152,8 @@ def _seq_forward(kind, variant, q, k, v, g, beta, initial_state, scale, chunk_si
             need = int(lib.dr_workspace_bytes(ctypes.byref(d), 0))
             ws = torch.empty(need, dtype=torch.uint8, device=dev) if need > 0 else None
             st = lib.dr_chunk_fwd(ctypes.byref(d), _ptr(qn), _ptr(kn), _ptr(vn), _ptr(gn), _ptr(bn),
-                                  _ptr(h0), _ptr(o), _ptr(hT), _ptr(ws), max(need, 0), None, _stream(dev))
+                                  _ptr(h0), _ptr(o), _ptr(hT), _ptr(ws), max(need, 0), _ptr(_status(dev)),
+                                  _stream(dev))
         else:
             st = lib.dr_recurrent_fwd(ctypes.byref(d), _ptr(qn), _ptr(kn), _ptr(vn), _ptr(gn), _ptr(bn),
                                       _ptr(h0), _ptr(o), _ptr(hT), _stream(dev))
@@ -165,7 +191,7 @@ def _step(variant, q, k, v, g, beta, state, scale, l2norm, out_dtype, inplace=Fa
     d.qk_heads = Hq
     with torch.cuda.device(dev):
         st = _lib.load().dr_step(ctypes.byref(d), _ptr(qn), _ptr(kn), _ptr(vn), _ptr(gn), _ptr(bn),
-                                 _ptr(s_in), _ptr(s_out), _ptr(o), _stream(dev))
+                                 _ptr(s_in), _ptr(s_out), _ptr(o), _ptr(_status(dev)), _stream(dev))
     _lib.check(st, "dr_step")
     return (o if o.dtype == out_dtype else o.to(out_dtype)), s_out
 
@@ -311,7 +337,7 @@ def chunk_forward_saving(variant, q, k, v, g, beta, initial_state=None, scale=No
     hT = torch.empty((B, H, K, V), dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
         st = lib.dr_chunk_fwd_saving(ctypes.byref(d), _ptr(qn), _ptr(kn), _ptr(vn), _ptr(gn), _ptr(bn), _ptr(h0),
-                                     _ptr(o), _ptr(hT), _ptr(ws), ws.numel(), None, _stream(dev))
+                                     _ptr(o), _ptr(hT), _ptr(ws), ws.numel(), _ptr(_status(dev)), _stream(dev))
     _lib.check(st, "dr_chunk_fwd_saving")
     return (o if o.dtype == out_dtype else o.to(out_dtype)), hT, ws
 
@@ -340,11 +366,11 @@ def chunk_backward(variant, q, k, v, g, beta, d_o, initial_state=None, d_final_s
         if saved is None:
             st = lib.dr_chunk_bwd(ctypes.byref(d), _ptr(qn), _ptr(kn), _ptr(vn), _ptr(gn), _ptr(bn), _ptr(h0), _ptr(don),
                                   _ptr(dhT), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dbeta), _ptr(dg), _ptr(dh0), _ptr(ws),
-                                  ws.numel(), None, _stream(dev))
+                                  ws.numel(), _ptr(_status(dev)), _stream(dev))
         else:
             st = lib.dr_chunk_bwd_saved(ctypes.byref(d), _ptr(qn), _ptr(kn), _ptr(vn), _ptr(gn), _ptr(bn), _ptr(don),
                                         _ptr(dhT), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dbeta), _ptr(dg), _ptr(dh0),
-                                        _ptr(ws), ws.numel(), None, _stream(dev))
+                                        _ptr(ws), ws.numel(), _ptr(_status(dev)), _stream(dev))
     _lib.check(st, "dr_chunk_bwd")
     return dict(dq=dq.to(q.dtype), dk=dk.to(k.dtype), dv=dv.to(v.dtype), dg=dg, dbeta=dbeta, dh0=dh0)
 

@@ -14,7 +14,7 @@ ROOT = Path(__file__).resolve().parents[1]
 
 
 def _header_functions():
-    text = (ROOT / "include" / "deltarule_sm100.h").read_text()
+    text = "".join(p.read_text() for p in sorted((ROOT / "include").glob("*.h")))
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(dr_[a-z0-9_]+)\s*\(", text)))
 
@@ -54,10 +54,35 @@ def test_validation_status_codes():
     assert call(_desc(variant=1), g=None) == -6   # Gated DeltaNet needs g
     assert call(_desc(chunk=24), g=16) == -7      # reference: ValueError when chunk % 16 != 0
     assert call(_desc(variant=5), g=16) == -6
-    assert lib.dr_step(ctypes.byref(_desc(T=2)), 16, 16, 16, 16, 16, 16, 16, 16, None) == -2
+    assert lib.dr_step(ctypes.byref(_desc(T=2)), 16, 16, 16, 16, 16, 16, 16, 16, None, None) == -2
     assert lib.dr_workspace_bytes(ctypes.byref(_desc()), 0) == 0
-    for s in range(-10, 1):
+    for s in range(-11, 1):
         assert lib.dr_strerror(s)
+    assert lib.dr_check_status(None, None) == -1            # the status word is required
+    assert lib.dr_debug_wait_timeout(None, 16, None) == -1
+    assert lib.dr_debug_wait_timeout(16, 0, None) == -2     # attempts out of range, refused before any launch
+
+
+def test_device_status_maps_to_an_exception():
+    """Host side of the status word: DR_ERR_DEVICE becomes a DeltaRuleError that names the DR_DEV_* bits."""
+    with pytest.raises(_lib.DeltaRuleError) as ei:
+        _lib.check(-10, "dr_check_status")
+    assert ei.value.status == -10 and "device-side" in str(ei.value)
+
+
+def test_two_kernel_forward_without_workspace_is_an_error_not_a_downgrade():
+    """KDA at the tensor-core shape resolves to the two-kernel path; a call that brings no workspace gets
+    DR_ERR_WORKSPACE whether the path was chosen by AUTO or by name (validation only: nothing is launched)."""
+    import torch
+    from linearnexus_b200 import ops
+    lib = _lib.load()
+    q = torch.empty(0, dtype=torch.bfloat16)
+    g = torch.empty(0, dtype=torch.float32)
+    for path in (None, "split"):
+        d = ops._desc(_lib.DR_KDA, _lib.DR_LAYOUT_BHTD, 1, 1, 64, 128, 128, 64, q, g, torch.float32, True, 0.1, path)
+        assert lib.dr_chunk_fwd(ctypes.byref(d), 16, 16, 16, 16, 16, None, 16, None, None, 0, None, None) == -5
+    d = ops._desc(_lib.DR_KDA, _lib.DR_LAYOUT_BHTD, 1, 1, 64, 128, 128, 64, q, g, torch.float32, True, 0.1, "split")
+    assert lib.dr_chunk_fwd(ctypes.byref(d), 16, 16, 16, 16, 16, None, 16, None, 24, 1 << 30, None, None) == -4
 
 
 def test_ops_refuse_cpu_tensors():
@@ -142,6 +167,11 @@ def test_block_op_entry_points_validate_on_the_host():
     assert lib.dr_short_conv_silu(al, al, None, None, ctypes.c_void_p(al.value + 16), None, 1, 1, 8, 9, 1, 1, None) == -2
     assert lib.dr_short_conv_silu(al, al, None, None, al, None, 1, 1, 8, 4, 1, 1, None) == -9      # in place
     assert lib.dr_short_conv_silu(al, al, None, None, ctypes.c_void_p(al.value + 8), None, 1, 1, 8, 4, 1, 1, None) == -4
+    y = ctypes.c_void_p(al.value + 64)
+    w4 = ctypes.c_void_p(al.value + 4)        # the taps and the bias are read as float4: 4-byte alignment is not enough
+    assert lib.dr_short_conv_silu(al, w4, None, None, y, None, 1, 1, 8, 4, 1, 1, None) == -4
+    assert lib.dr_short_conv_silu(al, al, w4, None, y, None, 1, 1, 8, 4, 1, 1, None) == -4
+    assert lib.dr_short_conv_silu(al, w4, None, None, y, None, 1, 1, 8, 1, 1, 1, None) != -4     # W == 1: weight unused
     assert lib.dr_gate_activations(2, al, None, al, None, al, None, 1, 1, 1, 1, 0, 0, 1.0, 20.0, None) == -6
     assert lib.dr_gate_activations(0, al, None, al, None, al, None, 1, 1, 1, 4, 0, 0, 1.0, 20.0, None) == -2
     assert lib.dr_gate_activations(0, al, al, al, None, al, None, 1, 1, 1, 1, 0, 0, 1.0, 20.0, None) == -1

@@ -102,7 +102,8 @@ def test_split_serves_scalar_and_no_decay(variant):
     assert _rel(o, o1) <= BF16_TOL and _rel(hT, hT1) <= BF16_TOL
 
 
-def test_split_without_workspace_falls_back_or_errors():
+def test_split_without_workspace_is_refused():
+    """No silent downgrade: the two-kernel path without its workspace is DR_ERR_WORKSPACE, by name or by AUTO."""
     import ctypes
     from linearnexus_b200 import ops
     inp = O.make_inputs("kda", 1, 1, 64, 128, 128, seed=1, io_dtype=torch.bfloat16)
@@ -112,7 +113,7 @@ def test_split_without_workspace_falls_back_or_errors():
     hT = torch.empty(1, 1, 128, 128, device="cuda")
     vp = lambda t: ctypes.c_void_p(t.data_ptr())
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-    for path, want in ((None, 0), ("split", -5)):
+    for path, want in ((None, -5), ("split", -5), ("fp32", 0)):
         d = ops._desc(_lib.DR_KDA, _lib.DR_LAYOUT_BHTD, 1, 1, 64, 128, 128, 64, cu["q"], cu["g"], torch.float32, True,
                       128 ** -0.5, path)
         st = lib.dr_chunk_fwd(ctypes.byref(d), vp(cu["q"]), vp(cu["k"]), vp(cu["v"]), vp(cu["g"]), vp(cu["beta"]),
