@@ -7,31 +7,35 @@
 //
 // Four groups of four warps (one warp per 32-lane quarter of tensor memory in each group) form a
 // pipeline over the chunks of the sequence.  Each group has its own instruction stream, so the short
-// dependent phases of one group fill the issue slots the others leave idle:
+// dependent phases of one group fill the issue slots the others leave idle.  A tcgen05.mma instruction
+// occupies the tensor pipe (and its issuing thread) for about 64 cycles whatever its N <= 128; the 40
+// instructions of a chunk are spread over elected threads of three groups so that only products (3) and
+// (5) sit on the serial chain.
 //
 //   PA (warps 0-3)   state-independent, chunk n:
 //     K,Q rows land by TMA as one [K;Q] tile already in core-matrix order (3-deep ring, one chunk ahead).
 //     The l2 norms are not applied to the tiles: they are folded into row and column factors (rk from the
 //     diagonal of D1, rq from the raw Q rows).
 //     (1) D1 = [K;Q] K^T                             128x64x128  smem x smem, issued one chunk ahead
-//         X = D1[i][j] e^{G_i-G_j} (i>j, fp32) -> fp32 matrix;  A_qk = D1[64+i][j] e^{G_i-G_j} (i>=j) -> bf16 tile
+//         X = D1[i][j] e^{G_i-G_j} (i>=j, fp32) -> fp32 matrix;  A_qk = D1[64+i][j] e^{G_i-G_j} (i>=j) -> bf16 tile
 //   PB (warps 4-7)   chunk n, one hand-over behind PA:
 //         T = (I + diag(beta rk^2) X)^-1 in place: 8x8 blocks by substitution, three merge levels on mma.sync tf32
 //         -> Tb = T diag(beta rk), Tw = T diag(beta e^G rk^2)   bf16 tiles
-//   CB (warps 12-15) the products and copies that feed or drain the chain:
-//     (2) U^T = V^T Tb^T  -> TMEM (stage accumulator)  128x64x64   smem(MN-major) x smem
-//         W^T = K^T Tw^T  -> idle TMEM columns -> bf16 tile W (MN-major B operand: 16-byte stores)
-//         output of the previous chunk: O^T[v][i] = rq_i (e^{G_i} Dq[v][i] + Do[v][i]) -> staging tile -> TMA store
+//   CB (warps 12-15) everything around the chain, as early as its inputs allow:
+//         rq_i = scale / (||q_i|| + eps)
+//     (2) W^T = K^T Tw^T  -> the stage accumulator (still idle) -> bf16 tile W (MN-major B operand: 16-byte stores)
+//         U^T = V^T Tb^T  -> the stage accumulator            128x64x64   smem(MN-major) x smem
+//         output of the previous chunk: O^T[v][i] = rq_i (e^{G_i} Dq[v][i] + Do[v][i]) -> staging tile (the V
+//         buffer) -> one TMA store;  then  Dq = S^T Q^T of this chunk               128x64x128
 //   CA (warps 8-11)  the serial chain over the state:
 //         bf16 copy of S^T for the products; fp32 S^T pre-multiplied by e^{G_L}
 //     (3) V_new^T = U^T - S^T W^T  (accumulated onto U^T with negate-A)                    128x64x128
-//         Dq = S^T Q^T                                                                     128x64x128
 //         V_new^T -> bf16, plain and decayed by e^{G_L-G_c}
 //     (5) S^T += (V_new^T e^{G_L-G_c}) K   (K read MN-major)                                128x128x64
 //     (4) Do = V_new^T A_qk^T                                                              128x64x64
 //
 // The [K;Q] tile is stored once as 8x8 core matrices and serves as A and B of (1), MN-major
-// A of (2), K-major B of (3) and MN-major B of (5).  Hand-overs are mbarriers (arrive counts of a whole
+// A of (2), K-major B of Dq and MN-major B of (5).  Hand-overs are mbarriers (arrive counts of a whole
 // group, or tcgen05.commit for product completion); every wait is bounded: a wait that runs out sets
 // DR_DEV_TIMEOUT in the status word and the kernel finishes without further waiting.
 #pragma once
@@ -56,20 +60,21 @@ constexpr int kGrp = 128;
 constexpr uint32_t TM_S = 0;      // S^T fp32                                   128
 constexpr uint32_t TM_SB = 128;   // bf16 copy of S^T (A operand)                 64
 constexpr uint32_t TM_D1 = 192;   // D1                                           64
-constexpr uint32_t TM_DU = 256;   // 2 stages x 64: U^T -> V_new^T -> Do          128
+constexpr uint32_t TM_DU = 256;   // 2 stages x 64: W^T, then U^T -> V_new^T -> Do   128
 constexpr uint32_t TM_DQ = 384;   // S^T Q^^T                                     64
-constexpr uint32_t TM_VA = 448;   // V_new^T bf16 (before that: W^T fp32, 64 columns from here)   32
+constexpr uint32_t TM_VA = 448;   // V_new^T bf16                                 32
 constexpr uint32_t TM_VB = 480;   // decayed V_new^T bf16                         32
 constexpr uint32_t TM_COLS = 512;
 
 // shared-memory map (bytes)
 constexpr int QK_TILE = 128 * 128 * 2;        // [K (64 rows); Q (64 rows)] x 128 raw bf16, 32 KB
 constexpr int SM_QKR = 0;                     // ring of 3 such tiles (chunk n uses tile n % 3)
-constexpr int SM_STAGE = 3 * QK_TILE;         // two stages follow
-constexpr int ST_W = 0;                       // W as [128 k][64 c] core matrices (16 KB); reused as the O staging tile
-constexpr int ST_AQK = ST_W + 128 * 64 * 2;   // A_qk [64][64]                           8 KB
-constexpr int STAGE_BYTES = ST_AQK + 64 * 64 * 2;
-constexpr int SM_V = SM_STAGE + 2 * STAGE_BYTES;  // V [64][128] core-matrix tile       16 KB
+constexpr int W_TILE = 128 * 64 * 2;          // W as [128 k][64 c] core matrices, 16 KB
+constexpr int SM_W = 3 * QK_TILE;             // one W tile
+constexpr int SM_O = SM_W + W_TILE;           // O staging tile [64][128] bf16 row-major, 16 KB
+constexpr int AQK_TILE = 64 * 64 * 2;         // A_qk [64][64] bf16, 8 KB
+constexpr int SM_AQK = SM_O + 64 * 128 * 2;   // three A_qk tiles (chunk n uses n % 3)
+constexpr int SM_V = SM_AQK + 3 * AQK_TILE;   // V [64][128] core-matrix tile, 16 KB
 constexpr int SM_TB = SM_V + 64 * 128 * 2;    // T diag(beta)        [64][64] bf16
 constexpr int SM_TW = SM_TB + 64 * 64 * 2;    // T diag(beta e^G)    [64][64] bf16
 constexpr int AKK_BYTES = 64 * LDT * 4;       // X, then T in place: fp32 [64][68]
@@ -77,12 +82,12 @@ constexpr int SM_AKK = SM_TW + 64 * 64 * 2;   // two such matrices (chunk n uses
 constexpr int SM_TOTAL = SM_AKK + 2 * AKK_BYTES;
 
 struct alignas(16) Ctl {
-  uint64_t full[2], empty[2], akk[2], akkfree[2], kq[3], vb, barP, barW, barUW, uwfree, wrdy, bar1, bar2s, bar2, oload;
-  alignas(16) float gb[3][128];      // raw beta (0..63) and g (64..127) of chunk m in slot m % 3
-  alignas(16) float sc[3][384];      // of chunk m in slot m % 3: G, e^G, e^{G_L-G}, beta (64 each); G log2(e) (64);
-                         // 2^{G2_32 - G2_j}, j < 32 (32); 2^{G2_i - G2_32}, i >= 32 (32)
-  alignas(16) float rq[2][64];       // per stage: scale / (||q_i|| + eps)
-  alignas(16) float keep[2][128];    // per stage, CB-private: rq_i e^{G_i} (0..63) and rq_i (64..127) of the chunk whose output is pending
+  uint64_t full[2], empty[2], akk[2], akkfree[2], kq[3], vb, barP, barW, barUW, uwfree, wrdy, sbrdy, bar1, bar2s, bar2,
+      barDq;
+  alignas(16) float gb[128];         // raw beta (0..63) and g (64..127) of the chunk being scanned
+  alignas(16) float rq[3][64];       // scale / (||q_i|| + eps) of chunk m in slot m % 3
+  alignas(16) float sc[3][320];      // of chunk m in slot m % 3: G, e^G, e^{G_L-G}, beta, G log2(e) (64 each)
+  alignas(16) float keep[2][128];    // per stage, CB-private: rq_i e^{G_i} (0..63) and rq_i (64..127)
   alignas(16) float rk[2][64];       // per X buffer: 1 / (||k_j|| + eps)
   alignas(16) float rs[2][64];       // per X buffer: beta_i rk_i^2, row factor of the unit-lower system
   uint32_t tmem_base;
@@ -90,8 +95,7 @@ struct alignas(16) Ctl {
 };
 
 // Kernel parameters: the common forward parameters plus the TMA tensor maps (see make_input_map /
-// make_output_map).  qc2/qc4 (vc2/vc4) are the fixed coordinates of this layout: the column-block origin
-// and the outermost index are derived from (b, h) in the kernel.
+// make_output_map); the map coordinates of a sequence are derived from (b, h) in the kernel.
 struct alignas(64) Sm100Params {
   CUtensorMap tk, tq, tv, to;
   FwdParams p;
@@ -129,6 +133,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int grp = warp >> 2;             // 0 PA, 1 PB, 2 CA, 3 CB
   const int gt = tid & (kGrp - 1);       // thread index inside its group = tensor-memory lane it owns
+  const int wq = warp & 3;
   const int T = p.map.T;
   const int unit = blockIdx.x;
   const int b = unit / p.map.H, h = unit % p.map.H;
@@ -147,7 +152,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
       tc::mbar_init(tc::smem_u32(&ctl.full[i]), kGrp);
-      tc::mbar_init(tc::smem_u32(&ctl.empty[i]), 2 * kGrp);
+      tc::mbar_init(tc::smem_u32(&ctl.empty[i]), kGrp);
       tc::mbar_init(tc::smem_u32(&ctl.akk[i]), kGrp);
       tc::mbar_init(tc::smem_u32(&ctl.akkfree[i]), kGrp);
     }
@@ -158,10 +163,11 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
     tc::mbar_init(tc::smem_u32(&ctl.barUW), 1);
     tc::mbar_init(tc::smem_u32(&ctl.uwfree), 1);
     tc::mbar_init(tc::smem_u32(&ctl.wrdy), kGrp);
+    tc::mbar_init(tc::smem_u32(&ctl.sbrdy), kGrp);
     tc::mbar_init(tc::smem_u32(&ctl.bar1), 1);
     tc::mbar_init(tc::smem_u32(&ctl.bar2s), 1);
     tc::mbar_init(tc::smem_u32(&ctl.bar2), 1);
-    tc::mbar_init(tc::smem_u32(&ctl.oload), kGrp);
+    tc::mbar_init(tc::smem_u32(&ctl.barDq), 1);
     tc::fence_mbar_init();
     ctl.abort = 0;
   }
@@ -169,7 +175,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
   __syncthreads();
   tc::tc_fence_after();
   const uint32_t tbase = ctl.tmem_base;
-  const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+  const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
   volatile int* abort_p = &ctl.abort;
 
   auto wait_bar = [&](uint64_t* bar, uint32_t parity) {
@@ -193,16 +199,17 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
     // =========================== PA: K,Q tiles, D1, decay masks ======================================
     const __nv_bfloat16* gq = reinterpret_cast<const __nv_bfloat16*>(p.q);
     const __nv_bfloat16* gk = reinterpret_cast<const __nv_bfloat16*>(p.k);
-    const float* gg = reinterpret_cast<const float*>(p.g);
-    const int wq = warp & 3;
+    const float* gg = p.g ? reinterpret_cast<const float*>(p.g) + s_base : nullptr;
+    const float* gbeta = p.beta + s_base;
 
     // K,Q rows (raw bf16), g and beta of chunk m -> ring tile m % 3 / raw scalars.  The l2 normalisation is
-    // NOT applied to the tiles: it is folded into the factors rk, rs, rq.
+    // NOT applied to the tiles: it is folded into the factors rk, rs, rq.  Warp 0 fetches the scalars (and
+    // later scans them); with TMA its first lane also issues the tile copies.
     auto issue_kq = [&](int m) {
       const int t0m = m * kC, rowsm = min(kC, T - t0m);
       uint8_t* dQK = smem + SM_QKR + (m % 3) * QK_TILE;
       if (kTma) {
-        if (gt == 32) {  // a warp other than the one that issues the products
+        if (gt == 0) {
           const uint32_t bar = tc::smem_u32(&ctl.kq[m % 3]);
           tc::mbar_arrive_expect_tx(bar, 2u * 64 * 256);
           tc::tma_load_5d(tc::smem_u32(dQK), &P.tk, 0, 0, qc2, m * 8, qc4, bar);
@@ -210,7 +217,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         }
       } else {
         const int rin = gt & 7, kb = gt >> 3;
-#pragma unroll
+#pragma unroll 2
         for (int rb = 0; rb < 8; ++rb) {
           const int r = rb * 8 + rin;
           const bool live = r < rowsm;
@@ -219,13 +226,16 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
           tc::cp_async16(tc::smem_u32(dQK + tc::core_off(64 + r, kb * 8, RBS)), gq + off, live);
         }
       }
-      {
-        float* dG = ctl.gb[m % 3];
-        const int r = gt & 63;
-        const bool live = r < rowsm;
-        const int64_t off = s_base + (int64_t)(t0m + (live ? r : 0)) * s_tok;
-        if (gt < 64) tc::cp_async4(tc::smem_u32(dG + r), p.beta + off, live);                    // beta
-        else tc::cp_async4(tc::smem_u32(dG + 64 + r), gg ? gg + off : p.beta + off, live && gg);  // g (0 without decay)
+      if (warp == 0) {
+        float* dG = ctl.gb;
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const int r = lane + 32 * hf;
+          const bool live = r < rowsm;
+          const int64_t off = live ? (int64_t)(t0m + r) * s_tok : 0;
+          tc::cp_async4(tc::smem_u32(dG + r), gbeta + off, live);                          // beta
+          tc::cp_async4(tc::smem_u32(dG + 64 + r), gg ? gg + off : gbeta, live && gg);     // g (0 without decay)
+        }
       }
       tc::cp_async_commit();
     };
@@ -238,13 +248,12 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       }
     };
 
-    // inclusive scan of the log decay over the 64 rows of a chunk (one warp): G, e^G, e^{G_L - G}, beta, and
-    // the factors of the decay mask: for a row i >= 32 and a column j < 32,
-    // e^{G_i - G_j} = 2^{G2_i - G2_32} 2^{G2_32 - G2_j} with both exponents <= 0 (G2 = G log2 e)
+    // inclusive scan of the log decay over the 64 rows of a chunk (one warp): G, e^G, e^{G_L - G}, beta and
+    // G2 = G log2(e) (the decay mask takes its exponentials in base 2)
     auto scan_stage = [&](int m) {
       constexpr float kLog2e = 1.4426950408889634f;
       float* zG = ctl.sc[m % 3];
-      const float* raw = ctl.gb[m % 3];
+      const float* raw = ctl.gb;
       zG[192 + lane] = raw[lane]; zG[224 + lane] = raw[32 + lane];   // beta
       float a = raw[64 + lane], bq = raw[96 + lane];
 #pragma unroll
@@ -256,14 +265,11 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       const float tot = __shfl_sync(0xffffffffu, a, 31);
       bq += tot;
       const float last = __shfl_sync(0xffffffffu, bq, 31);
-      const float g32 = __shfl_sync(0xffffffffu, bq, 0);     // G of row 32
       zG[lane] = a; zG[lane + 32] = bq;
       zG[64 + lane] = tc::fast_exp2(a * kLog2e); zG[96 + lane] = tc::fast_exp2(bq * kLog2e);
       zG[128 + lane] = tc::fast_exp2(fminf(last - a, 0.f) * kLog2e);
       zG[160 + lane] = tc::fast_exp2(fminf(last - bq, 0.f) * kLog2e);
       zG[256 + lane] = a * kLog2e; zG[288 + lane] = bq * kLog2e;
-      zG[320 + lane] = tc::fast_exp2(fminf(g32 - a, 0.f) * kLog2e);
-      zG[352 + lane] = tc::fast_exp2(fminf(bq - g32, 0.f) * kLog2e);
     };
 
     // first product of chunk m: D1 = [K;Q] K^T on the raw rows (B = first 64 rows of the same tile)
@@ -281,20 +287,20 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
 
     issue_kq(0);
     land_kq(0);
-    group_sync128(1);
-    if (warp == 1) scan_stage(0);
-    if (gt == 0) issue_d1(0);
+    if (warp == 0) { __syncwarp(); scan_stage(0); }
+    if (gt == 64) issue_d1(0);
     uint32_t phP = 0;
     PROF_DECL
     for (int n = 0; n < nchunks; ++n) {
       const int s = n & 1;
-      uint8_t* sAqk = smem + SM_STAGE + s * STAGE_BYTES + ST_AQK;
+      uint8_t* sAqk = smem + SM_AQK + (n % 3) * AQK_TILE;
       float* sX = sAkk0 + s * (64 * LDT);
       const float* sG = ctl.sc[n % 3];
       const float* sBeta = sG + 192;
       group_sync128(1);  // the scalars of this chunk (scan) are visible
       PROF(0);
-      // chunk n-2 has left the consumers and PB: tile (n+1) % 3, stage s and X buffer s are free
+      // chunk n-2 has left the consumer and PB: ring tile, A_qk tile, scalar and rq slots (n+1) % 3 and X buffer s
+      // are free
       if (n >= 2) {
         wait_bar(&ctl.empty[s], ((n >> 1) - 1) & 1);
         wait_bar(&ctl.akkfree[s], ((n >> 1) - 1) & 1);
@@ -306,112 +312,101 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       tc::tc_fence_after();
       PROF(3);
       {
+        // one pass per 32-column half at or below this warp's diagonal (rows 0..31: one, rows 32..63: two), the same
+        // code for both: x = D1 . 2^{min(G2_i - G2_j, 0)}.  X keeps whatever lands above the diagonal (the inverse
+        // reads the strict lower triangle only; the diagonal holds ||k_i||^2 until the inverse overwrites it);
+        // the A_qk tile is an operand of product (4) and gets exact zeros there.  The row factor beta_i rk_i^2 and
+        // the column factors rk_j are applied later (rs in the solve, rk in the Tb/Tw tiles).
         const int i = gt & 63;
         const bool qrow = gt >= 64;        // warps 2,3 hold the Q rows (A_qk); warps 0,1 the K rows (X)
-        const int hown = wq & 1;           // the 32-column half that holds this warp's diagonal
+        const int nh = 1 + (wq & 1);
         const float* sG2 = sG + 256;
-        if (hown) {
-          // rows 32..63 x columns 0..31 lie wholly below the diagonal: factorised decay, no exponentials here
-          const float ai = sG[352 + (i - 32)];
-          uint32_t r[32];
-          tc::tmem_ld32(tbase + TM_D1 + lane_addr, r);
-          tc::tc_wait_ld();
-          if (!qrow) {
-#pragma unroll
-            for (int j4 = 0; j4 < 8; ++j4) {
-              const float4 c4 = *reinterpret_cast<const float4*>(sG + 320 + 4 * j4);
-              float4 o4;
-              o4.x = __uint_as_float(r[4 * j4 + 0]) * ai * c4.x; o4.y = __uint_as_float(r[4 * j4 + 1]) * ai * c4.y;
-              o4.z = __uint_as_float(r[4 * j4 + 2]) * ai * c4.z; o4.w = __uint_as_float(r[4 * j4 + 3]) * ai * c4.w;
-              *reinterpret_cast<float4*>(sX + i * LDT + 4 * j4) = o4;
-            }
-          } else {
-#pragma unroll
-            for (int j8 = 0; j8 < 4; ++j8) {
-              const float4 ca = *reinterpret_cast<const float4*>(sG + 320 + 8 * j8);
-              const float4 cb = *reinterpret_cast<const float4*>(sG + 320 + 8 * j8 + 4);
-              uint4 out;
-              out.x = tc::pack_bf16(__uint_as_float(r[8 * j8 + 0]) * ai * ca.x, __uint_as_float(r[8 * j8 + 1]) * ai * ca.y);
-              out.y = tc::pack_bf16(__uint_as_float(r[8 * j8 + 2]) * ai * ca.z, __uint_as_float(r[8 * j8 + 3]) * ai * ca.w);
-              out.z = tc::pack_bf16(__uint_as_float(r[8 * j8 + 4]) * ai * cb.x, __uint_as_float(r[8 * j8 + 5]) * ai * cb.y);
-              out.w = tc::pack_bf16(__uint_as_float(r[8 * j8 + 6]) * ai * cb.z, __uint_as_float(r[8 * j8 + 7]) * ai * cb.w);
-              *reinterpret_cast<uint4*>(sAqk + tc::core_off(i, 8 * j8, A_RBS)) = out;
-            }
-          }
-        }
-        {
-          // the half with the diagonal: exact pairwise decay 2^{min(G2_i - G2_j, 0)}, masked to the lower triangle
-          const int c0 = 32 * hown;
-          const float Gi = sG2[i];
+        const float Gi = sG2[i];
+#pragma unroll 1
+        for (int hh = 0; hh < nh; ++hh) {
+          const int c0 = 32 * hh;
           uint32_t r[32];
           tc::tmem_ld32(tbase + TM_D1 + lane_addr + c0, r);
           tc::tc_wait_ld();
+#pragma unroll
+          for (int j4 = 0; j4 < 8; ++j4) {
+            const float4 g4 = *reinterpret_cast<const float4*>(sG2 + c0 + 4 * j4);
+            r[4 * j4 + 0] = __float_as_uint(__uint_as_float(r[4 * j4 + 0]) * tc::fast_exp2(fminf(Gi - g4.x, 0.f)));
+            r[4 * j4 + 1] = __float_as_uint(__uint_as_float(r[4 * j4 + 1]) * tc::fast_exp2(fminf(Gi - g4.y, 0.f)));
+            r[4 * j4 + 2] = __float_as_uint(__uint_as_float(r[4 * j4 + 2]) * tc::fast_exp2(fminf(Gi - g4.z, 0.f)));
+            r[4 * j4 + 3] = __float_as_uint(__uint_as_float(r[4 * j4 + 3]) * tc::fast_exp2(fminf(Gi - g4.w, 0.f)));
+          }
           if (!qrow) {
-            // X = (K K^T) . E on the raw rows, lower triangle INCLUDING the diagonal (= ||k_i||^2, which the inverse
-            // never reads and overwrites); the row factor beta_i rk_i^2 and the column factors rk_j are applied
-            // later (rs in the solve, rk in the Tb/Tw tiles)
 #pragma unroll
-            for (int j4 = 0; j4 < 8; ++j4) {
-              const float4 g4 = *reinterpret_cast<const float4*>(sG2 + c0 + 4 * j4);
-              const float gj[4] = {g4.x, g4.y, g4.z, g4.w};
-              float4 o4;
-              float* o = reinterpret_cast<float*>(&o4);
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const int jj = c0 + 4 * j4 + e;
-                const float x = __uint_as_float(r[4 * j4 + e]) * tc::fast_exp2(fminf(Gi - gj[e], 0.f));
-                o[e] = jj <= i ? x : 0.f;
-              }
-              *reinterpret_cast<float4*>(sX + i * LDT + c0 + 4 * j4) = o4;
-            }
-            const float d = sX[i * LDT + i];   // this thread's own store
-            const float rk = p.l2norm ? 1.f / (sqrtf(d) + 1e-6f) : 1.f;
-            ctl.rk[s][i] = rk;
-            ctl.rs[s][i] = sBeta[i] * rk * rk;
+            for (int j4 = 0; j4 < 8; ++j4)
+              *reinterpret_cast<uint4*>(sX + i * LDT + c0 + 4 * j4) = make_uint4(r[4 * j4], r[4 * j4 + 1], r[4 * j4 + 2], r[4 * j4 + 3]);
           } else {
+            const int lim = i - c0;   // columns c0 + e with e <= lim are at or below the diagonal
 #pragma unroll
             for (int j8 = 0; j8 < 4; ++j8) {
-              const float4 ga = *reinterpret_cast<const float4*>(sG2 + c0 + 8 * j8);
-              const float4 gb4 = *reinterpret_cast<const float4*>(sG2 + c0 + 8 * j8 + 4);
-              const float gj[8] = {ga.x, ga.y, ga.z, ga.w, gb4.x, gb4.y, gb4.z, gb4.w};
               uint4 out;
               uint32_t* o32 = reinterpret_cast<uint32_t*>(&out);
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
-                const int j0 = c0 + 8 * j8 + 2 * e;
-                float x0 = __uint_as_float(r[8 * j8 + 2 * e]) * tc::fast_exp2(fminf(Gi - gj[2 * e], 0.f));
-                float x1 = __uint_as_float(r[8 * j8 + 2 * e + 1]) * tc::fast_exp2(fminf(Gi - gj[2 * e + 1], 0.f));
-                x0 = j0 <= i ? x0 : 0.f;
-                x1 = j0 + 1 <= i ? x1 : 0.f;
+                const int e0 = 8 * j8 + 2 * e;
+                const float x0 = e0 <= lim ? __uint_as_float(r[e0]) : 0.f;
+                const float x1 = e0 + 1 <= lim ? __uint_as_float(r[e0 + 1]) : 0.f;
                 o32[e] = tc::pack_bf16(x0, x1);
               }
               *reinterpret_cast<uint4*>(sAqk + tc::core_off(i, c0 + 8 * j8, A_RBS)) = out;
             }
-            if (!hown) {   // rows 0..31: columns 32..63 lie above the diagonal
-#pragma unroll
-              for (int j8 = 0; j8 < 4; ++j8)
-                *reinterpret_cast<uint4*>(sAqk + tc::core_off(i, 32 + 8 * j8, A_RBS)) = make_uint4(0u, 0u, 0u, 0u);
-            }
           }
+        }
+        if (!qrow) {
+          const float d = sX[i * LDT + i];   // this thread's own store
+          const float rk = p.l2norm ? 1.f / (sqrtf(d) + 1e-6f) : 1.f;
+          ctl.rk[s][i] = rk;
+          ctl.rs[s][i] = sBeta[i] * rk * rk;
+        } else if (nh == 1) {   // rows 0..31: columns 32..63 lie above the diagonal
+#pragma unroll
+          for (int j8 = 0; j8 < 4; ++j8)
+            *reinterpret_cast<uint4*>(sAqk + tc::core_off(i, 32 + 8 * j8, A_RBS)) = make_uint4(0u, 0u, 0u, 0u);
         }
       }
       PROF(4);
-      if (n + 1 < nchunks) land_kq(n + 1);   // the next chunk's beta, g (and, without TMA, its K,Q rows)
       tc::fence_async_smem();                // the A_qk tile is read by the tensor cores
       tc::tc_fence_before();
+      arrive(&ctl.akk[s]);                   // X, A_qk, rk, rs of chunk n are ready: PB starts
       group_sync128(1);                      // every warp has drained D1 from tensor memory
       PROF(5);
+      // what the NEXT chunk needs from this group, behind the hand-over
       if (n + 1 < nchunks) {
-        if (gt == 0) issue_d1(n + 1);        // completes behind PB's inverse of this chunk
-        if (warp == 1) scan_stage(n + 1);
+        land_kq(n + 1);                      // the next chunk's beta, g (and, without TMA, its K,Q rows)
+        if (gt == 64) issue_d1(n + 1);       // completes behind PB's inverse of this chunk
+        if (warp == 0) { __syncwarp(); scan_stage(n + 1); }
       }
-      arrive(&ctl.akk[s]);   // X, A_qk, rk, rs and the scalars of chunk n are ready
       PROF(6);
     }
   } else if (grp == 1) {
     // =========================== PB: inverse, Tb / Tw tiles ==========================================
     uint8_t* sTb = smem + SM_TB;
     uint8_t* sTw = smem + SM_TW;
+    // rq_i = scale / (||q_i|| + eps) of chunk m from the raw rows 64..127 of its tile, two threads per row
+    auto q_norms = [&](int m) {
+      wait_bar(&ctl.kq[m % 3], (m / 3) & 1);
+      const uint8_t* sQKp = smem + SM_QKR + (m % 3) * QK_TILE;
+      const int row = gt >> 1, hf = gt & 1;
+      float ss = 0.f;
+#pragma unroll 2
+      for (int it = 0; it < 8; ++it) {
+        const uint4 c = *reinterpret_cast<const uint4*>(sQKp + tc::core_off(64 + row, (8 * hf + it) * 8, RBS));
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&c);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h2[e]);
+          ss += f.x * f.x + f.y * f.y;
+        }
+      }
+      ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+      if (hf == 0) ctl.rq[m % 3][row] = p.l2norm ? p.scale / (sqrtf(ss) + 1e-6f) : p.scale;
+    };
+
+    q_norms(0);
     PROF_DECL
     for (int n = 0; n < nchunks; ++n) {
       const int s = n & 1;
@@ -420,24 +415,6 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       const float* sBeta = ctl.sc[n % 3] + 192;
       wait_bar(&ctl.akk[s], (n >> 1) & 1);
       PROF(10);
-      {  // rq_i = scale / (||q_i|| + eps) from the raw rows 64..127 of the tile (it has landed: D1 has read it),
-         // two threads per row
-        const uint8_t* sQKp = smem + SM_QKR + (n % 3) * QK_TILE;
-        const int row = gt >> 1, hf = gt & 1;
-        float ss = 0.f;
-#pragma unroll 2
-        for (int it = 0; it < 8; ++it) {
-          const uint4 c = *reinterpret_cast<const uint4*>(sQKp + tc::core_off(64 + row, (8 * hf + it) * 8, RBS));
-          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&c);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 f = __bfloat1622float2(h2[e]);
-            ss += f.x * f.x + f.y * f.y;
-          }
-        }
-        ss += __shfl_xor_sync(0xffffffffu, ss, 1);
-        if (hf == 0) ctl.rq[s][row] = p.l2norm ? p.scale / (sqrtf(ss) + 1e-6f) : p.scale;
-      }
       block_inverse_64_inplace(sT, ctl.rs[s], gt, SyncPB());
       PROF(11);
       // the U^T, W^T products of the previous chunk have read Tb, Tw
@@ -477,13 +454,15 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       arrive(&ctl.full[s]);      // A_qk, Tb, Tw and the scalars of chunk n are ready
       arrive(&ctl.akkfree[s]);   // the X/T buffer may be overwritten
       PROF(13);
+      if (n + 1 < nchunks) q_norms(n + 1);   // in this group's idle time; published by its next arrival on `full`
+      PROF(14);
     }
   } else if (grp == 2) {
     // =========================== CA: the serial chain over the state =================================
     // initial state: S^T[v][k] = h0[k][v] (thread = value column v)
     {
       const float* h0 = p.h0 ? p.h0 + (int64_t)unit * kD * kD : nullptr;
-#pragma unroll
+#pragma unroll 1
       for (int cc = 0; cc < 4; ++cc) {
         const int c0 = 32 * cc;
         uint32_t r[32];
@@ -497,17 +476,18 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
     PROF_DECL
     for (int n = 0; n < nchunks; ++n) {
       const int s = n & 1;
-      const uint8_t* sQKc = smem + SM_QKR + (n % 3) * QK_TILE;
-      uint8_t* st = smem + SM_STAGE + s * STAGE_BYTES;
-      const uint32_t aQK = tc::smem_u32(sQKc), aW = tc::smem_u32(st + ST_W), aAqk = tc::smem_u32(st + ST_AQK);
+      const uint32_t aQK = tc::smem_u32(smem + SM_QKR + (n % 3) * QK_TILE);
+      const uint32_t aW = tc::smem_u32(smem + SM_W);
+      const uint32_t aAqk = tc::smem_u32(smem + SM_AQK + (n % 3) * AQK_TILE);
       const float* sEG = ctl.sc[n % 3] + 64;
       const float* sWd = sEG + 64;
-      wait_bar(&ctl.full[s], (n >> 1) & 1);
-      PROF(20);
       if (n >= 1) {
-        wait_bar(&ctl.bar2s, (n - 1) & 1);   // the state update of the previous chunk is complete
-        arrive(&ctl.empty[s ^ 1]);           // ... and so is every earlier product that read its K,Q tile
+        wait_bar(&ctl.bar2s, (n - 1) & 1);   // the state update of the previous chunk is complete, and with it
+        wait_bar(&ctl.barDq, (n - 1) & 1);   // every earlier product of the chain; Dq has read the bf16 state
+        arrive(&ctl.empty[s ^ 1]);           // chunk n-1: its K,Q tile and the A_qk tile of chunk n-2 are free
       }
+      PROF(20);
+      wait_bar(&ctl.full[s], (n >> 1) & 1);
       tc::tc_fence_after();
       PROF(21);
       // ---- state pass: bf16 copy of S^T for the products; fp32 master pre-multiplied by e^{G_L} --------
@@ -534,9 +514,10 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         tc::tc_wait_st();
       }
       tc::tc_fence_before();
+      arrive(&ctl.sbrdy);        // CB's elected thread issues Dq from the bf16 copy
       group_sync128(3);
       PROF(22);
-      // ---- (3) V_new^T = U^T - S^T W^T ;  Dq = S^T Q^T --------------------------------------------------
+      // ---- (3) V_new^T = U^T - S^T W^T --------------------------------------------------------------------
       if (gt == 0) {
         wait_bar(&ctl.wrdy, n & 1);          // W tile written by CB
         wait_bar(&ctl.barUW, n & 1);         // U^T complete
@@ -548,15 +529,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
           tc::mma_ts(tbase + TM_DU + 64 * s, tbase + TM_SB + ks * 8, desc_adv(wd0, ks * 2 * A_RBS), id_n64_bmn_neg, 1);
         tc::mma_commit(tc::smem_u32(&ctl.bar1));
         PROF(24);
-        if (n >= 1) wait_bar(&ctl.oload, (n - 1) & 1);   // the output epilogue of chunk n-1 has read Dq
-        tc::tc_fence_after();
-        PROF(25);
-        const uint64_t qd0 = tc::smem_desc(aQK + 8 * RBS, 128, RBS);   // Q^ = rows 64..127 of the tile
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          tc::mma_ts(tbase + TM_DQ, tbase + TM_SB + ks * 8, desc_adv(qd0, ks * 256), id_n64, ks > 0);
       }
-      PROF(26);
       wait_bar(&ctl.bar1, ph1); ph1 ^= 1;
       tc::tc_fence_after();
       PROF(27);
@@ -568,10 +541,14 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         tc::tmem_ld32(tbase + TM_DU + 64 * s + lane_addr + c0, r);
         tc::tc_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float x0 = __uint_as_float(r[2 * j]), x1 = __uint_as_float(r[2 * j + 1]);
-          pa[j] = tc::pack_bf16(x0, x1);
-          pb[j] = tc::pack_bf16(x0 * sWd[c0 + 2 * j], x1 * sWd[c0 + 2 * j + 1]);
+        for (int j4 = 0; j4 < 8; ++j4) {
+          const float4 w4 = *reinterpret_cast<const float4*>(sWd + c0 + 4 * j4);
+          const float x0 = __uint_as_float(r[4 * j4]), x1 = __uint_as_float(r[4 * j4 + 1]);
+          const float x2 = __uint_as_float(r[4 * j4 + 2]), x3 = __uint_as_float(r[4 * j4 + 3]);
+          pa[2 * j4] = tc::pack_bf16(x0, x1);
+          pa[2 * j4 + 1] = tc::pack_bf16(x2, x3);
+          pb[2 * j4] = tc::pack_bf16(x0 * w4.x, x1 * w4.y);
+          pb[2 * j4 + 1] = tc::pack_bf16(x2 * w4.z, x3 * w4.w);
         }
         tc::tmem_st16(tbase + TM_VA + lane_addr + c0 / 2, pa);
         tc::tmem_st16(tbase + TM_VB + lane_addr + c0 / 2, pb);
@@ -601,7 +578,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
     tc::tc_fence_after();
     if (p.hT) {
       float* hT = p.hT + (int64_t)unit * kD * kD;
-#pragma unroll
+#pragma unroll 1
       for (int cc = 0; cc < 4; ++cc) {
         const int c0 = 32 * cc;
         uint32_t r[32];
@@ -613,10 +590,11 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
     }
     wait_bar(&ctl.bar2, (nchunks - 1) & 1);   // every product has completed before tensor memory is released
   } else {
-    // =========================== CB: U^T / W^T products, W tile, output =================================
+    // =========================== CB: q norms, W tile, U^T, output, Dq ==================================
     const __nv_bfloat16* gv = reinterpret_cast<const __nv_bfloat16*>(p.v);
     __nv_bfloat16* go = reinterpret_cast<__nv_bfloat16*>(p.o);
     uint8_t* sV = smem + SM_V;
+    __nv_bfloat16* sO = reinterpret_cast<__nv_bfloat16*>(smem + SM_O);
     // V rows of chunk m -> core-matrix tile
     auto issue_v = [&](int m) {
       if (kTma) {
@@ -628,7 +606,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       } else {
         const int t0m = m * kC, rowsm = min(kC, T - t0m);
         const int rin = gt & 7, kb = gt >> 3;
-#pragma unroll
+#pragma unroll 2
         for (int rb = 0; rb < 8; ++rb) {
           const int r = rb * 8 + rin;
           const bool live = r < rowsm;
@@ -636,23 +614,28 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
           tc::cp_async16(tc::smem_u32(sV + tc::core_off(r, kb * 8, RBS)), src, live);
         }
         tc::cp_async_commit();
-      }
-    };
-    auto land_v = [&]() {
-      if (!kTma) {
         tc::cp_async_wait_all();
         tc::fence_async_smem();
         arrive(&ctl.vb);
       }
     };
-    // O^T of chunk m: rq_i (e^{G_i} Dq + Do) -> staging tile (the stage's W region, no longer needed)
-    // -> one tiled store; releases the accumulators and stage m & 1.
-    auto out_epilogue = [&](int m) {
+    // Dq = S^T Q^T of chunk m (elected thread): the bf16 state copy of chunk m is ready and the Dq columns
+    // have been read by the output epilogue of chunk m-1
+    auto issue_dq = [&](int m) {
+      wait_bar(&ctl.sbrdy, m & 1);
+      tc::tc_fence_after();
+      const uint64_t qd0 = tc::smem_desc(tc::smem_u32(smem + SM_QKR + (m % 3) * QK_TILE) + 8 * RBS, 128, RBS);   // rows 64..127
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        tc::mma_ts(tbase + TM_DQ, tbase + TM_SB + ks * 8, desc_adv(qd0, ks * 256), id_n64, ks > 0);
+      tc::mma_commit(tc::smem_u32(&ctl.barDq));
+    };
+    // O^T of chunk m: rq_i (e^{G_i} Dq + Do) -> staging tile -> one tiled store.  `next` >= 0: Dq of that chunk is
+    // issued as soon as every thread has read the Dq columns.
+    auto out_epilogue = [&](int m, int next) {
       const int sm_ = m & 1;
-      uint8_t* stm = smem + SM_STAGE + sm_ * STAGE_BYTES;
       const float* sEGm = ctl.keep[sm_];        // rq_i e^{G_i}
       const float* sRQm = ctl.keep[sm_] + 64;   // rq_i
-      __nv_bfloat16* sO = reinterpret_cast<__nv_bfloat16*>(stm + ST_W);
       const int t0m = m * kC;
       const int rowsm = min(kC, T - t0m);
 #pragma unroll 1
@@ -662,9 +645,15 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         tc::tmem_ld32(tbase + TM_DQ + lane_addr + c0, rq);
         tc::tmem_ld32(tbase + TM_DU + 64 * sm_ + lane_addr + c0, ro);
         tc::tc_wait_ld();
-        if (hh == 1) {
+        if (hh == 0) {
+          // the previous output store has read the staging tile (its issuing thread waits; the barrier below
+          // passes that on before anyone writes the tile)
+          if (P.use_tma_out && gt == 0) tc::bulk_wait_read_all();
+          group_sync128(4);
+        } else {
           tc::tc_fence_before();
-          arrive(&ctl.oload);   // Dq and this stage's accumulator are in registers
+          group_sync128(4);      // Dq and this stage's accumulator are in registers, in every thread
+          if (next >= 0 && gt == 0) issue_dq(next);
         }
         if (p.o) {
           // each thread owns one value column v and 32 tokens; neighbouring lanes swap halves of token pairs so
@@ -711,50 +700,32 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
     };
 
     issue_v(0);
-    land_v();
     PROF_DECL
     for (int n = 0; n < nchunks; ++n) {
       const int s = n & 1;
-      uint8_t* st = smem + SM_STAGE + s * STAGE_BYTES;
       const uint32_t aQK = tc::smem_u32(smem + SM_QKR + (n % 3) * QK_TILE);
-      uint8_t* sWt = st + ST_W;
-      if (n >= 1) {
-        wait_bar(&ctl.bar2, (n - 1) & 1);   // chunk n-1 is complete: its V_new operands, W tile and A_qk tile are dead
-        arrive(&ctl.empty[s ^ 1]);
-      }
-      PROF(30);
+      uint8_t* sWt = smem + SM_W;
       wait_bar(&ctl.full[s], (n >> 1) & 1);
       tc::tc_fence_after();
       PROF(31);
-      // the scalars the output epilogue of this chunk will need, kept where PA cannot overwrite them
+      // ---- (2a) W^T = K^T Tw^T -> this stage's accumulator, idle until U^T is issued into it ---------------
+      if (gt == 0) {
+        const uint64_t kd0 = tc::smem_desc(aQK, RBS, 128);   // K MN-major, 16 chunk rows per step
+        const uint64_t twd0 = tc::smem_desc(tc::smem_u32(smem + SM_TW), 128, A_RBS);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          tc::mma_ss(tbase + TM_DU + 64 * s, desc_adv(kd0, ks * 2 * RBS), desc_adv(twd0, ks * 256), id_n64_amn, ks > 0);
+        tc::mma_commit(tc::smem_u32(&ctl.barW));
+      }
+      // the scalars this chunk's output epilogue will need, kept where PA cannot overwrite them
       if (gt < 64) {
-        const float rqi = ctl.rq[s][gt];
+        const float rqi = ctl.rq[n % 3][gt];
         ctl.keep[s][gt] = ctl.sc[n % 3][64 + gt] * rqi;
         ctl.keep[s][64 + gt] = rqi;
       }
-      // ---- (2) W^T = K^T Tw^T -> the (idle) bf16 V_new columns;  U^T = V^T Tb^T -> stage accumulator ----------
-      if (gt == 0) {
-        // the output store that read this stage's staging tile has finished reading it; every other thread
-        // learns that through the completion barrier of the products issued next
-        if (P.use_tma_out) tc::bulk_wait_read_all();
-        wait_bar(&ctl.vb, n & 1);
-        tc::tc_fence_after();
-        const uint32_t aV = tc::smem_u32(sV), aTb = tc::smem_u32(smem + SM_TB), aTw = tc::smem_u32(smem + SM_TW);
-        const uint64_t kd0 = tc::smem_desc(aQK, RBS, 128);   // K MN-major, 16 chunk rows per step
-        const uint64_t twd0 = tc::smem_desc(aTw, 128, A_RBS);
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          tc::mma_ss(tbase + TM_VA, desc_adv(kd0, ks * 2 * RBS), desc_adv(twd0, ks * 256), id_n64_amn, ks > 0);
-        tc::mma_commit(tc::smem_u32(&ctl.barW));   // the W tile is on the chain's path: it does not wait for U^T
-        const uint64_t vd0 = tc::smem_desc(aV, RBS, 128);
-        const uint64_t tbd0 = tc::smem_desc(aTb, 128, A_RBS);
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          tc::mma_ss(tbase + TM_DU + 64 * s, desc_adv(vd0, ks * 2 * RBS), desc_adv(tbd0, ks * 256), id_n64_amn, ks > 0);
-        tc::mma_commit(tc::smem_u32(&ctl.barUW));
-      }
       PROF(32);
       wait_bar(&ctl.barW, n & 1);
+      if (n >= 1) wait_bar(&ctl.bar1, (n - 1) & 1);   // product (3) of the previous chunk has read the W tile
       tc::tc_fence_after();
       PROF(33);
       // ---- W^T[k][c] (lane = k) -> bf16 tile, key rows x chunk rows in core-matrix order (MN-major B of (3)) ---
@@ -762,7 +733,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       for (int hh = 0; hh < 2; ++hh) {
         const int c0 = 32 * hh;
         uint32_t r[32];
-        tc::tmem_ld32(tbase + TM_VA + lane_addr + c0, r);
+        tc::tmem_ld32(tbase + TM_DU + 64 * s + lane_addr + c0, r);
         tc::tc_wait_ld();
 #pragma unroll
         for (int cb = 0; cb < 4; ++cb) {
@@ -777,21 +748,44 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       tc::fence_async_smem();
       tc::tc_fence_before();
       arrive(&ctl.wrdy);
-      // Tb, Tw and the V tile are free once U^T has completed too: tell PB, and fetch the next chunk's V rows
-      wait_bar(&ctl.barUW, n & 1);
-      if (gt == 0) arrive(&ctl.uwfree);
-      if (n + 1 < nchunks) issue_v(n + 1);
+      group_sync128(4);   // W^T has left the accumulator in every thread; the kept scalars are visible
       PROF(34);
-      if (n + 1 < nchunks) land_v();
-      group_sync128(4);   // the kept scalars of this chunk are visible to the whole group (read one iteration later)
+      // ---- (2b) U^T = V^T Tb^T -> the same accumulator ---------------------------------------------------
+      if (gt == 0) {
+        tc::tc_fence_after();
+        wait_bar(&ctl.vb, n & 1);
+        tc::tc_fence_after();
+        const uint64_t vd0 = tc::smem_desc(tc::smem_u32(sV), RBS, 128);
+        const uint64_t tbd0 = tc::smem_desc(tc::smem_u32(smem + SM_TB), 128, A_RBS);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          tc::mma_ss(tbase + TM_DU + 64 * s, desc_adv(vd0, ks * 2 * RBS), desc_adv(tbd0, ks * 256), id_n64_amn, ks > 0);
+        tc::mma_commit(tc::smem_u32(&ctl.barUW));
+      }
+      if (gt == 0) {
+        wait_bar(&ctl.barUW, n & 1);   // V, Tb, Tw have been read: release Tb / Tw, fetch the next chunk's V rows
+        arrive(&ctl.uwfree);
+      }
+      if (n + 1 < nchunks) {
+        if (!kTma) wait_bar(&ctl.barUW, n & 1);   // every thread copies V rows
+        issue_v(n + 1);
+      }
       PROF(35);
-      if (n >= 1) out_epilogue(n - 1);
+      // ---- output of the previous chunk, then Dq of this one ---------------------------------------------
+      if (n >= 1) {
+        wait_bar(&ctl.bar2, (n - 1) & 1);   // Do and Dq of chunk n-1 are complete
+        wait_bar(&ctl.barDq, (n - 1) & 1);
+        tc::tc_fence_after();
+        out_epilogue(n - 1, n);
+      } else if (gt == 0) {
+        issue_dq(0);
+      }
       PROF(36);
     }
     wait_bar(&ctl.bar2, (nchunks - 1) & 1);
+    wait_bar(&ctl.barDq, (nchunks - 1) & 1);
     tc::tc_fence_after();
-    group_sync128(4);
-    out_epilogue(nchunks - 1);
+    out_epilogue(nchunks - 1, -1);
     if (P.use_tma_out && gt == 0) tc::bulk_wait_all();
   }
   tc::tc_fence_before();

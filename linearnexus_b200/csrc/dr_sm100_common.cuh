@@ -58,7 +58,7 @@ __device__ __forceinline__ void inverse_merge_level(const float* __restrict__ sA
   constexpr int TPP = MT * NT, NPAIR = 32 / BS, TILES = NPAIR * TPP;
   const int g = lane >> 2, t = lane & 3;
   // step 1: X = diag(rs) A_10 T_00   -> scratch at the mirrored block (rows c0.., columns r0..)
-#pragma unroll 1
+#pragma unroll
   for (int tile = w; tile < TILES; tile += NW) {
     const int pr = tile / TPP, rem = tile % TPP;
     const int mt = rem / NT, nt = rem % NT;
@@ -90,7 +90,7 @@ __device__ __forceinline__ void inverse_merge_level(const float* __restrict__ sA
   }
   sync();
   // step 2: T_10 = -T_11 X
-#pragma unroll 1
+#pragma unroll
   for (int tile = w; tile < TILES; tile += NW) {
     const int pr = tile / TPP, rem = tile % TPP;
     const int mt = rem / NT, nt = rem % NT;
