@@ -386,26 +386,15 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
     // =========================== PB: inverse, Tb / Tw tiles ==========================================
     uint8_t* sTb = smem + SM_TB;
     uint8_t* sTw = smem + SM_TW;
-    // rq_i = scale / (||q_i|| + eps) of chunk m from the raw rows 64..127 of its tile, two threads per row
+    // rq_i = scale / (||q_i|| + eps) of chunk m from the raw rows 64..127 of its tile
     auto q_norms = [&](int m) {
       wait_bar(&ctl.kq[m % 3], (m / 3) & 1);
-      const uint8_t* sQKp = smem + SM_QKR + (m % 3) * QK_TILE;
-      const int row = gt >> 1, hf = gt & 1;
-      float ss = 0.f;
-#pragma unroll 2
-      for (int it = 0; it < 8; ++it) {
-        const uint4 c = *reinterpret_cast<const uint4*>(sQKp + tc::core_off(64 + row, (8 * hf + it) * 8, RBS));
-        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&c);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f = __bfloat1622float2(h2[e]);
-          ss += f.x * f.x + f.y * f.y;
-        }
-      }
-      ss += __shfl_xor_sync(0xffffffffu, ss, 1);
-      if (hf == 0) ctl.rq[m % 3][row] = p.l2norm ? p.scale / (sqrtf(ss) + 1e-6f) : p.scale;
+      float* dst = ctl.rq[m % 3];
+      const float scale = p.scale;
+      const bool l2 = p.l2norm != 0;
+      row_sq_norms_64(smem + SM_QKR + (m % 3) * QK_TILE, 64, wq, lane,
+                      [&](int r, float ss) { dst[r] = l2 ? scale / (sqrtf(ss) + 1e-6f) : scale; });
     };
-
     q_norms(0);
     PROF_DECL
     for (int n = 0; n < nchunks; ++n) {

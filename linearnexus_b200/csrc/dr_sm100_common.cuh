@@ -38,6 +38,38 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
+// ||x_r||^2 for 64 rows of a bf16 core-matrix tile (rows row0 .. row0+63, 128 columns, row-block stride RBS) on
+// the warp-level tensor cores: warp w of a four-warp group takes rows 16w .. 16w+15, forms their 16x16 Gram
+// block with mma.sync m16n8k16 (the A fragments double as the B fragments) and keeps the diagonal.  A core
+// matrix (8 rows x 16 bytes, 128 contiguous bytes) is exactly one ldmatrix 8x8 matrix.
+// out(r, value) is called once per row by the lane that holds its diagonal entry.
+template <class Out>
+__device__ __forceinline__ void row_sq_norms_64(const uint8_t* tile, int row0, int w, int lane, Out out) {
+  const int mi = lane >> 3, rin = lane & 7;
+  const uint32_t base = tc::smem_u32(tile) + (uint32_t)(((row0 >> 3) + 2 * w + (mi & 1)) * RBS + (mi >> 1) * 128 + rin * 16);
+  float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks) {
+    uint32_t a[4];
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
+                 : "r"(base + ks * 256));
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d0[0]), "+f"(d0[1]), "+f"(d0[2]), "+f"(d0[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(a[0]), "r"(a[2]));
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d1[0]), "+f"(d1[1]), "+f"(d1[2]), "+f"(d1[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(a[1]), "r"(a[3]));
+  }
+  const int g = lane >> 2, t = lane & 3;
+  if (t == (g >> 1)) {   // this lane holds entries (g, g) of the first and (g+8, g+8) of the second product
+    out(16 * w + g, (g & 1) ? d0[1] : d0[0]);
+    out(16 * w + 8 + g, (g & 1) ? d1[3] : d1[2]);
+  }
+}
+
 // ---------------------------------------------------------------------------------------------------
 // T = (I + diag(rs) A)^-1 for a strictly lower-triangular 64x64 A (fp32, row stride LDT).
 // 8x8 diagonal blocks by forward substitution on the CUDA cores, then three merge levels
