@@ -6,16 +6,21 @@
 One "step" is one pass of the hot path over one batch of seeded synthetic input.  The default
 workload is the configuration the headline metric is quoted on: Gated DeltaNet chunkwise
 forward, bf16 q/k/v/o with fp32 accumulation, B=8, T=4096, H=16, d_k=d_v=128, chunk 64.
-With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank runs the same
-per-GPU batch on its own (batch x head) units -- weak scaling, no collective on the data path;
-NCCL only carries the barrier and the max-over-ranks of the device time.
+
+With N > 1 (launched by torch.distributed.run, one rank per GPU) the global batch is N x the per-GPU
+batch; every rank builds exactly its rows of it (the rows carry their own seeds, so the cut equals
+`linearnexus_b200.shard.shard_inputs` of the whole batch) and runs them with no collective on the data
+path -- weak scaling.  NCCL carries the barrier, the max-over-ranks of the device time and the gather of
+every rank's parity figures.  `strong` (N > 1, forward workloads) times the SAME global batch as N = 1
+cut over the ranks.
 
 Rank 0 prints ONE JSON line.  `value` is device-timed throughput with inputs resident in HBM;
 `e2e` is the same metric through the public op with host (pinned) inputs and outputs, copies
-inside the timed region; `roofline` is the dominant kernel against the measured peak;
-`cpu_baseline` is the CPU oracle timed on a bounded sample of the same workload.
-`--impl reference` times that CPU path alone (the reference itself needs JAX, which is not
-installed on these machines; the oracle restates its maths in torch).
+inside the timed region; `roofline` is the dominant kernel against the measured peak; `parity` is the
+largest error of sampled (batch, head) units of the timed configuration against the float64 recurrence
+(computed outside the timed regions); `cpu_baseline` is the CPU oracle timed on a bounded sample of the
+same workload.  `--impl reference` times that CPU path alone (the reference itself needs JAX, which is
+not installed on these machines; the oracle restates its maths in torch).
 """
 from __future__ import annotations
 
@@ -35,26 +40,22 @@ import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
 WORKLOADS = {
-    # name: variant, B, T, H, K, V, chunk, io dtype, kind
+    # name: variant, B (per GPU), T, H, K, V, chunk, kind
     "gdn_fwd": dict(variant="gated", B=8, T=4096, H=16, K=128, V=128, chunk=64, kind="chunk_fwd", cfg_id=2),
+    # the same call on the blocks' native [B,T,H,D] storage (transposed views, no copies)
+    "gdn_fwd_bthd": dict(variant="gated", B=8, T=4096, H=16, K=128, V=128, chunk=64, kind="chunk_fwd", cfg_id=2, bthd=True),
     "kda_fwd": dict(variant="kda", B=4, T=8192, H=32, K=128, V=128, chunk=64, kind="chunk_fwd", cfg_id=3),
     # same shape with the decay and the output in bf16 (the block's activation dtype; opt-in output dtype)
     "kda_fwd_bf16": dict(variant="kda", B=4, T=8192, H=32, K=128, V=128, chunk=64, kind="chunk_fwd", cfg_id=3,
                          g_bf16=True, out_bf16=True),
+    # 1024 consecutive decode steps on fresh inputs walk a [1024, ...] buffer (step i uses entry i % 1024)
     "gdn_decode": dict(variant="gated", B=256, T=1, H=32, K=128, V=128, chunk=0, kind="decode", cfg_id=4),
     # training configuration: B=16 over 8 GPUs = 2 batch rows per GPU; forward + backward
     "gdn_fwd_bwd": dict(variant="gated", B=2, T=4096, H=16, K=128, V=128, chunk=64, kind="fwd_bwd", cfg_id=5),
     "deltanet_fwd_fp32": dict(variant="delta", B=2, T=512, H=4, K=64, V=64, chunk=64, kind="chunk_fwd", cfg_id=1),
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel (ncu, see profiles/*.md)
-NCU_TRAFFIC = {
-    "gdn_fwd:chunk_tcgen05": 504.4e6,   # profiles/chunk_sm100_kernel_gdn_fwd.md (B=4 capture scaled by sequences)
-    "kda_fwd:chunk_split_tcgen05": 3.78e9,    # profiles/kda_split_kernels.md: both kernels, B=1 capture x 4 sequences-wise
-    "gdn_decode:step": 1026.8e6,        # profiles/step_kernel_gdn_decode.md (full size)
-    "gdn_decode:step_stream": 1023.5e6, # same file, second capture
-    "gdn_fwd_bwd:bwd_saved": 2123.1e6,  # profiles/bwd_chunk_kernel_phases.md: saving forward + pre-pass + adjoint + finalize (full size)
-}
+DECODE_BUFFER = 1024
 
 
 def alg_flops_per_token_head(C, K, V):
@@ -62,13 +63,22 @@ def alg_flops_per_token_head(C, K, V):
     return 6 * C * K + 4 * C * V + 6 * K * V + C * C / 3.0
 
 
-def alg_bytes_per_token_head(w, io_bytes=2):
-    K, V = w["K"], w["V"]
+def alg_bytes(w, io_bytes=2):
+    """Algorithmic bytes of one step: every input and output once at its storage width."""
+    B, H, T, K, V = w["B"], w["H"], w["T"], w["K"], w["V"]
+    units = B * H
     if w["kind"] == "decode":
-        return 2 * 4 * K * V + io_bytes * (2 * K + V) + 8 + io_bytes * V
-    g_bytes = (2 if w.get("g_bf16") else 4) * K if w["variant"] == "kda" else 4
+        return units * (2 * 4 * K * V + io_bytes * (2 * K + V) + 8 + io_bytes * V)
+    g_bytes = (2 if w.get("g_bf16") else 4) * K if w["variant"] == "kda" else (4 if w["variant"] == "gated" else 0)
     o_bytes = 4 if w["variant"] == "kda" and not w.get("out_bf16") else io_bytes
-    return io_bytes * (2 * K + V) + o_bytes * V + g_bytes + 4
+    per_token = io_bytes * (2 * K + V) + o_bytes * V + g_bytes + 4
+    total = units * T * per_token + units * 4 * K * V            # + final state
+    if w["variant"] == "kda":
+        total += units * 4 * K * V                               # + initial state
+    if w["kind"] == "fwd_bwd":
+        # backward alone: read q,k,v,do and g,beta; write dq,dk,dv and dbeta,dg
+        total += units * T * (io_bytes * (2 * K + 2 * V) + 8 + io_bytes * (2 * K + V) + 8)
+    return total
 
 
 def load_peaks():
@@ -78,6 +88,15 @@ def load_peaks():
         return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
                 "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", 0.0)), "source": "measured"}
     return dict(FALLBACK_PEAKS, source="fallback")
+
+
+def ncu_traffic(workload, path):
+    """DRAM bytes per launch of the step's kernels from the committed profiler captures (null when none)."""
+    p = ROOT / "profiles" / "ncu_traffic.json"
+    if not p.exists():
+        return None
+    rec = json.loads(p.read_text()).get(f"{workload}:{path}")
+    return None if rec is None else rec["dram_bytes_per_step"]
 
 
 class ClockSampler:
@@ -128,63 +147,116 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def make_host_inputs(w, seed, n_sets=1):
-    """Seeded inputs on the host in the op's [B,H,T,D] layout (bf16 q,k,v; fp32 g, beta)."""
-    from oracle.delta_rule_oracle import make_inputs  # input generator only; nothing is computed by the oracle here
+def host_rows(w, lo, hi):
+    """Rows lo..hi-1 of the workload's global batch (pinned host memory, the op's [B,H,T,D] layout)."""
+    from linearnexus_b200.synthetic import make_rows
     io = torch.float32 if w["cfg_id"] == 1 else torch.bfloat16
-    sets = []
-    for s in range(n_sets):
-        h0 = 0.02 if w["kind"] == "decode" or w["variant"] == "kda" else None
-        sets.append(make_inputs(w["variant"], w["B"], w["H"], w["T"], w["K"], w["V"], seed + s, io_dtype=io, h0_std=h0,
-                                g_dtype=torch.bfloat16 if w.get("g_bf16") else torch.float32))
-    return sets
+    h0 = 0.02 if w["kind"] == "decode" or w["variant"] == "kda" else None
+    host = make_rows(w["variant"], lo, hi, w["H"], w["T"], w["K"], w["V"], seed=1234 + w["cfg_id"], io_dtype=io,
+                     h0_std=h0, g_dtype=torch.bfloat16 if w.get("g_bf16") else torch.float32)
+    return {k: (None if v is None else v.contiguous().pin_memory()) for k, v in host.items()}
+
+
+def rel_err(got, ref):
+    got, ref = got.double().cpu(), ref.double()
+    return float((got - ref).abs().max() / ref.abs().max().clamp_min(1e-30))
+
+
+def forward_parity(w, host, o, hT, n_units=4, seed=0):
+    """Largest relative error (max|x - ref| / max|ref|) of o and the final state over `n_units` sampled (b, h)
+    units against the float64 token recurrence of the oracle."""
+    from oracle import delta_rule_oracle as O   # checker only: outside every timed region
+    B, H = host["q"].shape[0], host["q"].shape[1]
+    rng = np.random.default_rng(seed)
+    units = sorted({(int(rng.integers(B)), int(rng.integers(H))) for _ in range(4 * n_units)})[:n_units]
+    eo = es = 0.0
+    for (b, h) in units:
+        cut = lambda t: None if t is None else t[b:b + 1, h:h + 1].double()
+        q, k, v, g, beta, h0 = (cut(host[x]) for x in ("q", "k", "v", "g", "beta", "h0"))
+        if w["variant"] == "delta":
+            ro, rS = O.delta_rule_recurrent(q, k, v, beta, h0, compute_dtype=torch.float64)
+        elif w["variant"] == "gated":
+            ro, rS = O.gated_delta_rule_recurrent(q, k, v, g, beta, initial_state=h0, compute_dtype=torch.float64)
+        else:
+            ro, rS = O.kda_recurrent(q, k, v, g, beta, initial_state=h0, compute_dtype=torch.float64)
+        eo = max(eo, rel_err(o[b:b + 1, h:h + 1], ro))
+        es = max(es, rel_err(hT[b:b + 1, h:h + 1], rS))
+    return {"o_rel": eo, "state_rel": es, "units": len(units), "against": "float64 token recurrence (oracle)"}
 
 
 def run_ours(args, w, rank, world, dev):
     import linearnexus_b200 as L
-    from linearnexus_b200 import _lib
-    lib = _lib.load()  # raises if the CUDA library is missing: there is no fallback
+    from linearnexus_b200 import _lib, ops
+    _lib.load()  # raises if the CUDA library is missing: there is no fallback
 
-    host = make_host_inputs(w, 1234 + w["cfg_id"] + 1000 * rank)[0]
-    pin = {k: (None if v is None else v.contiguous().pin_memory()) for k, v in host.items()}
+    B = w["B"]
+    pin = host_rows(w, rank * B, (rank + 1) * B)
     devt = {k: (None if v is None else v.to(dev, non_blocking=True)) for k, v in pin.items()}
     torch.cuda.synchronize(dev)
     decode = w["kind"] == "decode"
-    tokens_per_step = w["B"] * w["T"]
+    fwd_bwd = w["kind"] == "fwd_bwd"
+    tokens_per_step = B * w["T"]
     kda_kw = dict(out_dtype=torch.bfloat16) if w.get("out_bf16") else {}
+    if w.get("bthd"):   # the blocks' storage: [B,T,H,D] arrays seen as [B,H,T,D] views (what a transpose-free block passes)
+        for x in ("q", "k", "v", "g", "beta"):
+            devt[x] = devt[x].transpose(1, 2).contiguous().transpose(1, 2)
 
+    def forward(t, **extra):
+        if w["variant"] == "gated":
+            return L.gated_delta_rule_chunkwise(t["q"], t["k"], t["v"], t["g"], t["beta"], chunk_size=w["chunk"], **extra)
+        if w["variant"] == "kda":
+            return L.kda_chunkwise(t["q"], t["k"], t["v"], t["g"], t["beta"], initial_state=t["h0"], chunk_size=w["chunk"],
+                                   **kda_kw, **extra)
+        return L.delta_rule_chunkwise(t["q"], t["k"], t["v"], t["beta"], chunk_size=w["chunk"], **extra)
+
+    dec = None
     if decode:
-        q, k, v, g, beta = (devt[x][:, :, 0].contiguous() if devt[x] is not None else None for x in ("q", "k", "v", "g", "beta"))
-        state = devt["h0"].clone()
+        # fresh q, k, v, g, beta for every one of DECODE_BUFFER consecutive steps, generated on the device
+        gen = torch.Generator(device=dev).manual_seed(4321 + rank)
+        H, K, V = w["H"], w["K"], w["V"]
+        rn = lambda *s: torch.randn(*s, generator=gen, device=dev)
+        nrm = lambda x: x / (x.norm(dim=-1, keepdim=True) + 1e-6)
+        dec = dict(q=nrm(rn(DECODE_BUFFER, B, H, K)).bfloat16(), k=nrm(rn(DECODE_BUFFER, B, H, K)).bfloat16(),
+                   v=rn(DECODE_BUFFER, B, H, V).bfloat16(),
+                   g=torch.nn.functional.logsigmoid(rn(DECODE_BUFFER, B, H) + 4.0), beta=torch.sigmoid(rn(DECODE_BUFFER, B, H)))
+        state0 = devt["h0"].clone()
+        state = devt["h0"]
+        counter = [0]
 
         def step():
-            return L.gated_delta_rule_step(q, k, v, g, beta, state, inplace=True)
-    elif w["kind"] == "fwd_bwd":
-        from linearnexus_b200 import ops as _ops
-        gen = torch.Generator().manual_seed(7)
-        d_o = torch.randn(w["B"], w["H"], w["T"], w["V"], generator=gen).to(torch.bfloat16).to(dev)
+            i = counter[0] % DECODE_BUFFER
+            counter[0] += 1
+            return L.gated_delta_rule_step(dec["q"][i], dec["k"][i], dec["v"][i], dec["g"][i], dec["beta"][i], state, inplace=True)
+    elif fwd_bwd:
+        gen = torch.Generator().manual_seed(7 + rank)
+        d_o = torch.randn(B, w["H"], w["T"], w["V"], generator=gen).to(torch.bfloat16)
+        pin_do = d_o.pin_memory()
+        d_o = pin_do.to(dev)
 
         def step():   # one forward (which keeps the per-chunk states) + the backward that uses them
-            o, hT, saved = _ops.chunk_forward_saving("gated", devt["q"], devt["k"], devt["v"], devt["g"], devt["beta"],
-                                                     chunk_size=w["chunk"])
-            gr = _ops.chunk_backward("gated", devt["q"], devt["k"], devt["v"], devt["g"], devt["beta"], d_o,
-                                     chunk_size=w["chunk"], saved=saved)
-            return o, gr["dq"]
-    elif w["variant"] == "gated":
-        def step():
-            return L.gated_delta_rule_chunkwise(devt["q"], devt["k"], devt["v"], devt["g"], devt["beta"], chunk_size=w["chunk"])
-    elif w["variant"] == "kda":
-        def step():
-            return L.kda_chunkwise(devt["q"], devt["k"], devt["v"], devt["g"], devt["beta"], initial_state=devt["h0"],
-                                   chunk_size=w["chunk"], **kda_kw)
+            o, hT, saved = ops.chunk_forward_saving("gated", devt["q"], devt["k"], devt["v"], devt["g"], devt["beta"],
+                                                    chunk_size=w["chunk"])
+            gr = ops.chunk_backward("gated", devt["q"], devt["k"], devt["v"], devt["g"], devt["beta"], d_o,
+                                    chunk_size=w["chunk"], saved=saved)
+            return o, hT, gr
     else:
         def step():
-            return L.delta_rule_chunkwise(devt["q"], devt["k"], devt["v"], devt["beta"], chunk_size=w["chunk"])
+            return forward(devt)
 
     def barrier():
         if world > 1:
             torch.distributed.barrier()
         torch.cuda.synchronize(dev)
+
+    def timed(fn, steps):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        barrier()
+        ev[0].record()
+        for i in range(steps):
+            fn()
+            ev[i + 1].record()
+        barrier()
+        return ev[0].elapsed_time(ev[-1]), [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]
 
     for _ in range(args.warmup):
         step()
@@ -200,70 +272,89 @@ def run_ours(args, w, rank, world, dev):
     if rank == 0:
         sampler.start()
     # ---- device-timed region: inputs resident in HBM, K steps, CUDA events on the launch stream ----
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     n0 = _lib.launch_count()
-    barrier()
-    ev[0].record()
-    for i in range(args.steps):
-        step()
-        ev[i + 1].record()
-    barrier()
+    total_ms, per_launch_ms = timed(step, args.steps)
     launches = _lib.launch_count() - n0
     path = _lib.last_path()
-    total_ms = ev[0].elapsed_time(ev[-1])
-    per_launch_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
     clocks = sampler.stop() if rank == 0 else None
+    ops.check_device_status(dev)   # a bounded wait that ran out inside a kernel raises here
+
+    # ---- parity of the timed configuration (outside the timed regions) ----
+    if decode:
+        from oracle import delta_rule_oracle as O
+        n_par = min(max(args.steps, 8), 64)
+        sub = [(int(b), int(h)) for b, h in np.random.default_rng(rank).integers(0, [B, w["H"]], size=(16, 2))]
+        S = state0.clone()
+        ref = torch.stack([state0[b, h] for b, h in sub]).double().cpu()[:, None]   # [16,1,K,V]
+        eo = 0.0
+        for i in range(n_par):
+            o, _ = L.gated_delta_rule_step(dec["q"][i], dec["k"][i], dec["v"][i], dec["g"][i], dec["beta"][i], S, inplace=True)
+            pick = lambda t: torch.stack([t[i][b, h] for b, h in sub]).double().cpu()[:, None]
+            ro, ref = O.gated_delta_rule_step(pick(dec["q"]), pick(dec["k"]), pick(dec["v"]), pick(dec["g"]), pick(dec["beta"]),
+                                              ref, compute_dtype=torch.float64)
+            eo = max(eo, rel_err(torch.stack([o[b, h] for b, h in sub])[:, None], ro))
+        es = float((torch.stack([S[b, h] for b, h in sub]).double().cpu()[:, None] - ref).abs().max())
+        parity = {"o_rel": eo, "state_abs": es, "units": len(sub), "steps": n_par,
+                  "against": "float64 gated_delta_rule_step (oracle), consecutive in-place steps"}
+        del S
+    else:
+        out = step()
+        torch.cuda.synchronize(dev)
+        parity = forward_parity(w, pin, out[0], out[1], seed=rank)
+    ops.check_device_status(dev)
 
     # ---- end-to-end region: host (pinned) inputs -> public op -> host outputs, copies timed ----
-    names = ("q", "k", "v", "g", "beta") if not decode else ()
-    fwd_bwd = w["kind"] == "fwd_bwd"
-    pin_do = d_o.cpu().pin_memory() if fwd_bwd else None
+    names = ("q", "k", "v", "g", "beta")
     out_host = None
     e2e_steps = max(1, min(args.steps, 5))
 
     def e2e_step():
         nonlocal out_host
         if decode:
-            qh, kh, vh, gh, bh = (pin[x][:, :, 0].contiguous().pin_memory() for x in ("q", "k", "v", "g", "beta"))
-            ins = [t.to(dev, non_blocking=True) for t in (qh, kh, vh, gh, bh)]
+            i = counter[0] % 8
+            counter[0] += 1
+            ins = [e2e_in[x][i].to(dev, non_blocking=True) for x in names]
             o, _ = L.gated_delta_rule_step(*ins, state, inplace=True)
             outs = [o]
+        elif not fwd_bwd and not w.get("bthd"):
+            # the public host-memory entry point: batch slices, H2D / kernel / D2H overlapped on three streams
+            if out_host is None:
+                o_dt = torch.float32 if w["variant"] == "kda" and not w.get("out_bf16") else pin["q"].dtype
+                out_host = [torch.empty((B, w["H"], w["T"], w["V"]), dtype=o_dt).pin_memory(),
+                            torch.empty((B, w["H"], w["K"], w["V"]), dtype=torch.float32).pin_memory()]
+            kw = dict(chunk_size=w["chunk"], **kda_kw)
+            if pin.get("h0") is not None:
+                kw["initial_state"] = pin["h0"]
+            L.chunkwise_from_host(w["variant"], pin["q"], pin["k"], pin["v"], pin["g"], pin["beta"],
+                                  out=out_host[0], final_state=out_host[1], **kw)
+            return
         else:
-            if not fwd_bwd:
-                # the public host-memory entry point: batch slices, H2D / kernel / D2H overlapped on three streams
-                if out_host is None:
-                    o_dt = torch.float32 if w["variant"] == "kda" and not w.get("out_bf16") else pin["q"].dtype
-                    out_host = [torch.empty((w["B"], w["H"], w["T"], w["V"]), dtype=o_dt).pin_memory(),
-                                torch.empty((w["B"], w["H"], w["K"], w["V"]), dtype=torch.float32).pin_memory()]
-                kw = dict(chunk_size=w["chunk"], **kda_kw)
-                if pin.get("h0") is not None:
-                    kw["initial_state"] = pin["h0"]
-                L.chunkwise_from_host(w["variant"], pin["q"], pin["k"], pin["v"], pin["g"], pin["beta"],
-                                      out=out_host[0], final_state=out_host[1], **kw)
-                return out_host
             ins = {x: (None if pin[x] is None else pin[x].to(dev, non_blocking=True)) for x in names}
+            ins["h0"] = devt["h0"]
+            if w.get("bthd"):
+                for x in names:
+                    ins[x] = ins[x].transpose(1, 2).contiguous().transpose(1, 2)
             if fwd_bwd:
                 do_dev = pin_do.to(dev, non_blocking=True)
-                o, hT, saved = _ops.chunk_forward_saving("gated", ins["q"], ins["k"], ins["v"], ins["g"], ins["beta"],
-                                                         chunk_size=w["chunk"])
-                gr = _ops.chunk_backward("gated", ins["q"], ins["k"], ins["v"], ins["g"], ins["beta"], do_dev,
-                                         chunk_size=w["chunk"], saved=saved)
-            elif w["variant"] == "gated":
-                o, hT = L.gated_delta_rule_chunkwise(ins["q"], ins["k"], ins["v"], ins["g"], ins["beta"], chunk_size=w["chunk"])
-            elif w["variant"] == "kda":
-                o, hT = L.kda_chunkwise(ins["q"], ins["k"], ins["v"], ins["g"], ins["beta"], initial_state=devt["h0"], chunk_size=w["chunk"])
+                o, hT, saved = ops.chunk_forward_saving("gated", ins["q"], ins["k"], ins["v"], ins["g"], ins["beta"],
+                                                        chunk_size=w["chunk"])
+                gr = ops.chunk_backward("gated", ins["q"], ins["k"], ins["v"], ins["g"], ins["beta"], do_dev,
+                                        chunk_size=w["chunk"], saved=saved)
+                outs = [o, hT] + [gr[x] for x in ("dq", "dk", "dv", "dg", "dbeta")]
             else:
-                o, hT = L.delta_rule_chunkwise(ins["q"], ins["k"], ins["v"], ins["beta"], chunk_size=w["chunk"])
-            outs = [o, hT] + ([gr[x] for x in ("dq", "dk", "dv", "dg", "dbeta")] if fwd_bwd else [])
+                outs = list(forward(ins))
         if out_host is None:
             out_host = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in outs]
         for h_, t in zip(out_host, outs):
             h_.copy_(t, non_blocking=True)
-        return outs
 
+    if decode:
+        e2e_in = {x: dec[x][:8].cpu().pin_memory() for x in names}   # host copies of the first buffer entries
+        counter[0] = 0
+        e2e_steps = min(e2e_steps, 8)
     e2e_step()
-    barrier()
     t_e0 = torch.cuda.Event(enable_timing=True); t_e1 = torch.cuda.Event(enable_timing=True)
+    barrier()
     t_e0.record()
     for _ in range(e2e_steps):
         e2e_step()
@@ -271,25 +362,62 @@ def run_ours(args, w, rank, world, dev):
     barrier()
     e2e_ms = t_e0.elapsed_time(t_e1) / e2e_steps
     if decode:
-        h2d = sum(pin[x][:, :, 0].numel() * pin[x].element_size() for x in ("q", "k", "v", "g", "beta"))
+        h2d = sum(e2e_in[x][0].numel() * e2e_in[x].element_size() for x in names)
     else:
         h2d = sum(pin[x].numel() * pin[x].element_size() for x in names if pin[x] is not None)
         if fwd_bwd:
             h2d += pin_do.numel() * pin_do.element_size()
-        elif pin.get("h0") is not None:
+        elif pin.get("h0") is not None and not w.get("bthd"):
             h2d += pin["h0"].numel() * pin["h0"].element_size()
     d2h = sum(t.numel() * t.element_size() for t in out_host)
 
-    times = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
+    # ---- strong scaling of the forward: the N = 1 global batch cut over the ranks ----
+    strong = None
+    if world > 1 and w["kind"] == "chunk_fwd" and not args.no_strong:
+        from linearnexus_b200.shard import shard_inputs
+        Bg = B                                    # the same global batch as a 1-GPU run
+        whole = {k: v for k, v in host_rows(w, 0, Bg).items()}
+        mine, mode = shard_inputs(whole, world, rank)
+        md = {k: (None if v is None else v.contiguous().to(dev)) for k, v in mine.items()}
+        if w.get("bthd"):
+            for x in names:
+                md[x] = md[x].transpose(1, 2).contiguous().transpose(1, 2)
+        for _ in range(3):
+            forward(md)
+        s_ms, _ = timed(lambda: forward(md), args.steps)
+        so, sh = forward(md)
+        torch.cuda.synchronize(dev)
+        sp = forward_parity(w, mine, so, sh, n_units=2, seed=rank)
+        strong = dict(ms=s_ms / args.steps, mode=mode, units=int(md["q"].shape[0] * md["q"].shape[1]), parity=sp)
+
+    times = torch.tensor([total_ms, e2e_ms, strong["ms"] if strong else 0.0, parity["o_rel"],
+                          parity.get("state_rel", parity.get("state_abs", 0.0)),
+                          strong["parity"]["o_rel"] if strong else 0.0, strong["parity"]["state_rel"] if strong else 0.0],
+                         dtype=torch.float64, device=dev)
+    per_rank = None
     if world > 1:
-        torch.distributed.all_reduce(times, op=torch.distributed.ReduceOp.MAX)
-    total_ms, e2e_ms = times.tolist()
+        gathered = [torch.empty_like(times) for _ in range(world)]
+        torch.distributed.all_gather(gathered, times)     # NCCL: every rank's times and parity figures
+        allv = torch.stack(gathered)
+        per_rank = allv[:, 3:5].tolist()
+        times = allv.max(dim=0).values                     # slowest rank, worst error
+    total_ms, e2e_ms, strong_ms, p_o, p_s, sp_o, sp_s = times.tolist()
+    parity["o_rel"] = p_o
+    parity["state_rel" if "state_rel" in parity else "state_abs"] = p_s
+    if per_rank is not None:
+        parity["per_rank"] = per_rank
+        parity["units"] = parity["units"] * world
     ms_per_step = total_ms / args.steps
-    value = world * tokens_per_step / (ms_per_step * 1e-3)
-    e2e_value = world * tokens_per_step / (e2e_ms * 1e-3)
-    return dict(ms_per_step=ms_per_step, value=value, e2e_value=e2e_value, h2d=h2d, d2h=d2h,
-                launches=launches, path=path, clocks=clocks, kernel_ms=float(np.mean(per_launch_ms)),
-                inputs=host)
+    res = dict(ms_per_step=ms_per_step, value=world * tokens_per_step / (ms_per_step * 1e-3),
+               e2e_value=world * tokens_per_step / (e2e_ms * 1e-3), h2d=h2d, d2h=d2h, launches=launches, path=path,
+               clocks=clocks, kernel_ms=float(np.mean(per_launch_ms)), parity=parity, strong=None)
+    if strong:
+        res["strong"] = {"global_batch": B, "units_per_rank": strong["units"], "sharded_over": strong["mode"],
+                         "ms_per_step": strong_ms, "value": B * w["T"] / (strong_ms * 1e-3), "unit": "tokens/s",
+                         "parity": {"o_rel": sp_o, "state_rel": sp_s},
+                         "note": "one CTA per (batch, head) sequence: the cut leaves units_per_rank CTAs for 148 SMs, "
+                                 "so the step time stays that of one sequence"}
+    return res
 
 
 def cpu_oracle_sample(w, target_s=12.0, threads=None):
@@ -327,7 +455,7 @@ def cpu_oracle_sample(w, target_s=12.0, threads=None):
     # the workload has B*H units; the sample has batch*heads of them
     scale = (batch * heads) / (w["B"] * w["H"])
     value = (w["B"] * w["T"]) * scale / sec
-    sample = (f"{'gated_delta_rule_step' if w['kind'] == 'decode' else w['variant'] + ' chunkwise'} oracle (torch fp32, CPU) on "
+    sample = (f"{'gated_delta_rule_step' if w['kind'] == 'decode' else w['variant'] + ' chunkwise'} oracle (torch fp32, CPU, forward only) on "
               f"B={batch},H={heads},T={w['T']},K={w['K']},V={w['V']} ({reps} reps, {sec:.3f} s each), "
               f"scaled linearly in B*H to the full workload")
     return dict(value=value, cores=cores, sample=sample, sec_per_rep=sec, reps=reps)
@@ -342,6 +470,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU seconds the cpu_baseline sample may take")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-strong", action="store_true", help="skip the strong-scaling sub-record of multi-GPU forward runs")
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (profiling captures of a small case)")
     ap.add_argument("--no-steady-warmup", action="store_true",
                     help="skip the ~50 ms of extra untimed launches (profiler captures: keeps the launch count small)")
@@ -355,10 +484,12 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     metric = ("decode_tokens_per_sec" if w["kind"] == "decode" else
               "delta_rule_fwd_bwd_tokens_per_sec" if w["kind"] == "fwd_bwd" else "delta_rule_fwd_tokens_per_sec")
-    config = {"workload": f"{args.workload}: {w['variant']} {'decode step' if w['kind'] == 'decode' else 'chunkwise forward'} "
-                          f"B={w['B']} T={w['T']} H={w['H']} d_k={w['K']} d_v={w['V']} chunk={w['chunk']} per GPU",
+    what = {"decode": "decode step", "fwd_bwd": "chunkwise forward + backward"}.get(w["kind"], "chunkwise forward")
+    config = {"workload": f"{args.workload}: {w['variant']} {what} "
+                          f"B={w['B']} T={w['T']} H={w['H']} d_k={w['K']} d_v={w['V']} chunk={w['chunk']} per GPU"
+                          + (", inputs stored [B,T,H,D]" if w.get("bthd") else ""),
               "per_gpu_batch": w["B"], "global_batch": w["B"] * world, "seq_len": w["T"], "heads": w["H"],
-              "sharding": f"batch x head units, {world} rank(s), no data-path collective",
+              "sharding": f"rows of one seeded global batch, {world} rank(s), no data-path collective",
               "l2": "inputs larger than L2 (no flush needed)" if w["cfg_id"] != 1 else "inputs fit in L2 (latency-bound case)"}
 
     if args.impl == "reference":
@@ -379,7 +510,10 @@ def main():
                 "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": info["cores"], "kind": "port",
                                  "sample": info["sample"]},
                 "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-                "note": "the reference is pure JAX and JAX is not installed here; this is the CPU oracle that restates it"}
+                "note": "the reference is pure JAX and JAX is not installed here; this is the CPU oracle that restates it. "
+                        "One host times a bounded sample and the figure is its throughput in tokens/s, which does not "
+                        "depend on how many GPUs the other arm uses: at N > 1 it is the rate at which this host's cores "
+                        "would work through the N-GPU global batch"}
         print(json.dumps(line))
         return
 
@@ -397,14 +531,13 @@ def main():
         units = w["B"] * w["H"] * w["T"]
         C = w["chunk"] or 64
         # duration of the step's kernels together (one launch for the fused forward and the decode step;
-        # intra + state pass for the two-kernel forward; forward + adjoint + finalize for fwd_bwd)
+        # intra + state pass for the two-kernel forward; forward + pre-pass + adjoint + finalize for fwd_bwd)
         ktime = res["ms_per_step"] * 1e-3
+        alg_b = alg_bytes(w, 4 if w["cfg_id"] == 1 else 2)
         if w["kind"] == "decode":
-            alg_b = alg_bytes_per_token_head(w) * units
             roof = {"bound": "hbm", "achieved": alg_b / ktime / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s"}
         else:
             flops = alg_flops_per_token_head(C, w["K"], w["V"]) * units * (3 if w["kind"] == "fwd_bwd" else 1)
-            alg_b = alg_bytes_per_token_head(w, 4 if w["cfg_id"] == 1 else 2) * units
             tf = flops / ktime / 1e12
             hb = alg_b / ktime / 1e9
             if w["variant"] == "kda":
@@ -418,8 +551,7 @@ def main():
         roof["peak_source"] = peaks["source"]
         roof["kernel"] = res["path"]
         roof["alg_bytes_per_launch"] = alg_b
-        # DRAM bytes per launch from the ncu captures summarised under profiles/ (per workload and kernel)
-        roof["traffic"] = NCU_TRAFFIC.get(f"{args.workload}:{res['path']}") if not args.batch else None
+        roof["traffic"] = ncu_traffic(args.workload, res["path"]) if not args.batch else None
         cpu = None
         if not args.no_cpu_baseline:
             c = cpu_oracle_sample(w, target_s=args.cpu_seconds)
@@ -429,7 +561,10 @@ def main():
                 "vs_baseline": None, "dtype": "f32" if w["cfg_id"] == 1 else "bf16", "data": "synthetic", "config": config,
                 "e2e": {"value": res["e2e_value"], "unit": "tokens/s", "h2d_bytes_per_step": res["h2d"],
                         "d2h_bytes_per_step": res["d2h"]},
-                "gpu_launches": res["launches"], "clocks": res["clocks"], "roofline": roof, "cpu_baseline": cpu}
+                "gpu_launches": res["launches"], "clocks": res["clocks"], "roofline": roof, "parity": res["parity"],
+                "cpu_baseline": cpu}
+        if res["strong"]:
+            line["strong"] = res["strong"]
         print(json.dumps(line))
     if world > 1:
         torch.distributed.destroy_process_group()

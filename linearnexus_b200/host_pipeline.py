@@ -51,9 +51,9 @@ class HostPipeline:
                             **op_kwargs) -> Tuple[Tensor, Tensor]:
         """``variant`` in {"delta", "gated", "kda"}; q, k, v, g, beta as for the chunkwise op but in pinned host
         memory, ``[B,H,T,D]``.  Returns ``(o, final_state)`` as pinned host tensors (``out`` / ``final_state`` when
-        given).  ``slices``: number of pieces the work is cut into (default 8 pieces of the flattened batch x head
-        axis -- every piece costs one kernel's latency, measured best at 4-8 -- or one per batch row when the
-        tensors are not plain contiguous [B,H,T,D]).  The call returns when
+        given).  ``slices``: number of pieces the work is cut into (default: one piece per 8 MB of input, at most 8,
+        of the flattened batch x head axis -- every piece costs one kernel's latency, measured best at 4-8 for
+        large calls -- or one per batch row when the tensors are not plain contiguous [B,H,T,D]).  The call returns when
         the results are in host memory."""
         if variant not in _FWD:
             raise ValueError(f"unknown variant {variant!r}")
@@ -75,7 +75,11 @@ class HostPipeline:
             g = None if g is None else g.view(1, U, *g.shape[2:])
             beta = beta.reshape(1, U, T)
             initial_state = None if initial_state is None else initial_state.view(1, U, K, V)
-            n = max(1, min(U, 8 if slices is None else int(slices)))
+            if slices is None:
+                # every slice costs one launch and a handful of copies: small calls (a few MB) go as one piece
+                in_bytes = sum(t.numel() * t.element_size() for t in (q, k, v, g, beta) if t is not None)
+                slices = max(1, min(8, in_bytes // (8 << 20)))
+            n = max(1, min(U, int(slices)))
             bounds = [(U * i // n, U * (i + 1) // n) for i in range(n)]
             ax = 1
         else:

@@ -71,3 +71,18 @@ def test_two_ranks_shard_and_gather(B, H, mode):
     assert got_mode == mode
     assert eo < 1e-6 and eh < 1e-6
     assert tmax == 2.0
+
+
+def test_rows_built_per_rank_equal_the_cut_of_the_global_batch():
+    """The benchmark builds only a rank's rows of the global batch; that must be what shard_inputs cuts out of it."""
+    from linearnexus_b200.synthetic import make_rows
+    whole = make_rows("gated", 0, 4, 2, 24, 8, 8, seed=11, h0_std=0.1)
+    for world in (2, 4):
+        for rank in range(world):
+            cut, mode = shard_inputs(whole, world, rank)
+            lo, hi = unit_range(4, world, rank)
+            mine = make_rows("gated", lo, hi, 2, 24, 8, 8, seed=11, h0_std=0.1)
+            assert mode == "batch"
+            for name in whole:
+                assert torch.equal(cut[name], mine[name]), name
+    assert make_rows("delta", 0, 1, 2, 8, 4, 4, seed=1)["g"] is None

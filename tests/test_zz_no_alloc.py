@@ -82,6 +82,37 @@ def test_static_scratch_backward_matches_workspace_backward_twice():
             assert ((got[name] - ref[name]).abs().max() / denom).item() <= 2e-4, name
 
 
+def test_static_scratch_backward_bf16_tensor_core_shape_against_the_oracle():
+    """K = V = 128, bf16: the saving forward on tcgen05, the pre-pass and the tensor-core adjoint all work out of
+    the built-in array.  Checked against the float64 autograd of the recurrence (2e-2 relative, the bf16 bar),
+    not only against the workspace entry point."""
+    lib = _lib.load()
+    B, H, T, K, V = 1, 2, 256, 128, 128
+    d = _desc(B, H, T, K, V, 64)
+    d.qkv_dtype = d.out_dtype = _lib.DR_BF16
+    assert 0 < lib.dr_workspace_bytes(ctypes.byref(d), 1) <= STATIC_BYTES
+    inp = O.make_inputs("gated", B, H, T, K, V, seed=9, io_dtype=torch.bfloat16, h0_std=0.02)
+    gen = torch.Generator().manual_seed(9)
+    inp["do"] = torch.randn(B, H, T, V, generator=gen).bfloat16()
+    inp["dhT"] = torch.randn(B, H, K, V, generator=gen) * 0.1
+    x = {k: v.cuda().contiguous() for k, v in inp.items()}
+    ref = O.delta_rule_grads("gated", inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], inp["h0"], inp["do"], inp["dhT"])
+    for _ in range(2):   # twice in a row: the second call finds the first call's leftovers in the array
+        mk = lambda *s, dt=torch.float32: torch.full(s, float("nan"), device="cuda", dtype=dt)
+        out = dict(dq=mk(B, H, T, K, dt=torch.bfloat16), dk=mk(B, H, T, K, dt=torch.bfloat16), dv=mk(B, H, T, V, dt=torch.bfloat16),
+                   dbeta=mk(B, H, T), dg=mk(B, H, T), dh0=mk(B, H, K, V))
+        st = lib.dr_chunk_bwd_static(ctypes.byref(d), _vp(x["q"]), _vp(x["k"]), _vp(x["v"]), _vp(x["g"]), _vp(x["beta"]),
+                                     _vp(x["h0"]), _vp(x["do"]), _vp(x["dhT"]), _vp(out["dq"]), _vp(out["dk"]), _vp(out["dv"]),
+                                     _vp(out["dbeta"]), _vp(out["dg"]), _vp(out["dh0"]), None,
+                                     ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        assert st == 0, lib.dr_strerror(st)
+        for name in out:
+            got, want = out[name].double().cpu(), ref[name].double()
+            assert torch.isfinite(got).all(), name
+            assert ((got - want).abs().max() / want.abs().max()).item() <= 2e-2, name
+
+
 def test_static_scratch_limit_is_enforced():
     lib = _lib.load()
     d = _desc(8, 16, 4096, 128, 128, 64)  # needs hundreds of MiB of scratch
