@@ -139,6 +139,21 @@ int dr_chunk_fwd(const DrDesc* desc, const void* q, const void* k, const void* v
                  size_t workspace_bytes, int32_t* status_dev, void* stream);
 
 /*
+ * Chunkwise forward over a PACKED batch of variable-length sequences (the layout core/padding.py:13-53 of the
+ * reference produces with compute_unpadded_indices / unpad: valid tokens of all sequences back to back).
+ * q,k [total_T, Hq, K]  v,o [total_T, H, V]  beta [total_T, H]  g [total_T, H] or [total_T, H, K], token-major;
+ * cu_seqlens_host: n_seqs + 1 token offsets in HOST memory (cu_seqlens[0] = 0, cu_seqlens[n_seqs] = total_T);
+ * h0, hT: float32 [n_seqs, H, K, V] or null.  desc: B and T are ignored (B = 1 and T = each sequence's length are
+ * filled in per sequence), layout must be DR_LAYOUT_BTHD.  Every sequence starts from its own initial state and
+ * is cut into chunks from its own first token, so no chunk straddles a boundary; the result equals the
+ * reference op run on each sequence alone.  One launch sequence per sequence on `stream`, no copies; workspace as
+ * for dr_chunk_fwd sized for the longest sequence (dr_workspace_bytes with T = that length, B = 1).
+ */
+int dr_chunk_fwd_varlen(const DrDesc* desc, const void* q, const void* k, const void* v, const void* g,
+                        const float* beta, const int32_t* cu_seqlens_host, int32_t n_seqs, const float* h0, void* o,
+                        float* hT, void* workspace, size_t workspace_bytes, int32_t* status_dev, void* stream);
+
+/*
  * Token-by-token forward.  Replaces
  *   delta_rule_recurrent         modules/linear_attn/delta_net.py:126-213
  *   delta_rule_recurrent_pallas  kernels/pallas/delta_rule.py:47-281

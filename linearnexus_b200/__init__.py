@@ -11,6 +11,8 @@ from .ops import (delta_rule_chunkwise, delta_rule_recurrent, delta_rule_recurre
                   gated_delta_rule_step, kda_chunkwise, kda_recurrent, kda_step)
 from .state import DeltaNetState, GatedDeltaNetState, KDAState
 from .host_pipeline import HostPipeline, chunkwise_from_host
+from .ops import check_device_status
+from .varlen import chunkwise_varlen, compute_unpadded_indices, pad, unpad
 from .block_ops import (depthwise_conv1d_causal, gated_deltanet_gates, kda_gate, rmsnorm_gated,
                         short_conv_silu)
 
@@ -20,6 +22,7 @@ __all__ = [
     "kda_recurrent", "kda_chunkwise", "kda_step",
     "DeltaNetState", "GatedDeltaNetState", "KDAState",
     "KernelBackend", "backend_availability", "select_kernel_backend",
-    "HostPipeline", "chunkwise_from_host",
+    "HostPipeline", "chunkwise_from_host", "check_device_status",
+    "chunkwise_varlen", "compute_unpadded_indices", "unpad", "pad",
     "depthwise_conv1d_causal", "short_conv_silu", "gated_deltanet_gates", "kda_gate", "rmsnorm_gated",
 ]

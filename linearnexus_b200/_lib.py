@@ -33,7 +33,7 @@ EXPORTS = ["dr_version", "dr_strerror", "dr_last_cuda_error", "dr_launch_count",
            "dr_workspace_bytes", "dr_chunk_fwd", "dr_recurrent_fwd", "dr_step", "dr_chunk_bwd",
            "dr_debug_umma_selftest", "dr_chunk_bwd_static", "dr_chunk_fwd_saving", "dr_chunk_bwd_saved",
            "dr_short_conv_silu", "dr_gate_activations", "dr_gated_rmsnorm", "dr_check_status",
-           "dr_last_device_status", "dr_debug_wait_timeout"]
+           "dr_last_device_status", "dr_debug_wait_timeout", "dr_chunk_fwd_varlen"]
 
 
 class DrDesc(ctypes.Structure):
@@ -114,6 +114,9 @@ def load() -> ctypes.CDLL:
         lib.dr_workspace_bytes.argtypes = [dp, ctypes.c_int]
         lib.dr_chunk_fwd.restype = ctypes.c_int
         lib.dr_chunk_fwd.argtypes = [dp, vp, vp, vp, vp, fp, fp, vp, fp, vp, ctypes.c_size_t, ip, vp]
+        lib.dr_chunk_fwd_varlen.restype = ctypes.c_int
+        lib.dr_chunk_fwd_varlen.argtypes = [dp, vp, vp, vp, vp, fp, ctypes.POINTER(ctypes.c_int32), ctypes.c_int32, fp, vp, fp,
+                                            vp, ctypes.c_size_t, ip, vp]
         lib.dr_recurrent_fwd.restype = ctypes.c_int
         lib.dr_recurrent_fwd.argtypes = [dp, vp, vp, vp, vp, fp, fp, vp, fp, vp]
         lib.dr_step.restype = ctypes.c_int

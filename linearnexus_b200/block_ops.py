@@ -76,9 +76,12 @@ def depthwise_conv1d_causal(inputs: Tensor, weight: Tensor, bias: Optional[Tenso
     else:
         new_cache = torch.empty((B, W - 1, C), dtype=x.dtype, device=dev)
     lib = _lib.load()
+    # the fp32 copies of the parameters stay bound to names until the call has been enqueued: a temporary would
+    # be released (and its block handed to the next cast) before the kernel reads it
+    w32 = weight.float().contiguous()
+    b32 = None if bias is None else bias.float().contiguous()
     with torch.cuda.device(dev):
-        st = lib.dr_short_conv_silu(_ptr(x), _ptr(weight.float().contiguous()),
-                                    _ptr(None if bias is None else bias.float().contiguous()), _ptr(cin), _ptr(y),
+        st = lib.dr_short_conv_silu(_ptr(x), _ptr(w32), _ptr(b32), _ptr(cin), _ptr(y),
                                     _ptr(new_cache if W > 1 else None), B, T, C, W, _NATIVE[x.dtype],
                                     int(activation == "silu"), _stream(dev))
     _lib.check(st, "dr_short_conv_silu")
@@ -98,9 +101,10 @@ def _gates(mode, a, b, A_log, bias, H, K, beta_scale, threshold):
     g = torch.empty((B, T, H) if K == 1 and mode == 0 else (B, T, H, K), dtype=torch.float32, device=dev)
     beta = None if b is None else torch.empty((B, T, H), dtype=torch.float32, device=dev)
     lib = _lib.load()
+    A32 = A_log.float().contiguous()          # kept alive until the call has been enqueued (see above)
+    bias32 = None if bias is None else bias.float().contiguous()
     with torch.cuda.device(dev):
-        st = lib.dr_gate_activations(mode, _ptr(a2), _ptr(b2), _ptr(A_log.float().contiguous()),
-                                     _ptr(None if bias is None else bias.float().contiguous()), _ptr(g), _ptr(beta),
+        st = lib.dr_gate_activations(mode, _ptr(a2), _ptr(b2), _ptr(A32), _ptr(bias32), _ptr(g), _ptr(beta),
                                      B, T, H, K, _NATIVE[a2.dtype], _NATIVE[b2.dtype] if b2 is not None else DR_F32,
                                      float(beta_scale), float(threshold), _stream(dev))
     _lib.check(st, "dr_gate_activations")
@@ -149,8 +153,9 @@ def rmsnorm_gated(o: Tensor, weight: Tensor, gate: Optional[Tensor] = None, eps:
     out_dtype = o2.dtype if out_dtype is None else out_dtype
     y = torch.empty((B, T, H, V), dtype=out_dtype if out_dtype in _NATIVE else torch.float32, device=o2.device)
     lib = _lib.load()
+    w32 = weight.float().contiguous()         # kept alive until the call has been enqueued
     with torch.cuda.device(o2.device):
-        st = lib.dr_gated_rmsnorm(_ptr(o2), _ptr(g2), _ptr(weight.float().contiguous()), _ptr(y), B, H, T, V,
+        st = lib.dr_gated_rmsnorm(_ptr(o2), _ptr(g2), _ptr(w32), _ptr(y), B, H, T, V,
                                   DR_LAYOUT_BHTD if o_layout == "bhtd" else DR_LAYOUT_BTHD, _NATIVE[o2.dtype],
                                   _NATIVE[g2.dtype] if g2 is not None else DR_F32, _NATIVE[y.dtype], float(eps),
                                   _stream(o2.device))

@@ -74,8 +74,12 @@ int validate_fwd_ptrs(const DrDesc* d, const void* q, const void* k, const void*
                       const float* beta, const float* h0, void* o, float* hT) {
   if (!q || !k || !v || !beta || !o) return DR_ERR_NULL;
   if (d->variant == DR_DELTA ? g != nullptr : g == nullptr) return DR_ERR_VARIANT;
-  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(beta) ||
-      (g && !aligned16(g)) || (h0 && !aligned16(h0)) || (hT && !aligned16(hT)))
+  // rows of q, k, v, o, per-channel g and the states are read with 16-byte accesses; beta and a scalar g are
+  // read one element at a time (a sequence of a packed batch may start at any token)
+  const bool g_rows = d->variant == DR_KDA;
+  const uintptr_t g_mask = g_rows ? 15u : (d->g_dtype == DR_BF16 ? 1u : 3u);
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || (reinterpret_cast<uintptr_t>(beta) & 3u) ||
+      (g && (reinterpret_cast<uintptr_t>(g) & g_mask)) || (h0 && !aligned16(h0)) || (hT && !aligned16(hT)))
     return DR_ERR_ALIGN;
   return DR_OK;
 }
@@ -190,6 +194,34 @@ int dr_chunk_fwd(const DrDesc* d, const void* q, const void* k, const void* v, c
   tl_path = "recurrent";
   g_launches.fetch_add(1);
   return check_cuda(dr::launch_recurrent(p, st));
+}
+
+int dr_chunk_fwd_varlen(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
+                        const float* beta, const int32_t* cu, int32_t n_seqs, const float* h0, void* o, float* hT,
+                        void* workspace, size_t workspace_bytes, int32_t* status_dev, void* stream) {
+  if (!d || !cu) return DR_ERR_NULL;
+  if (n_seqs < 1 || d->layout != DR_LAYOUT_BTHD || cu[0] != 0) return DR_ERR_SHAPE;
+  for (int i = 0; i < n_seqs; ++i)
+    if (cu[i + 1] <= cu[i]) return DR_ERR_SHAPE;   // offsets strictly increasing: no empty sequence
+  const int Hq = d->qk_heads > 0 ? d->qk_heads : d->H;
+  const size_t es = d->qkv_dtype == DR_BF16 ? 2 : 4, eo = d->out_dtype == DR_BF16 ? 2 : 4, eg = d->g_dtype == DR_BF16 ? 2 : 4;
+  const size_t g_row = d->variant == DR_KDA ? (size_t)d->H * d->K : (size_t)d->H;
+  const size_t state = (size_t)d->H * d->K * d->V;
+  for (int i = 0; i < n_seqs; ++i) {
+    DrDesc ds = *d;
+    ds.B = 1;
+    ds.T = cu[i + 1] - cu[i];
+    const size_t t0 = (size_t)cu[i];
+    const char* qi = static_cast<const char*>(q) + t0 * Hq * d->K * es;
+    const char* ki = static_cast<const char*>(k) + t0 * Hq * d->K * es;
+    const char* vi = static_cast<const char*>(v) + t0 * d->H * d->V * es;
+    const char* gi = g ? static_cast<const char*>(g) + t0 * g_row * eg : nullptr;
+    char* oi = static_cast<char*>(o) + t0 * d->H * d->V * eo;
+    const int s = dr_chunk_fwd(&ds, qi, ki, vi, gi, beta + t0 * d->H, h0 ? h0 + i * state : nullptr, oi,
+                               hT ? hT + i * state : nullptr, workspace, workspace_bytes, status_dev, stream);
+    if (s != DR_OK) return s;
+  }
+  return DR_OK;
 }
 
 int dr_recurrent_fwd(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,

@@ -211,7 +211,8 @@ def delta_rule_recurrent(q, k, v, beta, initial_state=None, scale=None, backend=
 
 def delta_rule_chunkwise(q, k, v, beta, initial_state=None, chunk_size=64, scale=None, backend=None,
                          path=None) -> Tuple[Tensor, Tensor]:
-    """WY chunk form (delta_net.py:216-354).  Any ``chunk_size`` >= 1; ``backend`` ignored as in the reference."""
+    """WY chunk form (delta_net.py:216-354).  Any ``chunk_size`` >= 1; ``backend`` ignored as in the reference.
+    Differentiable (``loss.backward()``) for ``chunk_size <= 64`` and ``K <= 128``; other shapes run forward only."""
     return _seq_forward("chunk", DR_DELTA, q, k, v, None, beta, initial_state, scale, chunk_size, False, q.dtype, path)
 
 
@@ -375,6 +376,13 @@ def chunk_backward(variant, q, k, v, g, beta, d_o, initial_state=None, d_final_s
     return dict(dq=dq.to(q.dtype), dk=dk.to(k.dtype), dv=dv.to(v.dtype), dg=dg, dbeta=dbeta, dh0=dh0)
 
 
+def backward_supported(variant: str, K: int, chunk_size: int) -> bool:
+    """Shapes the backward kernels cover: chunk_size <= 64 and K <= 128 (and K % 16 == 0 for "kda").  The forward
+    entry points accept more (longer chunks and K up to 256 run on the token-recurrent kernel); the reference
+    differentiates any shape through jax.grad."""
+    return chunk_size <= 64 and K <= 128 and (variant != "kda" or K % 16 == 0)
+
+
 class _ChunkFn(torch.autograd.Function):
     """Forward that keeps the per-chunk states for its backward (one forward per training step).  Inputs the
     saving forward does not take (grouped q/k heads, an explicit kernel path) fall back to forward + recomputation."""
@@ -383,10 +391,10 @@ class _ChunkFn(torch.autograd.Function):
     def forward(ctx, variant, q, k, v, g, beta, initial_state, scale, chunk_size, l2norm, out_dtype, path):
         saved = None
         with torch.no_grad():
-            if path is None:
+            if path is None and backward_supported(variant, q.shape[-1], chunk_size):
                 o, hT, saved = chunk_forward_saving(variant, q, k, v, g, beta, initial_state, scale, chunk_size,
                                                     l2norm, out_dtype)
-            else:
+            else:   # an explicit kernel path, or a shape only the forward covers (backward() then says so)
                 o, hT = _seq_forward("chunk", _VARIANTS[variant], q, k, v, g, beta, initial_state, scale, chunk_size,
                                      l2norm, out_dtype, path)
         ctx.save_for_backward(q, k, v, g if g is not None else q.new_empty(0), beta,
@@ -399,6 +407,10 @@ class _ChunkFn(torch.autograd.Function):
     def backward(ctx, d_o, d_hT):
         q, k, v, g, beta, h0 = ctx.saved_tensors
         variant, scale, chunk_size, l2norm, has_g, has_h0 = ctx.meta
+        if not backward_supported(variant, q.shape[-1], chunk_size):
+            raise NotImplementedError(
+                f"the backward kernels cover chunk_size <= 64 and K <= 128 (K % 16 == 0 for 'kda'); got chunk_size="
+                f"{chunk_size}, K={q.shape[-1]}.  The forward of this shape is available (this call ran it).")
         saved, ctx.saved_ws = ctx.saved_ws, None   # consumed: a second backward recomputes
         gr = chunk_backward(variant, q, k, v, g if has_g else None, beta, d_o, h0 if has_h0 else None, d_hT,
                             scale=scale, chunk_size=chunk_size, use_qk_l2norm=l2norm, saved=saved)

@@ -49,7 +49,8 @@ def test_validation_status_codes():
     assert call(_desc(K=130)) == -2
     assert call(_desc(V=1024)) == -2
     assert call(_desc(qkv_dtype=7)) == -3
-    assert call(_desc(), g=16 + 4) == -4          # misaligned g
+    assert call(_desc(), g=16 + 2) == -4          # misaligned g (a scalar fp32 decay needs 4-byte alignment)
+    assert call(_desc(variant=2), g=16 + 4) == -4  # per-channel decay rows are read 16 bytes at a time
     assert call(_desc(variant=0), g=16) == -6     # DeltaNet must not get g
     assert call(_desc(variant=1), g=None) == -6   # Gated DeltaNet needs g
     assert call(_desc(chunk=24), g=16) == -7      # reference: ValueError when chunk % 16 != 0

@@ -158,3 +158,17 @@ def test_tensor_core_backward_odd_shapes(variant, K, V, T, Hq, H):
         assert torch.isfinite(x).all(), name
         err = (x - y).abs().max() / y.abs().max().clamp_min(1e-20)
         assert err <= 2e-2, (name, float(err))   # the bf16 bar: max|x - ref| / max|ref|
+
+
+def test_forward_of_grad_inputs_runs_for_shapes_the_backward_does_not_cover():
+    """chunk_size 128 has a forward (token-recurrent kernel) but no backward: a call on requires_grad inputs still
+    returns the forward result, and only .backward() reports the limit."""
+    inp = O.make_inputs("gated", 1, 2, 256, 64, 64, seed=4)
+    cu = {k: (None if v is None else v.cuda()) for k, v in inp.items()}
+    q = cu["q"].clone().requires_grad_(True)
+    o, hT = L.gated_delta_rule_chunkwise(q, cu["k"], cu["v"], cu["g"], cu["beta"], chunk_size=128)
+    with torch.no_grad():
+        o2, hT2 = L.gated_delta_rule_chunkwise(cu["q"], cu["k"], cu["v"], cu["g"], cu["beta"], chunk_size=128)
+    assert torch.equal(o, o2) and torch.equal(hT, hT2)
+    with pytest.raises(NotImplementedError, match="chunk_size <= 64"):
+        o.sum().backward()

@@ -167,3 +167,46 @@ def test_block_ops_against_golden_vectors():
     _close(bk, torch.from_numpy(G["kda_gate.beta_out"]), torch.float32)
     yn = BO.rmsnorm_gated(c("norm.o"), c("norm.w"), c("norm.gate"), eps=1e-5)
     _close(yn, torch.from_numpy(G["norm.y"]), torch.float32)
+
+
+def test_parameters_of_a_bf16_model_and_strided_parameters():
+    """Parameters that are not fp32-contiguous (a bf16 model; a strided slice of a fused parameter) are converted
+    inside the wrappers; the converted copies must stay alive until the kernel has been enqueued.  A_log and dt_bias
+    (and weight / bias rows) have the same size, which is exactly the case where a released temporary would be
+    handed to the next conversion."""
+    g = torch.Generator().manual_seed(12)
+    B, T, H = 2, 64, 8
+    a = (torch.randn(B, T, H, generator=g) * 3).bfloat16()
+    b = (torch.randn(B, T, H, generator=g) * 3).bfloat16()
+    A_log = torch.randn(H, generator=g).bfloat16()
+    dt_bias = torch.randn(H, generator=g).bfloat16()
+    g_ref, b_ref = O.gdn_gate_activations(a, b, A_log.float(), dt_bias.float(), False)
+    gg, beta = BO.gated_deltanet_gates(a.cuda(), b.cuda(), A_log.cuda(), dt_bias.cuda())
+    _close(gg, g_ref, torch.float32)
+    _close(beta, b_ref, torch.float32)
+    # strided fp32 parameters: every second entry of a wider tensor
+    wide = torch.randn(2 * H, generator=g)
+    A2, d2 = wide[::2], torch.randn(2 * H, generator=g)[1::2]
+    g_ref, b_ref = O.gdn_gate_activations(a, b, A2, d2, True)
+    gg, beta = BO.gated_deltanet_gates(a.cuda(), b.cuda(), wide.cuda()[::2], d2.cuda(), True)
+    _close(gg, g_ref, torch.float32)
+    _close(beta, b_ref, torch.float32)
+    # conv taps and bias in bf16, both [.., C] with W == 1 row of bias-sized data next to them
+    C, W = 128, 4
+    x = torch.randn(B, T, C, generator=g).bfloat16()
+    w = (torch.randn(W, C, generator=g) * 0.5).bfloat16()
+    bs = torch.randn(C, generator=g).bfloat16()
+    y_ref, _ = O.short_conv_silu(x, w.float(), bs.float(), None, apply_silu=True)
+    y, _ = BO.short_conv_silu(x.cuda(), w.cuda(), bs.cuda())
+    _close(y, y_ref, torch.bfloat16)
+    # norm weight in bf16 and as a strided view
+    V = 128
+    o = torch.randn(B, H, T, V, generator=g).bfloat16()
+    gate = torch.randn(B, T, H, V, generator=g).bfloat16()
+    nw = (torch.rand(2 * V, generator=g) + 0.5)
+    ref = O.gated_rmsnorm(o.transpose(1, 2), nw[::2], gate, eps=1e-5)
+    y = BO.rmsnorm_gated(o.cuda(), nw.cuda()[::2], gate.cuda(), eps=1e-5)
+    _close(y, ref, torch.bfloat16)
+    ref = O.gated_rmsnorm(o.transpose(1, 2), nw[:V].bfloat16().float(), gate, eps=1e-5)
+    y = BO.rmsnorm_gated(o.cuda(), nw[:V].bfloat16().cuda(), gate.cuda(), eps=1e-5)
+    _close(y, ref, torch.bfloat16)
