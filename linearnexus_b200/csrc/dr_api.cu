@@ -98,7 +98,7 @@ int sm_count() {
 
 bool tcgen05_eligible(const DrDesc* d) {
   return dr::sm100::kAvailable && d->K == 128 && d->V == 128 && d->chunk == 64 &&
-         d->qkv_dtype == DR_BF16 && (d->variant == DR_GATED || d->variant == DR_DELTA) &&
+         d->qkv_dtype == DR_BF16 && d->out_dtype == DR_BF16 && (d->variant == DR_GATED || d->variant == DR_DELTA) &&
          (d->variant == DR_DELTA || d->g_dtype == DR_F32);
 }
 

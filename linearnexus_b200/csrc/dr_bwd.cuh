@@ -193,14 +193,6 @@ __host__ __device__ inline BwdSmem bwd_layout(int C, int K, int VS, bool kda, bo
   return L;
 }
 
-#ifdef DR_PROFILE
-#define BPROF(idx)                                                                                  \
-  do {                                                                                              \
-    if (blockIdx.x == gridDim.x / 2 && tid == 0) { const unsigned long long t_ = clock64(); sm100::g_prof[idx] += t_ - bp0; bp0 = t_; } \
-  } while (0)
-#else
-#define BPROF(idx)
-#endif
 
 // TC: the products run on mma.sync tf32 (bf16 inputs: well inside their 2e-2 tolerance); otherwise exact fp32.
 template <int VS, bool KDA, bool TC>
@@ -245,14 +237,10 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
       if ((c >> 4) > (r >> 4)) { sX[r * lda + c] = 0.f; sA[r * lda + c] = 0.f; sT[r * ldt + c] = 0.f; }
     }
   }
-#ifdef DR_PROFILE
-  unsigned long long bp0 = clock64();
-#endif
   for (int n = N - 1; n >= 0; --n) {
     const int t0 = n * C;
     const int rows = min(C, T - t0);
     __syncthreads();
-    BPROF(150);
     // ---- stage q^, k^ (fp32, normalised / scaled), g, beta, v, dO, S0 --------------------------------
     if constexpr (TC) {
       {
@@ -416,7 +404,6 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
     }
     if constexpr (TC) tc::cp_async_wait_1();   // A, T, k^ have landed; X, q^ may still be in flight
     __syncthreads();
-    BPROF(151);
     if (KDA) {
       for (int i = tid; i < K; i += NTHR) {
         float acc = 0.f;
@@ -439,7 +426,6 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
       }
       for (int i = tid; i < K; i += NTHR) sEL[i] = expf(gl);
     }
-    BPROF(152);
     // ---- X = tril(K^K^^T.E,-1) (not yet scaled by beta), A = tril(Q^K^^T.E) ---------------------------
     if constexpr (TC) {
       // X and A (decay folded in) came from the pre-pass
@@ -474,7 +460,6 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
     }
     }
     __syncthreads();
-    BPROF(153);
     auto ld2 = [](const float* ptr) { return *reinterpret_cast<const float2*>(ptr); };
     // explicit inverse (tf32 merge products) instead of the substitutions: exact-path kernel, bf16 inputs only
     const bool use_inv = KDA && !TC && NW == 16 && C == 64 && p.qkv_dt == DR_BF16;
@@ -522,7 +507,6 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
     }
     }
     __syncthreads();
-    BPROF(154);
     // ---- Vn = M^-1 R : forward substitution, 8 lanes per column -----------------------------------------
     if constexpr (TC) {
       // with the explicit inverse T = (I + diag(beta) X)^-1 of the pre-pass, Vn = T R on the tensor cores
@@ -575,7 +559,6 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
       }
     }
     __syncthreads();
-    BPROF(155);
     // ---- dVn = A^T dO + (K^ e^{G_L-G}) dS1 -----------------------------------------------------------------
     if constexpr (TC) {
       {
@@ -623,7 +606,6 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
     }
     }
     __syncthreads();
-    BPROF(156);
     // ---- dR = M^-T dVn : back substitution ---------------------------------------------------------------------
     if constexpr (TC) {
       constexpr int NT = VS / 8 / NTW;
@@ -671,7 +653,6 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
       }
     }
     __syncthreads();
-    BPROF(157);
     // ---- dV = beta dR ; dbeta += dR.V ; dA = tril(dO Vn^T).E ; dX = beta tril(-dR Vn^T).E ; dbeta += dM.X ------
     for (int i = tid; i < C * VS; i += NTHR) {
       const int c = i / VS, vv = i % VS;
@@ -740,7 +721,6 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
     }
     }
     __syncthreads();
-    BPROF(158);
     // ---- per (row i, channel k): dQ^, dK^, dG, dbeta; lane = channel, warp = rows ----------------------------------
     if constexpr (TC) {
       // warp w owns rows 16*(w/NTW)..; the channel tiles are dealt to the NTW warps of a row panel in pairs.
@@ -894,7 +874,6 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
       }
     }
     }
-    BPROF(159);
     // ---- dS0 = (Q^ e^G)^T dO + e^{G_L} dS1 - (beta K^ e^G)^T dR ; dG_L += e^{G_L} <dS1, S0> -------------------------
     if constexpr (TC) {
       // rows = channels k (panels of 16), columns = the VS value columns cut into NTW / 2 parts; the warps of one
@@ -980,7 +959,6 @@ __global__ void __launch_bounds__(bwd_threads(TC)) bwd_chunk_kernel(const BwdPar
       for (int kk = warp * STREAMS + sub; kk < K; kk += NW * STREAMS, ++slot) sdS[kk * ldv + vv] = ds_new[slot];
     }
     }
-    BPROF(160);
     for (int c = tid; c < rows; c += NTHR) atomicAdd(p.dbeta + s_base + (t0 + c) * s_tok, sdBeta[c]);
   }
   __syncthreads();

@@ -68,26 +68,26 @@ constexpr uint32_t TM_COLS = 512;
 
 // shared-memory map (bytes)
 constexpr int QK_TILE = 128 * 128 * 2;        // [K (64 rows); Q (64 rows)] x 128 raw bf16, 32 KB
-constexpr int SM_QKR = 0;                     // ring of 3 such tiles (chunk n uses tile n % 3)
+constexpr int kRing = 4;                      // K,Q tiles in flight: one each in PA, PB, the consumer + one landing
+constexpr int SM_QKR = 0;                     // ring of kRing such tiles (chunk n uses tile n % kRing)
 constexpr int W_TILE = 128 * 64 * 2;          // W as [128 k][64 c] core matrices, 16 KB
-constexpr int SM_W = 3 * QK_TILE;             // one W tile
-constexpr int SM_O = SM_W + W_TILE;           // O staging tile [64][128] bf16 row-major, 16 KB
+constexpr int SM_W = kRing * QK_TILE;         // one W tile
 constexpr int AQK_TILE = 64 * 64 * 2;         // A_qk [64][64] bf16, 8 KB
-constexpr int SM_AQK = SM_O + 64 * 128 * 2;   // three A_qk tiles (chunk n uses n % 3)
+constexpr int SM_AQK = SM_W + W_TILE;         // three A_qk tiles (chunk n uses n % 3)
 constexpr int SM_V = SM_AQK + 3 * AQK_TILE;   // V [64][128] core-matrix tile, 16 KB
-constexpr int SM_TB = SM_V + 64 * 128 * 2;    // T diag(beta)        [64][64] bf16
-constexpr int SM_TW = SM_TB + 64 * 64 * 2;    // T diag(beta e^G)    [64][64] bf16
-constexpr int AKK_BYTES = 64 * LDT * 4;       // X, then T in place: fp32 [64][68]
-constexpr int SM_AKK = SM_TW + 64 * 64 * 2;   // two such matrices (chunk n uses n & 1)
+constexpr int AKK_BYTES = 64 * LDT * 4;       // X, then T in place (fp32 [64][68]), then the bf16 tiles
+constexpr int SM_AKK = SM_V + 64 * 128 * 2;   // two such buffers (chunk n uses n & 1)
+constexpr int XB_TB = 0;                      //   T diag(beta rk)         [64][64] bf16 core-matrix tile, 8 KB
+constexpr int XB_TW = 64 * 64 * 2;            //   T diag(beta e^G rk^2)   [64][64] bf16, 8 KB
 constexpr int SM_TOTAL = SM_AKK + 2 * AKK_BYTES;
 
 struct alignas(16) Ctl {
-  uint64_t full[2], empty[2], akk[2], akkfree[2], kq[3], vb, barP, barW, barUW, uwfree, wrdy, sbrdy, bar1, bar2s, bar2,
-      barDq;
+  uint64_t full[3], empty[3], akk[2], xfree[2], kq[kRing], vb, barP, barW, barUW, wrdy, sbrdy, bar1, bar2s, bar2, barDq;
   alignas(16) float gb[128];         // raw beta (0..63) and g (64..127) of the chunk being scanned
-  alignas(16) float rq[3][64];       // scale / (||q_i|| + eps) of chunk m in slot m % 3
-  alignas(16) float sc[3][320];      // of chunk m in slot m % 3: G, e^G, e^{G_L-G}, beta, G log2(e) (64 each)
-  alignas(16) float keep[2][128];    // per stage, CB-private: rq_i e^{G_i} (0..63) and rq_i (64..127)
+  alignas(16) float rq[4][64];       // scale / (||q_i|| + eps) of chunk m in slot m % 4
+  alignas(16) float sc[4][256];      // of chunk m in slot m % 4: e^G, e^{G_L-G}, beta, G log2(e) (64 each)
+  alignas(16) float keep[3][128];    // CB-private, chunk m in slot m % 3: rq_i e^{G_i} (0..63) and rq_i (64..127); three
+                                     // slots so that a group barrier lies between the last read and the next write of one
   alignas(16) float rk[2][64];       // per X buffer: 1 / (||k_j|| + eps)
   alignas(16) float rs[2][64];       // per X buffer: beta_i rk_i^2, row factor of the unit-lower system
   uint32_t tmem_base;
@@ -97,26 +97,9 @@ struct alignas(16) Ctl {
 // Kernel parameters: the common forward parameters plus the TMA tensor maps (see make_input_map /
 // make_output_map); the map coordinates of a sequence are derived from (b, h) in the kernel.
 struct alignas(64) Sm100Params {
-  CUtensorMap tk, tq, tv, to;
+  CUtensorMap tk, tq, tv;
   FwdParams p;
-  int use_tma_out;
 };
-
-#ifdef DR_PROFILE
-__device__ unsigned long long g_prof[192];
-#define PROF_DECL unsigned long long prof_t0 = clock64();
-#define PROF(idx)                                              \
-  do {                                                         \
-    if (blockIdx.x == 0 && gt == 0) {                          \
-      const unsigned long long prof_t = clock64();             \
-      atomicAdd(&g_prof[idx], prof_t - prof_t0);               \
-      prof_t0 = prof_t;                                        \
-    }                                                          \
-  } while (0)
-#else
-#define PROF_DECL
-#define PROF(idx)
-#endif
 
 // A shared-memory descriptor whose start address is `bytes` further on (the address field holds bytes / 16 and
 // cannot carry out of its 14 bits for addresses inside one CTA's shared memory).
@@ -150,18 +133,19 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
     tc::tmem_relinquish();
   }
   if (tid == 0) {
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 3; ++i) {
       tc::mbar_init(tc::smem_u32(&ctl.full[i]), kGrp);
       tc::mbar_init(tc::smem_u32(&ctl.empty[i]), kGrp);
-      tc::mbar_init(tc::smem_u32(&ctl.akk[i]), kGrp);
-      tc::mbar_init(tc::smem_u32(&ctl.akkfree[i]), kGrp);
     }
-    for (int i = 0; i < 3; ++i) tc::mbar_init(tc::smem_u32(&ctl.kq[i]), kTma ? 1 : kGrp);
+    for (int i = 0; i < 2; ++i) {
+      tc::mbar_init(tc::smem_u32(&ctl.akk[i]), kGrp);
+      tc::mbar_init(tc::smem_u32(&ctl.xfree[i]), 1);
+    }
+    for (int i = 0; i < kRing; ++i) tc::mbar_init(tc::smem_u32(&ctl.kq[i]), kTma ? 1 : kGrp);
     tc::mbar_init(tc::smem_u32(&ctl.vb), kTma ? 1 : kGrp);
     tc::mbar_init(tc::smem_u32(&ctl.barP), 1);
     tc::mbar_init(tc::smem_u32(&ctl.barW), 1);
     tc::mbar_init(tc::smem_u32(&ctl.barUW), 1);
-    tc::mbar_init(tc::smem_u32(&ctl.uwfree), 1);
     tc::mbar_init(tc::smem_u32(&ctl.wrdy), kGrp);
     tc::mbar_init(tc::smem_u32(&ctl.sbrdy), kGrp);
     tc::mbar_init(tc::smem_u32(&ctl.bar1), 1);
@@ -207,10 +191,10 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
     // later scans them); with TMA its first lane also issues the tile copies.
     auto issue_kq = [&](int m) {
       const int t0m = m * kC, rowsm = min(kC, T - t0m);
-      uint8_t* dQK = smem + SM_QKR + (m % 3) * QK_TILE;
+      uint8_t* dQK = smem + SM_QKR + (m % kRing) * QK_TILE;
       if (kTma) {
         if (gt == 0) {
-          const uint32_t bar = tc::smem_u32(&ctl.kq[m % 3]);
+          const uint32_t bar = tc::smem_u32(&ctl.kq[m % kRing]);
           tc::mbar_arrive_expect_tx(bar, 2u * 64 * 256);
           tc::tma_load_5d(tc::smem_u32(dQK), &P.tk, 0, 0, qc2, m * 8, qc4, bar);
           tc::tma_load_5d(tc::smem_u32(dQK) + 64 * 256, &P.tq, 0, 0, qc2, m * 8, qc4, bar);
@@ -244,7 +228,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       tc::cp_async_wait_all();
       if (!kTma) {
         tc::fence_async_smem();
-        arrive(&ctl.kq[m % 3]);
+        arrive(&ctl.kq[m % kRing]);
       }
     };
 
@@ -252,9 +236,9 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
     // G2 = G log2(e) (the decay mask takes its exponentials in base 2)
     auto scan_stage = [&](int m) {
       constexpr float kLog2e = 1.4426950408889634f;
-      float* zG = ctl.sc[m % 3];
+      float* zG = ctl.sc[m % 4];
       const float* raw = ctl.gb;
-      zG[192 + lane] = raw[lane]; zG[224 + lane] = raw[32 + lane];   // beta
+      zG[128 + lane] = raw[lane]; zG[160 + lane] = raw[32 + lane];   // beta
       float a = raw[64 + lane], bq = raw[96 + lane];
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -265,19 +249,18 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       const float tot = __shfl_sync(0xffffffffu, a, 31);
       bq += tot;
       const float last = __shfl_sync(0xffffffffu, bq, 31);
-      zG[lane] = a; zG[lane + 32] = bq;
-      zG[64 + lane] = tc::fast_exp2(a * kLog2e); zG[96 + lane] = tc::fast_exp2(bq * kLog2e);
-      zG[128 + lane] = tc::fast_exp2(fminf(last - a, 0.f) * kLog2e);
-      zG[160 + lane] = tc::fast_exp2(fminf(last - bq, 0.f) * kLog2e);
-      zG[256 + lane] = a * kLog2e; zG[288 + lane] = bq * kLog2e;
+      zG[lane] = tc::fast_exp2(a * kLog2e); zG[32 + lane] = tc::fast_exp2(bq * kLog2e);
+      zG[64 + lane] = tc::fast_exp2(fminf(last - a, 0.f) * kLog2e);
+      zG[96 + lane] = tc::fast_exp2(fminf(last - bq, 0.f) * kLog2e);
+      zG[192 + lane] = a * kLog2e; zG[224 + lane] = bq * kLog2e;
     };
 
     // first product of chunk m: D1 = [K;Q] K^T on the raw rows (B = first 64 rows of the same tile)
     auto issue_d1 = [&](int m) {
-      wait_bar(&ctl.kq[m % 3], (m / 3) & 1);
+      wait_bar(&ctl.kq[m % kRing], (m / kRing) & 1);
       tc::tc_fence_after();
-      const uint64_t ad0 = tc::smem_desc(tc::smem_u32(smem + SM_QKR + (m % 3) * QK_TILE), 128, RBS);
-#pragma unroll
+      const uint64_t ad0 = tc::smem_desc(tc::smem_u32(smem + SM_QKR + (m % kRing) * QK_TILE), 128, RBS);
+#pragma unroll 1
       for (int ks = 0; ks < 8; ++ks) {
         const uint64_t ad = desc_adv(ad0, ks * 256);
         tc::mma_ss(tbase + TM_D1, ad, ad, id_n64, ks > 0);
@@ -290,27 +273,20 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
     if (warp == 0) { __syncwarp(); scan_stage(0); }
     if (gt == 64) issue_d1(0);
     uint32_t phP = 0;
-    PROF_DECL
     for (int n = 0; n < nchunks; ++n) {
       const int s = n & 1;
       uint8_t* sAqk = smem + SM_AQK + (n % 3) * AQK_TILE;
       float* sX = sAkk0 + s * (64 * LDT);
-      const float* sG = ctl.sc[n % 3];
-      const float* sBeta = sG + 192;
+      const float* sG = ctl.sc[n % 4];
+      const float* sBeta = sG + 128;
       group_sync128(1);  // the scalars of this chunk (scan) are visible
-      PROF(0);
-      // chunk n-2 has left the consumer and PB: ring tile, A_qk tile, scalar and rq slots (n+1) % 3 and X buffer s
-      // are free
-      if (n >= 2) {
-        wait_bar(&ctl.empty[s], ((n >> 1) - 1) & 1);
-        wait_bar(&ctl.akkfree[s], ((n >> 1) - 1) & 1);
-      }
-      PROF(1);
+      // chunk n-3 has left the consumer: ring tile, scalar and rq slots (n+1) % 4 and A_qk tile n % 3 are free;
+      // chunk n-2 has left PB and its U^T, W^T products: X buffer s is free
+      if (n >= 3) wait_bar(&ctl.empty[n % 3], ((n / 3) - 1) & 1);
+      if (n >= 2) wait_bar(&ctl.xfree[s], ((n >> 1) - 1) & 1);
       if (n + 1 < nchunks) issue_kq(n + 1);
-      PROF(2);
       wait_bar(&ctl.barP, phP); phP ^= 1;   // D1 of this chunk was issued during the previous iteration
       tc::tc_fence_after();
-      PROF(3);
       {
         // one pass per 32-column half at or below this warp's diagonal (rows 0..31: one, rows 32..63: two), the same
         // code for both: x = D1 . 2^{min(G2_i - G2_j, 0)}.  X keeps whatever lands above the diagonal (the inverse
@@ -320,16 +296,15 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         const int i = gt & 63;
         const bool qrow = gt >= 64;        // warps 2,3 hold the Q rows (A_qk); warps 0,1 the K rows (X)
         const int nh = 1 + (wq & 1);
-        const float* sG2 = sG + 256;
+        const float* sG2 = sG + 192;
         const float Gi = sG2[i];
 #pragma unroll 1
-        for (int hh = 0; hh < nh; ++hh) {
-          const int c0 = 32 * hh;
-          uint32_t r[32];
-          tc::tmem_ld32(tbase + TM_D1 + lane_addr + c0, r);
+        for (int c0 = 0; c0 < 32 * nh; c0 += 16) {
+          uint32_t r[16];
+          tc::tmem_ld16(tbase + TM_D1 + lane_addr + c0, r);
           tc::tc_wait_ld();
 #pragma unroll
-          for (int j4 = 0; j4 < 8; ++j4) {
+          for (int j4 = 0; j4 < 4; ++j4) {
             const float4 g4 = *reinterpret_cast<const float4*>(sG2 + c0 + 4 * j4);
             r[4 * j4 + 0] = __float_as_uint(__uint_as_float(r[4 * j4 + 0]) * tc::fast_exp2(fminf(Gi - g4.x, 0.f)));
             r[4 * j4 + 1] = __float_as_uint(__uint_as_float(r[4 * j4 + 1]) * tc::fast_exp2(fminf(Gi - g4.y, 0.f)));
@@ -338,12 +313,12 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
           }
           if (!qrow) {
 #pragma unroll
-            for (int j4 = 0; j4 < 8; ++j4)
+            for (int j4 = 0; j4 < 4; ++j4)
               *reinterpret_cast<uint4*>(sX + i * LDT + c0 + 4 * j4) = make_uint4(r[4 * j4], r[4 * j4 + 1], r[4 * j4 + 2], r[4 * j4 + 3]);
           } else {
             const int lim = i - c0;   // columns c0 + e with e <= lim are at or below the diagonal
 #pragma unroll
-            for (int j8 = 0; j8 < 4; ++j8) {
+            for (int j8 = 0; j8 < 2; ++j8) {
               uint4 out;
               uint32_t* o32 = reinterpret_cast<uint32_t*>(&out);
 #pragma unroll
@@ -368,48 +343,41 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
             *reinterpret_cast<uint4*>(sAqk + tc::core_off(i, 32 + 8 * j8, A_RBS)) = make_uint4(0u, 0u, 0u, 0u);
         }
       }
-      PROF(4);
       tc::fence_async_smem();                // the A_qk tile is read by the tensor cores
       tc::tc_fence_before();
       arrive(&ctl.akk[s]);                   // X, A_qk, rk, rs of chunk n are ready: PB starts
       group_sync128(1);                      // every warp has drained D1 from tensor memory
-      PROF(5);
       // what the NEXT chunk needs from this group, behind the hand-over
       if (n + 1 < nchunks) {
         land_kq(n + 1);                      // the next chunk's beta, g (and, without TMA, its K,Q rows)
         if (gt == 64) issue_d1(n + 1);       // completes behind PB's inverse of this chunk
         if (warp == 0) { __syncwarp(); scan_stage(n + 1); }
       }
-      PROF(6);
     }
   } else if (grp == 1) {
     // =========================== PB: inverse, Tb / Tw tiles ==========================================
-    uint8_t* sTb = smem + SM_TB;
-    uint8_t* sTw = smem + SM_TW;
     // rq_i = scale / (||q_i|| + eps) of chunk m from the raw rows 64..127 of its tile
     auto q_norms = [&](int m) {
-      wait_bar(&ctl.kq[m % 3], (m / 3) & 1);
-      float* dst = ctl.rq[m % 3];
+      wait_bar(&ctl.kq[m % kRing], (m / kRing) & 1);
+      float* dst = ctl.rq[m % 4];
       const float scale = p.scale;
       const bool l2 = p.l2norm != 0;
-      row_sq_norms_64(smem + SM_QKR + (m % 3) * QK_TILE, 64, wq, lane,
+      row_sq_norms_64(smem + SM_QKR + (m % kRing) * QK_TILE, 64, wq, lane,
                       [&](int r, float ss) { dst[r] = l2 ? scale / (sqrtf(ss) + 1e-6f) : scale; });
     };
     q_norms(0);
-    PROF_DECL
     for (int n = 0; n < nchunks; ++n) {
       const int s = n & 1;
       float* sT = sAkk0 + s * (64 * LDT);
-      const float* sEG = ctl.sc[n % 3] + 64;
-      const float* sBeta = ctl.sc[n % 3] + 192;
+      uint8_t* sTb = reinterpret_cast<uint8_t*>(sT) + XB_TB;
+      uint8_t* sTw = reinterpret_cast<uint8_t*>(sT) + XB_TW;
+      const float* sEG = ctl.sc[n % 4];
+      const float* sBeta = ctl.sc[n % 4] + 128;
       wait_bar(&ctl.akk[s], (n >> 1) & 1);
-      PROF(10);
       block_inverse_64_inplace(sT, ctl.rs[s], gt, SyncPB());
-      PROF(11);
-      // the U^T, W^T products of the previous chunk have read Tb, Tw
-      if (n >= 1) wait_bar(&ctl.uwfree, (n - 1) & 1);
-      PROF(12);
       {
+        // Tb = T diag(beta rk), Tw = T diag(beta e^G rk^2) as bf16 tiles IN PLACE of T: every thread takes its 32
+        // entries of T into registers, the group synchronises, then the tiles are written over the matrix
         const int rin = gt & 7, jb = (gt >> 3) & 7, rbq = gt >> 6;
         float bj[8], bw[8];
 #pragma unroll
@@ -418,12 +386,18 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
           bj[e] = sBeta[8 * jb + e] * rkj;
           bw[e] = bj[e] * sEG[8 * jb + e] * rkj;
         }
-#pragma unroll 1
+        float4 t0v[4], t1v[4];
+#pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int i = 8 * (2 * j + rbq) + rin;
-          const float4 t0v = *reinterpret_cast<const float4*>(sT + i * LDT + 8 * jb);
-          const float4 t1v = *reinterpret_cast<const float4*>(sT + i * LDT + 8 * jb + 4);
-          float t[8] = {t0v.x, t0v.y, t0v.z, t0v.w, t1v.x, t1v.y, t1v.z, t1v.w};
+          t0v[j] = *reinterpret_cast<const float4*>(sT + i * LDT + 8 * jb);
+          t1v[j] = *reinterpret_cast<const float4*>(sT + i * LDT + 8 * jb + 4);
+        }
+        group_sync128(2);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int i = 8 * (2 * j + rbq) + rin;
+          float t[8] = {t0v[j].x, t0v[j].y, t0v[j].z, t0v[j].w, t1v[j].x, t1v[j].y, t1v[j].z, t1v[j].w};
 #pragma unroll
           for (int e = 0; e < 8; ++e) t[e] = (8 * jb + e <= i) ? t[e] : 0.f;
           uint4 ob, ow;
@@ -440,11 +414,8 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         }
       }
       tc::fence_async_smem();
-      arrive(&ctl.full[s]);      // A_qk, Tb, Tw and the scalars of chunk n are ready
-      arrive(&ctl.akkfree[s]);   // the X/T buffer may be overwritten
-      PROF(13);
+      arrive(&ctl.full[n % 3]);   // A_qk, Tb, Tw and the scalars of chunk n are ready
       if (n + 1 < nchunks) q_norms(n + 1);   // in this group's idle time; published by its next arrival on `full`
-      PROF(14);
     }
   } else if (grp == 2) {
     // =========================== CA: the serial chain over the state =================================
@@ -462,75 +433,66 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       tc::tc_wait_st();
     }
     uint32_t ph1 = 0;
-    PROF_DECL
     for (int n = 0; n < nchunks; ++n) {
       const int s = n & 1;
-      const uint32_t aQK = tc::smem_u32(smem + SM_QKR + (n % 3) * QK_TILE);
+      const uint32_t aQK = tc::smem_u32(smem + SM_QKR + (n % kRing) * QK_TILE);
       const uint32_t aW = tc::smem_u32(smem + SM_W);
       const uint32_t aAqk = tc::smem_u32(smem + SM_AQK + (n % 3) * AQK_TILE);
-      const float* sEG = ctl.sc[n % 3] + 64;
+      const float* sEG = ctl.sc[n % 4];
       const float* sWd = sEG + 64;
       if (n >= 1) {
         wait_bar(&ctl.bar2s, (n - 1) & 1);   // the state update of the previous chunk is complete, and with it
         wait_bar(&ctl.barDq, (n - 1) & 1);   // every earlier product of the chain; Dq has read the bf16 state
-        arrive(&ctl.empty[s ^ 1]);           // chunk n-1: its K,Q tile and the A_qk tile of chunk n-2 are free
+        arrive(&ctl.empty[(n - 1) % 3]);     // chunk n-1 has left the consumer: its K,Q tile, A_qk tile and scalars are free
       }
-      PROF(20);
-      wait_bar(&ctl.full[s], (n >> 1) & 1);
+      wait_bar(&ctl.full[n % 3], (n / 3) & 1);
       tc::tc_fence_after();
-      PROF(21);
       // ---- state pass: bf16 copy of S^T for the products; fp32 master pre-multiplied by e^{G_L} --------
       {
         const float gl = sEG[63];
 #pragma unroll 1
-        for (int cc = 0; cc < 4; ++cc) {
-          const int c0 = 32 * cc;
-          uint32_t r[32], pk[16];
-          tc::tmem_ld32(tbase + TM_S + lane_addr + c0, r);
+        for (int c0 = 0; c0 < kD; c0 += 16) {
+          uint32_t r[16], pk[8];
+          tc::tmem_ld16(tbase + TM_S + lane_addr + c0, r);
           tc::tc_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) pk[j] = tc::pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+          for (int j = 0; j < 8; ++j) pk[j] = tc::pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
           if (p.ckpt) {  // state at the start of this chunk, [K][V] row-major, for the backward
             float* ck = p.ckpt + ((int64_t)unit * nchunks + n) * kD * kD;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) ck[(c0 + j) * kD + gt] = __uint_as_float(r[j]);
+            for (int j = 0; j < 16; ++j) ck[(c0 + j) * kD + gt] = __uint_as_float(r[j]);
           }
 #pragma unroll
-          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * gl);
-          tc::tmem_st16(tbase + TM_SB + lane_addr + c0 / 2, pk);
-          tc::tmem_st32(tbase + TM_S + lane_addr + c0, r);
+          for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * gl);
+          tc::tmem_st8(tbase + TM_SB + lane_addr + c0 / 2, pk);
+          tc::tmem_st16(tbase + TM_S + lane_addr + c0, r);
         }
         tc::tc_wait_st();
       }
       tc::tc_fence_before();
       arrive(&ctl.sbrdy);        // CB's elected thread issues Dq from the bf16 copy
       group_sync128(3);
-      PROF(22);
       // ---- (3) V_new^T = U^T - S^T W^T --------------------------------------------------------------------
       if (gt == 0) {
         wait_bar(&ctl.wrdy, n & 1);          // W tile written by CB
         wait_bar(&ctl.barUW, n & 1);         // U^T complete
         tc::tc_fence_after();
-        PROF(23);
         const uint64_t wd0 = tc::smem_desc(aW, A_RBS, 128);   // W MN-major: 16 key rows per step
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
           tc::mma_ts(tbase + TM_DU + 64 * s, tbase + TM_SB + ks * 8, desc_adv(wd0, ks * 2 * A_RBS), id_n64_bmn_neg, 1);
         tc::mma_commit(tc::smem_u32(&ctl.bar1));
-        PROF(24);
       }
       wait_bar(&ctl.bar1, ph1); ph1 ^= 1;
       tc::tc_fence_after();
-      PROF(27);
       // ---- V_new^T -> bf16 (plain, and decayed by e^{G_L - G_c}) ---------------------------------------------
 #pragma unroll 1
-      for (int hh = 0; hh < 2; ++hh) {
-        const int c0 = 32 * hh;
-        uint32_t r[32], pa[16], pb[16];
-        tc::tmem_ld32(tbase + TM_DU + 64 * s + lane_addr + c0, r);
+      for (int c0 = 0; c0 < kC; c0 += 16) {
+        uint32_t r[16], pa[8], pb[8];
+        tc::tmem_ld16(tbase + TM_DU + 64 * s + lane_addr + c0, r);
         tc::tc_wait_ld();
 #pragma unroll
-        for (int j4 = 0; j4 < 8; ++j4) {
+        for (int j4 = 0; j4 < 4; ++j4) {
           const float4 w4 = *reinterpret_cast<const float4*>(sWd + c0 + 4 * j4);
           const float x0 = __uint_as_float(r[4 * j4]), x1 = __uint_as_float(r[4 * j4 + 1]);
           const float x2 = __uint_as_float(r[4 * j4 + 2]), x3 = __uint_as_float(r[4 * j4 + 3]);
@@ -539,13 +501,12 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
           pb[2 * j4] = tc::pack_bf16(x0 * w4.x, x1 * w4.y);
           pb[2 * j4 + 1] = tc::pack_bf16(x2 * w4.z, x3 * w4.w);
         }
-        tc::tmem_st16(tbase + TM_VA + lane_addr + c0 / 2, pa);
-        tc::tmem_st16(tbase + TM_VB + lane_addr + c0 / 2, pb);
+        tc::tmem_st8(tbase + TM_VA + lane_addr + c0 / 2, pa);
+        tc::tmem_st8(tbase + TM_VB + lane_addr + c0 / 2, pb);
       }
       tc::tc_wait_st();
       tc::tc_fence_before();
       group_sync128(3);
-      PROF(28);
       // ---- (5) S^T += (decayed V_new^T) K^ ;  (4) Do = V_new^T A_qk^T -------------------------------------------
       if (gt == 0) {
         tc::tc_fence_after();
@@ -560,7 +521,6 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
           tc::mma_ts(tbase + TM_DU + 64 * s, tbase + TM_VA + ks * 8, desc_adv(ad0, ks * 256), id_n64, ks > 0);
         tc::mma_commit(tc::smem_u32(&ctl.bar2));
       }
-      PROF(29);
     }
     // final state: hT[k][v] = S^T[v][k]
     wait_bar(&ctl.bar2s, (nchunks - 1) & 1);
@@ -583,7 +543,6 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
     const __nv_bfloat16* gv = reinterpret_cast<const __nv_bfloat16*>(p.v);
     __nv_bfloat16* go = reinterpret_cast<__nv_bfloat16*>(p.o);
     uint8_t* sV = smem + SM_V;
-    __nv_bfloat16* sO = reinterpret_cast<__nv_bfloat16*>(smem + SM_O);
     // V rows of chunk m -> core-matrix tile
     auto issue_v = [&](int m) {
       if (kTma) {
@@ -613,43 +572,38 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
     auto issue_dq = [&](int m) {
       wait_bar(&ctl.sbrdy, m & 1);
       tc::tc_fence_after();
-      const uint64_t qd0 = tc::smem_desc(tc::smem_u32(smem + SM_QKR + (m % 3) * QK_TILE) + 8 * RBS, 128, RBS);   // rows 64..127
-#pragma unroll
+      const uint64_t qd0 = tc::smem_desc(tc::smem_u32(smem + SM_QKR + (m % kRing) * QK_TILE) + 8 * RBS, 128, RBS);   // rows 64..127
+#pragma unroll 1
       for (int ks = 0; ks < 8; ++ks)
         tc::mma_ts(tbase + TM_DQ, tbase + TM_SB + ks * 8, desc_adv(qd0, ks * 256), id_n64, ks > 0);
       tc::mma_commit(tc::smem_u32(&ctl.barDq));
     };
-    // O^T of chunk m: rq_i (e^{G_i} Dq + Do) -> staging tile -> one tiled store.  `next` >= 0: Dq of that chunk is
-    // issued as soon as every thread has read the Dq columns.
+    // O^T of chunk m: rq_i (e^{G_i} Dq + Do), straight from the accumulators to global memory.  Each thread owns
+    // one value column v and 64 tokens; neighbouring lanes swap halves of token pairs so that every lane stores
+    // two adjacent columns of one token (a warp writes 64 contiguous bytes of each of two token rows per
+    // instruction).  `next` >= 0: Dq of that chunk is issued as soon as every thread has read the Dq columns.
     auto out_epilogue = [&](int m, int next) {
       const int sm_ = m & 1;
-      const float* sEGm = ctl.keep[sm_];        // rq_i e^{G_i}
-      const float* sRQm = ctl.keep[sm_] + 64;   // rq_i
+      const float* sEGm = ctl.keep[m % 3];        // rq_i e^{G_i}
+      const float* sRQm = ctl.keep[m % 3] + 64;   // rq_i
       const int t0m = m * kC;
       const int rowsm = min(kC, T - t0m);
+      const bool odd = gt & 1;
+      __nv_bfloat16* orow = go ? go + vo_base + (int64_t)(t0m + (odd ? 1 : 0)) * vo_tok + (gt & ~1) : nullptr;
 #pragma unroll 1
-      for (int hh = 0; hh < 2; ++hh) {
-        const int c0 = 32 * hh;
-        uint32_t rq[32], ro[32];
-        tc::tmem_ld32(tbase + TM_DQ + lane_addr + c0, rq);
-        tc::tmem_ld32(tbase + TM_DU + 64 * sm_ + lane_addr + c0, ro);
+      for (int c0 = 0; c0 < kC; c0 += 16) {
+        uint32_t rq[16], ro[16];
+        tc::tmem_ld16(tbase + TM_DQ + lane_addr + c0, rq);
+        tc::tmem_ld16(tbase + TM_DU + 64 * sm_ + lane_addr + c0, ro);
         tc::tc_wait_ld();
-        if (hh == 0) {
-          // the previous output store has read the staging tile (its issuing thread waits; the barrier below
-          // passes that on before anyone writes the tile)
-          if (P.use_tma_out && gt == 0) tc::bulk_wait_read_all();
-          group_sync128(4);
-        } else {
+        if (c0 == kC - 16) {
           tc::tc_fence_before();
           group_sync128(4);      // Dq and this stage's accumulator are in registers, in every thread
           if (next >= 0 && gt == 0) issue_dq(next);
         }
-        if (p.o) {
-          // each thread owns one value column v and 32 tokens; neighbouring lanes swap halves of token pairs so
-          // that every lane stores two adjacent columns of one token with one 32-bit store
-          const bool odd = gt & 1;
+        if (go) {
 #pragma unroll
-          for (int j4 = 0; j4 < 8; ++j4) {
+          for (int j4 = 0; j4 < 4; ++j4) {
             const float4 e4 = *reinterpret_cast<const float4*>(sEGm + c0 + 4 * j4);
             const float4 q4 = *reinterpret_cast<const float4*>(sRQm + c0 + 4 * j4);
             const float ee[4] = {e4.x, e4.y, e4.z, e4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
@@ -662,70 +616,48 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
               const uint32_t other = __shfl_xor_sync(0xffffffffu, mine, 1);   // the same of column v ^ 1
               // even lane: token j, columns (v, v+1); odd lane: token j+1, columns (v-1, v)
               const uint32_t word = odd ? __byte_perm(other, mine, 0x7632) : __byte_perm(mine, other, 0x5410);
-              *reinterpret_cast<uint32_t*>(sO + (c0 + j + (odd ? 1 : 0)) * kD + (gt & ~1)) = word;
+              if (c0 + j + (odd ? 1 : 0) < rowsm)
+                *reinterpret_cast<uint32_t*>(orow + (int64_t)(c0 + j) * vo_tok) = word;
             }
           }
         }
       }
-      if (!p.o) return;          // output not wanted (checkpoint-only forward of the backward)
-      if (P.use_tma_out) {
-        tc::fence_async_smem();
-        group_sync128(4);
-        if (gt == 0) {  // one tiled store of the whole chunk; rows past T are clipped by the tensor map
-          tc::tma_store_4d(&P.to, tc::smem_u32(sO), 0, t0m, h, b);
-          tc::bulk_commit();   // its shared-memory reads are awaited before the tile is written again
-        }
-      } else {
-        group_sync128(4);
-        const int r = gt >> 1, hf = gt & 1;
-        if (r < rowsm) {
-          __nv_bfloat16* dst = go + vo_base + (int64_t)(t0m + r) * vo_tok + 64 * hf;
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            reinterpret_cast<uint4*>(dst)[j] = reinterpret_cast<const uint4*>(sO + r * kD + 64 * hf)[j];
-        }
-        group_sync128(4);
-      }
     };
 
     issue_v(0);
-    PROF_DECL
     for (int n = 0; n < nchunks; ++n) {
       const int s = n & 1;
-      const uint32_t aQK = tc::smem_u32(smem + SM_QKR + (n % 3) * QK_TILE);
+      const uint32_t aQK = tc::smem_u32(smem + SM_QKR + (n % kRing) * QK_TILE);
       uint8_t* sWt = smem + SM_W;
-      wait_bar(&ctl.full[s], (n >> 1) & 1);
+      const uint32_t aXB = tc::smem_u32(reinterpret_cast<uint8_t*>(sAkk0 + s * (64 * LDT)));   // Tb, Tw of this chunk
+      wait_bar(&ctl.full[n % 3], (n / 3) & 1);
       tc::tc_fence_after();
-      PROF(31);
       // ---- (2a) W^T = K^T Tw^T -> this stage's accumulator, idle until U^T is issued into it ---------------
       if (gt == 0) {
         const uint64_t kd0 = tc::smem_desc(aQK, RBS, 128);   // K MN-major, 16 chunk rows per step
-        const uint64_t twd0 = tc::smem_desc(tc::smem_u32(smem + SM_TW), 128, A_RBS);
-#pragma unroll
+        const uint64_t twd0 = tc::smem_desc(aXB + XB_TW, 128, A_RBS);
+#pragma unroll 1
         for (int ks = 0; ks < 4; ++ks)
           tc::mma_ss(tbase + TM_DU + 64 * s, desc_adv(kd0, ks * 2 * RBS), desc_adv(twd0, ks * 256), id_n64_amn, ks > 0);
         tc::mma_commit(tc::smem_u32(&ctl.barW));
       }
       // the scalars this chunk's output epilogue will need, kept where PA cannot overwrite them
       if (gt < 64) {
-        const float rqi = ctl.rq[n % 3][gt];
-        ctl.keep[s][gt] = ctl.sc[n % 3][64 + gt] * rqi;
-        ctl.keep[s][64 + gt] = rqi;
+        const float rqi = ctl.rq[n % 4][gt];
+        ctl.keep[n % 3][gt] = ctl.sc[n % 4][gt] * rqi;
+        ctl.keep[n % 3][64 + gt] = rqi;
       }
-      PROF(32);
       wait_bar(&ctl.barW, n & 1);
       if (n >= 1) wait_bar(&ctl.bar1, (n - 1) & 1);   // product (3) of the previous chunk has read the W tile
       tc::tc_fence_after();
-      PROF(33);
       // ---- W^T[k][c] (lane = k) -> bf16 tile, key rows x chunk rows in core-matrix order (MN-major B of (3)) ---
 #pragma unroll 1
-      for (int hh = 0; hh < 2; ++hh) {
-        const int c0 = 32 * hh;
-        uint32_t r[32];
-        tc::tmem_ld32(tbase + TM_DU + 64 * s + lane_addr + c0, r);
+      for (int c0 = 0; c0 < kC; c0 += 16) {
+        uint32_t r[16];
+        tc::tmem_ld16(tbase + TM_DU + 64 * s + lane_addr + c0, r);
         tc::tc_wait_ld();
 #pragma unroll
-        for (int cb = 0; cb < 4; ++cb) {
+        for (int cb = 0; cb < 2; ++cb) {
           uint4 out;
           out.x = tc::pack_bf16(__uint_as_float(r[8 * cb + 0]), __uint_as_float(r[8 * cb + 1]));
           out.y = tc::pack_bf16(__uint_as_float(r[8 * cb + 2]), __uint_as_float(r[8 * cb + 3]));
@@ -738,28 +670,26 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       tc::tc_fence_before();
       arrive(&ctl.wrdy);
       group_sync128(4);   // W^T has left the accumulator in every thread; the kept scalars are visible
-      PROF(34);
       // ---- (2b) U^T = V^T Tb^T -> the same accumulator ---------------------------------------------------
       if (gt == 0) {
         tc::tc_fence_after();
         wait_bar(&ctl.vb, n & 1);
         tc::tc_fence_after();
         const uint64_t vd0 = tc::smem_desc(tc::smem_u32(sV), RBS, 128);
-        const uint64_t tbd0 = tc::smem_desc(tc::smem_u32(smem + SM_TB), 128, A_RBS);
-#pragma unroll
+        const uint64_t tbd0 = tc::smem_desc(aXB + XB_TB, 128, A_RBS);
+#pragma unroll 1
         for (int ks = 0; ks < 4; ++ks)
           tc::mma_ss(tbase + TM_DU + 64 * s, desc_adv(vd0, ks * 2 * RBS), desc_adv(tbd0, ks * 256), id_n64_amn, ks > 0);
         tc::mma_commit(tc::smem_u32(&ctl.barUW));
       }
       if (gt == 0) {
-        wait_bar(&ctl.barUW, n & 1);   // V, Tb, Tw have been read: release Tb / Tw, fetch the next chunk's V rows
-        arrive(&ctl.uwfree);
+        wait_bar(&ctl.barUW, n & 1);   // V, Tb, Tw have been read: release the X buffer, fetch the next chunk's V rows
+        arrive(&ctl.xfree[s]);
       }
       if (n + 1 < nchunks) {
         if (!kTma) wait_bar(&ctl.barUW, n & 1);   // every thread copies V rows
         issue_v(n + 1);
       }
-      PROF(35);
       // ---- output of the previous chunk, then Dq of this one ---------------------------------------------
       if (n >= 1) {
         wait_bar(&ctl.bar2, (n - 1) & 1);   // Do and Dq of chunk n-1 are complete
@@ -769,13 +699,11 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       } else if (gt == 0) {
         issue_dq(0);
       }
-      PROF(36);
     }
     wait_bar(&ctl.bar2, (nchunks - 1) & 1);
     wait_bar(&ctl.barDq, (nchunks - 1) & 1);
     tc::tc_fence_after();
     out_epilogue(nchunks - 1, -1);
-    if (P.use_tma_out && gt == 0) tc::bulk_wait_all();
   }
   tc::tc_fence_before();
   __syncthreads();
@@ -792,7 +720,6 @@ inline cudaError_t launch_chunk(const FwdParams& p, cudaStream_t stream) {
   const bool tma_in = p.map.T % 8 == 0 && make_input_map(&P.tk, p.k, p.map.B, p.map.Hq, p.map.T, bthd) &&
                       make_input_map(&P.tq, p.q, p.map.B, p.map.Hq, p.map.T, bthd) &&
                       make_input_map(&P.tv, p.v, p.map.B, p.map.H, p.map.T, bthd);
-  P.use_tma_out = p.o != nullptr && make_output_map(&P.to, p.o, p.map);
   auto kern = tma_in ? chunk_sm100_kernel<true> : chunk_sm100_kernel<false>;
   thread_local int attr_dev[2] = {-1, -1};
   int dev = -1;

@@ -112,14 +112,6 @@ __device__ __forceinline__ uint4 pack8(const float (&x)[8]) {
   return u;
 }
 
-#ifdef DR_PROFILE
-#define KPROF(idx)                                                                                   \
-  do {                                                                                               \
-    if (blockIdx.x == gridDim.x / 2 && tid == 0) { const unsigned long long t_ = clock64(); sm100::g_prof[idx] += t_ - kp0; kp0 = t_; } \
-  } while (0)
-#else
-#define KPROF(idx)
-#endif
 
 __global__ void __launch_bounds__(kThreads, 2) intra_kernel(const FwdParams p, uint8_t* __restrict__ ws, const int copy_v) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -146,9 +138,6 @@ __global__ void __launch_bounds__(kThreads, 2) intra_kernel(const FwdParams p, u
   const int64_t s_base = p.map.base(b, h, 1), s_tok = p.map.tok(1);
   uint8_t* rec = ws + ((int64_t)unit * nchunks + n) * WS_REC;
   constexpr float kLog2e = 1.4426950408889634f;
-#ifdef DR_PROFILE
-  unsigned long long kp0 = clock64();
-#endif
 
   // ---- load: raw k, q rows, their norm factors, the log decay (in log2 units); lane = four channels ---------
   // (all global loads of the warp's eight rows are issued before the first is used)
@@ -172,7 +161,6 @@ __global__ void __launch_bounds__(kThreads, 2) intra_kernel(const FwdParams p, u
         }
       }
     }
-    KPROF(149);
     float bt = 0.f;
     if (lane < 8 && warp + 8 * lane < rows) bt = p.beta[s_base + (t0 + warp + 8 * lane) * s_tok];
 #pragma unroll
@@ -197,7 +185,6 @@ __global__ void __launch_bounds__(kThreads, 2) intra_kernel(const FwdParams p, u
       }
     }
   }
-  KPROF(147);
   // V rows -> the record's tile, 16 bytes per piece (coalesced writes); skipped when the state kernel can fetch
   // the rows itself through a tensor map
   if (copy_v) {
@@ -213,9 +200,7 @@ __global__ void __launch_bounds__(kThreads, 2) intra_kernel(const FwdParams p, u
       *reinterpret_cast<uint4*>(rec + WS_V + piece * 16) = u;
     }
   }
-  KPROF(148);
   __syncthreads();
-  KPROF(140);
   // ---- G = inclusive prefix sum of the log decay over the rows of the chunk, per channel ---------------------
   // thread = (8-row segment, four channels): local scan, then the totals of the earlier segments are added;
   // the segment totals live in the first rows of the (still unused) T array
@@ -242,7 +227,6 @@ __global__ void __launch_bounds__(kThreads, 2) intra_kernel(const FwdParams p, u
           make_float4(loc[r].x + pre.x, loc[r].y + pre.y, loc[r].z + pre.z, loc[r].w + pre.w);
     __syncthreads();
   }
-  KPROF(141);
   // ---- chunk-local products on mma.sync (bf16) -------------------------------------------------------------------
   // Rows of sub-block bi against the columns of blocks 0..bi; operands  x_i e^{G_i - G_n}  and  k_j e^{G_n - G_j}
   // (n = first row of bi) are formed in registers; the k and q rows share their decay factors and the column
@@ -322,7 +306,6 @@ __global__ void __launch_bounds__(kThreads, 2) intra_kernel(const FwdParams p, u
       }
     }
   }
-  KPROF(142);
   // ---- diagonal 16x16 blocks exactly (fp32), only for blocks whose decay range is too wide for the product form ----
   // Two warps per block, 64 channels each, two channels per lane; the 16 rows of k and the per-row decay
   // d_r = e^{G_r - G_{r-1}} stay in registers, so e^{G_i - G_j} is a running product (no exponentials per pair).
@@ -399,10 +382,8 @@ __global__ void __launch_bounds__(kThreads, 2) intra_kernel(const FwdParams p, u
     }
   }
   __syncthreads();
-  KPROF(143);
   // ---- T = (I + diag(beta) A_kk)^-1 -----------------------------------------------------------------------------
   sm100::block_inverse_64(sAkk, sBeta, sT, tid);
-  KPROF(144);
   // ---- record tiles: T diag(beta), A_qk, Qg = scale q^ e^G, Kd = k^ e^{G_L - G}, e^{G_L} ------------------------
 #pragma unroll
   for (int it = 0; it < 2; ++it) {
@@ -456,7 +437,6 @@ __global__ void __launch_bounds__(kThreads, 2) intra_kernel(const FwdParams p, u
   }
   if (tid < kD) reinterpret_cast<float*>(rec + WS_EGL)[tid] = ex2(sG[63 * LDF + tid]);
   __syncthreads();
-  KPROF(145);
   // ---- W = (T diag(beta)) (k^ e^G): 64x128x64 on mma.sync (tf32); warp = 16 rows x 64 channels ----------------------
   // (A_kk is dead after the inverse: its array takes the bf16 staging tile of W; bf16 -> tf32 is exact)
   {
@@ -496,7 +476,6 @@ __global__ void __launch_bounds__(kThreads, 2) intra_kernel(const FwdParams p, u
     piece128(piece, row, col);
     *reinterpret_cast<uint4*>(rec + WS_W + piece * 16) = *reinterpret_cast<const uint4*>(sWst + row * LDH + col);
   }
-  KPROF(146);
 }
 
 // ---- state kernel ----------------------------------------------------------------------------------------------
@@ -725,22 +704,14 @@ __global__ void __launch_bounds__(kStateThreads, 1) state_kernel(const __grid_co
       }
     };
 
-#ifdef DR_PROFILE
-    unsigned long long sp0 = clock64();
-#define SPROF(idx) do { if (blockIdx.x == 0 && tid == 0) { const unsigned long long t_ = clock64(); sm100::g_prof[idx] += t_ - sp0; sp0 = t_; } } while (0)
-#else
-#define SPROF(idx)
-#endif
     for (int n = 0; n < nchunks; ++n) {
       const int s = n & 1;
       const float* sEGL = reinterpret_cast<const float*>(smem + s * WS_REC + WS_EGL);
       wait_bar(&ctl.full[s], (n >> 1) & 1);
-      SPROF(170);
       if (n > 0) {
         wait_bar(&ctl.bar2, (n - 1) & 1);   // the previous chunk's state update and Do have completed
         tc::tc_fence_after();
       }
-      SPROF(171);
       // ---- state pass: bf16 copy of S^T for the products; fp32 master decayed per key channel -------------------
       {
 #pragma unroll
@@ -765,12 +736,9 @@ __global__ void __launch_bounds__(kStateThreads, 1) state_kernel(const __grid_co
       }
       tc::tc_fence_before();
       arrive(&ctl.go1);
-      SPROF(172);
       if (n > 0) output_epilogue(n - 1);   // overlaps the products of this chunk
-      SPROF(173);
       wait_bar(&ctl.bar1, n & 1);
       tc::tc_fence_after();
-      SPROF(174);
       // ---- Vn^T -> bf16 -------------------------------------------------------------------------------------------
       {
         const int c0 = 32 * hs;
@@ -784,7 +752,6 @@ __global__ void __launch_bounds__(kStateThreads, 1) state_kernel(const __grid_co
       tc::tc_wait_st();
       tc::tc_fence_before();
       arrive(&ctl.go3);
-      SPROF(175);
     }
     if (nchunks > 0) {
       wait_bar(&ctl.bar2, (nchunks - 1) & 1);
