@@ -10,8 +10,10 @@ torch-on-CPU restatements of
 It checks the CUDA kernels of ``dr_block_ops.cuh``; it is never the product path.  Only ``tests/``,
 ``__graft_entry__.smoke()`` and ``bench.py``'s CPU-baseline legs may import it.
 
-PARITY UNPINNED: the reference has no golden vectors for these helpers and JAX cannot be imported here; the
-restatement follows the cited lines (operation order, where the fp32 casts sit, the kernel_size == 1 shortcut).
+PINNED against the reference's own source for the conv, ``kda_gate``, ``RMSNorm`` and ``FusedRMSNormGated``
+(``tests/golden/reference_vectors.npz``: the reference's files executed over a numpy stand-in for ``jax.numpy``,
+``tests/golden/make_reference_vectors.py``; checked in ``tests/test_reference_vectors.py``).  The two gate lines of
+the Gated DeltaNet block sit inside its ``__call__`` and are restated from the cited lines only.
 """
 from __future__ import annotations
 

@@ -9,13 +9,17 @@ quirks).  It is the checker for the CUDA kernels; it is never the product path.
 Only ``tests/``, ``__graft_entry__.smoke()`` and ``bench.py``'s CPU-baseline /
 ``--impl reference`` legs may import it.
 
-PARITY UNPINNED: the reference ships no golden vectors for these ops and JAX is
-not importable where this oracle was written, so it could not be run against the
-reference itself.  It is pinned only by re-expressing the reference's own
-self-consistency tests (chunk == recurrent, step == recurrent at T=1, beta=0
-keeps the state at zero; ``tests/test_deltanet.py:64-157,281-346``,
-``tests/test_gated_deltanet.py:310-339``, ``tests/test_kda.py:219-290``) and by a
-float64 token recurrence as the mathematical truth.
+PINNED against the reference's own source: ``tests/golden/reference_vectors.npz`` holds inputs and
+outputs of the reference's nine functions themselves, their source files executed over a numpy
+stand-in for ``jax.numpy`` / ``lax.scan`` (``tests/golden/make_reference_vectors.py``; JAX is
+not installed where this was written, and the reference ships no golden vectors).
+``tests/test_reference_vectors.py`` holds every function here, in float32 and in float64, within
+float32 round-off (2e-5) of those outputs, at K = V = 32/48 and at the K = V = 128, chunk 64 shapes
+of the tensor-core kernels.  The gradients are the autograd of this pinned forward (the reference's
+are JAX autodiff of its forward, which the stand-in cannot run).  The reference's own
+self-consistency tests are re-expressed as well (chunk == recurrent, step == recurrent at T=1,
+beta=0 keeps the state at zero; ``tests/test_deltanet.py:64-157,281-346``,
+``tests/test_gated_deltanet.py:310-339``, ``tests/test_kda.py:219-290``).
 
 ``compute_dtype`` selects the arithmetic type: ``torch.float32`` follows the
 reference (which computes everything in fp32), ``torch.float64`` gives the
