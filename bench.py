@@ -53,6 +53,11 @@ WORKLOADS = {
     # training configuration: B=16 over 8 GPUs = 2 batch rows per GPU; forward + backward
     "gdn_fwd_bwd": dict(variant="gated", B=2, T=4096, H=16, K=128, V=128, chunk=64, kind="fwd_bwd", cfg_id=5),
     "deltanet_fwd_fp32": dict(variant="delta", B=2, T=512, H=4, K=64, V=64, chunk=64, kind="chunk_fwd", cfg_id=1),
+    # the other matrix-state scans (token recurrence, state in registers); the reference quotes no configuration for
+    # them, so they take the headline's batch, length and head count at those models' usual head sizes
+    "dplr_fwd": dict(variant="dplr", B=8, T=4096, H=16, K=64, V=64, chunk=0, kind="scan", cfg_id=6),
+    "rwkv6_fwd": dict(variant="rwkv6", B=8, T=4096, H=16, K=64, V=64, chunk=0, kind="scan", cfg_id=7),
+    "ssd_fwd": dict(variant="ssd", B=8, T=4096, H=16, K=128, V=64, chunk=0, kind="scan", cfg_id=8, groups=1),
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 DECODE_BUFFER = 1024
@@ -67,6 +72,12 @@ def alg_bytes(w, io_bytes=2):
     """Algorithmic bytes of one step: every input and output once at its storage width."""
     B, H, T, K, V = w["B"], w["H"], w["T"], w["K"], w["V"]
     units = B * H
+    if w["kind"] == "scan":
+        state = units * 2 * 4 * K * V                       # initial state in, final state out
+        if w["variant"] == "ssd":                           # x, y per head; B, C per group; dt float32 per head
+            return B * T * (H * (2 * io_bytes * V + 4) + w["groups"] * 2 * io_bytes * K) + state
+        n_key = 5 if w["variant"] == "dplr" else 3          # q k a b gk | r k w
+        return units * T * io_bytes * (n_key * K + 2 * V) + state
     if w["kind"] == "decode":
         return units * (2 * 4 * K * V + io_bytes * (2 * K + V) + 8 + io_bytes * V)
     g_bytes = (2 if w.get("g_bf16") else 4) * K if w["variant"] == "kda" else (4 if w["variant"] == "gated" else 0)
@@ -182,6 +193,158 @@ def forward_parity(w, host, o, hT, n_units=4, seed=0):
         eo = max(eo, rel_err(o[b:b + 1, h:h + 1], ro))
         es = max(es, rel_err(hT[b:b + 1, h:h + 1], rS))
     return {"o_rel": eo, "state_rel": es, "units": len(units), "against": "float64 token recurrence (oracle)"}
+
+
+# ---- the other scans (RWKV-7 DPLR, RWKV-6, Mamba-2 SSD) -----------------------------------------------------------
+
+def scan_host_inputs(w, rows, seed, heads=None):
+    """Seeded inputs of one scan workload, `rows` batch rows, float32 values rounded to bf16 where stored as bf16."""
+    H, T, K, V = heads or w["H"], w["T"], w["K"], w["V"]
+    rng = np.random.default_rng(seed)
+    f = lambda *s, scale=1.0: torch.from_numpy(rng.standard_normal(s, dtype=np.float32)) * scale
+    bf = lambda t: t.to(torch.bfloat16)
+    if w["variant"] == "dplr":
+        kk = torch.nn.functional.normalize(f(rows, H, T, K), dim=-1)
+        return dict(q=bf(f(rows, H, T, K)), k=bf(f(rows, H, T, K, scale=0.5)), v=bf(f(rows, H, T, V)), a=bf(-kk),
+                    b=bf(kk * torch.sigmoid(f(rows, H, T, K))), gk=bf(-torch.exp(f(rows, H, T, K) - 1.0)),
+                    h0=f(rows, H, K, V, scale=0.02))
+    if w["variant"] == "rwkv6":
+        return dict(r=bf(f(rows, H, T, K)), k=bf(f(rows, H, T, K, scale=0.5)), v=bf(f(rows, H, T, V)),
+                    w=bf(-f(rows, H, T, K).abs() - 0.5), u=f(H, K, scale=0.5), h0=f(rows, H, K, V, scale=0.02))
+    G = w["groups"] if heads is None else 1
+    return dict(x=bf(f(rows, T, H, V)), dt=f(rows, T, H, scale=0.5), A=-torch.exp(f(H, scale=0.5)),
+                B=bf(f(rows, T, G, K, scale=0.5)), C=bf(f(rows, T, G, K, scale=0.5)), D=f(H), dt_bias=f(H, scale=0.3),
+                h0=f(rows, H, V, K, scale=0.02))
+
+
+def scan_call(mod, w, t, cd=None):
+    """The public function of the workload on tensors `t`; `mod` is the package or (with cd) the oracle module."""
+    kw = {} if cd is None else dict(compute_dtype=cd)
+    if w["variant"] == "dplr":
+        return mod.dplr_delta_rule_recurrent(t["q"], t["k"], t["v"], t["a"], t["b"], t["gk"], scale=w["K"] ** -0.5,
+                                             initial_state=t["h0"], **kw)
+    if w["variant"] == "rwkv6":
+        return mod.rwkv6_recurrent(t["r"], t["k"], t["v"], t["w"], t["u"], scale=w["K"] ** -0.5, initial_state=t["h0"], **kw)
+    return mod.ssd_chunk_scan(t["x"], t["dt"], t["A"], t["B"], t["C"], t["D"], chunk_size=256, n_groups=t["B"].shape[2],
+                              ssm_state=t["h0"], dt_bias=t["dt_bias"], dt_limit=(0.001, 5.0), **kw)
+
+
+def scan_unit(w, host, b, h):
+    """Inputs of the single (batch b, head h) sequence, float64, for the oracle."""
+    d = lambda x: x.double()
+    if w["variant"] == "ssd":
+        g = h // (host["x"].shape[2] // host["B"].shape[2])
+        return dict(x=d(host["x"][b:b + 1, :, h:h + 1]), dt=d(host["dt"][b:b + 1, :, h:h + 1]), A=d(host["A"][h:h + 1]),
+                    B=d(host["B"][b:b + 1, :, g:g + 1]), C=d(host["C"][b:b + 1, :, g:g + 1]), D=d(host["D"][h:h + 1]),
+                    dt_bias=d(host["dt_bias"][h:h + 1]), h0=d(host["h0"][b:b + 1, h:h + 1]))
+    out = {k: d(v[b:b + 1, h:h + 1]) for k, v in host.items() if k != "u"}
+    if "u" in host:
+        out["u"] = d(host["u"][h:h + 1])
+    return out
+
+
+def run_scan(args, w, rank, world, dev):
+    import linearnexus_b200 as L
+    from linearnexus_b200 import _lib
+    from oracle import linear_recurrences_oracle as R   # checker only: outside every timed region
+    _lib.load()
+    B = w["B"]
+    host = scan_host_inputs(w, B, seed=(1234 + w["cfg_id"]) * 4096 + rank)
+    pin = {k: v.contiguous().pin_memory() for k, v in host.items()}
+    devt = {k: v.to(dev, non_blocking=True) for k, v in pin.items()}
+    torch.cuda.synchronize(dev)
+    step = lambda: scan_call(L, w, devt)
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(dev.index)
+    if rank == 0:
+        sampler.start()
+    n0 = _lib.launch_count()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    barrier()
+    ev[0].record()
+    for i in range(args.steps):
+        step()
+        ev[i + 1].record()
+    barrier()
+    total_ms = ev[0].elapsed_time(ev[-1])
+    launches = _lib.launch_count() - n0
+    path = _lib.last_path()
+    clocks = sampler.stop() if rank == 0 else None
+
+    o, hT = step()
+    torch.cuda.synchronize(dev)
+    rng = np.random.default_rng(rank)
+    units = sorted({(int(rng.integers(B)), int(rng.integers(w["H"]))) for _ in range(8)})[:2]
+    eo = es = 0.0
+    for (b, h) in units:
+        ro, rs = scan_call(R, w, scan_unit(w, host, b, h), cd=torch.float64)
+        got_o = o[b:b + 1, :, h:h + 1] if w["variant"] == "ssd" else o[b:b + 1, h:h + 1]
+        eo, es = max(eo, rel_err(got_o, ro)), max(es, rel_err(hT[b:b + 1, h:h + 1], rs))
+    parity = {"o_rel": eo, "state_rel": es, "units": len(units), "against": "float64 token recurrence (oracle)"}
+
+    # end to end: pinned host inputs -> device -> public function -> pinned host outputs, all inside the timed region
+    out_host = [torch.empty(o.shape, dtype=o.dtype).pin_memory(), torch.empty(hT.shape, dtype=hT.dtype).pin_memory()]
+
+    def e2e_step():
+        t = {k: v.to(dev, non_blocking=True) for k, v in pin.items()}
+        oo, ss = scan_call(L, w, t)
+        out_host[0].copy_(oo, non_blocking=True)
+        out_host[1].copy_(ss, non_blocking=True)
+
+    e2e_step()
+    e2e_steps = max(1, min(args.steps, 5))
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    t1.record()
+    barrier()
+    e2e_ms = t0.elapsed_time(t1) / e2e_steps
+    times = torch.tensor([total_ms, e2e_ms, eo, es], dtype=torch.float64, device=dev)
+    if world > 1:
+        gathered = [torch.empty_like(times) for _ in range(world)]
+        torch.distributed.all_gather(gathered, times)
+        allv = torch.stack(gathered)
+        parity["per_rank"] = allv[:, 2:4].tolist()
+        parity["units"] *= world
+        times = allv.max(dim=0).values
+    total_ms, e2e_ms, parity["o_rel"], parity["state_rel"] = times.tolist()
+    ms = total_ms / args.steps
+    tokens = B * w["T"]
+    return dict(ms_per_step=ms, value=world * tokens / (ms * 1e-3), e2e_value=world * tokens / (e2e_ms * 1e-3),
+                h2d=sum(v.numel() * v.element_size() for v in pin.values()),
+                d2h=sum(v.numel() * v.element_size() for v in out_host), launches=launches, path=path, clocks=clocks,
+                kernel_ms=ms, parity=parity, strong=None)
+
+
+def cpu_scan_sample(w, target_s=12.0):
+    """The float32 CPU oracle of a scan workload on a few heads of one batch row at the full length, scaled linearly."""
+    from oracle import linear_recurrences_oracle as R
+    torch.set_num_threads(os.cpu_count() or 1)
+    heads = 4
+    inp = {k: (v.float() if v.dtype == torch.bfloat16 else v) for k, v in scan_host_inputs(w, 1, seed=99, heads=heads).items()}
+    scan_call(R, w, inp, cd=torch.float32)
+    t0, reps = time.perf_counter(), 0
+    while True:
+        scan_call(R, w, inp, cd=torch.float32)
+        reps += 1
+        el = time.perf_counter() - t0
+        if el >= target_s or reps >= 200:
+            break
+    sec = el / reps
+    value = w["B"] * w["T"] * (heads / (w["B"] * w["H"])) / sec
+    sample = (f"{w['variant']} oracle (torch fp32, CPU) on B=1,H={heads},T={w['T']},K={w['K']},V={w['V']} "
+              f"({reps} reps, {sec:.3f} s each), scaled linearly in B*H to the full workload")
+    return dict(value=value, cores=torch.get_num_threads(), sample=sample, sec_per_rep=sec, reps=reps)
 
 
 def run_ours(args, w, rank, world, dev):
@@ -423,6 +586,8 @@ def run_ours(args, w, rank, world, dev):
 def cpu_oracle_sample(w, target_s=12.0, threads=None):
     """Times the CPU oracle (torch fp32 restatement of the reference op) on a bounded sample of
     the workload: a (batch x head) slice at the full sequence length, scaled linearly."""
+    if w["kind"] == "scan":
+        return cpu_scan_sample(w, target_s)
     from oracle import delta_rule_oracle as O
     # torchrun exports OMP_NUM_THREADS=1: the CPU arm is meant to use every host core it can
     torch.set_num_threads(threads or os.cpu_count() or 1)
@@ -483,8 +648,9 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     metric = ("decode_tokens_per_sec" if w["kind"] == "decode" else
-              "delta_rule_fwd_bwd_tokens_per_sec" if w["kind"] == "fwd_bwd" else "delta_rule_fwd_tokens_per_sec")
-    what = {"decode": "decode step", "fwd_bwd": "chunkwise forward + backward"}.get(w["kind"], "chunkwise forward")
+              "delta_rule_fwd_bwd_tokens_per_sec" if w["kind"] == "fwd_bwd" else
+              f"{w['variant']}_scan_fwd_tokens_per_sec" if w["kind"] == "scan" else "delta_rule_fwd_tokens_per_sec")
+    what = {"decode": "decode step", "fwd_bwd": "chunkwise forward + backward", "scan": "scan forward"}.get(w["kind"], "chunkwise forward")
     config = {"workload": f"{args.workload}: {w['variant']} {what} "
                           f"B={w['B']} T={w['T']} H={w['H']} d_k={w['K']} d_v={w['V']} chunk={w['chunk']} per GPU"
                           + (", inputs stored [B,T,H,D]" if w.get("bthd") else ""),
@@ -523,7 +689,7 @@ def main():
     torch.cuda.set_device(dev)
     if world > 1:
         torch.distributed.init_process_group("nccl", device_id=dev)
-    res = run_ours(args, w, rank, world, dev)
+    res = run_scan(args, w, rank, world, dev) if w["kind"] == "scan" else run_ours(args, w, rank, world, dev)
     if world > 1:
         torch.distributed.barrier()
     if rank == 0:
@@ -534,7 +700,7 @@ def main():
         # intra + state pass for the two-kernel forward; forward + pre-pass + adjoint + finalize for fwd_bwd)
         ktime = res["ms_per_step"] * 1e-3
         alg_b = alg_bytes(w, 4 if w["cfg_id"] == 1 else 2)
-        if w["kind"] == "decode":
+        if w["kind"] in ("decode", "scan"):
             roof = {"bound": "hbm", "achieved": alg_b / ktime / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s"}
         else:
             flops = alg_flops_per_token_head(C, w["K"], w["V"]) * units * (3 if w["kind"] == "fwd_bwd" else 1)
@@ -558,7 +724,8 @@ def main():
             cpu = {"value": c["value"], "unit": "tokens/s", "cores": c["cores"], "kind": "port", "sample": c["sample"]}
         line = {"metric": metric, "value": res["value"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": "f32" if w["cfg_id"] == 1 else "bf16", "data": "synthetic", "config": config,
+                "vs_baseline": None, "dtype": "f32" if w["cfg_id"] == 1 or w["kind"] == "scan" else "bf16", "data": "synthetic",
+                "config": config,
                 "e2e": {"value": res["e2e_value"], "unit": "tokens/s", "h2d_bytes_per_step": res["h2d"],
                         "d2h_bytes_per_step": res["d2h"]},
                 "gpu_launches": res["launches"], "clocks": res["clocks"], "roofline": roof, "parity": res["parity"],

@@ -265,6 +265,36 @@ int dr_gate_activations(int mode, const void* a, const void* b, const float* A_l
 int dr_gated_rmsnorm(const void* o, const void* gate, const float* weight, void* y, int B, int H, int T, int V,
                      int o_layout, int o_dtype, int gate_dtype, int y_dtype, float eps, void* stream);
 
+/*
+ * Other matrix-state scans of the reference, token by token with the fp32 state in registers (no chunk form yet).
+ * io_dtype tags every activation tensor and the output; states, u, A, D, dt_bias are float32.  h0 null = zero state,
+ * hT null = not wanted, hT may be h0 (in place: the decode step).  T = 1 is the single-step function.
+ * K, V (N, P for the SSD) in 1..256.  Activation pointers need the alignment of their element type only.
+ *
+ * dr_dplr_recurrent -- dplr_delta_rule_recurrent / dplr_delta_rule_step (modules/linear_attn/rwkv7.py:114-259):
+ *   h <- exp(gk) * h + b (a^T h) + k v^T;  o = h^T (q * scale).  q, k, a, b, gk [B,H,T,K] (or [B,T,H,K] with
+ *   DR_LAYOUT_BTHD), v, o [.., V]; state [B,H,K,V].
+ *
+ * dr_rwkv6_recurrent -- rwkv6_recurrent / rwkv6_step (modules/linear_attn/rwkv6.py:115-189, 360-398), which is also
+ *   what the reference's RWKV6Block runs in "chunk" mode (rwkv6.py:837-850):
+ *   o = (h + (u * k) v^T)^T (sigmoid(r) * scale);  h <- exp(-exp(w)) * h + k v^T.  u float32 [H,K].
+ *
+ * dr_ssd_scan -- ssd_chunk_scan / ssd_recurrent_step (modules/ssm/mamba2.py:161-425), as the token recurrence the
+ *   chunked scan equals: dt' = clamp(softplus(dt + dt_bias[h]), dt_lo, dt_hi);
+ *   state <- exp(A[h] dt') state + (dt' x) B^T;  y = state C + D[h] x.
+ *   x, y [B,T,H,P]; dt [B,T,H] (dt_dtype); Bm, Cm [B,T,G,N] with H % G == 0 (head h reads group h / (H/G));
+ *   state [B,H,P,N].
+ */
+int dr_dplr_recurrent(const void* q, const void* k, const void* v, const void* a, const void* b, const void* gk,
+                      const float* h0, void* o, float* hT, int B, int H, int T, int K, int V, float scale,
+                      int io_dtype, int layout, void* stream);
+int dr_rwkv6_recurrent(const void* r, const void* k, const void* v, const void* w, const float* u, const float* h0,
+                       void* o, float* hT, int B, int H, int T, int K, int V, float scale, int io_dtype, int layout,
+                       void* stream);
+int dr_ssd_scan(const void* x, const void* dt, const float* A, const void* Bm, const void* Cm, const float* D,
+                const float* dt_bias, const float* h0, void* y, float* hT, int B, int T, int H, int P, int N,
+                int groups, float dt_lo, float dt_hi, int io_dtype, int dt_dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -13,6 +13,8 @@ from .state import DeltaNetState, GatedDeltaNetState, KDAState
 from .host_pipeline import HostPipeline, chunkwise_from_host
 from .ops import check_device_status
 from .varlen import chunkwise_varlen, compute_unpadded_indices, pad, unpad
+from .recurrences import (dplr_delta_rule_recurrent, dplr_delta_rule_step, rwkv6_chunkwise, rwkv6_recurrent,
+                          rwkv6_step, ssd_chunk_scan, ssd_recurrent_step)
 from .block_ops import (depthwise_conv1d_causal, gated_deltanet_gates, kda_gate, rmsnorm_gated,
                         short_conv_silu)
 
@@ -24,5 +26,7 @@ __all__ = [
     "KernelBackend", "backend_availability", "select_kernel_backend",
     "HostPipeline", "chunkwise_from_host", "check_device_status",
     "chunkwise_varlen", "compute_unpadded_indices", "unpad", "pad",
+    "dplr_delta_rule_recurrent", "dplr_delta_rule_step", "rwkv6_recurrent", "rwkv6_chunkwise", "rwkv6_step",
+    "ssd_chunk_scan", "ssd_recurrent_step",
     "depthwise_conv1d_causal", "short_conv_silu", "gated_deltanet_gates", "kda_gate", "rmsnorm_gated",
 ]

@@ -33,7 +33,8 @@ EXPORTS = ["dr_version", "dr_strerror", "dr_last_cuda_error", "dr_launch_count",
            "dr_workspace_bytes", "dr_chunk_fwd", "dr_recurrent_fwd", "dr_step", "dr_chunk_bwd",
            "dr_debug_umma_selftest", "dr_chunk_bwd_static", "dr_chunk_fwd_saving", "dr_chunk_bwd_saved",
            "dr_short_conv_silu", "dr_gate_activations", "dr_gated_rmsnorm", "dr_check_status",
-           "dr_last_device_status", "dr_debug_wait_timeout", "dr_chunk_fwd_varlen"]
+           "dr_last_device_status", "dr_debug_wait_timeout", "dr_chunk_fwd_varlen", "dr_dplr_recurrent",
+           "dr_rwkv6_recurrent", "dr_ssd_scan"]
 
 
 class DrDesc(ctypes.Structure):
@@ -143,6 +144,12 @@ def load() -> ctypes.CDLL:
         lib.dr_gate_activations.argtypes = [ci, vp, vp, fp, fp, fp, fp, ci, ci, ci, ci, ci, ci, cf, cf, vp]
         lib.dr_gated_rmsnorm.restype = ctypes.c_int
         lib.dr_gated_rmsnorm.argtypes = [vp, vp, fp, vp, ci, ci, ci, ci, ci, ci, ci, ci, cf, vp]
+        lib.dr_dplr_recurrent.restype = ctypes.c_int
+        lib.dr_dplr_recurrent.argtypes = [vp, vp, vp, vp, vp, vp, fp, vp, fp, ci, ci, ci, ci, ci, cf, ci, ci, vp]
+        lib.dr_rwkv6_recurrent.restype = ctypes.c_int
+        lib.dr_rwkv6_recurrent.argtypes = [vp, vp, vp, vp, fp, fp, vp, fp, ci, ci, ci, ci, ci, cf, ci, ci, vp]
+        lib.dr_ssd_scan.restype = ctypes.c_int
+        lib.dr_ssd_scan.argtypes = [vp, vp, fp, vp, vp, fp, fp, fp, vp, fp, ci, ci, ci, ci, ci, ci, cf, cf, ci, ci, vp]
         lib.dr_debug_umma_selftest.restype = ctypes.c_int
         lib.dr_debug_umma_selftest.argtypes = [vp, vp, fp, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ip, vp]
         _lib = lib

@@ -14,6 +14,7 @@
 #include "dr_bwd.cuh"
 #include "dr_block_ops.cuh"
 #include "dr_common.cuh"
+#include "dr_linrec.cuh"
 #include "dr_recurrent.cuh"
 #include "dr_step.cuh"
 
@@ -114,6 +115,23 @@ int resolve_chunk_path(const DrDesc* d) {
 }
 
 bool fp32_chunk_eligible(const DrDesc* d) { return d->chunk <= 64 && d->K <= 128; }
+
+// A [B,H,T,D] / [B,T,H,D] activation as the strided per-token vector the scans of dr_linrec.cuh read.
+dr::LrVec lr_vec(const void* p, int H, int T, int D, int dt, int bthd, int hdiv = 1) {
+  dr::LrVec v;
+  v.p = p; v.dt = dt; v.hdiv = hdiv;
+  if (bthd) { v.sb = (int64_t)T * H * D; v.sh = D; v.st = (int64_t)H * D; }
+  else { v.sb = (int64_t)H * T * D; v.sh = (int64_t)T * D; v.st = D; }
+  return v;
+}
+bool elem_aligned(const void* p, int dt) { return (reinterpret_cast<uintptr_t>(p) & (dt == DR_BF16 ? 1u : 3u)) == 0; }
+
+int validate_linrec(int B, int H, int T, int K, int V, int io_dtype) {
+  if (!dtype_ok(io_dtype)) return DR_ERR_DTYPE;
+  if (B < 1 || H < 1 || T < 1 || K < 1 || K > 256 || V < 1 || V > 256) return DR_ERR_SHAPE;
+  if ((int64_t)B * H * ((V + 31) / 32) >= ((int64_t)1 << 31)) return DR_ERR_SHAPE;
+  return DR_OK;
+}
 
 }  // namespace
 
@@ -479,6 +497,83 @@ int dr_gated_rmsnorm(const void* o, const void* gate, const float* weight, void*
   tl_path = "gated_rmsnorm";
   cudaError_t e = dr::blk::launch_gated_rmsnorm(p, o_dtype, gate ? gate_dtype : o_dtype, y_dtype, sm_count(),
                                                 reinterpret_cast<cudaStream_t>(stream));
+  g_launches.fetch_add(1);
+  return check_cuda(e);
+}
+
+int dr_dplr_recurrent(const void* q, const void* k, const void* v, const void* a, const void* b, const void* gk,
+                      const float* h0, void* o, float* hT, int B, int H, int T, int K, int V, float scale,
+                      int io_dtype, int layout, void* stream) {
+  if (!q || !k || !v || !a || !b || !gk || !o) return DR_ERR_NULL;
+  if (layout != DR_LAYOUT_BHTD && layout != DR_LAYOUT_BTHD) return DR_ERR_SHAPE;
+  int s = validate_linrec(B, H, T, K, V, io_dtype);
+  if (s != DR_OK) return s;
+  for (const void* ptr : {q, k, v, a, b, gk, (const void*)o})
+    if (!elem_aligned(ptr, io_dtype)) return DR_ERR_ALIGN;
+  const int bthd = layout == DR_LAYOUT_BTHD;
+  dr::LinRecParams p{};
+  p.q = lr_vec(q, H, T, K, io_dtype, bthd); p.k = lr_vec(k, H, T, K, io_dtype, bthd);
+  p.w = lr_vec(gk, H, T, K, io_dtype, bthd); p.a = lr_vec(a, H, T, K, io_dtype, bthd);
+  p.b = lr_vec(b, H, T, K, io_dtype, bthd); p.v = lr_vec(v, H, T, V, io_dtype, bthd);
+  const dr::LrVec ov = lr_vec(o, H, T, V, io_dtype, bthd);
+  p.o = o; p.o_sb = ov.sb; p.o_sh = ov.sh; p.o_st = ov.st; p.o_dt = io_dtype;
+  p.h0 = h0; p.hT = hT; p.s_k = V; p.s_v = 1;
+  p.B = B; p.H = H; p.T = T; p.K = K; p.V = V; p.scale = scale;
+  tl_path = "dplr_recurrent";
+  cudaError_t e = dr::launch_linrec(dr::LR_DPLR, p, reinterpret_cast<cudaStream_t>(stream));
+  g_launches.fetch_add(1);
+  return check_cuda(e);
+}
+
+int dr_rwkv6_recurrent(const void* r, const void* k, const void* v, const void* w, const float* u, const float* h0,
+                       void* o, float* hT, int B, int H, int T, int K, int V, float scale, int io_dtype, int layout,
+                       void* stream) {
+  if (!r || !k || !v || !w || !u || !o) return DR_ERR_NULL;
+  if (layout != DR_LAYOUT_BHTD && layout != DR_LAYOUT_BTHD) return DR_ERR_SHAPE;
+  int s = validate_linrec(B, H, T, K, V, io_dtype);
+  if (s != DR_OK) return s;
+  for (const void* ptr : {r, k, v, w, (const void*)o})
+    if (!elem_aligned(ptr, io_dtype)) return DR_ERR_ALIGN;
+  const int bthd = layout == DR_LAYOUT_BTHD;
+  dr::LinRecParams p{};
+  p.q = lr_vec(r, H, T, K, io_dtype, bthd); p.k = lr_vec(k, H, T, K, io_dtype, bthd);
+  p.w = lr_vec(w, H, T, K, io_dtype, bthd); p.v = lr_vec(v, H, T, V, io_dtype, bthd);
+  p.a = p.q; p.b = p.q;
+  const dr::LrVec ov = lr_vec(o, H, T, V, io_dtype, bthd);
+  p.o = o; p.o_sb = ov.sb; p.o_sh = ov.sh; p.o_st = ov.st; p.o_dt = io_dtype;
+  p.u = u; p.h0 = h0; p.hT = hT; p.s_k = V; p.s_v = 1;
+  p.B = B; p.H = H; p.T = T; p.K = K; p.V = V; p.scale = scale;
+  tl_path = "rwkv6_recurrent";
+  cudaError_t e = dr::launch_linrec(dr::LR_RWKV6, p, reinterpret_cast<cudaStream_t>(stream));
+  g_launches.fetch_add(1);
+  return check_cuda(e);
+}
+
+int dr_ssd_scan(const void* x, const void* dt, const float* A, const void* Bm, const void* Cm, const float* D,
+                const float* dt_bias, const float* h0, void* y, float* hT, int B, int T, int H, int P, int N,
+                int groups, float dt_lo, float dt_hi, int io_dtype, int dt_dtype, void* stream) {
+  if (!x || !dt || !A || !Bm || !Cm || !D || !y) return DR_ERR_NULL;
+  int s = validate_linrec(B, H, T, N, P, io_dtype);
+  if (s != DR_OK) return s;
+  if (!dtype_ok(dt_dtype)) return DR_ERR_DTYPE;
+  if (groups < 1 || groups > H || H % groups) return DR_ERR_SHAPE;
+  for (const void* ptr : {x, Bm, Cm, (const void*)y})
+    if (!elem_aligned(ptr, io_dtype)) return DR_ERR_ALIGN;
+  if (!elem_aligned(dt, dt_dtype)) return DR_ERR_ALIGN;
+  dr::LinRecParams p{};
+  // key axis = the N state channels (B writes, C reads), value axis = the P channels of the head
+  p.q = lr_vec(Cm, groups, T, N, io_dtype, 1, H / groups);
+  p.k = lr_vec(Bm, groups, T, N, io_dtype, 1, H / groups);
+  p.w = p.q; p.a = p.q; p.b = p.q;
+  p.v = lr_vec(x, H, T, P, io_dtype, 1);
+  p.dt = lr_vec(dt, H, T, 1, dt_dtype, 1);
+  const dr::LrVec ov = lr_vec(y, H, T, P, io_dtype, 1);
+  p.o = y; p.o_sb = ov.sb; p.o_sh = ov.sh; p.o_st = ov.st; p.o_dt = io_dtype;
+  p.A = A; p.D = D; p.dt_bias = dt_bias; p.h0 = h0; p.hT = hT;
+  p.s_k = 1; p.s_v = N;   // state stored [P, N]
+  p.B = B; p.H = H; p.T = T; p.K = N; p.V = P; p.scale = 1.f; p.dt_lo = dt_lo; p.dt_hi = dt_hi;
+  tl_path = "ssd_scan";
+  cudaError_t e = dr::launch_linrec(dr::LR_SSD, p, reinterpret_cast<cudaStream_t>(stream));
   g_launches.fetch_add(1);
   return check_cuda(e);
 }
