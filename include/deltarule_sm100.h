@@ -282,7 +282,7 @@ int dr_gated_rmsnorm(const void* o, const void* gate, const float* weight, void*
  * dr_ssd_scan -- ssd_chunk_scan / ssd_recurrent_step (modules/ssm/mamba2.py:161-425), as the token recurrence the
  *   chunked scan equals: dt' = clamp(softplus(dt + dt_bias[h]), dt_lo, dt_hi);
  *   state <- exp(A[h] dt') state + (dt' x) B^T;  y = state C + D[h] x.
- *   x, y [B,T,H,P]; dt [B,T,H] (dt_dtype); Bm, Cm [B,T,G,N] with H % G == 0 (head h reads group h / (H/G));
+ *   x, y [B,T,H,P]; dt float32 [B,T,H]; Bm, Cm [B,T,G,N] with H % G == 0 (head h reads group h / (H/G));
  *   state [B,H,P,N].
  */
 int dr_dplr_recurrent(const void* q, const void* k, const void* v, const void* a, const void* b, const void* gk,
@@ -293,7 +293,7 @@ int dr_rwkv6_recurrent(const void* r, const void* k, const void* v, const void* 
                        void* stream);
 int dr_ssd_scan(const void* x, const void* dt, const float* A, const void* Bm, const void* Cm, const float* D,
                 const float* dt_bias, const float* h0, void* y, float* hT, int B, int T, int H, int P, int N,
-                int groups, float dt_lo, float dt_hi, int io_dtype, int dt_dtype, void* stream);
+                int groups, float dt_lo, float dt_hi, int io_dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -149,7 +149,7 @@ def load() -> ctypes.CDLL:
         lib.dr_rwkv6_recurrent.restype = ctypes.c_int
         lib.dr_rwkv6_recurrent.argtypes = [vp, vp, vp, vp, fp, fp, vp, fp, ci, ci, ci, ci, ci, cf, ci, ci, vp]
         lib.dr_ssd_scan.restype = ctypes.c_int
-        lib.dr_ssd_scan.argtypes = [vp, vp, fp, vp, vp, fp, fp, fp, vp, fp, ci, ci, ci, ci, ci, ci, cf, cf, ci, ci, vp]
+        lib.dr_ssd_scan.argtypes = [vp, vp, fp, vp, vp, fp, fp, fp, vp, fp, ci, ci, ci, ci, ci, ci, cf, cf, ci, vp]
         lib.dr_debug_umma_selftest.restype = ctypes.c_int
         lib.dr_debug_umma_selftest.argtypes = [vp, vp, fp, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ip, vp]
         _lib = lib

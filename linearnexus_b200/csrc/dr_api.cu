@@ -129,7 +129,7 @@ bool elem_aligned(const void* p, int dt) { return (reinterpret_cast<uintptr_t>(p
 int validate_linrec(int B, int H, int T, int K, int V, int io_dtype) {
   if (!dtype_ok(io_dtype)) return DR_ERR_DTYPE;
   if (B < 1 || H < 1 || T < 1 || K < 1 || K > 256 || V < 1 || V > 256) return DR_ERR_SHAPE;
-  if ((int64_t)B * H * ((V + 31) / 32) >= ((int64_t)1 << 31)) return DR_ERR_SHAPE;
+  if ((int64_t)B * H * ((V + 63) / 64) >= ((int64_t)1 << 31)) return DR_ERR_SHAPE;
   return DR_OK;
 }
 
@@ -520,7 +520,7 @@ int dr_dplr_recurrent(const void* q, const void* k, const void* v, const void* a
   p.h0 = h0; p.hT = hT; p.s_k = V; p.s_v = 1;
   p.B = B; p.H = H; p.T = T; p.K = K; p.V = V; p.scale = scale;
   tl_path = "dplr_recurrent";
-  cudaError_t e = dr::launch_linrec(dr::LR_DPLR, p, reinterpret_cast<cudaStream_t>(stream));
+  cudaError_t e = dr::launch_linrec(dr::LR_DPLR, io_dtype == DR_BF16, p, reinterpret_cast<cudaStream_t>(stream));
   g_launches.fetch_add(1);
   return check_cuda(e);
 }
@@ -544,36 +544,35 @@ int dr_rwkv6_recurrent(const void* r, const void* k, const void* v, const void* 
   p.u = u; p.h0 = h0; p.hT = hT; p.s_k = V; p.s_v = 1;
   p.B = B; p.H = H; p.T = T; p.K = K; p.V = V; p.scale = scale;
   tl_path = "rwkv6_recurrent";
-  cudaError_t e = dr::launch_linrec(dr::LR_RWKV6, p, reinterpret_cast<cudaStream_t>(stream));
+  cudaError_t e = dr::launch_linrec(dr::LR_RWKV6, io_dtype == DR_BF16, p, reinterpret_cast<cudaStream_t>(stream));
   g_launches.fetch_add(1);
   return check_cuda(e);
 }
 
 int dr_ssd_scan(const void* x, const void* dt, const float* A, const void* Bm, const void* Cm, const float* D,
                 const float* dt_bias, const float* h0, void* y, float* hT, int B, int T, int H, int P, int N,
-                int groups, float dt_lo, float dt_hi, int io_dtype, int dt_dtype, void* stream) {
+                int groups, float dt_lo, float dt_hi, int io_dtype, void* stream) {
   if (!x || !dt || !A || !Bm || !Cm || !D || !y) return DR_ERR_NULL;
   int s = validate_linrec(B, H, T, N, P, io_dtype);
   if (s != DR_OK) return s;
-  if (!dtype_ok(dt_dtype)) return DR_ERR_DTYPE;
   if (groups < 1 || groups > H || H % groups) return DR_ERR_SHAPE;
   for (const void* ptr : {x, Bm, Cm, (const void*)y})
     if (!elem_aligned(ptr, io_dtype)) return DR_ERR_ALIGN;
-  if (!elem_aligned(dt, dt_dtype)) return DR_ERR_ALIGN;
+  if (!elem_aligned(dt, DR_F32)) return DR_ERR_ALIGN;
   dr::LinRecParams p{};
   // key axis = the N state channels (B writes, C reads), value axis = the P channels of the head
   p.q = lr_vec(Cm, groups, T, N, io_dtype, 1, H / groups);
   p.k = lr_vec(Bm, groups, T, N, io_dtype, 1, H / groups);
   p.w = p.q; p.a = p.q; p.b = p.q;
   p.v = lr_vec(x, H, T, P, io_dtype, 1);
-  p.dt = lr_vec(dt, H, T, 1, dt_dtype, 1);
+  p.dt = lr_vec(dt, H, T, 1, DR_F32, 1);
   const dr::LrVec ov = lr_vec(y, H, T, P, io_dtype, 1);
   p.o = y; p.o_sb = ov.sb; p.o_sh = ov.sh; p.o_st = ov.st; p.o_dt = io_dtype;
   p.A = A; p.D = D; p.dt_bias = dt_bias; p.h0 = h0; p.hT = hT;
   p.s_k = 1; p.s_v = N;   // state stored [P, N]
   p.B = B; p.H = H; p.T = T; p.K = N; p.V = P; p.scale = 1.f; p.dt_lo = dt_lo; p.dt_hi = dt_hi;
   tl_path = "ssd_scan";
-  cudaError_t e = dr::launch_linrec(dr::LR_SSD, p, reinterpret_cast<cudaStream_t>(stream));
+  cudaError_t e = dr::launch_linrec(dr::LR_SSD, io_dtype == DR_BF16, p, reinterpret_cast<cudaStream_t>(stream));
   g_launches.fetch_add(1);
   return check_cuda(e);
 }

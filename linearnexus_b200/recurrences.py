@@ -158,7 +158,7 @@ def ssd_chunk_scan(hidden_states: Tensor, dt: Tensor, A: Tensor, B: Tensor, C: T
         raise ValueError(f"B/C carry {G} groups; n_groups={n_groups}, heads={H}")
     od = x.dtype
     x, Bm, Cm = (t.contiguous() for t in _common_io(x, B, C))
-    dtn = _native(dt).contiguous()
+    dtn = dt.to(torch.float32).contiguous()
     f32 = lambda t: None if t is None else t.to(torch.float32).contiguous()
     A32, D32, bias32 = f32(A), f32(D), f32(dt_bias)
     h0 = _state(ssm_state, (Bt, H, P, N), x.device)
@@ -170,8 +170,7 @@ def ssd_chunk_scan(hidden_states: Tensor, dt: Tensor, A: Tensor, B: Tensor, C: T
     lo, hi = float(dt_limit[0]), min(float(dt_limit[1]), 3.0e38)
     with torch.cuda.device(x.device):
         st = _lib.load().dr_ssd_scan(_ptr(x), _ptr(dtn), _ptr(A32), _ptr(Bm), _ptr(Cm), _ptr(D32), _ptr(bias32), _ptr(h0),
-                                     _ptr(y), _ptr(hT), Bt, T, H, P, N, G, lo, hi, _NATIVE[x.dtype], _NATIVE[dtn.dtype],
-                                     _stream(x.device))
+                                     _ptr(y), _ptr(hT), Bt, T, H, P, N, G, lo, hi, _NATIVE[x.dtype], _stream(x.device))
     _lib.check(st, "dr_ssd_scan")
     return y.to(od), hT
 
