@@ -14,7 +14,7 @@
 // receptance, softplus and clamp of dt); one __syncthreads per block.  Tokens past the end of the sequence are
 // staged as no-ops (decay 1, nothing written), so the TB tokens of a block run as straight-line code.
 //
-// What bounds it: 5 K V (DPLR), 4 K V (RWKV-6), 2 K V (SSD) fp32 multiply-adds per token and head on the CUDA
+// What bounds it: 5 K V (DPLR), 4 K V (RWKV-6), 3 K V (SSD) fp32 multiply-adds per token and head on the CUDA
 // cores, and one dependent reduce-then-update chain per token.  The tensor cores need the chunked forms.
 #pragma once
 
