@@ -342,8 +342,11 @@ inline cudaError_t launch_linrec_kind(const LinRecParams& p, cudaStream_t stream
   const int nvs = (p.V + kLrCols - 1) / kLrCols;
   const dim3 grid((unsigned)((int64_t)p.B * p.H * nvs)), block(kLrThreads);
   const int kp = (p.K + kLrParts - 1) / kLrParts;
-  if (kp <= 4) linrec_kernel<KIND, 4, 8, BF><<<grid, block, 0, stream>>>(p);
-  else if (kp <= 8) linrec_kernel<KIND, 8, 8, BF><<<grid, block, 0, stream>>>(p);
+  // tokens per block for the small key tiles: the DPLR body is the longest (its eight unrolled tokens overflow the
+  // instruction cache: 1.33 -> 1.16 ms with four), the other two rules prefer fewer barriers (RWKV-6 1.16 vs 1.46 ms)
+  constexpr int TBS = KIND == LR_DPLR ? 4 : 8;
+  if (kp <= 4) linrec_kernel<KIND, 4, TBS, BF><<<grid, block, 0, stream>>>(p);
+  else if (kp <= 8) linrec_kernel<KIND, 8, TBS, BF><<<grid, block, 0, stream>>>(p);
   else if (kp <= 16) linrec_kernel<KIND, 16, 4, BF><<<grid, block, 0, stream>>>(p);
   else linrec_kernel<KIND, 32, 2, BF><<<grid, block, 0, stream>>>(p);
   return cudaGetLastError();
