@@ -158,6 +158,26 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def h2d_probe(pin_tensors, dev, barrier, reps=3):
+    """Host-to-device bandwidth of this rank with every rank copying at once: `reps` copies of the step's pinned
+    inputs between two barriers, device-timed.  Explains the end-to-end figure: the copies of all ranks share the
+    host's memory and PCIe roots."""
+    ts = [t for t in pin_tensors if t is not None]
+    dst = [torch.empty(t.shape, dtype=t.dtype, device=dev) for t in ts]
+    for d_, t in zip(dst, ts):
+        d_.copy_(t, non_blocking=True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(reps):
+        for d_, t in zip(dst, ts):
+            d_.copy_(t, non_blocking=True)
+    e1.record()
+    barrier()
+    nbytes = reps * sum(t.numel() * t.element_size() for t in ts)
+    return nbytes / (e0.elapsed_time(e1) * 1e-3) / 1e9
+
+
 def host_rows(w, lo, hi):
     """Rows lo..hi-1 of the workload's global batch (pinned host memory, the op's [B,H,T,D] layout)."""
     from linearnexus_b200.synthetic import make_rows
@@ -309,7 +329,8 @@ def run_scan(args, w, rank, world, dev):
     t1.record()
     barrier()
     e2e_ms = t0.elapsed_time(t1) / e2e_steps
-    times = torch.tensor([total_ms, e2e_ms, eo, es], dtype=torch.float64, device=dev)
+    h2d_gbs = h2d_probe(list(pin.values()), dev, barrier)
+    times = torch.tensor([total_ms, e2e_ms, eo, es, -h2d_gbs], dtype=torch.float64, device=dev)
     if world > 1:
         gathered = [torch.empty_like(times) for _ in range(world)]
         torch.distributed.all_gather(gathered, times)
@@ -317,13 +338,13 @@ def run_scan(args, w, rank, world, dev):
         parity["per_rank"] = allv[:, 2:4].tolist()
         parity["units"] *= world
         times = allv.max(dim=0).values
-    total_ms, e2e_ms, parity["o_rel"], parity["state_rel"] = times.tolist()
+    total_ms, e2e_ms, parity["o_rel"], parity["state_rel"], neg_h2d = times.tolist()
     ms = total_ms / args.steps
     tokens = B * w["T"]
     return dict(ms_per_step=ms, value=world * tokens / (ms * 1e-3), e2e_value=world * tokens / (e2e_ms * 1e-3),
                 h2d=sum(v.numel() * v.element_size() for v in pin.values()),
                 d2h=sum(v.numel() * v.element_size() for v in out_host), launches=launches, path=path, clocks=clocks,
-                kernel_ms=ms, parity=parity, strong=None)
+                kernel_ms=ms, parity=parity, strong=None, h2d_gbs=-neg_h2d)
 
 
 def cpu_scan_sample(w, target_s=12.0):
@@ -533,6 +554,7 @@ def run_ours(args, w, rank, world, dev):
         elif pin.get("h0") is not None and not w.get("bthd"):
             h2d += pin["h0"].numel() * pin["h0"].element_size()
     d2h = sum(t.numel() * t.element_size() for t in out_host)
+    h2d_gbs = h2d_probe([e2e_in[x] for x in names] if decode else [pin[x] for x in names], dev, barrier)
 
     # ---- strong scaling of the forward: the N = 1 global batch cut over the ranks ----
     strong = None
@@ -555,7 +577,8 @@ def run_ours(args, w, rank, world, dev):
 
     times = torch.tensor([total_ms, e2e_ms, strong["ms"] if strong else 0.0, parity["o_rel"],
                           parity.get("state_rel", parity.get("state_abs", 0.0)),
-                          strong["parity"]["o_rel"] if strong else 0.0, strong["parity"]["state_rel"] if strong else 0.0],
+                          strong["parity"]["o_rel"] if strong else 0.0, strong["parity"]["state_rel"] if strong else 0.0,
+                          -h2d_gbs],
                          dtype=torch.float64, device=dev)
     per_rank = None
     if world > 1:
@@ -564,7 +587,7 @@ def run_ours(args, w, rank, world, dev):
         allv = torch.stack(gathered)
         per_rank = allv[:, 3:5].tolist()
         times = allv.max(dim=0).values                     # slowest rank, worst error
-    total_ms, e2e_ms, strong_ms, p_o, p_s, sp_o, sp_s = times.tolist()
+    total_ms, e2e_ms, strong_ms, p_o, p_s, sp_o, sp_s, neg_h2d = times.tolist()   # max over ranks; slowest copy
     parity["o_rel"] = p_o
     parity["state_rel" if "state_rel" in parity else "state_abs"] = p_s
     if per_rank is not None:
@@ -573,7 +596,7 @@ def run_ours(args, w, rank, world, dev):
     ms_per_step = total_ms / args.steps
     res = dict(ms_per_step=ms_per_step, value=world * tokens_per_step / (ms_per_step * 1e-3),
                e2e_value=world * tokens_per_step / (e2e_ms * 1e-3), h2d=h2d, d2h=d2h, launches=launches, path=path,
-               clocks=clocks, kernel_ms=float(np.mean(per_launch_ms)), parity=parity, strong=None)
+               clocks=clocks, kernel_ms=float(np.mean(per_launch_ms)), parity=parity, strong=None, h2d_gbs=-neg_h2d)
     if strong:
         res["strong"] = {"global_batch": B, "units_per_rank": strong["units"], "sharded_over": strong["mode"],
                          "ms_per_step": strong_ms, "value": B * w["T"] / (strong_ms * 1e-3), "unit": "tokens/s",
@@ -727,7 +750,9 @@ def main():
                 "vs_baseline": None, "dtype": "f32" if w["cfg_id"] == 1 or w["kind"] == "scan" else "bf16", "data": "synthetic",
                 "config": config,
                 "e2e": {"value": res["e2e_value"], "unit": "tokens/s", "h2d_bytes_per_step": res["h2d"],
-                        "d2h_bytes_per_step": res["d2h"]},
+                        "d2h_bytes_per_step": res["d2h"],
+                        # pinned host -> device GB/s of the slowest rank with all ranks copying at once (the ceiling of e2e)
+                        "h2d_gbs_slowest_rank": res["h2d_gbs"]},
                 "gpu_launches": res["launches"], "clocks": res["clocks"], "roofline": roof, "parity": res["parity"],
                 "cpu_baseline": cpu}
         if res["strong"]:
