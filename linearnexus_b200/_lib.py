@@ -17,8 +17,8 @@ _PKG = Path(__file__).resolve().parent
 _ROOT = _PKG.parent
 # DELTARULE_SM100_LIB points the loader at another build of the same library (profiling builds).
 LIB_PATH = Path(os.environ.get("DELTARULE_SM100_LIB", _PKG / "libdeltarule_sm100.so"))
-_SOURCES = ["dr_api.cu"]
-_HEADERS = sorted(f.name for f in (_PKG / "csrc").glob("*.cuh"))
+_SOURCES = ["dr_api.cu", "dr_scans.cu"]   # translation units, compiled side by side
+_HEADERS = sorted(f.name for f in list((_PKG / "csrc").glob("*.cuh")) + list((_PKG / "csrc").glob("*.h")))
 
 # DrVariant / DrDtype / DrLayout / DrChunkPath (include/deltarule_sm100.h)
 DR_DELTA, DR_GATED, DR_KDA = 0, 1, 2
@@ -56,11 +56,16 @@ class DeltaRuleError(RuntimeError):
         self.status = status
 
 
+def nvcc_flags() -> list[str]:
+    return ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
+            f"-I{_ROOT / 'include'}", f"-I{_PKG / 'csrc'}"]
+
+
 def nvcc_command(out: Path | None = None, extra: list[str] | None = None) -> list[str]:
+    """One nvcc invocation that compiles and links every unit (profiling builds; `build_library` compiles the units in
+    parallel instead)."""
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-           "-shared", "-Xcompiler", "-fPIC", f"-I{_ROOT / 'include'}", f"-I{_PKG / 'csrc'}"]
-    cmd += extra or []
+    cmd = [nvcc] + nvcc_flags() + ["-shared"] + (extra or [])
     cmd += ["-o", str(out or LIB_PATH)] + [str(_PKG / "csrc" / s) for s in _SOURCES]
     return cmd
 
@@ -69,20 +74,40 @@ def library_is_stale() -> bool:
     if not LIB_PATH.exists():
         return True
     t = LIB_PATH.stat().st_mtime
-    deps = [_PKG / "csrc" / f for f in _SOURCES + _HEADERS] + [_ROOT / "include" / "deltarule_sm100.h"]
+    deps = [_PKG / "csrc" / f for f in _SOURCES + _HEADERS] + list((_ROOT / "include").glob("*.h"))
     return any(d.exists() and d.stat().st_mtime > t for d in deps)
 
 
 def build_library(force: bool = False, verbose: bool = False) -> Path:
-    """Compile the CUDA sources for sm_100a into the package directory (cross-compiles without a GPU)."""
+    """Compile the CUDA sources for sm_100a into the package directory (cross-compiles without a GPU): one object
+    per translation unit, the units in parallel, then one link."""
     if force or library_is_stale():
-        cmd = nvcc_command()
-        res = subprocess.run(cmd, capture_output=True, text=True)
-        if verbose or res.returncode:
-            print(" ".join(cmd))
-            print(res.stdout, res.stderr)
-        if res.returncode:
-            raise RuntimeError("nvcc failed building libdeltarule_sm100.so:\n" + res.stderr)
+        import tempfile
+        nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+        with tempfile.TemporaryDirectory(prefix="deltarule_sm100_") as tmp:
+            objs, procs = [], []
+            for src in _SOURCES:
+                obj = Path(tmp) / (Path(src).stem + ".o")
+                cmd = [nvcc] + nvcc_flags() + ["-c", "-o", str(obj), str(_PKG / "csrc" / src)]
+                objs.append(obj)
+                procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)))
+            link = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB_PATH)] + [str(o) for o in objs]
+            failed = ""
+            for cmd, pr in procs:
+                out, err = pr.communicate()
+                if verbose or pr.returncode:
+                    print(" ".join(cmd))
+                    print(out, err)
+                if pr.returncode:
+                    failed += err
+            if failed:
+                raise RuntimeError("nvcc failed building libdeltarule_sm100.so:\n" + failed)
+            res = subprocess.run(link, capture_output=True, text=True)
+            if verbose or res.returncode:
+                print(" ".join(link))
+                print(res.stdout, res.stderr)
+            if res.returncode:
+                raise RuntimeError("nvcc failed linking libdeltarule_sm100.so:\n" + res.stderr)
     return LIB_PATH
 
 

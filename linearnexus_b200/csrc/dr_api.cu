@@ -14,8 +14,7 @@
 #include "dr_bwd.cuh"
 #include "dr_block_ops.cuh"
 #include "dr_common.cuh"
-#include "dr_linrec.cuh"
-#include "dr_recurrent.cuh"
+#include "dr_scan_launch.h"
 #include "dr_step.cuh"
 
 namespace {

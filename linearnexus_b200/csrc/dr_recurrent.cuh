@@ -246,7 +246,7 @@ inline cudaError_t launch_recurrent_variant(const FwdParams& p, cudaStream_t str
   return cudaGetLastError();
 }
 
-inline cudaError_t launch_recurrent(const FwdParams& p, cudaStream_t stream) {
+cudaError_t launch_recurrent(const FwdParams& p, cudaStream_t stream) {
   if (p.variant == DR_KDA) return launch_recurrent_variant<DR_KDA>(p, stream);
   if (p.variant == DR_GATED) return launch_recurrent_variant<DR_GATED>(p, stream);
   return launch_recurrent_variant<DR_DELTA>(p, stream);
