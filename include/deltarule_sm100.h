@@ -52,7 +52,7 @@ typedef enum DrStatus {
 
 /* Which kernel family serves a chunk-forward call. */
 typedef enum DrChunkPath {
-  DR_PATH_AUTO = 0,   /* tensor-core kernel when the shape qualifies, else the fp32 kernel */
+  DR_PATH_AUTO = 0,   /* tensor-core kernel when the shape qualifies, else the register-resident token recurrence */
   DR_PATH_FP32 = 1,   /* CUDA-core fp32 chunk kernel (any K,V multiple of 16 up to 256) */
   DR_PATH_TCGEN05 = 2, /* tcgen05/TMEM bf16-operand kernel (K=V=128, chunk 64, bf16 q,k,v) */
   DR_PATH_SPLIT = 3    /* two kernels: chunk-parallel intra-chunk pass + tcgen05 state pass over a caller

@@ -28,6 +28,7 @@
 #pragma once
 
 #include "dr_chunk_fp32.cuh"
+#include "dr_scan_launch.h"
 #include "dr_chunk_sm100.cuh"
 #include "dr_kda_sm100.cuh"
 #include "dr_common.cuh"
@@ -1318,7 +1319,9 @@ inline cudaError_t launch_bwd_forward(const DrDesc* d, const void* q, const void
     e = kda::launch_chunk(f, ckpt + units * N * K * V, stream, &n2);
     *launches += n2;
   } else {
-    e = launch_chunk_fp32(f, stream);
+    // every other shape: the token recurrence (the same function of the inputs as the chunk form, and on the CUDA
+    // cores 4-11x faster than the fp32 chunk kernel) leaves the state at each chunk start on its way
+    e = launch_recurrent(f, stream);
     ++*launches;
   }
   return e;

@@ -11,7 +11,8 @@
 // products run while the three shuffle rounds of v_old are in flight, and the sums of the squares for the l2
 // normalisation depend on the inputs alone.  The output sums of a block are reduced over the eight key parts at
 // once (reduce-scatter, lane p ends with the four column sums of token p).  Tokens past the end are staged as
-// no-ops (k = 0, beta = 0, decay 1).  Works for any K <= 256 and any V (tail columns masked).
+// no-ops (k = 0, beta = 0, decay 1).  Works for any K <= 256 and any V (tail columns masked); writes the state at
+// every chunk start when the caller keeps checkpoints for the backward (p.ckpt, chunk size p.C).
 #pragma once
 
 #include "dr_common.cuh"
@@ -134,6 +135,16 @@ __global__ void __launch_bounds__(kLrThreads) recurrent_kernel(const FwdParams p
       const float4 x4 = *reinterpret_cast<const float4*>(&s_v[buf][tt][cg * kLrCW]);
       const float xv[kLrCW] = {x4.x, x4.y, x4.z, x4.w};
       const float gs = s_sc[buf][tt][0], beta = s_sc[buf][tt][1];
+      if (p.ckpt && t0 + tt < T && (t0 + tt) % p.C == 0) {   // the state at the start of every chunk, for the backward
+        float* ck = p.ckpt + ((int64_t)unit * ((T + p.C - 1) / p.C) + (t0 + tt) / p.C) * K * V;
+#pragma unroll
+        for (int i = 0; i < KP; ++i) {
+          const int kk = part * KP + i;
+#pragma unroll
+          for (int c = 0; c < kLrCW; ++c)
+            if (kk < K && vc0 + c < V) ck[(int64_t)kk * V + vc0 + c] = S[i][c];
+        }
+      }
       float qr[KP], kr[KP];
       float nq = 0.f, nk = 0.f, qk = 0.f;
 #pragma unroll
@@ -213,7 +224,7 @@ __global__ void __launch_bounds__(kLrThreads) recurrent_kernel(const FwdParams p
     {
       constexpr int kShare = kLrParts / TB;
       const int tok = part / kShare;
-      if (part % kShare == 0 && t0 + tok < T) {
+      if (p.o && part % kShare == 0 && t0 + tok < T) {
         const int64_t at = v_base + (int64_t)(t0 + tok) * v_tok + vc0;
 #pragma unroll
         for (int c = 0; c < kLrCW; ++c)

@@ -85,6 +85,8 @@ def test_tcgen05_is_default_for_headline_shape():
     L.gated_delta_rule_chunkwise(cu["q"], cu["k"], cu["v"], cu["g"], cu["beta"])
     assert _lib.last_path() == "chunk_tcgen05"
     L.gated_delta_rule_chunkwise(cu["q"].float(), cu["k"].float(), cu["v"].float(), cu["g"], cu["beta"])
+    assert _lib.last_path() == "recurrent"   # no tensor-core kernel for fp32 storage: the token recurrence
+    L.gated_delta_rule_chunkwise(cu["q"].float(), cu["k"].float(), cu["v"].float(), cu["g"], cu["beta"], path="fp32")
     assert _lib.last_path() == "chunk_fp32"
 
 
