@@ -580,12 +580,13 @@ def run_ours(args, w, rank, world, dev):
                           strong["parity"]["o_rel"] if strong else 0.0, strong["parity"]["state_rel"] if strong else 0.0,
                           -h2d_gbs],
                          dtype=torch.float64, device=dev)
-    per_rank = None
+    per_rank = per_rank_ms = None
     if world > 1:
         gathered = [torch.empty_like(times) for _ in range(world)]
         torch.distributed.all_gather(gathered, times)     # NCCL: every rank's times and parity figures
         allv = torch.stack(gathered)
         per_rank = allv[:, 3:5].tolist()
+        per_rank_ms = (allv[:, 0] / args.steps).tolist()
         times = allv.max(dim=0).values                     # slowest rank, worst error
     total_ms, e2e_ms, strong_ms, p_o, p_s, sp_o, sp_s, neg_h2d = times.tolist()   # max over ranks; slowest copy
     parity["o_rel"] = p_o
@@ -596,7 +597,8 @@ def run_ours(args, w, rank, world, dev):
     ms_per_step = total_ms / args.steps
     res = dict(ms_per_step=ms_per_step, value=world * tokens_per_step / (ms_per_step * 1e-3),
                e2e_value=world * tokens_per_step / (e2e_ms * 1e-3), h2d=h2d, d2h=d2h, launches=launches, path=path,
-               clocks=clocks, kernel_ms=float(np.mean(per_launch_ms)), parity=parity, strong=None, h2d_gbs=-neg_h2d)
+               clocks=clocks, kernel_ms=float(np.mean(per_launch_ms)), parity=parity, strong=None, h2d_gbs=-neg_h2d,
+               per_rank_ms=per_rank_ms)
     if strong:
         res["strong"] = {"global_batch": B, "units_per_rank": strong["units"], "sharded_over": strong["mode"],
                          "ms_per_step": strong_ms, "value": B * w["T"] / (strong_ms * 1e-3), "unit": "tokens/s",
@@ -757,6 +759,8 @@ def main():
                 "cpu_baseline": cpu}
         if res["strong"]:
             line["strong"] = res["strong"]
+        if res.get("per_rank_ms"):
+            line["ms_per_step_per_rank"] = res["per_rank_ms"]   # `ms_per_step` is their maximum
         print(json.dumps(line))
     if world > 1:
         torch.distributed.destroy_process_group()
