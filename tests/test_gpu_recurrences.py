@@ -203,3 +203,12 @@ def test_bad_arguments_raise():
         L.ssd_chunk_scan(torch.zeros(1, 4, 3, 8, device="cuda"), torch.zeros(1, 4, 3, device="cuda"), torch.zeros(3, device="cuda"),
                          torch.zeros(1, 4, 2, 8, device="cuda"), torch.zeros(1, 4, 2, 8, device="cuda"), torch.zeros(3, device="cuda"),
                          n_groups=2)
+
+
+def test_rwkv6_token_major_views_give_the_same_bits():
+    r, k, v, w, u, h0 = (G("rwkv6", x) for x in ("r", "k", "v", "w", "u", "h0"))
+    tr = lambda x: x.transpose(1, 2).contiguous().transpose(1, 2)
+    o, s = L.rwkv6_recurrent(r, k, v, w, u, scale=0.5, initial_state=h0)
+    o2, s2 = L.rwkv6_recurrent(tr(r), tr(k), tr(v), tr(w), u, scale=0.5, initial_state=h0)
+    assert torch.equal(o2, o) and torch.equal(s2, s)
+    assert not o2.is_contiguous() and o2.transpose(1, 2).is_contiguous()   # the output keeps the inputs' storage order
