@@ -63,7 +63,7 @@ typedef enum DrChunkPath {
 /* Values the device status word can take (written by kernels, never trapped). */
 #define DR_DEV_OK 0
 #define DR_DEV_TIMEOUT 1 /* a bounded wait on an mbarrier ran out */
-#define DR_DEV_BOUNDS 2  /* an index check failed (debug builds) */
+#define DR_DEV_BOUNDS 2  /* an index check failed: only the debug build (compiled with -DDR_BOUNDS_CHECK) checks */
 
 typedef struct DrDesc {
   int32_t variant;       /* DrVariant */
@@ -163,7 +163,7 @@ int dr_chunk_fwd_varlen(const DrDesc* desc, const void* q, const void* k, const 
  */
 int dr_recurrent_fwd(const DrDesc* desc, const void* q, const void* k, const void* v,
                      const void* g, const float* beta, const float* h0, void* o, float* hT,
-                     void* stream);
+                     int32_t* status_dev, void* stream);
 
 /*
  * Single-token decode step (desc->T must be 1).  Replaces
@@ -287,13 +287,13 @@ int dr_gated_rmsnorm(const void* o, const void* gate, const float* weight, void*
  */
 int dr_dplr_recurrent(const void* q, const void* k, const void* v, const void* a, const void* b, const void* gk,
                       const float* h0, void* o, float* hT, int B, int H, int T, int K, int V, float scale,
-                      int io_dtype, int layout, void* stream);
+                      int io_dtype, int layout, int32_t* status_dev, void* stream);
 int dr_rwkv6_recurrent(const void* r, const void* k, const void* v, const void* w, const float* u, const float* h0,
                        void* o, float* hT, int B, int H, int T, int K, int V, float scale, int io_dtype, int layout,
-                       void* stream);
+                       int32_t* status_dev, void* stream);
 int dr_ssd_scan(const void* x, const void* dt, const float* A, const void* Bm, const void* Cm, const float* D,
                 const float* dt_bias, const float* h0, void* y, float* hT, int B, int T, int H, int P, int N,
-                int groups, float dt_lo, float dt_hi, int io_dtype, void* stream);
+                int groups, float dt_lo, float dt_hi, int io_dtype, int32_t* status_dev, void* stream);
 
 #ifdef __cplusplus
 }

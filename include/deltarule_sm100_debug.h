@@ -28,6 +28,18 @@ int dr_debug_umma_selftest(const void* a, const void* b, float* d_out, int kd, i
  */
 int dr_debug_wait_timeout(int32_t* status_dev, uint32_t attempts, void* stream);
 
+/*
+ * The index checks of the debug build.  linearnexus_b200/libdeltarule_sm100_bounds.so is this library compiled with
+ * -DDR_BOUNDS_CHECK: the kernels that index global memory by hand (token recurrences and scans, the fp32 chunk kernel,
+ * the plain loads and stores of the fused tcgen05 forward) compare every index with the size of the caller's array
+ * first; an index outside sets DR_DEV_BOUNDS in *status_dev and the access is skipped (no trap, no fault).
+ * dr_debug_bounds_checked() tells which build is loaded (1: checks compiled in).  dr_debug_bounds_probe runs the check
+ * routine itself on (idx, n) without touching memory: *in_range_dev = 1 when 0 <= idx < n, else 0 and -- in the debug
+ * build only -- the status bit.
+ */
+int dr_debug_bounds_checked(void);
+int dr_debug_bounds_probe(int32_t* status_dev, int64_t idx, int64_t n, int32_t* in_range_dev, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -17,6 +17,8 @@ _PKG = Path(__file__).resolve().parent
 _ROOT = _PKG.parent
 # DELTARULE_SM100_LIB points the loader at another build of the same library (profiling builds).
 LIB_PATH = Path(os.environ.get("DELTARULE_SM100_LIB", _PKG / "libdeltarule_sm100.so"))
+# the same sources with the index checks compiled in (-DDR_BOUNDS_CHECK); tests load it through DELTARULE_SM100_LIB
+BOUNDS_LIB_PATH = _PKG / "libdeltarule_sm100_bounds.so"
 _SOURCES = ["dr_api.cu", "dr_scans.cu"]   # translation units, compiled side by side
 _HEADERS = sorted(f.name for f in list((_PKG / "csrc").glob("*.cuh")) + list((_PKG / "csrc").glob("*.h")))
 
@@ -34,7 +36,7 @@ EXPORTS = ["dr_version", "dr_strerror", "dr_last_cuda_error", "dr_launch_count",
            "dr_debug_umma_selftest", "dr_chunk_bwd_static", "dr_chunk_fwd_saving", "dr_chunk_bwd_saved",
            "dr_short_conv_silu", "dr_gate_activations", "dr_gated_rmsnorm", "dr_check_status",
            "dr_last_device_status", "dr_debug_wait_timeout", "dr_chunk_fwd_varlen", "dr_dplr_recurrent",
-           "dr_rwkv6_recurrent", "dr_ssd_scan"]
+           "dr_rwkv6_recurrent", "dr_ssd_scan", "dr_debug_bounds_checked", "dr_debug_bounds_probe"]
 
 
 class DrDesc(ctypes.Structure):
@@ -70,28 +72,32 @@ def nvcc_command(out: Path | None = None, extra: list[str] | None = None) -> lis
     return cmd
 
 
-def library_is_stale() -> bool:
-    if not LIB_PATH.exists():
+def library_is_stale(path: Path | None = None) -> bool:
+    path = path or LIB_PATH
+    if not path.exists():
         return True
-    t = LIB_PATH.stat().st_mtime
+    t = path.stat().st_mtime
     deps = [_PKG / "csrc" / f for f in _SOURCES + _HEADERS] + list((_ROOT / "include").glob("*.h"))
     return any(d.exists() and d.stat().st_mtime > t for d in deps)
 
 
-def build_library(force: bool = False, verbose: bool = False) -> Path:
+def build_library(force: bool = False, verbose: bool = False, bounds: bool = False) -> Path:
     """Compile the CUDA sources for sm_100a into the package directory (cross-compiles without a GPU): one object
-    per translation unit, the units in parallel, then one link."""
-    if force or library_is_stale():
+    per translation unit, the units in parallel, then one link.  ``bounds=True`` builds the debug library with the
+    index checks (BOUNDS_LIB_PATH) instead."""
+    target = BOUNDS_LIB_PATH if bounds else LIB_PATH
+    extra = ["-DDR_BOUNDS_CHECK"] if bounds else []
+    if force or library_is_stale(target):
         import tempfile
         nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
         with tempfile.TemporaryDirectory(prefix="deltarule_sm100_") as tmp:
             objs, procs = [], []
             for src in _SOURCES:
                 obj = Path(tmp) / (Path(src).stem + ".o")
-                cmd = [nvcc] + nvcc_flags() + ["-c", "-o", str(obj), str(_PKG / "csrc" / src)]
+                cmd = [nvcc] + nvcc_flags() + extra + ["-c", "-o", str(obj), str(_PKG / "csrc" / src)]
                 objs.append(obj)
                 procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)))
-            link = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB_PATH)] + [str(o) for o in objs]
+            link = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(target)] + [str(o) for o in objs]
             failed = ""
             for cmd, pr in procs:
                 out, err = pr.communicate()
@@ -108,7 +114,7 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
                 print(res.stdout, res.stderr)
             if res.returncode:
                 raise RuntimeError("nvcc failed linking libdeltarule_sm100.so:\n" + res.stderr)
-    return LIB_PATH
+    return target
 
 
 _lib = None
@@ -144,7 +150,7 @@ def load() -> ctypes.CDLL:
         lib.dr_chunk_fwd_varlen.argtypes = [dp, vp, vp, vp, vp, fp, ctypes.POINTER(ctypes.c_int32), ctypes.c_int32, fp, vp, fp,
                                             vp, ctypes.c_size_t, ip, vp]
         lib.dr_recurrent_fwd.restype = ctypes.c_int
-        lib.dr_recurrent_fwd.argtypes = [dp, vp, vp, vp, vp, fp, fp, vp, fp, vp]
+        lib.dr_recurrent_fwd.argtypes = [dp, vp, vp, vp, vp, fp, fp, vp, fp, ip, vp]
         lib.dr_step.restype = ctypes.c_int
         lib.dr_step.argtypes = [dp, vp, vp, vp, vp, fp, fp, fp, vp, ip, vp]
         lib.dr_check_status.restype = ctypes.c_int
@@ -170,11 +176,14 @@ def load() -> ctypes.CDLL:
         lib.dr_gated_rmsnorm.restype = ctypes.c_int
         lib.dr_gated_rmsnorm.argtypes = [vp, vp, fp, vp, ci, ci, ci, ci, ci, ci, ci, ci, cf, vp]
         lib.dr_dplr_recurrent.restype = ctypes.c_int
-        lib.dr_dplr_recurrent.argtypes = [vp, vp, vp, vp, vp, vp, fp, vp, fp, ci, ci, ci, ci, ci, cf, ci, ci, vp]
+        lib.dr_dplr_recurrent.argtypes = [vp, vp, vp, vp, vp, vp, fp, vp, fp, ci, ci, ci, ci, ci, cf, ci, ci, ip, vp]
         lib.dr_rwkv6_recurrent.restype = ctypes.c_int
-        lib.dr_rwkv6_recurrent.argtypes = [vp, vp, vp, vp, fp, fp, vp, fp, ci, ci, ci, ci, ci, cf, ci, ci, vp]
+        lib.dr_rwkv6_recurrent.argtypes = [vp, vp, vp, vp, fp, fp, vp, fp, ci, ci, ci, ci, ci, cf, ci, ci, ip, vp]
         lib.dr_ssd_scan.restype = ctypes.c_int
-        lib.dr_ssd_scan.argtypes = [vp, vp, fp, vp, vp, fp, fp, fp, vp, fp, ci, ci, ci, ci, ci, ci, cf, cf, ci, vp]
+        lib.dr_ssd_scan.argtypes = [vp, vp, fp, vp, vp, fp, fp, fp, vp, fp, ci, ci, ci, ci, ci, ci, cf, cf, ci, ip, vp]
+        lib.dr_debug_bounds_checked.restype = ctypes.c_int
+        lib.dr_debug_bounds_probe.restype = ctypes.c_int
+        lib.dr_debug_bounds_probe.argtypes = [ip, ctypes.c_int64, ctypes.c_int64, ip, vp]
         lib.dr_debug_umma_selftest.restype = ctypes.c_int
         lib.dr_debug_umma_selftest.argtypes = [vp, vp, fp, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ip, vp]
         _lib = lib

@@ -67,6 +67,7 @@ dr::FwdParams make_fwd(const DrDesc* d, const void* q, const void* k, const void
   p.K = d->K; p.V = d->V; p.C = d->chunk;
   p.variant = d->variant; p.qkv_dt = d->qkv_dtype; p.g_dt = d->g_dtype; p.out_dt = d->out_dtype;
   p.l2norm = d->use_qk_l2norm; p.scale = d->scale;
+  p.set_extents();
   return p;
 }
 
@@ -121,9 +122,10 @@ int resolve_chunk_path(const DrDesc* d) {
 bool fp32_chunk_eligible(const DrDesc* d) { return d->chunk <= 64 && d->K <= 128; }
 
 // A [B,H,T,D] / [B,T,H,D] activation as the strided per-token vector the scans of dr_linrec.cuh read.
-dr::LrVec lr_vec(const void* p, int H, int T, int D, int dt, int bthd, int hdiv = 1) {
+dr::LrVec lr_vec(const void* p, int B, int H, int T, int D, int dt, int bthd, int hdiv = 1) {
   dr::LrVec v;
   v.p = p; v.dt = dt; v.hdiv = hdiv;
+  v.n = (int64_t)B * H * T * D;
   if (bthd) { v.sb = (int64_t)T * H * D; v.sh = D; v.st = (int64_t)H * D; }
   else { v.sb = (int64_t)H * T * D; v.sh = (int64_t)T * D; v.st = D; }
   return v;
@@ -135,6 +137,10 @@ int validate_linrec(int B, int H, int T, int K, int V, int io_dtype) {
   if (B < 1 || H < 1 || T < 1 || K < 1 || K > 256 || V < 1 || V > 256) return DR_ERR_SHAPE;
   if ((int64_t)B * H * ((V + 63) / 64) >= ((int64_t)1 << 31)) return DR_ERR_SHAPE;
   return DR_OK;
+}
+
+__global__ void bounds_probe_kernel(int32_t* status, int64_t idx, int64_t n, int32_t* in_range) {
+  *in_range = dr::in_bounds(status, idx, n) ? 1 : 0;
 }
 
 }  // namespace
@@ -246,12 +252,12 @@ int dr_chunk_fwd_varlen(const DrDesc* d, const void* q, const void* k, const voi
 }
 
 int dr_recurrent_fwd(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
-                     const float* beta, const float* h0, void* o, float* hT, void* stream) {
+                     const float* beta, const float* h0, void* o, float* hT, int32_t* status_dev, void* stream) {
   int s = validate_common(d, false);
   if (s != DR_OK) return s;
   s = validate_fwd_ptrs(d, q, k, v, g, beta, h0, o, hT);
   if (s != DR_OK) return s;
-  const dr::FwdParams p = make_fwd(d, q, k, v, g, beta, h0, o, hT, nullptr);
+  const dr::FwdParams p = make_fwd(d, q, k, v, g, beta, h0, o, hT, status_dev);
   tl_path = "recurrent";
   g_launches.fetch_add(1);
   return check_cuda(dr::launch_recurrent(p, reinterpret_cast<cudaStream_t>(stream)));
@@ -506,7 +512,7 @@ int dr_gated_rmsnorm(const void* o, const void* gate, const float* weight, void*
 
 int dr_dplr_recurrent(const void* q, const void* k, const void* v, const void* a, const void* b, const void* gk,
                       const float* h0, void* o, float* hT, int B, int H, int T, int K, int V, float scale,
-                      int io_dtype, int layout, void* stream) {
+                      int io_dtype, int layout, int32_t* status_dev, void* stream) {
   if (!q || !k || !v || !a || !b || !gk || !o) return DR_ERR_NULL;
   if (layout != DR_LAYOUT_BHTD && layout != DR_LAYOUT_BTHD) return DR_ERR_SHAPE;
   int s = validate_linrec(B, H, T, K, V, io_dtype);
@@ -515,13 +521,14 @@ int dr_dplr_recurrent(const void* q, const void* k, const void* v, const void* a
     if (!elem_aligned(ptr, io_dtype)) return DR_ERR_ALIGN;
   const int bthd = layout == DR_LAYOUT_BTHD;
   dr::LinRecParams p{};
-  p.q = lr_vec(q, H, T, K, io_dtype, bthd); p.k = lr_vec(k, H, T, K, io_dtype, bthd);
-  p.w = lr_vec(gk, H, T, K, io_dtype, bthd); p.a = lr_vec(a, H, T, K, io_dtype, bthd);
-  p.b = lr_vec(b, H, T, K, io_dtype, bthd); p.v = lr_vec(v, H, T, V, io_dtype, bthd);
-  const dr::LrVec ov = lr_vec(o, H, T, V, io_dtype, bthd);
+  p.q = lr_vec(q, B, H, T, K, io_dtype, bthd); p.k = lr_vec(k, B, H, T, K, io_dtype, bthd);
+  p.w = lr_vec(gk, B, H, T, K, io_dtype, bthd); p.a = lr_vec(a, B, H, T, K, io_dtype, bthd);
+  p.b = lr_vec(b, B, H, T, K, io_dtype, bthd); p.v = lr_vec(v, B, H, T, V, io_dtype, bthd);
+  const dr::LrVec ov = lr_vec(o, B, H, T, V, io_dtype, bthd);
   p.o = o; p.o_sb = ov.sb; p.o_sh = ov.sh; p.o_st = ov.st; p.o_dt = io_dtype;
   p.h0 = h0; p.hT = hT; p.s_k = V; p.s_v = 1;
   p.B = B; p.H = H; p.T = T; p.K = K; p.V = V; p.scale = scale;
+  p.status = status_dev; p.n_o = ov.n; p.n_state = (int64_t)B * H * K * V;
   tl_path = "dplr_recurrent";
   cudaError_t e = dr::launch_linrec(dr::LR_DPLR, io_dtype == DR_BF16, p, reinterpret_cast<cudaStream_t>(stream));
   g_launches.fetch_add(1);
@@ -530,7 +537,7 @@ int dr_dplr_recurrent(const void* q, const void* k, const void* v, const void* a
 
 int dr_rwkv6_recurrent(const void* r, const void* k, const void* v, const void* w, const float* u, const float* h0,
                        void* o, float* hT, int B, int H, int T, int K, int V, float scale, int io_dtype, int layout,
-                       void* stream) {
+                       int32_t* status_dev, void* stream) {
   if (!r || !k || !v || !w || !u || !o) return DR_ERR_NULL;
   if (layout != DR_LAYOUT_BHTD && layout != DR_LAYOUT_BTHD) return DR_ERR_SHAPE;
   int s = validate_linrec(B, H, T, K, V, io_dtype);
@@ -539,13 +546,14 @@ int dr_rwkv6_recurrent(const void* r, const void* k, const void* v, const void* 
     if (!elem_aligned(ptr, io_dtype)) return DR_ERR_ALIGN;
   const int bthd = layout == DR_LAYOUT_BTHD;
   dr::LinRecParams p{};
-  p.q = lr_vec(r, H, T, K, io_dtype, bthd); p.k = lr_vec(k, H, T, K, io_dtype, bthd);
-  p.w = lr_vec(w, H, T, K, io_dtype, bthd); p.v = lr_vec(v, H, T, V, io_dtype, bthd);
+  p.q = lr_vec(r, B, H, T, K, io_dtype, bthd); p.k = lr_vec(k, B, H, T, K, io_dtype, bthd);
+  p.w = lr_vec(w, B, H, T, K, io_dtype, bthd); p.v = lr_vec(v, B, H, T, V, io_dtype, bthd);
   p.a = p.q; p.b = p.q;
-  const dr::LrVec ov = lr_vec(o, H, T, V, io_dtype, bthd);
+  const dr::LrVec ov = lr_vec(o, B, H, T, V, io_dtype, bthd);
   p.o = o; p.o_sb = ov.sb; p.o_sh = ov.sh; p.o_st = ov.st; p.o_dt = io_dtype;
   p.u = u; p.h0 = h0; p.hT = hT; p.s_k = V; p.s_v = 1;
   p.B = B; p.H = H; p.T = T; p.K = K; p.V = V; p.scale = scale;
+  p.status = status_dev; p.n_o = ov.n; p.n_state = (int64_t)B * H * K * V;
   tl_path = "rwkv6_recurrent";
   cudaError_t e = dr::launch_linrec(dr::LR_RWKV6, io_dtype == DR_BF16, p, reinterpret_cast<cudaStream_t>(stream));
   g_launches.fetch_add(1);
@@ -554,7 +562,7 @@ int dr_rwkv6_recurrent(const void* r, const void* k, const void* v, const void* 
 
 int dr_ssd_scan(const void* x, const void* dt, const float* A, const void* Bm, const void* Cm, const float* D,
                 const float* dt_bias, const float* h0, void* y, float* hT, int B, int T, int H, int P, int N,
-                int groups, float dt_lo, float dt_hi, int io_dtype, void* stream) {
+                int groups, float dt_lo, float dt_hi, int io_dtype, int32_t* status_dev, void* stream) {
   if (!x || !dt || !A || !Bm || !Cm || !D || !y) return DR_ERR_NULL;
   int s = validate_linrec(B, H, T, N, P, io_dtype);
   if (s != DR_OK) return s;
@@ -564,20 +572,36 @@ int dr_ssd_scan(const void* x, const void* dt, const float* A, const void* Bm, c
   if (!elem_aligned(dt, DR_F32)) return DR_ERR_ALIGN;
   dr::LinRecParams p{};
   // key axis = the N state channels (B writes, C reads), value axis = the P channels of the head
-  p.q = lr_vec(Cm, groups, T, N, io_dtype, 1, H / groups);
-  p.k = lr_vec(Bm, groups, T, N, io_dtype, 1, H / groups);
+  p.q = lr_vec(Cm, B, groups, T, N, io_dtype, 1, H / groups);
+  p.k = lr_vec(Bm, B, groups, T, N, io_dtype, 1, H / groups);
   p.w = p.q; p.a = p.q; p.b = p.q;
-  p.v = lr_vec(x, H, T, P, io_dtype, 1);
-  p.dt = lr_vec(dt, H, T, 1, DR_F32, 1);
-  const dr::LrVec ov = lr_vec(y, H, T, P, io_dtype, 1);
+  p.v = lr_vec(x, B, H, T, P, io_dtype, 1);
+  p.dt = lr_vec(dt, B, H, T, 1, DR_F32, 1);
+  const dr::LrVec ov = lr_vec(y, B, H, T, P, io_dtype, 1);
   p.o = y; p.o_sb = ov.sb; p.o_sh = ov.sh; p.o_st = ov.st; p.o_dt = io_dtype;
   p.A = A; p.D = D; p.dt_bias = dt_bias; p.h0 = h0; p.hT = hT;
   p.s_k = 1; p.s_v = N;   // state stored [P, N]
   p.B = B; p.H = H; p.T = T; p.K = N; p.V = P; p.scale = 1.f; p.dt_lo = dt_lo; p.dt_hi = dt_hi;
+  p.status = status_dev; p.n_o = ov.n; p.n_state = (int64_t)B * H * P * N;
   tl_path = "ssd_scan";
   cudaError_t e = dr::launch_linrec(dr::LR_SSD, io_dtype == DR_BF16, p, reinterpret_cast<cudaStream_t>(stream));
   g_launches.fetch_add(1);
   return check_cuda(e);
+}
+
+int dr_debug_bounds_checked(void) {
+#ifdef DR_BOUNDS_CHECK
+  return 1;
+#else
+  return 0;
+#endif
+}
+
+int dr_debug_bounds_probe(int32_t* status_dev, int64_t idx, int64_t n, int32_t* in_range_dev, void* stream) {
+  if (!status_dev || !in_range_dev) return DR_ERR_NULL;
+  bounds_probe_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(status_dev, idx, n, in_range_dev);
+  g_launches.fetch_add(1);
+  return check_cuda(cudaGetLastError());
 }
 
 }  // extern "C"

@@ -1305,6 +1305,7 @@ inline cudaError_t launch_bwd_forward(const DrDesc* d, const void* q, const void
   f.K = K; f.V = V; f.C = C;
   f.variant = d->variant; f.qkv_dt = d->qkv_dtype; f.g_dt = d->g_dtype; f.out_dt = o ? d->out_dtype : d->qkv_dtype;
   f.l2norm = d->use_qk_l2norm; f.scale = d->scale;
+  f.set_extents();
   const bool tc_shape = sm100::kAvailable && K == 128 && V == 128 && C == 64 && d->qkv_dtype == DR_BF16;
   // the tensor-core forwards write the same checkpoints when the shape qualifies
   const bool fused = tc_shape && (d->variant == DR_DELTA || (d->variant == DR_GATED && d->g_dtype == DR_F32)) &&

@@ -78,7 +78,8 @@ __global__ void __launch_bounds__(kCfThreads) chunk_fp32_kernel(const FwdParams 
 
   for (int i = tid; i < K * kCfCols; i += kCfThreads) {
     const int kk = i / kCfCols, vv = i % kCfCols;
-    sS[kk * ldv + vv] = (p.h0 && v0 + vv < V) ? p.h0[((int64_t)unit * K + kk) * V + v0 + vv] : 0.f;
+    sS[kk * ldv + vv] = (p.h0 && v0 + vv < V && in_bounds(p.status, ((int64_t)unit * K + kk) * V + v0 + vv, p.n_state))
+                            ? p.h0[((int64_t)unit * K + kk) * V + v0 + vv] : 0.f;
   }
 
   const int nchunks = (T + C - 1) / C;
@@ -90,7 +91,8 @@ __global__ void __launch_bounds__(kCfThreads) chunk_fp32_kernel(const FwdParams 
       float* ck = p.ckpt + ((int64_t)unit * nchunks + n) * K * V;
       for (int i = tid; i < K * kCfCols; i += kCfThreads) {
         const int kk = i / kCfCols, vv = i % kCfCols;
-        if (v0 + vv < V) ck[(int64_t)kk * V + v0 + vv] = sS[kk * ldv + vv];
+        if (v0 + vv < V && in_bounds(p.status, (ck - p.ckpt) + (int64_t)kk * V + v0 + vv, p.n_ckpt))
+          ck[(int64_t)kk * V + v0 + vv] = sS[kk * ldv + vv];
       }
     }
     // ---- (1) stage q, k (normalised, q scaled), g, beta, beta*v -------------------------
@@ -100,9 +102,12 @@ __global__ void __launch_bounds__(kCfThreads) chunk_fp32_kernel(const FwdParams 
       for (int i = lane; i < K; i += 32) {
         float qv = 0.f, kv = 0.f, gv = 0.f;
         if (live) {
-          qv = ld_elem(p.q, qk_base + (t0 + c) * qk_tok + i, p.qkv_dt);
-          kv = ld_elem(p.k, qk_base + (t0 + c) * qk_tok + i, p.qkv_dt);
-          if (kda) gv = ld_elem(p.g, gk_base + (t0 + c) * gk_tok + i, p.g_dt);
+          if (in_bounds(p.status, qk_base + (t0 + c) * qk_tok + i, p.n_qk)) {
+            qv = ld_elem(p.q, qk_base + (t0 + c) * qk_tok + i, p.qkv_dt);
+            kv = ld_elem(p.k, qk_base + (t0 + c) * qk_tok + i, p.qkv_dt);
+          }
+          if (kda && in_bounds(p.status, gk_base + (t0 + c) * gk_tok + i, p.n_gk))
+            gv = ld_elem(p.g, gk_base + (t0 + c) * gk_tok + i, p.g_dt);
         }
         sQ[c * ldk + i] = qv;
         sK[c * ldk + i] = kv;
@@ -123,15 +128,17 @@ __global__ void __launch_bounds__(kCfThreads) chunk_fp32_kernel(const FwdParams 
         sK[c * ldk + i] *= kmul;
       }
       if (lane == 0) {
-        sBeta[c] = live ? p.beta[s_base + (t0 + c) * s_tok] : 0.f;
-        sGs[c] = (live && gated) ? ld_elem(p.g, s_base + (t0 + c) * s_tok, p.g_dt) : 0.f;
+        const bool there = live && in_bounds(p.status, s_base + (t0 + c) * s_tok, p.n_tok);
+        sBeta[c] = there ? p.beta[s_base + (t0 + c) * s_tok] : 0.f;
+        sGs[c] = (there && gated) ? ld_elem(p.g, s_base + (t0 + c) * s_tok, p.g_dt) : 0.f;
       }
     }
     __syncthreads();
     for (int i = tid; i < C * kCfCols; i += kCfThreads) {
       const int c = i / kCfCols, vv = i % kCfCols;
       float x = 0.f;
-      if (c < rows && v0 + vv < V) x = ld_elem(p.v, v_base + (t0 + c) * v_tok + v0 + vv, p.qkv_dt);
+      if (c < rows && v0 + vv < V && in_bounds(p.status, v_base + (t0 + c) * v_tok + v0 + vv, p.n_v))
+        x = ld_elem(p.v, v_base + (t0 + c) * v_tok + v0 + vv, p.qkv_dt);
       sU[c * ldv + vv] = sBeta[c] * x;
     }
     // cumulative sums of the log decay along the chunk
@@ -252,7 +259,8 @@ __global__ void __launch_bounds__(kCfThreads) chunk_fp32_kernel(const FwdParams 
       if (c < rows) {
         float acc = oacc[r];
         for (int j = 0; j <= c; ++j) acc += sAqk[c * lda + j] * sVn[j * ldv + lane];
-        if (p.o && v0 + lane < V) st_elem(p.o, v_base + (t0 + c) * v_tok + v0 + lane, p.out_dt, acc);
+        if (p.o && v0 + lane < V && in_bounds(p.status, v_base + (t0 + c) * v_tok + v0 + lane, p.n_v))
+          st_elem(p.o, v_base + (t0 + c) * v_tok + v0 + lane, p.out_dt, acc);
       }
     }
     // ---- (7) S <- e^{G_last} S + K~^T V_new -------------------------------------------------
@@ -277,7 +285,8 @@ __global__ void __launch_bounds__(kCfThreads) chunk_fp32_kernel(const FwdParams 
   if (p.hT) {
     for (int i = tid; i < K * kCfCols; i += kCfThreads) {
       const int kk = i / kCfCols, vv = i % kCfCols;
-      if (v0 + vv < V) p.hT[((int64_t)unit * K + kk) * V + v0 + vv] = sS[kk * ldv + vv];
+      if (v0 + vv < V && in_bounds(p.status, ((int64_t)unit * K + kk) * V + v0 + vv, p.n_state))
+        p.hT[((int64_t)unit * K + kk) * V + v0 + vv] = sS[kk * ldv + vv];
     }
   }
 }

@@ -427,7 +427,8 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         const int c0 = 32 * cc;
         uint32_t r[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) r[j] = h0 ? __float_as_uint(h0[(c0 + j) * kD + gt]) : 0u;
+        for (int j = 0; j < 32; ++j)
+          r[j] = (h0 && in_bounds(p.status, (h0 - p.h0) + (c0 + j) * kD + gt, p.n_state)) ? __float_as_uint(h0[(c0 + j) * kD + gt]) : 0u;
         tc::tmem_st32(tbase + TM_S + lane_addr + c0, r);
       }
       tc::tc_wait_st();
@@ -460,7 +461,8 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
           if (p.ckpt) {  // state at the start of this chunk, [K][V] row-major, for the backward
             float* ck = p.ckpt + ((int64_t)unit * nchunks + n) * kD * kD;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) ck[(c0 + j) * kD + gt] = __uint_as_float(r[j]);
+            for (int j = 0; j < 16; ++j)
+              if (in_bounds(p.status, (ck - p.ckpt) + (c0 + j) * kD + gt, p.n_ckpt)) ck[(c0 + j) * kD + gt] = __uint_as_float(r[j]);
           }
 #pragma unroll
           for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * gl);
@@ -534,7 +536,8 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         tc::tmem_ld32(tbase + TM_S + lane_addr + c0, r);
         tc::tc_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) hT[(c0 + j) * kD + gt] = __uint_as_float(r[j]);
+        for (int j = 0; j < 32; ++j)
+          if (in_bounds(p.status, (hT - p.hT) + (c0 + j) * kD + gt, p.n_state)) hT[(c0 + j) * kD + gt] = __uint_as_float(r[j]);
       }
     }
     wait_bar(&ctl.bar2, (nchunks - 1) & 1);   // every product has completed before tensor memory is released
@@ -616,7 +619,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
               const uint32_t other = __shfl_xor_sync(0xffffffffu, mine, 1);   // the same of column v ^ 1
               // even lane: token j, columns (v, v+1); odd lane: token j+1, columns (v-1, v)
               const uint32_t word = odd ? __byte_perm(other, mine, 0x7632) : __byte_perm(mine, other, 0x5410);
-              if (c0 + j + (odd ? 1 : 0) < rowsm)
+              if (c0 + j + (odd ? 1 : 0) < rowsm && in_bounds(p.status, (orow - go) + (int64_t)(c0 + j) * vo_tok + 1, p.n_v))
                 *reinterpret_cast<uint32_t*>(orow + (int64_t)(c0 + j) * vo_tok) = word;
             }
           }

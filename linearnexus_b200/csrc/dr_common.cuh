@@ -39,6 +39,19 @@ __device__ __forceinline__ void st_elem(void* p, int64_t i, int dt, float x) {
     reinterpret_cast<float*>(p)[i] = x;
 }
 
+// Index checks of the debug build (-DDR_BOUNDS_CHECK, linearnexus_b200/libdeltarule_sm100_bounds.so): the kernels that
+// index global memory by hand ask in_bounds() before an access; an index outside [0, n) sets DR_DEV_BOUNDS in the
+// status word and the access is skipped -- never a trap, never a fault.  The release build compiles the checks away.
+#ifdef DR_BOUNDS_CHECK
+__device__ __forceinline__ bool in_bounds(int32_t* status, int64_t i, int64_t n) {
+  if (i >= 0 && i < n) return true;
+  if (status) atomicOr(status, DR_DEV_BOUNDS);
+  return false;
+}
+#else
+__device__ __forceinline__ bool in_bounds(int32_t*, int64_t, int64_t) { return true; }
+#endif
+
 __device__ __forceinline__ float warp_sum(float x) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
@@ -61,6 +74,17 @@ struct FwdParams {
   int K, V, C;
   int variant, qkv_dt, g_dt, out_dt, l2norm;
   float scale;
+  // element counts of the caller's arrays (what the index checks of the debug build compare against)
+  int64_t n_qk, n_v, n_gk, n_tok, n_state, n_ckpt;
+  __host__ void set_extents() {
+    const int64_t bh = (int64_t)map.B * map.H, bhq = (int64_t)map.B * map.Hq;
+    n_qk = bhq * map.T * K;
+    n_v = bh * map.T * V;
+    n_gk = bh * map.T * K;
+    n_tok = bh * map.T;
+    n_state = bh * K * V;
+    n_ckpt = C > 0 ? bh * ((map.T + C - 1) / C) * K * V : 0;
+  }
 };
 
 }  // namespace dr

@@ -100,7 +100,8 @@ __global__ void __launch_bounds__(kLrThreads) linrec_kernel(const LinRecParams p
     const int kk = part * KP + i;
 #pragma unroll
     for (int c = 0; c < kLrCW; ++c)
-      S[i][c] = (p.h0 && vc0 + c < V && kk < K) ? p.h0[s_unit + kk * p.s_k + (vc0 + c) * p.s_v] : 0.f;
+      S[i][c] = (p.h0 && vc0 + c < V && kk < K && in_bounds(p.status, s_unit + kk * p.s_k + (vc0 + c) * p.s_v, p.n_state))
+                    ? p.h0[s_unit + kk * p.s_k + (vc0 + c) * p.s_v] : 0.f;
     if (KIND == LR_RWKV6) ur[i] = kk < K ? p.u[(int64_t)h * K + kk] : 0.f;
   }
 
@@ -112,17 +113,23 @@ __global__ void __launch_bounds__(kLrThreads) linrec_kernel(const LinRecParams p
       const int tok = e / KA, i = e % KA;
       const bool ok = i < K && t0 + tok < T;
 #pragma unroll
-      for (int j = 0; j < NV; ++j)
-        f[j][s] = ld_raw<BF>(vecs[j]->p, base[j] + (int64_t)(t0 + tok) * vecs[j]->st + i, ok);
+      for (int j = 0; j < NV; ++j) {
+        const int64_t at = base[j] + (int64_t)(t0 + tok) * vecs[j]->st + i;
+        f[j][s] = ld_raw<BF>(vecs[j]->p, at, ok && in_bounds(p.status, at, vecs[j]->n));
+      }
     }
 #pragma unroll
     for (int s = 0; s < NX; ++s) {
       const int e = tid + s * kLrThreads;
       const int tok = e / kLrCols, c = e % kLrCols;
       const bool ok = e < TB * kLrCols && v0 + c < V && t0 + tok < T;
-      fx[s] = ld_raw<BF>(p.v.p, v_base + (int64_t)(t0 + tok) * p.v.st + v0 + c, ok);
+      const int64_t va = v_base + (int64_t)(t0 + tok) * p.v.st + v0 + c;
+      fx[s] = ld_raw<BF>(p.v.p, va, ok && in_bounds(p.status, va, p.v.n));
     }
-    if (KIND == LR_SSD) fdt = ld_raw<false>(p.dt.p, dt_base + (int64_t)(t0 + tid) * p.dt.st, tid < TB && t0 + tid < T);   // dt is float32
+    if (KIND == LR_SSD) {   // dt is float32
+      const int64_t da = dt_base + (int64_t)(t0 + tid) * p.dt.st;
+      fdt = ld_raw<false>(p.dt.p, da, tid < TB && t0 + tid < T && in_bounds(p.status, da, p.dt.n));
+    }
   };
   auto commit = [&](int buf, int t0) {
 #pragma unroll
@@ -290,7 +297,7 @@ __global__ void __launch_bounds__(kLrThreads) linrec_kernel(const LinRecParams p
         const int64_t at = o_base + (int64_t)(t0 + tok) * p.o_st + vc0;
 #pragma unroll
         for (int c = 0; c < kLrCW; ++c)
-          if (vc0 + c < V) st_elem(p.o, at + c, p.o_dt, ob[c]);
+          if (vc0 + c < V && in_bounds(p.status, at + c, p.n_o)) st_elem(p.o, at + c, p.o_dt, ob[c]);
       }
     }
     if (t0 + TB < T) commit(buf ^ 1, t0 + TB);
@@ -302,7 +309,8 @@ __global__ void __launch_bounds__(kLrThreads) linrec_kernel(const LinRecParams p
       const int kk = part * KP + i;
 #pragma unroll
       for (int c = 0; c < kLrCW; ++c)
-        if (kk < K && vc0 + c < V) p.hT[s_unit + kk * p.s_k + (vc0 + c) * p.s_v] = S[i][c];
+        if (kk < K && vc0 + c < V && in_bounds(p.status, s_unit + kk * p.s_k + (vc0 + c) * p.s_v, p.n_state))
+          p.hT[s_unit + kk * p.s_k + (vc0 + c) * p.s_v] = S[i][c];
     }
   }
 }

@@ -74,7 +74,8 @@ __global__ void __launch_bounds__(kLrThreads) recurrent_kernel(const FwdParams p
     const int kk = part * KP + i;
 #pragma unroll
     for (int c = 0; c < kLrCW; ++c)
-      S[i][c] = (p.h0 && vc0 + c < V && kk < K) ? p.h0[s_unit + (int64_t)kk * V + vc0 + c] : 0.f;
+      S[i][c] = (p.h0 && vc0 + c < V && kk < K && in_bounds(p.status, s_unit + (int64_t)kk * V + vc0 + c, p.n_state))
+                    ? p.h0[s_unit + (int64_t)kk * V + vc0 + c] : 0.f;
   }
 
   uint32_t f16[NV][NS], f32[NV][NS], x16[NX], x32[NX], g16 = 0, g32 = 0, braw = 0;
@@ -83,25 +84,32 @@ __global__ void __launch_bounds__(kLrThreads) recurrent_kernel(const FwdParams p
     for (int s = 0; s < NS; ++s) {
       const int e = tid + s * kLrThreads;
       const int tok = e / KA, i = e % KA;
-      const bool ok = i < K && t0 + tok < T;
+      const bool live = i < K && t0 + tok < T;
       const int64_t at = qk_base + (int64_t)(t0 + tok) * qk_tok + i;
+      const bool ok = live && in_bounds(p.status, at, p.n_qk);
       ld_raw_either(p.q, at, p.qkv_dt, ok, f16[0][s], f32[0][s]);
       ld_raw_either(p.k, at, p.qkv_dt, ok, f16[1][s], f32[1][s]);
-      if (VARIANT == DR_KDA) ld_raw_either(p.g, gk_base + (int64_t)(t0 + tok) * gk_tok + i, p.g_dt, ok, f16[2][s], f32[2][s]);
+      if (VARIANT == DR_KDA) {
+        const int64_t ga = gk_base + (int64_t)(t0 + tok) * gk_tok + i;
+        ld_raw_either(p.g, ga, p.g_dt, live && in_bounds(p.status, ga, p.n_gk), f16[2][s], f32[2][s]);
+      }
     }
 #pragma unroll
     for (int s = 0; s < NX; ++s) {
       const int e = tid + s * kLrThreads;
       const int tok = e / kLrCols, c = e % kLrCols;
-      const bool ok = e < TB * kLrCols && v0 + c < V && t0 + tok < T;
-      ld_raw_either(p.v, v_base + (int64_t)(t0 + tok) * v_tok + v0 + c, p.qkv_dt, ok, x16[s], x32[s]);
+      const int64_t va = v_base + (int64_t)(t0 + tok) * v_tok + v0 + c;
+      const bool ok = e < TB * kLrCols && v0 + c < V && t0 + tok < T && in_bounds(p.status, va, p.n_v);
+      ld_raw_either(p.v, va, p.qkv_dt, ok, x16[s], x32[s]);
     }
     // threads 0..TB-1: beta of token tid; threads TB..2TB-1: the scalar log decay of token tid - TB
     if (tid < TB) {
       uint32_t unused;
-      ld_raw_either(p.beta, s_base + (int64_t)(t0 + tid) * s_tok, DR_F32, t0 + tid < T, unused, braw);
+      const int64_t ba = s_base + (int64_t)(t0 + tid) * s_tok;
+      ld_raw_either(p.beta, ba, DR_F32, t0 + tid < T && in_bounds(p.status, ba, p.n_tok), unused, braw);
     } else if (VARIANT == DR_GATED && tid < 2 * TB) {
-      ld_raw_either(p.g, s_base + (int64_t)(t0 + tid - TB) * s_tok, p.g_dt, t0 + tid - TB < T, g16, g32);
+      const int64_t ga = s_base + (int64_t)(t0 + tid - TB) * s_tok;
+      ld_raw_either(p.g, ga, p.g_dt, t0 + tid - TB < T && in_bounds(p.status, ga, p.n_tok), g16, g32);
     }
   };
   auto commit = [&](int buf) {
@@ -142,7 +150,8 @@ __global__ void __launch_bounds__(kLrThreads) recurrent_kernel(const FwdParams p
           const int kk = part * KP + i;
 #pragma unroll
           for (int c = 0; c < kLrCW; ++c)
-            if (kk < K && vc0 + c < V) ck[(int64_t)kk * V + vc0 + c] = S[i][c];
+            if (kk < K && vc0 + c < V && in_bounds(p.status, (ck - p.ckpt) + (int64_t)kk * V + vc0 + c, p.n_ckpt))
+              ck[(int64_t)kk * V + vc0 + c] = S[i][c];
         }
       }
       float qr[KP], kr[KP];
@@ -228,7 +237,7 @@ __global__ void __launch_bounds__(kLrThreads) recurrent_kernel(const FwdParams p
         const int64_t at = v_base + (int64_t)(t0 + tok) * v_tok + vc0;
 #pragma unroll
         for (int c = 0; c < kLrCW; ++c)
-          if (vc0 + c < V) st_elem(p.o, at + c, p.out_dt, ob[c]);
+          if (vc0 + c < V && in_bounds(p.status, at + c, p.n_v)) st_elem(p.o, at + c, p.out_dt, ob[c]);
       }
     }
     if (t0 + TB < T) commit(buf ^ 1);
@@ -240,7 +249,8 @@ __global__ void __launch_bounds__(kLrThreads) recurrent_kernel(const FwdParams p
       const int kk = part * KP + i;
 #pragma unroll
       for (int c = 0; c < kLrCW; ++c)
-        if (kk < K && vc0 + c < V) p.hT[s_unit + (int64_t)kk * V + vc0 + c] = S[i][c];
+        if (kk < K && vc0 + c < V && in_bounds(p.status, s_unit + (int64_t)kk * V + vc0 + c, p.n_state))
+          p.hT[s_unit + (int64_t)kk * V + vc0 + c] = S[i][c];
     }
   }
 }

@@ -14,6 +14,7 @@ struct LrVec {
   int64_t sb, sh, st;  // element strides over batch, head, token
   int dt;              // DrDtype
   int hdiv;            // head h reads row h / hdiv (grouped B and C of the SSD)
+  int64_t n;           // elements in the array (index checks of the debug build)
   __device__ __forceinline__ int64_t at(int b, int h, int t) const {
     return (int64_t)b * sb + (int64_t)(h / hdiv) * sh + (int64_t)t * st;
   }
@@ -33,6 +34,8 @@ struct LinRecParams {
   const float* h0;       // null: zero state
   float* hT;             // null: not wanted (may alias h0: every thread reads its entries before it writes them)
   int64_t s_k, s_v;      // state entry (key kk, value vv) of unit n at n*K*V + kk*s_k + vv*s_v
+  int32_t* status;       // device status word or null
+  int64_t n_o, n_state;  // elements of o and of each state array
   int B, H, T, K, V;
   float scale, dt_lo, dt_hi;
 };

@@ -156,7 +156,7 @@ def _seq_forward(kind, variant, q, k, v, g, beta, initial_state, scale, chunk_si
                                   _stream(dev))
         else:
             st = lib.dr_recurrent_fwd(ctypes.byref(d), _ptr(qn), _ptr(kn), _ptr(vn), _ptr(gn), _ptr(bn),
-                                      _ptr(h0), _ptr(o), _ptr(hT), _stream(dev))
+                                      _ptr(h0), _ptr(o), _ptr(hT), _ptr(_status(dev)), _stream(dev))
     if st == -7:
         raise ValueError(f"chunk_size (BT={chunk_size}) must be divisible by BC=16.")
     _lib.check(st, f"dr_{kind}_fwd")

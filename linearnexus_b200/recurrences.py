@@ -13,7 +13,7 @@ import torch
 
 from . import _lib
 from ._lib import DR_LAYOUT_BHTD, DR_LAYOUT_BTHD
-from .ops import _NATIVE, _is_bthd_view, _native, _ptr, _require_cuda, _stream
+from .ops import _NATIVE, _is_bthd_view, _native, _ptr, _require_cuda, _status, _stream
 
 Tensor = torch.Tensor
 
@@ -69,7 +69,7 @@ def dplr_delta_rule_recurrent(q: Tensor, k: Tensor, v: Tensor, a: Tensor, b: Ten
     o = _empty_like_layout(q, V, layout)
     with torch.cuda.device(q.device):
         st = _lib.load().dr_dplr_recurrent(_ptr(q), _ptr(k), _ptr(v), _ptr(a), _ptr(b), _ptr(gk), _ptr(h0), _ptr(o), _ptr(hT),
-                                           B, H, T, K, V, float(scale), _NATIVE[q.dtype], layout, _stream(q.device))
+                                           B, H, T, K, V, float(scale), _NATIVE[q.dtype], layout, _ptr(_status(q.device)), _stream(q.device))
     _lib.check(st, "dr_dplr_recurrent")
     return o.to(od), hT
 
@@ -110,7 +110,7 @@ def rwkv6_recurrent(r: Tensor, k: Tensor, v: Tensor, w: Tensor, u: Tensor, scale
     o = _empty_like_layout(r, V, layout)
     with torch.cuda.device(r.device):
         st = _lib.load().dr_rwkv6_recurrent(_ptr(r), _ptr(k), _ptr(v), _ptr(w), _ptr(u32), _ptr(h0), _ptr(o), _ptr(hT),
-                                            B, H, T, K, V, float(scale), _NATIVE[r.dtype], layout, _stream(r.device))
+                                            B, H, T, K, V, float(scale), _NATIVE[r.dtype], layout, _ptr(_status(r.device)), _stream(r.device))
     _lib.check(st, "dr_rwkv6_recurrent")
     return o.to(od), hT
 
@@ -170,7 +170,7 @@ def ssd_chunk_scan(hidden_states: Tensor, dt: Tensor, A: Tensor, B: Tensor, C: T
     lo, hi = float(dt_limit[0]), min(float(dt_limit[1]), 3.0e38)
     with torch.cuda.device(x.device):
         st = _lib.load().dr_ssd_scan(_ptr(x), _ptr(dtn), _ptr(A32), _ptr(Bm), _ptr(Cm), _ptr(D32), _ptr(bias32), _ptr(h0),
-                                     _ptr(y), _ptr(hT), Bt, T, H, P, N, G, lo, hi, _NATIVE[x.dtype], _stream(x.device))
+                                     _ptr(y), _ptr(hT), Bt, T, H, P, N, G, lo, hi, _NATIVE[x.dtype], _ptr(_status(x.device)), _stream(x.device))
     _lib.check(st, "dr_ssd_scan")
     return y.to(od), hT
 
