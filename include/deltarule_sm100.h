@@ -188,6 +188,9 @@ int dr_step(const DrDesc* desc, const void* q, const void* k, const void* v, con
  * dr_chunk_bwd_saved, which is dr_chunk_bwd without the recomputation.  Under jax this is the fwd / bwd pair of a
  * jax.custom_vjp around the three *_chunkwise functions, the workspace being the residual.
  * desc->path is ignored (the forward kernel is chosen by shape as in dr_chunk_bwd); out_dtype as in dr_chunk_fwd.
+ * For bf16 DeltaNet / Gated DeltaNet the saving forward also leaves the adjoint's chunk-parallel pre-pass results in
+ * the workspace; that kernel runs beside the forward on a non-blocking side stream the library creates once per
+ * device, forked from and joined to `stream` with events (stream order as seen by the caller is unchanged).
  */
 int dr_chunk_fwd_saving(const DrDesc* desc, const void* q, const void* k, const void* v, const void* g,
                         const float* beta, const float* h0, void* o, float* hT, void* bwd_workspace,

@@ -442,8 +442,9 @@ int dr_chunk_bwd_static(const DrDesc* d, const void* q, const void* k, const voi
   int launches = 0;
   // launch_bwd zeroes the accumulators it adds into and overwrites the checkpoints before reading them,
   // so whatever an earlier call left in the array is never consumed.
+  // own_stream = false: this entry creates nothing, not even a stream or an event (everything runs on `stream`)
   cudaError_t e = dr::launch_bwd(d, q, k, v, g, beta, h0, d_o, d_hT, dq, dk, dv, dbeta, dg, dh0, scratch, status_dev,
-                                 reinterpret_cast<cudaStream_t>(stream), &launches);
+                                 reinterpret_cast<cudaStream_t>(stream), &launches, false);
   g_launches.fetch_add(launches);
   return check_cuda(e);
 }

@@ -27,6 +27,8 @@
 // records [B*H][N][3*64*64 + 2*64*K], all fp32.
 #pragma once
 
+#include <mutex>
+
 #include "dr_chunk_fp32.cuh"
 #include "dr_scan_launch.h"
 #include "dr_chunk_sm100.cuh"
@@ -1287,14 +1289,93 @@ inline int64_t bwd_workspace_bytes(const DrDesc* d) {
   return f * (int64_t)sizeof(float);
 }
 
+// Where the pieces of the backward workspace lie (all fp32): checkpoints | dq^ copies | dk^ copies | dG | pre-pass records.
+struct BwdRegions {
+  float *ckpt, *dq_acc, *dk_acc, *dg_acc, *pre;
+  int64_t N, units, rows, nvs;
+  size_t dg_floats;
+};
+inline BwdRegions bwd_regions(const DrDesc* d, void* workspace) {
+  BwdRegions r;
+  const int C = d->chunk, K = d->K, V = d->V;
+  r.N = (d->T + C - 1) / C; r.units = (int64_t)d->B * d->H; r.rows = r.units * r.N * C;
+  r.nvs = (V + kBwSlice - 1) / kBwSlice;
+  r.ckpt = reinterpret_cast<float*>(workspace);
+  r.dq_acc = r.ckpt + r.units * r.N * K * V;      // [nvs][rows][K], one copy per value slice (fully overwritten)
+  r.dk_acc = r.dq_acc + r.nvs * r.rows * K;
+  r.dg_floats = d->variant == DR_GATED ? r.rows : d->variant == DR_KDA ? r.rows * K : 0;
+  r.dg_acc = d->variant == DR_DELTA ? nullptr : r.dk_acc + r.nvs * r.rows * K;
+  r.pre = r.dk_acc + r.nvs * r.rows * K + r.dg_floats;   // [units][N][3][64][64] + q^, k^: tensor-core path only
+  return r;
+}
+
+// The chunk-parallel pre-pass of the tensor-core adjoint (X, A, T, q^, k^ of every chunk).  It reads q, k, g, beta
+// only, so it belongs to the forward half of a training step: launch_bwd_forward runs it beside the checkpointing
+// forward, which at training batch sizes (one CTA per sequence) leaves most SMs idle.
+inline cudaError_t launch_bwd_pre(const DrDesc* d, const void* q, const void* k, const void* g, const float* beta,
+                                  void* workspace, cudaStream_t stream, int* launches) {
+  const BwdRegions r = bwd_regions(d, workspace);
+  BwdParams p{};
+  p.q = q; p.k = k; p.g = g; p.beta = beta; p.pre = r.pre;
+  p.map.B = d->B; p.map.H = d->H; p.map.T = d->T; p.map.bthd = d->layout == DR_LAYOUT_BTHD;
+  p.map.Hq = d->qk_heads > 0 ? d->qk_heads : d->H;
+  p.K = d->K; p.V = d->V; p.C = d->chunk; p.N = (int)r.N;
+  p.variant = d->variant; p.qkv_dt = d->qkv_dtype; p.g_dt = d->g_dtype; p.l2norm = d->use_qk_l2norm; p.scale = d->scale;
+  const size_t psmem = bwd_pre_smem_bytes(d->K);
+  cudaError_t e = cudaFuncSetAttribute(bwd_pre_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)psmem);
+  if (e != cudaSuccess) return e;
+  bwd_pre_kernel<<<(unsigned)(r.units * r.N), kBwThreads, psmem, stream>>>(p);
+  ++*launches;
+  return cudaGetLastError();
+}
+
+// One non-blocking side stream per device, created on first use (the only stream the library owns).
+inline cudaError_t bwd_side_stream(cudaStream_t* out) {
+  static std::mutex mu;
+  static cudaStream_t streams[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!streams[dev]) {
+    e = cudaStreamCreateWithFlags(&streams[dev], cudaStreamNonBlocking);
+    if (e != cudaSuccess) return e;
+  }
+  *out = streams[dev];
+  return cudaSuccess;
+}
+
 // The checkpointing forward of the backward: state at the start of every chunk -> the head of the workspace.
 // With o / hT given it is also the forward a training step needs (dr_chunk_fwd_saving), so that step runs one
 // forward instead of two.  KDA at the tensor-core shape uses the two-kernel forward with its records parked in the
 // accumulator part of the workspace (262 KB per chunk there against 82 KB of records; the adjoint overwrites it).
+// own_stream: the pre-pass may run on the library's side stream, forked from and joined to `stream` with events
+// (false for callers that must not create streams or events: the pre-pass then runs on `stream` before the forward).
 inline cudaError_t launch_bwd_forward(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
                                       const float* beta, const float* h0, void* o, float* hT, void* workspace,
-                                      int32_t* status, cudaStream_t stream, int* launches) {
+                                      int32_t* status, cudaStream_t stream, int* launches, bool own_stream = true) {
   const int C = d->chunk, K = d->K, V = d->V;
+  cudaEvent_t joined = nullptr;
+  if (d->variant != DR_KDA && bwd_tensor_core_path(d)) {
+    cudaStream_t side = nullptr;
+    cudaEvent_t forked = nullptr;
+    if (own_stream && bwd_side_stream(&side) == cudaSuccess &&
+        cudaEventCreateWithFlags(&forked, cudaEventDisableTiming) == cudaSuccess &&
+        cudaEventCreateWithFlags(&joined, cudaEventDisableTiming) == cudaSuccess) {
+      cudaError_t ef = cudaEventRecord(forked, stream);
+      if (ef == cudaSuccess) ef = cudaStreamWaitEvent(side, forked, 0);
+      if (ef == cudaSuccess) ef = launch_bwd_pre(d, q, k, g, beta, workspace, side, launches);
+      if (ef == cudaSuccess) ef = cudaEventRecord(joined, side);
+      cudaEventDestroy(forked);   // released once the work recorded in it has completed
+      if (ef != cudaSuccess) { cudaEventDestroy(joined); return ef; }
+    } else {
+      if (forked) cudaEventDestroy(forked);
+      if (joined) { cudaEventDestroy(joined); joined = nullptr; }
+      const cudaError_t ep = launch_bwd_pre(d, q, k, g, beta, workspace, stream, launches);
+      if (ep != cudaSuccess) return ep;
+    }
+  }
   const int64_t N = (d->T + C - 1) / C, units = (int64_t)d->B * d->H;
   float* ckpt = reinterpret_cast<float*>(workspace);
   FwdParams f;
@@ -1325,6 +1406,11 @@ inline cudaError_t launch_bwd_forward(const DrDesc* d, const void* q, const void
     e = launch_recurrent(f, stream);
     ++*launches;
   }
+  if (joined) {   // what follows on `stream` waits for the pre-pass as well
+    const cudaError_t ej = cudaStreamWaitEvent(stream, joined, 0);
+    cudaEventDestroy(joined);
+    if (e == cudaSuccess) e = ej;
+  }
   return e;
 }
 
@@ -1333,16 +1419,10 @@ inline cudaError_t launch_bwd_adjoint(const DrDesc* d, const void* q, const void
                                       void* dv, float* dbeta, float* dg, float* dh0, void* workspace,
                                       cudaStream_t stream, int* launches) {
   const int C = d->chunk, K = d->K, V = d->V;
-  const int64_t N = (d->T + C - 1) / C, units = (int64_t)d->B * d->H, rows = units * N * C;
-  float* ws = reinterpret_cast<float*>(workspace);
-  float* ckpt = ws;
-  const int VSl = kBwSlice;
-  const int64_t nvs = (V + VSl - 1) / VSl;
-  float* dq_acc = ckpt + units * N * K * V;      // [nvs][rows][K], one copy per value slice (fully overwritten)
-  float* dk_acc = dq_acc + nvs * rows * K;
-  float* dg_acc = d->variant == DR_DELTA ? nullptr : dk_acc + nvs * rows * K;
-  const size_t dg_floats = d->variant == DR_GATED ? rows : d->variant == DR_KDA ? rows * K : 0;
-  float* pre = dk_acc + nvs * rows * K + dg_floats;   // [units][N][3][64][64], tensor-core path only
+  const BwdRegions rg = bwd_regions(d, workspace);
+  const int64_t N = rg.N, units = rg.units, rows = rg.rows, nvs = rg.nvs;
+  float *ckpt = rg.ckpt, *dq_acc = rg.dq_acc, *dk_acc = rg.dk_acc, *dg_acc = rg.dg_acc, *pre = rg.pre;
+  const size_t dg_floats = rg.dg_floats;
   cudaError_t e = cudaSuccess;
   if (dg_floats) e = cudaMemsetAsync(dg_acc, 0, dg_floats * sizeof(float), stream);
   if (e != cudaSuccess) return e;
@@ -1371,15 +1451,8 @@ inline cudaError_t launch_bwd_adjoint(const DrDesc* d, const void* q, const void
     const bool tc = bwd_tensor_core_path(d);
     const size_t smem = bwd_layout(C, K, VS, false, tc).total * sizeof(float);
     if (tc) {
-      // slice-independent pieces (X, A, T) once per chunk, all chunks in parallel
+      // the slice-independent pieces (X, A, T, q^, k^ of every chunk) were left in the workspace by launch_bwd_forward
       p.pre = pre;
-      const size_t psmem = bwd_pre_smem_bytes(K);
-      e = cudaFuncSetAttribute(bwd_pre_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)psmem);
-      if (e != cudaSuccess) return e;
-      bwd_pre_kernel<<<(unsigned)(units * N), kBwThreads, psmem, stream>>>(p);
-      e = cudaGetLastError();
-      if (e != cudaSuccess) return e;
-      ++*launches;
       e = cudaFuncSetAttribute(bwd_chunk_kernel<VS, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return e;
       bwd_chunk_kernel<VS, false, true><<<(unsigned)(units * ((V + VS - 1) / VS)), bwd_threads(true), smem, stream>>>(p);
@@ -1408,9 +1481,10 @@ inline cudaError_t launch_bwd_adjoint(const DrDesc* d, const void* q, const void
 inline cudaError_t launch_bwd(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
                               const float* beta, const float* h0, const void* d_o, const float* d_hT, void* dq,
                               void* dk, void* dv, float* dbeta, float* dg, float* dh0, void* workspace,
-                              int32_t* status, cudaStream_t stream, int* launches) {
+                              int32_t* status, cudaStream_t stream, int* launches, bool own_stream = true) {
   // only the forward has bounded waits that can report; the adjoint kernels synchronise with block barriers
-  cudaError_t e = launch_bwd_forward(d, q, k, v, g, beta, h0, nullptr, nullptr, workspace, status, stream, launches);
+  cudaError_t e = launch_bwd_forward(d, q, k, v, g, beta, h0, nullptr, nullptr, workspace, status, stream, launches,
+                                     own_stream);
   if (e != cudaSuccess) return e;
   return launch_bwd_adjoint(d, q, k, v, g, beta, d_o, d_hT, dq, dk, dv, dbeta, dg, dh0, workspace, stream, launches);
 }

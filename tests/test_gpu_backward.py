@@ -124,14 +124,17 @@ def test_autograd_uses_the_saved_states():
     from linearnexus_b200 import _lib
     inp = O.make_inputs("gated", 1, 2, 128, 128, 128, seed=4, io_dtype=torch.bfloat16)
     leaf = {k_: (None if v_ is None else v_.cuda().requires_grad_(v_.is_floating_point())) for k_, v_ in inp.items()}
+    nf = _lib.launch_count()
     o, hT = L.gated_delta_rule_chunkwise(leaf["q"], leaf["k"], leaf["v"], leaf["g"], leaf["beta"])
     assert _lib.last_path() == "fwd_saving"
+    # the forward that keeps the per-chunk states, with the adjoint's chunk-parallel pre-pass beside it
+    assert _lib.launch_count() - nf == 2
     n0 = _lib.launch_count()
     (o.float().square().sum() + hT.sum()).backward()
     torch.cuda.synchronize()
-    # pre-pass + adjoint + finalize only: no forward recomputation (the path name is per host thread; autograd
+    # adjoint + finalize only: no forward recomputation, no pre-pass (the path name is per host thread; autograd
     # runs elsewhere, so the launch counter is the witness)
-    assert _lib.launch_count() - n0 == 3
+    assert _lib.launch_count() - n0 == 2
     assert leaf["q"].grad is not None and torch.isfinite(leaf["q"].grad.float()).all()
 
 
