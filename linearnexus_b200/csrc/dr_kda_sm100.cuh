@@ -83,6 +83,13 @@ __device__ __forceinline__ float2 bf2(uint32_t u) {
   return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u));
 }
 
+// two bf16 products in one instruction (operands and result packed in 32 bits)
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
 // four consecutive elements starting at element index i (a multiple of 4)
 __device__ __forceinline__ void ld4(const void* p, int64_t i, int dt, float (&x)[4]) {
   if (dt == DR_BF16) {
@@ -265,17 +272,18 @@ __global__ void __launch_bounds__(kThreads, 2) intra_kernel(const FwdParams p, u
         const float2 gb = *reinterpret_cast<const float2*>(sG + r1 * LDF + k0);
         const float2 gc = *reinterpret_cast<const float2*>(sG + r0 * LDF + k0 + 8);
         const float2 gd = *reinterpret_cast<const float2*>(sG + r1 * LDF + k0 + 8);
-        const float ea0 = ex2(ga.x - gn0.x), ea1 = ex2(ga.y - gn0.y), eb0 = ex2(gb.x - gn0.x), eb1 = ex2(gb.y - gn0.y);
-        const float ec0 = ex2(gc.x - gn1.x), ec1 = ex2(gc.y - gn1.y), ed0 = ex2(gd.x - gn1.x), ed1 = ex2(gd.y - gn1.y);
-        float2 x;
-        x = bf2(*reinterpret_cast<const uint32_t*>(sK + r0 * LDH + k0));     ak[0] = tc::pack_bf16(x.x * ea0, x.y * ea1);
-        x = bf2(*reinterpret_cast<const uint32_t*>(sK + r1 * LDH + k0));     ak[1] = tc::pack_bf16(x.x * eb0, x.y * eb1);
-        x = bf2(*reinterpret_cast<const uint32_t*>(sK + r0 * LDH + k0 + 8)); ak[2] = tc::pack_bf16(x.x * ec0, x.y * ec1);
-        x = bf2(*reinterpret_cast<const uint32_t*>(sK + r1 * LDH + k0 + 8)); ak[3] = tc::pack_bf16(x.x * ed0, x.y * ed1);
-        x = bf2(*reinterpret_cast<const uint32_t*>(sQ + r0 * LDH + k0));     aq[0] = tc::pack_bf16(x.x * ea0, x.y * ea1);
-        x = bf2(*reinterpret_cast<const uint32_t*>(sQ + r1 * LDH + k0));     aq[1] = tc::pack_bf16(x.x * eb0, x.y * eb1);
-        x = bf2(*reinterpret_cast<const uint32_t*>(sQ + r0 * LDH + k0 + 8)); aq[2] = tc::pack_bf16(x.x * ec0, x.y * ec1);
-        x = bf2(*reinterpret_cast<const uint32_t*>(sQ + r1 * LDH + k0 + 8)); aq[3] = tc::pack_bf16(x.x * ed0, x.y * ed1);
+        // decay factors as bf16 pairs, shared by the k and the q row; the products are packed bf16 multiplies (the
+        // operands of the tensor-core product are bf16 either way: one rounding of the factor, one of the product)
+        const uint32_t ea = tc::pack_bf16(ex2(ga.x - gn0.x), ex2(ga.y - gn0.y)), eb = tc::pack_bf16(ex2(gb.x - gn0.x), ex2(gb.y - gn0.y));
+        const uint32_t ec = tc::pack_bf16(ex2(gc.x - gn1.x), ex2(gc.y - gn1.y)), ed = tc::pack_bf16(ex2(gd.x - gn1.x), ex2(gd.y - gn1.y));
+        ak[0] = mul_bf16x2(*reinterpret_cast<const uint32_t*>(sK + r0 * LDH + k0), ea);
+        ak[1] = mul_bf16x2(*reinterpret_cast<const uint32_t*>(sK + r1 * LDH + k0), eb);
+        ak[2] = mul_bf16x2(*reinterpret_cast<const uint32_t*>(sK + r0 * LDH + k0 + 8), ec);
+        ak[3] = mul_bf16x2(*reinterpret_cast<const uint32_t*>(sK + r1 * LDH + k0 + 8), ed);
+        aq[0] = mul_bf16x2(*reinterpret_cast<const uint32_t*>(sQ + r0 * LDH + k0), ea);
+        aq[1] = mul_bf16x2(*reinterpret_cast<const uint32_t*>(sQ + r1 * LDH + k0), eb);
+        aq[2] = mul_bf16x2(*reinterpret_cast<const uint32_t*>(sQ + r0 * LDH + k0 + 8), ec);
+        aq[3] = mul_bf16x2(*reinterpret_cast<const uint32_t*>(sQ + r1 * LDH + k0 + 8), ed);
       }
 #pragma unroll
       for (int i = 0; i < 3; ++i) {
@@ -283,11 +291,11 @@ __global__ void __launch_bounds__(kThreads, 2) intra_kernel(const FwdParams p, u
           const int j = 8 * (nt0 + i) + g;
           const float2 gj0 = *reinterpret_cast<const float2*>(sG + j * LDF + k0);
           const float2 gj1 = *reinterpret_cast<const float2*>(sG + j * LDF + k0 + 8);
-          const float2 y0 = bf2(*reinterpret_cast<const uint32_t*>(sK + j * LDH + k0));
-          const float2 y1 = bf2(*reinterpret_cast<const uint32_t*>(sK + j * LDH + k0 + 8));
           uint32_t bb[2];
-          bb[0] = tc::pack_bf16(y0.x * ex2(gn0.x - gj0.x), y0.y * ex2(gn0.y - gj0.y));
-          bb[1] = tc::pack_bf16(y1.x * ex2(gn1.x - gj1.x), y1.y * ex2(gn1.y - gj1.y));
+          bb[0] = mul_bf16x2(*reinterpret_cast<const uint32_t*>(sK + j * LDH + k0),
+                             tc::pack_bf16(ex2(gn0.x - gj0.x), ex2(gn0.y - gj0.y)));
+          bb[1] = mul_bf16x2(*reinterpret_cast<const uint32_t*>(sK + j * LDH + k0 + 8),
+                             tc::pack_bf16(ex2(gn1.x - gj1.x), ex2(gn1.y - gj1.y)));
           mma_bf16(dk[i], ak, bb);
           mma_bf16(dq[i], aq, bb);
         }
