@@ -213,6 +213,17 @@ int dr_chunk_bwd(const DrDesc* desc, const void* q, const void* k, const void* v
                  size_t workspace_bytes, int32_t* status_dev, void* stream);
 
 /* Size of the scratch array built into the library for dr_chunk_bwd_static: 32 MiB per GPU. */
+/*
+ * dr_chunk_bwd over a PACKED batch (the tensors of dr_chunk_fwd_varlen; d_o, dq, dk, dv packed like their
+ * primal tensors; dbeta [total_T, H], dg like g, both float32; d_hT, dh0 float32 [n_seqs, H, K, V] or null).
+ * Each sequence is differentiated on its own, one after another on `stream`, so one workspace sized for the longest
+ * sequence (dr_workspace_bytes(desc with B = 1 and T = that length, 1)) serves all of them.
+ */
+int dr_chunk_bwd_varlen(const DrDesc* desc, const void* q, const void* k, const void* v, const void* g,
+                        const float* beta, const int32_t* cu_seqlens_host, int32_t n_seqs, const float* h0,
+                        const void* d_o, const float* d_hT, void* dq, void* dk, void* dv, float* dbeta, float* dg,
+                        float* dh0, void* workspace, size_t workspace_bytes, int32_t* status_dev, void* stream);
+
 #define DR_STATIC_SCRATCH_BYTES (32u << 20)
 
 /*

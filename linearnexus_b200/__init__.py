@@ -12,7 +12,7 @@ from .ops import (delta_rule_chunkwise, delta_rule_recurrent, delta_rule_recurre
 from .state import DeltaNetState, GatedDeltaNetState, KDAState
 from .host_pipeline import HostPipeline, chunkwise_from_host
 from .ops import check_device_status
-from .varlen import chunkwise_varlen, compute_unpadded_indices, pad, unpad
+from .varlen import chunk_backward_varlen, chunkwise_varlen, compute_unpadded_indices, pad, unpad
 from .recurrences import (dplr_delta_rule_recurrent, dplr_delta_rule_step, rwkv6_chunkwise, rwkv6_recurrent,
                           rwkv6_step, ssd_chunk_scan, ssd_recurrent_step)
 from .block_ops import (depthwise_conv1d_causal, gated_deltanet_gates, kda_gate, rmsnorm_gated,
@@ -25,7 +25,7 @@ __all__ = [
     "DeltaNetState", "GatedDeltaNetState", "KDAState",
     "KernelBackend", "backend_availability", "select_kernel_backend",
     "HostPipeline", "chunkwise_from_host", "check_device_status",
-    "chunkwise_varlen", "compute_unpadded_indices", "unpad", "pad",
+    "chunkwise_varlen", "chunk_backward_varlen", "compute_unpadded_indices", "unpad", "pad",
     "dplr_delta_rule_recurrent", "dplr_delta_rule_step", "rwkv6_recurrent", "rwkv6_chunkwise", "rwkv6_step",
     "ssd_chunk_scan", "ssd_recurrent_step",
     "depthwise_conv1d_causal", "short_conv_silu", "gated_deltanet_gates", "kda_gate", "rmsnorm_gated",

@@ -36,7 +36,7 @@ EXPORTS = ["dr_version", "dr_strerror", "dr_last_cuda_error", "dr_launch_count",
            "dr_debug_umma_selftest", "dr_chunk_bwd_static", "dr_chunk_fwd_saving", "dr_chunk_bwd_saved",
            "dr_short_conv_silu", "dr_gate_activations", "dr_gated_rmsnorm", "dr_check_status",
            "dr_last_device_status", "dr_debug_wait_timeout", "dr_chunk_fwd_varlen", "dr_dplr_recurrent",
-           "dr_rwkv6_recurrent", "dr_ssd_scan", "dr_debug_bounds_checked", "dr_debug_bounds_probe"]
+           "dr_rwkv6_recurrent", "dr_ssd_scan", "dr_debug_bounds_checked", "dr_debug_bounds_probe", "dr_chunk_bwd_varlen"]
 
 
 class DrDesc(ctypes.Structure):
@@ -161,6 +161,9 @@ def load() -> ctypes.CDLL:
         lib.dr_chunk_bwd.restype = ctypes.c_int
         lib.dr_chunk_bwd.argtypes = [dp, vp, vp, vp, vp, fp, fp, vp, fp, vp, vp, vp, fp, fp, fp, vp,
                                      ctypes.c_size_t, ip, vp]
+        lib.dr_chunk_bwd_varlen.restype = ctypes.c_int
+        lib.dr_chunk_bwd_varlen.argtypes = [dp, vp, vp, vp, vp, fp, ctypes.POINTER(ctypes.c_int32), ctypes.c_int32, fp, vp, fp,
+                                            vp, vp, vp, fp, fp, fp, vp, ctypes.c_size_t, ip, vp]
         lib.dr_chunk_bwd_static.restype = ctypes.c_int
         lib.dr_chunk_bwd_static.argtypes = [dp, vp, vp, vp, vp, fp, fp, vp, fp, vp, vp, vp, fp, fp, fp, ip, vp]
         lib.dr_chunk_fwd_saving.restype = ctypes.c_int
@@ -198,7 +201,7 @@ def check(status: int, where: str) -> None:
             text += f" (cudaError {lib.dr_last_cuda_error()})"
         if status == -10:
             bits = lib.dr_last_device_status()
-            text += " (" + ", ".join(n for b, n in DEVICE_STATUS_BITS.items() if bits & b) + ")"
+            text += " (" + ", ".join(n for b, n in DEVICE_STATUS_BITS.items() if bits & b) + f"; status word 0x{bits & 0xffffffff:x})"
         raise DeltaRuleError(status, text, where)
 
 

@@ -348,6 +348,37 @@ int dr_chunk_bwd(const DrDesc* d, const void* q, const void* k, const void* v, c
   return check_cuda(e);
 }
 
+int dr_chunk_bwd_varlen(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
+                        const float* beta, const int32_t* cu, int32_t n_seqs, const float* h0, const void* d_o,
+                        const float* d_hT, void* dq, void* dk, void* dv, float* dbeta, float* dg, float* dh0,
+                        void* workspace, size_t workspace_bytes, int32_t* status_dev, void* stream) {
+  if (!d || !cu) return DR_ERR_NULL;
+  if (n_seqs < 1 || d->layout != DR_LAYOUT_BTHD || cu[0] != 0) return DR_ERR_SHAPE;
+  for (int i = 0; i < n_seqs; ++i)
+    if (cu[i + 1] <= cu[i]) return DR_ERR_SHAPE;
+  if (!q || !k || !v || !d_o || !dq || !dk || !dv || !beta || !dbeta) return DR_ERR_NULL;
+  const int Hq = d->qk_heads > 0 ? d->qk_heads : d->H;
+  const size_t es = d->qkv_dtype == DR_BF16 ? 2 : 4, eg = d->g_dtype == DR_BF16 ? 2 : 4;
+  const size_t g_row = d->variant == DR_KDA ? (size_t)d->H * d->K : (size_t)d->H;
+  const size_t state = (size_t)d->H * d->K * d->V;
+  // the sequences run one after another on `stream`, so they can share the workspace
+  for (int i = 0; i < n_seqs; ++i) {
+    DrDesc ds = *d;
+    ds.B = 1;
+    ds.T = cu[i + 1] - cu[i];
+    const size_t t0 = (size_t)cu[i];
+    const size_t oqk = t0 * Hq * d->K * es, ov = t0 * d->H * d->V * es;
+    auto at = [](const void* p, size_t off) { return p ? static_cast<const char*>(p) + off : nullptr; };
+    auto atw = [](void* p, size_t off) { return p ? static_cast<char*>(p) + off : nullptr; };
+    const int s = dr_chunk_bwd(&ds, at(q, oqk), at(k, oqk), at(v, ov), at(g, t0 * g_row * eg), beta + t0 * d->H,
+                               h0 ? h0 + i * state : nullptr, at(d_o, ov), d_hT ? d_hT + i * state : nullptr,
+                               atw(dq, oqk), atw(dk, oqk), atw(dv, ov), dbeta + t0 * d->H, dg ? dg + t0 * g_row : nullptr,
+                               dh0 ? dh0 + i * state : nullptr, workspace, workspace_bytes, status_dev, stream);
+    if (s != DR_OK) return s;
+  }
+  return DR_OK;
+}
+
 int dr_chunk_fwd_saving(const DrDesc* d, const void* q, const void* k, const void* v, const void* g,
                         const float* beta, const float* h0, void* o, float* hT, void* workspace,
                         size_t workspace_bytes, int32_t* status_dev, void* stream) {

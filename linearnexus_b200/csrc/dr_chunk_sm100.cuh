@@ -92,6 +92,8 @@ struct alignas(16) Ctl {
   alignas(16) float rs[2][64];       // per X buffer: beta_i rk_i^2, row factor of the unit-lower system
   uint32_t tmem_base;
   int abort;
+  uint64_t bar2b;                    // the output products' barrier of the odd chunks (bar2: even chunks); it fills what
+                                     // was padding, the block is as large as without it
 };
 
 // Kernel parameters: the common forward parameters plus the TMA tensor maps (see make_input_map /
@@ -104,6 +106,22 @@ struct alignas(64) Sm100Params {
 // A shared-memory descriptor whose start address is `bytes` further on (the address field holds bytes / 16 and
 // cannot carry out of its 14 bits for addresses inside one CTA's shared memory).
 __device__ __forceinline__ uint64_t desc_adv(uint64_t d, uint32_t bytes) { return d + (uint64_t)(bytes >> 4); }
+
+// The rest of a wait whose first try_wait came back empty, kept out of line (the kernel's speed follows its code size).
+// Bounded; when the bound runs out every later wait of the CTA returns at once (abort flag), DR_DEV_TIMEOUT is set, and
+// the first such wait of the launch leaves its place in bits 8..15 of the status word (bits 8..13: the barrier's number
+// in the control block, 63 for one behind the float arrays; bits 14..15: the warp group).
+__device__ __noinline__ void wait_more(uint32_t bar, uint32_t parity, int32_t* status, int* abort_flag, uint32_t bar_offset,
+                                       uint32_t grp) {
+  volatile int* ab = abort_flag;
+  if (*ab) return;
+  if (tc::mbar_wait_slow(bar, parity, kWaitLimit)) return;
+  *ab = 1;
+  if (!status) return;
+  const uint32_t num = bar_offset / 8u < 63u ? bar_offset / 8u : 63u;
+  atomicCAS(status, 0, DR_DEV_TIMEOUT | (int)((num | (grp << 6)) << 8));
+  atomicOr(status, DR_DEV_TIMEOUT);
+}
 
 struct SyncPB { __device__ __forceinline__ void operator()() const { group_sync128(2); } };
 
@@ -151,6 +169,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
     tc::mbar_init(tc::smem_u32(&ctl.bar1), 1);
     tc::mbar_init(tc::smem_u32(&ctl.bar2s), 1);
     tc::mbar_init(tc::smem_u32(&ctl.bar2), 1);
+    tc::mbar_init(tc::smem_u32(&ctl.bar2b), 1);
     tc::mbar_init(tc::smem_u32(&ctl.barDq), 1);
     tc::fence_mbar_init();
     ctl.abort = 0;
@@ -163,12 +182,8 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
   volatile int* abort_p = &ctl.abort;
 
   auto wait_bar = [&](uint64_t* bar, uint32_t parity) {
-    if (!*abort_p) {
-      if (!tc::mbar_wait_compact(tc::smem_u32(bar), parity, kWaitLimit)) {
-        *abort_p = 1;
-        if (p.status) atomicOr(p.status, DR_DEV_TIMEOUT);
-      }
-    }
+    if (tc::mbar_try(tc::smem_u32(bar), parity)) return;   // the common case, and all that a call site carries
+    wait_more(tc::smem_u32(bar), parity, p.status, &ctl.abort, (uint32_t)((const char*)bar - (const char*)&ctl), (uint32_t)grp);
   };
   auto arrive = [&](uint64_t* bar) { mbar_arrive(tc::smem_u32(bar)); };
 
@@ -521,7 +536,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
           tc::mma_ts(tbase + TM_DU + 64 * s, tbase + TM_VA + ks * 8, desc_adv(ad0, ks * 256), id_n64, ks > 0);
-        tc::mma_commit(tc::smem_u32(&ctl.bar2));
+        tc::mma_commit(tc::smem_u32((n & 1) ? &ctl.bar2b : &ctl.bar2));
       }
     }
     // final state: hT[k][v] = S^T[v][k]
@@ -540,7 +555,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
           if (in_bounds(p.status, (hT - p.hT) + (c0 + j) * kD + gt, p.n_state)) hT[(c0 + j) * kD + gt] = __uint_as_float(r[j]);
       }
     }
-    wait_bar(&ctl.bar2, (nchunks - 1) & 1);   // every product has completed before tensor memory is released
+    wait_bar(((nchunks - 1) & 1) ? &ctl.bar2b : &ctl.bar2, ((nchunks - 1) >> 1) & 1);   // every product has completed before tensor memory is released
   } else {
     // =========================== CB: q norms, W tile, U^T, output, Dq ==================================
     const __nv_bfloat16* gv = reinterpret_cast<const __nv_bfloat16*>(p.v);
@@ -695,7 +710,11 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       }
       // ---- output of the previous chunk, then Dq of this one ---------------------------------------------
       if (n >= 1) {
-        wait_bar(&ctl.bar2, (n - 1) & 1);   // Do and Dq of chunk n-1 are complete
+        // Do and Dq of chunk n-1 are complete.  Do alternates between two barriers (even / odd chunks): the chain can
+        // commit chunk n's Do before this group gets here (it only needs the W tile, released above), and a parity wait
+        // on one barrier could not tell that phase from the one before chunk n-1's and would never return.  It cannot
+        // commit chunk n+1's: that needs the next W tile, which this group writes after this wait.
+        wait_bar(((n - 1) & 1) ? &ctl.bar2b : &ctl.bar2, ((n - 1) >> 1) & 1);
         wait_bar(&ctl.barDq, (n - 1) & 1);
         tc::tc_fence_after();
         out_epilogue(n - 1, n);
@@ -703,7 +722,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         issue_dq(0);
       }
     }
-    wait_bar(&ctl.bar2, (nchunks - 1) & 1);
+    wait_bar(((nchunks - 1) & 1) ? &ctl.bar2b : &ctl.bar2, ((nchunks - 1) >> 1) & 1);
     wait_bar(&ctl.barDq, (nchunks - 1) & 1);
     tc::tc_fence_after();
     out_epilogue(nchunks - 1, -1);

@@ -123,3 +123,62 @@ def chunkwise_varlen(variant: str, q: Tensor, k: Tensor, v: Tensor, g: Optional[
         raise ValueError(f"chunk_size (BT={chunk_size}) must be divisible by BC=16.")
     _lib.check(st, "dr_chunk_fwd_varlen")
     return (o if o.dtype == out_dtype else o.to(out_dtype)), hT
+
+
+def chunk_backward_varlen(variant: str, q: Tensor, k: Tensor, v: Tensor, g: Optional[Tensor], beta: Tensor, d_o: Tensor,
+                          cu_seqlens: Sequence[int], initial_state: Optional[Tensor] = None,
+                          d_final_state: Optional[Tensor] = None, scale: Optional[float] = None, chunk_size: int = 64,
+                          use_qk_l2norm: Optional[bool] = None) -> dict:
+    """Gradients of ``sum(o * d_o) + sum(final_state * d_final_state)`` of :func:`chunkwise_varlen` over a packed
+    batch, in one library call (``dr_chunk_bwd_varlen``).  Tensors as in :func:`chunkwise_varlen`; ``d_o``
+    ``[total_T, H, V]``, ``d_final_state`` ``[n_seqs, H, K, V]`` or None.  Returns a dict: dq, dk, dv in the q/k/v
+    dtype, dbeta float32 ``[total_T, H]``, dg float32 like g (None for "delta"), dh0 float32 ``[n_seqs, H, K, V]``."""
+    if variant not in _VAR:
+        raise ValueError(f"unknown variant {variant!r}")
+    if (g is None) != (variant == "delta"):
+        raise ValueError("g must be given for 'gated' / 'kda' and omitted for 'delta'")
+    cu = [int(c) for c in (cu_seqlens.tolist() if isinstance(cu_seqlens, Tensor) else cu_seqlens)]
+    n = len(cu) - 1
+    if n < 1 or cu[0] != 0 or cu[-1] != q.shape[0] or any(b <= a for a, b in zip(cu, cu[1:])):
+        raise ValueError("cu_seqlens must rise strictly from 0 to the number of packed tokens")
+    if use_qk_l2norm is None:
+        use_qk_l2norm = variant != "delta"
+    ops._require_cuda(q, k, v, g, beta, d_o, initial_state, d_final_state)
+    total, Hq, K = q.shape
+    H, V = v.shape[1], v.shape[2]
+    if not ops.backward_supported(variant, K, chunk_size):
+        raise NotImplementedError("the backward kernels cover chunk_size <= 64 and K <= 128 (K % 16 == 0 for 'kda')")
+    for name, t in (("initial_state", initial_state), ("d_final_state", d_final_state)):
+        if t is not None and tuple(t.shape) != (n, H, K, V):
+            raise ValueError(f"{name} must be [n_seqs,H,K,V]={n, H, K, V}")
+    if scale is None:
+        scale = K ** -0.5
+    dev = q.device
+    native = ops._NATIVE
+    common = torch.float32 if any(t.dtype not in native for t in (q, k, v)) or len({q.dtype, k.dtype, v.dtype}) > 1 else q.dtype
+    qn, kn, vn, don = (t.to(common).contiguous() for t in (q, k, v, d_o))
+    gn = None if g is None else ops._native(g).contiguous()
+    bn = beta.to(torch.float32).contiguous()
+    f32 = lambda t: None if t is None else t.to(device=dev, dtype=torch.float32).contiguous()
+    h0, dhT = f32(initial_state), f32(d_final_state)
+    longest = max(b - a for a, b in zip(cu, cu[1:]))
+    d = ops._desc(_VAR[variant], DR_LAYOUT_BTHD, 1, H, longest, K, V, chunk_size, qn, gn, common, use_qk_l2norm, scale)
+    d.qk_heads = Hq
+    lib = _lib.load()
+    need = int(lib.dr_workspace_bytes(ctypes.byref(d), 1))
+    _lib.check(need if need < 0 else 0, "dr_workspace_bytes")
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+    dq, dk, dv = torch.empty_like(qn), torch.empty_like(kn), torch.empty_like(vn)
+    dbeta = torch.empty((total, H), dtype=torch.float32, device=dev)
+    dg = None if g is None else torch.empty(gn.shape, dtype=torch.float32, device=dev)
+    dh0 = torch.empty((n, H, K, V), dtype=torch.float32, device=dev)
+    cu_arr = (ctypes.c_int32 * (n + 1))(*cu)
+    P = ops._ptr
+    with torch.cuda.device(dev):
+        st = lib.dr_chunk_bwd_varlen(ctypes.byref(d), P(qn), P(kn), P(vn), P(gn), P(bn), cu_arr, n, P(h0), P(don), P(dhT),
+                                     P(dq), P(dk), P(dv), P(dbeta), P(dg), P(dh0), P(ws), ws.numel(),
+                                     P(ops._status(dev)), ops._stream(dev))
+    if st == -7:
+        raise ValueError(f"chunk_size (BT={chunk_size}) must be divisible by BC=16.")
+    _lib.check(st, "dr_chunk_bwd_varlen")
+    return dict(dq=dq.to(q.dtype), dk=dk.to(k.dtype), dv=dv.to(v.dtype), dg=dg, dbeta=dbeta, dh0=dh0)

@@ -91,3 +91,36 @@ def test_packed_entry_point_validates_offsets():
     d.layout = 0                               # packed batches are token-major
     ok = (ctypes.c_int32 * 2)(0, 10)
     assert lib.dr_chunk_fwd_varlen(ctypes.byref(d), 16, 16, 16, 16, 16, ok, 1, None, 16, None, None, 0, None, None) == -2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("variant,io,K,tol", [("gated", torch.bfloat16, 128, 2e-2), ("kda", torch.float32, 32, 2e-4),
+                                              ("delta", torch.float32, 64, 2e-4)])
+def test_packed_backward_equals_each_sequence_alone(variant, io, K, tol):
+    """dr_chunk_bwd_varlen against the float64 oracle's gradients of every sequence taken alone."""
+    lens = [130, 64, 1, 77]
+    H = 2
+    seqs, packed, cu = _packed(variant, lens, H, K, K, io, seed=60)
+    t = {k: (None if v is None else v.cuda()) for k, v in packed.items()}
+    gen = torch.Generator().manual_seed(2)
+    d_o = torch.randn(sum(lens), H, K, generator=gen).to(io)
+    d_hT = torch.randn(len(lens), H, K, K, generator=gen) * 0.1
+    got = L.chunk_backward_varlen(variant, t["q"], t["k"], t["v"], t["g"], t["beta"], d_o.cuda(), cu,
+                                  initial_state=t["h0"], d_final_state=d_hT.cuda())
+    L.check_device_status()
+    assert got["dq"].shape == t["q"].shape and got["dbeta"].shape == (sum(lens), H) and got["dh0"].shape == (len(lens), H, K, K)
+    f = lambda x: None if x is None else (x.float() if x.dtype == torch.bfloat16 else x)
+    rel = lambda a, b: ((a.double().cpu() - b.double()).abs().max() / b.double().abs().max().clamp_min(1e-30)).item()
+    for i, s in enumerate(seqs):
+        do_i = f(d_o[cu[i]:cu[i + 1]]).transpose(0, 1)[None]
+        ref = O.delta_rule_grads(variant, f(s["q"]), f(s["k"]), f(s["v"]), s["g"], s["beta"], s["h0"], do_i, d_hT[i:i + 1],
+                                 use_qk_l2norm=(variant != "delta"))
+        sl = slice(cu[i], cu[i + 1])
+        tok = lambda x: x[sl].transpose(0, 1)[None]       # packed [T_i, H, ...] -> [1, H, T_i, ...]
+        if lens[i] > 1:   # a one-token sequence has gradients near zero in places: compared through the others' scale
+            for name in ("dq", "dk", "dv"):
+                assert rel(tok(got[name]), ref[name]) <= tol, (i, name)
+            assert rel(tok(got["dbeta"]), ref["dbeta"]) <= tol, (i, "dbeta")
+            if ref["dg"] is not None:
+                assert rel(tok(got["dg"]), ref["dg"]) <= tol, (i, "dg")
+        assert rel(got["dh0"][i:i + 1], ref["dh0"]) <= tol, (i, "dh0")
