@@ -107,22 +107,6 @@ struct alignas(64) Sm100Params {
 // cannot carry out of its 14 bits for addresses inside one CTA's shared memory).
 __device__ __forceinline__ uint64_t desc_adv(uint64_t d, uint32_t bytes) { return d + (uint64_t)(bytes >> 4); }
 
-// The rest of a wait whose first try_wait came back empty, kept out of line (the kernel's speed follows its code size).
-// Bounded; when the bound runs out every later wait of the CTA returns at once (abort flag), DR_DEV_TIMEOUT is set, and
-// the first such wait of the launch leaves its place in bits 8..15 of the status word (bits 8..13: the barrier's number
-// in the control block, 63 for one behind the float arrays; bits 14..15: the warp group).
-__device__ __noinline__ void wait_more(uint32_t bar, uint32_t parity, int32_t* status, int* abort_flag, uint32_t bar_offset,
-                                       uint32_t grp) {
-  volatile int* ab = abort_flag;
-  if (*ab) return;
-  if (tc::mbar_wait_slow(bar, parity, kWaitLimit)) return;
-  *ab = 1;
-  if (!status) return;
-  const uint32_t num = bar_offset / 8u < 63u ? bar_offset / 8u : 63u;
-  atomicCAS(status, 0, DR_DEV_TIMEOUT | (int)((num | (grp << 6)) << 8));
-  atomicOr(status, DR_DEV_TIMEOUT);
-}
-
 struct SyncPB { __device__ __forceinline__ void operator()() const { group_sync128(2); } };
 
 template <bool kTma>
@@ -179,7 +163,6 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
   tc::tc_fence_after();
   const uint32_t tbase = ctl.tmem_base;
   const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
-  volatile int* abort_p = &ctl.abort;
 
   auto wait_bar = [&](uint64_t* bar, uint32_t parity) {
     if (tc::mbar_try(tc::smem_u32(bar), parity)) return;   // the common case, and all that a call site carries

@@ -555,14 +555,10 @@ __global__ void __launch_bounds__(kStateThreads, 1) state_kernel(const __grid_co
   tc::tc_fence_after();
   const uint32_t tbase = ctl.tmem_base;
   const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-  volatile int* abort_p = &ctl.abort;
   auto wait_bar = [&](uint64_t* bar, uint32_t parity) {
-    if (!*abort_p) {
-      if (!tc::mbar_wait_bounded(tc::smem_u32(bar), parity, sm100::kWaitLimit)) {
-        *abort_p = 1;
-        if (p.status) atomicOr(p.status, DR_DEV_TIMEOUT);
-      }
-    }
+    if (tc::mbar_try(tc::smem_u32(bar), parity)) return;
+    sm100::wait_more(tc::smem_u32(bar), parity, p.status, &ctl.abort, (uint32_t)((const char*)bar - (const char*)&ctl),
+                     (uint32_t)(warp == 8 ? 1 : 0));
   };
   auto arrive = [&](uint64_t* bar) { sm100::mbar_arrive(tc::smem_u32(bar)); };
   auto workers_sync = [&]() { asm volatile("bar.sync 1, 256;" ::: "memory"); };

@@ -26,6 +26,22 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
+// The rest of a wait whose first try_wait came back empty, kept out of line (the kernel's speed follows its code size).
+// Bounded; when the bound runs out every later wait of the CTA returns at once (abort flag), DR_DEV_TIMEOUT is set, and
+// the first such wait of the launch leaves its place in bits 8..15 of the status word (bits 8..13: the barrier's number
+// in the control block, 63 for one behind the float arrays; bits 14..15: the warp group).
+__device__ __noinline__ void wait_more(uint32_t bar, uint32_t parity, int32_t* status, int* abort_flag, uint32_t bar_offset,
+                                       uint32_t grp) {
+  volatile int* ab = abort_flag;
+  if (*ab) return;
+  if (tc::mbar_wait_slow(bar, parity, kWaitLimit)) return;
+  *ab = 1;
+  if (!status) return;
+  const uint32_t num = bar_offset / 8u < 63u ? bar_offset / 8u : 63u;
+  atomicCAS(status, 0, DR_DEV_TIMEOUT | (int)((num | (grp << 6)) << 8));
+  atomicOr(status, DR_DEV_TIMEOUT);
+}
+
 __device__ __forceinline__ uint32_t to_tf32(float x) {
   uint32_t r;
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
