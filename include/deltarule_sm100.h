@@ -64,6 +64,10 @@ typedef enum DrChunkPath {
 #define DR_DEV_OK 0
 #define DR_DEV_TIMEOUT 1 /* a bounded wait on an mbarrier ran out */
 #define DR_DEV_BOUNDS 2  /* an index check failed: only the debug build (compiled with -DDR_BOUNDS_CHECK) checks */
+/* With DR_DEV_TIMEOUT from the tcgen05 kernels, bits 8..15 say where the first wait of the launch gave up: the number
+ * of the barrier in the kernel's control block (bits 8..13) and the warp group that waited (bits 14..15).  For reading
+ * by the library's maintainers; callers test the low bits only. */
+#define DR_DEV_SITE(word) (((word) >> 8) & 0xff)
 
 typedef struct DrDesc {
   int32_t variant;       /* DrVariant */

@@ -544,10 +544,14 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
     const __nv_bfloat16* gv = reinterpret_cast<const __nv_bfloat16*>(p.v);
     __nv_bfloat16* go = reinterpret_cast<__nv_bfloat16*>(p.o);
     uint8_t* sV = smem + SM_V;
+    // The group's three products per chunk are issued by threads of three different warps (a product blocks its issuing
+    // thread for 330-540 cycles, and the warps meet again at the group's next barrier): W^T by thread 0, U^T and the V
+    // copy by thread 32, Dq by thread 64.  Each commits to its own barrier.
+    constexpr int kUThread = 32, kDqThread = 64;
     // V rows of chunk m -> core-matrix tile
     auto issue_v = [&](int m) {
       if (kTma) {
-        if (gt == 0) {
+        if (gt == kUThread) {
           const uint32_t bar = tc::smem_u32(&ctl.vb);
           tc::mbar_arrive_expect_tx(bar, 64u * 256);
           tc::tma_load_5d(tc::smem_u32(sV), &P.tv, 0, 0, vc2, m * 8, vc4, bar);
@@ -600,7 +604,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         if (c0 == kC - 16) {
           tc::tc_fence_before();
           group_sync128(4);      // Dq and this stage's accumulator are in registers, in every thread
-          if (next >= 0 && gt == 0) issue_dq(next);
+          if (next >= 0 && gt == kDqThread) issue_dq(next);
         }
         if (go) {
 #pragma unroll
@@ -672,7 +676,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       arrive(&ctl.wrdy);
       group_sync128(4);   // W^T has left the accumulator in every thread; the kept scalars are visible
       // ---- (2b) U^T = V^T Tb^T -> the same accumulator ---------------------------------------------------
-      if (gt == 0) {
+      if (gt == kUThread) {
         tc::tc_fence_after();
         wait_bar(&ctl.vb, n & 1);
         tc::tc_fence_after();
@@ -682,8 +686,6 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         for (int ks = 0; ks < 4; ++ks)
           tc::mma_ss(tbase + TM_DU + 64 * s, desc_adv(vd0, ks * 2 * RBS), desc_adv(tbd0, ks * 256), id_n64_amn, ks > 0);
         tc::mma_commit(tc::smem_u32(&ctl.barUW));
-      }
-      if (gt == 0) {
         wait_bar(&ctl.barUW, n & 1);   // V, Tb, Tw have been read: release the X buffer, fetch the next chunk's V rows
         arrive(&ctl.xfree[s]);
       }
@@ -701,7 +703,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         wait_bar(&ctl.barDq, (n - 1) & 1);
         tc::tc_fence_after();
         out_epilogue(n - 1, n);
-      } else if (gt == 0) {
+      } else if (gt == kDqThread) {
         issue_dq(0);
       }
     }
