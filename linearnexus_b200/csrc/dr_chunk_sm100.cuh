@@ -184,7 +184,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
     const float* gg = p.g ? reinterpret_cast<const float*>(p.g) + s_base : nullptr;
     const float* gbeta = p.beta + s_base;
 
-    // K,Q rows (raw bf16), g and beta of chunk m -> ring tile m % 3 / raw scalars.  The l2 normalisation is
+    // K,Q rows (raw bf16), g and beta of chunk m -> ring tile m % kRing / raw scalars.  The l2 normalisation is
     // NOT applied to the tiles: it is folded into the factors rk, rs, rq.  Warp 0 fetches the scalars (and
     // later scans them); with TMA its first lane also issues the tile copies.
     auto issue_kq = [&](int m) {
@@ -270,6 +270,7 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
     land_kq(0);
     if (warp == 0) { __syncwarp(); scan_stage(0); }
     if (gt == 64) issue_d1(0);
+    if (nchunks > 1) issue_kq(1);   // the copies run two chunks ahead of the masks (see the end of the loop body)
     uint32_t phP = 0;
     for (int n = 0; n < nchunks; ++n) {
       const int s = n & 1;
@@ -278,11 +279,9 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       const float* sG = ctl.sc[n % 4];
       const float* sBeta = sG + 128;
       group_sync128(1);  // the scalars of this chunk (scan) are visible
-      // chunk n-3 has left the consumer: ring tile, scalar and rq slots (n+1) % 4 and A_qk tile n % 3 are free;
-      // chunk n-2 has left PB and its U^T, W^T products: X buffer s is free
-      if (n >= 3) wait_bar(&ctl.empty[n % 3], ((n / 3) - 1) & 1);
+      // chunk n-2 has left PB and its U^T, W^T products: X buffer s is free.  (Chunk n-3 has left the consumer, so the
+      // A_qk tile n % 3 is free: waited for at the end of the previous iteration.)
       if (n >= 2) wait_bar(&ctl.xfree[s], ((n >> 1) - 1) & 1);
-      if (n + 1 < nchunks) issue_kq(n + 1);
       wait_bar(&ctl.barP, phP); phP ^= 1;   // D1 of this chunk was issued during the previous iteration
       tc::tc_fence_after();
       {
@@ -351,6 +350,12 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
         if (gt == 64) issue_d1(n + 1);       // completes behind PB's inverse of this chunk
         if (warp == 0) { __syncwarp(); scan_stage(n + 1); }
       }
+      // chunk n-2 has left the consumer: its ring tile and its scalar and rq slots, (n+2) % 4, are free.  The copies of
+      // chunk n+2 start here, BEFORE this group waits for chunk n+1's tile at the end of the next iteration: a tile
+      // copy (2048 box rows of 16 bytes) takes about as long as a whole iteration, and with the next copy issued only
+      // after the previous tile had landed this group's loop was the longest of the four.
+      if (n >= 2) wait_bar(&ctl.empty[(n - 2) % 3], ((n - 2) / 3) & 1);
+      if (n + 2 < nchunks) issue_kq(n + 2);
     }
   } else if (grp == 1) {
     // =========================== PB: inverse, Tb / Tw tiles ==========================================
