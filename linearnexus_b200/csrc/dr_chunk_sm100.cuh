@@ -612,23 +612,28 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
           if (next >= 0 && gt == kDqThread) issue_dq(next);
         }
         if (go) {
+          // phases kept apart by hand: 8 packed pairs, then 8 exchanges, then 8 stores
+          uint32_t mine[8], other[8];
 #pragma unroll
           for (int j4 = 0; j4 < 4; ++j4) {
             const float4 e4 = *reinterpret_cast<const float4*>(sEGm + c0 + 4 * j4);
             const float4 q4 = *reinterpret_cast<const float4*>(sRQm + c0 + 4 * j4);
-            const float ee[4] = {e4.x, e4.y, e4.z, e4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
+            mine[2 * j4] = tc::pack_bf16(e4.x * __uint_as_float(rq[4 * j4]) + q4.x * __uint_as_float(ro[4 * j4]),
+                                         e4.y * __uint_as_float(rq[4 * j4 + 1]) + q4.y * __uint_as_float(ro[4 * j4 + 1]));
+            mine[2 * j4 + 1] = tc::pack_bf16(e4.z * __uint_as_float(rq[4 * j4 + 2]) + q4.z * __uint_as_float(ro[4 * j4 + 2]),
+                                             e4.w * __uint_as_float(rq[4 * j4 + 3]) + q4.w * __uint_as_float(ro[4 * j4 + 3]));
+          }
 #pragma unroll
-            for (int e2 = 0; e2 < 2; ++e2) {
-              const int j = 4 * j4 + 2 * e2;
-              const float o0 = ee[2 * e2] * __uint_as_float(rq[j]) + qq[2 * e2] * __uint_as_float(ro[j]);
-              const float o1 = ee[2 * e2 + 1] * __uint_as_float(rq[j + 1]) + qq[2 * e2 + 1] * __uint_as_float(ro[j + 1]);
-              const uint32_t mine = tc::pack_bf16(o0, o1);               // (token j, token j+1) of column v
-              const uint32_t other = __shfl_xor_sync(0xffffffffu, mine, 1);   // the same of column v ^ 1
-              // even lane: token j, columns (v, v+1); odd lane: token j+1, columns (v-1, v)
-              const uint32_t word = odd ? __byte_perm(other, mine, 0x7632) : __byte_perm(mine, other, 0x5410);
-              if (c0 + j + (odd ? 1 : 0) < rowsm && in_bounds(p.status, (orow - go) + (int64_t)(c0 + j) * vo_tok + 1, p.n_v))
-                *reinterpret_cast<uint32_t*>(orow + (int64_t)(c0 + j) * vo_tok) = word;
-            }
+          for (int e = 0; e < 8; ++e) other[e] = __shfl_xor_sync(0xffffffffu, mine[e], 1);
+          __nv_bfloat16* op = orow + (int64_t)c0 * vo_tok;
+          const int64_t step = 2 * vo_tok;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            // even lane: token 2e, columns (v, v+1); odd lane: token 2e+1, columns (v-1, v)
+            const uint32_t word = odd ? __byte_perm(other[e], mine[e], 0x7632) : __byte_perm(mine[e], other[e], 0x5410);
+            if (c0 + 2 * e + (odd ? 1 : 0) < rowsm && in_bounds(p.status, (op - go) + 1, p.n_v))
+              *reinterpret_cast<uint32_t*>(op) = word;
+            op += step;
           }
         }
       }
