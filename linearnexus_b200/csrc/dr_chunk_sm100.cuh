@@ -13,7 +13,8 @@
 // (5) sit on the serial chain.
 //
 //   PA (warps 0-3)   state-independent, chunk n:
-//     K,Q rows land by TMA as one [K;Q] tile already in core-matrix order (3-deep ring, one chunk ahead).
+//     K,Q rows land by TMA as one [K;Q] tile already in core-matrix order (4-slot ring; the copy of chunk n+2 is
+//     issued as soon as chunk n-2 has left the consumer, before this group waits for chunk n+1's tile).
 //     The l2 norms are not applied to the tiles: they are folded into row and column factors (rk from the
 //     diagonal of D1, rq from the raw Q rows).
 //     (1) D1 = [K;Q] K^T                             128x64x128  smem x smem, issued one chunk ahead
@@ -21,12 +22,14 @@
 //   PB (warps 4-7)   chunk n, one hand-over behind PA:
 //         T = (I + diag(beta rk^2) X)^-1 in place: 8x8 blocks by substitution, three merge levels on mma.sync tf32
 //         -> Tb = T diag(beta rk), Tw = T diag(beta e^G rk^2)   bf16 tiles
-//   CB (warps 12-15) everything around the chain, as early as its inputs allow:
-//         rq_i = scale / (||q_i|| + eps)
+//         rq_i = scale / (||q_i|| + eps) of the next chunk (mma.sync on the raw Q rows)
+//   CB (warps 12-15) everything around the chain, as early as its inputs allow; its products are issued by
+//         threads of three different warps (0: W^T, 32: U^T and the V copy, 64: Dq):
 //     (2) W^T = K^T Tw^T  -> the stage accumulator (still idle) -> bf16 tile W (MN-major B operand: 16-byte stores)
 //         U^T = V^T Tb^T  -> the stage accumulator            128x64x64   smem(MN-major) x smem
-//         output of the previous chunk: O^T[v][i] = rq_i (e^{G_i} Dq[v][i] + Do[v][i]) -> staging tile (the V
-//         buffer) -> one TMA store;  then  Dq = S^T Q^T of this chunk               128x64x128
+//         output of the previous chunk: O^T[v][i] = rq_i (e^{G_i} Dq[v][i] + Do[v][i]), from the accumulators
+//         to global memory (lane pairs exchange halves: 4-byte stores, 64 contiguous bytes per token row and warp);
+//         then  Dq = S^T Q^T of this chunk                                                 128x64x128
 //   CA (warps 8-11)  the serial chain over the state:
 //         bf16 copy of S^T for the products; fp32 S^T pre-multiplied by e^{G_L}
 //     (3) V_new^T = U^T - S^T W^T  (accumulated onto U^T with negate-A)                    128x64x128
@@ -37,7 +40,10 @@
 // The [K;Q] tile is stored once as 8x8 core matrices and serves as A and B of (1), MN-major
 // A of (2), K-major B of Dq and MN-major B of (5).  Hand-overs are mbarriers (arrive counts of a whole
 // group, or tcgen05.commit for product completion); every wait is bounded: a wait that runs out sets
-// DR_DEV_TIMEOUT in the status word and the kernel finishes without further waiting.
+// DR_DEV_TIMEOUT in the status word (with the barrier and group that gave up) and the kernel finishes without
+// further waiting.  A wait site is one mbarrier.try_wait; the bounded loop, the abort flag and the record live in
+// one out-of-line function (the hand-over latency and the size of the four loop bodies are what the step time
+// follows).  A barrier whose waiter can lag its producer by more than one completion is doubled (bar2 / bar2b).
 #pragma once
 
 #include <cuda.h>
