@@ -216,7 +216,6 @@ int dr_chunk_bwd(const DrDesc* desc, const void* q, const void* k, const void* v
                  void* dk, void* dv, float* dbeta, float* dg, float* dh0, void* workspace,
                  size_t workspace_bytes, int32_t* status_dev, void* stream);
 
-/* Size of the scratch array built into the library for dr_chunk_bwd_static: 32 MiB per GPU. */
 /*
  * dr_chunk_bwd over a PACKED batch (the tensors of dr_chunk_fwd_varlen; d_o, dq, dk, dv packed like their
  * primal tensors; dbeta [total_T, H], dg like g, both float32; d_hT, dh0 float32 [n_seqs, H, K, V] or null).
@@ -228,6 +227,7 @@ int dr_chunk_bwd_varlen(const DrDesc* desc, const void* q, const void* k, const 
                         const void* d_o, const float* d_hT, void* dq, void* dk, void* dv, float* dbeta, float* dg,
                         float* dh0, void* workspace, size_t workspace_bytes, int32_t* status_dev, void* stream);
 
+/* Size of the scratch array built into the library for dr_chunk_bwd_static: 32 MiB per GPU. */
 #define DR_STATIC_SCRATCH_BYTES (32u << 20)
 
 /*
