@@ -453,7 +453,6 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       if (n >= 1) {
         wait_bar(&ctl.bar2s, (n - 1) & 1);   // the state update of the previous chunk is complete, and with it
         wait_bar(&ctl.barDq, (n - 1) & 1);   // every earlier product of the chain; Dq has read the bf16 state
-        arrive(&ctl.empty[(n - 1) % 3]);     // chunk n-1 has left the consumer: its K,Q tile, A_qk tile and scalars are free
       }
       wait_bar(&ctl.full[n % 3], (n / 3) & 1);
       tc::tc_fence_after();
@@ -482,6 +481,13 @@ __global__ void __launch_bounds__(kThreads, 1) chunk_sm100_kernel(const __grid_c
       }
       tc::tc_fence_before();
       arrive(&ctl.sbrdy);        // CB's elected thread issues Dq from the bf16 copy
+      if (n >= 1) {
+        // Chunk n-1 has left the consumer: its K,Q tile, A_qk tile and scalars are free.  Its last product, Do, was issued
+        // behind the state update and reads the A_qk tile: it has its own barrier, and by now (a state pass later) the
+        // wait costs nothing, whereas at the top of the iteration it would sit on the chain.
+        wait_bar(((n - 1) & 1) ? &ctl.bar2b : &ctl.bar2, ((n - 1) >> 1) & 1);
+        arrive(&ctl.empty[(n - 1) % 3]);
+      }
       group_sync128(3);
       // ---- (3) V_new^T = U^T - S^T W^T --------------------------------------------------------------------
       if (gt == 0) {
