@@ -29,6 +29,13 @@ int dr_debug_umma_selftest(const void* a, const void* b, float* d_out, int kd, i
 int dr_debug_wait_timeout(int32_t* status_dev, uint32_t attempts, void* stream);
 
 /*
+ * The same through the wait routine of the tcgen05 kernels with its full bound (about one second): DR_DEV_TIMEOUT plus,
+ * in bits 8..15 of the word (DR_DEV_SITE), the barrier number (0..63) and warp group (0..3) given here, as a kernel
+ * would record where its first wait gave up.
+ */
+int dr_debug_wait_site(int32_t* status_dev, uint32_t barrier_number, uint32_t group, void* stream);
+
+/*
  * The index checks of the debug build.  linearnexus_b200/libdeltarule_sm100_bounds.so is this library compiled with
  * -DDR_BOUNDS_CHECK: the kernels that index global memory by hand (token recurrences and scans, the fp32 chunk kernel,
  * the plain loads and stores of the fused tcgen05 forward) compare every index with the size of the caller's array

@@ -31,12 +31,21 @@ DR_PATH_AUTO, DR_PATH_FP32, DR_PATH_TCGEN05, DR_PATH_SPLIT = 0, 1, 2, 3
 # bits of the device status word (DR_DEV_* in include/deltarule_sm100.h)
 DEVICE_STATUS_BITS = {1: "a bounded wait on an mbarrier ran out", 2: "an index check failed"}
 
+
+def device_status_site(word: int):
+    """(barrier number, warp group) of the first wait that gave up in a tcgen05 kernel, from bits 8..15 of the device
+    status word (DR_DEV_SITE in include/deltarule_sm100.h); None when the word carries no timeout."""
+    if not word & 1:
+        return None
+    site = (word >> 8) & 0xFF
+    return site & 0x3F, site >> 6
+
 EXPORTS = ["dr_version", "dr_strerror", "dr_last_cuda_error", "dr_launch_count", "dr_last_path",
            "dr_workspace_bytes", "dr_chunk_fwd", "dr_recurrent_fwd", "dr_step", "dr_chunk_bwd",
            "dr_debug_umma_selftest", "dr_chunk_bwd_static", "dr_chunk_fwd_saving", "dr_chunk_bwd_saved",
            "dr_short_conv_silu", "dr_gate_activations", "dr_gated_rmsnorm", "dr_check_status",
            "dr_last_device_status", "dr_debug_wait_timeout", "dr_chunk_fwd_varlen", "dr_dplr_recurrent",
-           "dr_rwkv6_recurrent", "dr_ssd_scan", "dr_debug_bounds_checked", "dr_debug_bounds_probe", "dr_chunk_bwd_varlen"]
+           "dr_rwkv6_recurrent", "dr_ssd_scan", "dr_debug_bounds_checked", "dr_debug_bounds_probe", "dr_chunk_bwd_varlen", "dr_debug_wait_site"]
 
 
 class DrDesc(ctypes.Structure):
@@ -158,6 +167,8 @@ def load() -> ctypes.CDLL:
         lib.dr_last_device_status.restype = ctypes.c_int
         lib.dr_debug_wait_timeout.restype = ctypes.c_int
         lib.dr_debug_wait_timeout.argtypes = [ip, ctypes.c_uint32, vp]
+        lib.dr_debug_wait_site.restype = ctypes.c_int
+        lib.dr_debug_wait_site.argtypes = [ip, ctypes.c_uint32, ctypes.c_uint32, vp]
         lib.dr_chunk_bwd.restype = ctypes.c_int
         lib.dr_chunk_bwd.argtypes = [dp, vp, vp, vp, vp, fp, fp, vp, fp, vp, vp, vp, fp, fp, fp, vp,
                                      ctypes.c_size_t, ip, vp]
@@ -201,7 +212,9 @@ def check(status: int, where: str) -> None:
             text += f" (cudaError {lib.dr_last_cuda_error()})"
         if status == -10:
             bits = lib.dr_last_device_status()
-            text += " (" + ", ".join(n for b, n in DEVICE_STATUS_BITS.items() if bits & b) + f"; status word 0x{bits & 0xffffffff:x})"
+            text += " (" + ", ".join(n for b, n in DEVICE_STATUS_BITS.items() if bits & b) + f"; status word 0x{bits & 0xffffffff:x}"
+            site = device_status_site(bits)
+            text += f", first at barrier {site[0]} of warp group {site[1]})" if site else ")"
         raise DeltaRuleError(status, text, where)
 
 

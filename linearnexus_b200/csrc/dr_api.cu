@@ -315,6 +315,15 @@ int dr_debug_wait_timeout(int32_t* status_dev, uint32_t attempts, void* stream) 
   return check_cuda(cudaGetLastError());
 }
 
+int dr_debug_wait_site(int32_t* status_dev, uint32_t barrier_number, uint32_t group, void* stream) {
+  if (!status_dev) return DR_ERR_NULL;
+  if (barrier_number > 63 || group > 3) return DR_ERR_SHAPE;
+  tl_path = "wait_site";
+  g_launches.fetch_add(1);
+  dr::sm100::wait_site_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(status_dev, barrier_number, group);
+  return check_cuda(cudaGetLastError());
+}
+
 int dr_debug_umma_selftest(const void* a, const void* b, float* d_out, int kd, int n, int a_in_tmem,
                             int b_mn_major, int32_t* status_dev, void* stream) {
   if (!a || !b || !d_out) return DR_ERR_NULL;

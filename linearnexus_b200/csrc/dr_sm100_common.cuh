@@ -42,6 +42,21 @@ __device__ __noinline__ void wait_more(uint32_t bar, uint32_t parity, int32_t* s
   atomicOr(status, DR_DEV_TIMEOUT);
 }
 
+// Test kernel of the record above: one thread waits, with this very routine and its full bound (about a second of SM
+// clock), on an mbarrier that nothing arrives on.  The status word gets DR_DEV_TIMEOUT and the site given here; a second
+// wait of the same CTA returns at once (abort flag) and leaves the record alone.  The kernel returns normally.
+__global__ void wait_site_kernel(int32_t* status, uint32_t barrier_number, uint32_t grp) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    tc::mbar_init(tc::smem_u32(&bar), 1);
+    tc::fence_mbar_init();
+    if (!tc::mbar_try(tc::smem_u32(&bar), 0)) wait_more(tc::smem_u32(&bar), 0, status, &abort_flag, barrier_number * 8u, grp);
+    if (!tc::mbar_try(tc::smem_u32(&bar), 0)) wait_more(tc::smem_u32(&bar), 0, status, &abort_flag, 0u, 0u);
+  }
+}
+
 __device__ __forceinline__ uint32_t to_tf32(float x) {
   uint32_t r;
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));

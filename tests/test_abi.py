@@ -62,6 +62,8 @@ def test_validation_status_codes():
     assert lib.dr_check_status(None, None) == -1            # the status word is required
     assert lib.dr_debug_wait_timeout(None, 16, None) == -1
     assert lib.dr_debug_wait_timeout(16, 0, None) == -2     # attempts out of range, refused before any launch
+    assert lib.dr_debug_wait_site(None, 1, 1, None) == -1
+    assert lib.dr_debug_wait_site(16, 64, 0, None) == -2 and lib.dr_debug_wait_site(16, 0, 4, None) == -2
 
 
 def test_device_status_maps_to_an_exception():
@@ -69,6 +71,14 @@ def test_device_status_maps_to_an_exception():
     with pytest.raises(_lib.DeltaRuleError) as ei:
         _lib.check(-10, "dr_check_status")
     assert ei.value.status == -10 and "device-side" in str(ei.value)
+
+
+def test_status_word_names_where_a_wait_gave_up():
+    """Bits 8..15 of the status word: barrier number (6 bits) and warp group (2 bits) of the first wait that ran out."""
+    assert _lib.device_status_site(0) is None
+    assert _lib.device_status_site(2) is None                      # an index check alone carries no site
+    assert _lib.device_status_site(0x9701) == (23, 2)              # barrier 23 of the control block, third group
+    assert _lib.device_status_site(0x0001 | (63 << 8) | (3 << 14)) == (63, 3)
 
 
 def test_two_kernel_forward_without_workspace_is_an_error_not_a_downgrade():

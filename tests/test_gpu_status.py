@@ -40,6 +40,26 @@ def test_wait_that_runs_out_sets_status_and_host_raises():
     assert ((hT.double().cpu() - rS).abs().max() / rS.abs().max()).item() <= 2e-2
 
 
+def test_the_status_word_names_the_wait_that_gave_up():
+    """The wait routine of the tcgen05 kernels, run to the end of its bound (about a second) on an mbarrier that
+    nothing arrives on: DR_DEV_TIMEOUT plus the barrier number and warp group of that wait in bits 8..15; a second
+    wait of the same CTA returns at once and leaves the record alone; the context stays usable."""
+    lib = _lib.load()
+    dev = torch.device("cuda", 0)
+    ops.check_device_status()
+    word = ops._status(dev)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.dr_debug_wait_site(ctypes.c_void_p(word.data_ptr()), 23, 2, stream) == 0
+    with pytest.raises(_lib.DeltaRuleError) as ei:
+        ops.check_device_status()
+    bits = lib.dr_last_device_status()
+    assert bits & 1 and _lib.device_status_site(bits) == (23, 2)
+    assert "barrier 23 of warp group 2" in str(ei.value)
+    ops.check_device_status()                       # cleared
+    x = torch.arange(8, device=dev).sum().item()    # the context is intact
+    assert x == 28
+
+
 def test_every_op_family_passes_the_status_word_and_leaves_it_clean():
     """Forward (fused, two-kernel, fp32), decode (streamed and per-unit kernel) and training pair all run with a
     live status word; none of them reports anything on healthy inputs."""
